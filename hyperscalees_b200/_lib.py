@@ -1,0 +1,102 @@
+"""ctypes binding of libhses_b200.so (the C ABI declared in include/hses.h).
+
+There is no fallback: if the shared object is missing or cannot be loaded the
+import of any compute entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhses_b200.so")
+
+c_f32p = C.POINTER(C.c_float)
+c_i32p = C.POINTER(C.c_int32)
+
+# every symbol include/hses.h declares, in declaration order
+EXPORTS = [
+    "hses_last_error", "hses_version", "hses_ctx_create", "hses_ctx_destroy",
+    "hses_ctx_calibration_info", "hses_noise_seed", "hses_normal_fill", "hses_lora_factors",
+    "hses_dense_noise", "hses_poisson_encode", "hses_lif_scan",
+    "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
+    "hses_member_mean", "hses_convert_fitnesses", "hses_es_update_workspace_bytes",
+    "hses_es_update", "hses_es_update_dense", "hses_solver_step",
+]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("t_steps", C.c_int32), ("n_pop", C.c_int64), ("bm", C.c_int32),
+        ("k", C.c_int32), ("x_row_stride", C.c_int64), ("param", C.c_void_p), ("a", C.c_int32),
+        ("param_row_stride", C.c_int64), ("sigma", C.c_float), ("rank", C.c_int32),
+        ("key", C.c_uint64), ("epoch", C.c_int32), ("first_thread", C.c_int32),
+        ("noise_reuse", C.c_int32), ("perturb", C.c_int32), ("lif", C.c_int32),
+        ("tau_m", C.c_float), ("v_th", C.c_float), ("reset_mode", C.c_int32), ("out_scale", C.c_float), ("out", C.c_void_p),
+        ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class SolverDesc(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("lr", C.c_float), ("beta1", C.c_float),
+                ("beta2", C.c_float), ("eps", C.c_float), ("weight_decay", C.c_float)]
+
+
+class HsesError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"hses status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m hyperscalees_b200._build` "
+            "(there is no CPU or PyTorch fallback for the CUDA path)")
+    L = C.CDLL(LIB_PATH)
+    vp, i32, i64, u64, f32, sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_size_t
+    L.hses_last_error.restype = C.c_char_p
+    L.hses_last_error.argtypes = []
+    L.hses_version.restype = C.c_int
+    L.hses_ctx_create.argtypes = [C.c_int, C.POINTER(vp)]
+    L.hses_ctx_destroy.argtypes = [vp]
+    L.hses_ctx_calibration_info.argtypes = [vp, C.POINTER(u64), C.POINTER(u64)]
+    L.hses_noise_seed.restype = u64
+    L.hses_noise_seed.argtypes = [u64, i32, i32]
+    L.hses_normal_fill.argtypes = [vp, vp, u64, vp, sz]
+    L.hses_lora_factors.argtypes = [vp, vp, u64, i32, i32, vp, i32, i64, i32, i32, i32, f32, i32, vp, vp]
+    L.hses_dense_noise.argtypes = [vp, vp, u64, i32, i32, vp, i32, i64, i32, i32, f32, vp]
+    L.hses_poisson_encode.argtypes = [vp, vp, vp, i64, i32, i64, i32, C.POINTER(C.c_uint32), vp]
+    L.hses_lif_scan.argtypes = [vp, vp, vp, i32, i64, i32, i64, vp, f32, f32, i32, vp]
+    L.hses_perturbed_linear_workspace_bytes.restype = sz
+    L.hses_perturbed_linear_workspace_bytes.argtypes = [C.POINTER(LinearArgs)]
+    L.hses_perturbed_linear.argtypes = [vp, vp, C.POINTER(LinearArgs)]
+    L.hses_time_mean.argtypes = [vp, vp, vp, i32, i64, i32, i64, vp, i64]
+    L.hses_fitness.argtypes = [vp, vp, vp, i64, i32, vp, i32, vp]
+    L.hses_member_mean.argtypes = [vp, vp, vp, i64, i32, vp]
+    L.hses_convert_fitnesses.argtypes = [vp, vp, vp, i64, i32, vp, vp]
+    L.hses_es_update_workspace_bytes.restype = sz
+    L.hses_es_update_workspace_bytes.argtypes = [i32, i32, i32, i64]
+    L.hses_es_update.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp, vp, sz]
+    L.hses_es_update_dense.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, f32, vp, vp]
+    L.hses_solver_step.argtypes = [vp, vp, C.POINTER(SolverDesc), i32, f32, vp, vp, vp, vp, i64]
+    for name in EXPORTS:
+        fn = getattr(L, name)
+        if fn.restype is C.c_int and name not in ("hses_version",):
+            fn.restype = C.c_int
+    _lib = L
+    return L
+
+
+def check(status: int):
+    if status != 0:
+        msg = load().hses_last_error()
+        raise HsesError(status, msg.decode() if msg else "")

@@ -1,0 +1,86 @@
+// Shared declarations of the library's translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/hses.h"
+#include "rng.cuh"
+
+namespace hses {
+
+void set_error(const std::string& msg);
+
+struct DeviceTables {
+    // libm calibration
+    double2* log_tab = nullptr;
+    uint32_t* log_flip = nullptr;
+    uint32_t* cos_flip = nullptr;
+    uint32_t* log_delta = nullptr;
+    uint32_t* cos_delta = nullptr;
+    float log_of_zero = 0.0f;
+    uint64_t n_log_flips = 0, n_cos_flips = 0;
+    // generator jump tables: entry k advances the state by 2^k steps
+    uint64_t* jump_pow2 = nullptr;  // kJumpLevels matrices
+};
+
+constexpr int kJumpLevels = 48;
+
+}  // namespace hses
+
+struct hses_ctx {
+    int device = 0;
+    int sm_count = 0;
+    hses::DeviceTables t;
+    hses::LibmCal cal() const {
+        hses::LibmCal c;
+        c.log_tab = t.log_tab;
+        c.log_flip = t.log_flip;
+        c.cos_flip = t.cos_flip;
+        c.log_delta = t.log_delta;
+        c.cos_delta = t.cos_delta;
+        c.log_of_zero = t.log_of_zero;
+        return c;
+    }
+};
+
+#define HSES_CUDA(call)                                                                   \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess) {                                                          \
+            hses::set_error(std::string(#call) + " failed: " + cudaGetErrorString(e_));   \
+            return HSES_ERR_CUDA;                                                         \
+        }                                                                                 \
+    } while (0)
+
+#define HSES_REQUIRE(cond, msg)                                   \
+    do {                                                          \
+        if (!(cond)) {                                            \
+            hses::set_error(std::string(__func__) + ": " + (msg)); \
+            return HSES_ERR_INVALID;                              \
+        }                                                         \
+    } while (0)
+
+#define HSES_LAUNCH_CHECK()                                                                 \
+    do {                                                                                    \
+        cudaError_t e_ = cudaGetLastError();                                                \
+        if (e_ != cudaSuccess) {                                                            \
+            hses::set_error(std::string(__func__) + ": launch failed: " + cudaGetErrorString(e_)); \
+            return HSES_ERR_CUDA;                                                           \
+        }                                                                                   \
+    } while (0)
+
+namespace hses {
+// Raw factors of `pairs` antithetic pairs starting at first_pair:
+// A (pairs, a, r) and B (pairs, b, r), row-major.  When pair_weight is given
+// (device, 2 floats per pair: the fitnesses of the even and the odd member),
+// A is multiplied by (f_even - f_odd).
+int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
+                        int32_t first_pair, int64_t pairs, int rank, int a, int b,
+                        const float* pair_weight, float* A, float* B);
+}  // namespace hses
+
+static inline cudaStream_t as_stream(hses_stream s) { return reinterpret_cast<cudaStream_t>(s); }

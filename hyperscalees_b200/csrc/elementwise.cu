@@ -1,0 +1,396 @@
+// HBM-bound elementwise kernels: Poisson encode, LIF scan, fitness, z-score,
+// solver step.  All of them stream their operands once; rows are pitched.
+#include "common.cuh"
+
+namespace hses {
+
+// ---------------------------------------------------------------------------
+// Poisson encode (poisson_encode_fused_oxide.rs:36-105)
+// ---------------------------------------------------------------------------
+// The reference compares u = fl((k+1)/8388609) with p at every step, k being
+// the top 23 bits of the xorshift32 output.  fl(n/8388609) is monotone in n,
+// so "u < p" is "n < n*(p)" with n* the smallest n whose quotient reaches p.
+// n* is found once per element with exact divisions; the T steps are then
+// integer-only.
+__device__ __forceinline__ uint32_t poisson_threshold(float p) {
+    const float D = 8388609.0f;
+    float guess = __fmul_rn(p, D);
+    uint32_t c = guess >= 1.0f ? (guess < 8388609.0f ? (uint32_t)guess : 8388609u) : 1u;
+    while (c > 1u && __fdiv_rn((float)(c - 1u), D) >= p) --c;
+    while (c <= 8388608u && __fdiv_rn((float)c, D) < p) ++c;
+    return c;
+}
+
+__device__ __forceinline__ uint32_t poisson_seed(uint32_t idx, uint32_t mix) {
+    return 1000000007u * idx + mix + 0x9E3779B9u;
+}
+
+__device__ __forceinline__ uint32_t xs32(uint32_t x) {
+    x ^= x << 13;
+    x ^= x >> 17;
+    x ^= x << 5;
+    return x;
+}
+
+template <int VEC>
+__global__ void poisson_kernel(const float* __restrict__ probs, int64_t batch, int in_dim,
+                               int64_t stride, int T, uint32_t mix, float* __restrict__ out) {
+    int64_t vec_per_row = in_dim / VEC;
+    int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= batch * vec_per_row) return;
+    int64_t row = v / vec_per_row;
+    int col = (int)(v - row * vec_per_row) * VEC;
+    size_t base = (size_t)row * stride + col;
+    size_t out_step = (size_t)batch * stride;
+    float p[VEC];
+    if constexpr (VEC == 4) {
+        float4 q = *reinterpret_cast<const float4*>(probs + base);
+        p[0] = q.x; p[1] = q.y; p[2] = q.z; p[3] = q.w;
+    } else {
+        p[0] = probs[base];
+    }
+    uint32_t x[VEC], thr[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        x[i] = poisson_seed((uint32_t)(row * in_dim + col + i), mix);
+        thr[i] = poisson_threshold(p[i]);
+    }
+    for (int t = 0; t < T; ++t) {
+        float s[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            x[i] = xs32(x[i]);
+            s[i] = ((x[i] >> 9) + 1u) < thr[i] ? 1.0f : 0.0f;
+        }
+        float* dst = out + (size_t)t * out_step + base;
+        if constexpr (VEC == 4)
+            __stcs(reinterpret_cast<float4*>(dst), make_float4(s[0], s[1], s[2], s[3]));
+        else
+            dst[0] = s[0];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// LIF scan (snn.rs:53-97, lif_fused_oxide.rs:37-70)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float lif_update(float& v, float cur, float leak, float v_th, int reset) {
+    float d = __fadd_rn(-v, cur);
+    float m = __fmul_rn(d, leak);
+    float c = __fadd_rn(v, m);
+    float s = c >= v_th ? 1.0f : 0.0f;
+    v = reset == HSES_RESET_HARD ? __fmul_rn(c, __fadd_rn(-s, 1.0f)) : __fsub_rn(c, __fmul_rn(s, v_th));
+    return s;
+}
+
+template <int VEC>
+__global__ void lif_scan_kernel(const float* __restrict__ cur, int T, int64_t n, int h,
+                                int64_t stride, float* __restrict__ v_io, float leak, float v_th,
+                                int reset, float* __restrict__ spikes) {
+    int64_t vec_per_row = h / VEC;
+    int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n * vec_per_row) return;
+    int64_t row = e / vec_per_row;
+    int col = (int)(e - row * vec_per_row) * VEC;
+    size_t base = (size_t)row * stride + col;
+    size_t step = (size_t)n * stride;
+    float v[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = 0.0f;
+    if (v_io) {
+        if constexpr (VEC == 4) {
+            float4 q = *reinterpret_cast<const float4*>(v_io + base);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+            v[0] = v_io[base];
+        }
+    }
+    for (int t = 0; t < T; ++t) {
+        float c[VEC], s[VEC];
+        const float* src = cur + (size_t)t * step + base;
+        if constexpr (VEC == 4) {
+            float4 q = __ldcs(reinterpret_cast<const float4*>(src));
+            c[0] = q.x; c[1] = q.y; c[2] = q.z; c[3] = q.w;
+        } else {
+            c[0] = src[0];
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s[i] = lif_update(v[i], c[i], leak, v_th, reset);
+        float* dst = spikes + (size_t)t * step + base;
+        if constexpr (VEC == 4)
+            __stcs(reinterpret_cast<float4*>(dst), make_float4(s[0], s[1], s[2], s[3]));
+        else
+            dst[0] = s[0];
+    }
+    if (v_io) {
+        if constexpr (VEC == 4)
+            *reinterpret_cast<float4*>(v_io + base) = make_float4(v[0], v[1], v[2], v[3]);
+        else
+            v_io[base] = v[0];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// mean over time (snn.rs:278): sum in step order, then one division
+// ---------------------------------------------------------------------------
+__global__ void time_mean_kernel(const float* __restrict__ x, int T, int64_t n, int h,
+                                 int64_t stride, float* __restrict__ out, int64_t out_stride) {
+    int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n * h) return;
+    int64_t row = e / h;
+    int col = (int)(e - row * h);
+    size_t step = (size_t)n * stride;
+    float s = 0.0f;
+    for (int t = 0; t < T; ++t) s = __fadd_rn(s, x[(size_t)t * step + (size_t)row * stride + col]);
+    out[(size_t)row * out_stride + col] = __fdiv_rn(s, (float)T);
+}
+
+// ---------------------------------------------------------------------------
+// fitness (snn_mnist.rs:180-201) and per-member mean
+// ---------------------------------------------------------------------------
+__global__ void fitness_kernel(const float* __restrict__ logits, int64_t n, int classes,
+                               const int32_t* __restrict__ labels, int reward,
+                               float* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float* row = logits + (size_t)i * classes;
+    float mx = row[0];
+    int arg = 0;
+    for (int c = 1; c < classes; ++c)
+        if (row[c] > mx) { mx = row[c]; arg = c; }
+    int label = labels[i];
+    if (reward == HSES_REWARD_BINARY) {
+        out[i] = arg == label ? 1.0f : 0.0f;
+    } else {
+        float sum = 0.0f;
+        for (int c = 0; c < classes; ++c) sum = __fadd_rn(sum, expf(__fsub_rn(row[c], mx)));
+        float picked = (label >= 0 && label < classes) ? row[label] : __int_as_float(0x7fc00000);
+        out[i] = __fsub_rn(__fsub_rn(picked, mx), logf(sum));
+    }
+}
+
+__global__ void member_mean_kernel(const float* __restrict__ x, int64_t n_pop, int bm,
+                                   float* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pop) return;
+    float s = 0.0f;
+    for (int j = 0; j < bm; ++j) s = __fadd_rn(s, x[(size_t)i * bm + j]);
+    out[i] = __fdiv_rn(s, (float)bm);
+}
+
+// ---------------------------------------------------------------------------
+// z-score (noiser.rs:517-537): one block, fixed reduction order
+// ---------------------------------------------------------------------------
+constexpr int kZThreads = 1024;
+__global__ void zscore_kernel(const float* __restrict__ raw, int64_t n, int group_size,
+                              float* __restrict__ out, float* __restrict__ stats) {
+    __shared__ float s_sum[kZThreads];
+    __shared__ float s_sq[kZThreads];
+    float a = 0.0f, b = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += kZThreads) {
+        float x = raw[i];
+        a = __fadd_rn(a, x);
+        b = __fadd_rn(b, __fmul_rn(x, x));
+    }
+    s_sum[threadIdx.x] = a;
+    s_sq[threadIdx.x] = b;
+    __syncthreads();
+    for (int stride = kZThreads / 2; stride > 0; stride >>= 1) {
+        if (threadIdx.x < stride) {
+            s_sum[threadIdx.x] = __fadd_rn(s_sum[threadIdx.x], s_sum[threadIdx.x + stride]);
+            s_sq[threadIdx.x] = __fadd_rn(s_sq[threadIdx.x], s_sq[threadIdx.x + stride]);
+        }
+        __syncthreads();
+    }
+    float nf = (float)n;
+    float mean = __fdiv_rn(s_sum[0], nf);
+    float var = __fsub_rn(__fdiv_rn(s_sq[0], nf), __fmul_rn(mean, mean));
+    float sd = __fsqrt_rn(__fadd_rn(var, 1e-5f));
+    float inv = __fdiv_rn(1.0f, sd);
+    if (threadIdx.x == 0 && stats) { stats[0] = mean; stats[1] = sd; }
+    if (group_size == 0) {
+        for (int64_t i = threadIdx.x; i < n; i += kZThreads)
+            out[i] = __fmul_rn(__fadd_rn(raw[i], -mean), inv);
+    } else {
+        int64_t groups = n / group_size;
+        for (int64_t g = threadIdx.x; g < groups; g += kZThreads) {
+            float gs = 0.0f;
+            for (int j = 0; j < group_size; ++j) gs = __fadd_rn(gs, raw[g * group_size + j]);
+            float gmean = __fdiv_rn(gs, (float)group_size);
+            for (int j = 0; j < group_size; ++j)
+                out[g * group_size + j] = __fmul_rn(__fsub_rn(raw[g * group_size + j], gmean), inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// solver (noiser.rs:155-224)
+// ---------------------------------------------------------------------------
+struct SolverConsts {
+    int kind;
+    float lr, beta1, beta2, eps, wd;
+    float omb1, omb2, ibc1, ibc2, grad_scale;
+};
+__global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float* __restrict__ g,
+                              float* __restrict__ m, float* __restrict__ v, int64_t len) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= len) return;
+    float gi = c.grad_scale == 1.0f ? g[i] : __fmul_rn(g[i], c.grad_scale);
+    if (c.kind == HSES_SGD) {
+        p[i] = __fsub_rn(p[i], __fmul_rn(gi, c.lr));
+        return;
+    }
+    float mn = __fadd_rn(__fmul_rn(m[i], c.beta1), __fmul_rn(gi, c.omb1));
+    float vn = __fadd_rn(__fmul_rn(v[i], c.beta2), __fmul_rn(__fmul_rn(gi, gi), c.omb2));
+    m[i] = mn;
+    v[i] = vn;
+    float mh = __fmul_rn(mn, c.ibc1), vh = __fmul_rn(vn, c.ibc2);
+    float denom = __fadd_rn(__fsqrt_rn(vh), c.eps);
+    float term = __fmul_rn(__fdiv_rn(mh, denom), -c.lr);
+    float pi = p[i];
+    p[i] = c.wd == 0.0f ? __fadd_rn(pi, term) : __fadd_rn(__fadd_rn(pi, term), __fmul_rn(pi, c.wd));
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace hses
+
+using namespace hses;
+
+extern "C" {
+
+int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs, int64_t batch,
+                        int32_t in_dim, int64_t row_stride, int32_t T, const uint32_t seeds[4],
+                        float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(batch >= 0 && in_dim >= 1 && row_stride >= in_dim, "bad shape");
+    HSES_REQUIRE(T >= 1, "T must be >= 1");
+    HSES_REQUIRE(seeds != nullptr, "seeds is NULL");
+    HSES_REQUIRE((double)batch * in_dim < 4294967296.0,
+                 "batch*in_dim must fit the 32-bit element index of the reference stream");
+    if (batch == 0) return HSES_OK;
+    HSES_REQUIRE(probs != nullptr && out != nullptr, "NULL pointer");
+    uint32_t mix = seeds[0] ^ seeds[1] ^ seeds[2] ^ seeds[3];
+    bool vec = (in_dim % 4 == 0) && (row_stride % 4 == 0) && aligned16(probs) && aligned16(out);
+    if (vec) {
+        int64_t total = batch * (in_dim / 4);
+        poisson_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+            probs, batch, in_dim, row_stride, T, mix, out);
+    } else {
+        int64_t total = batch * in_dim;
+        poisson_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+            probs, batch, in_dim, row_stride, T, mix, out);
+    }
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_lif_scan(hses_ctx* ctx, hses_stream stream, const float* cur, int32_t T, int64_t n,
+                  int32_t h, int64_t row_stride, float* v, float tau_m, float v_th,
+                  int32_t reset_mode, float* spikes) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(T >= 1 && n >= 0 && h >= 1 && row_stride >= h, "bad shape");
+    HSES_REQUIRE(reset_mode == HSES_RESET_HARD || reset_mode == HSES_RESET_SUBTRACT, "bad reset mode");
+    HSES_REQUIRE(tau_m != 0.0f, "tau_m must be non-zero");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(cur != nullptr && spikes != nullptr, "NULL pointer");
+    float leak = 1.0f / tau_m;
+    bool vec = (h % 4 == 0) && (row_stride % 4 == 0) && aligned16(cur) && aligned16(spikes) &&
+               (v == nullptr || aligned16(v));
+    if (vec) {
+        int64_t total = n * (h / 4);
+        lif_scan_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+            cur, T, n, h, row_stride, v, leak, v_th, reset_mode, spikes);
+    } else {
+        int64_t total = n * h;
+        lif_scan_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+            cur, T, n, h, row_stride, v, leak, v_th, reset_mode, spikes);
+    }
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_time_mean(hses_ctx* ctx, hses_stream stream, const float* x, int32_t T, int64_t n,
+                   int32_t h, int64_t row_stride, float* out, int64_t out_row_stride) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(T >= 1 && n >= 0 && h >= 1 && row_stride >= h && out_row_stride >= h, "bad shape");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && out != nullptr, "NULL pointer");
+    int64_t total = n * h;
+    time_mean_kernel<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+        x, T, n, h, row_stride, out, out_row_stride);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_fitness(hses_ctx* ctx, hses_stream stream, const float* logits, int64_t n, int32_t classes,
+                 const int32_t* labels, int32_t reward, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 0 && classes >= 1, "bad shape");
+    HSES_REQUIRE(reward == HSES_REWARD_LOGLIK || reward == HSES_REWARD_BINARY, "bad reward");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(logits != nullptr && labels != nullptr && out != nullptr, "NULL pointer");
+    fitness_kernel<<<(unsigned)((n + 127) / 128), 128, 0, as_stream(stream)>>>(logits, n, classes,
+                                                                             labels, reward, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_member_mean(hses_ctx* ctx, hses_stream stream, const float* per_sample, int64_t n_pop,
+                     int32_t bm, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n_pop >= 0 && bm >= 1, "bad shape");
+    if (n_pop == 0) return HSES_OK;
+    HSES_REQUIRE(per_sample != nullptr && out != nullptr, "NULL pointer");
+    member_mean_kernel<<<(unsigned)((n_pop + 127) / 128), 128, 0, as_stream(stream)>>>(per_sample,
+                                                                                     n_pop, bm, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_convert_fitnesses(hses_ctx* ctx, hses_stream stream, const float* raw, int64_t n,
+                           int32_t group_size, float* out, float* stats) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 1, "n must be >= 1");
+    HSES_REQUIRE(group_size >= 0, "group_size must be >= 0");
+    HSES_REQUIRE(group_size == 0 || n % group_size == 0, "n must be a multiple of group_size");
+    HSES_REQUIRE(raw != nullptr && out != nullptr, "NULL pointer");
+    zscore_kernel<<<1, kZThreads, 0, as_stream(stream)>>>(raw, n, group_size, out, stats);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solver, int32_t step,
+                     float grad_scale, float* param, const float* grad, float* m, float* v,
+                     int64_t len) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(solver != nullptr, "solver is NULL");
+    HSES_REQUIRE(solver->kind == HSES_SGD || solver->kind == HSES_ADAM || solver->kind == HSES_ADAMW,
+                 "unknown solver kind");
+    HSES_REQUIRE(len >= 0, "len must be >= 0");
+    if (len == 0) return HSES_OK;
+    HSES_REQUIRE(param != nullptr && grad != nullptr, "NULL pointer");
+    SolverConsts c{};
+    c.kind = solver->kind;
+    c.lr = solver->lr;
+    c.grad_scale = grad_scale;
+    if (solver->kind != HSES_SGD) {
+        HSES_REQUIRE(m != nullptr && v != nullptr, "Adam needs moment buffers");
+        HSES_REQUIRE(step >= 1, "step is the counter after the increment (>= 1)");
+        float t = (float)step;
+        float bc1 = 1.0f - powf(solver->beta1, t);
+        float bc2 = 1.0f - powf(solver->beta2, t);
+        c.beta1 = solver->beta1;
+        c.beta2 = solver->beta2;
+        c.eps = solver->eps;
+        c.wd = solver->kind == HSES_ADAMW ? solver->weight_decay : 0.0f;
+        c.omb1 = 1.0f - solver->beta1;
+        c.omb2 = 1.0f - solver->beta2;
+        c.ibc1 = 1.0f / bc1;
+        c.ibc2 = 1.0f / bc2;
+    }
+    solver_kernel<<<(unsigned)((len + 255) / 256), 256, 0, as_stream(stream)>>>(c, param, grad, m, v, len);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,269 @@
+// Perturbed linear layer y = x·Wᵀ + (x·B_i)·A_iᵀ for a whole population
+// (do_mm, hyperscalees-noiser/src/eggroll.rs:419-446) with an optional fused
+// LIF step (lif_step, hyperscalees-models/src/snn.rs:53-65).
+//
+// This file holds the dispatcher and the general fp32 SIMT path, which takes
+// any shape and pitch.  The tensor-core path for tile-aligned shapes lives in
+// linear_tc.cu.
+#include "common.cuh"
+#include "linear.cuh"
+
+namespace hses {
+
+// ---------------------------------------------------------------------------
+// SIMT path, three launches:
+//   1. raw factors of every antithetic pair into scratch (pair-folded: the
+//      two members of a pair share one draw, eggroll.rs:60-65);
+//   2. t = x·B_pair, (rows, r);
+//   3. tiled fp32 GEMM x·Wᵀ whose epilogue adds t·(±sigma/sqrt(r)·A_pair)ᵀ
+//      and applies the LIF step.
+// ---------------------------------------------------------------------------
+
+// scratch layout: A (pairs, a, r) | B (pairs, b, r) | t (rows, r)
+struct SimtScratch {
+    float* A;
+    float* B;
+    float* t;
+    size_t bytes;
+};
+static SimtScratch simt_scratch(const hses_linear_args& g, void* base) {
+    int64_t first_pair = g.first_thread / 2;
+    int64_t last_pair = (g.first_thread + g.n_pop - 1) / 2;
+    size_t pairs = (size_t)(last_pair - first_pair + 1);
+    size_t rows = (size_t)g.t_steps * g.n_pop * g.bm;
+    size_t na = pairs * g.a * g.rank, nb = pairs * g.k * g.rank, nt = rows * g.rank;
+    auto up = [](size_t v) { return (v + 63) / 64 * 64; };
+    SimtScratch s;
+    s.A = reinterpret_cast<float*>(base);
+    s.B = s.A + up(na);
+    s.t = s.B + up(nb);
+    s.bytes = (up(na) + up(nb) + up(nt)) * sizeof(float);
+    return s;
+}
+
+// t[R, q] = sum_k x[R, k] * B_pair(R)[k, q]; one warp per row, lanes over k.
+__global__ void lowrank_project_kernel(const float* __restrict__ x, int64_t rows, int bm,
+                                       int64_t n_pop, int k, int64_t x_stride, int rank,
+                                       int32_t first_thread, int32_t first_pair,
+                                       const float* __restrict__ B, float* __restrict__ t) {
+    int64_t R = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    int lane = threadIdx.x & 31;
+    if (R >= rows) return;
+    int64_t member = (R / bm) % n_pop;
+    int64_t pair = (first_thread + member) / 2 - first_pair;
+    const float* xr = x + (size_t)R * x_stride;
+    const float* Bp = B + (size_t)pair * k * rank;
+    for (int q0 = 0; q0 < rank; q0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+        for (int kk = lane; kk < k; kk += 32) {
+            float xv = xr[kk];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (q0 + j < rank) acc[j] = fmaf(xv, Bp[(size_t)kk * rank + q0 + j], acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float v = acc[j];
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            if (lane == 0 && q0 + j < rank) t[(size_t)R * rank + q0 + j] = v;
+        }
+    }
+}
+
+constexpr int TM = 128, TN = 128, TK = 16, TT = 256;  // tile sizes, threads
+
+struct EpilogueArgs {
+    int perturb, lif, reset;
+    float base_sigma, leak, v_th, out_scale;
+    int rank, bm;
+    int64_t n_pop;
+    int32_t first_thread, first_pair;
+    const float* A;  // (pairs, a, r)
+    const float* t;  // (rows, r)
+    float* out;
+    int64_t out_stride;
+    float* pot;
+};
+
+__global__ void __launch_bounds__(TT)
+linear_simt_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t x_stride,
+                   const float* __restrict__ w, int a, int64_t w_stride, EpilogueArgs ep) {
+    __shared__ __align__(16) float sx[TK][TM + 4];
+    __shared__ __align__(16) float sw[TK][TN + 4];
+    int64_t row0 = (int64_t)blockIdx.y * TM;
+    int col0 = blockIdx.x * TN;
+    int tid = threadIdx.x;
+    // a thread owns rows {tr..tr+3, 64+tr..64+tr+3} and the same pattern of
+    // columns, so its shared-memory reads are two conflict-free float4 loads
+    int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < k; k0 += TK) {
+        // each thread loads 8 elements of each tile: element e -> (row e/16, k e%16)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int idx = tid + e * TT;
+            int r = idx / TK, kk = idx % TK;
+            int64_t gr = row0 + r;
+            sx[kk][r] = (gr < rows && k0 + kk < k) ? x[(size_t)gr * x_stride + k0 + kk] : 0.0f;
+            int gc = col0 + r;
+            sw[kk][r] = (gc < a && k0 + kk < k) ? w[(size_t)gc * w_stride + k0 + kk] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            float xa[8], wb[8];
+            *reinterpret_cast<float4*>(&xa[0]) = *reinterpret_cast<const float4*>(&sx[kk][tr]);
+            *reinterpret_cast<float4*>(&xa[4]) = *reinterpret_cast<const float4*>(&sx[kk][64 + tr]);
+            *reinterpret_cast<float4*>(&wb[0]) = *reinterpret_cast<const float4*>(&sw[kk][tc]);
+            *reinterpret_cast<float4*>(&wb[4]) = *reinterpret_cast<const float4*>(&sw[kk][64 + tc]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int64_t R = row0 + (i < 4 ? tr + i : 64 + tr + i - 4);
+        if (R >= rows) continue;
+        const float* Ap = nullptr;
+        const float* tr_ = nullptr;
+        float scale = 0.0f;
+        if (ep.perturb) {
+            int64_t member = (R / ep.bm) % ep.n_pop;
+            int32_t thread_id = ep.first_thread + (int32_t)member;
+            Ap = ep.A + (size_t)(thread_id / 2 - ep.first_pair) * a * ep.rank;
+            tr_ = ep.t + (size_t)R * ep.rank;
+            scale = (thread_id % 2 == 0) ? ep.base_sigma : -ep.base_sigma;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int n = col0 + (j < 4 ? tc + j : 64 + tc + j - 4);
+            if (n >= a) continue;
+            float y = acc[i][j];
+            if (ep.perturb) {
+                float u = 0.0f;
+                for (int q = 0; q < ep.rank; ++q)
+                    u = fmaf(tr_[q], __fmul_rn(Ap[(size_t)n * ep.rank + q], scale), u);
+                y = __fadd_rn(y, u);
+            }
+            size_t o = (size_t)R * ep.out_stride + n;
+            if (ep.lif) {
+                // lif_step from v = 0: charged = 0 + ((-0) + y) * leak
+                float c = __fmul_rn(y, ep.leak);
+                if (ep.pot) ep.pot[o] = c;
+                ep.out[o] = c >= ep.v_th ? 1.0f : 0.0f;
+            } else {
+                ep.out[o] = __fmul_rn(y, ep.out_scale);
+            }
+        }
+    }
+}
+
+static int check_args(const hses_linear_args* g) {
+    HSES_REQUIRE(g != nullptr, "args is NULL");
+    HSES_REQUIRE(g->t_steps >= 1 && g->n_pop >= 1 && g->bm >= 1 && g->k >= 1 && g->a >= 1, "bad shape");
+    HSES_REQUIRE(g->x_row_stride >= g->k && g->param_row_stride >= g->k && g->out_row_stride >= g->a,
+                 "row stride smaller than the row");
+    HSES_REQUIRE((double)g->t_steps * (double)g->n_pop * g->bm < 2147483648.0, "too many rows");
+    HSES_REQUIRE(g->x != nullptr && g->param != nullptr && g->out != nullptr, "NULL pointer");
+    if (g->perturb) {
+        HSES_REQUIRE(g->rank >= 1 && g->rank <= 1024, "rank out of range");
+        HSES_REQUIRE(g->first_thread >= 0 && g->noise_reuse >= 0, "negative thread id or noise_reuse");
+        HSES_REQUIRE((int64_t)g->first_thread + g->n_pop < (1ll << 31), "thread id overflow");
+    }
+    if (g->lif) {
+        HSES_REQUIRE(g->tau_m != 0.0f, "tau_m must be non-zero");
+        HSES_REQUIRE(g->reset_mode == HSES_RESET_HARD || g->reset_mode == HSES_RESET_SUBTRACT,
+                     "bad reset mode");
+    }
+    HSES_REQUIRE(g->algo >= HSES_ALGO_AUTO && g->algo <= HSES_ALGO_TENSOR, "unknown algo");
+    return HSES_OK;
+}
+
+static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
+    int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
+    EpilogueArgs ep{};
+    ep.perturb = g.perturb;
+    ep.lif = g.lif;
+    ep.reset = g.reset_mode;
+    ep.rank = g.rank;
+    ep.bm = g.bm;
+    ep.n_pop = g.n_pop;
+    ep.first_thread = g.first_thread;
+    ep.first_pair = g.first_thread / 2;
+    ep.out = g.out;
+    ep.out_stride = g.out_row_stride;
+    ep.pot = g.lif ? g.potentials : nullptr;
+    ep.leak = g.lif ? 1.0f / g.tau_m : 0.0f;
+    ep.v_th = g.v_th;
+    ep.out_scale = g.out_scale;
+    if (g.perturb) {
+        SimtScratch s = simt_scratch(g, g.workspace);
+        HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= s.bytes,
+                     "workspace too small; see hses_perturbed_linear_workspace_bytes");
+        ep.base_sigma = g.sigma / sqrtf((float)g.rank);
+        ep.A = s.A;
+        ep.t = s.t;
+        int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - ep.first_pair + 1;
+        int rc = launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse),
+                                     ep.first_pair, pairs, g.rank, g.a, g.k, nullptr, s.A, s.B);
+        if (rc != HSES_OK) return rc;
+        lowrank_project_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+            g.x, rows, g.bm, g.n_pop, g.k, g.x_row_stride, g.rank, g.first_thread, ep.first_pair,
+            s.B, s.t);
+        HSES_LAUNCH_CHECK();
+    }
+    int64_t row_tiles = (rows + TM - 1) / TM;
+    HSES_REQUIRE(row_tiles <= 65535ll * 32768ll, "too many rows");
+    HSES_REQUIRE(row_tiles <= 65535, "too many rows for the SIMT path (rows/128 must be <= 65535)");
+    dim3 grid((unsigned)((g.a + TN - 1) / TN), (unsigned)row_tiles);
+    linear_simt_kernel<<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a,
+                                            g.param_row_stride, ep);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // namespace hses
+
+using namespace hses;
+
+extern "C" {
+
+size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
+    if (g == nullptr || g->t_steps < 1 || g->n_pop < 1 || g->bm < 1 || g->k < 1 || g->a < 1) return 0;
+    if (!g->perturb) return 0;
+    size_t tc = 0;
+    if (g->algo != HSES_ALGO_SIMT && tensor_path_supports(*g)) {
+        tc = tensor_path_workspace_bytes(*g);
+        if (g->algo == HSES_ALGO_TENSOR) return tc;
+    }
+    size_t simt = simt_scratch(*g, nullptr).bytes;
+    if (g->algo == HSES_ALGO_AUTO && tensor_path_supports(*g)) return tc;
+    return simt;
+}
+
+int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_args* g) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    int rc = check_args(g);
+    if (rc != HSES_OK) return rc;
+    bool tc_ok = tensor_path_supports(*g);
+    if (g->algo == HSES_ALGO_TENSOR && !tc_ok) {
+        set_error("hses_perturbed_linear: the tensor-core path does not cover this shape");
+        return HSES_ERR_UNSUPPORTED;
+    }
+    if (g->algo == HSES_ALGO_TENSOR || (g->algo == HSES_ALGO_AUTO && tc_ok))
+        return run_tensor_path(ctx, as_stream(stream), *g);
+    return run_simt(ctx, as_stream(stream), *g);
+}
+
+}  // extern "C"

@@ -1,0 +1,214 @@
+// Materialising kernels for the noise stream: normal_fill, lora_factors,
+// dense_noise and the dense-leaf update.  The fused forward/update kernels
+// regenerate the same values in registers; these entry points exist for
+// callers that want the tensors (parity checks, the trainer's cached-noise
+// path) and for the small PARAM-class leaves.
+#include "common.cuh"
+
+namespace hses {
+
+// Normals are produced in chunks of kChunk per thread; a thread reaches its
+// chunk with a jump of 2*kChunk*chunk_index generator steps.
+constexpr int kChunk = 16;
+
+__global__ void normal_fill_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t seed,
+                                   float* __restrict__ out, size_t n) {
+    size_t chunk = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t begin = chunk * kChunk;
+    if (begin >= n) return;
+    uint64_t s = jump_by(pow2, seed | 1ull, 2ull * begin);
+    size_t end = begin + kChunk < n ? begin + kChunk : n;
+    for (size_t i = begin; i < end; ++i) out[i] = next_normal(s, cal);
+}
+
+// One thread per (member, row of the (a+b, r) block).  Rows [0,b) are B, rows
+// [b,a+b) are A (eggroll.rs:98-101).
+__global__ void lora_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
+                                    int32_t true_epoch, const int32_t* __restrict__ thread_ids,
+                                    int32_t first_thread, int64_t n_members, int rank, int a, int b,
+                                    float base_sigma, int layout, float* __restrict__ A,
+                                    float* __restrict__ B) {
+    int64_t member = blockIdx.x;
+    int row = blockIdx.y * blockDim.x + threadIdx.x;
+    if (member >= n_members || row >= a + b) return;
+    bool is_a = row >= b;
+    if (is_a ? (A == nullptr) : (B == nullptr)) return;
+    int32_t tid = thread_ids ? thread_ids[member] : first_thread + (int32_t)member;
+    float scale = (tid % 2 == 0) ? base_sigma : -base_sigma;  // sign * base_sigma
+    uint64_t s = noise_seed(key, true_epoch, tid / 2) | 1ull;
+    s = jump_by(pow2, s, 2ull * (uint64_t)rank * (uint64_t)row);
+    int m = is_a ? row - b : row;
+    int dim = is_a ? a : b;
+    float* dst = is_a ? A : B;
+    for (int q = 0; q < rank; ++q) {
+        float z = next_normal(s, cal);
+        if (is_a) z = fmul(z, scale);
+        size_t off = layout == HSES_LAYOUT_NAR
+                         ? ((size_t)member * dim + m) * rank + q
+                         : ((size_t)member * rank + q) * dim + m;
+        dst[off] = z;
+    }
+}
+
+__global__ void dense_noise_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
+                                   int32_t true_epoch, const int32_t* __restrict__ thread_ids,
+                                   int32_t first_thread, int64_t n_members, int len,
+                                   float base_sigma, float* __restrict__ out) {
+    int64_t member = blockIdx.x;
+    int begin = (blockIdx.y * blockDim.x + threadIdx.x) * kChunk;
+    if (member >= n_members || begin >= len) return;
+    int32_t tid = thread_ids ? thread_ids[member] : first_thread + (int32_t)member;
+    float scale = (tid % 2 == 0) ? base_sigma : -base_sigma;
+    uint64_t s = noise_seed(key, true_epoch, tid / 2) | 1ull;
+    s = jump_by(pow2, s, 2ull * (uint64_t)begin);
+    int end = begin + kChunk < len ? begin + kChunk : len;
+    for (int i = begin; i < end; ++i) out[(size_t)member * len + i] = fmul(next_normal(s, cal), scale);
+}
+
+// Dense-leaf update: block c owns elements [c*kChunk, (c+1)*kChunk); its
+// threads stride over the antithetic pairs, then reduce in a fixed order so
+// that every rank obtains the same bits.
+constexpr int kDenseThreads = 256;
+__global__ void es_update_dense_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
+                                       int32_t true_epoch, int32_t first_pair, int64_t n_pairs,
+                                       int len, float sigma, float out_scale,
+                                       const float* __restrict__ fitness, float* __restrict__ grad) {
+    __shared__ float red[kDenseThreads];
+    int begin = blockIdx.x * kChunk;
+    int cnt = len - begin < kChunk ? len - begin : kChunk;
+    float acc[kChunk];
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) acc[i] = 0.0f;
+    for (int64_t p = threadIdx.x; p < n_pairs; p += kDenseThreads) {
+        // member 2p has sign +1, member 2p+1 sign -1 (eggroll.rs:60-65)
+        float w = fmul(fitness[2 * p] - fitness[2 * p + 1], sigma);
+        uint64_t s = noise_seed(key, true_epoch, first_pair + (int32_t)p) | 1ull;
+        s = jump_by(pow2, s, 2ull * (uint64_t)begin);
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i)
+            if (i < cnt) acc[i] = fmaf(w, next_normal(s, cal), acc[i]);
+    }
+    for (int i = 0; i < cnt; ++i) {
+        red[threadIdx.x] = acc[i];
+        __syncthreads();
+        for (int stride = kDenseThreads / 2; stride > 0; stride >>= 1) {
+            if (threadIdx.x < stride) red[threadIdx.x] += red[threadIdx.x + stride];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) grad[begin + i] = red[0] * out_scale;
+        __syncthreads();
+    }
+}
+
+// Pair-folded raw factors for the scratch-based paths (see common.cuh).
+__global__ void pair_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
+                                    int32_t true_epoch, int32_t first_pair, int64_t pairs, int rank,
+                                    int a, int b, const float* __restrict__ pair_weight,
+                                    float* __restrict__ A, float* __restrict__ B) {
+    int64_t p = blockIdx.x;
+    int row = blockIdx.y * blockDim.x + threadIdx.x;
+    if (p >= pairs || row >= a + b) return;
+    uint64_t s = noise_seed(key, true_epoch, first_pair + (int32_t)p) | 1ull;
+    s = jump_by(pow2, s, 2ull * (uint64_t)rank * (uint64_t)row);
+    bool is_a = row >= b;
+    float* dst = is_a ? A + ((size_t)p * a + (row - b)) * rank : B + ((size_t)p * b + row) * rank;
+    float w = 1.0f;
+    if (is_a && pair_weight) w = __fsub_rn(pair_weight[2 * p], pair_weight[2 * p + 1]);
+    for (int q = 0; q < rank; ++q) {
+        float z = next_normal(s, cal);
+        dst[q] = (is_a && pair_weight) ? __fmul_rn(z, w) : z;
+    }
+}
+
+int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
+                        int32_t first_pair, int64_t pairs, int rank, int a, int b,
+                        const float* pair_weight, float* A, float* B) {
+    int rows = a + b;
+    HSES_REQUIRE((rows + 127) / 128 <= 65535, "a + b too large");
+    HSES_REQUIRE(pairs >= 1 && pairs < (1ll << 31), "pair count out of range");
+    dim3 grid((unsigned)pairs, (unsigned)((rows + 127) / 128));
+    pair_factors_kernel<<<grid, 128, 0, stream>>>(ctx->cal(), ctx->t.jump_pow2, key, true_epoch,
+                                                  first_pair, pairs, rank, a, b, pair_weight, A, B);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // namespace hses
+
+using namespace hses;
+
+extern "C" {
+
+int hses_normal_fill(hses_ctx* ctx, hses_stream stream, uint64_t seed, float* out, size_t n) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(out != nullptr, "out is NULL");
+    HSES_REQUIRE(n < (1ull << 40), "n too large");
+    size_t chunks = (n + kChunk - 1) / kChunk;
+    unsigned blocks = (unsigned)((chunks + 127) / 128);
+    normal_fill_kernel<<<blocks, 128, 0, as_stream(stream)>>>(ctx->cal(), ctx->t.jump_pow2, seed, out, n);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_lora_factors(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                      int32_t noise_reuse, const int32_t* thread_ids, int32_t first_thread,
+                      int64_t n_members, int32_t rank, int32_t a, int32_t b, float base_sigma,
+                      int32_t layout, float* A, float* B) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n_members >= 0 && n_members < (1ll << 31), "n_members out of range");
+    HSES_REQUIRE(rank >= 1 && a >= 1 && b >= 1, "rank, a and b must be positive");
+    HSES_REQUIRE(layout == HSES_LAYOUT_NAR || layout == HSES_LAYOUT_NRA, "unknown layout");
+    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
+    HSES_REQUIRE(thread_ids != nullptr || first_thread >= 0, "thread ids must be non-negative");
+    if (n_members == 0 || (A == nullptr && B == nullptr)) return HSES_OK;
+    int rows = a + b;
+    HSES_REQUIRE((rows + 127) / 128 <= 65535, "a + b too large");
+    dim3 grid((unsigned)n_members, (unsigned)((rows + 127) / 128));
+    lora_factors_kernel<<<grid, 128, 0, as_stream(stream)>>>(
+        ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), thread_ids,
+        first_thread, n_members, rank, a, b, base_sigma, layout, A, B);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_dense_noise(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                     int32_t noise_reuse, const int32_t* thread_ids, int32_t first_thread,
+                     int64_t n_members, int32_t rows, int32_t cols, float base_sigma, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n_members >= 0 && n_members < (1ll << 31), "n_members out of range");
+    HSES_REQUIRE(rows >= 1 && cols >= 1 && (int64_t)rows * cols < (1ll << 24), "bad leaf shape");
+    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
+    if (n_members == 0) return HSES_OK;
+    HSES_REQUIRE(out != nullptr, "out is NULL");
+    int len = rows * cols;
+    int chunks = (len + kChunk - 1) / kChunk;
+    dim3 grid((unsigned)n_members, (unsigned)((chunks + 63) / 64));
+    dense_noise_kernel<<<grid, 64, 0, as_stream(stream)>>>(
+        ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), thread_ids,
+        first_thread, n_members, len, base_sigma, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                         int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                         int32_t len, float sigma, const float* fitness, float* grad) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
+                 "members must form whole antithetic pairs");
+    HSES_REQUIRE(n_total >= n, "n_total < n");
+    HSES_REQUIRE(len >= 1 && len <= (1 << 20), "len out of range");
+    HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");
+    // grad = -( (sum/N) * sqrt(N) ), eggroll.rs:349,402-403
+    float nf = (float)n_total;
+    float out_scale = -(1.0f / nf) * sqrtf(nf);
+    int blocks = (len + kChunk - 1) / kChunk;
+    es_update_dense_kernel<<<blocks, kDenseThreads, 0, as_stream(stream)>>>(
+        ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), first_thread / 2,
+        n / 2, len, sigma, out_scale, fitness, grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,167 @@
+// Fitness-weighted update of a LoRA-noised matrix
+// (simple_lora_update + do_update_with, hyperscalees-noiser/src/eggroll.rs:353-404):
+//   grad = -sqrt(N) * (1/N) * sum_i f_i A_i B_iᵀ.
+// Antithetic members 2p and 2p+1 share one draw with A negated, so the sum
+// folds to sum_p (f_2p - f_2p+1) * base_sigma * Araw_p Braw_pᵀ — a dense
+// contraction (a, K)·(K, b) over K = pairs * rank, the same 2-D GEMM form as
+// lora_einsum_raw (eggroll.rs:726-738).
+//
+// General path: the raw factors of a chunk of pairs are regenerated into
+// scratch (A pre-multiplied by the pair weight), a split-K fp32 GEMM writes
+// per-split partial sums, and a final pass adds the partials in a fixed order
+// so that every rank ends up with bit-identical gradients.
+#include "common.cuh"
+
+namespace hses {
+
+constexpr int UM = 128, UN = 128, UK = 16, UT = 256;
+constexpr size_t kFactorChunkBytes = 256ull << 20;
+
+struct UpdatePlan {
+    int64_t pairs, chunk_pairs;
+    int splits;
+    size_t a_elems, b_elems, partial_elems, bytes;
+};
+
+static UpdatePlan plan_update(int a, int b, int rank, int64_t n) {
+    UpdatePlan p;
+    p.pairs = n / 2;
+    size_t per_pair = (size_t)(a + b) * rank * sizeof(float);
+    int64_t fit = (int64_t)(kFactorChunkBytes / per_pair);
+    if (fit < 1) fit = 1;
+    p.chunk_pairs = p.pairs < fit ? p.pairs : fit;
+    int tiles = ((a + UM - 1) / UM) * ((b + UN - 1) / UN);
+    int want = (2 * 148 + tiles - 1) / tiles;
+    if (want > 64) want = 64;
+    if (want > p.chunk_pairs) want = (int)p.chunk_pairs;
+    if (want < 1) want = 1;
+    p.splits = want;
+    auto up = [](size_t v) { return (v + 63) / 64 * 64; };
+    p.a_elems = up((size_t)p.chunk_pairs * a * rank);
+    p.b_elems = up((size_t)p.chunk_pairs * b * rank);
+    p.partial_elems = up((size_t)p.splits * a * b);
+    p.bytes = (p.a_elems + p.b_elems + p.partial_elems) * sizeof(float);
+    return p;
+}
+
+// partial[split][m][n] (+)= sum over the split's pairs and q of A[p][m][q]*B[p][n][q]
+__global__ void __launch_bounds__(UT)
+update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t pairs, int rank,
+                   int a, int b, int accumulate, float* __restrict__ partial) {
+    __shared__ __align__(16) float sa[UK][UM + 4];
+    __shared__ __align__(16) float sb[UK][UN + 4];
+    int m0 = blockIdx.y * UM, n0 = blockIdx.x * UN;
+    int split = blockIdx.z, splits = gridDim.z;
+    int64_t p_lo = pairs * split / splits, p_hi = pairs * (split + 1) / splits;
+    int64_t k_lo = p_lo * rank, k_hi = p_hi * rank;
+    int tid = threadIdx.x;
+    int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    for (int64_t k0 = k_lo; k0 < k_hi; k0 += UK) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int idx = tid + e * UT;
+            int r = idx / UK, kk = idx % UK;
+            int64_t kg = k0 + kk;
+            int64_t p = kg / rank;
+            int q = (int)(kg - p * rank);
+            bool kin = kg < k_hi;
+            sa[kk][r] = (kin && m0 + r < a) ? A[((size_t)p * a + m0 + r) * rank + q] : 0.0f;
+            sb[kk][r] = (kin && n0 + r < b) ? B[((size_t)p * b + n0 + r) * rank + q] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < UK; ++kk) {
+            float xa[8], wb[8];
+            *reinterpret_cast<float4*>(&xa[0]) = *reinterpret_cast<const float4*>(&sa[kk][tr]);
+            *reinterpret_cast<float4*>(&xa[4]) = *reinterpret_cast<const float4*>(&sa[kk][64 + tr]);
+            *reinterpret_cast<float4*>(&wb[0]) = *reinterpret_cast<const float4*>(&sb[kk][tc]);
+            *reinterpret_cast<float4*>(&wb[4]) = *reinterpret_cast<const float4*>(&sb[kk][64 + tc]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float* dst = partial + (size_t)split * a * b;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int m = m0 + (i < 4 ? tr + i : 64 + tr + i - 4);
+        if (m >= a) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int n = n0 + (j < 4 ? tc + j : 64 + tc + j - 4);
+            if (n >= b) continue;
+            size_t o = (size_t)m * b + n;
+            dst[o] = accumulate ? dst[o] + acc[i][j] : acc[i][j];
+        }
+    }
+}
+
+__global__ void update_reduce_kernel(const float* __restrict__ partial, int splits, size_t len,
+                                     float scale, float* __restrict__ grad) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= len) return;
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * len + i]);
+    grad[i] = __fmul_rn(s, scale);
+}
+
+}  // namespace hses
+
+using namespace hses;
+
+extern "C" {
+
+size_t hses_es_update_workspace_bytes(int32_t a, int32_t b, int32_t rank, int64_t n) {
+    if (a < 1 || b < 1 || rank < 1 || n < 2) return 0;
+    return plan_update(a, b, rank, n).bytes;
+}
+
+int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                   int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                   int32_t rank, int32_t a, int32_t b, float sigma, const float* fitness,
+                   float* grad, void* workspace, size_t workspace_bytes) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
+                 "members must form whole antithetic pairs");
+    HSES_REQUIRE(n_total >= n, "n_total < n");
+    HSES_REQUIRE(rank >= 1 && rank <= 1024 && a >= 1 && b >= 1, "bad shape");
+    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
+    HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");
+    UpdatePlan p = plan_update(a, b, rank, n);
+    HSES_REQUIRE(workspace != nullptr && workspace_bytes >= p.bytes,
+                 "workspace too small; see hses_es_update_workspace_bytes");
+    HSES_REQUIRE((a + UM - 1) / UM <= 65535, "a too large");
+    cudaStream_t st = as_stream(stream);
+    float* wsA = reinterpret_cast<float*>(workspace);
+    float* wsB = wsA + p.a_elems;
+    float* partial = wsB + p.b_elems;
+    int32_t te = true_epoch_of(epoch, noise_reuse);
+    dim3 grid((unsigned)((b + UN - 1) / UN), (unsigned)((a + UM - 1) / UM), (unsigned)p.splits);
+    int chunk_idx = 0;
+    for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
+        int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
+        int rc = launch_pair_factors(ctx, st, key, te, first_thread / 2 + (int32_t)done, cnt, rank, a,
+                                     b, fitness + 2 * done, wsA, wsB);
+        if (rc != HSES_OK) return rc;
+        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, partial);
+        HSES_LAUNCH_CHECK();
+    }
+    // grad = -( (sum * base_sigma / N) * sqrt(N) ), eggroll.rs:365-372, 402-403
+    float nf = (float)n_total;
+    float scale = -((sigma / sqrtf((float)rank)) * (1.0f / nf)) * sqrtf(nf);
+    size_t len = (size_t)a * b;
+    update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
+                                                                       grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,302 @@
+"""Tensor-level wrappers over the C ABI: every function checks its torch
+tensors (CUDA, fp32, unit inner stride), forwards raw pointers, shapes and row
+strides, and enqueues on torch's current stream.  PyTorch only supplies device
+memory and streams here; all arithmetic happens in the CUDA library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .core import current_stream, get_context
+
+RESET_HARD, RESET_SUBTRACT = 0, 1
+REWARD_LOGLIK, REWARD_BINARY = 0, 1
+SGD, ADAM, ADAMW = 0, 1, 2
+LAYOUT_NAR, LAYOUT_NRA = 0, 1
+ALGO_AUTO, ALGO_SIMT, ALGO_TENSOR = 0, 1, 2
+
+_U64 = (1 << 64) - 1
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _check(t: torch.Tensor, name: str, dtype=torch.float32, ndim: Optional[int] = None):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name} must have {ndim} dims, got {t.dim()}")
+    if t.dim() > 0 and t.stride(-1) != 1 and t.size(-1) > 1:
+        raise ValueError(f"{name} must have unit stride along its last dim")
+
+
+def _rows_2d(t: torch.Tensor, name: str) -> Tuple[int, int, int]:
+    """View a (..., cols) tensor whose leading dims are mutually contiguous as
+    pitched rows; returns (rows, cols, row_stride)."""
+    cols = t.size(-1)
+    rows = t.numel() // max(cols, 1)
+    stride = t.stride(-2) if t.dim() >= 2 else cols
+    expect = stride
+    for d in range(t.dim() - 2, -1, -1):
+        if t.size(d) != 1 and t.stride(d) != expect:
+            raise ValueError(f"{name}: leading dims must be contiguous over pitched rows")
+        expect *= t.size(d)
+    return rows, cols, stride
+
+
+def noise_seed(key: int, true_epoch: int, true_thread: int) -> int:
+    return int(_lib.load().hses_noise_seed(C.c_uint64(key & _U64), true_epoch, true_thread))
+
+
+def normal_fill(seed: int, n: int, device=None) -> torch.Tensor:
+    ctx = get_context(device)
+    out = torch.empty(n, dtype=torch.float32, device=torch.device("cuda", ctx.device))
+    _lib.check(_lib.load().hses_normal_fill(ctx.handle, current_stream(), C.c_uint64(seed & _U64),
+                                            _ptr(out), n))
+    return out
+
+
+def lora_factors(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int,
+                 base_sigma: float, n_members: int, first_thread: int = 0,
+                 thread_ids: Optional[torch.Tensor] = None, layout: int = LAYOUT_NAR,
+                 want_a: bool = True, want_b: bool = True, device=None):
+    ctx = get_context(device)
+    dev = torch.device("cuda", ctx.device)
+    if thread_ids is not None:
+        _check(thread_ids, "thread_ids", torch.int32, 1)
+        n_members = thread_ids.numel()
+    sa = (n_members, a, rank) if layout == LAYOUT_NAR else (n_members, rank, a)
+    sb = (n_members, b, rank) if layout == LAYOUT_NAR else (n_members, rank, b)
+    A = torch.empty(sa, dtype=torch.float32, device=dev) if want_a else None
+    B = torch.empty(sb, dtype=torch.float32, device=dev) if want_b else None
+    _lib.check(_lib.load().hses_lora_factors(
+        ctx.handle, current_stream(), C.c_uint64(key & _U64), epoch, noise_reuse, _ptr(thread_ids),
+        first_thread, n_members, rank, a, b, base_sigma, layout, _ptr(A), _ptr(B)))
+    return A, B
+
+
+def dense_noise(key: int, epoch: int, noise_reuse: int, rows: int, cols: int, base_sigma: float,
+                n_members: int, first_thread: int = 0, thread_ids: Optional[torch.Tensor] = None,
+                device=None) -> torch.Tensor:
+    ctx = get_context(device)
+    if thread_ids is not None:
+        _check(thread_ids, "thread_ids", torch.int32, 1)
+        n_members = thread_ids.numel()
+    out = torch.empty((n_members, rows, cols), dtype=torch.float32,
+                      device=torch.device("cuda", ctx.device))
+    _lib.check(_lib.load().hses_dense_noise(
+        ctx.handle, current_stream(), C.c_uint64(key & _U64), epoch, noise_reuse, _ptr(thread_ids),
+        first_thread, n_members, rows, cols, base_sigma, _ptr(out)))
+    return out
+
+
+def poisson_encode(probs: torch.Tensor, T: int, seeds: Sequence[int],
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """probs (batch, in_dim) pitched -> spikes (T, batch, in_dim) with the same pitch."""
+    _check(probs, "probs", ndim=2)
+    batch, in_dim = probs.shape
+    stride = probs.stride(0) if batch > 1 else max(probs.stride(0), in_dim)
+    if out is None:
+        buf = torch.empty((T, batch, stride), dtype=torch.float32, device=probs.device)
+        out = buf[:, :, :in_dim]
+    else:
+        _check(out, "out", ndim=3)
+        if tuple(out.shape) != (T, batch, in_dim) or out.stride(1) != stride or \
+                (T > 1 and out.stride(0) != batch * stride):
+            raise ValueError("out must be (T, batch, in_dim) with the pitch of probs")
+    ctx = get_context(probs.device)
+    sd = (C.c_uint32 * 4)(*[int(s) & 0xFFFFFFFF for s in seeds])
+    _lib.check(_lib.load().hses_poisson_encode(ctx.handle, current_stream(), _ptr(probs), batch,
+                                               in_dim, stride, T, sd, _ptr(out)))
+    return out
+
+
+def lif_scan(cur: torch.Tensor, tau_m: float, v_th: float, v: Optional[torch.Tensor] = None,
+             reset_mode: int = RESET_HARD, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """cur (T, n, h) pitched -> spikes of the same layout; v (n, h) is updated in place."""
+    _check(cur, "cur", ndim=3)
+    T, n, h = cur.shape
+    stride = cur.stride(1)
+    if T > 1 and cur.stride(0) != n * stride:
+        raise ValueError("cur: time steps must be n*row_stride apart")
+    if out is None:
+        buf = torch.empty((T, n, stride), dtype=torch.float32, device=cur.device)
+        out = buf[:, :, :h]
+    else:
+        _check(out, "out", ndim=3)
+        if tuple(out.shape) != (T, n, h) or out.stride(1) != stride:
+            raise ValueError("out must match cur's shape and pitch")
+    if v is not None:
+        _check(v, "v", ndim=2)
+        if tuple(v.shape) != (n, h) or (n > 1 and v.stride(0) != stride):
+            raise ValueError("v must be (n, h) with cur's row pitch")
+    ctx = get_context(cur.device)
+    _lib.check(_lib.load().hses_lif_scan(ctx.handle, current_stream(), _ptr(cur), T, n, h, stride,
+                                         _ptr(v), tau_m, v_th, reset_mode, _ptr(out)))
+    return out
+
+
+_workspaces = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Grow-only scratch buffer per device (the library itself never allocates scratch)."""
+    if nbytes == 0:
+        return None
+    buf = _workspaces.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[device] = buf
+    return buf
+
+
+def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: int, t_steps: int = 1,
+                     sigma: float = 0.0, rank: int = 1, key: int = 0, epoch: int = 0,
+                     first_thread: int = 0, noise_reuse: int = 0, perturb: bool = True,
+                     lif: bool = False, tau_m: float = 20.0, v_th: float = 0.3,
+                     reset_mode: int = RESET_HARD, out_scale: float = 1.0,
+                     out: Optional[torch.Tensor] = None, want_potentials: bool = False,
+                     algo: int = ALGO_AUTO):
+    """do_mm over a population (+ optional LIF step).  x: (..., k) with
+    t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
+    the charged potentials."""
+    _check(x, "x")
+    _check(param, "param", ndim=2)
+    rows, k, xs = _rows_2d(x, "x")
+    if rows != t_steps * n_pop * bm:
+        raise ValueError(f"x has {rows} rows, expected t_steps*n_pop*bm = {t_steps * n_pop * bm}")
+    a, k2 = param.shape
+    if k2 != k:
+        raise ValueError("param must be (a, k) with k = x's last dim")
+    if out is None:
+        out = torch.empty((rows, a), dtype=torch.float32, device=x.device)
+    else:
+        _check(out, "out", ndim=2)
+        if tuple(out.shape) != (rows, a):
+            raise ValueError("out must be (rows, a)")
+    pot = None
+    if want_potentials:
+        pot = torch.empty((rows, out.stride(0)), dtype=torch.float32, device=x.device)[:, :a]
+    g = _lib.LinearArgs()
+    g.x, g.t_steps, g.n_pop, g.bm, g.k, g.x_row_stride = x.data_ptr(), t_steps, n_pop, bm, k, xs
+    g.param, g.a, g.param_row_stride = param.data_ptr(), a, param.stride(0) if a > 1 else max(param.stride(0), k)
+    g.sigma, g.rank, g.key, g.epoch = sigma, rank, key & _U64, epoch
+    g.first_thread, g.noise_reuse, g.perturb, g.lif = first_thread, noise_reuse, int(perturb), int(lif)
+    g.tau_m, g.v_th, g.reset_mode, g.out_scale = tau_m, v_th, reset_mode, out_scale
+    g.out, g.out_row_stride = out.data_ptr(), out.stride(0) if rows > 1 else max(out.stride(0), a)
+    g.potentials = pot.data_ptr() if pot is not None else None
+    g.algo = algo
+    L = _lib.load()
+    need = int(L.hses_perturbed_linear_workspace_bytes(C.byref(g)))
+    ws = _workspace(x.device, need)
+    g.workspace = ws.data_ptr() if ws is not None else None
+    g.workspace_bytes = need
+    ctx = get_context(x.device)
+    _lib.check(L.hses_perturbed_linear(ctx.handle, current_stream(), C.byref(g)))
+    return (out, pot) if want_potentials else out
+
+
+def time_mean(x: torch.Tensor) -> torch.Tensor:
+    """x (T, n, h) pitched -> dense (n, h) mean over T."""
+    _check(x, "x", ndim=3)
+    T, n, h = x.shape
+    stride = x.stride(1)
+    if T > 1 and x.stride(0) != n * stride:
+        raise ValueError("x: time steps must be n*row_stride apart")
+    out = torch.empty((n, h), dtype=torch.float32, device=x.device)
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_time_mean(ctx.handle, current_stream(), _ptr(x), T, n, h, stride,
+                                          _ptr(out), h))
+    return out
+
+
+def fitness(logits: torch.Tensor, labels: torch.Tensor, reward: int = REWARD_LOGLIK) -> torch.Tensor:
+    _check(logits, "logits", ndim=2)
+    _check(labels, "labels", torch.int32, 1)
+    logits = logits.contiguous()
+    n, c = logits.shape
+    out = torch.empty(n, dtype=torch.float32, device=logits.device)
+    ctx = get_context(logits.device)
+    _lib.check(_lib.load().hses_fitness(ctx.handle, current_stream(), _ptr(logits), n, c,
+                                        _ptr(labels), reward, _ptr(out)))
+    return out
+
+
+def member_mean(per_sample: torch.Tensor, n_pop: int, bm: int) -> torch.Tensor:
+    _check(per_sample, "per_sample", ndim=1)
+    out = torch.empty(n_pop, dtype=torch.float32, device=per_sample.device)
+    ctx = get_context(per_sample.device)
+    _lib.check(_lib.load().hses_member_mean(ctx.handle, current_stream(), _ptr(per_sample), n_pop,
+                                            bm, _ptr(out)))
+    return out
+
+
+def convert_fitnesses(raw: torch.Tensor, group_size: int = 0, want_stats: bool = False):
+    _check(raw, "raw", ndim=1)
+    out = torch.empty_like(raw)
+    stats = torch.empty(2, dtype=torch.float32, device=raw.device) if want_stats else None
+    ctx = get_context(raw.device)
+    _lib.check(_lib.load().hses_convert_fitnesses(ctx.handle, current_stream(), _ptr(raw),
+                                                  raw.numel(), group_size, _ptr(out), _ptr(stats)))
+    return (out, stats) if want_stats else out
+
+
+def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int, sigma: float,
+              fitness_: torch.Tensor, first_thread: int = 0, n_total: Optional[int] = None,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _check(fitness_, "fitness", ndim=1)
+    n = fitness_.numel()
+    if out is None:
+        out = torch.empty((a, b), dtype=torch.float32, device=fitness_.device)
+    L = _lib.load()
+    need = int(L.hses_es_update_workspace_bytes(a, b, rank, n))
+    ws = _workspace(fitness_.device, need)
+    ctx = get_context(fitness_.device)
+    _lib.check(L.hses_es_update(ctx.handle, current_stream(), C.c_uint64(key & _U64), epoch,
+                                noise_reuse, first_thread, n, n if n_total is None else n_total,
+                                rank, a, b, sigma, _ptr(fitness_), _ptr(out), _ptr(ws), need))
+    return out
+
+
+def es_update_dense(key: int, epoch: int, noise_reuse: int, shape: Tuple[int, int], sigma: float,
+                    fitness_: torch.Tensor, first_thread: int = 0,
+                    n_total: Optional[int] = None) -> torch.Tensor:
+    _check(fitness_, "fitness", ndim=1)
+    n = fitness_.numel()
+    out = torch.empty(shape, dtype=torch.float32, device=fitness_.device)
+    ctx = get_context(fitness_.device)
+    _lib.check(_lib.load().hses_es_update_dense(
+        ctx.handle, current_stream(), C.c_uint64(key & _U64), epoch, noise_reuse, first_thread, n,
+        n if n_total is None else n_total, shape[0] * shape[1], sigma, _ptr(fitness_), _ptr(out)))
+    return out
+
+
+def solver_step(kind: int, step: int, param: torch.Tensor, grad: torch.Tensor,
+                m: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None, lr: float = 0.01,
+                beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                weight_decay: float = 0.0, grad_scale: float = 1.0) -> None:
+    """In-place optimizer step on a contiguous parameter tensor."""
+    for t, name in ((param, "param"), (grad, "grad")):
+        _check(t, name)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    desc = _lib.SolverDesc(kind, lr, beta1, beta2, eps, weight_decay)
+    ctx = get_context(param.device)
+    _lib.check(_lib.load().hses_solver_step(ctx.handle, current_stream(), C.byref(desc), step,
+                                            grad_scale, _ptr(param), _ptr(grad), _ptr(m), _ptr(v),
+                                            param.numel()))
+
+
+def base_sigma(sigma: float, rank: int) -> float:
+    """sigma / sqrt(rank) in fp32, as the callers of get_lora_update_params compute it
+    (eggroll.rs:365, 433)."""
+    import numpy as np
+    return float(np.float32(sigma) / np.sqrt(np.float32(rank)))

@@ -1,0 +1,205 @@
+/*
+ * hses.h — C ABI of the B200-native EggRoll population step.
+ *
+ * Conventions (they follow the raw-pointer seam the reference already uses
+ * for its native kernels, hyperscalees/src/oxide.rs:96-146):
+ *   - every pointer marked "device" is a CUDA device pointer owned by the
+ *     caller; outputs are caller-allocated, nothing here frees caller memory;
+ *   - matrices are row-major fp32 with an explicit row stride in ELEMENTS
+ *     (Burn pitches rows to 256 B, oxide.rs:225-232), unless stated otherwise;
+ *   - work is enqueued on the caller's stream and never synchronised inside
+ *     an entry point (oxide.rs:119-125); the only blocking call is
+ *     hses_ctx_create;
+ *   - every entry point returns an hses_status; on failure
+ *     hses_last_error() gives a message for the calling thread.  Shape
+ *     violations are reported, not aborted on;
+ *   - a context belongs to one device and is not thread-safe; distinct
+ *     contexts are independent.
+ *
+ * There is no CPU fallback: every compute entry point launches CUDA kernels
+ * built for sm_100a and fails if that is impossible.
+ */
+#ifndef HSES_H
+#define HSES_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hses_ctx hses_ctx;
+typedef void* hses_stream; /* cudaStream_t */
+
+enum hses_status {
+    HSES_OK = 0,
+    HSES_ERR_INVALID = 1,     /* bad argument / unsupported shape */
+    HSES_ERR_CUDA = 2,        /* a CUDA runtime call failed */
+    HSES_ERR_CALIBRATION = 3, /* libm calibration found a non-adjacent value */
+    HSES_ERR_UNSUPPORTED = 4  /* requested algorithm cannot run this shape */
+};
+
+enum hses_reset_mode { HSES_RESET_HARD = 0, HSES_RESET_SUBTRACT = 1 };
+enum hses_reward { HSES_REWARD_LOGLIK = 0, HSES_REWARD_BINARY = 1 };
+enum hses_solver_kind { HSES_SGD = 0, HSES_ADAM = 1, HSES_ADAMW = 2 };
+enum hses_factor_layout {
+    HSES_LAYOUT_NAR = 0, /* A (n,a,r), B (n,b,r): batched_lora_noise, eggroll.rs:116-130 */
+    HSES_LAYOUT_NRA = 1  /* A (n,r,a), B (n,r,b): batched forward / einsum layout, snn.rs:472-476 */
+};
+enum hses_linear_algo { HSES_ALGO_AUTO = 0, HSES_ALGO_SIMT = 1, HSES_ALGO_TENSOR = 2 };
+
+const char* hses_last_error(void);
+int hses_version(void);
+
+/* ---- context: replaces hyperscalees-core default_device()/is_gpu()
+ *      (hyperscalees-core/src/lib.rs:6-23) and the process-global kernel
+ *      caches of oxide.rs:197-202.  Creation uploads the generator's jump
+ *      tables and calibrates the device logf/cosf against the host libm over
+ *      all 2^24 uniforms (blocking, well under a second). ------------------- */
+int hses_ctx_create(int device, hses_ctx** out);
+int hses_ctx_destroy(hses_ctx* ctx);
+/* How many of the 2^24 inputs the host libm rounds away from the correctly
+ * rounded value (diagnostic; tests compare it with their own count). */
+int hses_ctx_calibration_info(const hses_ctx* ctx, uint64_t* log_flips, uint64_t* cos_flips);
+
+/* ---- seed hash: noise_seed, hyperscalees-noiser/src/noiser.rs:495-506 ---- */
+uint64_t hses_noise_seed(uint64_t key, int32_t true_epoch, int32_t true_thread);
+
+/* ---- DeterministicNoise::normal_tensor, noiser.rs:481-490: n standard
+ *      normals of the stream seeded by `seed`, in stream order. ------------ */
+int hses_normal_fill(hses_ctx* ctx, hses_stream stream, uint64_t seed, float* out /*device*/,
+                     size_t n);
+
+/* ---- get_lora_update_params / batched_lora_noise, eggroll.rs:86-130.
+ *      Member i uses thread id thread_ids[i] (device int32) or, when
+ *      thread_ids is NULL, first_thread + i.  A is scaled by sign*base_sigma
+ *      (sign = -1 for odd thread ids), B is the raw normal block.  Either
+ *      output may be NULL. -------------------------------------------------- */
+int hses_lora_factors(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                      int32_t noise_reuse, const int32_t* thread_ids /*device or NULL*/,
+                      int32_t first_thread, int64_t n_members, int32_t rank, int32_t a, int32_t b,
+                      float base_sigma, int32_t layout, float* A /*device*/, float* B /*device*/);
+
+/* ---- get_nonlora_update_params, eggroll.rs:312-324: sign*base_sigma*N(0,1)
+ *      of shape (rows, cols) per member, out is (n, rows, cols). ----------- */
+int hses_dense_noise(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                     int32_t noise_reuse, const int32_t* thread_ids /*device or NULL*/,
+                     int32_t first_thread, int64_t n_members, int32_t rows, int32_t cols,
+                     float base_sigma, float* out /*device*/);
+
+/* ---- poisson_encode_fused, oxide.rs:573-625 /
+ *      hyperscalees-kernels/src/poisson_encode_fused_oxide.rs:61-106.
+ *      probs (batch, in_dim) pitched; out (T, batch, in_dim) with the same
+ *      pitch.  Unlike the reference wrapper (wall-clock seeds, oxide.rs:205-223)
+ *      the four seed words are explicit, so the spikes are reproducible. ---- */
+int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs /*device*/,
+                        int64_t batch, int32_t in_dim, int64_t row_stride, int32_t T,
+                        const uint32_t seeds[4], float* out /*device*/);
+
+/* ---- lif_fused, oxide.rs:489-543 / lif_fused_oxide.rs:37-70, run_lif
+ *      snn.rs:73-97.  cur and spikes are (T, n, h) pitched; v is (n, h)
+ *      pitched, read as v0 and overwritten with the final potential, or NULL
+ *      for v0 = 0 with no write-back. --------------------------------------- */
+int hses_lif_scan(hses_ctx* ctx, hses_stream stream, const float* cur /*device*/, int32_t T,
+                  int64_t n, int32_t h, int64_t row_stride, float* v /*device or NULL*/,
+                  float tau_m, float v_th, int32_t reset_mode, float* spikes /*device*/);
+
+/* ---- do_mm, eggroll.rs:419-446, for a whole population in one call, with
+ *      an optional fused lif_step (snn.rs:53-65) from v0 = 0.
+ *      x is (t_steps, n_pop, bm, k): row R belongs to member (R / bm) % n_pop,
+ *      whose thread id is first_thread + member.  param is (a, k).
+ *      out is (t_steps*n_pop*bm, a): y = x·paramᵀ + (x·B)·Aᵀ when lif == 0,
+ *      else the 0/1 spikes of one LIF step applied to y.  potentials
+ *      (optional, same shape) receives the charged membrane before reset. --- */
+typedef struct {
+    const float* x; /* device */
+    int32_t t_steps;
+    int64_t n_pop;
+    int32_t bm;
+    int32_t k;
+    int64_t x_row_stride;
+    const float* param; /* device, (a, k) */
+    int32_t a;
+    int64_t param_row_stride;
+    float sigma; /* EggRoll sigma; the kernel uses sigma / sqrt(rank) */
+    int32_t rank;
+    uint64_t key;
+    int32_t epoch;
+    int32_t first_thread;
+    int32_t noise_reuse;
+    int32_t perturb; /* 0: clean x·paramᵀ (iterinfo = None) */
+    int32_t lif;     /* 0: write y; 1: write spikes of one LIF step */
+    float tau_m;
+    float v_th;
+    int32_t reset_mode;
+    float out_scale; /* lif == 0 only: y is multiplied by this (readout gain, snn.rs:280-281) */
+    float* out; /* device */
+    int64_t out_row_stride;
+    float* potentials; /* device or NULL */
+    int32_t algo;      /* hses_linear_algo */
+    void* workspace;   /* device scratch, hses_perturbed_linear_workspace_bytes() */
+    size_t workspace_bytes;
+} hses_linear_args;
+/* Scratch the call needs for these shapes and this algo (0 is possible). */
+size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);
+int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_args* args);
+
+/* ---- mean firing rate over the time axis, spikes.mean_dim(0) of snn.rs:278:
+ *      x (T, n, h) pitched -> out (n, h) with its own pitch. ---------------- */
+int hses_time_mean(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int32_t T,
+                   int64_t n, int32_t h, int64_t row_stride, float* out /*device*/,
+                   int64_t out_row_stride);
+
+/* ---- fitness_from_logits_reward, hyperscalees-envs/src/snn_mnist.rs:180-201.
+ *      logits (n, classes) dense; labels device int32; out (n). ------------- */
+int hses_fitness(hses_ctx* ctx, hses_stream stream, const float* logits /*device*/, int64_t n,
+                 int32_t classes, const int32_t* labels /*device*/, int32_t reward,
+                 float* out /*device*/);
+
+/* ---- mean over each member's bm consecutive samples: (n_pop*bm) -> (n_pop) */
+int hses_member_mean(hses_ctx* ctx, hses_stream stream, const float* per_sample /*device*/,
+                     int64_t n_pop, int32_t bm, float* out /*device*/);
+
+/* ---- convert_fitnesses, eggroll.rs:967-992 / noiser.rs:517-537.  stats
+ *      (optional, device, 2 floats) receives {mean, std}. ------------------- */
+int hses_convert_fitnesses(hses_ctx* ctx, hses_stream stream, const float* raw /*device*/,
+                           int64_t n, int32_t group_size, float* out /*device*/,
+                           float* stats /*device or NULL*/);
+
+/* ---- simple_lora_update + do_update_with, eggroll.rs:353-404:
+ *      grad(a,b) = -sqrt(N) * (1/N) * sum_i f_i A_i B_iᵀ with the factors
+ *      regenerated from seeds.  Members are first_thread .. first_thread+n-1
+ *      (n even, first_thread even: antithetic pairs are folded).  `fitness`
+ *      holds the n converted fitnesses.  n_total is the N of the formula
+ *      (= n unless the caller splits the population and sums partial grads).
+ *      workspace: device scratch of hses_es_update_workspace_bytes(). ------- */
+size_t hses_es_update_workspace_bytes(int32_t a, int32_t b, int32_t rank, int64_t n);
+int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                   int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                   int32_t rank, int32_t a, int32_t b, float sigma,
+                   const float* fitness /*device*/, float* grad /*device (a,b) dense*/,
+                   void* workspace /*device*/, size_t workspace_bytes);
+
+/* ---- simple_full_update + do_update_with, eggroll.rs:331-350, 384-404, for
+ *      dense (PARAM-class) leaves of `len` = rows*cols elements. ----------- */
+int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                         int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                         int32_t len, float sigma, const float* fitness /*device*/,
+                         float* grad /*device*/);
+
+/* ---- Solver::update, noiser.rs:155-224.  step is the counter value after
+ *      the increment (1 on the first Adam step).  m, v may be NULL for SGD.
+ *      grad_scale multiplies the gradient first (clip_by_global_norm). ----- */
+typedef struct {
+    int32_t kind; /* hses_solver_kind */
+    float lr, beta1, beta2, eps, weight_decay;
+} hses_solver;
+int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solver, int32_t step,
+                     float grad_scale, float* param /*device*/, const float* grad /*device*/,
+                     float* m /*device*/, float* v /*device*/, int64_t len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HSES_H */
