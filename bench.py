@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""Benchmark of the EggRoll population hot path on B200.
+
+Workload (N = 1): the perturbed-linear microbenchmark — per-member input x of
+shape [n_pop = 8192, Bm = 16, K = 1024] and W [1024, 1024], fp32 N(0,1), rank-16
+factors from the counter RNG (seed key below), one LIF step, spikes out.  A
+"step" is one pass of hses_perturbed_linear over that batch.  With N > 1 every
+rank runs the same per-GPU batch on its own slice of a population of N*8192
+members (weak scaling, no data-path collective: the path emits spikes only).
+
+Metric: member-evaluations per second = n_pop * Bm * T (T = 1) per second.
+
+    python bench.py --gpus N --steps K --warmup W            # the CUDA path
+    python bench.py --impl reference --gpus N --steps K ...   # CPU restatement of the reference
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "member_evals_per_sec"
+UNIT = "member-evals/s"
+KEY = 0x3C6EF372FE94F82A          # base key of parameter index 1
+SIGMA, RANK, TAU_M, V_TH = 0.02, 16, 20.0, 0.3
+N_POP, BM, K_DIM, A_DIM = 8192, 16, 1024, 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed regions run."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        rows = []
+        with open(self.tmp.name) as fh:
+            for line in fh:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) == 7:
+                    rows.append(parts)
+        os.unlink(self.tmp.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[0]) for r in rows if r[0].replace(".", "").isdigit())
+        # "under load": the upper half of the samples (idle gaps between regions pull the rest down)
+        load = sm[len(sm) // 2:] if sm else []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        power = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": float(np.median(load)) if load else None,
+                "sm_max_mhz": float(rows[0][1]) if rows[0][1].replace(".", "").isdigit() else None,
+                "power_w_max": max(power) if power else None, "samples": len(rows), "reasons": reasons}
+
+
+def synth_inputs(rank: int, n_pop: int):
+    """Seeded synthetic inputs of the microbenchmark's shapes (seed 1; ranks differ in x)."""
+    g = np.random.Generator(np.random.PCG64(1))
+    w = g.standard_normal((A_DIM, K_DIM), dtype=np.float32)   # param = Wᵀ, (a, k)
+    gx = np.random.Generator(np.random.PCG64(1000 + rank))
+    x = gx.standard_normal((n_pop, BM, K_DIM), dtype=np.float32)
+    return x, w
+
+
+def cpu_rate(oracle, x, w, target_seconds: float, first_thread: int = 0):
+    """Times the CPU restatement on a bounded sample of members; returns (evals/s, members, seconds)."""
+    probe = min(16, x.shape[0])
+    t0 = time.perf_counter()
+    oracle.perturbed_linear_lif(x[:probe], w, SIGMA, RANK, KEY, first_thread=first_thread, tau_m=TAU_M,
+                                v_th=V_TH, acc64=2)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    members = int(min(x.shape[0], max(probe, probe * target_seconds / dt)))
+    members -= members % 2
+    t0 = time.perf_counter()
+    oracle.perturbed_linear_lif(x[:members], w, SIGMA, RANK, KEY, first_thread=first_thread, tau_m=TAU_M,
+                                v_th=V_TH, acc64=2)
+    dt = time.perf_counter() - t0
+    return members * BM / dt, members, dt
+
+
+def config_dict(n_gpus: int):
+    return {"workload": "perturbed-linear microbench: x[8192,16,1024] fp32, W[1024,1024], rank 16, sigma 0.02, "
+                        "one LIF step (tau_m 20, v_th 0.3), spikes out",
+            "n_pop_per_gpu": N_POP, "bm": BM, "k": K_DIM, "a": A_DIM, "rank": RANK, "t_steps": 1,
+            "population_total": N_POP * n_gpus,
+            "l2_policy": "inputs (537 MB) and outputs (537 MB) exceed the 126 MB L2, no flush needed"}
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    # a bounded slice of the same workload: enough members for ~2 s of CPU work per step
+    x, w = synth_inputs(0, 512)
+    rates = []
+    members = secs = 0
+    for i in range(args.warmup + args.steps):
+        r, members, secs = cpu_rate(O, x, w, 2.0)
+        if i >= args.warmup:
+            rates.append((r, secs))
+    total_evals = sum(r * s for r, s in rates)
+    total_s = sum(s for _, s in rates)
+    value = total_evals / total_s
+    cores = O.num_threads()
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_s / max(len(rates), 1),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_dict(args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{members} of {N_POP} members per step ({members * BM} rows), "
+                                       "C restatement of the reference path, OpenMP over members"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+            "note": "the reference's Rust/Burn CPU path cannot be built on this box (no Rust toolchain); "
+                    "this is the timed CPU restatement"}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank: int, local_rank: int, world: int):
+    import torch
+    import torch.distributed as dist
+    from hyperscalees_b200 import core, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = core.get_context(local_rank)
+    peaks = measured_peaks()
+
+    x_np, w_np = synth_inputs(rank, N_POP)
+    x_host = torch.from_numpy(x_np).pin_memory()
+    w_dev = torch.from_numpy(w_np).to(dev)
+    x_dev = torch.empty_like(x_host, device=dev)
+    x_dev.copy_(x_host)
+    out_dev = torch.empty((N_POP * BM, A_DIM), dtype=torch.float32, device=dev)
+    out_host = torch.empty((N_POP * BM, A_DIM), dtype=torch.float32).pin_memory()
+    first_thread = rank * N_POP
+
+    def step():
+        ops.perturbed_linear(x_dev, w_dev, n_pop=N_POP, bm=BM, sigma=SIGMA, rank=RANK, key=KEY,
+                             first_thread=first_thread, lif=True, tau_m=TAU_M, v_th=V_TH, out=out_dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, iters):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ctx.profile_enable(False)
+    ms_total = timed(step, args.steps)
+    launches = sum(v[0] for v in ctx.profile_read().values())
+
+    # per-kernel device time over the same K steps, CUDA events on the launching stream
+    ctx.profile_enable(True)
+    timed(step, args.steps)
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+
+    # end to end through the public call with host buffers: H2D of the inputs, the step, D2H of the spikes
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        step()
+        out_host.copy_(out_dev, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if sampler else None
+
+    evals_per_step = N_POP * BM * world
+    value = evals_per_step * args.steps / (ms_total * 1e-3)
+    e2e_value = evals_per_step * args.steps / (ms_e2e * 1e-3)
+
+    if rank == 0:
+        top = max(prof.items(), key=lambda kv: kv[1][1])
+        top_name, (top_n, top_ms) = top
+        rows = N_POP * BM
+        # algorithmic work of one launch of the dominant kernel:
+        #   GEMM 2*rows*K*A plus the rank-r epilogue 2*rows*r*A (+ 2*rows*r*K when fused)
+        flops = 2.0 * rows * K_DIM * A_DIM + 2.0 * rows * RANK * A_DIM
+        if top_name.startswith("linear_tc"):
+            flops += 2.0 * rows * RANK * K_DIM
+        per_launch_s = top_ms * 1e-3 / top_n
+        achieved = flops / per_launch_s / 1e12
+        roofline = {"kernel": top_name, "bound": "tensor", "achieved": achieved,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "peak_source": f"{peaks['source']} bf16 cuBLAS burst; the kernel computes in fp32/TF32 "
+                                   "(nominal TF32 peak is half of bf16)",
+                    "traffic": None, "algorithmic_flops_per_launch": flops,
+                    "avg_launch_ms": per_launch_s * 1e3,
+                    "kernel_time_share": {k: round(v[1] / sum(p[1] for p in prof.values()), 4) for k, v in prof.items()}}
+        cpu = None
+        if world == 1:
+            from oracle import oracle as O
+            O.build()
+            r, members, secs = cpu_rate(O, x_np, w_np, 12.0)
+            cpu = {"value": r, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+                   "sample": f"{members} of {N_POP} members ({members * BM} rows, {secs:.1f} s), C restatement "
+                             "of the reference path, OpenMP over members"}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config_dict(world), "roofline": roofline, "cpu_baseline": cpu,
+                "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                        "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
+                "gpu_launches": int(launches), "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

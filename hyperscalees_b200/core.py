@@ -42,6 +42,19 @@ class Context:
         _lib.check(self._lib.hses_ctx_calibration_info(self.handle, C.byref(a), C.byref(b)))
         return int(a.value), int(b.value)
 
+    def profile_enable(self, timing: bool = True) -> None:
+        """Clear the launch counters; with timing, bracket every launch with CUDA events."""
+        _lib.check(self._lib.hses_profile_enable(self.handle, int(timing)))
+
+    def profile_read(self):
+        """{kernel name: (launches, total device ms)} since the last profile_enable."""
+        out = {}
+        for i in range(int(self._lib.hses_profile_count(self.handle))):
+            name, n, ms = C.c_char_p(), C.c_int64(), C.c_double()
+            _lib.check(self._lib.hses_profile_read(self.handle, i, C.byref(name), C.byref(n), C.byref(ms)))
+            out[name.value.decode()] = (int(n.value), float(ms.value))
+        return out
+
     def close(self):
         if self.handle:
             self._lib.hses_ctx_destroy(self.handle)

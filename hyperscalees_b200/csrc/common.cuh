@@ -6,6 +6,7 @@
 #include <stdio.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/hses.h"
 #include "rng.cuh"
@@ -29,12 +30,49 @@ struct DeviceTables {
 
 constexpr int kJumpLevels = 48;
 
+// Per-context launch counters and optional CUDA-event timing of every kernel
+// the library launches (hses_profile_* in the C ABI).
+struct KernelStat {
+    const char* name = nullptr;
+    int64_t launches = 0;
+    double ms = 0.0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;
+};
+struct Profiler {
+    bool timing = false;
+    std::vector<KernelStat> stats;
+    std::vector<cudaEvent_t> pool;
+    KernelStat& get(const char* name);
+    cudaEvent_t event();
+};
+struct KernelScope {
+    Profiler* prof;
+    KernelStat* stat;
+    cudaStream_t stream;
+    cudaEvent_t start = nullptr;
+    KernelScope(Profiler& p, cudaStream_t s, const char* name) : prof(&p), stat(&p.get(name)), stream(s) {
+        stat->launches++;
+        if (p.timing) {
+            start = p.event();
+            cudaEventRecord(start, s);
+        }
+    }
+    ~KernelScope() {
+        if (start) {
+            cudaEvent_t stop = prof->event();
+            cudaEventRecord(stop, stream);
+            stat->pending.emplace_back(start, stop);
+        }
+    }
+};
+
 }  // namespace hses
 
 struct hses_ctx {
     int device = 0;
     int sm_count = 0;
     hses::DeviceTables t;
+    hses::Profiler prof;
     hses::LibmCal cal() const {
         hses::LibmCal c;
         c.log_tab = t.log_tab;
@@ -63,6 +101,9 @@ struct hses_ctx {
             return HSES_ERR_INVALID;                              \
         }                                                         \
     } while (0)
+
+// Counts (and, when profiling is on, times) the kernel launched right after it.
+#define HSES_KERNEL(ctx, stream, name) hses::KernelScope hses_kernel_scope_((ctx)->prof, (stream), (name))
 
 #define HSES_LAUNCH_CHECK()                                                                 \
     do {                                                                                    \

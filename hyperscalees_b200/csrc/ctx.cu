@@ -12,6 +12,25 @@ namespace hses {
 static thread_local std::string g_last_error;
 void set_error(const std::string& msg) { g_last_error = msg; }
 
+KernelStat& Profiler::get(const char* name) {
+    for (auto& k : stats)
+        if (k.name == name || strcmp(k.name, name) == 0) return k;
+    stats.reserve(64);  // KernelStat references stay valid for the few dozen kernels that exist
+    stats.emplace_back();
+    stats.back().name = name;
+    return stats.back();
+}
+cudaEvent_t Profiler::event() {
+    if (!pool.empty()) {
+        cudaEvent_t e = pool.back();
+        pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
 // ---------------------------------------------------------------------------
 // xorshift64 as a linear map on GF(2)^64 (noiser.rs:449-455): column j of a
 // matrix is the image of the state with only bit j set.
@@ -173,6 +192,44 @@ int hses_ctx_create(int device, hses_ctx** out) {
 
 int hses_ctx_destroy(hses_ctx* ctx) {
     delete ctx;
+    return HSES_OK;
+}
+
+int hses_profile_enable(hses_ctx* ctx, int timing) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    for (auto& k : ctx->prof.stats) {
+        for (auto& pr : k.pending) {
+            cudaEventSynchronize(pr.second);
+            ctx->prof.pool.push_back(pr.first);
+            ctx->prof.pool.push_back(pr.second);
+        }
+        k.pending.clear();
+        k.launches = 0;
+        k.ms = 0.0;
+    }
+    ctx->prof.timing = timing != 0;
+    return HSES_OK;
+}
+
+int hses_profile_count(hses_ctx* ctx) { return ctx ? (int)ctx->prof.stats.size() : 0; }
+
+int hses_profile_read(hses_ctx* ctx, int index, const char** name, int64_t* launches,
+                      double* total_ms) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(index >= 0 && index < (int)ctx->prof.stats.size(), "index out of range");
+    KernelStat& k = ctx->prof.stats[index];
+    for (auto& pr : k.pending) {
+        HSES_CUDA(cudaEventSynchronize(pr.second));
+        float ms = 0.0f;
+        HSES_CUDA(cudaEventElapsedTime(&ms, pr.first, pr.second));
+        k.ms += ms;
+        ctx->prof.pool.push_back(pr.first);
+        ctx->prof.pool.push_back(pr.second);
+    }
+    k.pending.clear();
+    if (name) *name = k.name;
+    if (launches) *launches = k.launches;
+    if (total_ms) *total_ms = k.ms;
     return HSES_OK;
 }
 

@@ -273,10 +273,12 @@ int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs, i
     bool vec = (in_dim % 4 == 0) && (row_stride % 4 == 0) && aligned16(probs) && aligned16(out);
     if (vec) {
         int64_t total = batch * (in_dim / 4);
+        HSES_KERNEL(ctx, as_stream(stream), "poisson_encode");
         poisson_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
             probs, batch, in_dim, row_stride, T, mix, out);
     } else {
         int64_t total = batch * in_dim;
+        HSES_KERNEL(ctx, as_stream(stream), "poisson_encode");
         poisson_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
             probs, batch, in_dim, row_stride, T, mix, out);
     }
@@ -298,10 +300,12 @@ int hses_lif_scan(hses_ctx* ctx, hses_stream stream, const float* cur, int32_t T
                (v == nullptr || aligned16(v));
     if (vec) {
         int64_t total = n * (h / 4);
+        HSES_KERNEL(ctx, as_stream(stream), "lif_scan");
         lif_scan_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
             cur, T, n, h, row_stride, v, leak, v_th, reset_mode, spikes);
     } else {
         int64_t total = n * h;
+        HSES_KERNEL(ctx, as_stream(stream), "lif_scan");
         lif_scan_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
             cur, T, n, h, row_stride, v, leak, v_th, reset_mode, spikes);
     }
@@ -316,6 +320,7 @@ int hses_time_mean(hses_ctx* ctx, hses_stream stream, const float* x, int32_t T,
     if (n == 0) return HSES_OK;
     HSES_REQUIRE(x != nullptr && out != nullptr, "NULL pointer");
     int64_t total = n * h;
+    HSES_KERNEL(ctx, as_stream(stream), "time_mean");
     time_mean_kernel<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
         x, T, n, h, row_stride, out, out_row_stride);
     HSES_LAUNCH_CHECK();
@@ -329,6 +334,7 @@ int hses_fitness(hses_ctx* ctx, hses_stream stream, const float* logits, int64_t
     HSES_REQUIRE(reward == HSES_REWARD_LOGLIK || reward == HSES_REWARD_BINARY, "bad reward");
     if (n == 0) return HSES_OK;
     HSES_REQUIRE(logits != nullptr && labels != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "fitness");
     fitness_kernel<<<(unsigned)((n + 127) / 128), 128, 0, as_stream(stream)>>>(logits, n, classes,
                                                                              labels, reward, out);
     HSES_LAUNCH_CHECK();
@@ -341,6 +347,7 @@ int hses_member_mean(hses_ctx* ctx, hses_stream stream, const float* per_sample,
     HSES_REQUIRE(n_pop >= 0 && bm >= 1, "bad shape");
     if (n_pop == 0) return HSES_OK;
     HSES_REQUIRE(per_sample != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "member_mean");
     member_mean_kernel<<<(unsigned)((n_pop + 127) / 128), 128, 0, as_stream(stream)>>>(per_sample,
                                                                                      n_pop, bm, out);
     HSES_LAUNCH_CHECK();
@@ -354,6 +361,7 @@ int hses_convert_fitnesses(hses_ctx* ctx, hses_stream stream, const float* raw, 
     HSES_REQUIRE(group_size >= 0, "group_size must be >= 0");
     HSES_REQUIRE(group_size == 0 || n % group_size == 0, "n must be a multiple of group_size");
     HSES_REQUIRE(raw != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "zscore");
     zscore_kernel<<<1, kZThreads, 0, as_stream(stream)>>>(raw, n, group_size, out, stats);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
@@ -388,6 +396,7 @@ int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solve
         c.ibc1 = 1.0f / bc1;
         c.ibc2 = 1.0f / bc2;
     }
+    HSES_KERNEL(ctx, as_stream(stream), "solver");
     solver_kernel<<<(unsigned)((len + 255) / 256), 256, 0, as_stream(stream)>>>(c, param, grad, m, v, len);
     HSES_LAUNCH_CHECK();
     return HSES_OK;

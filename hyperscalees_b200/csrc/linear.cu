@@ -218,6 +218,7 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         int rc = launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse),
                                      ep.first_pair, pairs, g.rank, g.a, g.k, nullptr, s.A, s.B);
         if (rc != HSES_OK) return rc;
+        HSES_KERNEL(ctx, st, "lowrank_project");
         lowrank_project_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
             g.x, rows, g.bm, g.n_pop, g.k, g.x_row_stride, g.rank, g.first_thread, ep.first_pair,
             s.B, s.t);
@@ -227,6 +228,7 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     HSES_REQUIRE(row_tiles <= 65535ll * 32768ll, "too many rows");
     HSES_REQUIRE(row_tiles <= 65535, "too many rows for the SIMT path (rows/128 must be <= 65535)");
     dim3 grid((unsigned)((g.a + TN - 1) / TN), (unsigned)row_tiles);
+    HSES_KERNEL(ctx, st, "linear_simt");
     linear_simt_kernel<<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a,
                                             g.param_row_stride, ep);
     HSES_LAUNCH_CHECK();

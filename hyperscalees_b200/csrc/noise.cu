@@ -127,6 +127,7 @@ int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_
     HSES_REQUIRE((rows + 127) / 128 <= 65535, "a + b too large");
     HSES_REQUIRE(pairs >= 1 && pairs < (1ll << 31), "pair count out of range");
     dim3 grid((unsigned)pairs, (unsigned)((rows + 127) / 128));
+    HSES_KERNEL(ctx, stream, "pair_factors");
     pair_factors_kernel<<<grid, 128, 0, stream>>>(ctx->cal(), ctx->t.jump_pow2, key, true_epoch,
                                                   first_pair, pairs, rank, a, b, pair_weight, A, B);
     HSES_LAUNCH_CHECK();
@@ -146,6 +147,7 @@ int hses_normal_fill(hses_ctx* ctx, hses_stream stream, uint64_t seed, float* ou
     HSES_REQUIRE(n < (1ull << 40), "n too large");
     size_t chunks = (n + kChunk - 1) / kChunk;
     unsigned blocks = (unsigned)((chunks + 127) / 128);
+    HSES_KERNEL(ctx, as_stream(stream), "normal_fill");
     normal_fill_kernel<<<blocks, 128, 0, as_stream(stream)>>>(ctx->cal(), ctx->t.jump_pow2, seed, out, n);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
@@ -165,6 +167,7 @@ int hses_lora_factors(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t e
     int rows = a + b;
     HSES_REQUIRE((rows + 127) / 128 <= 65535, "a + b too large");
     dim3 grid((unsigned)n_members, (unsigned)((rows + 127) / 128));
+    HSES_KERNEL(ctx, as_stream(stream), "lora_factors");
     lora_factors_kernel<<<grid, 128, 0, as_stream(stream)>>>(
         ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), thread_ids,
         first_thread, n_members, rank, a, b, base_sigma, layout, A, B);
@@ -184,6 +187,7 @@ int hses_dense_noise(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t ep
     int len = rows * cols;
     int chunks = (len + kChunk - 1) / kChunk;
     dim3 grid((unsigned)n_members, (unsigned)((chunks + 63) / 64));
+    HSES_KERNEL(ctx, as_stream(stream), "dense_noise");
     dense_noise_kernel<<<grid, 64, 0, as_stream(stream)>>>(
         ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), thread_ids,
         first_thread, n_members, len, base_sigma, out);
@@ -204,6 +208,7 @@ int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_
     float nf = (float)n_total;
     float out_scale = -(1.0f / nf) * sqrtf(nf);
     int blocks = (len + kChunk - 1) / kChunk;
+    HSES_KERNEL(ctx, as_stream(stream), "es_update_dense");
     es_update_dense_kernel<<<blocks, kDenseThreads, 0, as_stream(stream)>>>(
         ctx->cal(), ctx->t.jump_pow2, key, true_epoch_of(epoch, noise_reuse), first_thread / 2,
         n / 2, len, sigma, out_scale, fitness, grad);

@@ -151,6 +151,7 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
         int rc = launch_pair_factors(ctx, st, key, te, first_thread / 2 + (int32_t)done, cnt, rank, a,
                                      b, fitness + 2 * done, wsA, wsB);
         if (rc != HSES_OK) return rc;
+        HSES_KERNEL(ctx, st, "update_gemm");
         update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, partial);
         HSES_LAUNCH_CHECK();
     }
@@ -158,6 +159,7 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
     float nf = (float)n_total;
     float scale = -((sigma / sqrtf((float)rank)) * (1.0f / nf)) * sqrtf(nf);
     size_t len = (size_t)a * b;
+    HSES_KERNEL(ctx, st, "update_reduce");
     update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
                                                                        grad);
     HSES_LAUNCH_CHECK();

@@ -63,6 +63,19 @@ int hses_ctx_destroy(hses_ctx* ctx);
  * rounded value (diagnostic; tests compare it with their own count). */
 int hses_ctx_calibration_info(const hses_ctx* ctx, uint64_t* log_flips, uint64_t* cos_flips);
 
+/* ---- launch accounting.  Every kernel the library launches is counted per
+ *      context; with timing on, each launch is also bracketed by CUDA events
+ *      on the launching stream.  hses_profile_enable clears the counters;
+ *      hses_profile_read waits for the recorded events of entry `index`
+ *      (0 .. hses_profile_count()-1) and returns its name, launch count and
+ *      summed device time.  The reference's closest facility is the
+ *      ACC_TIMING / ACC_PHASE wall-clock switches of
+ *      hyperscalees/src/bin/accumulate_train.rs:722-768. -------------------- */
+int hses_profile_enable(hses_ctx* ctx, int timing);
+int hses_profile_count(hses_ctx* ctx);
+int hses_profile_read(hses_ctx* ctx, int index, const char** name, int64_t* launches,
+                      double* total_ms);
+
 /* ---- seed hash: noise_seed, hyperscalees-noiser/src/noiser.rs:495-506 ---- */
 uint64_t hses_noise_seed(uint64_t key, int32_t true_epoch, int32_t true_thread);
 

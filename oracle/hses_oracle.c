@@ -138,6 +138,22 @@ static inline float dot_f64(const float *p, const float *q, int n, int sp, int s
     return (float)acc;
 }
 
+/* Baseline-timing variant of the dot product: sixteen independent partial
+ * sums so the compiler can keep SIMD lanes busy (a tuned CPU GEMM, which the
+ * reference's CPU backend uses, does not accumulate strictly in index order
+ * either).  Selected with acc mode 2; parity checks use modes 0 and 1. */
+__attribute__((target_clones("avx512f", "avx2", "default")))
+static float dot_fast(const float *p, const float *q, int n) {
+    float acc[16] = {0};
+    int i = 0;
+    for (; i + 16 <= n; i += 16)
+        for (int j = 0; j < 16; ++j) acc[j] += p[i + j] * q[i + j];
+    float s = 0.0f;
+    for (int j = 0; j < 16; ++j) s += acc[j];
+    for (; i < n; ++i) s += p[i] * q[i];
+    return s;
+}
+
 /* y = x·paramᵀ + (x·B)·Aᵀ with pre-generated factors; evaluation order of
  * eggroll.rs:427,443: base first, then t = x·B, u = t·Aᵀ, y = base + u. */
 static void mm_with_factors(const float *x, int bm, const float *param, int a, int b,
@@ -148,16 +164,17 @@ static void mm_with_factors(const float *x, int bm, const float *param, int a, i
         for (int m = 0; m < bm; ++m)
             for (int q = 0; q < rank; ++q)
                 t[(size_t)m * rank + q] =
-                    acc64 ? dot_f64(x + (size_t)m * b, B + q, b, 1, rank)
-                          : dot_f32(x + (size_t)m * b, B + q, b, 1, rank);
+                    acc64 == 1 ? dot_f64(x + (size_t)m * b, B + q, b, 1, rank)
+                               : dot_f32(x + (size_t)m * b, B + q, b, 1, rank);
     }
     for (int m = 0; m < bm; ++m) {
         for (int n = 0; n < a; ++n) {
-            float base = acc64 ? dot_f64(x + (size_t)m * b, param + (size_t)n * b, b, 1, 1)
-                               : dot_f32(x + (size_t)m * b, param + (size_t)n * b, b, 1, 1);
+            float base = acc64 == 2 ? dot_fast(x + (size_t)m * b, param + (size_t)n * b, b)
+                         : acc64 ? dot_f64(x + (size_t)m * b, param + (size_t)n * b, b, 1, 1)
+                                 : dot_f32(x + (size_t)m * b, param + (size_t)n * b, b, 1, 1);
             if (A) {
-                float u = acc64 ? dot_f64(t + (size_t)m * rank, A + (size_t)n * rank, rank, 1, 1)
-                                : dot_f32(t + (size_t)m * rank, A + (size_t)n * rank, rank, 1, 1);
+                float u = acc64 == 1 ? dot_f64(t + (size_t)m * rank, A + (size_t)n * rank, rank, 1, 1)
+                                     : dot_f32(t + (size_t)m * rank, A + (size_t)n * rank, rank, 1, 1);
                 base = base + u;
             }
             y[(size_t)m * a + n] = base;

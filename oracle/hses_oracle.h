@@ -51,9 +51,10 @@ void hso_nonlora_params(float base_sigma, uint64_t key, int32_t epoch,
                         int32_t noise_reuse, float *out);
 
 /* ---- perturbed linear (eggroll.rs:419-446) ----------------------------- */
-/* y(bm,a) = x(bm,b)·paramᵀ + (x·B)·Aᵀ ; iter==0 -> clean.  acc64!=0
- * accumulates every dot product in double (used to locate near-threshold
- * elements), otherwise fp32 in index order. */
+/* y(bm,a) = x(bm,b)·paramᵀ + (x·B)·Aᵀ ; iter==0 -> clean.  acc64 selects the
+ * accumulation of the dot products: 0 = fp32 in index order, 1 = double (used
+ * to locate near-threshold elements), 2 = fp32 with SIMD-friendly partial sums
+ * for the base product (CPU-baseline timing only). */
 void hso_do_mm(const float *x, int bm, const float *param, int a, int b,
                float sigma, int rank, uint64_t key, int has_iter, int32_t epoch,
                int32_t thread_id, int32_t noise_reuse, int acc64, float *y);

@@ -1,0 +1,102 @@
+"""End-to-end parity of the SNN population step (encode -> perturbed layers ->
+LIF -> readout -> fitness -> z-score -> update -> solver) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.as_tensor(np.ascontiguousarray(a), device="cuda")
+
+
+def synth(n_samples, seed=0):
+    g = np.random.Generator(np.random.PCG64(seed))
+    img = g.random((n_samples, 784), dtype=np.float32)
+    img[g.random((n_samples, 784)) < 0.8] = 0.0
+    labels = g.integers(0, 10, n_samples).astype(np.int32)
+    return img, labels
+
+
+@pytest.mark.parametrize("dims,tau_m,v_th,reset", [
+    ([784, 128, 128, 10], 20.0, 0.3, 0),       # the reference's two-hidden-layer model
+    ([784, 128, 128, 128, 10], 2.0, 1.0, 1),   # three hidden layers, subtractive reset
+    ([784, 32, 10], 1.0, 0.3, 0),              # smoke-test regime (snn_mnist_train.rs:119-120)
+])
+def test_population_forward_matches_oracle(hs, oracle, dims, tau_m, v_th, reset):
+    from hyperscalees_b200 import models, noiser, ops
+    n_pop, bm, T, rank, sigma = 6, 4, 8, 4, 0.05
+    img, labels = synth(n_pop * bm)
+    seeds = [1, 2, 3, 4]
+    net = models.SnnMlp(dims, tau_m=tau_m, v_th=v_th, reset_mode=reset, seed=0)
+    # boost the weights so that hidden layers actually fire with tau_m = 20
+    net.weights = [w * (8.0 if tau_m > 1.5 else 1.0) for w in net.weights]
+    keys = models.default_base_keys(len(dims))
+    frozen, nz = noiser.init_noiser(net.params(), sigma, 0.01, 0, False, 0, rank, noiser.Solver.sgd(0.01))
+    spikes = ops.poisson_encode(dev(img), T, seeds)
+    want_spk = oracle.poisson_encode(img, T, seeds)
+    assert torch.equal(spikes.cpu(), torch.from_numpy(want_spk))
+    logits, hidden = net.forward_population(spikes.reshape(T, n_pop, bm, 784), frozen, nz, keys, epoch=0,
+                                            first_thread=0, want_hidden=True)
+    om = oracle.Snn([w.cpu().numpy() for w in net.weights], keys, 1.0, tau_m, v_th, None, reset, sigma, rank, 0)
+    tot = mism = 0
+    for i in range(n_pop):
+        xs = want_spk[:, i * bm:(i + 1) * bm, :]
+        wl, wh = om.forward(xs, (0, i), want_hidden=True)
+        gh = hidden[:, i * bm:(i + 1) * bm, :].cpu().numpy()
+        mism += int((gh != wh).sum())
+        tot += wh.size
+        if (gh == wh).all():
+            gl = logits[i * bm:(i + 1) * bm].cpu().numpy()
+            assert np.abs(gl - wl).max() <= 1e-4 * max(1.0, np.abs(wl).max())
+    assert mism / tot <= 1e-4
+    assert 0.005 < hidden.mean().item() < 0.9  # the network is neither silent nor saturated
+
+
+def test_snn_model_forward_is_clean_and_reproducible(hs):
+    # hyperscalees-models/src/snn.rs:784-800: the clean forward is deterministic
+    from hyperscalees_b200 import models
+    net = models.SnnModel(784, 128, 128, 10)
+    x = (torch.rand(8, 5, 784, device="cuda") < 0.2).float()
+    a, b = net.forward(x), net.forward(x)
+    assert a.shape == (5, 10) and torch.equal(a, b)
+
+
+def test_population_step_moves_parameters_like_oracle(hs, oracle):
+    """One full ES step on a small population: parameters after the step match
+    the oracle's (fitness within 1e-3 relative, update within 1e-3 relative)."""
+    from hyperscalees_b200 import envs, models, noiser, ops
+    dims, n_pop, bm, T, rank, sigma, lr = [784, 64, 32, 10], 16, 2, 8, 4, 0.1, 0.05
+    img, labels = synth(n_pop * bm, seed=3)
+    seeds = [9, 8, 7, 6]
+    net = models.SnnMlp(dims, tau_m=1.0, v_th=0.3, seed=1)
+    keys = models.default_base_keys(len(dims))
+    frozen, nz = noiser.init_noiser(net.params(), sigma, lr, 0, False, 0, rank, noiser.Solver.adamw(lr))
+    spikes = ops.poisson_encode(dev(img), T, seeds).reshape(T, n_pop, bm, 784)
+    logits = net.forward_population(spikes, frozen, nz, keys)
+    per_sample = envs.fitness_from_logits_reward(logits, dev(labels), envs.Loglik)
+    raw = ops.member_mean(per_sample, n_pop, bm)
+    fit = noiser.EggRoll().convert_fitnesses(frozen, nz, raw)
+    infos = [noiser.IterInfo(0, i) for i in range(n_pop)]
+    new_params = noiser.EggRoll().do_updates(frozen, nz, net.params(), keys, fit, infos, net.es_map())
+
+    om = oracle.Snn([w.cpu().numpy() for w in net.weights], keys, 1.0, 1.0, 0.3, None, 0, sigma, rank, 0)
+    spk = oracle.poisson_encode(img, T, seeds)
+    oraw = np.empty(n_pop, np.float32)
+    for i in range(n_pop):
+        lg = om.forward(spk[:, i * bm:(i + 1) * bm], (0, i))
+        oraw[i] = oracle.fitness(lg, labels[i * bm:(i + 1) * bm]).sum(dtype=np.float32) / np.float32(bm)
+    assert np.allclose(raw.cpu().numpy(), oraw, rtol=1e-3, atol=1e-4)
+    ofit = oracle.convert_fitnesses(oraw)
+    for p, np_, key, cls in zip(net.params(), new_params, keys, net.es_map()):
+        a, b = p.shape
+        if cls == 1:
+            grad = oracle.lora_grad(sigma, key, a, b, rank, ofit, [0] * n_pop, list(range(n_pop)))
+        else:
+            grad = oracle.full_grad(sigma, key, a, b, ofit, [0] * n_pop, list(range(n_pop)))
+        want, _, _ = oracle.solver_update(oracle.ADAMW, 1, p.cpu().numpy(), grad, lr=lr, weight_decay=1e-4)
+        got = np_.cpu().numpy()
+        assert np.abs(got - p.cpu().numpy()).max() > 0  # the step moved the parameter
+        assert np.abs(got - want).max() <= 1e-3 * np.abs(want - p.cpu().numpy()).max() + 1e-6
+    assert nz.opt_state.step == 1

@@ -1,0 +1,59 @@
+"""Parity of the fitness-weighted update with the CPU oracle (rtol 1e-3, fp32 accumulate)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+KEY = 0xDAA66D2C7DDF743F
+
+
+def dev(a):
+    return torch.as_tensor(np.ascontiguousarray(a), device="cuda")
+
+
+@pytest.mark.parametrize("a,b,rank,n,first", [
+    (2, 2, 1, 2, 0), (128, 784, 4, 64, 0), (10, 128, 8, 30, 4), (130, 70, 3, 18, 2), (48, 48, 16, 256, 0),
+])
+def test_es_update_matches_oracle(hs, oracle, a, b, rank, n, first):
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(n + a)
+    f = g.standard_normal(n).astype(np.float32)
+    got = ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), first_thread=first).cpu().numpy()
+    want = oracle.lora_grad(0.2, KEY, a, b, rank, f, [5] * n, list(range(first, first + n)), 2)
+    assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max()
+
+
+def test_es_update_is_deterministic(hs):
+    from hyperscalees_b200 import ops
+    f = torch.randn(512, device="cuda")
+    g1 = ops.es_update(KEY, 0, 0, 8, 64, 96, 0.1, f)
+    g2 = ops.es_update(KEY, 0, 0, 8, 64, 96, 0.1, f)
+    assert torch.equal(g1, g2)
+
+
+def test_es_update_shards_sum_to_whole(hs):
+    # a population split across ranks: partial gradients with n_total = N add up
+    from hyperscalees_b200 import ops
+    f = torch.randn(128, device="cuda")
+    whole = ops.es_update(KEY, 0, 0, 4, 32, 40, 0.1, f)
+    parts = sum(ops.es_update(KEY, 0, 0, 4, 32, 40, 0.1, f[i:i + 32].contiguous(), first_thread=i, n_total=128)
+                for i in range(0, 128, 32))
+    assert torch.allclose(whole, parts, rtol=1e-4, atol=1e-6)
+
+
+def test_antithetic_pair_with_equal_fitness_cancels(hs):
+    from hyperscalees_b200 import ops
+    f = torch.tensor([0.7, 0.7, -1.2, -1.2], device="cuda")
+    assert ops.es_update(KEY, 0, 0, 4, 16, 16, 0.3, f).abs().max().item() == 0.0
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (2, 1), (3, 17)])
+def test_es_update_dense_matches_oracle(hs, oracle, shape):
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(shape[1])
+    n = 40
+    f = g.standard_normal(n).astype(np.float32)
+    got = ops.es_update_dense(KEY, 1, 0, shape, 0.3, dev(f), first_thread=2).cpu().numpy()
+    want = oracle.full_grad(0.3, KEY, shape[0], shape[1], f, [1] * n, list(range(2, 2 + n)), 0)
+    assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max() + 1e-7
