@@ -201,7 +201,7 @@ int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
                  "members must form whole antithetic pairs");
-    HSES_REQUIRE(n_total >= n, "n_total < n");
+    HSES_REQUIRE(n_total >= 1, "n_total must be >= 1");
     HSES_REQUIRE(len >= 1 && len <= (1 << 20), "len out of range");
     HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");
     // grad = -( (sum/N) * sqrt(N) ), eggroll.rs:349,402-403

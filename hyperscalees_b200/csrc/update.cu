@@ -131,7 +131,7 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
                  "members must form whole antithetic pairs");
-    HSES_REQUIRE(n_total >= n, "n_total < n");
+    HSES_REQUIRE(n_total >= 1, "n_total must be >= 1");
     HSES_REQUIRE(rank >= 1 && rank <= 1024 && a >= 1 && b >= 1, "bad shape");
     HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
     HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");

@@ -217,7 +217,7 @@ class Snn:
         dims = [ws[0].shape[1]] + [w.shape[0] for w in ws]
         dims_c = (C.c_int * len(dims))(*dims)
         wp = (_f32p * len(ws))(*[w.ctypes.data_as(_f32p) for w in ws])
-        keys = (C.c_uint64 * len(ws))(*[int(k) & (2**64 - 1) for k in self.keys])
+        keys = (C.c_uint64 * len(ws))(*[int(k) & (2**64 - 1) for k in list(self.keys)[:len(ws)]])
         vl = None
         if self.v_th_layer is not None:
             vl = (C.c_float * len(self.v_th_layer))(*self.v_th_layer)
