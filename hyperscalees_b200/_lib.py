@@ -22,7 +22,8 @@ EXPORTS = [
     "hses_dense_noise", "hses_poisson_encode", "hses_lif_scan",
     "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
     "hses_member_mean", "hses_convert_fitnesses", "hses_es_update_workspace_bytes",
-    "hses_es_update", "hses_es_update_dense", "hses_solver_step",
+    "hses_es_update", "hses_es_update_static_scratch_bytes", "hses_es_update_static",
+    "hses_es_update_dense", "hses_solver_step",
 ]
 
 
@@ -90,6 +91,9 @@ def load():
     L.hses_es_update_workspace_bytes.restype = sz
     L.hses_es_update_workspace_bytes.argtypes = [i32, i32, i32, i64]
     L.hses_es_update.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp, vp, sz]
+    L.hses_es_update_static_scratch_bytes.restype = sz
+    L.hses_es_update_static_scratch_bytes.argtypes = []
+    L.hses_es_update_static.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp]
     L.hses_es_update_dense.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, f32, vp, vp]
     L.hses_solver_step.argtypes = [vp, vp, C.POINTER(SolverDesc), i32, f32, vp, vp, vp, vp, i64]
     for name in EXPORTS:

@@ -10,6 +10,9 @@
 // scratch (A pre-multiplied by the pair weight), a split-K fp32 GEMM writes
 // per-split partial sums, and a final pass adds the partials in a fixed order
 // so that every rank ends up with bit-identical gradients.
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace hses {
@@ -113,6 +116,65 @@ __global__ void update_reduce_kernel(const float* __restrict__ partial, int spli
     grad[i] = __fmul_rn(s, scale);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant: the scratch of the update lives in a fixed array in
+// device memory that is part of the library image.  In host code the array's
+// name only stands in for the symbol; its device address is looked up once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels get.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = 16ull << 20;
+static __device__ __align__(256) unsigned char g_static_update_scratch[kStaticScratchBytes];
+
+static std::mutex g_static_mutex;
+static std::map<int, float*> g_static_ptr;  // device ordinal -> address of the array on that device
+
+static int static_scratch_for_device(int device, float** out) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    auto it = g_static_ptr.find(device);
+    if (it != g_static_ptr.end()) {
+        *out = it->second;
+        return HSES_OK;
+    }
+    int current = -1;
+    HSES_CUDA(cudaGetDevice(&current));
+    HSES_REQUIRE(current == device, "the context's device must be the current CUDA device");
+    void* ptr = nullptr;
+    HSES_CUDA(cudaGetSymbolAddress(&ptr, g_static_update_scratch));
+    HSES_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned NULL");
+    g_static_ptr[device] = reinterpret_cast<float*>(ptr);
+    *out = reinterpret_cast<float*>(ptr);
+    return HSES_OK;
+}
+
+// Splits the fixed array into per-split partial sums and one chunk of factors.
+static bool plan_update_static(int a, int b, int rank, int64_t n, UpdatePlan* out) {
+    UpdatePlan p;
+    p.pairs = n / 2;
+    auto up = [](size_t v) { return (v + 63) / 64 * 64; };
+    size_t budget = kStaticScratchBytes / sizeof(float);
+    size_t per_pair = (size_t)(a + b) * rank;
+    size_t ab = (size_t)a * b;
+    int tiles = ((a + UM - 1) / UM) * ((b + UN - 1) / UN);
+    int splits = (2 * 148 + tiles - 1) / tiles;
+    if (splits > 16) splits = 16;
+    // partial sums may take at most half of the array; the rest holds factors
+    while (splits > 1 && up((size_t)splits * ab) > budget / 2) --splits;
+    if (up((size_t)splits * ab) + 2 * 64 + per_pair > budget) return false;
+    size_t left = budget - up((size_t)splits * ab) - 2 * 64;
+    int64_t fit = (int64_t)(left / per_pair);
+    if (fit < 1) return false;
+    p.chunk_pairs = p.pairs < fit ? p.pairs : fit;
+    if (splits > p.chunk_pairs) splits = (int)p.chunk_pairs;
+    p.splits = splits;
+    p.a_elems = up((size_t)p.chunk_pairs * a * rank);
+    p.b_elems = up((size_t)p.chunk_pairs * b * rank);
+    p.partial_elems = up((size_t)p.splits * ab);
+    p.bytes = (p.a_elems + p.b_elems + p.partial_elems) * sizeof(float);
+    if (p.bytes > kStaticScratchBytes) return false;
+    *out = p;
+    return true;
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -156,6 +218,59 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
         HSES_LAUNCH_CHECK();
     }
     // grad = -( (sum * base_sigma / N) * sqrt(N) ), eggroll.rs:365-372, 402-403
+    float nf = (float)n_total;
+    float scale = -((sigma / sqrtf((float)rank)) * (1.0f / nf)) * sqrtf(nf);
+    size_t len = (size_t)a * b;
+    HSES_KERNEL(ctx, st, "update_reduce");
+    update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
+                                                                       grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+size_t hses_es_update_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                          int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                          int32_t rank, int32_t a, int32_t b, float sigma, const float* fitness,
+                          float* grad) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
+                 "members must form whole antithetic pairs");
+    HSES_REQUIRE(n_total >= 1, "n_total must be >= 1");
+    HSES_REQUIRE(rank >= 1 && rank <= 1024 && a >= 1 && b >= 1, "bad shape");
+    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
+    HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");
+    HSES_REQUIRE((a + UM - 1) / UM <= 65535, "a too large");
+    UpdatePlan p;
+    if (!plan_update_static(a, b, rank, n, &p)) {
+        set_error("hses_es_update_static: a=" + std::to_string(a) + ", b=" + std::to_string(b) +
+                  ", rank=" + std::to_string(rank) + " does not fit the built-in scratch of " +
+                  std::to_string(kStaticScratchBytes) + " bytes (partial sums plus the factors of "
+                  "one antithetic pair must fit); use hses_es_update with a caller workspace");
+        return HSES_ERR_INVALID;
+    }
+    float* base = nullptr;
+    int rc = static_scratch_for_device(ctx->device, &base);
+    if (rc != HSES_OK) return rc;
+    cudaStream_t st = as_stream(stream);
+    float* wsA = base;
+    float* wsB = wsA + p.a_elems;
+    float* partial = wsB + p.b_elems;
+    int32_t te = true_epoch_of(epoch, noise_reuse);
+    dim3 grid((unsigned)((b + UN - 1) / UN), (unsigned)((a + UM - 1) / UM), (unsigned)p.splits);
+    int chunk_idx = 0;
+    for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
+        int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
+        rc = launch_pair_factors(ctx, st, key, te, first_thread / 2 + (int32_t)done, cnt, rank, a, b,
+                                 fitness + 2 * done, wsA, wsB);
+        if (rc != HSES_OK) return rc;
+        HSES_KERNEL(ctx, st, "update_gemm");
+        // the first chunk overwrites the partial sums, so nothing left behind by an
+        // earlier call is read
+        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, partial);
+        HSES_LAUNCH_CHECK();
+    }
     float nf = (float)n_total;
     float scale = -((sigma / sqrtf((float)rank)) * (1.0f / nf)) * sqrtf(nf);
     size_t len = (size_t)a * b;

@@ -194,6 +194,33 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
                    const float* fitness /*device*/, float* grad /*device (a,b) dense*/,
                    void* workspace /*device*/, size_t workspace_bytes);
 
+/* ---- hses_es_update for callers that cannot hand over a workspace.  It has
+ *      no counterpart in the reference.  Some hosts of this library never get
+ *      to call cudaMalloc themselves: a plugin running inside another runtime's
+ *      memory pool, a process whose device memory is fully pre-partitioned, or a
+ *      step that must not touch the allocator because it would synchronise the
+ *      device.  For them the scratch (factor chunk + split-K partial sums) is a
+ *      fixed array of hses_es_update_static_scratch_bytes() = 16 MiB that is
+ *      part of the library's device image, so every GPU that loads the library
+ *      carries it until the process exits.  The call allocates nothing and
+ *      frees nothing.  Limits and rules:
+ *        - the partial sums (a*b floats per split) plus the factors of at least
+ *          one antithetic pair ((a+b)*rank floats) must fit in the array,
+ *          otherwise HSES_ERR_INVALID is returned with a message;
+ *        - the first call on a device looks up the array's device address (the
+ *          context's device must be current); make that first call before any
+ *          stream capture begins;
+ *        - all calls share the one array: it keeps whatever the last call left,
+ *          nothing in it needs clearing beforehand (the first chunk overwrites
+ *          the partial sums), and two calls that overlap on the GPU (different
+ *          streams, or different contexts on one device) race on it.
+ *      Results equal hses_es_update up to the fp32 summation order. --------- */
+size_t hses_es_update_static_scratch_bytes(void);
+int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                          int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
+                          int32_t rank, int32_t a, int32_t b, float sigma,
+                          const float* fitness /*device*/, float* grad /*device (a,b) dense*/);
+
 /* ---- simple_full_update + do_update_with, eggroll.rs:331-350, 384-404, for
  *      dense (PARAM-class) leaves of `len` = rows*cols elements. ----------- */
 int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
