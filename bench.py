@@ -235,10 +235,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         top_name, (top_n, top_ms) = top
         rows = N_POP * BM
         # algorithmic work of one launch of the dominant kernel:
-        #   GEMM 2*rows*K*A plus the rank-r epilogue 2*rows*r*A (+ 2*rows*r*K when fused)
+        #   GEMM 2*rows*K*A plus the rank-r epilogue 2*rows*r*A
         flops = 2.0 * rows * K_DIM * A_DIM + 2.0 * rows * RANK * A_DIM
-        if top_name.startswith("linear_tc"):
-            flops += 2.0 * rows * RANK * K_DIM
         per_launch_s = top_ms * 1e-3 / top_n
         achieved = flops / per_launch_s / 1e12
         roofline = {"kernel": top_name, "bound": "tensor", "achieved": achieved,

@@ -17,7 +17,7 @@ c_i32p = C.POINTER(C.c_int32)
 # every symbol include/hses.h declares, in declaration order
 EXPORTS = [
     "hses_last_error", "hses_version", "hses_ctx_create", "hses_ctx_destroy",
-    "hses_ctx_calibration_info", "hses_profile_enable", "hses_profile_count", "hses_profile_read",
+    "hses_ctx_calibration_info", "hses_ctx_device_status", "hses_profile_enable", "hses_profile_count", "hses_profile_read",
     "hses_noise_seed", "hses_normal_fill", "hses_lora_factors",
     "hses_dense_noise", "hses_poisson_encode", "hses_lif_scan",
     "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
@@ -71,6 +71,7 @@ def load():
     L.hses_ctx_create.argtypes = [C.c_int, C.POINTER(vp)]
     L.hses_ctx_destroy.argtypes = [vp]
     L.hses_ctx_calibration_info.argtypes = [vp, C.POINTER(u64), C.POINTER(u64)]
+    L.hses_ctx_device_status.argtypes = [vp, C.POINTER(C.c_int)]
     L.hses_profile_enable.argtypes = [vp, C.c_int]
     L.hses_profile_count.argtypes = [vp]
     L.hses_profile_read.argtypes = [vp, C.c_int, C.POINTER(C.c_char_p), C.POINTER(i64), C.POINTER(C.c_double)]

@@ -42,6 +42,12 @@ class Context:
         _lib.check(self._lib.hses_ctx_calibration_info(self.handle, C.byref(a), C.byref(b)))
         return int(a.value), int(b.value)
 
+    def device_status(self) -> int:
+        """Synchronises and returns the code a kernel left when a bounded wait ran out (0 = none)."""
+        st = C.c_int()
+        _lib.check(self._lib.hses_ctx_device_status(self.handle, C.byref(st)))
+        return int(st.value)
+
     def profile_enable(self, timing: bool = True) -> None:
         """Clear the launch counters; with timing, bracket every launch with CUDA events."""
         _lib.check(self._lib.hses_profile_enable(self.handle, int(timing)))

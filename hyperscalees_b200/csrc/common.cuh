@@ -26,7 +26,13 @@ struct DeviceTables {
     uint64_t n_log_flips = 0, n_cos_flips = 0;
     // generator jump tables: entry k advances the state by 2^k steps
     uint64_t* jump_pow2 = nullptr;  // kJumpLevels matrices
+    // one int per device: kernels with bounded waits record here why they gave up
+    int* status_word = nullptr;
 };
+
+// Nibble table (kJumpWords uint64) that advances the generator by `distance`
+// steps, built on first use and cached per device.
+int get_hop_table(hses_ctx* ctx, uint64_t distance, const uint64_t** dev_tab);
 
 constexpr int kJumpLevels = 48;
 

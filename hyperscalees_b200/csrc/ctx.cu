@@ -81,12 +81,53 @@ __global__ void candidates_kernel(const double2* __restrict__ log_tab, int which
 static std::mutex g_tables_mutex;
 static std::map<int, std::shared_ptr<DeviceTables>> g_tables;
 
+// host copies of T^(2^k) and the per-device cache of composed hop tables
+static std::vector<BitMat> g_pow2_host;
+static std::mutex g_hop_mutex;
+static std::map<std::pair<int, uint64_t>, uint64_t*> g_hop_tables;
+
+static void ensure_pow2_host() {
+    if (!g_pow2_host.empty()) return;
+    BitMat m = step_matrix();
+    for (int k = 0; k < kJumpLevels; ++k) {
+        g_pow2_host.push_back(m);
+        m = compose(m, m);
+    }
+}
+
+int get_hop_table(hses_ctx* ctx, uint64_t distance, const uint64_t** dev_tab) {
+    std::lock_guard<std::mutex> lock(g_hop_mutex);
+    auto key = std::make_pair(ctx->device, distance);
+    auto it = g_hop_tables.find(key);
+    if (it != g_hop_tables.end()) {
+        *dev_tab = it->second;
+        return HSES_OK;
+    }
+    HSES_REQUIRE(distance < (1ull << kJumpLevels), "hop distance too large");
+    ensure_pow2_host();
+    BitMat m;
+    for (int j = 0; j < 64; ++j) m.col[j] = 1ull << j;  // identity
+    for (int k = 0; k < kJumpLevels; ++k)
+        if ((distance >> k) & 1) m = compose(g_pow2_host[k], m);
+    uint64_t host[kJumpWords];
+    nibble_table(m, host);
+    uint64_t* dev = nullptr;
+    HSES_CUDA(cudaMalloc(&dev, sizeof(host)));
+    HSES_CUDA(cudaMemcpy(dev, host, sizeof(host), cudaMemcpyHostToDevice));
+    g_hop_tables[key] = dev;
+    *dev_tab = dev;
+    return HSES_OK;
+}
+
 static int build_tables(DeviceTables& t) {
     // log helper table
     double host_tab[128];
     build_log_table(host_tab);
     HSES_CUDA(cudaMalloc(&t.log_tab, sizeof(host_tab)));
     HSES_CUDA(cudaMemcpy(t.log_tab, host_tab, sizeof(host_tab), cudaMemcpyHostToDevice));
+
+    HSES_CUDA(cudaMalloc(&t.status_word, sizeof(int)));
+    HSES_CUDA(cudaMemset(t.status_word, 0, sizeof(int)));
 
     // jump tables T^(2^k)
     {
@@ -192,6 +233,13 @@ int hses_ctx_create(int device, hses_ctx** out) {
 
 int hses_ctx_destroy(hses_ctx* ctx) {
     delete ctx;
+    return HSES_OK;
+}
+
+int hses_ctx_device_status(hses_ctx* ctx, int* status) {
+    HSES_REQUIRE(ctx != nullptr && status != nullptr, "NULL pointer");
+    HSES_CUDA(cudaMemcpy(status, ctx->t.status_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) HSES_CUDA(cudaMemset(ctx->t.status_word, 0, sizeof(int)));
     return HSES_OK;
 }
 

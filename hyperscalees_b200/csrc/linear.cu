@@ -243,15 +243,11 @@ extern "C" {
 
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     if (g == nullptr || g->t_steps < 1 || g->n_pop < 1 || g->bm < 1 || g->k < 1 || g->a < 1) return 0;
-    if (!g->perturb) return 0;
-    size_t tc = 0;
-    if (g->algo != HSES_ALGO_SIMT && tensor_path_supports(*g)) {
-        tc = tensor_path_workspace_bytes(*g);
-        if (g->algo == HSES_ALGO_TENSOR) return tc;
-    }
-    size_t simt = simt_scratch(*g, nullptr).bytes;
-    if (g->algo == HSES_ALGO_AUTO && tensor_path_supports(*g)) return tc;
-    return simt;
+    // the tensor path always needs room for the split weights, the general path
+    // only needs scratch when it perturbs
+    if (g->algo != HSES_ALGO_SIMT && tensor_path_supports(*g)) return tensor_path_workspace_bytes(*g);
+    if (g->algo == HSES_ALGO_TENSOR || !g->perturb) return 0;
+    return simt_scratch(*g, nullptr).bytes;
 }
 
 int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_args* g) {

@@ -1,13 +1,633 @@
-// Tensor-core (tcgen05 / TMEM / TMA) path of the perturbed linear layer.
+// Tensor-core path of the perturbed linear layer (do_mm,
+// hyperscalees-noiser/src/eggroll.rs:419-446, + lif_step, snn.rs:53-65).
+//
+//   launch 1  split_tf32      W -> W_hi + W_lo, both exactly representable in TF32
+//   launch 2  lowrank_t       t = x·B_pair, B regenerated from the seed stream in
+//                             shared memory, never written to HBM
+//   launch 3  linear_tc       persistent, one CTA per SM, warp-specialised:
+//       warp 0      TMA producer: x, W_hi, W_lo tiles -> 128B-swizzled smem ring
+//       warp 1      MMA issuer: tcgen05.mma kind::tf32, three passes per k-step
+//                   (x_hi·W_hi + x_hi·W_lo + x_lo·W_hi), fp32 accumulators in TMEM,
+//                   two accumulator buffers so the epilogue overlaps the next chunk
+//       warps 2-3   split the x tile in place into x_hi / x_lo (same offsets, so
+//                   the swizzle pattern is preserved)
+//       warps 4-7   epilogue: TMEM -> registers, regenerate the A rows of the
+//                   warp's antithetic pair in registers, add t·(±s·A)ᵀ, LIF step,
+//                   store spikes
+// Three TF32 passes make every product fp32-equivalent (2^-21 relative residue);
+// a single pass (5e-4) would break the spike tolerance.  No TMA multicast and no
+// cluster launch is used anywhere.  Every barrier wait is bounded: a wait that
+// runs out records a code in the context's status word, all roles leave their
+// loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
 #include "linear.cuh"
 
 namespace hses {
 
-bool tensor_path_supports(const hses_linear_args&) { return false; }
-size_t tensor_path_workspace_bytes(const hses_linear_args&) { return 0; }
-int run_tensor_path(hses_ctx*, cudaStream_t, const hses_linear_args&) {
-    set_error("tensor path not available");
-    return HSES_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
+constexpr int BK = 32;            // fp32 elements per k-block = one 128 B swizzle row
+constexpr int NTHREADS = 256;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (i > 64) __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
+
+// K-major operand tile with 128 B rows and 128 B swizzle: 8-row groups are 1024 B
+// apart (stride byte offset), the leading byte offset is unused for this layout.
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);  // start address, 16 B units
+    d |= (uint64_t)1 << 16;                             // leading byte offset (ignored)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset
+    d |= (uint64_t)1 << 46;                             // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                             // layout type: 128 B swizzle
+    return d;
+}
+// kind::tf32, fp32 accumulator, both operands K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t make_idesc(int bn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+struct TcArgs {
+    int64_t rows;
+    int k, a;
+    int bm;
+    int64_t n_pop;
+    int perturb, lif;
+    int rank;
+    uint64_t key;
+    int32_t true_epoch, first_thread;
+    float base_sigma, leak, v_th, out_scale;
+    const float* t;       // (rows, rank)
+    float* out;
+    int64_t out_stride;
+    float* pot;
+    const uint64_t* pow2; // T^(2^k) tables
+    const uint64_t* hop;  // T^(2*rank*31)
+    LibmCal cal;
+    int* status;
+};
+
+template <int BN>
+struct TcSmem {
+    static constexpr int STAGES = BN == 256 ? 2 : 3;
+    static constexpr int X_BYTES = BM_TILE * BK * 4;
+    static constexpr int W_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
+    static constexpr int A_STRIDE = 36;  // floats per staged A row (rank <= 32, padded: conflict-free float4)
+    static constexpr int A_BYTES = 4 * 32 * A_STRIDE * 4;
+    static constexpr int HOP_BYTES = kJumpWords * 8;
+    static constexpr int BAR_BYTES = 128;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + A_BYTES + HOP_BYTES + BAR_BYTES + 1024;
+};
+
+// ----------------------------------------------------------------------- kernel
+template <int BN>
+__global__ void __launch_bounds__(NTHREADS, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_whi,
+                 const __grid_constant__ CUtensorMap tm_wlo, const TcArgs g) {
+    using S = TcSmem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* stage_base = smem;
+    float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* hop_s = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::A_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::A_BYTES + S::HOP_BYTES);
+    uint64_t* full = bars;                   // [STAGES] TMA landed
+    uint64_t* xready = bars + S::STAGES;     // [STAGES] x split done
+    uint64_t* empty = bars + 2 * S::STAGES;  // [STAGES] MMAs finished reading the stage
+    uint64_t* tfull = bars + 3 * S::STAGES;  // [2] accumulator ready
+    uint64_t* tempty = tfull + 2;            // [2] accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (int)(g.rows / BM_TILE);
+    const int n_chunks = g.a / BN;
+    const int k_blocks = g.k / BK;
+
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        for (int s = 0; s < S::STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&xready[s], 64);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull[b], 1);
+            mbar_init(&tempty[b], 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < kJumpWords; i += NTHREADS) hop_s[i] = g.hop ? g.hop[i] : 0ull;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(2 * BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+                for (int c = 0; c < n_chunks && ok; ++c) {
+                    for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                        int s = it % S::STAGES;
+                        uint32_t ph = (it / S::STAGES) & 1;
+                        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
+                        uint8_t* st = stage_base + s * S::STAGE_BYTES;
+                        mbar_expect_tx(&full[s], S::X_BYTES + 2 * S::W_BYTES);
+                        tma_load_2d(st, &tm_x, kb * BK, mt * BM_TILE, &full[s]);
+                        tma_load_2d(st + 2 * S::X_BYTES, &tm_whi, kb * BK, c * BN, &full[s]);
+                        tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
+                    }
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: give them a
+                // bounded moment before the block is torn down
+                for (int s = 0; s < S::STAGES; ++s)
+                    for (uint32_t i = 0; i < 4096; ++i) {
+                        if (mbar_try(&full[s], 0) || mbar_try(&full[s], 1)) break;
+                        __nanosleep(256);
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(BN);
+            uint32_t it = 0, acc_it = 0;
+            bool ok = true;
+            for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+                for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
+                    int b = acc_it & 1;
+                    if (!mbar_wait(&tempty[b], ((acc_it >> 1) & 1) ^ 1, abort_flag, g.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    uint32_t d = tmem_base + (uint32_t)(b * BN);
+                    for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                        int s = it % S::STAGES;
+                        uint32_t ph = (it / S::STAGES) & 1;
+                        if (!mbar_wait(&full[s], ph, abort_flag, g.status, 3) ||
+                            !mbar_wait(&xready[s], ph, abort_flag, g.status, 4)) { ok = false; break; }
+                        tc_fence_after();
+                        uint8_t* st = stage_base + s * S::STAGE_BYTES;
+                        uint64_t dxh = make_smem_desc(st), dxl = make_smem_desc(st + S::X_BYTES);
+                        uint64_t dwh = make_smem_desc(st + 2 * S::X_BYTES);
+                        uint64_t dwl = make_smem_desc(st + 2 * S::X_BYTES + S::W_BYTES);
+#pragma unroll
+                        for (int ks = 0; ks < BK / 8; ++ks) {
+                            uint64_t off = (uint64_t)(ks * 32 >> 4);  // 8 tf32 = 32 B along K
+                            umma_tf32(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
+                            umma_tf32(d, dxh + off, dwl + off, idesc, 1);
+                            umma_tf32(d, dxh + off, dwh + off, idesc, 1);
+                        }
+                        umma_commit(&empty[s]);
+                    }
+                    if (ok) umma_commit(&tfull[b]);
+                }
+            }
+        }
+    } else if (warp < 4) {
+        // -------------------------------------------------- split x into hi / lo parts
+        const int tid = threadIdx.x - 64;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+            for (int c = 0; c < n_chunks && ok; ++c) {
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    int s = it % S::STAGES;
+                    uint32_t ph = (it / S::STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph, abort_flag, g.status, 5)) { ok = false; break; }
+                    float4* xh = reinterpret_cast<float4*>(stage_base + s * S::STAGE_BYTES);
+                    float4* xl = reinterpret_cast<float4*>(stage_base + s * S::STAGE_BYTES + S::X_BYTES);
+#pragma unroll 4
+                    for (int i = 0; i < S::X_BYTES / 16 / 64; ++i) {
+                        int idx = tid + 64 * i;
+                        float4 v = xh[idx], h, l;
+                        h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+                        l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y);
+                        l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
+                        xh[idx] = h;
+                        xl[idx] = l;
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(&xready[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q4 = warp - 4;  // TMEM lane quadrant of this warp
+        float* my_a = a_stage + q4 * 32 * S::A_STRIDE;
+        uint32_t acc_it = 0;
+        bool ok = true;
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+            const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
+            float tq[32];
+            bool odd_member = false;
+            uint64_t a_state = 0;
+            if (g.perturb) {
+                int64_t member = (R / g.bm) % g.n_pop;
+                int32_t thread_id = g.first_thread + (int32_t)member;
+                odd_member = (thread_id & 1) != 0;  // sign -1: A of the pair is negated for this row
+#pragma unroll
+                for (int q = 0; q < 32; ++q) tq[q] = q < g.rank ? g.t[(size_t)R * g.rank + q] : 0.0f;
+                // all lanes of the warp share one antithetic pair; lane l starts on A row l
+                int64_t member0 = (((int64_t)mt * BM_TILE + q4 * 32) / g.bm) % g.n_pop;
+                int32_t pair = (g.first_thread + (int32_t)member0) / 2;
+                uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
+                a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)g.rank * (uint64_t)(g.k + lane));
+            }
+            for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
+                int b = acc_it & 1;
+                if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
+                tc_fence_after();
+                for (int cb = 0; cb < BN / 32; ++cb) {
+                    const int n0 = c * BN + cb * 32;
+                    if (g.perturb) {
+                        // lane l regenerates A row n0 + l of the pair, scaled by base_sigma; the
+                        // sign of the consuming row's member is applied to the finished dot product
+                        // (negating every term of a sum negates the sum exactly)
+                        for (int q = 0; q < g.rank; ++q)
+                            my_a[lane * S::A_STRIDE + q] = __fmul_rn(next_normal(a_state, g.cal), g.base_sigma);
+                        a_state = jump_apply(hop_s, a_state);  // on to row n0 + 32 + l
+                        __syncwarp();
+                    }
+                    uint32_t acc[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32), acc);
+                    float y[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = __uint_as_float(acc[j]);
+                        if (g.perturb) {
+                            float u = 0.0f;
+                            const float4* ar = reinterpret_cast<const float4*>(my_a + j * S::A_STRIDE);
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                if (q * 4 < g.rank) {
+                                    float4 av = ar[q];
+                                    u = fmaf(tq[4 * q + 0], av.x, u);
+                                    u = fmaf(tq[4 * q + 1], av.y, u);
+                                    u = fmaf(tq[4 * q + 2], av.z, u);
+                                    u = fmaf(tq[4 * q + 3], av.w, u);
+                                }
+                            }
+                            v = __fadd_rn(v, odd_member ? -u : u);
+                        }
+                        y[j] = v;
+                    }
+                    float* orow = g.out + (size_t)R * g.out_stride + n0;
+                    if (g.lif) {
+                        float* prow = g.pot ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 cv = make_float4(__fmul_rn(y[j], g.leak), __fmul_rn(y[j + 1], g.leak),
+                                                    __fmul_rn(y[j + 2], g.leak), __fmul_rn(y[j + 3], g.leak));
+                            if (prow) *reinterpret_cast<float4*>(prow + j) = cv;
+                            float4 sv = make_float4(cv.x >= g.v_th ? 1.0f : 0.0f, cv.y >= g.v_th ? 1.0f : 0.0f,
+                                                    cv.z >= g.v_th ? 1.0f : 0.0f, cv.w >= g.v_th ? 1.0f : 0.0f);
+                            __stcs(reinterpret_cast<float4*>(orow + j), sv);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(orow + j) =
+                                make_float4(__fmul_rn(y[j], g.out_scale), __fmul_rn(y[j + 1], g.out_scale),
+                                            __fmul_rn(y[j + 2], g.out_scale), __fmul_rn(y[j + 3], g.out_scale));
+                    }
+                    if (g.perturb) __syncwarp();
+                }
+                tc_fence_before();
+                mbar_arrive(&tempty[b]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------ auxiliary kernels
+__global__ void split_tf32_kernel(const float* __restrict__ w, int a, int k, int64_t stride,
+                                  float* __restrict__ hi, float* __restrict__ lo) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)a * k) return;
+    size_t r = i / k, c = i - r * k;
+    float v = w[r * stride + c];
+    float h = to_tf32(v);
+    hi[i] = h;
+    lo[i] = to_tf32(v - h);
+}
+
+// t[R, q] = sum_k x[R, k] * B_pair[k, q].  One CTA per antithetic pair: 128 threads
+// regenerate 128 rows of B into shared memory (thread j owns rows j, j+128, ...),
+// then every thread accumulates four q's of one x row over that block.
+constexpr int LT_THREADS = 128;
+__global__ void __launch_bounds__(LT_THREADS)
+lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop127,
+                 uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
+                 int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, int rank,
+                 float* __restrict__ t) {
+    extern __shared__ float bs[];  // 128 x rank
+    __shared__ uint64_t hop_s[kJumpWords];
+    const int tid = threadIdx.x;
+    for (int i = tid; i < kJumpWords; i += LT_THREADS) hop_s[i] = hop127[i];
+    const int32_t first_pair = first_thread / 2;
+    const int32_t pair = first_pair + blockIdx.x;
+    // members of this pair inside the population slice
+    int64_t m_lo = (int64_t)pair * 2 - first_thread, m_hi = m_lo + 2;
+    if (m_lo < 0) m_lo = 0;
+    if (m_hi > n_pop) m_hi = n_pop;
+    const int rows_per_step = (int)(m_hi - m_lo) * bm;
+    const int total_rows = rows_per_step * t_steps;
+    const int qgroups = (rank + 3) / 4;
+    uint64_t s = noise_seed(key, true_epoch, pair) | 1ull;
+    s = jump_by(pow2, s, 2ull * (uint64_t)rank * (uint64_t)tid);
+    __syncthreads();
+    // work items: (row, q-group); each thread keeps up to 8 of them in registers
+    constexpr int MAXI = 8;
+    const int items = total_rows * qgroups;
+    for (int base = 0; base < items; base += LT_THREADS * MAXI) {
+        float acc[MAXI][4];
+#pragma unroll
+        for (int i = 0; i < MAXI; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+        uint64_t sb = s;  // every pass over the items replays the pair's B stream
+        for (int k0 = 0; k0 < k; k0 += LT_THREADS) {
+            if (k0 + tid < k) {
+                for (int q = 0; q < rank; ++q) bs[tid * rank + q] = next_normal(sb, cal);
+                sb = jump_apply(hop_s, sb);
+            }
+            __syncthreads();
+            const int kn = k - k0 < LT_THREADS ? k - k0 : LT_THREADS;
+#pragma unroll
+            for (int i = 0; i < MAXI; ++i) {
+                int item = base + tid + i * LT_THREADS;
+                if (item < items) {
+                    int lr = item / qgroups, qg = item - lr * qgroups;
+                    int step = lr / rows_per_step, rr = lr - step * rows_per_step;
+                    int64_t R = ((int64_t)step * n_pop + m_lo) * bm + rr;
+                    const float* xr = x + (size_t)R * x_stride + k0;
+                    for (int kk = 0; kk < kn; ++kk) {
+                        float xv = xr[kk];
+                        const float* br = bs + kk * rank + qg * 4;
+                        acc[i][0] = fmaf(xv, br[0], acc[i][0]);
+                        if (qg * 4 + 1 < rank) acc[i][1] = fmaf(xv, br[1], acc[i][1]);
+                        if (qg * 4 + 2 < rank) acc[i][2] = fmaf(xv, br[2], acc[i][2]);
+                        if (qg * 4 + 3 < rank) acc[i][3] = fmaf(xv, br[3], acc[i][3]);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < MAXI; ++i) {
+            int item = base + tid + i * LT_THREADS;
+            if (item < items) {
+                int lr = item / qgroups, qg = item - lr * qgroups;
+                int step = lr / rows_per_step, rr = lr - step * rows_per_step;
+                int64_t R = ((int64_t)step * n_pop + m_lo) * bm + rr;
+                for (int j = 0; j < 4; ++j)
+                    if (qg * 4 + j < rank) t[(size_t)R * rank + qg * 4 + j] = acc[i][j];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// 2-D fp32 map over (rows, cols) with `stride` floats between rows; box = (32, box_rows).
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int64_t stride, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return HSES_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)stride * 4};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+        return HSES_ERR_CUDA;
+    }
+    return HSES_OK;
+}
+
+struct TcScratch {
+    float *whi, *wlo, *t;
+    size_t bytes;
+};
+TcScratch tc_scratch(const hses_linear_args& g, void* base) {
+    auto up = [](size_t v) { return (v + 63) / 64 * 64; };
+    size_t nw = up((size_t)g.a * g.k);
+    size_t nt = g.perturb ? up((size_t)g.t_steps * g.n_pop * g.bm * g.rank) : 0;
+    TcScratch s;
+    s.whi = reinterpret_cast<float*>(base);
+    s.wlo = s.whi + nw;
+    s.t = s.wlo + nw;
+    s.bytes = (2 * nw + nt) * sizeof(float);
+    return s;
+}
+
+template <int BN>
+int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, const TcArgs& ta) {
+    CUtensorMap tm_x, tm_whi, tm_wlo;
+    int64_t rows = ta.rows;
+    int rc = make_map(&tm_x, g.x, rows, g.k, g.x_row_stride, BM_TILE);
+    if (rc == HSES_OK) rc = make_map(&tm_whi, sc.whi, g.a, g.k, g.k, BN);
+    if (rc == HSES_OK) rc = make_map(&tm_wlo, sc.wlo, g.a, g.k, g.k, BN);
+    if (rc != HSES_OK) return rc;
+    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   TcSmem<BN>::TOTAL));
+    int m_tiles = (int)(rows / BM_TILE);
+    int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;
+    HSES_KERNEL(ctx, st, "linear_tc");
+    linear_tc_kernel<BN><<<grid, NTHREADS, TcSmem<BN>::TOTAL, st>>>(tm_x, tm_whi, tm_wlo, ta);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace
+
+bool tensor_path_supports(const hses_linear_args& g) {
+    int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
+    if (rows % BM_TILE != 0 || g.k % BK != 0 || g.a % 128 != 0) return false;
+    if (g.x_row_stride % 4 != 0 || g.out_row_stride % 4 != 0) return false;
+    if (!aligned16(g.x) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
+    if (g.k > (1 << 20) || g.a > (1 << 20)) return false;
+    if (g.perturb) {
+        if (g.rank > 32 || g.rank % 4 != 0) return false;
+        // every 32-row slice of a tile must belong to one antithetic pair
+        bool pair_rows = (g.bm % 32 == 0) || (g.bm == 16 && g.first_thread % 2 == 0 && g.n_pop % 2 == 0);
+        if (!pair_rows) return false;
+    }
+    return true;
+}
+
+size_t tensor_path_workspace_bytes(const hses_linear_args& g) { return tc_scratch(g, nullptr).bytes; }
+
+int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
+    TcScratch sc = tc_scratch(g, g.workspace);
+    HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= sc.bytes && aligned16(g.workspace),
+                 "workspace too small or misaligned; see hses_perturbed_linear_workspace_bytes");
+    int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
+    {
+        size_t n = (size_t)g.a * g.k;
+        HSES_KERNEL(ctx, st, "split_tf32");
+        split_tf32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
+                                                                      sc.whi, sc.wlo);
+        HSES_LAUNCH_CHECK();
+    }
+    TcArgs ta{};
+    ta.rows = rows;
+    ta.k = g.k;
+    ta.a = g.a;
+    ta.bm = g.bm;
+    ta.n_pop = g.n_pop;
+    ta.perturb = g.perturb;
+    ta.lif = g.lif;
+    ta.rank = g.perturb ? g.rank : 0;
+    ta.key = g.key;
+    ta.true_epoch = true_epoch_of(g.epoch, g.noise_reuse);
+    ta.first_thread = g.first_thread;
+    ta.base_sigma = g.perturb ? g.sigma / sqrtf((float)g.rank) : 0.0f;
+    ta.leak = g.lif ? 1.0f / g.tau_m : 0.0f;
+    ta.v_th = g.v_th;
+    ta.out_scale = g.out_scale;
+    ta.t = sc.t;
+    ta.out = g.out;
+    ta.out_stride = g.out_row_stride;
+    ta.pot = g.lif ? g.potentials : nullptr;
+    ta.pow2 = ctx->t.jump_pow2;
+    ta.cal = ctx->cal();
+    ta.status = ctx->t.status_word;
+    ta.hop = nullptr;
+    if (g.perturb) {
+        const uint64_t *hop31 = nullptr, *hop127 = nullptr;
+        int rc = get_hop_table(ctx, 2ull * g.rank * 31, &hop31);
+        if (rc == HSES_OK) rc = get_hop_table(ctx, 2ull * g.rank * 127, &hop127);
+        if (rc != HSES_OK) return rc;
+        ta.hop = hop31;
+        int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
+        HSES_KERNEL(ctx, st, "lowrank_t");
+        lowrank_t_kernel<<<(unsigned)pairs, LT_THREADS, LT_THREADS * g.rank * sizeof(float), st>>>(
+            ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,
+            g.t_steps, g.n_pop, g.bm, g.k, g.rank, sc.t);
+        HSES_LAUNCH_CHECK();
+    }
+    if (g.a % 256 == 0) return launch_tc<256>(ctx, st, g, sc, ta);
+    return launch_tc<128>(ctx, st, g, sc, ta);
 }
 
 }  // namespace hses

@@ -63,6 +63,13 @@ int hses_ctx_destroy(hses_ctx* ctx);
  * rounded value (diagnostic; tests compare it with their own count). */
 int hses_ctx_calibration_info(const hses_ctx* ctx, uint64_t* log_flips, uint64_t* cos_flips);
 
+/* ---- device-side status.  Kernels that wait on barriers do so with an
+ *      iteration limit; one that gives up records a non-zero code here and
+ *      returns instead of hanging.  This call synchronises (it copies one int
+ *      back), reports the code and clears it; 0 means no kernel gave up.
+ *      The reference has no counterpart (its launches cannot time out). ----- */
+int hses_ctx_device_status(hses_ctx* ctx, int* status);
+
 /* ---- launch accounting.  Every kernel the library launches is counted per
  *      context; with timing on, each launch is also bracketed by CUDA events
  *      on the launching stream.  hses_profile_enable clears the counters;
