@@ -34,6 +34,9 @@ UNIT = "member-evals/s"
 KEY = 0x3C6EF372FE94F82A          # base key of parameter index 1
 SIGMA, RANK, TAU_M, V_TH = 0.02, 16, 20.0, 0.3
 N_POP, BM, K_DIM, A_DIM = 8192, 16, 1024, 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by its members, from the ncu
+# capture summarised in profiles/linear_tc_perturbed_linear_microbench.md
+NCU_TRAFFIC_BYTES_PER_MEMBER = {"linear_tc": (231.0e6 + 91.1e6) / 2048}
 
 
 def measured_peaks():
@@ -118,11 +121,12 @@ def cpu_rate(oracle, x, w, target_seconds: float, first_thread: int = 0):
 
 
 def config_dict(n_gpus: int):
-    return {"workload": "perturbed-linear microbench: x[8192,16,1024] fp32, W[1024,1024], rank 16, sigma 0.02, "
+    return {"workload": f"perturbed-linear microbench: x[{N_POP},16,1024] fp32, W[1024,1024], rank 16, sigma 0.02, "
                         "one LIF step (tau_m 20, v_th 0.3), spikes out",
             "n_pop_per_gpu": N_POP, "bm": BM, "k": K_DIM, "a": A_DIM, "rank": RANK, "t_steps": 1,
             "population_total": N_POP * n_gpus,
-            "l2_policy": "inputs (537 MB) and outputs (537 MB) exceed the 126 MB L2, no flush needed"}
+            "l2_policy": f"inputs ({N_POP * BM * K_DIM * 4 >> 20} MiB) and outputs ({N_POP * BM * A_DIM * 4 >> 20} MiB) "
+                         "exceed the 126 MB L2, no flush needed"}
 
 
 def run_reference(args, rank: int, world: int):
@@ -221,9 +225,12 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         step()
         out_host.copy_(out_dev, non_blocking=True)
 
-    for _ in range(2):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
+    if args.kernel_only:
+        ms_e2e = float("nan")
+    else:
+        for _ in range(2):
+            e2e_step()
+        ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if sampler else None
 
     evals_per_step = N_POP * BM * world
@@ -243,11 +250,13 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                     "peak_source": f"{peaks['source']} bf16 cuBLAS burst; the kernel computes in fp32/TF32 "
                                    "(nominal TF32 peak is half of bf16)",
-                    "traffic": None, "algorithmic_flops_per_launch": flops,
+                    "traffic": NCU_TRAFFIC_BYTES_PER_MEMBER.get(top_name, 0) * N_POP or None,
+                    "traffic_source": "ncu capture at n_pop=2048 (profiles/), scaled by members per launch",
+                    "algorithmic_flops_per_launch": flops,
                     "avg_launch_ms": per_launch_s * 1e3,
                     "kernel_time_share": {k: round(v[1] / sum(p[1] for p in prof.values()), 4) for k, v in prof.items()}}
         cpu = None
-        if world == 1:
+        if world == 1 and not args.kernel_only:
             from oracle import oracle as O
             O.build()
             r, members, secs = cpu_rate(O, x_np, w_np, 12.0)
@@ -272,7 +281,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--n-pop", type=int, default=8192,
+                    help="members per GPU; smaller values give the reduced case used for ncu captures")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
+    globals()["N_POP"] = args.n_pop
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -29,7 +29,7 @@ namespace {
 
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
 constexpr int BK = 32;            // fp32 elements per k-block = one 128 B swizzle row
-constexpr int NTHREADS = 256;
+constexpr int NTHREADS = 384;    // warps: 0 TMA, 1 MMA, 2-3 x split, 4-11 epilogue
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // ------------------------------------------------------------------ PTX helpers
@@ -141,9 +141,11 @@ struct TcArgs {
     int64_t out_stride;
     float* pot;
     const uint64_t* pow2; // T^(2^k) tables
-    const uint64_t* hop;  // T^(2*rank*31)
+    const uint64_t* hop;  // T^(2*rank*(32*epi_halves - 1))
     LibmCal cal;
     int* status;
+    int epi_halves;       // 2: warps 4-7 take even 32-column blocks, warps 8-11 odd ones; 1: warps 8-11 idle
+    int a_stride;         // floats per staged A row
 };
 
 template <int BN>
@@ -152,11 +154,13 @@ struct TcSmem {
     static constexpr int X_BYTES = BM_TILE * BK * 4;
     static constexpr int W_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
-    static constexpr int A_STRIDE = 36;  // floats per staged A row (rank <= 32, padded: conflict-free float4)
-    static constexpr int A_BYTES = 4 * 32 * A_STRIDE * 4;
     static constexpr int HOP_BYTES = kJumpWords * 8;
+    static constexpr int TAB_BYTES = 1024 + 2 * 1024;  // log helper table + two threshold tables
     static constexpr int BAR_BYTES = 128;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + A_BYTES + HOP_BYTES + BAR_BYTES + 1024;
+    static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
+    static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
+    // staged A rows: halves * 4 warps * 32 rows * (rank + 4) floats
+    static int a_bytes(int halves, int rank) { return halves * 4 * 32 * (rank + 4) * 4; }
 };
 
 // ----------------------------------------------------------------------- kernel
@@ -168,9 +172,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
-    float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES);
-    uint64_t* hop_s = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::A_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::A_BYTES + S::HOP_BYTES);
+    uint64_t* hop_s = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+    double2* log_tab_s = reinterpret_cast<double2*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES);
+    uint32_t* delta_s = reinterpret_cast<uint32_t*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + 1024);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES);
+    float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES +
+                                              S::BAR_BYTES);
     uint64_t* full = bars;                   // [STAGES] TMA landed
     uint64_t* xready = bars + S::STAGES;     // [STAGES] x split done
     uint64_t* empty = bars + 2 * S::STAGES;  // [STAGES] MMAs finished reading the stage
@@ -194,11 +201,20 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 128);
+            mbar_init(&tempty[b], 128 * g.epi_halves);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // small read-only tables go to shared memory: the epilogue's noise regeneration
+    // looks them up for every normal
     for (int i = threadIdx.x; i < kJumpWords; i += NTHREADS) hop_s[i] = g.hop ? g.hop[i] : 0ull;
+    if (g.perturb) {
+        for (int i = threadIdx.x; i < 64; i += NTHREADS) log_tab_s[i] = g.cal.log_tab[i];
+        for (int i = threadIdx.x; i < 256; i += NTHREADS) {
+            delta_s[i] = g.cal.log_delta[i];
+            delta_s[256 + i] = g.cal.cos_delta[i];
+        }
+    }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(2 * BN)
@@ -302,10 +318,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 }
             }
         }
-    } else {
+    } else if (warp - 4 < 4 * g.epi_halves) {
         // ------------------------------------------------------------------ epilogue
-        const int q4 = warp - 4;  // TMEM lane quadrant of this warp
-        float* my_a = a_stage + q4 * 32 * S::A_STRIDE;
+        const int q4 = (warp - 4) & 3;   // TMEM lane quadrant this warp may read (warp id mod 4)
+        const int half = (warp - 4) >> 2;
+        const int halves = g.epi_halves;
+        const int astr = g.a_stride;
+        float* my_a = a_stage + (half * 4 + q4) * 32 * astr;
+        LibmCal cal = g.cal;
+        cal.log_tab = log_tab_s;
+        cal.log_delta = delta_s;
+        cal.cos_delta = delta_s + 256;
         uint32_t acc_it = 0;
         bool ok = true;
         for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
@@ -319,25 +342,30 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 odd_member = (thread_id & 1) != 0;  // sign -1: A of the pair is negated for this row
 #pragma unroll
                 for (int q = 0; q < 32; ++q) tq[q] = q < g.rank ? g.t[(size_t)R * g.rank + q] : 0.0f;
-                // all lanes of the warp share one antithetic pair; lane l starts on A row l
+                // all lanes of the warp share one antithetic pair; lane l starts on A row 32*half + l
                 int64_t member0 = (((int64_t)mt * BM_TILE + q4 * 32) / g.bm) % g.n_pop;
                 int32_t pair = (g.first_thread + (int32_t)member0) / 2;
                 uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
-                a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)g.rank * (uint64_t)(g.k + lane));
+                a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)g.rank * (uint64_t)(g.k + half * 32 + lane));
             }
             for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                 int b = acc_it & 1;
                 if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
                 tc_fence_after();
-                for (int cb = 0; cb < BN / 32; ++cb) {
+                for (int cb = half; cb < BN / 32; cb += halves) {
                     const int n0 = c * BN + cb * 32;
                     if (g.perturb) {
                         // lane l regenerates A row n0 + l of the pair, scaled by base_sigma; the
                         // sign of the consuming row's member is applied to the finished dot product
                         // (negating every term of a sum negates the sum exactly)
-                        for (int q = 0; q < g.rank; ++q)
-                            my_a[lane * S::A_STRIDE + q] = __fmul_rn(next_normal(a_state, g.cal), g.base_sigma);
-                        a_state = jump_apply(hop_s, a_state);  // on to row n0 + 32 + l
+                        for (int q = 0; q < g.rank; q += 4) {
+                            float z[4];
+                            next_normals4(a_state, cal, z);
+                            *reinterpret_cast<float4*>(my_a + lane * astr + q) =
+                                make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
+                                            __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));
+                        }
+                        a_state = jump_apply(hop_s, a_state);  // on to this warp's next block of rows
                         __syncwarp();
                     }
                     uint32_t acc[32];
@@ -348,7 +376,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                         float v = __uint_as_float(acc[j]);
                         if (g.perturb) {
                             float u = 0.0f;
-                            const float4* ar = reinterpret_cast<const float4*>(my_a + j * S::A_STRIDE);
+                            const float4* ar = reinterpret_cast<const float4*>(my_a + j * astr);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 if (q * 4 < g.rank) {
@@ -421,8 +449,18 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                  float* __restrict__ t) {
     extern __shared__ float bs[];  // 128 x rank
     __shared__ uint64_t hop_s[kJumpWords];
+    __shared__ double2 log_tab_s[64];
+    __shared__ uint32_t delta_s[512];
     const int tid = threadIdx.x;
     for (int i = tid; i < kJumpWords; i += LT_THREADS) hop_s[i] = hop127[i];
+    for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
+    for (int i = tid; i < 256; i += LT_THREADS) {
+        delta_s[i] = cal.log_delta[i];
+        delta_s[256 + i] = cal.cos_delta[i];
+    }
+    cal.log_tab = log_tab_s;
+    cal.log_delta = delta_s;
+    cal.cos_delta = delta_s + 256;
     const int32_t first_pair = first_thread / 2;
     const int32_t pair = first_pair + blockIdx.x;
     // members of this pair inside the population slice
@@ -445,7 +483,11 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         uint64_t sb = s;  // every pass over the items replays the pair's B stream
         for (int k0 = 0; k0 < k; k0 += LT_THREADS) {
             if (k0 + tid < k) {
-                for (int q = 0; q < rank; ++q) bs[tid * rank + q] = next_normal(sb, cal);
+                for (int q = 0; q < rank; q += 4) {  // rank is a multiple of 4 on this path
+                    float z[4];
+                    next_normals4(sb, cal, z);
+                    *reinterpret_cast<float4*>(bs + tid * rank + q) = make_float4(z[0], z[1], z[2], z[3]);
+                }
                 sb = jump_apply(hop_s, sb);
             }
             __syncthreads();
@@ -539,19 +581,30 @@ TcScratch tc_scratch(const hses_linear_args& g, void* base) {
 }
 
 template <int BN>
-int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, const TcArgs& ta) {
+int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, TcArgs ta) {
+    // two epilogue warps per TMEM quadrant when their staged A rows fit in shared memory
+    ta.epi_halves = (TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(2, ta.rank) <= TcSmem<BN>::LIMIT) ? 2 : 1;
+    ta.a_stride = ta.rank + 4;
+    if (g.perturb) {
+        const uint64_t* hop = nullptr;
+        int hrc = get_hop_table(ctx, 2ull * g.rank * (32ull * ta.epi_halves - 1), &hop);
+        if (hrc != HSES_OK) return hrc;
+        ta.hop = hop;
+    }
     CUtensorMap tm_x, tm_whi, tm_wlo;
     int64_t rows = ta.rows;
     int rc = make_map(&tm_x, g.x, rows, g.k, g.x_row_stride, BM_TILE);
     if (rc == HSES_OK) rc = make_map(&tm_whi, sc.whi, g.a, g.k, g.k, BN);
     if (rc == HSES_OK) rc = make_map(&tm_wlo, sc.wlo, g.a, g.k, g.k, BN);
     if (rc != HSES_OK) return rc;
-    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   TcSmem<BN>::TOTAL));
+    using S = TcSmem<BN>;
+    int smem_bytes = S::FIXED + S::a_bytes(ta.epi_halves, ta.rank);
+    HSES_REQUIRE(smem_bytes <= S::LIMIT, "shared memory budget exceeded");
+    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     int m_tiles = (int)(rows / BM_TILE);
     int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;
     HSES_KERNEL(ctx, st, "linear_tc");
-    linear_tc_kernel<BN><<<grid, NTHREADS, TcSmem<BN>::TOTAL, st>>>(tm_x, tm_whi, tm_wlo, ta);
+    linear_tc_kernel<BN><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_whi, tm_wlo, ta);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -614,11 +667,9 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.status = ctx->t.status_word;
     ta.hop = nullptr;
     if (g.perturb) {
-        const uint64_t *hop31 = nullptr, *hop127 = nullptr;
-        int rc = get_hop_table(ctx, 2ull * g.rank * 31, &hop31);
-        if (rc == HSES_OK) rc = get_hop_table(ctx, 2ull * g.rank * 127, &hop127);
+        const uint64_t* hop127 = nullptr;
+        int rc = get_hop_table(ctx, 2ull * g.rank * 127, &hop127);
         if (rc != HSES_OK) return rc;
-        ta.hop = hop31;
         int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
         HSES_KERNEL(ctx, st, "lowrank_t");
         lowrank_t_kernel<<<(unsigned)pairs, LT_THREADS, LT_THREADS * g.rank * sizeof(float), st>>>(
