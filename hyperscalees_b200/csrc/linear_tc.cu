@@ -20,6 +20,7 @@
 // runs out records a code in the context's status word, all roles leave their
 // loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "linear.cuh"
 
@@ -29,7 +30,10 @@ namespace {
 
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
 constexpr int BK = 32;            // fp32 elements per k-block = one 128 B swizzle row
-constexpr int NTHREADS = 384;    // warps: 0 TMA, 1 MMA, 2-3 x split, 4-11 epilogue
+// warps: 0 TMA, 1 MMA, 2-5 epilogue (one per TMEM quadrant), 6-17 noise generators
+constexpr int NTHREADS = 576;
+constexpr int EPI_WARP0 = 2;
+constexpr int GEN_WARP0 = 6;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // ------------------------------------------------------------------ PTX helpers
@@ -104,6 +108,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ float to_tf32(float v) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -120,6 +131,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
     d |= (uint64_t)1 << 46;                             // descriptor version for sm_100
     d |= (uint64_t)2 << 61;                             // layout type: 128 B swizzle
     return d;
+}
+// Staged A rows are RANK floats long with no padding; 16-byte chunk q of row l is stored at
+// chunk q ^ a_swizzle(l), which spreads the eight lanes of a store phase over all banks.
+template <int RG>
+__device__ __forceinline__ int a_swizzle(int row) {
+    return RG <= 1 ? 0 : ((row * RG) >> 3) & (RG - 1);
 }
 // kind::tf32, fp32 accumulator, both operands K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t make_idesc(int bn) {
@@ -141,11 +158,11 @@ struct TcArgs {
     int64_t out_stride;
     float* pot;
     const uint64_t* pow2; // T^(2^k) tables
-    const uint64_t* hop;  // T^(2*rank*(32*epi_halves - 1))
+    const uint64_t* hop;  // T^(2*rank*(32*ring_depth - 1))
     LibmCal cal;
     int* status;
-    int epi_halves;       // 2: warps 4-7 take even 32-column blocks, warps 8-11 odd ones; 1: warps 8-11 idle
-    int a_stride;         // floats per staged A row
+    int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..3
+    unsigned long long* dbg;  // optional cycle counters of block 0 (role breakdown), or NULL
 };
 
 template <int BN>
@@ -156,18 +173,22 @@ struct TcSmem {
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
     static constexpr int HOP_BYTES = kJumpWords * 8;
     static constexpr int TAB_BYTES = 1024 + 2 * 1024;  // log helper table + two threshold tables
-    static constexpr int BAR_BYTES = 128;
+    static constexpr int BAR_BYTES = 384;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
-    // staged A rows: halves * 4 warps * 32 rows * (rank + 4) floats
-    static int a_bytes(int halves, int rank) { return halves * 4 * 32 * (rank + 4) * 4; }
+    // ring of staged A rows: 4 quadrants * depth slots * 32 rows * rank floats
+    static int a_bytes(int depth, int rank) { return 4 * depth * 32 * rank * 4; }
 };
 
 // ----------------------------------------------------------------------- kernel
-template <int BN>
+// RG = rank / 4 (0: clean product, no noise).  The rank is a template parameter so that the
+// per-column dot product unrolls exactly and the epilogue loop stays small enough for the
+// instruction cache.
+template <int BN, int RG>
 __global__ void __launch_bounds__(NTHREADS, 1)
-linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_whi,
-                 const __grid_constant__ CUtensorMap tm_wlo, const TcArgs g) {
+linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_constant__ CUtensorMap tm_xlo,
+                 const __grid_constant__ CUtensorMap tm_whi, const __grid_constant__ CUtensorMap tm_wlo,
+                 const TcArgs g) {
     using S = TcSmem<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -179,11 +200,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES +
                                               S::BAR_BYTES);
     uint64_t* full = bars;                   // [STAGES] TMA landed
-    uint64_t* xready = bars + S::STAGES;     // [STAGES] x split done
+    uint64_t* xready = bars + S::STAGES;     // [STAGES] unused (kept so the barrier block keeps its layout)
     uint64_t* empty = bars + 2 * S::STAGES;  // [STAGES] MMAs finished reading the stage
     uint64_t* tfull = bars + 3 * S::STAGES;  // [2] accumulator ready
     uint64_t* tempty = tfull + 2;            // [2] accumulator drained
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+    uint64_t* afull = tempty + 2;            // [4][3] ring slot staged
+    uint64_t* aempty = afull + 12;           // [4][3] ring slot consumed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aempty + 12);
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
 
@@ -196,19 +219,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         abort_flag_s = 0;
         for (int s = 0; s < S::STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&xready[s], 64);
+            mbar_init(&xready[s], 128);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 128 * g.epi_halves);
+            mbar_init(&tempty[b], 128);
+        }
+        for (int i = 0; i < 12; ++i) {
+            mbar_init(&afull[i], 32);
+            mbar_init(&aempty[i], 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // small read-only tables go to shared memory: the epilogue's noise regeneration
     // looks them up for every normal
     for (int i = threadIdx.x; i < kJumpWords; i += NTHREADS) hop_s[i] = g.hop ? g.hop[i] : 0ull;
-    if (g.perturb) {
+    if (RG > 0) {
         for (int i = threadIdx.x; i < 64; i += NTHREADS) log_tab_s[i] = g.cal.log_tab[i];
         for (int i = threadIdx.x; i < 256; i += NTHREADS) {
             delta_s[i] = g.cal.log_delta[i];
@@ -225,6 +252,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // role-level cycle accounting of block 0 (only when the host asked for it)
+    const bool dbg_on = g.dbg != nullptr && blockIdx.x == 0 && lane == 0;
+    auto tick = [&](int slot, long long t0) {
+        if (dbg_on) atomicAdd(&g.dbg[slot], (unsigned long long)(clock64() - t0));
+    };
+    const long long t_kernel = clock64();
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
@@ -236,10 +269,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         int s = it % S::STAGES;
                         uint32_t ph = (it / S::STAGES) & 1;
+                        long long t0 = clock64();
                         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
+                        tick(0, t0);
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
-                        mbar_expect_tx(&full[s], S::X_BYTES + 2 * S::W_BYTES);
-                        tma_load_2d(st, &tm_x, kb * BK, mt * BM_TILE, &full[s]);
+                        mbar_expect_tx(&full[s], 2 * S::X_BYTES + 2 * S::W_BYTES);
+                        tma_load_2d(st, &tm_xhi, kb * BK, mt * BM_TILE, &full[s]);
+                        tma_load_2d(st + S::X_BYTES, &tm_xlo, kb * BK, mt * BM_TILE, &full[s]);
                         tma_load_2d(st + 2 * S::X_BYTES, &tm_whi, kb * BK, c * BN, &full[s]);
                         tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
                     }
@@ -264,14 +300,17 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                     int b = acc_it & 1;
+                    long long t0 = clock64();
                     if (!mbar_wait(&tempty[b], ((acc_it >> 1) & 1) ^ 1, abort_flag, g.status, 2)) { ok = false; break; }
+                    tick(1, t0);
                     tc_fence_after();
                     uint32_t d = tmem_base + (uint32_t)(b * BN);
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         int s = it % S::STAGES;
                         uint32_t ph = (it / S::STAGES) & 1;
-                        if (!mbar_wait(&full[s], ph, abort_flag, g.status, 3) ||
-                            !mbar_wait(&xready[s], ph, abort_flag, g.status, 4)) { ok = false; break; }
+                        long long t1 = clock64();
+                        if (!mbar_wait(&full[s], ph, abort_flag, g.status, 3)) { ok = false; break; }
+                        tick(2, t1);
                         tc_fence_after();
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
                         uint64_t dxh = make_smem_desc(st), dxl = make_smem_desc(st + S::X_BYTES);
@@ -290,134 +329,146 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
                 }
             }
         }
-    } else if (warp < 4) {
-        // -------------------------------------------------- split x into hi / lo parts
-        const int tid = threadIdx.x - 64;
-        uint32_t it = 0;
-        bool ok = true;
-        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
-            for (int c = 0; c < n_chunks && ok; ++c) {
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    int s = it % S::STAGES;
-                    uint32_t ph = (it / S::STAGES) & 1;
-                    if (!mbar_wait(&full[s], ph, abort_flag, g.status, 5)) { ok = false; break; }
-                    float4* xh = reinterpret_cast<float4*>(stage_base + s * S::STAGE_BYTES);
-                    float4* xl = reinterpret_cast<float4*>(stage_base + s * S::STAGE_BYTES + S::X_BYTES);
-#pragma unroll 4
-                    for (int i = 0; i < S::X_BYTES / 16 / 64; ++i) {
-                        int idx = tid + 64 * i;
-                        float4 v = xh[idx], h, l;
-                        h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-                        l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y);
-                        l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
-                        xh[idx] = h;
-                        xl[idx] = l;
-                    }
-                    fence_proxy_async();
-                    mbar_arrive(&xready[s]);
-                }
-            }
-        }
-    } else if (warp - 4 < 4 * g.epi_halves) {
-        // ------------------------------------------------------------------ epilogue
-        const int q4 = (warp - 4) & 3;   // TMEM lane quadrant this warp may read (warp id mod 4)
-        const int half = (warp - 4) >> 2;
-        const int halves = g.epi_halves;
-        const int astr = g.a_stride;
-        float* my_a = a_stage + (half * 4 + q4) * 32 * astr;
-        LibmCal cal = g.cal;
-        cal.log_tab = log_tab_s;
-        cal.log_delta = delta_s;
-        cal.cos_delta = delta_s + 256;
+    } else if (warp < GEN_WARP0) {
+        // ------------------------------------------------ epilogue (one warp per TMEM quadrant)
+        constexpr int RANK = RG * 4;
+        const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
+        const int depth = g.ring_depth;
         uint32_t acc_it = 0;
+        uint32_t used0 = 0, used1 = 0, used2 = 0;  // how often each ring slot of this quadrant was consumed
         bool ok = true;
         for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
             const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
-            float tq[32];
+            float tq[RANK > 0 ? RANK : 1];
             bool odd_member = false;
-            uint64_t a_state = 0;
-            if (g.perturb) {
+            if (RG > 0) {
                 int64_t member = (R / g.bm) % g.n_pop;
                 int32_t thread_id = g.first_thread + (int32_t)member;
                 odd_member = (thread_id & 1) != 0;  // sign -1: A of the pair is negated for this row
 #pragma unroll
-                for (int q = 0; q < 32; ++q) tq[q] = q < g.rank ? g.t[(size_t)R * g.rank + q] : 0.0f;
-                // all lanes of the warp share one antithetic pair; lane l starts on A row 32*half + l
-                int64_t member0 = (((int64_t)mt * BM_TILE + q4 * 32) / g.bm) % g.n_pop;
-                int32_t pair = (g.first_thread + (int32_t)member0) / 2;
-                uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
-                a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)g.rank * (uint64_t)(g.k + half * 32 + lane));
+                for (int q = 0; q < RANK; q += 4) {
+                    float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * RANK + q);
+                    tq[q] = tv.x; tq[q + 1] = tv.y; tq[q + 2] = tv.z; tq[q + 3] = tv.w;
+                }
             }
+            int blk = 0;  // 32-column block index inside this M tile
             for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                 int b = acc_it & 1;
+                long long t0 = clock64();
                 if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
+                if (warp == EPI_WARP0) tick(7, t0);
                 tc_fence_after();
-                for (int cb = half; cb < BN / 32; cb += halves) {
+                for (int cb = 0; cb < BN / 32 && ok; ++cb, ++blk) {
                     const int n0 = c * BN + cb * 32;
-                    if (g.perturb) {
-                        // lane l regenerates A row n0 + l of the pair, scaled by base_sigma; the
-                        // sign of the consuming row's member is applied to the finished dot product
-                        // (negating every term of a sum negates the sum exactly)
-                        for (int q = 0; q < g.rank; q += 4) {
-                            float z[4];
-                            next_normals4(a_state, cal, z);
-                            *reinterpret_cast<float4*>(my_a + lane * astr + q) =
-                                make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
-                                            __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));
-                        }
-                        a_state = jump_apply(hop_s, a_state);  // on to this warp's next block of rows
-                        __syncwarp();
+                    const float* my_a = nullptr;
+                    int slot = 0;
+                    long long t2 = clock64();
+                    if (RG > 0) {
+                        // the generator warps of this quadrant have staged the A rows n0..n0+31
+                        slot = blk % depth;
+                        uint32_t u = slot == 0 ? used0 : (slot == 1 ? used1 : used2);
+                        if (!mbar_wait(&afull[q4 * 3 + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
+                        my_a = a_stage + (q4 * depth + slot) * 32 * RANK;
                     }
-                    uint32_t acc[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32), acc);
-                    float y[32];
+                    if (warp == EPI_WARP0) tick(8, t2);
+                    t2 = clock64();
+                    float* orow = g.out + (size_t)R * g.out_stride + n0;
+                    float* prow = (g.lif && g.pot) ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
+#pragma unroll 1
+                    for (int j0 = 0; j0 < 32; j0 += 8) {
+                        uint32_t acc[8];
+                        tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + j0), acc);
+                        float y[8];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float v = __uint_as_float(acc[j]);
-                        if (g.perturb) {
-                            float u = 0.0f;
-                            const float4* ar = reinterpret_cast<const float4*>(my_a + j * astr);
+                        for (int j = 0; j < 8; ++j) {
+                            float v = __uint_as_float(acc[j]);
+                            if (RG > 0) {
+                                // u = sum_q t[q] * (base_sigma * A[n0+j0+j][q]); the member's sign is applied to
+                                // the finished sum (negating every term of a sum negates the sum exactly)
+                                float u = 0.0f;
+                                const int row = j0 + j;
+                                const float4* ar = reinterpret_cast<const float4*>(my_a + row * RANK);
+                                const int sw = a_swizzle<RG>(row);
 #pragma unroll
-                            for (int q = 0; q < 8; ++q) {
-                                if (q * 4 < g.rank) {
-                                    float4 av = ar[q];
+                                for (int q = 0; q < RG; ++q) {
+                                    float4 av = ar[q ^ sw];
                                     u = fmaf(tq[4 * q + 0], av.x, u);
                                     u = fmaf(tq[4 * q + 1], av.y, u);
                                     u = fmaf(tq[4 * q + 2], av.z, u);
                                     u = fmaf(tq[4 * q + 3], av.w, u);
                                 }
+                                v = __fadd_rn(v, odd_member ? -u : u);
                             }
-                            v = __fadd_rn(v, odd_member ? -u : u);
+                            y[j] = v;
                         }
-                        y[j] = v;
-                    }
-                    float* orow = g.out + (size_t)R * g.out_stride + n0;
-                    if (g.lif) {
-                        float* prow = g.pot ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
+                        if (g.lif) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 cv = make_float4(__fmul_rn(y[j], g.leak), __fmul_rn(y[j + 1], g.leak),
-                                                    __fmul_rn(y[j + 2], g.leak), __fmul_rn(y[j + 3], g.leak));
-                            if (prow) *reinterpret_cast<float4*>(prow + j) = cv;
-                            float4 sv = make_float4(cv.x >= g.v_th ? 1.0f : 0.0f, cv.y >= g.v_th ? 1.0f : 0.0f,
-                                                    cv.z >= g.v_th ? 1.0f : 0.0f, cv.w >= g.v_th ? 1.0f : 0.0f);
-                            __stcs(reinterpret_cast<float4*>(orow + j), sv);
+                            for (int j = 0; j < 8; j += 4) {
+                                float4 cv = make_float4(__fmul_rn(y[j], g.leak), __fmul_rn(y[j + 1], g.leak),
+                                                        __fmul_rn(y[j + 2], g.leak), __fmul_rn(y[j + 3], g.leak));
+                                if (prow) *reinterpret_cast<float4*>(prow + j0 + j) = cv;
+                                float4 sv = make_float4(cv.x >= g.v_th ? 1.0f : 0.0f, cv.y >= g.v_th ? 1.0f : 0.0f,
+                                                        cv.z >= g.v_th ? 1.0f : 0.0f, cv.w >= g.v_th ? 1.0f : 0.0f);
+                                __stcs(reinterpret_cast<float4*>(orow + j0 + j), sv);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j += 4)
+                                *reinterpret_cast<float4*>(orow + j0 + j) =
+                                    make_float4(__fmul_rn(y[j], g.out_scale), __fmul_rn(y[j + 1], g.out_scale),
+                                                __fmul_rn(y[j + 2], g.out_scale), __fmul_rn(y[j + 3], g.out_scale));
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4*>(orow + j) =
-                                make_float4(__fmul_rn(y[j], g.out_scale), __fmul_rn(y[j + 1], g.out_scale),
-                                            __fmul_rn(y[j + 2], g.out_scale), __fmul_rn(y[j + 3], g.out_scale));
                     }
-                    if (g.perturb) __syncwarp();
+                    if (RG > 0) {
+                        mbar_arrive(&aempty[q4 * 3 + slot]);  // 32 arrivals hand the slot back
+                        if (slot == 0) ++used0; else if (slot == 1) ++used1; else ++used2;
+                    }
+                    if (warp == EPI_WARP0) tick(9, t2);
                 }
                 tc_fence_before();
                 mbar_arrive(&tempty[b]);
             }
         }
+    } else if (RG > 0 && (warp - GEN_WARP0) / 4 < g.ring_depth) {
+        // ------------------------------------------------------------ noise generators
+        // Generator (gq, gi) regenerates, for TMEM quadrant gq, the A rows of every 32-column
+        // block with index = gi (mod depth) into ring slot gi, scaled by base_sigma.  It runs
+        // ahead of the epilogue and never touches TMEM, so the regeneration overlaps the MMAs.
+        constexpr int RANK = RG * 4;
+        const int gq = (warp - GEN_WARP0) & 3, gi = (warp - GEN_WARP0) >> 2;
+        const int depth = g.ring_depth;
+        float* slot_a = a_stage + (gq * depth + gi) * 32 * RANK;
+        LibmCal cal = g.cal;
+        cal.log_tab = log_tab_s;
+        cal.log_delta = delta_s;
+        cal.cos_delta = delta_s + 256;
+        const int blocks_per_tile = g.a / 32;
+        const int sw = a_swizzle<RG>(lane);
+        uint32_t used = 0;
+        bool ok = true;
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+            // every row of this quadrant's 32-row slice belongs to one antithetic pair
+            int64_t member0 = (((int64_t)mt * BM_TILE + gq * 32) / g.bm) % g.n_pop;
+            int32_t pair = (g.first_thread + (int32_t)member0) / 2;
+            uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
+            uint64_t a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)RANK * (uint64_t)(g.k + gi * 32 + lane));
+            for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
+                if (!mbar_wait(&aempty[gq * 3 + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
+#pragma unroll 1
+                for (int q = 0; q < RG; ++q) {
+                    float z[4];
+                    next_normals4(a_state, cal, z);
+                    *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
+                        make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
+                                    __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));
+                }
+                a_state = jump_apply(hop_s, a_state);  // on to this generator's next block of rows
+                mbar_arrive(&afull[gq * 3 + gi]);      // 32 arrivals publish the slot
+            }
+        }
     }
 
+    if (threadIdx.x == 0) tick(11, t_kernel);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -436,6 +487,21 @@ __global__ void split_tf32_kernel(const float* __restrict__ w, int a, int k, int
     float h = to_tf32(v);
     hi[i] = h;
     lo[i] = to_tf32(v - h);
+}
+
+// Same split for four consecutive elements per thread (rows are multiples of four long and
+// 16-byte aligned on this path): streams x once and writes x_hi and x_lo.
+__global__ void split_tf32_vec4_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t stride,
+                                       float* __restrict__ hi, float* __restrict__ lo) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t per_row = (size_t)k / 4;
+    if (i >= (size_t)rows * per_row) return;
+    size_t r = i / per_row, c = (i - r * per_row) * 4;
+    float4 v = __ldcs(reinterpret_cast<const float4*>(x + r * stride + c));
+    float4 h = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
+    float4 l = make_float4(to_tf32(v.x - h.x), to_tf32(v.y - h.y), to_tf32(v.z - h.z), to_tf32(v.w - h.w));
+    *reinterpret_cast<float4*>(hi + r * (size_t)k + c) = h;
+    *reinterpret_cast<float4*>(lo + r * (size_t)k + c) = l;
 }
 
 // t[R, q] = sum_k x[R, k] * B_pair[k, q].  One CTA per antithetic pair: 128 threads
@@ -564,49 +630,74 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int64_
     return HSES_OK;
 }
 
+// cycle counters of the last launch when HSES_TC_DEBUG is set in the environment
+__device__ unsigned long long g_tc_dbg[16];
+
 struct TcScratch {
-    float *whi, *wlo, *t;
+    float *xhi, *xlo, *whi, *wlo, *t;
     size_t bytes;
 };
 TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     auto up = [](size_t v) { return (v + 63) / 64 * 64; };
     size_t nw = up((size_t)g.a * g.k);
-    size_t nt = g.perturb ? up((size_t)g.t_steps * g.n_pop * g.bm * g.rank) : 0;
+    size_t rows = (size_t)g.t_steps * g.n_pop * g.bm;
+    size_t nx = up(rows * g.k);
+    size_t nt = g.perturb ? up(rows * g.rank) : 0;
     TcScratch s;
-    s.whi = reinterpret_cast<float*>(base);
+    s.xhi = reinterpret_cast<float*>(base);
+    s.xlo = s.xhi + nx;
+    s.whi = s.xlo + nx;
     s.wlo = s.whi + nw;
     s.t = s.wlo + nw;
-    s.bytes = (2 * nw + nt) * sizeof(float);
+    s.bytes = (2 * nx + 2 * nw + nt) * sizeof(float);
     return s;
+}
+
+template <int BN, int RG>
+int launch_tc_rg(hses_ctx* ctx, cudaStream_t st, const CUtensorMap& tm_x, const CUtensorMap& tm_xlo,
+                 const CUtensorMap& tm_whi, const CUtensorMap& tm_wlo, const TcArgs& ta, int grid,
+                 int smem_bytes) {
+    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   smem_bytes));
+    HSES_KERNEL(ctx, st, "linear_tc");
+    linear_tc_kernel<BN, RG><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_xlo, tm_whi, tm_wlo, ta);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
 }
 
 template <int BN>
 int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, TcArgs ta) {
-    // two epilogue warps per TMEM quadrant when their staged A rows fit in shared memory
-    ta.epi_halves = (TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(2, ta.rank) <= TcSmem<BN>::LIMIT) ? 2 : 1;
-    ta.a_stride = ta.rank + 4;
+    // as many ring slots (and generator warps) per quadrant as shared memory allows, at most three
+    ta.ring_depth = 3;
+    while (ta.ring_depth > 1 && TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(ta.ring_depth, ta.rank) > TcSmem<BN>::LIMIT)
+        --ta.ring_depth;
     if (g.perturb) {
         const uint64_t* hop = nullptr;
-        int hrc = get_hop_table(ctx, 2ull * g.rank * (32ull * ta.epi_halves - 1), &hop);
+        int hrc = get_hop_table(ctx, 2ull * g.rank * (32ull * ta.ring_depth - 1), &hop);
         if (hrc != HSES_OK) return hrc;
         ta.hop = hop;
     }
-    CUtensorMap tm_x, tm_whi, tm_wlo;
+    CUtensorMap tm_x, tm_xlo, tm_whi, tm_wlo;
     int64_t rows = ta.rows;
-    int rc = make_map(&tm_x, g.x, rows, g.k, g.x_row_stride, BM_TILE);
+    int rc = make_map(&tm_x, sc.xhi, rows, g.k, g.k, BM_TILE);
+    if (rc == HSES_OK) rc = make_map(&tm_xlo, sc.xlo, rows, g.k, g.k, BM_TILE);
     if (rc == HSES_OK) rc = make_map(&tm_whi, sc.whi, g.a, g.k, g.k, BN);
     if (rc == HSES_OK) rc = make_map(&tm_wlo, sc.wlo, g.a, g.k, g.k, BN);
     if (rc != HSES_OK) return rc;
     using S = TcSmem<BN>;
-    int smem_bytes = S::FIXED + S::a_bytes(ta.epi_halves, ta.rank);
+    int smem_bytes = S::FIXED + S::a_bytes(ta.ring_depth, ta.rank);
     HSES_REQUIRE(smem_bytes <= S::LIMIT, "shared memory budget exceeded");
-    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
     int m_tiles = (int)(rows / BM_TILE);
     int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;
-    HSES_KERNEL(ctx, st, "linear_tc");
-    linear_tc_kernel<BN><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_whi, tm_wlo, ta);
-    HSES_LAUNCH_CHECK();
-    return HSES_OK;
+    switch (ta.rank / 4) {
+        case 0: return launch_tc_rg<BN, 0>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        case 1: return launch_tc_rg<BN, 1>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        case 2: return launch_tc_rg<BN, 2>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        case 4: return launch_tc_rg<BN, 4>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        case 8: return launch_tc_rg<BN, 8>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+    }
+    set_error("linear_tc: unsupported rank");
+    return HSES_ERR_UNSUPPORTED;
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
@@ -620,7 +711,7 @@ bool tensor_path_supports(const hses_linear_args& g) {
     if (!aligned16(g.x) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
     if (g.k > (1 << 20) || g.a > (1 << 20)) return false;
     if (g.perturb) {
-        if (g.rank > 32 || g.rank % 4 != 0) return false;
+        if (g.rank != 4 && g.rank != 8 && g.rank != 16 && g.rank != 32) return false;
         // every 32-row slice of a tile must belong to one antithetic pair
         bool pair_rows = (g.bm % 32 == 0) || (g.bm == 16 && g.first_thread % 2 == 0 && g.n_pop % 2 == 0);
         if (!pair_rows) return false;
@@ -640,6 +731,14 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         HSES_KERNEL(ctx, st, "split_tf32");
         split_tf32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
                                                                       sc.whi, sc.wlo);
+        HSES_LAUNCH_CHECK();
+    }
+    {
+        size_t n4 = (size_t)rows * (g.k / 4);
+        HSES_REQUIRE((n4 + 255) / 256 < (1ull << 31), "too many elements");
+        HSES_KERNEL(ctx, st, "split_x");
+        split_tf32_vec4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
+                                                                            sc.xlo);
         HSES_LAUNCH_CHECK();
     }
     TcArgs ta{};
@@ -666,6 +765,13 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.cal = ctx->cal();
     ta.status = ctx->t.status_word;
     ta.hop = nullptr;
+    ta.dbg = nullptr;
+    if (getenv("HSES_TC_DEBUG")) {
+        void* p = nullptr;
+        HSES_CUDA(cudaGetSymbolAddress(&p, g_tc_dbg));
+        HSES_CUDA(cudaMemsetAsync(p, 0, sizeof(unsigned long long) * 16, st));
+        ta.dbg = reinterpret_cast<unsigned long long*>(p);
+    }
     if (g.perturb) {
         const uint64_t* hop127 = nullptr;
         int rc = get_hop_table(ctx, 2ull * g.rank * 127, &hop127);
@@ -682,3 +788,12 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
 }
 
 }  // namespace hses
+
+// Diagnostic, not part of the declared ABI: copies the role cycle counters of the
+// last tensor-path launch made with HSES_TC_DEBUG set (synchronises the device).
+extern "C" int hses_internal_tc_cycles(unsigned long long* out16) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, hses::g_tc_dbg) != cudaSuccess) return 2;
+    if (cudaMemcpy(out16, p, sizeof(unsigned long long) * 16, cudaMemcpyDeviceToHost) != cudaSuccess) return 2;
+    return 0;
+}
