@@ -20,6 +20,7 @@
 // runs out records a code in the context's status word, all roles leave their
 // loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <stdlib.h>
 
 #include "linear.cuh"
@@ -29,7 +30,7 @@ namespace hses {
 namespace {
 
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
-constexpr int BK = 32;            // fp32 elements per k-block = one 128 B swizzle row
+constexpr int BK = 64;            // fp16 elements per k-block = one 128 B swizzle row
 // warps: 0 TMA, 1 MMA, 2-5 epilogue (one per TMEM quadrant), 6-17 noise generators
 constexpr int NTHREADS = 576;
 constexpr int EPI_WARP0 = 2;
@@ -83,11 +84,11 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                           uint32_t accumulate) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -138,9 +139,9 @@ template <int RG>
 __device__ __forceinline__ int a_swizzle(int row) {
     return RG <= 1 ? 0 : ((row * RG) >> 3) & (RG - 1);
 }
-// kind::tf32, fp32 accumulator, both operands K-major, M = 128, N = bn.
+// kind::f16 with fp16 operands (format 0), fp32 accumulator, both operands K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t make_idesc(int bn) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
 struct TcArgs {
@@ -154,6 +155,8 @@ struct TcArgs {
     int32_t true_epoch, first_thread;
     float base_sigma, leak, v_th, out_scale;
     const float* t;       // (rows, rank)
+    const float* row_scale;  // (rows): 2^-e of the power-of-two scale applied to each x row
+    const float* col_scale;  // (a):    the same for each row of the parameter
     float* out;
     int64_t out_stride;
     float* pot;
@@ -168,8 +171,8 @@ struct TcArgs {
 template <int BN>
 struct TcSmem {
     static constexpr int STAGES = BN == 256 ? 2 : 3;
-    static constexpr int X_BYTES = BM_TILE * BK * 4;
-    static constexpr int W_BYTES = BN * BK * 4;
+    static constexpr int X_BYTES = BM_TILE * BK * 2;
+    static constexpr int W_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
     static constexpr int HOP_BYTES = kJumpWords * 8;
     static constexpr int TAB_BYTES = 1024 + 2 * 1024;  // log helper table + two threshold tables
@@ -213,7 +216,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (int)(g.rows / BM_TILE);
     const int n_chunks = g.a / BN;
-    const int k_blocks = g.k / BK;
+    const int k_blocks = (g.k + BK - 1) / BK;  // a ragged last block is zero-filled by TMA
 
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
@@ -317,11 +320,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         uint64_t dwh = make_smem_desc(st + 2 * S::X_BYTES);
                         uint64_t dwl = make_smem_desc(st + 2 * S::X_BYTES + S::W_BYTES);
 #pragma unroll
-                        for (int ks = 0; ks < BK / 8; ++ks) {
-                            uint64_t off = (uint64_t)(ks * 32 >> 4);  // 8 tf32 = 32 B along K
-                            umma_tf32(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
-                            umma_tf32(d, dxh + off, dwl + off, idesc, 1);
-                            umma_tf32(d, dxh + off, dwh + off, idesc, 1);
+                        for (int ks = 0; ks < BK / 16; ++ks) {
+                            uint64_t off = (uint64_t)(ks * 32 >> 4);  // 16 fp16 = 32 B along K
+                            umma_f16(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
+                            umma_f16(d, dxh + off, dwl + off, idesc, 1);
+                            umma_f16(d, dxh + off, dwh + off, idesc, 1);
                         }
                         umma_commit(&empty[s]);
                     }
@@ -341,6 +344,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
             float tq[RANK > 0 ? RANK : 1];
             bool odd_member = false;
+            const float rs = g.row_scale[R];
             if (RG > 0) {
                 int64_t member = (R / g.bm) % g.n_pop;
                 int32_t thread_id = g.first_thread + (int32_t)member;
@@ -379,9 +383,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         uint32_t acc[8];
                         tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + j0), acc);
                         float y[8];
+                        const float4 cs0 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0);
+                        const float4 cs1 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0 + 4);
+                        const float cs[8] = {cs0.x, cs0.y, cs0.z, cs0.w, cs1.x, cs1.y, cs1.z, cs1.w};
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            float v = __uint_as_float(acc[j]);
+                            // undo the two power-of-two operand scales (exact)
+                            float v = __fmul_rn(__fmul_rn(__uint_as_float(acc[j]), rs), cs[j]);
                             if (RG > 0) {
                                 // u = sum_q t[q] * (base_sigma * A[n0+j0+j][q]); the member's sign is applied to
                                 // the finished sum (negating every term of a sum negates the sum exactly)
@@ -478,30 +486,50 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 }
 
 // ------------------------------------------------------------ auxiliary kernels
-__global__ void split_tf32_kernel(const float* __restrict__ w, int a, int k, int64_t stride,
-                                  float* __restrict__ hi, float* __restrict__ lo) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (size_t)a * k) return;
-    size_t r = i / k, c = i - r * k;
-    float v = w[r * stride + c];
-    float h = to_tf32(v);
-    hi[i] = h;
-    lo[i] = to_tf32(v - h);
-}
-
-// Same split for four consecutive elements per thread (rows are multiples of four long and
-// 16-byte aligned on this path): streams x once and writes x_hi and x_lo.
-__global__ void split_tf32_vec4_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t stride,
-                                       float* __restrict__ hi, float* __restrict__ lo) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    size_t per_row = (size_t)k / 4;
-    if (i >= (size_t)rows * per_row) return;
-    size_t r = i / per_row, c = (i - r * per_row) * 4;
-    float4 v = __ldcs(reinterpret_cast<const float4*>(x + r * stride + c));
-    float4 h = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-    float4 l = make_float4(to_tf32(v.x - h.x), to_tf32(v.y - h.y), to_tf32(v.z - h.z), to_tf32(v.w - h.w));
-    *reinterpret_cast<float4*>(hi + r * (size_t)k + c) = h;
-    *reinterpret_cast<float4*>(lo + r * (size_t)k + c) = l;
+// Operand preparation: every row is multiplied by a power of two that brings its largest
+// magnitude into [2^13, 2^14) and then split into two fp16 values, hi = fp16(v) and
+// lo = fp16(v - hi).  hi + lo carries 22 significant bits of v, and three fp16 MMA passes
+// (hi*hi + hi*lo + lo*hi, fp32 accumulate) give fp32-equivalent products at the fp16 tensor
+// rate and with half the shared-memory traffic of a TF32 split.  The scales are undone exactly
+// in the epilogue.  One warp per row; rows are multiples of four long and 16-byte aligned.
+__global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t stride,
+                                      __half* __restrict__ hi, __half* __restrict__ lo,
+                                      float* __restrict__ inv_scale) {
+    int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)r * stride);
+    int n4 = k >> 2;
+    float m = 0.0f;
+    for (int i = lane; i < n4; i += 32) {
+        float4 v = src[i];
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    // exponent of the row maximum; zero, denormal, infinite or NaN rows keep scale 1
+    int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
+    int e = 13 - ex;
+    if (ex <= -127 || ex >= 128) e = 0;
+    if (e > 100) e = 100;
+    if (e < -100) e = -100;
+    float s = __uint_as_float((uint32_t)(127 + e) << 23);
+    if (lane == 0) inv_scale[r] = __uint_as_float((uint32_t)(127 - e) << 23);
+    uint2* dh = reinterpret_cast<uint2*>(hi + (size_t)r * k);
+    uint2* dl = reinterpret_cast<uint2*>(lo + (size_t)r * k);
+    for (int i = lane; i < n4; i += 32) {
+        float4 v = src[i];
+        float f[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
+        __half h[4], l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h[j] = __float2half_rn(f[j]);
+            l[j] = __float2half_rn(f[j] - __half2float(h[j]));
+        }
+        dh[i] = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16),
+                           (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+        dl[i] = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
+                           (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+    }
 }
 
 // t[R, q] = sum_k x[R, k] * B_pair[k, q].  One CTA per antithetic pair: 128 threads
@@ -609,18 +637,18 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D fp32 map over (rows, cols) with `stride` floats between rows; box = (32, box_rows).
-int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int64_t stride, int box_rows) {
+// 2-D fp16 map over (rows, cols) with `stride` elements between rows; box = (64, box_rows).
+int make_map(CUtensorMap* map, const __half* base, int64_t rows, int cols, int64_t stride, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
         return HSES_ERR_CUDA;
     }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)stride * 4};
+    cuuint64_t strides[1] = {(cuuint64_t)stride * 2};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -634,22 +662,24 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int cols, int64_
 __device__ unsigned long long g_tc_dbg[16];
 
 struct TcScratch {
-    float *xhi, *xlo, *whi, *wlo, *t;
+    __half *xhi, *xlo, *whi, *wlo;
+    float *rs, *cs, *t;
     size_t bytes;
 };
 TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     auto up = [](size_t v) { return (v + 63) / 64 * 64; };
-    size_t nw = up((size_t)g.a * g.k);
     size_t rows = (size_t)g.t_steps * g.n_pop * g.bm;
-    size_t nx = up(rows * g.k);
-    size_t nt = g.perturb ? up(rows * g.rank) : 0;
+    size_t nw = up((size_t)g.a * g.k), nx = up(rows * g.k);   // fp16 elements
+    size_t nt = g.perturb ? up(rows * g.rank) : 0;             // floats
     TcScratch s;
-    s.xhi = reinterpret_cast<float*>(base);
+    s.xhi = reinterpret_cast<__half*>(base);
     s.xlo = s.xhi + nx;
     s.whi = s.xlo + nx;
     s.wlo = s.whi + nw;
-    s.t = s.wlo + nw;
-    s.bytes = (2 * nx + 2 * nw + nt) * sizeof(float);
+    s.rs = reinterpret_cast<float*>(s.wlo + nw);
+    s.cs = s.rs + up(rows);
+    s.t = s.cs + up((size_t)g.a);
+    s.bytes = (2 * nx + 2 * nw) * sizeof(__half) + (up(rows) + up((size_t)g.a) + nt) * sizeof(float);
     return s;
 }
 
@@ -706,9 +736,9 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
 bool tensor_path_supports(const hses_linear_args& g) {
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
-    if (rows % BM_TILE != 0 || g.k % BK != 0 || g.a % 128 != 0) return false;
-    if (g.x_row_stride % 4 != 0 || g.out_row_stride % 4 != 0) return false;
-    if (!aligned16(g.x) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
+    if (rows % BM_TILE != 0 || g.k % 8 != 0 || g.a % 128 != 0) return false;
+    if (g.x_row_stride % 4 != 0 || g.out_row_stride % 4 != 0 || g.param_row_stride % 4 != 0) return false;
+    if (!aligned16(g.x) || !aligned16(g.param) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
     if (g.k > (1 << 20) || g.a > (1 << 20)) return false;
     if (g.perturb) {
         if (g.rank != 4 && g.rank != 8 && g.rank != 16 && g.rank != 32) return false;
@@ -727,18 +757,15 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
                  "workspace too small or misaligned; see hses_perturbed_linear_workspace_bytes");
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
     {
-        size_t n = (size_t)g.a * g.k;
-        HSES_KERNEL(ctx, st, "split_tf32");
-        split_tf32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
-                                                                      sc.whi, sc.wlo);
+        HSES_KERNEL(ctx, st, "split_w");
+        split_f16_rows_kernel<<<(unsigned)((g.a + 7) / 8), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
+                                                                        sc.whi, sc.wlo, sc.cs);
         HSES_LAUNCH_CHECK();
     }
     {
-        size_t n4 = (size_t)rows * (g.k / 4);
-        HSES_REQUIRE((n4 + 255) / 256 < (1ull << 31), "too many elements");
         HSES_KERNEL(ctx, st, "split_x");
-        split_tf32_vec4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
-                                                                            sc.xlo);
+        split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
+                                                                         sc.xlo, sc.rs);
         HSES_LAUNCH_CHECK();
     }
     TcArgs ta{};
@@ -758,6 +785,8 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.v_th = g.v_th;
     ta.out_scale = g.out_scale;
     ta.t = sc.t;
+    ta.row_scale = sc.rs;
+    ta.col_scale = sc.cs;
     ta.out = g.out;
     ta.out_stride = g.out_row_stride;
     ta.pot = g.lif ? g.potentials : nullptr;
