@@ -31,10 +31,10 @@ namespace {
 
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
 constexpr int BK = 64;            // fp16 elements per k-block = one 128 B swizzle row
-// warps: 0 TMA, 1 MMA, 2-5 epilogue (one per TMEM quadrant), 6-17 noise generators
-constexpr int NTHREADS = 576;
+// warps: 0 TMA, 1 MMA, 2-9 epilogue (two per TMEM quadrant), 10-21 noise generators
+constexpr int NTHREADS = 704;
 constexpr int EPI_WARP0 = 2;
-constexpr int GEN_WARP0 = 6;
+constexpr int GEN_WARP0 = 10;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 // ------------------------------------------------------------------ PTX helpers
@@ -65,13 +65,18 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
+    // status word: bit (code) = this wait ran out; bit (16 + code) = a role was parked in
+    // this wait when another one gave up
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
+        if (*abort_flag) {
+            atomicOr(status, 1 << (16 + code));
+            return false;
+        }
         if (i > 64) __nanosleep(64);
     }
     *abort_flag = 1;
-    atomicCAS(status, 0, code);
+    atomicOr(status, 1 << code);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -227,11 +232,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull[b], 1);
-            mbar_init(&tempty[b], 128);
+            mbar_init(&tempty[b], 256);
         }
         for (int i = 0; i < 12; ++i) {
             mbar_init(&afull[i], 32);
-            mbar_init(&aempty[i], 32);
+            mbar_init(&aempty[i], 64);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -333,14 +338,20 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             }
         }
     } else if (warp < GEN_WARP0) {
-        // ------------------------------------------------ epilogue (one warp per TMEM quadrant)
+        // ----------------------------------------------- epilogue (two warps per TMEM quadrant:
+        // warp (q4, eh) takes columns [16*eh, 16*eh+16) of every 32-column block.  Both warps
+        // therefore consume every use of every ring slot in order, so a waiter is never more than
+        // one barrier phase behind — alternating whole blocks between the warps would let a
+        // parity wait alias with an older phase.)
         constexpr int RANK = RG * 4;
         const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
+        const int eh = (warp - EPI_WARP0) >> 2;
         const int depth = g.ring_depth;
+        const int blocks_per_tile = g.a / 32;
         uint32_t acc_it = 0;
-        uint32_t used0 = 0, used1 = 0, used2 = 0;  // how often each ring slot of this quadrant was consumed
+        int tile_no = 0;  // M tiles this CTA has finished: fixes how often each ring slot was used
         bool ok = true;
-        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++tile_no) {
             const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
             float tq[RANK > 0 ? RANK : 1];
             bool odd_member = false;
@@ -355,22 +366,24 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     tq[q] = tv.x; tq[q + 1] = tv.y; tq[q + 2] = tv.z; tq[q + 3] = tv.w;
                 }
             }
-            int blk = 0;  // 32-column block index inside this M tile
             for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                 int b = acc_it & 1;
                 long long t0 = clock64();
                 if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
                 if (warp == EPI_WARP0) tick(7, t0);
                 tc_fence_after();
-                for (int cb = 0; cb < BN / 32 && ok; ++cb, ++blk) {
+                for (int cb = 0; cb < BN / 32 && ok; ++cb) {
                     const int n0 = c * BN + cb * 32;
+                    const int blk = n0 >> 5;  // 32-column block index inside this M tile
                     const float* my_a = nullptr;
                     int slot = 0;
                     long long t2 = clock64();
                     if (RG > 0) {
                         // the generator warps of this quadrant have staged the A rows n0..n0+31
                         slot = blk % depth;
-                        uint32_t u = slot == 0 ? used0 : (slot == 1 ? used1 : used2);
+                        // uses of this slot so far: (blocks_per_tile - slot + depth - 1) / depth per finished tile
+                        uint32_t u = (uint32_t)tile_no * (uint32_t)((blocks_per_tile - slot + depth - 1) / depth) +
+                                     (uint32_t)(blk / depth);
                         if (!mbar_wait(&afull[q4 * 3 + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
                         my_a = a_stage + (q4 * depth + slot) * 32 * RANK;
                     }
@@ -379,7 +392,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     float* orow = g.out + (size_t)R * g.out_stride + n0;
                     float* prow = (g.lif && g.pot) ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
 #pragma unroll 1
-                    for (int j0 = 0; j0 < 32; j0 += 8) {
+                    for (int j0 = eh * 16; j0 < eh * 16 + 16; j0 += 8) {
                         uint32_t acc[8];
                         tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + j0), acc);
                         float y[8];
@@ -428,8 +441,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         }
                     }
                     if (RG > 0) {
-                        mbar_arrive(&aempty[q4 * 3 + slot]);  // 32 arrivals hand the slot back
-                        if (slot == 0) ++used0; else if (slot == 1) ++used1; else ++used2;
+                        mbar_arrive(&aempty[q4 * 3 + slot]);  // 64 arrivals (both warps) hand the slot back
                     }
                     if (warp == EPI_WARP0) tick(9, t2);
                 }
