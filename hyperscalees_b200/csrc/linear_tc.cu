@@ -544,20 +544,23 @@ __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows,
     }
 }
 
-// t[R, q] = sum_k x[R, k] * B_pair[k, q].  One CTA per antithetic pair: 128 threads
-// regenerate 128 rows of B into shared memory (thread j owns rows j, j+128, ...),
-// then every thread accumulates four q's of one x row over that block.
+// Per antithetic pair (one CTA): t[R, q] = sum_k x[R, k] * B_pair[k, q] for the pair's rows, with
+// B regenerated block by block into shared memory (thread j owns B rows j, j+128, ...), and, on
+// the way, the fp16 hi/lo split of those x rows (see split_f16_rows_kernel) so that x is read
+// from HBM once.  RANK_G = rank / 4.
 constexpr int LT_THREADS = 128;
+template <int RANK_G>
 __global__ void __launch_bounds__(LT_THREADS)
 lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop127,
                  uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
-                 int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, int rank,
-                 float* __restrict__ t) {
-    extern __shared__ float bs[];  // 128 x rank
+                 int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
+                 __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale) {
+    constexpr int RANK = RANK_G * 4;
+    __shared__ __align__(16) float bs[LT_THREADS * RANK];  // one block of B: 128 rows x rank
     __shared__ uint64_t hop_s[kJumpWords];
     __shared__ double2 log_tab_s[64];
     __shared__ uint32_t delta_s[512];
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < kJumpWords; i += LT_THREADS) hop_s[i] = hop127[i];
     for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
     for (int i = tid; i < 256; i += LT_THREADS) {
@@ -575,13 +578,53 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     if (m_hi > n_pop) m_hi = n_pop;
     const int rows_per_step = (int)(m_hi - m_lo) * bm;
     const int total_rows = rows_per_step * t_steps;
-    const int qgroups = (rank + 3) / 4;
+    auto global_row = [&](int lr) -> int64_t {
+        int step = lr / rows_per_step, rr = lr - step * rows_per_step;
+        return ((int64_t)step * n_pop + m_lo) * bm + rr;
+    };
+
+    // ---- operand split of this pair's x rows (one warp per row) ----
+    const int n4 = k >> 2;
+    for (int lr = warp; lr < total_rows; lr += LT_THREADS / 32) {
+        const int64_t R = global_row(lr);
+        const float4* src = reinterpret_cast<const float4*>(x + (size_t)R * x_stride);
+        float m = 0.0f;
+        for (int i = lane; i < n4; i += 32) {
+            float4 v = src[i];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
+        int e = 13 - ex;
+        if (ex <= -127 || ex >= 128) e = 0;
+        if (e > 100) e = 100;
+        if (e < -100) e = -100;
+        float sc = __uint_as_float((uint32_t)(127 + e) << 23);
+        if (lane == 0) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
+        uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R * k);
+        uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R * k);
+        for (int i = lane; i < n4; i += 32) {
+            float4 v = src[i];
+            float f[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+            uint32_t hb[4], lb[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __half h = __float2half_rn(f[j]);
+                hb[j] = __half_as_ushort(h);
+                lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
+            }
+            dh[i] = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+            dl[i] = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+        }
+    }
+
+    // ---- t = x * B ----
     uint64_t s = noise_seed(key, true_epoch, pair) | 1ull;
-    s = jump_by(pow2, s, 2ull * (uint64_t)rank * (uint64_t)tid);
+    s = jump_by(pow2, s, 2ull * (uint64_t)RANK * (uint64_t)tid);
     __syncthreads();
-    // work items: (row, q-group); each thread keeps up to 8 of them in registers
-    constexpr int MAXI = 8;
-    const int items = total_rows * qgroups;
+    // work items: (row, q-group of four); each thread keeps up to MAXI of them in registers
+    constexpr int MAXI = 4;
+    const int items = total_rows * RANK_G;
     for (int base = 0; base < items; base += LT_THREADS * MAXI) {
         float acc[MAXI][4];
 #pragma unroll
@@ -589,30 +632,38 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         uint64_t sb = s;  // every pass over the items replays the pair's B stream
         for (int k0 = 0; k0 < k; k0 += LT_THREADS) {
             if (k0 + tid < k) {
-                for (int q = 0; q < rank; q += 4) {  // rank is a multiple of 4 on this path
+#pragma unroll 1
+                for (int q = 0; q < RANK; q += 4) {
                     float z[4];
                     next_normals4(sb, cal, z);
-                    *reinterpret_cast<float4*>(bs + tid * rank + q) = make_float4(z[0], z[1], z[2], z[3]);
+                    *reinterpret_cast<float4*>(bs + tid * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
                 }
                 sb = jump_apply(hop_s, sb);
             }
             __syncthreads();
-            const int kn = k - k0 < LT_THREADS ? k - k0 : LT_THREADS;
+            const int kn = k - k0 < LT_THREADS ? k - k0 : LT_THREADS;  // multiple of 4
 #pragma unroll
             for (int i = 0; i < MAXI; ++i) {
                 int item = base + tid + i * LT_THREADS;
                 if (item < items) {
-                    int lr = item / qgroups, qg = item - lr * qgroups;
-                    int step = lr / rows_per_step, rr = lr - step * rows_per_step;
-                    int64_t R = ((int64_t)step * n_pop + m_lo) * bm + rr;
-                    const float* xr = x + (size_t)R * x_stride + k0;
-                    for (int kk = 0; kk < kn; ++kk) {
-                        float xv = xr[kk];
-                        const float* br = bs + kk * rank + qg * 4;
-                        acc[i][0] = fmaf(xv, br[0], acc[i][0]);
-                        if (qg * 4 + 1 < rank) acc[i][1] = fmaf(xv, br[1], acc[i][1]);
-                        if (qg * 4 + 2 < rank) acc[i][2] = fmaf(xv, br[2], acc[i][2]);
-                        if (qg * 4 + 3 < rank) acc[i][3] = fmaf(xv, br[3], acc[i][3]);
+                    int lr = item / RANK_G, qg = item - lr * RANK_G;
+                    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)global_row(lr) * x_stride + k0);
+                    const float* bq = bs + qg * 4;
+#pragma unroll 2
+                    for (int kk = 0; kk < kn; kk += 4) {
+                        float4 xv = xr[kk >> 2];
+                        float4 b0 = *reinterpret_cast<const float4*>(bq + (kk + 0) * RANK);
+                        float4 b1 = *reinterpret_cast<const float4*>(bq + (kk + 1) * RANK);
+                        float4 b2 = *reinterpret_cast<const float4*>(bq + (kk + 2) * RANK);
+                        float4 b3 = *reinterpret_cast<const float4*>(bq + (kk + 3) * RANK);
+                        acc[i][0] = fmaf(xv.x, b0.x, acc[i][0]); acc[i][1] = fmaf(xv.x, b0.y, acc[i][1]);
+                        acc[i][2] = fmaf(xv.x, b0.z, acc[i][2]); acc[i][3] = fmaf(xv.x, b0.w, acc[i][3]);
+                        acc[i][0] = fmaf(xv.y, b1.x, acc[i][0]); acc[i][1] = fmaf(xv.y, b1.y, acc[i][1]);
+                        acc[i][2] = fmaf(xv.y, b1.z, acc[i][2]); acc[i][3] = fmaf(xv.y, b1.w, acc[i][3]);
+                        acc[i][0] = fmaf(xv.z, b2.x, acc[i][0]); acc[i][1] = fmaf(xv.z, b2.y, acc[i][1]);
+                        acc[i][2] = fmaf(xv.z, b2.z, acc[i][2]); acc[i][3] = fmaf(xv.z, b2.w, acc[i][3]);
+                        acc[i][0] = fmaf(xv.w, b3.x, acc[i][0]); acc[i][1] = fmaf(xv.w, b3.y, acc[i][1]);
+                        acc[i][2] = fmaf(xv.w, b3.z, acc[i][2]); acc[i][3] = fmaf(xv.w, b3.w, acc[i][3]);
                     }
                 }
             }
@@ -622,11 +673,9 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         for (int i = 0; i < MAXI; ++i) {
             int item = base + tid + i * LT_THREADS;
             if (item < items) {
-                int lr = item / qgroups, qg = item - lr * qgroups;
-                int step = lr / rows_per_step, rr = lr - step * rows_per_step;
-                int64_t R = ((int64_t)step * n_pop + m_lo) * bm + rr;
-                for (int j = 0; j < 4; ++j)
-                    if (qg * 4 + j < rank) t[(size_t)R * rank + qg * 4 + j] = acc[i][j];
+                int lr = item / RANK_G, qg = item - lr * RANK_G;
+                *reinterpret_cast<float4*>(t + (size_t)global_row(lr) * RANK + qg * 4) =
+                    make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
             }
         }
     }
@@ -774,7 +823,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
                                                                         sc.whi, sc.wlo, sc.cs);
         HSES_LAUNCH_CHECK();
     }
-    {
+    if (!g.perturb) {  // with noise the pair kernel below splits x while it computes t
         HSES_KERNEL(ctx, st, "split_x");
         split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
                                                                          sc.xlo, sc.rs);
@@ -819,9 +868,17 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         if (rc != HSES_OK) return rc;
         int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
         HSES_KERNEL(ctx, st, "lowrank_t");
-        lowrank_t_kernel<<<(unsigned)pairs, LT_THREADS, LT_THREADS * g.rank * sizeof(float), st>>>(
-            ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,
-            g.t_steps, g.n_pop, g.bm, g.k, g.rank, sc.t);
+#define HSES_LT(RG)                                                                                          \
+    lowrank_t_kernel<RG><<<(unsigned)pairs, LT_THREADS, 0, st>>>(                                            \
+        ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
+        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs)
+        switch (g.rank / 4) {
+            case 1: HSES_LT(1); break;
+            case 2: HSES_LT(2); break;
+            case 4: HSES_LT(4); break;
+            default: HSES_LT(8); break;
+        }
+#undef HSES_LT
         HSES_LAUNCH_CHECK();
     }
     if (g.a % 256 == 0) return launch_tc<256>(ctx, st, g, sc, ta);
