@@ -300,3 +300,57 @@ def base_sigma(sigma: float, rank: int) -> float:
     (eggroll.rs:365, 433)."""
     import numpy as np
     return float(np.float32(sigma) / np.sqrt(np.float32(rank)))
+
+
+class HostPipeline:
+    """Runs `perturbed_linear` for host-resident inputs and outputs.
+
+    The population is cut into member chunks; the host-to-device copy of chunk c+1, the kernels
+    of chunk c and the device-to-host copy of chunk c-1 run on three streams, so that a step
+    costs about max(copy in, compute, copy out) instead of their sum.  `x_host` and `out_host`
+    must be pinned.  Only single-time-step inputs (n_pop, bm, k) are cut this way.
+    """
+
+    def __init__(self, n_pop: int, bm: int, k: int, a: int, chunks: int = 8, device=None):
+        ctx = get_context(device)
+        self.dev = torch.device("cuda", ctx.device)
+        if n_pop % (2 * chunks) != 0:
+            raise ValueError("n_pop must be a multiple of 2*chunks (chunks hold whole antithetic pairs)")
+        self.n_pop, self.bm, self.k, self.a, self.chunks = n_pop, bm, k, a, chunks
+        self.mc = n_pop // chunks
+        self.x_dev = [torch.empty((self.mc, bm, k), dtype=torch.float32, device=self.dev) for _ in range(2)]
+        self.o_dev = [torch.empty((self.mc * bm, a), dtype=torch.float32, device=self.dev) for _ in range(2)]
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+
+    def run(self, x_host: torch.Tensor, param: torch.Tensor, out_host: torch.Tensor, first_thread: int = 0, **kw):
+        if not (x_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("x_host and out_host must be pinned host tensors")
+        cur = torch.cuda.current_stream(self.dev)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_event(start)
+        ev_in, ev_run, ev_out = [], [], []
+        rows = self.mc * self.bm
+        for c in range(self.chunks):
+            b = c & 1
+            lo = c * self.mc
+            with torch.cuda.stream(self.s_in):
+                if c >= 2:
+                    self.s_in.wait_event(ev_run[c - 2])      # the kernels of chunk c-2 have read x_dev[b]
+                self.x_dev[b].copy_(x_host[lo:lo + self.mc], non_blocking=True)
+                e = torch.cuda.Event(); e.record(self.s_in); ev_in.append(e)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(ev_in[c])
+                if c >= 2:
+                    self.s_run.wait_event(ev_out[c - 2])     # o_dev[b] has been copied out
+                perturbed_linear(self.x_dev[b], param, n_pop=self.mc, bm=self.bm, first_thread=first_thread + lo,
+                                 out=self.o_dev[b], **kw)
+                e = torch.cuda.Event(); e.record(self.s_run); ev_run.append(e)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_run[c])
+                out_host[lo * self.bm:lo * self.bm + rows].copy_(self.o_dev[b], non_blocking=True)
+                e = torch.cuda.Event(); e.record(self.s_out); ev_out.append(e)
+        cur.wait_event(ev_out[-1])
+        cur.wait_event(ev_run[-1])
+        return out_host
