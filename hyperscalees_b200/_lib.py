@@ -23,7 +23,9 @@ EXPORTS = [
     "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
     "hses_member_mean", "hses_convert_fitnesses", "hses_es_update_workspace_bytes",
     "hses_es_update", "hses_es_update_static_scratch_bytes", "hses_es_update_static",
-    "hses_es_update_dense", "hses_solver_step",
+    "hses_es_update_dense", "hses_solver_step", "hses_snn_forward_workspace_bytes", "hses_snn_forward",
+    "hses_population_eval_workspace_bytes", "hses_population_eval", "hses_population_update_workspace_bytes",
+    "hses_population_update",
 ]
 
 
@@ -34,10 +36,23 @@ class LinearArgs(C.Structure):
         ("param_row_stride", C.c_int64), ("sigma", C.c_float), ("rank", C.c_int32),
         ("key", C.c_uint64), ("epoch", C.c_int32), ("first_thread", C.c_int32),
         ("noise_reuse", C.c_int32), ("perturb", C.c_int32), ("lif", C.c_int32),
-        ("tau_m", C.c_float), ("v_th", C.c_float), ("reset_mode", C.c_int32), ("out_scale", C.c_float), ("out", C.c_void_p),
+        ("tau_m", C.c_float), ("v_th", C.c_float), ("reset_mode", C.c_int32), ("out_scale", C.c_float), ("out_scale_ptr", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
+
+
+class SnnModelDesc(C.Structure):
+    _fields_ = [("n_layers", C.c_int32), ("dims", C.POINTER(C.c_int32)), ("weights", C.POINTER(C.c_void_p)),
+                ("weight_strides", C.POINTER(C.c_int64)), ("keys", C.POINTER(C.c_uint64)),
+                ("out_gain", C.c_float), ("out_gain_dev", C.c_void_p), ("tau_m", C.c_float),
+                ("v_th", C.POINTER(C.c_float)), ("reset_mode", C.c_int32)]
+
+
+class PopArgs(C.Structure):
+    _fields_ = [("T", C.c_int32), ("n_pop", C.c_int64), ("bm", C.c_int32), ("perturb", C.c_int32),
+                ("sigma", C.c_float), ("rank", C.c_int32), ("epoch", C.c_int32), ("first_thread", C.c_int32),
+                ("noise_reuse", C.c_int32)]
 
 
 class SolverDesc(C.Structure):
@@ -97,6 +112,18 @@ def load():
     L.hses_es_update_static.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp]
     L.hses_es_update_dense.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, f32, vp, vp]
     L.hses_solver_step.argtypes = [vp, vp, C.POINTER(SolverDesc), i32, f32, vp, vp, vp, vp, i64]
+    pm, pp = C.POINTER(SnnModelDesc), C.POINTER(PopArgs)
+    L.hses_snn_forward_workspace_bytes.restype = sz
+    L.hses_snn_forward_workspace_bytes.argtypes = [pm, pp]
+    L.hses_snn_forward.argtypes = [vp, vp, pm, pp, vp, i64, vp, vp, sz]
+    L.hses_population_eval_workspace_bytes.restype = sz
+    L.hses_population_eval_workspace_bytes.argtypes = [pm, pp]
+    L.hses_population_eval.argtypes = [vp, vp, pm, pp, vp, i64, vp, C.POINTER(C.c_uint32), i32, vp, vp, vp, sz]
+    L.hses_population_update_workspace_bytes.restype = sz
+    L.hses_population_update_workspace_bytes.argtypes = [pm, i32, i64]
+    L.hses_population_update.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64,
+                                         C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                         vp, sz]
     for name in EXPORTS:
         fn = getattr(L, name)
         if fn.restype is C.c_int and name not in ("hses_version",):

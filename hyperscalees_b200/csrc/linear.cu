@@ -77,6 +77,7 @@ constexpr int TM = 128, TN = 128, TK = 16, TT = 256;  // tile sizes, threads
 struct EpilogueArgs {
     int perturb, lif, reset;
     float base_sigma, leak, v_th, out_scale;
+    const float* out_scale_ptr;
     int rank, bm;
     int64_t n_pop;
     int32_t first_thread, first_pair;
@@ -163,7 +164,7 @@ linear_simt_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t x_s
                 if (ep.pot) ep.pot[o] = c;
                 ep.out[o] = c >= ep.v_th ? 1.0f : 0.0f;
             } else {
-                ep.out[o] = __fmul_rn(y, ep.out_scale);
+                ep.out[o] = __fmul_rn(y, ep.out_scale_ptr ? *ep.out_scale_ptr : ep.out_scale);
             }
         }
     }
@@ -207,6 +208,7 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ep.leak = g.lif ? 1.0f / g.tau_m : 0.0f;
     ep.v_th = g.v_th;
     ep.out_scale = g.out_scale;
+    ep.out_scale_ptr = g.out_scale_ptr;
     if (g.perturb) {
         SimtScratch s = simt_scratch(g, g.workspace);
         HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= s.bytes,

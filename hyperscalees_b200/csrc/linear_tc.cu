@@ -160,6 +160,7 @@ struct TcArgs {
     int32_t true_epoch, first_thread;
     float base_sigma, leak, v_th, out_scale;
     const float* t;       // (rows, rank)
+    const float* out_scale_ptr;  // device gain overriding out_scale, or NULL
     const float* row_scale;  // (rows): 2^-e of the power-of-two scale applied to each x row
     const float* col_scale;  // (a):    the same for each row of the parameter
     float* out;
@@ -346,6 +347,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         constexpr int RANK = RG * 4;
         const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
         const int eh = (warp - EPI_WARP0) >> 2;
+        const float out_scale = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
         const int depth = g.ring_depth;
         const int blocks_per_tile = g.a / 32;
         uint32_t acc_it = 0;
@@ -436,8 +438,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 #pragma unroll
                             for (int j = 0; j < 8; j += 4)
                                 *reinterpret_cast<float4*>(orow + j0 + j) =
-                                    make_float4(__fmul_rn(y[j], g.out_scale), __fmul_rn(y[j + 1], g.out_scale),
-                                                __fmul_rn(y[j + 2], g.out_scale), __fmul_rn(y[j + 3], g.out_scale));
+                                    make_float4(__fmul_rn(y[j], out_scale), __fmul_rn(y[j + 1], out_scale),
+                                                __fmul_rn(y[j + 2], out_scale), __fmul_rn(y[j + 3], out_scale));
                         }
                     }
                     if (RG > 0) {
@@ -845,6 +847,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.leak = g.lif ? 1.0f / g.tau_m : 0.0f;
     ta.v_th = g.v_th;
     ta.out_scale = g.out_scale;
+    ta.out_scale_ptr = g.out_scale_ptr;
     ta.t = sc.t;
     ta.row_scale = sc.rs;
     ta.col_scale = sc.cs;

@@ -124,3 +124,98 @@ class SnnModel(SnnMlp):
         frozen, noiser, base_keys, info = noise
         return self.forward_population(xx, frozen, noiser, base_keys, epoch=info.epoch,
                                        first_thread=info.thread_id)
+
+
+class PopulationStep:
+    """Drives the composite C entry points (`hses_population_eval` / `hses_population_update`):
+    encode -> perturbed forward -> fitness on this rank's shard, then — after the caller has
+    all-gathered the raw fitness when several GPUs share the population — z-score, noise-
+    regenerating update of every layer and the solver step, all enqueued on the current stream
+    without host round-trips.  Parameters (and Adam moments) live on the device and are updated
+    in place; `out_gain` is read from its device tensor by the readout."""
+
+    def __init__(self, net: SnnMlp, frozen: FrozenNoiserParams, noiser: NoiserParams,
+                 base_keys: Sequence[int], T: int, n_pop: int, bm: int, first_thread: int = 0,
+                 reward: int = ops.REWARD_LOGLIK):
+        import ctypes as C
+        from . import _lib
+        from .core import get_context
+        self.C, self._lib, self.L = C, _lib, _lib.load()
+        self.net, self.frozen, self.noiser = net, frozen, noiser
+        self.keys = [int(k) & ((1 << 64) - 1) for k in base_keys]
+        self.T, self.n_pop, self.bm, self.first_thread, self.reward = T, n_pop, bm, first_thread, reward
+        self.ctx = get_context(net.device)
+        self.params = [w.contiguous() for w in net.weights] + [net.out_gain.contiguous()]
+        net.weights, net.out_gain = self.params[:-1], self.params[-1]
+        kind = frozen.solver.kind
+        self.moments = None
+        if kind in ("adam", "adamw"):
+            self.moments = ([torch.zeros_like(p) for p in self.params], [torch.zeros_like(p) for p in self.params])
+        self._ws = None
+
+    def _model(self):
+        C, _lib = self.C, self._lib
+        n = len(self.net.weights)
+        dims = (C.c_int32 * (n + 1))(*self.net.dims)
+        wp = (C.c_void_p * n)(*[w.data_ptr() for w in self.net.weights])
+        ws = (C.c_int64 * n)(*[w.stride(0) for w in self.net.weights])
+        keys = (C.c_uint64 * n)(*self.keys[:n])
+        vth = (C.c_float * max(n - 1, 1))(*([self.net.v_th] * max(n - 1, 1)))
+        m = _lib.SnnModelDesc(n, dims, wp, ws, keys, 1.0, self.net.out_gain.data_ptr(), self.net.tau_m, vth,
+                              self.net.reset_mode)
+        self._keep = (dims, wp, ws, keys, vth)
+        return m
+
+    def _args(self, epoch: int, perturb: bool = True):
+        return self._lib.PopArgs(self.T, self.n_pop, self.bm, int(perturb), self.noiser.sigma, self.frozen.rank,
+                                 epoch, self.first_thread, self.frozen.noise_reuse)
+
+    def _scratch(self, nbytes: int) -> torch.Tensor:
+        if self._ws is None or self._ws.numel() < nbytes + 256:
+            self._ws = torch.empty(nbytes + 256, dtype=torch.uint8, device=self.net.device)
+        off = (-self._ws.data_ptr()) % 256
+        return self._ws[off:off + nbytes]
+
+    def eval(self, images: torch.Tensor, labels: torch.Tensor, seeds: Sequence[int], epoch: int = 0,
+             want_logits: bool = False, perturb: bool = True):
+        """images (n_pop*bm, in) probabilities, labels int32 -> raw fitness (n_pop,)."""
+        C = self.C
+        m, p = self._model(), self._args(epoch, perturb)
+        need = int(self.L.hses_population_eval_workspace_bytes(C.byref(m), C.byref(p)))
+        ws = self._scratch(need)
+        raw = torch.empty(self.n_pop, dtype=torch.float32, device=images.device)
+        logits = torch.empty((self.n_pop * self.bm, self.net.dims[-1]), dtype=torch.float32,
+                             device=images.device) if want_logits else None
+        sd = (C.c_uint32 * 4)(*[int(s) & 0xFFFFFFFF for s in seeds])
+        from .core import current_stream
+        self._lib.check(self.L.hses_population_eval(
+            self.ctx.handle, current_stream(), C.byref(m), C.byref(p), images.data_ptr(),
+            images.stride(0), labels.data_ptr(), sd, self.reward, raw.data_ptr(),
+            logits.data_ptr() if want_logits else None, ws.data_ptr(), need))
+        return (raw, logits) if want_logits else raw
+
+    def update(self, raw_fitness: torch.Tensor, epoch: int = 0, gain_key: Optional[int] = None) -> None:
+        """raw_fitness: the FULL population's raw fitness (thread ids 0..n-1). Updates parameters in place."""
+        C = self.C
+        m = self._model()
+        n_total = raw_fitness.numel()
+        need = int(self.L.hses_population_update_workspace_bytes(C.byref(m), self.frozen.rank, n_total))
+        ws = self._scratch(need)
+        sv = self.frozen.solver
+        kind = {"sgd": ops.SGD, "adam": ops.ADAM, "adamw": ops.ADAMW}[sv.kind]
+        desc = self._lib.SolverDesc(kind, sv.lr, sv.beta1, sv.beta2, sv.eps, sv.weight_decay if kind == ops.ADAMW else 0.0)
+        if kind != ops.SGD:
+            self.noiser.opt_state.step += 1
+        n = len(self.params)
+        pp = (C.c_void_p * n)(*[t.data_ptr() for t in self.params])
+        mp = vp = None
+        if self.moments is not None:
+            mp = (C.c_void_p * n)(*[t.data_ptr() for t in self.moments[0]])
+            vp = (C.c_void_p * n)(*[t.data_ptr() for t in self.moments[1]])
+        gk = self.keys[len(self.net.weights)] if gain_key is None else gain_key
+        from .core import current_stream
+        self._lib.check(self.L.hses_population_update(
+            self.ctx.handle, current_stream(), C.byref(m), self.noiser.sigma, self.frozen.rank, epoch,
+            self.frozen.noise_reuse, self.frozen.group_size, int(self.frozen.freeze_nonlora),
+            C.c_uint64(gk & ((1 << 64) - 1)), raw_fitness.data_ptr(), n_total, C.byref(desc),
+            self.noiser.opt_state.step, pp, mp, vp, ws.data_ptr(), need))

@@ -154,6 +154,8 @@ typedef struct {
     float v_th;
     int32_t reset_mode;
     float out_scale; /* lif == 0 only: y is multiplied by this (readout gain, snn.rs:280-281) */
+    const float* out_scale_ptr; /* device or NULL: when set, the gain is read from here instead
+                                   (a trained out_gain can stay on the device between steps) */
     float* out; /* device */
     int64_t out_row_stride;
     float* potentials; /* device or NULL */
@@ -245,6 +247,69 @@ typedef struct {
 int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solver, int32_t step,
                      float grad_scale, float* param /*device*/, const float* grad /*device*/,
                      float* m /*device*/, float* v /*device*/, int64_t len);
+
+/* ---- SNN population step as two calls around the (optional) fitness all-gather.
+ *      The model is the reference's SnnModel / TrainableVthSnn generalised to a list of layer
+ *      widths (hyperscalees-models/src/snn.rs:188-282, 388-416): per hidden layer a perturbed
+ *      linear over all T steps followed by the LIF scan, then the mean firing rate, the
+ *      perturbed readout and the clean out_gain.  Arrays inside hses_snn_model are HOST arrays;
+ *      weights[l] are device pointers to (dims[l+1], dims[l]) matrices with weight_strides[l]. */
+typedef struct {
+    int32_t n_layers;              /* hidden layers + readout */
+    const int32_t* dims;           /* n_layers + 1 entries: in, h1, ..., classes */
+    const float* const* weights;   /* n_layers device pointers */
+    const int64_t* weight_strides; /* n_layers row strides (elements) */
+    const uint64_t* keys;          /* n_layers base keys (one per parameter index) */
+    float out_gain;
+    const float* out_gain_dev;     /* device or NULL: overrides out_gain (the (1,1) parameter tensor) */
+    float tau_m;
+    const float* v_th;             /* n_layers - 1 thresholds, one per hidden layer */
+    int32_t reset_mode;
+} hses_snn_model;
+
+typedef struct {
+    int32_t T;
+    int64_t n_pop;
+    int32_t bm;                    /* samples per member */
+    int32_t perturb;               /* 0: clean forward (iterinfo = None) */
+    float sigma;
+    int32_t rank;
+    int32_t epoch;
+    int32_t first_thread;          /* thread id of member 0 of this shard */
+    int32_t noise_reuse;
+} hses_pop_args;
+
+/* spikes_in: (T, n_pop*bm, dims[0]) with row stride in_stride -> logits (n_pop*bm, classes) dense. */
+size_t hses_snn_forward_workspace_bytes(const hses_snn_model* m, const hses_pop_args* p);
+int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
+                     const float* spikes_in /*device*/, int64_t in_stride, float* logits /*device*/,
+                     void* workspace /*device*/, size_t workspace_bytes);
+
+/* First half of a step, the composition of hyperscalees/src/snn_mnist_train.rs:159-216 for a
+ * shard of the population: Poisson-encode images (n_pop*bm, dims[0]) with the given seed words,
+ * run the perturbed forward, score it (reward per sample, mean over each member's bm samples).
+ * raw_fitness receives n_pop values; logits_out (optional) the (n_pop*bm, classes) logits. */
+size_t hses_population_eval_workspace_bytes(const hses_snn_model* m, const hses_pop_args* p);
+int hses_population_eval(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
+                         const float* images /*device*/, int64_t image_stride,
+                         const int32_t* labels /*device*/, const uint32_t seeds[4], int32_t reward,
+                         float* raw_fitness /*device*/, float* logits_out /*device or NULL*/,
+                         void* workspace /*device*/, size_t workspace_bytes);
+
+/* Second half (snn_mnist_train.rs:218-232, EggRoll::convert_fitnesses + do_updates): z-score the
+ * FULL raw fitness vector (n_total values, thread ids 0..n_total-1, after any all-gather), build
+ * every layer's gradient from the regenerated noise, the dense-noise gradient of out_gain, and
+ * apply one solver step in place.  params: n_layers weight matrices (dense, device, updated in
+ * place) followed by the (1,1) out_gain tensor; m/v: matching moment buffers or NULL for SGD.
+ * step is the solver counter after the increment. */
+size_t hses_population_update_workspace_bytes(const hses_snn_model* m, int32_t rank, int64_t n_total);
+int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, float sigma,
+                           int32_t rank, int32_t epoch, int32_t noise_reuse, int32_t group_size,
+                           int32_t freeze_nonlora, uint64_t gain_key, const float* raw_fitness /*device*/,
+                           int64_t n_total, const hses_solver* solver, int32_t step,
+                           float* const* params /*host array of device pointers*/,
+                           float* const* m_bufs, float* const* v_bufs, void* workspace /*device*/,
+                           size_t workspace_bytes);
 
 #ifdef __cplusplus
 }

