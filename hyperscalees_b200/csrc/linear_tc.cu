@@ -546,11 +546,14 @@ __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows,
     }
 }
 
-// Per antithetic pair (one CTA): t[R, q] = sum_k x[R, k] * B_pair[k, q] for the pair's rows, with
-// B regenerated block by block into shared memory (thread j owns B rows j, j+128, ...), and, on
-// the way, the fp16 hi/lo split of those x rows (see split_f16_rows_kernel) so that x is read
-// from HBM once.  RANK_G = rank / 4.
+// t[R, q] = sum_k x[R, k] * B_pair[k, q].  CTA (pair, chunk) takes up to LT_ROWS of the pair's rows
+// (all time steps of both members count), regenerates B block by block into shared memory
+// (thread j owns B rows j, j+128, ...) and, on the way, writes the fp16 hi/lo split of its x rows
+// (see split_f16_rows_kernel) so that x is read from HBM once.  A pair with many rows is spread
+// over several CTAs, each regenerating the pair's B: that costs k*rank normals per CTA against
+// LT_ROWS*k*rank multiply-adds, and buys the parallelism small populations need.  RANK_G = rank / 4.
 constexpr int LT_THREADS = 128;
+constexpr int LT_ROWS = 128;
 template <int RANK_G>
 __global__ void __launch_bounds__(LT_THREADS)
 lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop127,
@@ -579,8 +582,11 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     if (m_lo < 0) m_lo = 0;
     if (m_hi > n_pop) m_hi = n_pop;
     const int rows_per_step = (int)(m_hi - m_lo) * bm;
-    const int total_rows = rows_per_step * t_steps;
+    const int row0 = blockIdx.y * LT_ROWS;  // first of this CTA's rows among the pair's rows
+    const int total_rows = min(LT_ROWS, rows_per_step * t_steps - row0);
+    if (total_rows <= 0) return;
     auto global_row = [&](int lr) -> int64_t {
+        lr += row0;
         int step = lr / rows_per_step, rr = lr - step * rows_per_step;
         return ((int64_t)step * n_pop + m_lo) * bm + rr;
     };
@@ -624,8 +630,8 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     uint64_t s = noise_seed(key, true_epoch, pair) | 1ull;
     s = jump_by(pow2, s, 2ull * (uint64_t)RANK * (uint64_t)tid);
     __syncthreads();
-    // work items: (row, q-group of four); each thread keeps up to MAXI of them in registers
-    constexpr int MAXI = 4;
+    // work items: (row, q-group of four); LT_ROWS rows give each thread at most RANK_G of them
+    constexpr int MAXI = RANK_G;
     const int items = total_rows * RANK_G;
     for (int base = 0; base < items; base += LT_THREADS * MAXI) {
         float acc[MAXI][4];
@@ -872,9 +878,10 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
         HSES_KERNEL(ctx, st, "lowrank_t");
 #define HSES_LT(RG)                                                                                          \
-    lowrank_t_kernel<RG><<<(unsigned)pairs, LT_THREADS, 0, st>>>(                                            \
+    lowrank_t_kernel<RG><<<lt_grid, LT_THREADS, 0, st>>>(                                            \
         ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
         g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs)
+        dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
         switch (g.rank / 4) {
             case 1: HSES_LT(1); break;
             case 2: HSES_LT(2); break;

