@@ -1,24 +1,23 @@
 // Tensor-core path of the perturbed linear layer (do_mm,
 // hyperscalees-noiser/src/eggroll.rs:419-446, + lif_step, snn.rs:53-65).
 //
-//   launch 1  split_tf32      W -> W_hi + W_lo, both exactly representable in TF32
-//   launch 2  lowrank_t       t = x·B_pair, B regenerated from the seed stream in
-//                             shared memory, never written to HBM
+//   launch 1  split_w         every row of W times a power of two, then fp16 hi + lo (22 bits)
+//   launch 2  lowrank_t       t = x·B_pair, B regenerated from the seed stream in shared memory,
+//                             never written to HBM; the same pass writes the fp16 split of x
 //   launch 3  linear_tc       persistent, one CTA per SM, warp-specialised:
-//       warp 0      TMA producer: x, W_hi, W_lo tiles -> 128B-swizzled smem ring
-//       warp 1      MMA issuer: tcgen05.mma kind::tf32, three passes per k-step
-//                   (x_hi·W_hi + x_hi·W_lo + x_lo·W_hi), fp32 accumulators in TMEM,
-//                   two accumulator buffers so the epilogue overlaps the next chunk
-//       warps 2-3   split the x tile in place into x_hi / x_lo (same offsets, so
-//                   the swizzle pattern is preserved)
-//       warps 4-7   epilogue: TMEM -> registers, regenerate the A rows of the
-//                   warp's antithetic pair in registers, add t·(±s·A)ᵀ, LIF step,
-//                   store spikes
-// Three TF32 passes make every product fp32-equivalent (2^-21 relative residue);
-// a single pass (5e-4) would break the spike tolerance.  No TMA multicast and no
-// cluster launch is used anywhere.  Every barrier wait is bounded: a wait that
-// runs out records a code in the context's status word, all roles leave their
-// loops, TMEM is released and the kernel returns.
+//       warp 0       TMA producer: x_hi, x_lo, W_hi, W_lo tiles -> 128B-swizzled smem ring
+//       warp 1       MMA issuer: tcgen05.mma kind::f16, three passes per k-step
+//                    (x_lo·W_hi + x_hi·W_lo + x_hi·W_hi), fp32 accumulators in TMEM, two
+//                    accumulator buffers so the epilogue overlaps the next 256-column chunk
+//       warps 2-9    epilogue, two per TMEM quadrant: TMEM -> registers, undo the operand
+//                    scales, add t·(±s·A)ᵀ from the staged A rows, LIF step, store spikes
+//       warps 10-21  noise generators, three per quadrant: regenerate the A rows of the
+//                    quadrant's antithetic pair into a shared-memory ring, ahead of the MMAs
+// Three fp16 passes on scaled hi/lo operands make every product fp32-equivalent (2^-21
+// relative residue); a single pass would break the spike tolerance.  No TMA multicast and no
+// cluster launch is used anywhere.  Every barrier wait is bounded: a wait that runs out
+// records a code in the context's status word, all roles leave their loops, TMEM is released
+// and the kernel returns.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <stdlib.h>
