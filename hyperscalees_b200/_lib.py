@@ -25,7 +25,7 @@ EXPORTS = [
     "hses_es_update", "hses_es_update_static_scratch_bytes", "hses_es_update_static",
     "hses_es_update_dense", "hses_solver_step", "hses_snn_forward_workspace_bytes", "hses_snn_forward",
     "hses_population_eval_workspace_bytes", "hses_population_eval", "hses_population_update_workspace_bytes",
-    "hses_population_update",
+    "hses_population_update", "hses_wkv7", "hses_spiking_attention",
 ]
 
 
@@ -124,6 +124,9 @@ def load():
     L.hses_population_update.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64,
                                          C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                          vp, sz]
+    L.hses_wkv7.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp]
+    L.hses_spiking_attention.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, f32, f32, f32, f32, i32,
+                                         vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)
         if fn.restype is C.c_int and name not in ("hses_version",):

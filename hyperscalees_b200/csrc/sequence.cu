@@ -1,0 +1,176 @@
+// Sequence-model kernels on the population path: the RWKV-7 state recurrence and the spiking
+// self-attention core.  One CTA per (sequence, head); the recurrent state stays in registers.
+#include "common.cuh"
+
+namespace hses {
+
+// ---------------------------------------------------------------------------
+// RWKV-7 inner loop (hyperscalees-models/src/llm.rs:235-296; models/llm/rwkv7.py:200-220):
+//   dec = exp(-exp(w));  sa = S a;  S = S * dec + v k^T + sa b^T;  out = S r
+// Thread i owns row i of the (S, S) state.  Operation order and rounding follow the
+// reference's op-by-op evaluation: (S*dec) + v*k, then + sa*b, dot products in index order.
+// ---------------------------------------------------------------------------
+template <int S>
+__global__ void __launch_bounds__(S)
+wkv7_kernel(const float* __restrict__ r, const float* __restrict__ w, const float* __restrict__ k,
+            const float* __restrict__ v, const float* __restrict__ a, const float* __restrict__ b,
+            const uint8_t* __restrict__ new_starts, int T, int H, float* __restrict__ state,
+            float* __restrict__ out) {
+    __shared__ float sh[6][S];  // r, dec, k, v, a, b of the current step
+    const int seq = blockIdx.x / H, h = blockIdx.x % H, i = threadIdx.x;
+    float st[S];
+    float* sp = state + (((size_t)seq * H + h) * S + i) * S;
+#pragma unroll
+    for (int j = 0; j < S; j += 4) {
+        float4 q = *reinterpret_cast<const float4*>(sp + j);
+        st[j] = q.x; st[j + 1] = q.y; st[j + 2] = q.z; st[j + 3] = q.w;
+    }
+    for (int t = 0; t < T; ++t) {
+        size_t o = (((size_t)seq * T + t) * H + h) * S + i;
+        __syncthreads();
+        sh[0][i] = r[o];
+        sh[1][i] = expf(-expf(w[o]));
+        sh[2][i] = k[o];
+        sh[3][i] = v[o];
+        sh[4][i] = a[o];
+        sh[5][i] = b[o];
+        __syncthreads();
+        if (new_starts && new_starts[(size_t)seq * T + t]) {
+#pragma unroll
+            for (int j = 0; j < S; ++j) st[j] = 0.0f;
+        }
+        float sa = 0.0f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) sa = __fadd_rn(sa, __fmul_rn(st[j], sh[4][j]));
+        const float vi = sh[3][i];
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < S; ++j) {
+            float s1 = __fadd_rn(__fmul_rn(st[j], sh[1][j]), __fmul_rn(vi, sh[2][j]));
+            st[j] = __fadd_rn(s1, __fmul_rn(sa, sh[5][j]));
+            acc = __fadd_rn(acc, __fmul_rn(st[j], sh[0][j]));
+        }
+        out[o] = acc;
+    }
+#pragma unroll
+    for (int j = 0; j < S; j += 4) *reinterpret_cast<float4*>(sp + j) = make_float4(st[j], st[j + 1], st[j + 2], st[j + 3]);
+}
+
+// ---------------------------------------------------------------------------
+// Spiking self-attention core on firing rates Q, K, V of shape (tokens, d) per (sequence, head).
+//   mode 0  spike product without softmax:  O = (beta * Q K^T) V
+//   mode 1  LIF-count row softmax (src/hyperscalees/models/snn_self_attention.py:45-98): each row
+//           of beta*QK^T is scaled by 1/(max|.| + 1e-6), then n_iter LIF steps with hard reset and
+//           global inhibition g_inh * sum(counts so far); weights = count / (sum(count) + 1e-6)
+// Thread i owns query row i; K and V of the head sit in shared memory.
+// ---------------------------------------------------------------------------
+constexpr int kMaxTokens = 128, kMaxHeadDim = 64;
+__global__ void spiking_attention_kernel(const float* __restrict__ Q, const float* __restrict__ K,
+                                         const float* __restrict__ V, int tokens, int heads, int d,
+                                         int64_t row_stride, int mode, float beta, float tau_m, float v_th,
+                                         float g_inh, int n_iter, float* __restrict__ O,
+                                         float* __restrict__ A_out) {
+    extern __shared__ float sm[];  // K (tokens, d) | V (tokens, d)
+    float* ks = sm;
+    float* vs = sm + tokens * d;
+    const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * d;
+    for (int e = threadIdx.x; e < tokens * d; e += blockDim.x) {
+        int tk = e / d, c = e - tk * d;
+        ks[e] = K[base + (size_t)tk * row_stride + c];
+        vs[e] = V[base + (size_t)tk * row_stride + c];
+    }
+    __syncthreads();
+    const int i = threadIdx.x;
+    if (i >= tokens) return;
+    float q[kMaxHeadDim];
+    for (int c = 0; c < d; ++c) q[c] = Q[base + (size_t)i * row_stride + c];
+    float hrow[kMaxTokens];
+    float amax = 0.0f;
+    for (int j = 0; j < tokens; ++j) {
+        float acc = 0.0f;
+        for (int c = 0; c < d; ++c) acc = __fadd_rn(acc, __fmul_rn(q[c], ks[j * d + c]));
+        hrow[j] = __fmul_rn(beta, acc);
+        amax = fmaxf(amax, fabsf(hrow[j]));
+    }
+    if (mode == 1) {
+        const float inv = __fadd_rn(amax, 1e-6f);
+        const float leak = 1.0f / tau_m;
+        float u[kMaxTokens], cnt[kMaxTokens];
+        for (int j = 0; j < tokens; ++j) { hrow[j] = __fdiv_rn(hrow[j], inv); u[j] = 0.0f; cnt[j] = 0.0f; }
+        for (int it = 0; it < n_iter; ++it) {
+            float G = 0.0f;
+            for (int j = 0; j < tokens; ++j) G = __fadd_rn(G, cnt[j]);
+            const float inh = __fmul_rn(g_inh, G);
+            for (int j = 0; j < tokens; ++j) {
+                float cur = __fsub_rn(hrow[j], inh);
+                float c = __fadd_rn(u[j], __fmul_rn(__fadd_rn(-u[j], cur), leak));
+                float s = c >= v_th ? 1.0f : 0.0f;
+                u[j] = __fmul_rn(c, __fadd_rn(-s, 1.0f));
+                cnt[j] = __fadd_rn(cnt[j], s);
+            }
+        }
+        float tot = 0.0f;
+        for (int j = 0; j < tokens; ++j) tot = __fadd_rn(tot, cnt[j]);
+        tot = __fadd_rn(tot, 1e-6f);
+        for (int j = 0; j < tokens; ++j) hrow[j] = __fdiv_rn(cnt[j], tot);
+    }
+    if (A_out)
+        for (int j = 0; j < tokens; ++j)
+            A_out[(((size_t)seq * heads + h) * tokens + i) * tokens + j] = hrow[j];
+    for (int c = 0; c < d; ++c) {
+        float acc = 0.0f;
+        for (int j = 0; j < tokens; ++j) acc = __fadd_rn(acc, __fmul_rn(hrow[j], vs[j * d + c]));
+        O[base + (size_t)i * row_stride + c] = acc;
+    }
+}
+
+}  // namespace hses
+
+using namespace hses;
+
+extern "C" {
+
+int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w, const float* k,
+              const float* v, const float* a, const float* b, const uint8_t* new_starts, int64_t n_seq,
+              int32_t T, int32_t H, int32_t S, float* state, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n_seq >= 0 && T >= 1 && H >= 1, "bad shape");
+    HSES_REQUIRE(S == 32 || S == 64, "head size must be 32 or 64");
+    HSES_REQUIRE(n_seq * H < (1ll << 31), "too many (sequence, head) pairs");
+    if (n_seq == 0) return HSES_OK;
+    HSES_REQUIRE(r && w && k && v && a && b && state && out, "NULL pointer");
+    HSES_REQUIRE(((uintptr_t)state & 15u) == 0, "state must be 16-byte aligned");
+    HSES_KERNEL(ctx, as_stream(stream), "wkv7");
+    unsigned grid = (unsigned)(n_seq * H);
+    if (S == 64)
+        wkv7_kernel<64><<<grid, 64, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
+    else
+        wkv7_kernel<32><<<grid, 32, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, const float* K, const float* V,
+                           int64_t n_seq, int32_t tokens, int32_t heads, int32_t head_dim, int64_t row_stride,
+                           int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
+                           float* O, float* A_out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n_seq >= 0 && tokens >= 1 && tokens <= kMaxTokens, "tokens must be in 1..128");
+    HSES_REQUIRE(heads >= 1 && head_dim >= 1 && head_dim <= kMaxHeadDim, "head_dim must be in 1..64");
+    HSES_REQUIRE(row_stride >= (int64_t)heads * head_dim, "row stride smaller than heads*head_dim");
+    HSES_REQUIRE(mode == 0 || mode == 1, "unknown mode");
+    HSES_REQUIRE(mode == 0 || (tau_m != 0.0f && n_iter >= 1), "bad LIF parameters");
+    HSES_REQUIRE(n_seq * heads < (1ll << 31), "too many (sequence, head) pairs");
+    if (n_seq == 0) return HSES_OK;
+    HSES_REQUIRE(Q && K && V && O, "NULL pointer");
+    int threads = (tokens + 31) / 32 * 32;
+    size_t smem = (size_t)2 * tokens * head_dim * sizeof(float);
+    HSES_KERNEL(ctx, as_stream(stream), "spiking_attention");
+    spiking_attention_kernel<<<(unsigned)(n_seq * heads), threads, smem, as_stream(stream)>>>(
+        Q, K, V, tokens, heads, head_dim, row_stride, mode, beta, tau_m, v_th, g_inh, n_iter, O, A_out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // extern "C"

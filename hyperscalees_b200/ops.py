@@ -354,3 +354,42 @@ class HostPipeline:
         cur.wait_event(ev_out[-1])
         cur.wait_event(ev_run[-1])
         return out_host
+
+
+def wkv7(r, w, k, v, a, b, state: torch.Tensor, new_starts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """rwkv7_inner_loop for a batch: inputs (n_seq, T, H, S); state (n_seq, H, S, S) is updated in place."""
+    for t, name in ((r, "r"), (w, "w"), (k, "k"), (v, "v"), (a, "a"), (b, "b")):
+        _check(t, name, ndim=4)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    _check(state, "state", ndim=4)
+    n_seq, T, H, S = r.shape
+    if tuple(state.shape) != (n_seq, H, S, S) or not state.is_contiguous():
+        raise ValueError("state must be a contiguous (n_seq, H, S, S) tensor")
+    if new_starts is not None:
+        _check(new_starts, "new_starts", torch.uint8, 2)
+    out = torch.empty_like(r)
+    ctx = get_context(r.device)
+    _lib.check(_lib.load().hses_wkv7(ctx.handle, current_stream(), _ptr(r), _ptr(w), _ptr(k), _ptr(v), _ptr(a),
+                                     _ptr(b), _ptr(new_starts), n_seq, T, H, S, _ptr(state), _ptr(out)))
+    return out
+
+
+def spiking_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int, mode: int = 0,
+                      beta: float = 1.0, tau_m: float = 2.0, v_th: float = 0.3, g_inh: float = 0.5,
+                      n_iter: int = 8, want_weights: bool = False):
+    """Q, K, V: (n_seq, tokens, heads*head_dim) firing rates -> O of the same shape."""
+    for t, name in ((Q, "Q"), (K, "K"), (V, "V")):
+        _check(t, name, ndim=3)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    n_seq, tokens, width = Q.shape
+    if width % heads:
+        raise ValueError("the model width must be a multiple of heads")
+    O = torch.empty_like(Q)
+    A = torch.empty((n_seq, heads, tokens, tokens), dtype=torch.float32, device=Q.device) if want_weights else None
+    ctx = get_context(Q.device)
+    _lib.check(_lib.load().hses_spiking_attention(ctx.handle, current_stream(), _ptr(Q), _ptr(K), _ptr(V), n_seq,
+                                                  tokens, heads, width // heads, width, mode, beta, tau_m, v_th,
+                                                  g_inh, n_iter, _ptr(O), _ptr(A)))
+    return (O, A) if want_weights else O

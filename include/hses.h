@@ -311,6 +311,24 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
                            float* const* m_bufs, float* const* v_bufs, void* workspace /*device*/,
                            size_t workspace_bytes);
 
+/* ---- rwkv7_inner_loop, hyperscalees-models/src/llm.rs:235-296, for a batch of sequences.
+ *      r, w, k, v, a, b, out: (n_seq, T, H, S) dense; state (n_seq, H, S, S) is read and left
+ *      holding the final state; new_starts (n_seq, T) bytes or NULL zeroes the state before a
+ *      step.  S is 32 or 64. ------------------------------------------------------------ */
+int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w, const float* k,
+              const float* v, const float* a, const float* b, const uint8_t* new_starts /*device or NULL*/,
+              int64_t n_seq, int32_t T, int32_t H, int32_t S, float* state, float* out);
+
+/* ---- spiking self-attention core on firing rates (src/hyperscalees/models/snn_self_attention.py:45-98;
+ *      the Rust port keeps a continuous variant, hyperscalees-models/src/snn_transformer.rs:80-102).
+ *      Q, K, V, O: (n_seq, tokens, heads*head_dim) with row_stride; mode 0: O = (beta Q K^T) V,
+ *      the spike product without softmax; mode 1: LIF-count row softmax (n_iter LIF steps with
+ *      global inhibition g_inh).  A_out (optional): (n_seq, heads, tokens, tokens) weights. ------ */
+int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, const float* K, const float* V,
+                           int64_t n_seq, int32_t tokens, int32_t heads, int32_t head_dim, int64_t row_stride,
+                           int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
+                           float* O, float* A_out /*device or NULL*/);
+
 #ifdef __cplusplus
 }
 #endif

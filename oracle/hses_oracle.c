@@ -637,3 +637,54 @@ void hso_wkv7(const float *r, const float *w, const float *k, const float *v,
     }
     free(sa);
 }
+
+/* ------------------------------------------------------------------------ */
+/* Spiking self-attention core                                              */
+/* ------------------------------------------------------------------------ */
+
+/* src/hyperscalees/models/snn_self_attention.py:45-98 (row_softmax_lif,
+ * self_attention_lif) for one head: Q, K, V are (tokens, d) firing rates.
+ * mode 0 is the spike product without softmax, O = (beta Q K^T) V, which has no
+ * reference counterpart beyond the two matmuls; mode 1 is the LIF-count row
+ * softmax: each row of beta*QK^T divided by (max|row| + 1e-6), n_iter LIF steps
+ * (hard reset, lif_step of snn_attention.py) driven by row - g_inh*sum(counts),
+ * weights = counts / (sum(counts) + 1e-6). */
+void hso_spiking_attention(const float *Q, const float *K, const float *V, int tokens, int d,
+                           int mode, float beta, float tau_m, float v_th, float g_inh, int n_iter,
+                           float *O, float *A) {
+    float *row = (float *)malloc(sizeof(float) * (size_t)tokens * 3);
+    float *u = row + tokens, *cnt = row + 2 * tokens;
+    for (int i = 0; i < tokens; ++i) {
+        float amax = 0.0f;
+        for (int j = 0; j < tokens; ++j) {
+            float acc = 0.0f;
+            for (int c = 0; c < d; ++c) acc += Q[(size_t)i * d + c] * K[(size_t)j * d + c];
+            row[j] = beta * acc;
+            if (fabsf(row[j]) > amax) amax = fabsf(row[j]);
+        }
+        if (mode == 1) {
+            float inv = amax + 1e-6f, leak = 1.0f / tau_m;
+            for (int j = 0; j < tokens; ++j) { row[j] = row[j] / inv; u[j] = 0.0f; cnt[j] = 0.0f; }
+            for (int it = 0; it < n_iter; ++it) {
+                float G = 0.0f;
+                for (int j = 0; j < tokens; ++j) G += cnt[j];
+                float inh = g_inh * G;
+                for (int j = 0; j < tokens; ++j) {
+                    float s = lif_one(&u[j], row[j] - inh, leak, v_th, HSO_RESET_HARD);
+                    cnt[j] += s;
+                }
+            }
+            float tot = 0.0f;
+            for (int j = 0; j < tokens; ++j) tot += cnt[j];
+            tot += 1e-6f;
+            for (int j = 0; j < tokens; ++j) row[j] = cnt[j] / tot;
+        }
+        if (A) memcpy(A + (size_t)i * tokens, row, sizeof(float) * (size_t)tokens);
+        for (int c = 0; c < d; ++c) {
+            float acc = 0.0f;
+            for (int j = 0; j < tokens; ++j) acc += row[j] * V[(size_t)j * d + c];
+            O[(size_t)i * d + c] = acc;
+        }
+    }
+    free(row);
+}

@@ -154,6 +154,12 @@ void hso_wkv7(const float *r, const float *w, const float *k, const float *v,
               const float *a, const float *b, const uint8_t *new_starts, int T,
               int H, int S, float *state, float *out);
 
+/* ---- spiking self-attention core for one head
+ *      (src/hyperscalees/models/snn_self_attention.py:45-98) ------------------ */
+void hso_spiking_attention(const float *Q, const float *K, const float *V, int tokens, int d,
+                           int mode, float beta, float tau_m, float v_th, float g_inh, int n_iter,
+                           float *O, float *A);
+
 int hso_num_threads(void);
 
 #ifdef __cplusplus

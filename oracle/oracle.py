@@ -360,3 +360,14 @@ def wkv7(r, w, k, v, a, b, state, new_starts=None):
     lib().hso_wkv7(rp, wp, kp, vp, ap, bp, ns.ctypes.data_as(_u8p) if ns is not None else None,
                    T, H, S, st.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p))
     return st, out
+
+
+def spiking_attention(Q, K, V, mode=0, beta=1.0, tau_m=2.0, v_th=0.3, g_inh=0.5, n_iter=8):
+    """One head: Q, K, V (tokens, d) -> (O (tokens, d), A (tokens, tokens))."""
+    Q, qp = _f(Q); K, kp = _f(K); V, vp = _f(V)
+    tokens, d = Q.shape
+    O = np.empty((tokens, d), dtype=np.float32)
+    A = np.empty((tokens, tokens), dtype=np.float32)
+    lib().hso_spiking_attention(qp, kp, vp, tokens, d, mode, C.c_float(beta), C.c_float(tau_m), C.c_float(v_th),
+                                C.c_float(g_inh), n_iter, O.ctypes.data_as(_f32p), A.ctypes.data_as(_f32p))
+    return O, A
