@@ -34,8 +34,8 @@ UNIT = "member-evals/s"
 KEY = 0x3C6EF372FE94F82A          # base key of parameter index 1
 SIGMA, RANK, TAU_M, V_TH = 0.02, 16, 20.0, 0.3
 N_POP, BM, K_DIM, A_DIM = 8192, 16, 1024, 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by its members, from the ncu
-# capture summarised in profiles/linear_tc_perturbed_linear_microbench.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by its members, from an ncu
+# capture of these kernels at n_pop = 2048 (its summary is kept in the profiles folder)
 NCU_TRAFFIC_BYTES_PER_MEMBER = {"linear_tc": (211.2e6 + 91.6e6) / 2048, "lowrank_t": (258.3e6 + 137.3e6) / 2048}
 
 
@@ -242,6 +242,30 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         for _ in range(2):
             e2e_step()
         ms_e2e = timed(e2e_step, args.steps)
+    # Secondary figure: the same step with the factors read from a device-resident cache that was
+    # generated once outside the timed region (the reference's LoraNoiseCache mode of operation,
+    # valid while the epoch bucket does not change).  The headline above regenerates every step.
+    cached = None
+    if not args.kernel_only:
+        t0 = time.perf_counter()
+        cache = ops.FactorCache(KEY, 0, 0, RANK, A_DIM, K_DIM, n_pairs=N_POP // 2,
+                                first_pair=first_thread // 2, device=dev)
+        torch.cuda.synchronize()
+        build_ms = (time.perf_counter() - t0) * 1e3
+
+        def cached_step():
+            ops.perturbed_linear(x_dev, w_dev, n_pop=N_POP, bm=BM, sigma=SIGMA, rank=RANK, key=KEY,
+                                 first_thread=first_thread, lif=True, tau_m=TAU_M, v_th=V_TH, out=out_dev,
+                                 cache=cache)
+
+        for _ in range(3):
+            cached_step()
+        ms_cached = timed(cached_step, args.steps)
+        cached = {"value": N_POP * BM * world * args.steps / (ms_cached * 1e-3), "unit": UNIT,
+                  "ms_per_step": ms_cached / args.steps, "cache_bytes_per_gpu": int(cache.data.numel() * 4),
+                  "cache_build_ms": build_ms,
+                  "note": "factors read from a device cache built once outside the timed region"}
+        del cache
     clocks = sampler.stop() if sampler else None
 
     evals_per_step = N_POP * BM * world
@@ -252,7 +276,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         top = max(prof.items(), key=lambda kv: kv[1][1])
         top_name, (top_n, top_ms) = top
         rows = N_POP * BM
-        # algorithmic work of one launch of the dominant kernel (see DESIGN.md):
+        # algorithmic work of one launch of the dominant kernel:
         #   GEMM 2*rows*K*A plus the rank-r epilogue 2*rows*r*A
         flops = 2.0 * rows * K_DIM * A_DIM + 2.0 * rows * RANK * A_DIM
         per_launch_s = top_ms * 1e-3 / top_n
@@ -281,7 +305,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                 "config": config_dict(world), "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
-                "gpu_launches": int(launches), "clocks": clocks}
+                "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -26,7 +26,23 @@ EXPORTS = [
     "hses_es_update_dense", "hses_solver_step", "hses_snn_forward_workspace_bytes", "hses_snn_forward",
     "hses_population_eval_workspace_bytes", "hses_population_eval", "hses_population_update_workspace_bytes",
     "hses_population_update", "hses_wkv7", "hses_spiking_attention",
+    "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
 ]
+
+
+class FactorCacheDesc(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("key", C.c_uint64), ("true_epoch", C.c_int32),
+                ("first_pair", C.c_int32), ("n_pairs", C.c_int64), ("rank", C.c_int32),
+                ("a", C.c_int32), ("b", C.c_int32)]
+
+
+class UpdateArgs(C.Structure):
+    _fields_ = [("key", C.c_uint64), ("epoch", C.c_int32), ("noise_reuse", C.c_int32),
+                ("first_thread", C.c_int32), ("n", C.c_int64), ("n_total", C.c_int64),
+                ("rank", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("sigma", C.c_float),
+                ("fitness", C.c_void_p), ("grad", C.c_void_p), ("workspace", C.c_void_p),
+                ("workspace_bytes", C.c_size_t), ("cache", C.POINTER(FactorCacheDesc)),
+                ("mode", C.c_int32)]
 
 
 class LinearArgs(C.Structure):
@@ -39,6 +55,7 @@ class LinearArgs(C.Structure):
         ("tau_m", C.c_float), ("v_th", C.c_float), ("reset_mode", C.c_int32), ("out_scale", C.c_float), ("out_scale_ptr", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("cache", C.POINTER(FactorCacheDesc)),
     ]
 
 
@@ -46,7 +63,8 @@ class SnnModelDesc(C.Structure):
     _fields_ = [("n_layers", C.c_int32), ("dims", C.POINTER(C.c_int32)), ("weights", C.POINTER(C.c_void_p)),
                 ("weight_strides", C.POINTER(C.c_int64)), ("keys", C.POINTER(C.c_uint64)),
                 ("out_gain", C.c_float), ("out_gain_dev", C.c_void_p), ("tau_m", C.c_float),
-                ("v_th", C.POINTER(C.c_float)), ("reset_mode", C.c_int32)]
+                ("v_th", C.POINTER(C.c_float)), ("reset_mode", C.c_int32),
+                ("caches", C.POINTER(C.POINTER(FactorCacheDesc)))]
 
 
 class PopArgs(C.Structure):
@@ -107,6 +125,11 @@ def load():
     L.hses_es_update_workspace_bytes.restype = sz
     L.hses_es_update_workspace_bytes.argtypes = [i32, i32, i32, i64]
     L.hses_es_update.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp, vp, sz]
+    L.hses_es_update_ex.argtypes = [vp, vp, C.POINTER(UpdateArgs)]
+    L.hses_factor_cache_bytes.restype = sz
+    L.hses_factor_cache_bytes.argtypes = [i64, i32, i32, i32]
+    L.hses_factor_cache_build.argtypes = [vp, vp, u64, i32, i32, i32, i64, i32, i32, i32, vp,
+                                          C.POINTER(FactorCacheDesc)]
     L.hses_es_update_static_scratch_bytes.restype = sz
     L.hses_es_update_static_scratch_bytes.argtypes = []
     L.hses_es_update_static.argtypes = [vp, vp, u64, i32, i32, i32, i64, i64, i32, i32, i32, f32, vp, vp]

@@ -191,6 +191,22 @@ static int check_args(const hses_linear_args* g) {
     return HSES_OK;
 }
 
+int resolve_factor_cache(const hses_linear_args& g, const float** A, const float** B) {
+    HSES_REQUIRE(g.cache != nullptr && g.cache->data != nullptr, "factor cache is NULL");
+    const hses_factor_cache& c = *g.cache;
+    HSES_REQUIRE(c.key == g.key && c.true_epoch == true_epoch_of(g.epoch, g.noise_reuse) &&
+                     c.rank == g.rank && c.a == g.a && c.b == g.k,
+                 "factor cache was built for another parameter, epoch bucket or shape");
+    int32_t first_pair = g.first_thread / 2;
+    int64_t last_pair = ((int64_t)g.first_thread + g.n_pop - 1) / 2;
+    HSES_REQUIRE(first_pair >= c.first_pair && last_pair < (int64_t)c.first_pair + c.n_pairs,
+                 "factor cache does not cover these members");
+    size_t off = (size_t)(first_pair - c.first_pair);
+    *A = c.data + off * c.a * c.rank;
+    *B = c.data + (size_t)c.n_pairs * c.a * c.rank + off * c.b * c.rank;
+    return HSES_OK;
+}
+
 static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
     EpilogueArgs ep{};
@@ -214,16 +230,22 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= s.bytes,
                      "workspace too small; see hses_perturbed_linear_workspace_bytes");
         ep.base_sigma = g.sigma / sqrtf((float)g.rank);
-        ep.A = s.A;
         ep.t = s.t;
-        int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - ep.first_pair + 1;
-        int rc = launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse),
-                                     ep.first_pair, pairs, g.rank, g.a, g.k, nullptr, s.A, s.B);
-        if (rc != HSES_OK) return rc;
+        const float *fa = s.A, *fb = s.B;
+        if (g.cache) {
+            int rc = resolve_factor_cache(g, &fa, &fb);
+            if (rc != HSES_OK) return rc;
+        } else {
+            int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - ep.first_pair + 1;
+            int rc = launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse),
+                                         ep.first_pair, pairs, g.rank, g.a, g.k, nullptr, s.A, s.B);
+            if (rc != HSES_OK) return rc;
+        }
+        ep.A = fa;
         HSES_KERNEL(ctx, st, "lowrank_project");
         lowrank_project_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
             g.x, rows, g.bm, g.n_pop, g.k, g.x_row_stride, g.rank, g.first_thread, ep.first_pair,
-            s.B, s.t);
+            fb, s.t);
         HSES_LAUNCH_CHECK();
     }
     int64_t row_tiles = (rows + TM - 1) / TM;

@@ -10,4 +10,8 @@ bool tensor_path_supports(const hses_linear_args& g);
 size_t tensor_path_workspace_bytes(const hses_linear_args& g);
 int run_tensor_path(hses_ctx* ctx, cudaStream_t stream, const hses_linear_args& g);
 
+// Checks args.cache against the call and returns the cached raw factors of the call's
+// first pair: A rows (pair, a, rank) and B rows (pair, k, rank).
+int resolve_factor_cache(const hses_linear_args& g, const float** A, const float** B);
+
 }  // namespace hses

@@ -167,6 +167,7 @@ struct TcArgs {
     float* pot;
     const uint64_t* pow2; // T^(2^k) tables
     const uint64_t* hop;  // T^(2*rank*(32*ring_depth - 1))
+    const float* cache_a; // cached raw A rows (pair, a, rank) from the call's first pair on, or NULL
     LibmCal cal;
     int* status;
     int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..3
@@ -471,6 +472,24 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             // every row of this quadrant's 32-row slice belongs to one antithetic pair
             int64_t member0 = (((int64_t)mt * BM_TILE + gq * 32) / g.bm) % g.n_pop;
             int32_t pair = (g.first_thread + (int32_t)member0) / 2;
+            if (g.cache_a) {
+                // the factors were generated earlier: stream this pair's rows from the cache
+                const float* src = g.cache_a + ((size_t)(pair - g.first_thread / 2) * g.a + gi * 32 + lane) * RANK;
+                for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
+                    float4 v[RG > 0 ? RG : 1];
+#pragma unroll
+                    for (int q = 0; q < RG; ++q) v[q] = __ldg(reinterpret_cast<const float4*>(src) + q);
+                    if (!mbar_wait(&aempty[gq * 3 + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
+#pragma unroll
+                    for (int q = 0; q < RG; ++q)
+                        *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
+                            make_float4(__fmul_rn(v[q].x, g.base_sigma), __fmul_rn(v[q].y, g.base_sigma),
+                                        __fmul_rn(v[q].z, g.base_sigma), __fmul_rn(v[q].w, g.base_sigma));
+                    src += (size_t)depth * 32 * RANK;
+                    mbar_arrive(&afull[gq * 3 + gi]);
+                }
+                continue;
+            }
             uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
             uint64_t a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)RANK * (uint64_t)(g.k + gi * 32 + lane));
             for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
@@ -546,34 +565,51 @@ __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows,
 }
 
 // t[R, q] = sum_k x[R, k] * B_pair[k, q].  CTA (pair, chunk) takes up to LT_ROWS of the pair's rows
-// (all time steps of both members count), regenerates B block by block into shared memory
-// (thread j owns B rows j, j+128, ...) and, on the way, writes the fp16 hi/lo split of its x rows
-// (see split_f16_rows_kernel) so that x is read from HBM once.  A pair with many rows is spread
-// over several CTAs, each regenerating the pair's B: that costs k*rank normals per CTA against
-// LT_ROWS*k*rank multiply-adds, and buys the parallelism small populations need.  RANK_G = rank / 4.
-constexpr int LT_THREADS = 128;
-constexpr int LT_ROWS = 128;
+// (all time steps of both members count) and, on the way, writes the fp16 hi/lo split of those
+// x rows (see split_f16_rows_kernel) so that x is read from HBM once.
+//
+// B is produced block by block in shared memory, LT_KB rows at a time, one row per thread: either
+// regenerated from the pair's stream or copied from a factor cache.  A pair with many rows is
+// spread over several CTAs, each regenerating the pair's B: that costs k*rank normals per CTA
+// against LT_ROWS*k*rank multiply-adds, and buys the parallelism small populations need.
+//
+// The product is laid out so that neither operand is the bottleneck of the load pipe: a warp owns
+// a tile of 8 rows; its lanes are (k-slice, group of four q), so the B block is read with
+// conflict-free 16-byte loads that are reused for all 8 rows, and x is read straight from global
+// memory, 16 bytes per lane and one 128-byte line per warp.  Each lane accumulates its k-slice
+// over the whole of k; the slices are added with shuffles at the end.  When the CTA has fewer
+// than eight row tiles the idle warps take a share of every B block (k-parts) and the parts are
+// added in a fixed order through shared memory.  RANK_G = rank / 4.
+constexpr int LT_THREADS = 256;
+constexpr int LT_ROWS = 64;
+constexpr int LT_KB = 256;
 template <int RANK_G>
-__global__ void __launch_bounds__(LT_THREADS)
-lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop127,
+__global__ void __launch_bounds__(LT_THREADS, 2)
+lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop_kb,
                  uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
                  int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
-                 __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale) {
+                 __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
+                 const float* __restrict__ cache_b) {
     constexpr int RANK = RANK_G * 4;
-    __shared__ __align__(16) float bs[LT_THREADS * RANK];  // one block of B: 128 rows x rank
+    constexpr int KQ = 32 / RANK_G;   // lanes along k
+    constexpr int KSTEP = 4 * KQ;     // k covered by one pass of a warp
+    __shared__ __align__(16) float bs[LT_KB * RANK];  // one block of B; reused for the k-part sums
     __shared__ uint64_t hop_s[kJumpWords];
     __shared__ double2 log_tab_s[64];
     __shared__ uint32_t delta_s[512];
+    __shared__ int64_t row_s[LT_ROWS];  // global row of each of this CTA's rows
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < kJumpWords; i += LT_THREADS) hop_s[i] = hop127[i];
-    for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
-    for (int i = tid; i < 256; i += LT_THREADS) {
-        delta_s[i] = cal.log_delta[i];
-        delta_s[256 + i] = cal.cos_delta[i];
+    if (!cache_b) {
+        for (int i = tid; i < kJumpWords; i += LT_THREADS) hop_s[i] = hop_kb[i];
+        for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
+        for (int i = tid; i < 256; i += LT_THREADS) {
+            delta_s[i] = cal.log_delta[i];
+            delta_s[256 + i] = cal.cos_delta[i];
+        }
+        cal.log_tab = log_tab_s;
+        cal.log_delta = delta_s;
+        cal.cos_delta = delta_s + 256;
     }
-    cal.log_tab = log_tab_s;
-    cal.log_delta = delta_s;
-    cal.cos_delta = delta_s + 256;
     const int32_t first_pair = first_thread / 2;
     const int32_t pair = first_pair + blockIdx.x;
     // members of this pair inside the population slice
@@ -584,16 +620,17 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     const int row0 = blockIdx.y * LT_ROWS;  // first of this CTA's rows among the pair's rows
     const int total_rows = min(LT_ROWS, rows_per_step * t_steps - row0);
     if (total_rows <= 0) return;
-    auto global_row = [&](int lr) -> int64_t {
-        lr += row0;
+    if (tid < LT_ROWS) {
+        int lr = row0 + (tid < total_rows ? tid : total_rows - 1);  // rows past the end repeat the last one
         int step = lr / rows_per_step, rr = lr - step * rows_per_step;
-        return ((int64_t)step * n_pop + m_lo) * bm + rr;
-    };
+        row_s[tid] = ((int64_t)step * n_pop + m_lo) * bm + rr;
+    }
+    __syncthreads();
 
-    // ---- operand split of this pair's x rows (one warp per row) ----
+    // ---- operand split of this CTA's x rows (one warp per row) ----
     const int n4 = k >> 2;
     for (int lr = warp; lr < total_rows; lr += LT_THREADS / 32) {
-        const int64_t R = global_row(lr);
+        const int64_t R = row_s[lr];
         const float4* src = reinterpret_cast<const float4*>(x + (size_t)R * x_stride);
         float m = 0.0f;
         for (int i = lane; i < n4; i += 32) {
@@ -626,65 +663,86 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     }
 
     // ---- t = x * B ----
-    uint64_t s = noise_seed(key, true_epoch, pair) | 1ull;
-    s = jump_by(pow2, s, 2ull * (uint64_t)RANK * (uint64_t)tid);
-    __syncthreads();
-    // work items: (row, q-group of four); LT_ROWS rows give each thread at most RANK_G of them
-    constexpr int MAXI = RANK_G;
-    const int items = total_rows * RANK_G;
-    for (int base = 0; base < items; base += LT_THREADS * MAXI) {
-        float acc[MAXI][4];
+    const int n_tiles = (total_rows + 7) >> 3;                     // 1..8
+    const int ksplit = n_tiles <= 1 ? 8 : n_tiles <= 2 ? 4 : n_tiles <= 4 ? 2 : 1;
+    const bool active = warp < n_tiles * ksplit;
+    const int tile = warp % n_tiles, kpart = warp / n_tiles;
+    const int part_len = LT_KB / ksplit;
+    const int kq = lane / RANK_G, qg = lane - kq * RANK_G;
+    const float* xrow[8];
 #pragma unroll
-        for (int i = 0; i < MAXI; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
-        uint64_t sb = s;  // every pass over the items replays the pair's B stream
-        for (int k0 = 0; k0 < k; k0 += LT_THREADS) {
-            if (k0 + tid < k) {
+    for (int r = 0; r < 8; ++r) xrow[r] = x + (size_t)row_s[tile * 8 + r] * x_stride;
+    float acc[8][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+
+    uint64_t sb = 0;
+    if (!cache_b) {
+        sb = noise_seed(key, true_epoch, pair) | 1ull;
+        sb = jump_by(pow2, sb, 2ull * (uint64_t)RANK * (uint64_t)tid);
+    }
+    // cached raw B rows of this pair, (k, rank) row-major like the block in shared memory
+    const float4* cb4 = cache_b ? reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK) : nullptr;
+    for (int k0 = 0; k0 < k; k0 += LT_KB) {
+        const int kn = k - k0 < LT_KB ? k - k0 : LT_KB;  // multiple of 4
+        if (cb4) {
+            for (int i = tid; i < kn * RANK_G; i += LT_THREADS)
+                reinterpret_cast<float4*>(bs)[i] = __ldg(cb4 + (size_t)k0 * RANK_G + i);
+        } else if (tid < kn) {
 #pragma unroll 1
-                for (int q = 0; q < RANK; q += 4) {
-                    float z[4];
-                    next_normals4(sb, cal, z);
-                    *reinterpret_cast<float4*>(bs + tid * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
-                }
-                sb = jump_apply(hop_s, sb);
+            for (int q = 0; q < RANK; q += 4) {
+                float z[4];
+                next_normals4(sb, cal, z);
+                *reinterpret_cast<float4*>(bs + tid * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
             }
-            __syncthreads();
-            const int kn = k - k0 < LT_THREADS ? k - k0 : LT_THREADS;  // multiple of 4
+            sb = jump_apply(hop_s, sb);
+        }
+        __syncthreads();
+        if (active) {
+            const int kend = min(kpart * part_len + part_len, kn);
+            for (int kk = kpart * part_len + 4 * kq; kk < kend; kk += KSTEP) {
+                const float* bq = bs + kk * RANK + qg * 4;
+                float4 b0 = *reinterpret_cast<const float4*>(bq);
+                float4 b1 = *reinterpret_cast<const float4*>(bq + RANK);
+                float4 b2 = *reinterpret_cast<const float4*>(bq + 2 * RANK);
+                float4 b3 = *reinterpret_cast<const float4*>(bq + 3 * RANK);
 #pragma unroll
-            for (int i = 0; i < MAXI; ++i) {
-                int item = base + tid + i * LT_THREADS;
-                if (item < items) {
-                    int lr = item / RANK_G, qg = item - lr * RANK_G;
-                    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)global_row(lr) * x_stride + k0);
-                    const float* bq = bs + qg * 4;
-#pragma unroll 2
-                    for (int kk = 0; kk < kn; kk += 4) {
-                        float4 xv = xr[kk >> 2];
-                        float4 b0 = *reinterpret_cast<const float4*>(bq + (kk + 0) * RANK);
-                        float4 b1 = *reinterpret_cast<const float4*>(bq + (kk + 1) * RANK);
-                        float4 b2 = *reinterpret_cast<const float4*>(bq + (kk + 2) * RANK);
-                        float4 b3 = *reinterpret_cast<const float4*>(bq + (kk + 3) * RANK);
-                        acc[i][0] = fmaf(xv.x, b0.x, acc[i][0]); acc[i][1] = fmaf(xv.x, b0.y, acc[i][1]);
-                        acc[i][2] = fmaf(xv.x, b0.z, acc[i][2]); acc[i][3] = fmaf(xv.x, b0.w, acc[i][3]);
-                        acc[i][0] = fmaf(xv.y, b1.x, acc[i][0]); acc[i][1] = fmaf(xv.y, b1.y, acc[i][1]);
-                        acc[i][2] = fmaf(xv.y, b1.z, acc[i][2]); acc[i][3] = fmaf(xv.y, b1.w, acc[i][3]);
-                        acc[i][0] = fmaf(xv.z, b2.x, acc[i][0]); acc[i][1] = fmaf(xv.z, b2.y, acc[i][1]);
-                        acc[i][2] = fmaf(xv.z, b2.z, acc[i][2]); acc[i][3] = fmaf(xv.z, b2.w, acc[i][3]);
-                        acc[i][0] = fmaf(xv.w, b3.x, acc[i][0]); acc[i][1] = fmaf(xv.w, b3.y, acc[i][1]);
-                        acc[i][2] = fmaf(xv.w, b3.z, acc[i][2]); acc[i][3] = fmaf(xv.w, b3.w, acc[i][3]);
-                    }
+                for (int r = 0; r < 8; ++r) {
+                    float4 xv = __ldg(reinterpret_cast<const float4*>(xrow[r] + k0 + kk));
+                    acc[r][0] = fmaf(xv.x, b0.x, acc[r][0]); acc[r][1] = fmaf(xv.x, b0.y, acc[r][1]);
+                    acc[r][2] = fmaf(xv.x, b0.z, acc[r][2]); acc[r][3] = fmaf(xv.x, b0.w, acc[r][3]);
+                    acc[r][0] = fmaf(xv.y, b1.x, acc[r][0]); acc[r][1] = fmaf(xv.y, b1.y, acc[r][1]);
+                    acc[r][2] = fmaf(xv.y, b1.z, acc[r][2]); acc[r][3] = fmaf(xv.y, b1.w, acc[r][3]);
+                    acc[r][0] = fmaf(xv.z, b2.x, acc[r][0]); acc[r][1] = fmaf(xv.z, b2.y, acc[r][1]);
+                    acc[r][2] = fmaf(xv.z, b2.z, acc[r][2]); acc[r][3] = fmaf(xv.z, b2.w, acc[r][3]);
+                    acc[r][0] = fmaf(xv.w, b3.x, acc[r][0]); acc[r][1] = fmaf(xv.w, b3.y, acc[r][1]);
+                    acc[r][2] = fmaf(xv.w, b3.z, acc[r][2]); acc[r][3] = fmaf(xv.w, b3.w, acc[r][3]);
                 }
             }
-            __syncthreads();
         }
+        __syncthreads();
+    }
+    // add the k-slices of the lanes (lanes that differ in kq), lowest lanes end up with the sums
 #pragma unroll
-        for (int i = 0; i < MAXI; ++i) {
-            int item = base + tid + i * LT_THREADS;
-            if (item < items) {
-                int lr = item / RANK_G, qg = item - lr * RANK_G;
-                *reinterpret_cast<float4*>(t + (size_t)global_row(lr) * RANK + qg * 4) =
-                    make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-            }
-        }
+    for (int off = RANK_G; off < 32; off <<= 1)
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[r][j] += __shfl_xor_sync(0xffffffffu, acc[r][j], off);
+    float* part = bs;  // [warp][8 rows][RANK]
+    if (active && kq == 0) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            *reinterpret_cast<float4*>(part + (warp * 8 + r) * RANK + qg * 4) =
+                make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    }
+    __syncthreads();
+    for (int e = tid; e < total_rows * RANK; e += LT_THREADS) {
+        int lr = e / RANK, q = e - lr * RANK;
+        int tl = lr >> 3, r = lr & 7;
+        float sum = 0.0f;
+        for (int p = 0; p < ksplit; ++p) sum += part[((tl + n_tiles * p) * 8 + r) * RANK + q];
+        t[(size_t)row_s[lr] * RANK + q] = sum;
     }
 }
 
@@ -864,6 +922,12 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.status = ctx->t.status_word;
     ta.hop = nullptr;
     ta.dbg = nullptr;
+    const float *cache_a = nullptr, *cache_b = nullptr;
+    if (g.perturb && g.cache) {
+        int crc = resolve_factor_cache(g, &cache_a, &cache_b);
+        if (crc != HSES_OK) return crc;
+    }
+    ta.cache_a = cache_a;
     if (getenv("HSES_TC_DEBUG")) {
         void* p = nullptr;
         HSES_CUDA(cudaGetSymbolAddress(&p, g_tc_dbg));
@@ -872,14 +936,14 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     }
     if (g.perturb) {
         const uint64_t* hop127 = nullptr;
-        int rc = get_hop_table(ctx, 2ull * g.rank * 127, &hop127);
+        int rc = get_hop_table(ctx, 2ull * g.rank * (LT_KB - 1), &hop127);
         if (rc != HSES_OK) return rc;
         int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
         HSES_KERNEL(ctx, st, "lowrank_t");
 #define HSES_LT(RG)                                                                                          \
     lowrank_t_kernel<RG><<<lt_grid, LT_THREADS, 0, st>>>(                                            \
         ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
-        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs)
+        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
         switch (g.rank / 4) {
             case 1: HSES_LT(1); break;

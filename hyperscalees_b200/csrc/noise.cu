@@ -100,23 +100,57 @@ __global__ void es_update_dense_kernel(LibmCal cal, const uint64_t* __restrict__
     }
 }
 
-// Pair-folded raw factors for the scratch-based paths (see common.cuh).
-__global__ void pair_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
-                                    int32_t true_epoch, int32_t first_pair, int64_t pairs, int rank,
-                                    int a, int b, const float* __restrict__ pair_weight,
-                                    float* __restrict__ A, float* __restrict__ B) {
-    int64_t p = blockIdx.x;
-    int row = blockIdx.y * blockDim.x + threadIdx.x;
+// Pair-folded raw factors for the scratch-based paths (see common.cuh).  CTA (pair, chunk)
+// writes kPfBlocks blocks of 128 rows of the pair's (b + a, rank) normal block: a thread jumps
+// to its first row once and from then on hops 127 rows ahead after each row it has written.
+constexpr int kPfBlocks = 8;
+__global__ void __launch_bounds__(128)
+pair_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t* __restrict__ hop127,
+                    uint64_t key, int32_t true_epoch, int32_t first_pair, int64_t pairs, int rank, int a,
+                    int b, const float* __restrict__ pair_weight, float* __restrict__ A,
+                    float* __restrict__ B) {
+    // tables that every normal reads stay in shared memory
+    __shared__ double2 log_tab_s[64];
+    __shared__ uint32_t delta_s[512];
+    __shared__ uint64_t hop_s[kJumpWords];
+    for (int i = threadIdx.x; i < 64; i += blockDim.x) log_tab_s[i] = cal.log_tab[i];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        delta_s[i] = cal.log_delta[i];
+        delta_s[256 + i] = cal.cos_delta[i];
+    }
+    for (int i = threadIdx.x; i < kJumpWords; i += blockDim.x) hop_s[i] = hop127[i];
+    __syncthreads();
+    cal.log_tab = log_tab_s;
+    cal.log_delta = delta_s;
+    cal.cos_delta = delta_s + 256;
+    const int64_t p = blockIdx.x;
+    int row = blockIdx.y * (128 * kPfBlocks) + threadIdx.x;
     if (p >= pairs || row >= a + b) return;
     uint64_t s = noise_seed(key, true_epoch, first_pair + (int32_t)p) | 1ull;
     s = jump_by(pow2, s, 2ull * (uint64_t)rank * (uint64_t)row);
-    bool is_a = row >= b;
-    float* dst = is_a ? A + ((size_t)p * a + (row - b)) * rank : B + ((size_t)p * b + row) * rank;
     float w = 1.0f;
-    if (is_a && pair_weight) w = __fsub_rn(pair_weight[2 * p], pair_weight[2 * p + 1]);
-    for (int q = 0; q < rank; ++q) {
-        float z = next_normal(s, cal);
-        dst[q] = (is_a && pair_weight) ? __fmul_rn(z, w) : z;
+    if (pair_weight) w = __fsub_rn(pair_weight[2 * p], pair_weight[2 * p + 1]);
+    for (int blk = 0; blk < kPfBlocks && row < a + b; ++blk, row += 128) {
+        const bool is_a = row >= b;
+        float* dst = is_a ? A + ((size_t)p * a + (row - b)) * rank : B + ((size_t)p * b + row) * rank;
+        const bool weigh = is_a && pair_weight;
+        if ((rank & 3) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            for (int q = 0; q < rank; q += 4) {
+                float z[4];
+                next_normals4(s, cal, z);
+                if (weigh) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) z[j] = __fmul_rn(z[j], w);
+                }
+                *reinterpret_cast<float4*>(dst + q) = make_float4(z[0], z[1], z[2], z[3]);
+            }
+        } else {
+            for (int q = 0; q < rank; ++q) {
+                float z = next_normal(s, cal);
+                dst[q] = weigh ? __fmul_rn(z, w) : z;
+            }
+        }
+        s = jump_apply(hop_s, s);
     }
 }
 
@@ -124,11 +158,15 @@ int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_
                         int32_t first_pair, int64_t pairs, int rank, int a, int b,
                         const float* pair_weight, float* A, float* B) {
     int rows = a + b;
-    HSES_REQUIRE((rows + 127) / 128 <= 65535, "a + b too large");
+    int chunks = (rows + 128 * kPfBlocks - 1) / (128 * kPfBlocks);
+    HSES_REQUIRE(chunks <= 65535, "a + b too large");
     HSES_REQUIRE(pairs >= 1 && pairs < (1ll << 31), "pair count out of range");
-    dim3 grid((unsigned)pairs, (unsigned)((rows + 127) / 128));
+    const uint64_t* hop127 = nullptr;
+    int rc = get_hop_table(ctx, 2ull * (uint64_t)rank * 127, &hop127);
+    if (rc != HSES_OK) return rc;
+    dim3 grid((unsigned)pairs, (unsigned)chunks);
     HSES_KERNEL(ctx, stream, "pair_factors");
-    pair_factors_kernel<<<grid, 128, 0, stream>>>(ctx->cal(), ctx->t.jump_pow2, key, true_epoch,
+    pair_factors_kernel<<<grid, 128, 0, stream>>>(ctx->cal(), ctx->t.jump_pow2, hop127, key, true_epoch,
                                                   first_pair, pairs, rank, a, b, pair_weight, A, B);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
@@ -139,6 +177,38 @@ int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_
 using namespace hses;
 
 extern "C" {
+
+size_t hses_factor_cache_bytes(int64_t n_pairs, int32_t rank, int32_t a, int32_t b) {
+    if (n_pairs < 1 || rank < 1 || a < 1 || b < 1) return 0;
+    return (size_t)n_pairs * (size_t)(a + b) * (size_t)rank * sizeof(float);
+}
+
+int hses_factor_cache_build(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                            int32_t noise_reuse, int32_t first_pair, int64_t n_pairs,
+                            int32_t rank, int32_t a, int32_t b, float* data,
+                            hses_factor_cache* cache) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(cache != nullptr && data != nullptr, "NULL pointer");
+    HSES_REQUIRE(n_pairs >= 1 && first_pair >= 0, "pair range out of bounds");
+    HSES_REQUIRE(rank >= 1 && a >= 1 && b >= 1, "rank, a and b must be positive");
+    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
+    HSES_REQUIRE((reinterpret_cast<uintptr_t>(data) & 15) == 0, "cache data must be 16-byte aligned");
+    int32_t te = true_epoch_of(epoch, noise_reuse);
+    float* A = data;
+    float* B = data + (size_t)n_pairs * a * rank;
+    int rc = launch_pair_factors(ctx, as_stream(stream), key, te, first_pair, n_pairs, rank, a, b,
+                                 nullptr, A, B);
+    if (rc != HSES_OK) return rc;
+    cache->data = data;
+    cache->key = key;
+    cache->true_epoch = te;
+    cache->first_pair = first_pair;
+    cache->n_pairs = n_pairs;
+    cache->rank = rank;
+    cache->a = a;
+    cache->b = b;
+    return HSES_OK;
+}
 
 int hses_normal_fill(hses_ctx* ctx, hses_stream stream, uint64_t seed, float* out, size_t n) {
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");

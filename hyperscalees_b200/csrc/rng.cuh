@@ -120,11 +120,33 @@ HSES_HD uint64_t noise_seed(uint64_t key, int32_t true_epoch, int32_t true_threa
     return h;
 }
 
+// One generator step (shifts 13, 7, 17).  On the device every 64-bit shift is
+// written as 32x32->64 multiplications by a power of two: the product of a word
+// with 2^s holds (word << s) in its low half and (word >> (32 - s)) in its high
+// half, and multiplications issue on the FMA pipe, which this code leaves idle,
+// instead of the integer pipe that bounds it.
 HSES_HD uint64_t xs64_step(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+    uint32_t lo = (uint32_t)x, hi = (uint32_t)(x >> 32);
+    uint64_t m = (uint64_t)lo * 8192u;                 // x ^= x << 13
+    uint32_t h = hi * 8192u;
+    lo ^= (uint32_t)m;
+    hi ^= h ^ (uint32_t)(m >> 32);
+    uint64_t mh = (uint64_t)hi * 33554432u;            // x ^= x >> 7
+    uint64_t ml = (uint64_t)lo * 33554432u;
+    lo ^= (uint32_t)(ml >> 32) ^ (uint32_t)mh;
+    hi ^= (uint32_t)(mh >> 32);
+    m = (uint64_t)lo * 131072u;                        // x ^= x << 17
+    h = hi * 131072u;
+    lo ^= (uint32_t)m;
+    hi ^= h ^ (uint32_t)(m >> 32);
+    return ((uint64_t)hi << 32) | lo;
+#else
     x ^= x << 13;
     x ^= x >> 7;
     x ^= x << 17;
     return x;
+#endif
 }
 
 // eggroll.rs:60-65: noise_reuse==0 pins the epoch bucket to 0; members 2p and
@@ -219,6 +241,19 @@ struct Rounded {
 };
 HSES_HD Rounded round_candidate(double y) {
     Rounded r;
+#if defined(__CUDA_ARCH__)
+    // Word-wise form of the code below.  The fp32 exponent field is the low
+    // eight bits of the fp64 one with bit 7 inverted (the biases differ by 896);
+    // rounding to nearest-even is an integer increment of the truncated pattern.
+    uint32_t hi = (uint32_t)__double2hiint(y), lo = (uint32_t)__double2loint(y);
+    uint32_t low = lo & 0x1fffffffu;
+    uint32_t fs = __funnelshift_l(lo, hi, 3);
+    uint32_t trunc = ((fs ^ 0x40000000u) & 0x7fffffffu) | (hi & 0x80000000u);
+    uint32_t up = (low + (trunc & 1u)) > 0x10000000u ? 1u : 0u;
+    r.bits = trunc + up;
+    r.alt = trunc + 1u - up;
+    r.dist = (uint32_t)abs((int32_t)low - 0x10000000);
+#else
     uint64_t yb = d2u(y);
     uint32_t low = (uint32_t)(yb & 0x1fffffffull);
     r.bits = f2u(d2f_rn(y));
@@ -228,6 +263,7 @@ HSES_HD Rounded round_candidate(double y) {
     uint32_t trunc = sign | (ex << 23) | (uint32_t)((yb >> 29) & 0x7fffffu);
     r.alt = (r.bits == trunc) ? trunc + 1u : trunc;
     r.dist = low >= 0x10000000u ? low - 0x10000000u : 0x10000000u - low;
+#endif
     return r;
 }
 

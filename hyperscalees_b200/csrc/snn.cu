@@ -42,6 +42,7 @@ hses_linear_args layer_args(const hses_snn_model* m, const hses_pop_args* p, int
     g.out_scale_ptr = readout ? m->out_gain_dev : nullptr;
     g.out_row_stride = m->dims[l + 1];
     g.algo = HSES_ALGO_AUTO;
+    g.cache = (p->perturb && m->caches) ? m->caches[l] : nullptr;
     return g;
 }
 
@@ -231,8 +232,25 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
     HSES_REQUIRE(!moments || (m_bufs != nullptr && v_bufs != nullptr), "Adam needs moment buffers");
     for (int l = 0; l < m->n_layers; ++l) {
         int a = m->dims[l + 1], b = m->dims[l];
-        rc = hses_es_update(ctx, stream, m->keys[l], epoch, noise_reuse, 0, n_total, n_total, rank, a, b, sigma, fit,
-                            grad, upd_ws, upd_bytes);
+        hses_update_args u{};
+        u.key = m->keys[l];
+        u.epoch = epoch;
+        u.noise_reuse = noise_reuse;
+        u.first_thread = 0;
+        u.n = n_total;
+        u.n_total = n_total;
+        u.rank = rank;
+        u.a = a;
+        u.b = b;
+        u.sigma = sigma;
+        u.fitness = fit;
+        u.grad = grad;
+        u.workspace = upd_ws;
+        u.workspace_bytes = upd_bytes;
+        u.mode = HSES_UPDATE_GRAD;
+        const hses_factor_cache* c = m->caches ? m->caches[l] : nullptr;
+        if (c && c->first_pair == 0 && c->n_pairs >= n_total / 2) u.cache = c;
+        rc = hses_es_update_ex(ctx, stream, &u);
         if (rc != HSES_OK) return rc;
         rc = hses_solver_step(ctx, stream, solver, step, 1.0f, params[l], grad, moments ? m_bufs[l] : nullptr,
                               moments ? v_bufs[l] : nullptr, (int64_t)a * b);

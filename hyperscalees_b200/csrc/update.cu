@@ -10,6 +10,7 @@
 // scratch (A pre-multiplied by the pair weight), a split-K fp32 GEMM writes
 // per-split partial sums, and a final pass adds the partials in a fixed order
 // so that every rank ends up with bit-identical gradients.
+#include <cstring>
 #include <map>
 #include <mutex>
 
@@ -50,7 +51,8 @@ static UpdatePlan plan_update(int a, int b, int rank, int64_t n) {
 // partial[split][m][n] (+)= sum over the split's pairs and q of A[p][m][q]*B[p][n][q]
 __global__ void __launch_bounds__(UT)
 update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t pairs, int rank,
-                   int a, int b, int accumulate, float* __restrict__ partial) {
+                   int a, int b, int accumulate, const float* __restrict__ pair_weight,
+                   float* __restrict__ partial) {
     __shared__ __align__(16) float sa[UK][UM + 4];
     __shared__ __align__(16) float sb[UK][UN + 4];
     int m0 = blockIdx.y * UM, n0 = blockIdx.x * UN;
@@ -74,7 +76,10 @@ update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int
             int64_t p = kg / rank;
             int q = (int)(kg - p * rank);
             bool kin = kg < k_hi;
-            sa[kk][r] = (kin && m0 + r < a) ? A[((size_t)p * a + m0 + r) * rank + q] : 0.0f;
+            float av = (kin && m0 + r < a) ? A[((size_t)p * a + m0 + r) * rank + q] : 0.0f;
+            // factors read from a cache are unweighted: apply (f_even - f_odd) of the pair here
+            if (pair_weight && kin) av = __fmul_rn(av, __fsub_rn(pair_weight[2 * p], pair_weight[2 * p + 1]));
+            sa[kk][r] = av;
             sb[kk][r] = (kin && n0 + r < b) ? B[((size_t)p * b + n0 + r) * rank + q] : 0.0f;
         }
         __syncthreads();
@@ -108,12 +113,13 @@ update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int
 }
 
 __global__ void update_reduce_kernel(const float* __restrict__ partial, int splits, size_t len,
-                                     float scale, float* __restrict__ grad) {
+                                     float scale, int accumulate, float* __restrict__ grad) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= len) return;
     float s = 0.0f;
     for (int k = 0; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * len + i]);
-    grad[i] = __fmul_rn(s, scale);
+    s = __fmul_rn(s, scale);
+    grad[i] = accumulate ? __fadd_rn(grad[i], s) : s;
 }
 
 // ---------------------------------------------------------------------------
@@ -186,46 +192,93 @@ size_t hses_es_update_workspace_bytes(int32_t a, int32_t b, int32_t rank, int64_
     return plan_update(a, b, rank, n).bytes;
 }
 
+int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(args != nullptr, "args is NULL");
+    const hses_update_args& u = *args;
+    const int a = u.a, b = u.b, rank = u.rank;
+    HSES_REQUIRE(u.n > 0 && u.n % 2 == 0 && u.first_thread >= 0 && u.first_thread % 2 == 0,
+                 "members must form whole antithetic pairs");
+    HSES_REQUIRE(u.n_total >= 1, "n_total must be >= 1");
+    HSES_REQUIRE(rank >= 1 && rank <= 1024 && a >= 1 && b >= 1, "bad shape");
+    HSES_REQUIRE(u.noise_reuse >= 0, "noise_reuse must be >= 0");
+    HSES_REQUIRE(u.fitness != nullptr && u.grad != nullptr, "NULL pointer");
+    HSES_REQUIRE(u.mode == HSES_UPDATE_GRAD || u.mode == HSES_UPDATE_RAW_ACC, "unknown update mode");
+    UpdatePlan p = plan_update(a, b, rank, u.n);
+    HSES_REQUIRE(u.workspace != nullptr && u.workspace_bytes >= p.bytes,
+                 "workspace too small; see hses_es_update_workspace_bytes");
+    HSES_REQUIRE((a + UM - 1) / UM <= 65535, "a too large");
+    cudaStream_t st = as_stream(stream);
+    float* wsA = reinterpret_cast<float*>(u.workspace);
+    float* wsB = wsA + p.a_elems;
+    float* partial = wsB + p.b_elems;
+    const int32_t te = true_epoch_of(u.epoch, u.noise_reuse);
+    const int32_t first_pair = u.first_thread / 2;
+    dim3 grid((unsigned)((b + UN - 1) / UN), (unsigned)((a + UM - 1) / UM), (unsigned)p.splits);
+    if (u.cache) {
+        const hses_factor_cache& c = *u.cache;
+        HSES_REQUIRE(c.data != nullptr && c.key == u.key && c.true_epoch == te && c.rank == rank &&
+                         c.a == a && c.b == b,
+                     "factor cache was built for another parameter, epoch bucket or shape");
+        HSES_REQUIRE(first_pair >= c.first_pair && first_pair + p.pairs <= c.first_pair + c.n_pairs,
+                     "factor cache does not cover these members");
+        const float* cA = c.data + (size_t)(first_pair - c.first_pair) * a * rank;
+        const float* cB = c.data + (size_t)c.n_pairs * a * rank + (size_t)(first_pair - c.first_pair) * b * rank;
+        HSES_KERNEL(ctx, st, "update_gemm");
+        update_gemm_kernel<<<grid, UT, 0, st>>>(cA, cB, p.pairs, rank, a, b, 0, u.fitness, partial);
+        HSES_LAUNCH_CHECK();
+    } else {
+        int chunk_idx = 0;
+        for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
+            int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
+            int rc = launch_pair_factors(ctx, st, u.key, te, first_pair + (int32_t)done, cnt, rank, a, b,
+                                         u.fitness + 2 * done, wsA, wsB);
+            if (rc != HSES_OK) return rc;
+            HSES_KERNEL(ctx, st, "update_gemm");
+            update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, nullptr, partial);
+            HSES_LAUNCH_CHECK();
+        }
+    }
+    const float base_sigma = u.sigma / sqrtf((float)rank);
+    float scale;
+    if (u.mode == HSES_UPDATE_GRAD) {
+        // grad = -( (sum * base_sigma / N) * sqrt(N) ), eggroll.rs:365-372, 402-403
+        float nf = (float)u.n_total;
+        scale = -(base_sigma * (1.0f / nf)) * sqrtf(nf);
+    } else {
+        scale = base_sigma;
+    }
+    size_t len = (size_t)a * b;
+    HSES_KERNEL(ctx, st, "update_reduce");
+    update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(
+        partial, p.splits, len, scale, u.mode == HSES_UPDATE_RAW_ACC, u.grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
 int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
                    int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,
                    int32_t rank, int32_t a, int32_t b, float sigma, const float* fitness,
                    float* grad, void* workspace, size_t workspace_bytes) {
-    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
-    HSES_REQUIRE(n > 0 && n % 2 == 0 && first_thread >= 0 && first_thread % 2 == 0,
-                 "members must form whole antithetic pairs");
-    HSES_REQUIRE(n_total >= 1, "n_total must be >= 1");
-    HSES_REQUIRE(rank >= 1 && rank <= 1024 && a >= 1 && b >= 1, "bad shape");
-    HSES_REQUIRE(noise_reuse >= 0, "noise_reuse must be >= 0");
-    HSES_REQUIRE(fitness != nullptr && grad != nullptr, "NULL pointer");
-    UpdatePlan p = plan_update(a, b, rank, n);
-    HSES_REQUIRE(workspace != nullptr && workspace_bytes >= p.bytes,
-                 "workspace too small; see hses_es_update_workspace_bytes");
-    HSES_REQUIRE((a + UM - 1) / UM <= 65535, "a too large");
-    cudaStream_t st = as_stream(stream);
-    float* wsA = reinterpret_cast<float*>(workspace);
-    float* wsB = wsA + p.a_elems;
-    float* partial = wsB + p.b_elems;
-    int32_t te = true_epoch_of(epoch, noise_reuse);
-    dim3 grid((unsigned)((b + UN - 1) / UN), (unsigned)((a + UM - 1) / UM), (unsigned)p.splits);
-    int chunk_idx = 0;
-    for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
-        int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
-        int rc = launch_pair_factors(ctx, st, key, te, first_thread / 2 + (int32_t)done, cnt, rank, a,
-                                     b, fitness + 2 * done, wsA, wsB);
-        if (rc != HSES_OK) return rc;
-        HSES_KERNEL(ctx, st, "update_gemm");
-        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, partial);
-        HSES_LAUNCH_CHECK();
-    }
-    // grad = -( (sum * base_sigma / N) * sqrt(N) ), eggroll.rs:365-372, 402-403
-    float nf = (float)n_total;
-    float scale = -((sigma / sqrtf((float)rank)) * (1.0f / nf)) * sqrtf(nf);
-    size_t len = (size_t)a * b;
-    HSES_KERNEL(ctx, st, "update_reduce");
-    update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
-                                                                       grad);
-    HSES_LAUNCH_CHECK();
-    return HSES_OK;
+    hses_update_args u;
+    memset(&u, 0, sizeof(u));
+    u.key = key;
+    u.epoch = epoch;
+    u.noise_reuse = noise_reuse;
+    u.first_thread = first_thread;
+    u.n = n;
+    u.n_total = n_total;
+    u.rank = rank;
+    u.a = a;
+    u.b = b;
+    u.sigma = sigma;
+    u.fitness = fitness;
+    u.grad = grad;
+    u.workspace = workspace;
+    u.workspace_bytes = workspace_bytes;
+    u.cache = nullptr;
+    u.mode = HSES_UPDATE_GRAD;
+    return hses_es_update_ex(ctx, stream, &u);
 }
 
 size_t hses_es_update_static_scratch_bytes(void) { return kStaticScratchBytes; }
@@ -268,7 +321,7 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
         HSES_KERNEL(ctx, st, "update_gemm");
         // the first chunk overwrites the partial sums, so nothing left behind by an
         // earlier call is read
-        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, partial);
+        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, nullptr, partial);
         HSES_LAUNCH_CHECK();
     }
     float nf = (float)n_total;
@@ -276,7 +329,7 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
     size_t len = (size_t)a * b;
     HSES_KERNEL(ctx, st, "update_reduce");
     update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
-                                                                       grad);
+                                                                       0, grad);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

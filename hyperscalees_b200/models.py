@@ -152,6 +152,25 @@ class PopulationStep:
         if kind in ("adam", "adamw"):
             self.moments = ([torch.zeros_like(p) for p in self.params], [torch.zeros_like(p) for p in self.params])
         self._ws = None
+        self.caches = None
+
+    def build_caches(self, epoch: int = 0, n_total: Optional[int] = None) -> int:
+        """Generates the factors of every layer once and keeps them on the device
+        (LoraNoiseCache, eggroll.rs:229-309); eval() and update() then read them instead of
+        regenerating.  Covers the whole population when n_total is given (needed for update()),
+        else this shard's members.  Valid until the epoch bucket changes; returns the bytes held."""
+        if n_total is None:
+            first_pair = self.first_thread // 2
+            n_pairs = (self.first_thread + self.n_pop - 1) // 2 - first_pair + 1
+        else:
+            first_pair, n_pairs = 0, n_total // 2
+        self.caches = [ops.FactorCache(self.keys[l], epoch, self.frozen.noise_reuse, self.frozen.rank,
+                                       w.shape[0], w.shape[1], n_pairs, first_pair, device=self.net.device)
+                       for l, w in enumerate(self.net.weights)]
+        return sum(c.data.numel() * 4 for c in self.caches)
+
+    def drop_caches(self) -> None:
+        self.caches = None
 
     def _model(self):
         C, _lib = self.C, self._lib
@@ -161,9 +180,12 @@ class PopulationStep:
         ws = (C.c_int64 * n)(*[w.stride(0) for w in self.net.weights])
         keys = (C.c_uint64 * n)(*self.keys[:n])
         vth = (C.c_float * max(n - 1, 1))(*([self.net.v_th] * max(n - 1, 1)))
+        cp = None
+        if self.caches is not None:
+            cp = (C.POINTER(_lib.FactorCacheDesc) * n)(*[C.pointer(c.desc) for c in self.caches])
         m = _lib.SnnModelDesc(n, dims, wp, ws, keys, 1.0, self.net.out_gain.data_ptr(), self.net.tau_m, vth,
-                              self.net.reset_mode)
-        self._keep = (dims, wp, ws, keys, vth)
+                              self.net.reset_mode, cp)
+        self._keep = (dims, wp, ws, keys, vth, cp)
         return m
 
     def _args(self, epoch: int, perturb: bool = True):

@@ -164,10 +164,11 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      lif: bool = False, tau_m: float = 20.0, v_th: float = 0.3,
                      reset_mode: int = RESET_HARD, out_scale: float = 1.0,
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
-                     algo: int = ALGO_AUTO):
+                     algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
-    the charged potentials."""
+    the charged potentials.  With `cache` the factors are read from it instead of
+    being regenerated (same bits)."""
     _check(x, "x")
     _check(param, "param", ndim=2)
     rows, k, xs = _rows_2d(x, "x")
@@ -194,6 +195,8 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.out, g.out_row_stride = out.data_ptr(), out.stride(0) if rows > 1 else max(out.stride(0), a)
     g.potentials = pot.data_ptr() if pot is not None else None
     g.algo = algo
+    if cache is not None:
+        g.cache = C.pointer(cache.desc)
     L = _lib.load()
     need = int(L.hses_perturbed_linear_workspace_bytes(C.byref(g)))
     ws = _workspace(x.device, need)
@@ -249,20 +252,66 @@ def convert_fitnesses(raw: torch.Tensor, group_size: int = 0, want_stats: bool =
     return (out, stats) if want_stats else out
 
 
+UPDATE_GRAD, UPDATE_RAW_ACC = 0, 1
+
+
+class FactorCache:
+    """Raw factors of a range of antithetic pairs of one parameter, resident on the device
+    (LoraNoiseCache, eggroll.rs:229-309).  Valid for the epoch bucket it was built for."""
+
+    def __init__(self, key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int,
+                 n_pairs: int, first_pair: int = 0, device=None):
+        ctx = get_context(device)
+        dev = torch.device("cuda", ctx.device)
+        L = _lib.load()
+        need = int(L.hses_factor_cache_bytes(n_pairs, rank, a, b))
+        if need == 0:
+            raise ValueError("empty factor cache")
+        self.data = torch.empty(need // 4, dtype=torch.float32, device=dev)
+        self.desc = _lib.FactorCacheDesc()
+        with torch.cuda.device(dev):
+            _lib.check(L.hses_factor_cache_build(ctx.handle, current_stream(), C.c_uint64(key & _U64),
+                                                 epoch, noise_reuse, first_pair, n_pairs, rank, a, b,
+                                                 _ptr(self.data), C.byref(self.desc)))
+        self.n_pairs, self.rank, self.a, self.b = n_pairs, rank, a, b
+
+    @property
+    def A(self) -> torch.Tensor:
+        """(n_pairs, a, rank) raw normals."""
+        return self.data[: self.n_pairs * self.a * self.rank].view(self.n_pairs, self.a, self.rank)
+
+    @property
+    def B(self) -> torch.Tensor:
+        """(n_pairs, b, rank) raw normals."""
+        return self.data[self.n_pairs * self.a * self.rank:].view(self.n_pairs, self.b, self.rank)
+
+
 def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int, sigma: float,
               fitness_: torch.Tensor, first_thread: int = 0, n_total: Optional[int] = None,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, cache: Optional[FactorCache] = None,
+              mode: int = UPDATE_GRAD) -> torch.Tensor:
+    """Fitness-weighted update of one LoRA-noised matrix.  mode UPDATE_RAW_ACC adds
+    sum_i s_i A_i B_i^T (A_i scaled by sign*sigma/sqrt(rank)) to `out` instead."""
     _check(fitness_, "fitness", ndim=1)
     n = fitness_.numel()
     if out is None:
-        out = torch.empty((a, b), dtype=torch.float32, device=fitness_.device)
+        if mode == UPDATE_RAW_ACC:
+            out = torch.zeros((a, b), dtype=torch.float32, device=fitness_.device)
+        else:
+            out = torch.empty((a, b), dtype=torch.float32, device=fitness_.device)
     L = _lib.load()
     need = int(L.hses_es_update_workspace_bytes(a, b, rank, n))
     ws = _workspace(fitness_.device, need)
     ctx = get_context(fitness_.device)
-    _lib.check(L.hses_es_update(ctx.handle, current_stream(), C.c_uint64(key & _U64), epoch,
-                                noise_reuse, first_thread, n, n if n_total is None else n_total,
-                                rank, a, b, sigma, _ptr(fitness_), _ptr(out), _ptr(ws), need))
+    u = _lib.UpdateArgs()
+    u.key, u.epoch, u.noise_reuse, u.first_thread = key & _U64, epoch, noise_reuse, first_thread
+    u.n, u.n_total, u.rank, u.a, u.b, u.sigma = n, n if n_total is None else n_total, rank, a, b, sigma
+    u.fitness, u.grad = fitness_.data_ptr(), out.data_ptr()
+    u.workspace, u.workspace_bytes = (ws.data_ptr() if ws is not None else None), need
+    if cache is not None:
+        u.cache = C.pointer(cache.desc)
+    u.mode = mode
+    _lib.check(L.hses_es_update_ex(ctx.handle, current_stream(), C.byref(u)))
     return out
 
 

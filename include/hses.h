@@ -125,6 +125,35 @@ int hses_lif_scan(hses_ctx* ctx, hses_stream stream, const float* cur /*device*/
                   int64_t n, int32_t h, int64_t row_stride, float* v /*device or NULL*/,
                   float tau_m, float v_th, int32_t reset_mode, float* spikes /*device*/);
 
+/* ---- LoraNoiseCache / build_lora_noise_cache, eggroll.rs:229-309: the raw
+ *      factors of a contiguous range of antithetic pairs of one parameter,
+ *      generated once and kept in device memory, so that the forward pass and
+ *      the update of a step (and, while the epoch bucket does not change, of
+ *      later steps) read them instead of regenerating them.  Reading a factor
+ *      costs 4 bytes of HBM traffic, regenerating it about 150 instructions.
+ *      Layout of `data`: A (n_pairs, a, rank) then B (n_pairs, b, rank), both
+ *      raw N(0,1): neither the member's sign nor sigma/sqrt(rank) is applied, so
+ *      one cache serves both members of a pair and any sigma.  The reference
+ *      keeps its cache in host memory, one entry per member, and only for
+ *      noise_reuse == 0; this one is valid for the epoch bucket it was built
+ *      for and is checked against key and bucket by every call that takes it. */
+typedef struct {
+    const float* data; /* device, hses_factor_cache_bytes() */
+    uint64_t key;
+    int32_t true_epoch; /* epoch bucket: 0 when noise_reuse == 0, else epoch / noise_reuse */
+    int32_t first_pair; /* = thread id / 2 of the first member covered */
+    int64_t n_pairs;
+    int32_t rank;
+    int32_t a;
+    int32_t b;
+} hses_factor_cache;
+size_t hses_factor_cache_bytes(int64_t n_pairs, int32_t rank, int32_t a, int32_t b);
+/* Fills `data` and writes the descriptor to *cache. */
+int hses_factor_cache_build(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
+                            int32_t noise_reuse, int32_t first_pair, int64_t n_pairs,
+                            int32_t rank, int32_t a, int32_t b, float* data /*device*/,
+                            hses_factor_cache* cache /*host, out*/);
+
 /* ---- do_mm, eggroll.rs:419-446, for a whole population in one call, with
  *      an optional fused lif_step (snn.rs:53-65) from v0 = 0.
  *      x is (t_steps, n_pop, bm, k): row R belongs to member (R / bm) % n_pop,
@@ -162,6 +191,8 @@ typedef struct {
     int32_t algo;      /* hses_linear_algo */
     void* workspace;   /* device scratch, hses_perturbed_linear_workspace_bytes() */
     size_t workspace_bytes;
+    const hses_factor_cache* cache; /* host pointer or NULL: take the factors from this cache
+                                       instead of regenerating them (same results, bit for bit) */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);
@@ -202,6 +233,39 @@ int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoc
                    int32_t rank, int32_t a, int32_t b, float sigma,
                    const float* fitness /*device*/, float* grad /*device (a,b) dense*/,
                    void* workspace /*device*/, size_t workspace_bytes);
+
+/* ---- The same contraction with two more choices, for the trainer's chunked
+ *      accumulation (accumulated_update / accumulated_update_cached,
+ *      eggroll.rs:550-702):
+ *        cache  when not NULL the factors are read from it, not regenerated;
+ *        mode   HSES_UPDATE_GRAD: what hses_es_update computes;
+ *               HSES_UPDATE_RAW_ACC: grad += sum_i s_i A_i B_iᵀ with A_i scaled
+ *               by sign*sigma/sqrt(rank) (lora_einsum_raw, eggroll.rs:726-738),
+ *               `fitness` holding raw scores; chunks of one step add up in
+ *               grad, and combine_affine_grads (eggroll.rs:902-915) turns the
+ *               sums into the gradient once mean and std are known.  The
+ *               companion sum of lora_einsum_ones over whole antithetic pairs
+ *               is exactly zero (A_2p+1 = -A_2p), so it needs no kernel. ---- */
+enum { HSES_UPDATE_GRAD = 0, HSES_UPDATE_RAW_ACC = 1 };
+typedef struct {
+    uint64_t key;
+    int32_t epoch;
+    int32_t noise_reuse;
+    int32_t first_thread;
+    int64_t n;
+    int64_t n_total;
+    int32_t rank;
+    int32_t a;
+    int32_t b;
+    float sigma;
+    const float* fitness; /* device, n */
+    float* grad;          /* device (a,b) dense */
+    void* workspace;      /* device, hses_es_update_workspace_bytes() */
+    size_t workspace_bytes;
+    const hses_factor_cache* cache; /* host pointer or NULL */
+    int32_t mode;
+} hses_update_args;
+int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args);
 
 /* ---- hses_es_update for callers that cannot hand over a workspace.  It has
  *      no counterpart in the reference.  Some hosts of this library never get
@@ -265,6 +329,10 @@ typedef struct {
     float tau_m;
     const float* v_th;             /* n_layers - 1 thresholds, one per hidden layer */
     int32_t reset_mode;
+    const hses_factor_cache* const* caches; /* NULL, or n_layers host pointers (NULL entries allowed):
+                                               factor caches the perturbed layers read instead of
+                                               regenerating; hses_population_update uses an entry
+                                               only when it covers the whole population */
 } hses_snn_model;
 
 typedef struct {
