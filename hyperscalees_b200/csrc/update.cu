@@ -51,7 +51,7 @@ static UpdatePlan plan_update(int a, int b, int rank, int64_t n) {
 // partial[split][m][n] (+)= sum over the split's pairs and q of A[p][m][q]*B[p][n][q]
 __global__ void __launch_bounds__(UT)
 update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t pairs, int rank,
-                   int a, int b, int accumulate, const float* __restrict__ pair_weight,
+                   int a, int b, int accumulate, const float* __restrict__ pair_weight, int sign_factors,
                    float* __restrict__ partial) {
     __shared__ __align__(16) float sa[UK][UM + 4];
     __shared__ __align__(16) float sb[UK][UN + 4];
@@ -77,10 +77,15 @@ update_gemm_kernel(const float* __restrict__ A, const float* __restrict__ B, int
             int q = (int)(kg - p * rank);
             bool kin = kg < k_hi;
             float av = (kin && m0 + r < a) ? A[((size_t)p * a + m0 + r) * rank + q] : 0.0f;
+            float bv = (kin && n0 + r < b) ? B[((size_t)p * b + n0 + r) * rank + q] : 0.0f;
+            if (sign_factors) {  // AltEggRoll contracts the sign patterns of the raw factors
+                av = av > 0.0f ? 1.0f : av < 0.0f ? -1.0f : 0.0f;
+                bv = bv > 0.0f ? 1.0f : bv < 0.0f ? -1.0f : 0.0f;
+            }
             // factors read from a cache are unweighted: apply (f_even - f_odd) of the pair here
             if (pair_weight && kin) av = __fmul_rn(av, __fsub_rn(pair_weight[2 * p], pair_weight[2 * p + 1]));
             sa[kk][r] = av;
-            sb[kk][r] = (kin && n0 + r < b) ? B[((size_t)p * b + n0 + r) * rank + q] : 0.0f;
+            sb[kk][r] = bv;
         }
         __syncthreads();
 #pragma unroll
@@ -225,17 +230,20 @@ int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args*
         const float* cA = c.data + (size_t)(first_pair - c.first_pair) * a * rank;
         const float* cB = c.data + (size_t)c.n_pairs * a * rank + (size_t)(first_pair - c.first_pair) * b * rank;
         HSES_KERNEL(ctx, st, "update_gemm");
-        update_gemm_kernel<<<grid, UT, 0, st>>>(cA, cB, p.pairs, rank, a, b, 0, u.fitness, partial);
+        update_gemm_kernel<<<grid, UT, 0, st>>>(cA, cB, p.pairs, rank, a, b, 0, u.fitness, u.sign_factors, partial);
         HSES_LAUNCH_CHECK();
     } else {
         int chunk_idx = 0;
         for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
             int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
+            // the sign variant must see the unweighted factors: the pair weight is applied by the loader
+            const float* w = u.fitness + 2 * done;
             int rc = launch_pair_factors(ctx, st, u.key, te, first_pair + (int32_t)done, cnt, rank, a, b,
-                                         u.fitness + 2 * done, wsA, wsB);
+                                         u.sign_factors ? nullptr : w, wsA, wsB);
             if (rc != HSES_OK) return rc;
             HSES_KERNEL(ctx, st, "update_gemm");
-            update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, nullptr, partial);
+            update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0,
+                                                    u.sign_factors ? w : nullptr, u.sign_factors, partial);
             HSES_LAUNCH_CHECK();
         }
     }
@@ -321,7 +329,7 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
         HSES_KERNEL(ctx, st, "update_gemm");
         // the first chunk overwrites the partial sums, so nothing left behind by an
         // earlier call is read
-        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, nullptr, partial);
+        update_gemm_kernel<<<grid, UT, 0, st>>>(wsA, wsB, cnt, rank, a, b, chunk_idx > 0, nullptr, 0, partial);
         HSES_LAUNCH_CHECK();
     }
     float nf = (float)n_total;

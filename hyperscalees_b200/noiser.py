@@ -205,6 +205,83 @@ def combine_affine_grads(grad_acc: Sequence[torch.Tensor], ones_acc: Sequence[to
     return out
 
 
+class LoraNoiseCache:
+    """eggroll.rs:229-309.  One device-resident factor cache per LoRA parameter (None for the
+    other classes), covering thread ids 0..batch-1.  The reference keeps (batch, a+b, r) in host
+    memory and only allows noise_reuse == 0; here the caches live on the GPU, hold one entry per
+    antithetic pair and are valid for the epoch bucket they were built for."""
+
+    def __init__(self, buffers, shapes, batch: int, rank: int):
+        self.buffers, self.shapes, self.batch, self.rank = buffers, shapes, batch, rank
+
+
+def build_lora_noise_cache(params: Sequence[torch.Tensor], base_keys: Sequence[int],
+                           es_classes: Sequence[int], batch: int, rank: int, noise_reuse: int,
+                           epoch: int = 0) -> LoraNoiseCache:
+    """eggroll.rs:275-309."""
+    if batch % 2:
+        raise ValueError("batch must consist of whole antithetic pairs")
+    buffers = []
+    for p, key, cls in zip(params, base_keys, es_classes):
+        if cls != MM_PARAM:
+            buffers.append(None)
+            continue
+        a, b = p.shape
+        buffers.append(ops.FactorCache(key, epoch, noise_reuse, rank, a, b, batch // 2, 0, device=p.device))
+    return LoraNoiseCache(buffers, [tuple(p.shape) for p in params], batch, rank)
+
+
+def accumulated_update_cached(frozen: FrozenNoiserParams, noiser: NoiserParams,
+                              params: Sequence[torch.Tensor], base_keys: Sequence[int],
+                              es_classes: Sequence[int], conv_full: torch.Tensor,
+                              thread_ids: Sequence[int], epoch: int, accumulate: int, chunk: int,
+                              noise_cache: Optional[LoraNoiseCache] = None) -> List[torch.Tensor]:
+    """eggroll.rs:579-702: the update of a batch of accumulate*chunk members computed chunk by
+    chunk — per chunk sum_i f_i A_i B_i^T (A_i carrying sign*sigma/sqrt(rank)) is added to an
+    accumulator, the total is scaled by -1/sqrt(batch), and the solver runs ONCE (its step
+    counter advances by one, not by `accumulate`).  Thread ids must be first, first+1, ... with
+    even `first` and even `chunk`, which is how the trainer numbers them."""
+    if len(params) == 0:
+        return []
+    batch = accumulate * chunk
+    tids = list(thread_ids)
+    if len(tids) != batch or conv_full.numel() != batch:
+        raise ValueError("thread_ids and conv_full must have accumulate*chunk entries")
+    if chunk % 2 or tids[0] % 2 or any(t != tids[0] + i for i, t in enumerate(tids)):
+        raise ValueError("thread ids must be consecutive, start even, and chunks must hold whole pairs")
+    scale = float(np.float32(-1.0) / np.sqrt(np.float32(batch)))
+    grads = []
+    for idx, (p, key, cls) in enumerate(zip(params, base_keys, es_classes)):
+        a, b = p.shape
+        acc = torch.zeros((a, b), dtype=torch.float32, device=p.device)
+        if cls == MM_PARAM:
+            cache = noise_cache.buffers[idx] if noise_cache is not None else None
+            for k in range(accumulate):
+                lo = k * chunk
+                ops.es_update(key, epoch, frozen.noise_reuse, frozen.rank, a, b, noiser.sigma,
+                              conv_full[lo:lo + chunk].contiguous(), first_thread=tids[lo], out=acc,
+                              cache=cache, mode=ops.UPDATE_RAW_ACC)
+        elif cls == PARAM and not frozen.freeze_nonlora:
+            for k in range(accumulate):
+                lo = k * chunk
+                # es_update_dense with n_total = chunk returns -sum_i f_i noise_i / sqrt(chunk)
+                g = ops.es_update_dense(key, epoch, frozen.noise_reuse, (a, b), noiser.sigma,
+                                        conv_full[lo:lo + chunk].contiguous(), first_thread=tids[lo],
+                                        n_total=chunk)
+                ops.solver_step(ops.SGD, 0, acc, g, lr=float(np.sqrt(np.float32(chunk))))  # acc -= sqrt(chunk)*g
+        g = torch.zeros_like(acc)
+        ops.solver_step(ops.SGD, 0, g, acc, lr=-scale)  # g = scale * acc
+        grads.append(g)
+    return frozen.solver.update(params, grads, noiser.opt_state)
+
+
+def accumulated_update(frozen, noiser, params, base_keys, es_classes, conv_full, thread_ids, epoch,
+                       accumulate, chunk) -> List[torch.Tensor]:
+    """eggroll.rs:550-575: the uncached form (factors regenerated chunk by chunk)."""
+    return accumulated_update_cached(frozen, noiser, params, base_keys, es_classes, conv_full,
+                                     thread_ids, epoch, accumulate, chunk, None)
+
+
 def _dense_fitness(scores: np.ndarray, iterinfos: Sequence[IterInfo], noise_reuse: int
                    ) -> Dict[int, Tuple[int, np.ndarray]]:
     """Scatter per-member scores into dense, pair-aligned vectors keyed by epoch bucket."""
@@ -228,6 +305,9 @@ def _dense_fitness(scores: np.ndarray, iterinfos: Sequence[IterInfo], noise_reus
 
 class EggRoll:
     """The EggRoll noiser (eggroll.rs:917-1005)."""
+
+    #: AltEggRoll sets this: its LoRA update contracts the signs of the factors.
+    sign_factors = False
 
     def do_mm(self, frozen: FrozenNoiserParams, noiser: NoiserParams, param: torch.Tensor,
               base_key: int, iterinfo: Optional[IterInfo], x: torch.Tensor) -> torch.Tensor:
@@ -308,7 +388,8 @@ class EggRoll:
             for lo, vec, ep in groups.values():
                 if cls == MM_PARAM:
                     g = ops.es_update(key, ep, frozen.noise_reuse, frozen.rank, a, b, noiser.sigma,
-                                      vec, first_thread=lo, n_total=n_total)
+                                      vec, first_thread=lo, n_total=n_total,
+                                      sign_factors=self.sign_factors)
                 elif cls == PARAM and not frozen.freeze_nonlora:
                     g = ops.es_update_dense(key, ep, frozen.noise_reuse, (a, b), noiser.sigma, vec,
                                             first_thread=lo, n_total=n_total)
@@ -330,3 +411,10 @@ class EggRoll:
             return []
         grads = self.grads(frozen, noiser, params, base_keys, fitnesses, iterinfos, es_classes)
         return frozen.solver.update(params, grads, noiser.opt_state)
+
+
+class AltEggRoll(EggRoll):
+    """hyperscalees-noiser/src/alteggroll.rs: EggRoll everywhere except the LoRA update, which
+    uses sign(A_i) * (sigma * f_i / sqrt(rank)) and sign(B_i) (alteggroll.rs:65-90)."""
+
+    sign_factors = True

@@ -289,7 +289,7 @@ class FactorCache:
 def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int, sigma: float,
               fitness_: torch.Tensor, first_thread: int = 0, n_total: Optional[int] = None,
               out: Optional[torch.Tensor] = None, cache: Optional[FactorCache] = None,
-              mode: int = UPDATE_GRAD) -> torch.Tensor:
+              mode: int = UPDATE_GRAD, sign_factors: bool = False) -> torch.Tensor:
     """Fitness-weighted update of one LoRA-noised matrix.  mode UPDATE_RAW_ACC adds
     sum_i s_i A_i B_i^T (A_i scaled by sign*sigma/sqrt(rank)) to `out` instead."""
     _check(fitness_, "fitness", ndim=1)
@@ -311,6 +311,7 @@ def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int,
     if cache is not None:
         u.cache = C.pointer(cache.desc)
     u.mode = mode
+    u.sign_factors = int(sign_factors)
     _lib.check(L.hses_es_update_ex(ctx.handle, current_stream(), C.byref(u)))
     return out
 

@@ -264,6 +264,8 @@ typedef struct {
     size_t workspace_bytes;
     const hses_factor_cache* cache; /* host pointer or NULL */
     int32_t mode;
+    int32_t sign_factors; /* 1: AltEggRoll's update, every factor entry replaced by its sign
+                             (hyperscalees-noiser/src/alteggroll.rs:65-90) */
 } hses_update_args;
 int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args);
 

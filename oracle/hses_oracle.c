@@ -377,10 +377,10 @@ void hso_snn_forward(const hso_snn_t *m, const float *spikes_in, int T, int bm,
 /* eggroll.rs:353-373 (simple_lora_update) followed by the -g*sqrt(N) of
  * do_update_with (eggroll.rs:384-404).  acc += (A_i·B_iᵀ)·f_i in member
  * order; the rank-r dot product is rounded before the fitness scale. */
-void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
-                   const float *scores, const int32_t *epochs,
-                   const int32_t *thread_ids, size_t n, int32_t noise_reuse,
-                   float *out) {
+static void lora_grad_impl(float sigma, uint64_t key, int a, int b, int rank,
+                           const float *scores, const int32_t *epochs,
+                           const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                           int sign_factors, float *out) {
     float base_sigma = sigma / sqrtf((float)rank);
     size_t ab = (size_t)a * b;
     int nthreads = hso_num_threads();
@@ -402,6 +402,13 @@ void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
         size_t lo = n * (size_t)tid / nt, hi = n * (size_t)(tid + 1) / nt;
         for (size_t i = lo; i < hi; ++i) {
             hso_lora_params(base_sigma, key, rank, epochs[i], thread_ids[i], a, b, noise_reuse, A, B);
+            if (sign_factors) {
+                /* alteggroll.rs:65-90: A_new = sign(A) * (sigma * f / sqrt(rank)), B_new = sign(B);
+                 * the fitness is folded in below, after the dot product, which is exact here
+                 * because every product is +-base_sigma or 0 */
+                for (int e = 0; e < a * rank; ++e) A[e] = (A[e] > 0.0f ? 1.0f : A[e] < 0.0f ? -1.0f : 0.0f) * base_sigma;
+                for (int e = 0; e < b * rank; ++e) B[e] = B[e] > 0.0f ? 1.0f : B[e] < 0.0f ? -1.0f : 0.0f;
+            }
             float f = scores[i];
             for (int p = 0; p < a; ++p)
                 for (int q = 0; q < b; ++q) {
@@ -419,6 +426,22 @@ void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
         out[j] = -((s * inv_n) * rootn);
     }
     free(partial);
+}
+
+void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
+                   const float *scores, const int32_t *epochs,
+                   const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                   float *out) {
+    lora_grad_impl(sigma, key, a, b, rank, scores, epochs, thread_ids, n, noise_reuse, 0, out);
+}
+
+/* AltEggRoll (hyperscalees-noiser/src/alteggroll.rs:65-90 + do_update_with): the same update
+ * with every factor entry replaced by its sign. */
+void hso_alt_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
+                       const float *scores, const int32_t *epochs,
+                       const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                       float *out) {
+    lora_grad_impl(sigma, key, a, b, rank, scores, epochs, thread_ids, n, noise_reuse, 1, out);
 }
 
 /* eggroll.rs:331-350 (simple_full_update) + do_update_with. */

@@ -106,6 +106,10 @@ void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
                    const float *scores, const int32_t *epochs,
                    const int32_t *thread_ids, size_t n, int32_t noise_reuse,
                    float *out);
+void hso_alt_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
+                   const float *scores, const int32_t *epochs,
+                   const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                   float *out);
 void hso_full_grad(float sigma, uint64_t key, int rows, int cols,
                    const float *scores, const int32_t *epochs,
                    const int32_t *thread_ids, size_t n, int32_t noise_reuse,

@@ -250,6 +250,16 @@ def lora_grad(sigma, key, a, b, rank, scores, epochs, thread_ids, noise_reuse=0)
     return out
 
 
+
+def alt_lora_grad(sigma, key, a, b, rank, scores, epochs, thread_ids, noise_reuse=0):
+    scores, sp = _f(scores)
+    epochs, ep = _i(epochs)
+    tids, tp = _i(thread_ids)
+    out = np.empty((a, b), dtype=np.float32)
+    lib().hso_alt_lora_grad(C.c_float(sigma), C.c_uint64(key), a, b, rank, sp, ep, tp,
+                        C.c_size_t(scores.size), noise_reuse, out.ctypes.data_as(_f32p))
+    return out
+
 def full_grad(sigma, key, rows, cols, scores, epochs, thread_ids, noise_reuse=0,
               freeze_nonlora=False):
     scores, sp = _f(scores)

@@ -57,3 +57,31 @@ def test_es_update_dense_matches_oracle(hs, oracle, shape):
     got = ops.es_update_dense(KEY, 1, 0, shape, 0.3, dev(f), first_thread=2).cpu().numpy()
     want = oracle.full_grad(0.3, KEY, shape[0], shape[1], f, [1] * n, list(range(2, 2 + n)), 0)
     assert np.abs(got - want).max() <= 1e-3 * np.abs(want).max() + 1e-7
+
+
+def test_alteggroll_sign_update_matches_oracle(hs, oracle):
+    """AltEggRoll (alteggroll.rs:65-90): the update contracts the sign patterns of the factors."""
+    from hyperscalees_b200 import ops
+    n, rank, a, b, sigma, key = 48, 4, 18, 30, 0.4, 123
+    f = np.random.default_rng(4).standard_normal(n).astype(np.float32)
+    want = oracle.alt_lora_grad(sigma, key, a, b, rank, f, [1] * n, list(range(n)), 0)
+    ft = torch.from_numpy(f).cuda()
+    got = ops.es_update(key, 1, 0, rank, a, b, sigma, ft, sign_factors=True)
+    assert np.allclose(got.cpu().numpy(), want, rtol=1e-3, atol=1e-6)
+    plain = ops.es_update(key, 1, 0, rank, a, b, sigma, ft)
+    assert not torch.equal(plain, got)     # alteggroll.rs:252-266: differs from EggRoll's update
+    cache = ops.FactorCache(key, 1, 0, rank, a, b, n // 2)
+    assert torch.equal(ops.es_update(key, 1, 0, rank, a, b, sigma, ft, cache=cache, sign_factors=True), got)
+
+
+def test_alteggroll_noiser_mirror(hs, oracle):
+    from hyperscalees_b200 import noiser
+    p = torch.zeros(2, 2, device="cuda")
+    frozen, nz = noiser.init_noiser([p], 0.5, 0.1, 0, False, 0, 1, noiser.Solver.sgd(0.1))
+    fit = torch.tensor([1.0, 0.0], device="cuda")
+    infos = [noiser.IterInfo(0, 0), noiser.IterInfo(0, 1)]
+    (g,) = noiser.AltEggRoll().grads(frozen, nz, [p], [7], fit, infos, [noiser.MM_PARAM])
+    # alteggroll.rs:205-243 with N = 2: entries are -(sigma/sqrt(r)) * sign(a_i) * sign(b_j) / N * sqrt(N)
+    A, B = oracle.lora_params(1.0, 7, 1, 0, 0, 2, 2, 0)
+    want = -(0.5 * np.sign(A) @ np.sign(B).T) / 2 * np.sqrt(2.0)
+    assert np.allclose(g.cpu().numpy(), want, rtol=1e-5)
