@@ -42,7 +42,7 @@ class UpdateArgs(C.Structure):
                 ("rank", C.c_int32), ("a", C.c_int32), ("b", C.c_int32), ("sigma", C.c_float),
                 ("fitness", C.c_void_p), ("grad", C.c_void_p), ("workspace", C.c_void_p),
                 ("workspace_bytes", C.c_size_t), ("cache", C.POINTER(FactorCacheDesc)),
-                ("mode", C.c_int32), ("sign_factors", C.c_int32)]
+                ("mode", C.c_int32), ("sign_factors", C.c_int32), ("algo", C.c_int32)]
 
 
 class LinearArgs(C.Structure):

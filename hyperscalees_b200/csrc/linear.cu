@@ -187,7 +187,7 @@ static int check_args(const hses_linear_args* g) {
         HSES_REQUIRE(g->reset_mode == HSES_RESET_HARD || g->reset_mode == HSES_RESET_SUBTRACT,
                      "bad reset mode");
     }
-    HSES_REQUIRE(g->algo >= HSES_ALGO_AUTO && g->algo <= HSES_ALGO_TENSOR, "unknown algo");
+    HSES_REQUIRE(g->algo >= HSES_ALGO_AUTO && g->algo <= HSES_ALGO_PAIR, "unknown algo");
     return HSES_OK;
 }
 
@@ -269,8 +269,11 @@ size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     if (g == nullptr || g->t_steps < 1 || g->n_pop < 1 || g->bm < 1 || g->k < 1 || g->a < 1) return 0;
     // the tensor path always needs room for the split weights, the general path
     // only needs scratch when it perturbs
-    if (g->algo != HSES_ALGO_SIMT && tensor_path_supports(*g)) return tensor_path_workspace_bytes(*g);
-    if (g->algo == HSES_ALGO_TENSOR || !g->perturb) return 0;
+    if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_TENSOR) && tensor_path_supports(*g))
+        return tensor_path_workspace_bytes(*g);
+    if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_PAIR) && pair_path_supports(*g))
+        return pair_path_workspace_bytes(*g);
+    if (g->algo == HSES_ALGO_TENSOR || g->algo == HSES_ALGO_PAIR || !g->perturb) return 0;
     return simt_scratch(*g, nullptr).bytes;
 }
 
@@ -285,6 +288,13 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
     }
     if (g->algo == HSES_ALGO_TENSOR || (g->algo == HSES_ALGO_AUTO && tc_ok))
         return run_tensor_path(ctx, as_stream(stream), *g);
+    bool pair_ok = pair_path_supports(*g);
+    if (g->algo == HSES_ALGO_PAIR && !pair_ok) {
+        set_error("hses_perturbed_linear: the per-pair path does not cover this shape");
+        return HSES_ERR_UNSUPPORTED;
+    }
+    if (g->algo == HSES_ALGO_PAIR || (g->algo == HSES_ALGO_AUTO && pair_ok))
+        return run_pair_path(ctx, as_stream(stream), *g);
     return run_simt(ctx, as_stream(stream), *g);
 }
 

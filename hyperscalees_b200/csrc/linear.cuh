@@ -10,6 +10,12 @@ bool tensor_path_supports(const hses_linear_args& g);
 size_t tensor_path_workspace_bytes(const hses_linear_args& g);
 int run_tensor_path(hses_ctx* ctx, cudaStream_t stream, const hses_linear_args& g);
 
+// The path for few rows per antithetic pair and wide factors (linear_pair.cu): clean product
+// through the other paths, then one CTA per pair that streams the pair's factors once.
+bool pair_path_supports(const hses_linear_args& g);
+size_t pair_path_workspace_bytes(const hses_linear_args& g);
+int run_pair_path(hses_ctx* ctx, cudaStream_t stream, const hses_linear_args& g);
+
 // Checks args.cache against the call and returns the cached raw factors of the call's
 // first pair: A rows (pair, a, rank) and B rows (pair, k, rank).
 int resolve_factor_cache(const hses_linear_args& g, const float** A, const float** B);

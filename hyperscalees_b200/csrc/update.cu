@@ -10,11 +10,13 @@
 // scratch (A pre-multiplied by the pair weight), a split-K fp32 GEMM writes
 // per-split partial sums, and a final pass adds the partials in a fixed order
 // so that every rank ends up with bit-identical gradients.
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
 
 #include "common.cuh"
+#include "update_tc.cuh"
 
 namespace hses {
 
@@ -194,7 +196,12 @@ extern "C" {
 
 size_t hses_es_update_workspace_bytes(int32_t a, int32_t b, int32_t rank, int64_t n) {
     if (a < 1 || b < 1 || rank < 1 || n < 2) return 0;
-    return plan_update(a, b, rank, n).bytes;
+    size_t bytes = plan_update(a, b, rank, n).bytes;
+    if (update_tc_supports(a, b, rank)) {
+        size_t tc = plan_update_tc(a, b, rank, n, true).bytes;
+        if (tc > bytes) bytes = tc;
+    }
+    return bytes;
 }
 
 int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args) {
@@ -209,11 +216,24 @@ int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args*
     HSES_REQUIRE(u.noise_reuse >= 0, "noise_reuse must be >= 0");
     HSES_REQUIRE(u.fitness != nullptr && u.grad != nullptr, "NULL pointer");
     HSES_REQUIRE(u.mode == HSES_UPDATE_GRAD || u.mode == HSES_UPDATE_RAW_ACC, "unknown update mode");
+    cudaStream_t st = as_stream(stream);
+    const float base_sigma_tc = u.sigma / sqrtf((float)rank);
+    HSES_REQUIRE(u.algo == HSES_ALGO_AUTO || u.algo == HSES_ALGO_SIMT || u.algo == HSES_ALGO_TENSOR, "unknown algo");
+    const bool tc_ok = update_tc_supports(a, b, rank);
+    if (u.algo == HSES_ALGO_TENSOR && !tc_ok) {
+        set_error("hses_es_update_ex: the tensor-core contraction does not cover this shape");
+        return HSES_ERR_UNSUPPORTED;
+    }
+    if (tc_ok && u.algo != HSES_ALGO_SIMT) {
+        // wide factors on tile-aligned shapes: the contraction runs on the tensor cores
+        float nf = (float)u.n_total;
+        float sc = u.mode == HSES_UPDATE_GRAD ? -(base_sigma_tc * (1.0f / nf)) * sqrtf(nf) : base_sigma_tc;
+        return run_update_tc(ctx, st, u, sc);
+    }
     UpdatePlan p = plan_update(a, b, rank, u.n);
     HSES_REQUIRE(u.workspace != nullptr && u.workspace_bytes >= p.bytes,
                  "workspace too small; see hses_es_update_workspace_bytes");
     HSES_REQUIRE((a + UM - 1) / UM <= 65535, "a too large");
-    cudaStream_t st = as_stream(stream);
     float* wsA = reinterpret_cast<float*>(u.workspace);
     float* wsB = wsA + p.a_elems;
     float* partial = wsB + p.b_elems;

@@ -1,0 +1,411 @@
+// Tensor-core form of the fitness-weighted update
+//   sum_p (f_2p - f_2p+1) * A_p B_pᵀ          (simple_lora_update, eggroll.rs:353-373, pair-folded)
+// as one dense contraction (a, K)·(K, b) over K = pairs * rank — the 2-D GEMM form of
+// lora_einsum_raw (eggroll.rs:726-738) — for the wide-rank, large-population case in which it
+// dominates the step (a multiple of 128, rank a multiple of 64).
+//
+//   launch 1  pair_weight_range   largest |f_2p - f_2p+1| -> one power-of-two scale for all weights
+//   launch 2  factor_split        raw factors (factor cache, or scratch pair_factors just filled)
+//                                 -> weighted A and B times fixed powers of two, each as fp16 hi + lo
+//   launch 3  update_tc           one CTA per (128 x bn output tile, K split): TMA brings the
+//                                 [128 x 64] / [bn x 64] hi and lo tiles of one pair at a time into
+//                                 128B-swizzled shared memory (3-D tensor maps over (q, row, pair)),
+//                                 tcgen05.mma kind::f16 accumulates hi*hi + hi*lo + lo*hi in TMEM
+//                                 over the split's pairs, four warps drain TMEM into the split's
+//                                 partial sums
+//   launch 4  update_tc_reduce    adds the splits in a fixed order, undoes the scales
+// Three fp16 passes keep the products fp32-equivalent; normals from 24-bit uniforms are bounded
+// by 5.8, so fixed scales cannot overflow.  No multicast, no cluster launch, bounded waits.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "tc_common.cuh"
+#include "update_tc.cuh"
+
+namespace hses {
+
+namespace {
+
+using namespace tc;
+
+constexpr int UT_BM = 128;
+constexpr int UT_BK = 64;
+constexpr int UT_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kExpA = 12, kExpB = 11;  // A' = (w * 2^-e_w) * A * 2^12 <= 23.7e3, B' = B * 2^11 <= 11.9e3
+constexpr size_t kHalfChunkBytes = 384ull << 20;  // fp16 operand copies of one chunk of pairs
+
+// largest |f_even - f_odd| over the call's pairs -> exponent e with 2^e >= max (0 when all zero)
+__global__ void pair_weight_range_kernel(const float* __restrict__ fitness, int64_t pairs, int* __restrict__ e_out) {
+    __shared__ float red[32];
+    float m = 0.0f;
+    for (int64_t p = threadIdx.x; p < pairs; p += blockDim.x)
+        m = fmaxf(m, fabsf(__fsub_rn(fitness[2 * p], fitness[2 * p + 1])));
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+        int e = 0;
+        if (m > 0.0f && m < INFINITY) {
+            frexpf(m, &e);  // m = f * 2^e, f in [0.5, 1)
+            if (e > 100) e = 100;
+            if (e < -100) e = -100;
+        }
+        *e_out = e;
+    }
+}
+
+__device__ __forceinline__ void split_store(const float (&f)[4], __half* hi, __half* lo, size_t i4) {
+    uint32_t hb[4], lb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __half h = __float2half_rn(f[j]);
+        hb[j] = __half_as_ushort(h);
+        lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
+    }
+    reinterpret_cast<uint2*>(hi)[i4] = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+    reinterpret_cast<uint2*>(lo)[i4] = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+}
+
+// One thread per four consecutive factor values (rank is a multiple of four, so they belong to
+// one pair).  weights: fitness of the chunk's first member on; sign_factors as in update.cu.
+__global__ void factor_split_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t pairs, int a,
+                                    int b, int rank, const float* __restrict__ fitness,
+                                    const int* __restrict__ e_w, int sign_factors, __half* __restrict__ ahi,
+                                    __half* __restrict__ alo, __half* __restrict__ bhi, __half* __restrict__ blo) {
+    const size_t na4 = (size_t)pairs * a * rank / 4, nb4 = (size_t)pairs * b * rank / 4;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < na4) {
+        const int64_t p = (int64_t)(i / ((size_t)a * rank / 4));
+        float w = __fsub_rn(fitness[2 * p], fitness[2 * p + 1]);
+        float4 v = __ldg(reinterpret_cast<const float4*>(A) + i);
+        float f[4] = {v.x, v.y, v.z, v.w};
+        const float sc = ldexpf(1.0f, kExpA - *e_w);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (sign_factors) f[j] = f[j] > 0.0f ? 1.0f : f[j] < 0.0f ? -1.0f : 0.0f;
+            f[j] = __fmul_rn(__fmul_rn(f[j], w), sc);  // the scale is a power of two: exact
+        }
+        split_store(f, ahi, alo, i);
+    } else if (i < na4 + nb4) {
+        const size_t j4 = i - na4;
+        float4 v = __ldg(reinterpret_cast<const float4*>(B) + j4);
+        float f[4] = {v.x, v.y, v.z, v.w};
+        const float sc = ldexpf(1.0f, kExpB);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (sign_factors) f[j] = f[j] > 0.0f ? 1.0f : f[j] < 0.0f ? -1.0f : 0.0f;
+            f[j] = __fmul_rn(f[j], sc);
+        }
+        split_store(f, bhi, blo, j4);
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+struct UtArgs {
+    int a, b, rank, bn;
+    int n_tiles;        // output column tiles of bn
+    int64_t pairs;      // pairs of this chunk
+    int splits;
+    int accumulate;     // add to the partial sums of earlier chunks
+    int tmem_cols;      // power of two >= bn
+    int stages;
+    float* partial;     // [splits][a][b]
+    int* status;
+};
+
+__global__ void __launch_bounds__(UT_THREADS, 1)
+update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_constant__ CUtensorMap tm_alo,
+                 const __grid_constant__ CUtensorMap tm_bhi, const __grid_constant__ CUtensorMap tm_blo,
+                 const UtArgs g) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int a_bytes = UT_BM * UT_BK * 2, b_bytes = g.bn * UT_BK * 2;
+    const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
+    uint64_t* full = bars;          // [stages]
+    uint64_t* empty = bars + 4;     // [stages]
+    uint64_t* tfull = bars + 8;     // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
+    const int64_t p_lo = g.pairs * split / g.splits, p_hi = g.pairs * (split + 1) / g.splits;
+    const int kq = g.rank / UT_BK;                      // k-blocks per pair
+    const int64_t k_blocks = (p_hi - p_lo) * kq;
+
+    if (threadIdx.x == 0) {
+        abort_flag_s = 0;
+        for (int s = 0; s < g.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tfull, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(g.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            int64_t it = 0;
+            for (int64_t p = p_lo; p < p_hi && ok; ++p) {
+                for (int qb = 0; qb < kq; ++qb, ++it) {
+                    int s = (int)(it % g.stages);
+                    uint32_t ph = (uint32_t)(it / g.stages) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 11)) { ok = false; break; }
+                    uint8_t* st = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
+                    tma_load_3d(st, &tm_ahi, qb * UT_BK, mt * UT_BM, (int)p, &full[s]);
+                    tma_load_3d(st + a_bytes, &tm_alo, qb * UT_BK, mt * UT_BM, (int)p, &full[s]);
+                    tma_load_3d(st + 2 * a_bytes, &tm_bhi, qb * UT_BK, nt * g.bn, (int)p, &full[s]);
+                    tma_load_3d(st + 2 * a_bytes + b_bytes, &tm_blo, qb * UT_BK, nt * g.bn, (int)p, &full[s]);
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: give them a bounded moment
+                for (int s = 0; s < g.stages; ++s)
+                    for (uint32_t i = 0; i < 4096; ++i) {
+                        if (mbar_try(&full[s], 0) || mbar_try(&full[s], 1)) break;
+                        __nanosleep(256);
+                    }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(g.bn);
+            bool ok = true;
+            for (int64_t it = 0; it < k_blocks; ++it) {
+                int s = (int)(it % g.stages);
+                uint32_t ph = (uint32_t)(it / g.stages) & 1;
+                if (!mbar_wait(&full[s], ph, abort_flag, g.status, 12)) { ok = false; break; }
+                tc_fence_after();
+                uint8_t* st = smem + (size_t)s * stage_bytes;
+                uint64_t dah = make_smem_desc(st), dal = make_smem_desc(st + a_bytes);
+                uint64_t dbh = make_smem_desc(st + 2 * a_bytes), dbl = make_smem_desc(st + 2 * a_bytes + b_bytes);
+#pragma unroll
+                for (int ks = 0; ks < UT_BK / 16; ++ks) {
+                    uint64_t off = (uint64_t)(ks * 32 >> 4);  // 16 fp16 = 32 B along K
+                    umma_f16(tmem_base, dal + off, dbh + off, idesc, (it | ks) != 0);
+                    umma_f16(tmem_base, dah + off, dbl + off, idesc, 1);
+                    umma_f16(tmem_base, dah + off, dbh + off, idesc, 1);
+                }
+                umma_commit(&empty[s]);
+            }
+            if (ok && k_blocks > 0) umma_commit(tfull);
+        }
+    } else {
+        // epilogue: warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32); lane = output row
+        const int q4 = warp & 3;
+        const int m = mt * UT_BM + q4 * 32 + lane;
+        float* dst = g.partial + ((size_t)split * g.a + m) * g.b;
+        bool have = k_blocks > 0;
+        if (have) have = mbar_wait(tfull, 0, abort_flag, g.status, 13);
+        have = __all_sync(0xffffffffu, have);  // the TMEM loads below are warp-wide
+        tc_fence_after();
+        const int n0 = nt * g.bn;
+        for (int j0 = 0; j0 < g.bn; j0 += 8) {
+            uint32_t acc[8];
+            if (have) {
+                tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)j0, acc);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int n = n0 + j0 + j;
+                if (n < g.b && m < g.a) {
+                    float v = __uint_as_float(acc[j]);
+                    dst[n] = g.accumulate ? dst[n] + v : v;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols)
+                     : "memory");
+    }
+}
+
+// grad (+)= scale * 2^(e_w - kExpA - kExpB) * sum over splits, splits added in index order
+__global__ void update_tc_reduce_kernel(const float* __restrict__ partial, int splits, size_t len, float scale,
+                                        const int* __restrict__ e_w, int accumulate, float* __restrict__ grad) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= len) return;
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * len + i]);
+    s = __fmul_rn(ldexpf(s, *e_w - kExpA - kExpB), scale);
+    grad[i] = accumulate ? __fadd_rn(grad[i], s) : s;
+}
+
+// 3-D fp16 map over (q, row, pair): `rows` rows of `rank` values per pair; box (64, box_rows, 1)
+int make_map_3d(CUtensorMap* map, const __half* base, int rank, int rows, int64_t pairs, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return HSES_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {(cuuint64_t)rank, (cuuint64_t)rows, (cuuint64_t)pairs};
+    cuuint64_t strides[2] = {(cuuint64_t)rank * 2, (cuuint64_t)rank * 2 * (cuuint64_t)rows};
+    cuuint32_t box[3] = {(cuuint32_t)UT_BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string((int)r));
+        return HSES_ERR_CUDA;
+    }
+    return HSES_OK;
+}
+
+size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+bool update_tc_supports(int a, int b, int rank) {
+    // rows of A beyond a and rows of B beyond b are zero-filled by TMA, so only the rank is constrained
+    return a >= 1 && rank >= UT_BK && rank % UT_BK == 0 && b >= 1 && b <= (1 << 20) && a <= (1 << 20);
+}
+
+UpdateTcPlan plan_update_tc(int a, int b, int rank, int64_t n, bool need_raw) {
+    UpdateTcPlan p{};
+    p.pairs = n / 2;
+    int tiles_n = (b + 255) / 256;
+    p.bn = ((b + tiles_n - 1) / tiles_n + 15) / 16 * 16;
+    p.n_tiles = (b + p.bn - 1) / p.bn;
+    p.m_tiles = (a + UT_BM - 1) / UT_BM;
+    size_t per_pair_half = (size_t)(a + b) * rank * 2 * 2;  // hi + lo
+    int64_t fit = (int64_t)(kHalfChunkBytes / per_pair_half);
+    if (fit < 1) fit = 1;
+    p.chunk_pairs = p.pairs < fit ? p.pairs : fit;
+    int tiles = p.n_tiles * p.m_tiles;
+    // one CTA per SM fits (the operand stages take most of the shared memory): one full wave
+    int want = 148 / tiles;
+    if (want > 64) want = 64;
+    if (want > p.chunk_pairs) want = (int)p.chunk_pairs;
+    if (want < 1) want = 1;
+    p.splits = want;
+    p.half_a = up256((size_t)p.chunk_pairs * a * rank * 2);
+    p.half_b = up256((size_t)p.chunk_pairs * b * rank * 2);
+    p.partial_bytes = up256((size_t)p.splits * a * b * sizeof(float));
+    p.raw_bytes = need_raw ? up256((size_t)p.chunk_pairs * (a + b) * rank * sizeof(float)) : 0;
+    p.bytes = 256 + 2 * p.half_a + 2 * p.half_b + p.partial_bytes + p.raw_bytes;
+    return p;
+}
+
+int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, float scale) {
+    const int a = u.a, b = u.b, rank = u.rank;
+    UpdateTcPlan p = plan_update_tc(a, b, rank, u.n, u.cache == nullptr);
+    HSES_REQUIRE(u.workspace != nullptr && u.workspace_bytes >= p.bytes && ((uintptr_t)u.workspace & 255u) == 0,
+                 "workspace too small or not 256-byte aligned; see hses_es_update_workspace_bytes");
+    uint8_t* base = reinterpret_cast<uint8_t*>(u.workspace);
+    int* e_w = reinterpret_cast<int*>(base);
+    __half* ahi = reinterpret_cast<__half*>(base + 256);
+    __half* alo = reinterpret_cast<__half*>(base + 256 + p.half_a);
+    __half* bhi = reinterpret_cast<__half*>(base + 256 + 2 * p.half_a);
+    __half* blo = reinterpret_cast<__half*>(base + 256 + 2 * p.half_a + p.half_b);
+    float* partial = reinterpret_cast<float*>(base + 256 + 2 * p.half_a + 2 * p.half_b);
+    float* raw = reinterpret_cast<float*>(base + 256 + 2 * p.half_a + 2 * p.half_b + p.partial_bytes);
+    const int32_t te = true_epoch_of(u.epoch, u.noise_reuse);
+    const int32_t first_pair = u.first_thread / 2;
+
+    const float *cA = nullptr, *cB = nullptr;
+    if (u.cache) {
+        const hses_factor_cache& c = *u.cache;
+        HSES_REQUIRE(c.data != nullptr && c.key == u.key && c.true_epoch == te && c.rank == rank && c.a == a &&
+                         c.b == b,
+                     "factor cache was built for another parameter, epoch bucket or shape");
+        HSES_REQUIRE(first_pair >= c.first_pair && first_pair + p.pairs <= c.first_pair + c.n_pairs,
+                     "factor cache does not cover these members");
+        cA = c.data + (size_t)(first_pair - c.first_pair) * a * rank;
+        cB = c.data + (size_t)c.n_pairs * a * rank + (size_t)(first_pair - c.first_pair) * b * rank;
+    }
+    {
+        HSES_KERNEL(ctx, st, "pair_weight_range");
+        pair_weight_range_kernel<<<1, 1024, 0, st>>>(u.fitness, p.pairs, e_w);
+        HSES_LAUNCH_CHECK();
+    }
+    UtArgs g{};
+    g.a = a;
+    g.b = b;
+    g.rank = rank;
+    g.bn = p.bn;
+    g.n_tiles = p.n_tiles;
+    g.splits = p.splits;
+    g.tmem_cols = p.bn > 128 ? 256 : p.bn > 64 ? 128 : p.bn > 32 ? 64 : 32;
+    g.partial = partial;
+    g.status = ctx->t.status_word;
+    const int stage_bytes = 2 * UT_BM * UT_BK * 2 + 2 * p.bn * UT_BK * 2;
+    g.stages = (232448 - 2048) / stage_bytes;
+    if (g.stages > 4) g.stages = 4;
+    HSES_REQUIRE(g.stages >= 2, "update_tc: tile does not fit in shared memory");
+    const int smem_bytes = g.stages * stage_bytes + 1024;
+    HSES_CUDA(cudaFuncSetAttribute(update_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+
+    int chunk_idx = 0;
+    for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
+        const int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
+        const float *srcA, *srcB;
+        if (u.cache) {
+            srcA = cA + (size_t)done * a * rank;
+            srcB = cB + (size_t)done * b * rank;
+        } else {
+            float* ra = raw;
+            float* rb = raw + (size_t)cnt * a * rank;
+            int rc = launch_pair_factors(ctx, st, u.key, te, first_pair + (int32_t)done, cnt, rank, a, b, nullptr, ra,
+                                         rb);
+            if (rc != HSES_OK) return rc;
+            srcA = ra;
+            srcB = rb;
+        }
+        {
+            size_t n4 = (size_t)cnt * (a + b) * rank / 4;
+            HSES_KERNEL(ctx, st, "factor_split");
+            factor_split_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(srcA, srcB, cnt, a, b, rank,
+                                                                            u.fitness + 2 * done, e_w,
+                                                                            u.sign_factors, ahi, alo, bhi, blo);
+            HSES_LAUNCH_CHECK();
+        }
+        CUtensorMap tm_ahi, tm_alo, tm_bhi, tm_blo;
+        int rc = make_map_3d(&tm_ahi, ahi, rank, a, cnt, UT_BM);
+        if (rc == HSES_OK) rc = make_map_3d(&tm_alo, alo, rank, a, cnt, UT_BM);
+        if (rc == HSES_OK) rc = make_map_3d(&tm_bhi, bhi, rank, b, cnt, p.bn);
+        if (rc == HSES_OK) rc = make_map_3d(&tm_blo, blo, rank, b, cnt, p.bn);
+        if (rc != HSES_OK) return rc;
+        g.pairs = cnt;
+        g.accumulate = chunk_idx > 0;
+        dim3 grid((unsigned)(p.n_tiles * p.m_tiles), (unsigned)p.splits);
+        HSES_KERNEL(ctx, st, "update_tc");
+        update_tc_kernel<<<grid, UT_THREADS, smem_bytes, st>>>(tm_ahi, tm_alo, tm_bhi, tm_blo, g);
+        HSES_LAUNCH_CHECK();
+    }
+    size_t len = (size_t)a * b;
+    HSES_KERNEL(ctx, st, "update_reduce");
+    update_tc_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale, e_w,
+                                                                          u.mode == HSES_UPDATE_RAW_ACC, u.grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+}  // namespace hses

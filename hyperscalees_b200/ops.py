@@ -18,7 +18,7 @@ RESET_HARD, RESET_SUBTRACT = 0, 1
 REWARD_LOGLIK, REWARD_BINARY = 0, 1
 SGD, ADAM, ADAMW = 0, 1, 2
 LAYOUT_NAR, LAYOUT_NRA = 0, 1
-ALGO_AUTO, ALGO_SIMT, ALGO_TENSOR = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT, ALGO_TENSOR, ALGO_PAIR = 0, 1, 2, 3
 
 _U64 = (1 << 64) - 1
 
@@ -289,7 +289,7 @@ class FactorCache:
 def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int, sigma: float,
               fitness_: torch.Tensor, first_thread: int = 0, n_total: Optional[int] = None,
               out: Optional[torch.Tensor] = None, cache: Optional[FactorCache] = None,
-              mode: int = UPDATE_GRAD, sign_factors: bool = False) -> torch.Tensor:
+              mode: int = UPDATE_GRAD, sign_factors: bool = False, algo: int = ALGO_AUTO) -> torch.Tensor:
     """Fitness-weighted update of one LoRA-noised matrix.  mode UPDATE_RAW_ACC adds
     sum_i s_i A_i B_i^T (A_i scaled by sign*sigma/sqrt(rank)) to `out` instead."""
     _check(fitness_, "fitness", ndim=1)
@@ -312,6 +312,7 @@ def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int,
         u.cache = C.pointer(cache.desc)
     u.mode = mode
     u.sign_factors = int(sign_factors)
+    u.algo = algo
     _lib.check(L.hses_es_update_ex(ctx.handle, current_stream(), C.byref(u)))
     return out
 

@@ -47,7 +47,7 @@ enum hses_factor_layout {
     HSES_LAYOUT_NAR = 0, /* A (n,a,r), B (n,b,r): batched_lora_noise, eggroll.rs:116-130 */
     HSES_LAYOUT_NRA = 1  /* A (n,r,a), B (n,r,b): batched forward / einsum layout, snn.rs:472-476 */
 };
-enum hses_linear_algo { HSES_ALGO_AUTO = 0, HSES_ALGO_SIMT = 1, HSES_ALGO_TENSOR = 2 };
+enum hses_linear_algo { HSES_ALGO_AUTO = 0, HSES_ALGO_SIMT = 1, HSES_ALGO_TENSOR = 2, HSES_ALGO_PAIR = 3 };
 
 const char* hses_last_error(void);
 int hses_version(void);
@@ -266,6 +266,9 @@ typedef struct {
     int32_t mode;
     int32_t sign_factors; /* 1: AltEggRoll's update, every factor entry replaced by its sign
                              (hyperscalees-noiser/src/alteggroll.rs:65-90) */
+    int32_t algo;         /* hses_linear_algo: AUTO takes the tcgen05 contraction when rank is a
+                             multiple of 64, else the general fp32 kernel; SIMT / TENSOR force
+                             one of them */
 } hses_update_args;
 int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args);
 

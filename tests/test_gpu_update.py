@@ -85,3 +85,51 @@ def test_alteggroll_noiser_mirror(hs, oracle):
     A, B = oracle.lora_params(1.0, 7, 1, 0, 0, 2, 2, 0)
     want = -(0.5 * np.sign(A) @ np.sign(B).T) / 2 * np.sqrt(2.0)
     assert np.allclose(g.cpu().numpy(), want, rtol=1e-5)
+
+
+@pytest.mark.parametrize("a,b,rank,n,first", [
+    (128, 784, 64, 64, 0),      # config-3 first layer: 4 column tiles of 208 (the last one ragged)
+    (128, 128, 128, 40, 4),     # two k-blocks per pair
+    (256, 136, 64, 8, 0),       # two row tiles, fewer pairs than the split count would like
+    (128, 16, 64, 2, 0),        # a single pair, the narrowest tile
+    (10, 128, 64, 24, 0),       # readout layer: fewer rows than one tile
+    (130, 70, 64, 6, 2),        # ragged in both directions
+])
+def test_tensor_core_update_matches_oracle_and_general_kernel(hs, oracle, a, b, rank, n, first):
+    """The tcgen05 contraction of the update against the oracle and against the fp32 kernel."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(a + b + n)
+    f = (g.standard_normal(n) * 3).astype(np.float32)
+    kw = dict(first_thread=first)
+    got = ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), algo=ops.ALGO_TENSOR, **kw)
+    general = ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), algo=ops.ALGO_SIMT, **kw)
+    want = oracle.lora_grad(0.2, KEY, a, b, rank, f, [5] * n, list(range(first, first + n)), 2)
+    scale = np.abs(want).max()
+    assert np.abs(got.cpu().numpy() - want).max() <= 1e-3 * scale
+    assert (got - general).abs().max().item() <= 2e-5 * scale      # three fp16 passes are fp32-equivalent
+    cache = ops.FactorCache(KEY, 5, 2, rank, a, b, n // 2, first // 2)
+    assert torch.equal(ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), cache=cache, algo=ops.ALGO_TENSOR, **kw), got)
+    # deterministic, raw accumulation and the sign variant go through the same kernels
+    assert torch.equal(ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), algo=ops.ALGO_TENSOR, **kw), got)
+    acc = torch.ones(a, b, device="cuda")
+    ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), out=acc, mode=ops.UPDATE_RAW_ACC, algo=ops.ALGO_TENSOR, **kw)
+    ref = torch.ones(a, b, device="cuda")
+    ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), out=ref, mode=ops.UPDATE_RAW_ACC, algo=ops.ALGO_SIMT, **kw)
+    assert (acc - ref).abs().max().item() <= 2e-5 * (ref - 1).abs().max().item()
+    s_tc = ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), sign_factors=True, algo=ops.ALGO_TENSOR, **kw)
+    s_ref = ops.es_update(KEY, 5, 2, rank, a, b, 0.2, dev(f), sign_factors=True, algo=ops.ALGO_SIMT, **kw)
+    assert (s_tc - s_ref).abs().max().item() <= 2e-5 * s_ref.abs().max().item()
+
+
+def test_tensor_core_update_tiny_and_huge_weights(hs):
+    """The weight scale is a power of two found on the device: very small and very large raw
+    scores must neither underflow nor overflow the fp16 operands."""
+    from hyperscalees_b200 import ops
+    for mag in (1e-6, 1.0, 3e4):
+        f = torch.randn(32, device="cuda") * mag
+        tc = ops.es_update(KEY, 0, 0, 64, 128, 64, 0.1, f, algo=ops.ALGO_TENSOR)
+        ref = ops.es_update(KEY, 0, 0, 64, 128, 64, 0.1, f, algo=ops.ALGO_SIMT)
+        assert torch.isfinite(tc).all()
+        assert (tc - ref).abs().max().item() <= 2e-5 * ref.abs().max().item()
+    z = ops.es_update(KEY, 0, 0, 64, 128, 64, 0.1, torch.zeros(32, device="cuda"), algo=ops.ALGO_TENSOR)
+    assert torch.count_nonzero(z).item() == 0
