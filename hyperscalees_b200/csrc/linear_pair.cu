@@ -23,8 +23,7 @@ namespace hses {
 namespace {
 
 constexpr int PP_THREADS = 256;
-constexpr int PP_KC_MAX = 128;          // columns of x (= rows of B) per pass, at most
-constexpr int PP_CHUNK_FLOATS = 4096;   // 16 KB of B per pass: rows per pass = min(128, 4096 / rank)
+constexpr int PP_CHUNK_FLOATS = 6144;   // at most 24 KB of B per pass
 constexpr int PP_STAGES = 3;            // passes in flight: two are being copied while one is consumed
 constexpr int PP_A_SMEM_FLOATS = 16384; // A of a pair is prefetched into shared memory up to 64 KB
 constexpr size_t kPairScratchBytes = 256ull << 20;  // factor scratch per chunk when regenerating
@@ -37,7 +36,8 @@ struct PairArgs {
     int t_steps;
     int64_t n_pop;
     int bm, k, a, rank;
-    int kc;            // rows of B per pass
+    int kc;            // rows of B per pass, a multiple of 4 * kslices
+    int kslices;       // k-slices a pass is split into (threads per slice: (RMAX / 8) * (rank / 8))
     int a_in_smem;     // A of the pair is copied to shared memory while t is computed
     int32_t first_thread;
     int32_t pair0;     // absolute index of the pair handled by block 0
@@ -65,13 +65,14 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 
 // The pair's B and the matching columns of its x rows stream through a ring of PP_STAGES
-// shared-memory stages filled by bulk-async copies (B rows of a pass are contiguous: one copy;
-// x: one copy per row), so that two passes are in flight while one is consumed and no thread
-// ever waits for a global load it issued itself.  A of the pair is copied to shared memory in
-// the background when it fits.
+// shared-memory stages filled by the copy engine, two copies per pass: the B rows of a pass are
+// contiguous (one untiled bulk copy) and the pair's x rows are one box (columns, the pair's
+// rows of a step, steps) of a 3-D tensor map over x.  Two passes are in flight while one is
+// consumed and no thread ever waits for a global load it issued itself.  A of the pair is
+// copied to shared memory in the background when it fits.
 template <int RMAX>
-__global__ void __launch_bounds__(PP_THREADS)
-pair_lowrank_kernel(PairArgs g) {
+__global__ void __launch_bounds__(PP_THREADS, 2)
+pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) {
     extern __shared__ __align__(128) float smem[];
     __shared__ int64_t row_s[32];
     __shared__ int odd_s[32];                 // the row's member has an odd thread id: A is negated
@@ -84,9 +85,9 @@ pair_lowrank_kernel(PairArgs g) {
         if (g.dbg != nullptr && blockIdx.x == 0 && tid == 0) g.dbg[slot] = (unsigned long long)(clock64() - t_start);
     };
     const int rank = g.rank, k = g.k, a = g.a, kc = g.kc;
-    const int xp = kc + 8;  // rows 8 banks apart: the row groups of a warp read distinct banks
+    const int xp = kc;
     const int bbuf_floats = PP_STAGES * kc * rank;
-    const int red_floats = (PP_THREADS / ((RMAX / 8) * (rank / 8))) * RMAX * rank;
+    const int red_floats = g.kslices * RMAX * rank;
     float* xs = smem;                                   // [PP_STAGES][RMAX][xp]
     float* bbuf = smem + PP_STAGES * RMAX * xp;         // [PP_STAGES][kc][rank]; later the k-slice sums
     float* red = bbuf;                                  // [kslices][RMAX][rank]; slice 0 becomes t
@@ -104,7 +105,7 @@ pair_lowrank_kernel(PairArgs g) {
         row_s[tid] = ((int64_t)step * g.n_pop + m_lo) * g.bm + rr;
         odd_s[tid] = (int)((g.first_thread + m_lo + rr / g.bm) & 1);
     }
-    // rows this pair does not have, and the tail columns of a short last pass, read as zero
+    // rows this pair does not have read as zero (the copies never write them)
     for (int i = tid; i < PP_STAGES * RMAX * xp; i += PP_THREADS) xs[i] = 0.0f;
     const float* Bp = g.B + (size_t)blockIdx.x * k * rank;
     const float* Ap = g.A + (size_t)blockIdx.x * a * rank;
@@ -120,11 +121,10 @@ pair_lowrank_kernel(PairArgs g) {
         const int s = c % PP_STAGES;
         const int k0 = c * kc;
         const int kn = k - k0 < kc ? k - k0 : kc;  // multiple of 4
-        mbar_expect_tx(&bars[s], (uint32_t)(kn * rank * 4 + rows * kn * 4));
+        // the box is always counted in full: columns past k arrive as zeros
+        mbar_expect_tx(&bars[s], (uint32_t)(kn * rank * 4 + rows * kc * 4));
         bulk_load(bbuf + (size_t)s * kc * rank, Bp + (size_t)k0 * rank, (uint32_t)(kn * rank * 4), &bars[s]);
-        for (int r = 0; r < rows; ++r)
-            bulk_load(xs + ((size_t)s * RMAX + r) * xp, g.x + (size_t)row_s[r] * g.x_stride + k0, (uint32_t)(kn * 4),
-                      &bars[s]);
+        tma_load_3d(xs + (size_t)s * RMAX * xp, &tm_x, k0, (int)(m_lo * g.bm), 0, &bars[s]);
     };
     if (tid == 0) {
         fence_proxy_async();  // the zero fill above precedes the copy engine's writes
@@ -136,15 +136,18 @@ pair_lowrank_kernel(PairArgs g) {
     }
 
     tick(0);
-    // ---- t = x_rows * B.  A thread owns an 8 x 8 tile of t (rows rg, rg+RG, ... and eight
-    // consecutive q) for one k-slice, so that every 16-byte shared-memory load feeds 8..32
-    // multiply-adds; the k-slices are added through shared memory afterwards. ----
+    // ---- t = x_rows * B.  A thread owns an 8 x 8 tile of t for one k-slice: rows rg, rg+RG, ...
+    // and the columns 4qg..4qg+3 and rank/2+4qg..+3, so that every 16-byte shared-memory load
+    // feeds 8..32 multiply-adds.  The eight lanes that share a load phase have the same rows (x
+    // is broadcast) and neighbouring 16-byte pieces of B (no bank conflicts).  The k-slices are
+    // added through shared memory afterwards. ----
     constexpr int RG = RMAX / 8;
     const int qgroups = rank / 8;
     const int tpk = RG * qgroups;            // threads per k-slice
-    const int kslices = PP_THREADS / tpk;    // >= 1 (rank <= 2048 / RMAX)
+    const int kslices = g.kslices;
     const int tt = tid % tpk, ks = tid / tpk;
-    const int rg = tt % RG, qg = tt / RG;
+    const int qg = tt % qgroups, rg = tt / qgroups;
+    const int q_lo = 4 * qg, q_hi = rank / 2 + 4 * qg;
     const bool active = ks < kslices;
     float acc[8][8];
 #pragma unroll
@@ -162,7 +165,7 @@ pair_lowrank_kernel(PairArgs g) {
         }
         if (ok) ok = mbar_wait(&bars[s], (uint32_t)(c / PP_STAGES) & 1, abort_flag, g.status, 20);
         if (active && ok) {
-            const float* bc = bbuf + (size_t)s * kc * rank + qg * 8;
+            const float* bc = bbuf + (size_t)s * kc * rank;
             const float* xc = xs + ((size_t)s * RMAX + rg) * xp;
             for (int kk = ks * 4; kk < kn; kk += 4 * kslices) {
                 float4 xv[8];
@@ -170,8 +173,8 @@ pair_lowrank_kernel(PairArgs g) {
                 for (int j = 0; j < 8; ++j) xv[j] = *reinterpret_cast<const float4*>(xc + (size_t)j * RG * xp + kk);
 #pragma unroll
                 for (int kq = 0; kq < 4; ++kq) {
-                    const float4 bl = *reinterpret_cast<const float4*>(bc + (size_t)(kk + kq) * rank);
-                    const float4 bh = *reinterpret_cast<const float4*>(bc + (size_t)(kk + kq) * rank + 4);
+                    const float4 bl = *reinterpret_cast<const float4*>(bc + (size_t)(kk + kq) * rank + q_lo);
+                    const float4 bh = *reinterpret_cast<const float4*>(bc + (size_t)(kk + kq) * rank + q_hi);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const float xval = kq == 0 ? xv[j].x : kq == 1 ? xv[j].y : kq == 2 ? xv[j].z : xv[j].w;
@@ -194,9 +197,9 @@ pair_lowrank_kernel(PairArgs g) {
     if (active) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            float* dst = red + ((size_t)ks * RMAX + rg + j * RG) * rank + qg * 8;
-            *reinterpret_cast<float4*>(dst) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+            float* dst = red + ((size_t)ks * RMAX + rg + j * RG) * rank;
+            *reinterpret_cast<float4*>(dst + q_lo) = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+            *reinterpret_cast<float4*>(dst + q_hi) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
         }
     }
     __syncthreads();
@@ -221,26 +224,37 @@ pair_lowrank_kernel(PairArgs g) {
     const float* ts = red;
     tick(2);
 
-    // ---- u = t * (s*A)ᵀ and the final transform of the rows.  A thread owns 8 rows x 4
-    // consecutive output columns: each 16-byte piece of t feeds 16 multiply-adds. ----
+    // ---- u = t * (s*A)ᵀ and the final transform of the rows.  A thread owns 4 rows x NC
+    // consecutive output columns; the clean product of its outputs is fetched first so that its
+    // latency hides behind the multiply-adds. ----
+    constexpr int NC = 2;
+    constexpr int RG4 = RMAX / 4;  // row groups of this phase: rows prg, prg + RG4, ...
     const float gain = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
     const int nq4 = rank / 4;
-    const int ngroups = (a + 3) / 4;
-    for (int item = tid; item < ngroups * RG; item += PP_THREADS) {
-        const int ng = item / RG, prg = item - ng * RG;
-        const int n0 = ng * 4;
-        float u[8][4];
+    const int ngroups = (a + NC - 1) / NC;
+    for (int item = tid; item < ngroups * RG4; item += PP_THREADS) {
+        const int ng = item / RG4, prg = item - ng * RG4;
+        const int n0 = ng * NC;
+        float u[4][NC], base[4][NC];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) u[j][0] = u[j][1] = u[j][2] = u[j][3] = 0.0f;
+        for (int j = 0; j < 4; ++j) {
+            const int r = prg + j * RG4;
+            const float* orow = g.out + (size_t)row_s[r < rows ? r : 0] * g.out_stride;
+#pragma unroll
+            for (int c4 = 0; c4 < NC; ++c4) {
+                u[j][c4] = 0.0f;
+                base[j][c4] = (r < rows && n0 + c4 < a) ? orow[n0 + c4] : 0.0f;
+            }
+        }
         const float* abase = (g.a_in_smem ? as : Ap);
-        // neighbouring column groups start at neighbouring 16-byte pieces: in shared memory
-        // the rows of A are rank floats apart, and without the rotation all lanes would hit
-        // the same banks
-        int q4 = ng % nq4;
+        // neighbouring threads start at neighbouring 16-byte pieces of their rows: the rows of A
+        // and of t are rank floats apart in shared memory, and without the rotation the lanes of
+        // a load phase would all hit the same banks
+        int q4 = item % nq4;
         for (int i = 0; i < nq4; ++i) {
-            float4 av[4];
+            float4 av[NC];
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c4 = 0; c4 < NC; ++c4) {
                 const int n = n0 + c4 < a ? n0 + c4 : a - 1;   // a ragged last group repeats the last column
                 const float4* an = reinterpret_cast<const float4*>(abase + (size_t)n * rank) + q4;
                 float4 v = g.a_in_smem ? *an : __ldg(an);
@@ -248,10 +262,10 @@ pair_lowrank_kernel(PairArgs g) {
                                      __fmul_rn(v.z, g.base_sigma), __fmul_rn(v.w, g.base_sigma));
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 tv = *reinterpret_cast<const float4*>(ts + (size_t)(prg + j * RG) * rank + q4 * 4);
+            for (int j = 0; j < 4; ++j) {
+                const float4 tv = *reinterpret_cast<const float4*>(ts + (size_t)(prg + j * RG4) * rank + q4 * 4);
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
+                for (int c4 = 0; c4 < NC; ++c4) {
                     u[j][c4] = fmaf(tv.x, av[c4].x, u[j][c4]);
                     u[j][c4] = fmaf(tv.y, av[c4].y, u[j][c4]);
                     u[j][c4] = fmaf(tv.z, av[c4].z, u[j][c4]);
@@ -262,18 +276,18 @@ pair_lowrank_kernel(PairArgs g) {
         }
         tick(3);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int r = prg + j * RG;
+        for (int j = 0; j < 4; ++j) {
+            const int r = prg + j * RG4;
             if (r < rows) {
                 const int64_t R = row_s[r];
                 const bool odd = odd_s[r] != 0;
                 float* orow = g.out + (size_t)R * g.out_stride;
                 float* prow = g.pot ? g.pot + (size_t)R * g.out_stride : nullptr;
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
+                for (int c4 = 0; c4 < NC; ++c4) {
                     const int n = n0 + c4;
                     if (n < a) {
-                        float y = __fadd_rn(orow[n], odd ? -u[j][c4] : u[j][c4]);
+                        float y = __fadd_rn(base[j][c4], odd ? -u[j][c4] : u[j][c4]);
                         if (g.lif) {
                             float cpot = __fmul_rn(y, g.leak);
                             if (prow) prow[n] = cpot;
@@ -289,10 +303,20 @@ pair_lowrank_kernel(PairArgs g) {
     tick(4);
 }
 
-int kc_of(int rank) {
-    int kc = PP_CHUNK_FLOATS / rank;
-    if (kc > PP_KC_MAX) kc = PP_KC_MAX;
-    return kc / 4 * 4;
+// k-slices of a pass: as many as the block has threads for, at most 64 (a pass is at most 256
+// columns, the limit of a TMA box)
+int kslices_of(int rmax, int rank) {
+    int ks = PP_THREADS / ((rmax / 8) * (rank / 8));
+    return ks > 64 ? 64 : ks;
+}
+// rows of B per pass: a multiple of 4 * kslices (every slice does the same number of steps),
+// as many as fit the per-pass budget, at least one step per slice
+int kc_of(int rmax, int rank) {
+    int unit = 4 * kslices_of(rmax, rank);
+    int m = PP_CHUNK_FLOATS / (rank * unit);
+    if (m < 1) m = 1;
+    if (m * unit > 256) m = 256 / unit;
+    return m * unit;
 }
 
 bool a_fits(const hses_linear_args& g) { return (size_t)g.a * g.rank <= (size_t)PP_A_SMEM_FLOATS; }
@@ -303,9 +327,9 @@ int rmax_of(const hses_linear_args& g) {
 }
 
 size_t pair_smem_bytes(int rmax, const hses_linear_args& g) {
-    int kc = kc_of(g.rank), kslices = PP_THREADS / ((rmax / 8) * (g.rank / 8));
+    int kc = kc_of(rmax, g.rank), kslices = kslices_of(rmax, g.rank);
     size_t bbuf = (size_t)PP_STAGES * kc * g.rank, red = (size_t)kslices * rmax * g.rank;
-    size_t fl = (size_t)PP_STAGES * rmax * (kc + 8) + (bbuf > red ? bbuf : red) +
+    size_t fl = (size_t)PP_STAGES * rmax * kc + (bbuf > red ? bbuf : red) +
                 (a_fits(g) ? (size_t)g.a * g.rank : 0);
     return fl * sizeof(float);
 }
@@ -386,7 +410,29 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     pa.out_scale_ptr = g.out_scale_ptr;
     const int rmax = rmax_of(g);
     const size_t smem = pair_smem_bytes(rmax, g);
-    pa.kc = kc_of(g.rank);
+    // x as (column, row within a step, step); a box holds the rows of one pair for one pass
+    CUtensorMap tm_x;
+    {
+        EncodeTiledFn fn = encode_fn();
+        if (!fn) {
+            set_error("cuTensorMapEncodeTiled is not available from the driver");
+            return HSES_ERR_CUDA;
+        }
+        const uint64_t rows_per_step = (uint64_t)g.n_pop * g.bm;
+        cuuint64_t dims[3] = {(cuuint64_t)g.k, (cuuint64_t)rows_per_step, (cuuint64_t)g.t_steps};
+        cuuint64_t strides[2] = {(cuuint64_t)g.x_row_stride * 4, (cuuint64_t)g.x_row_stride * 4 * rows_per_step};
+        cuuint32_t box[3] = {(cuuint32_t)kc_of(rmax, g.rank), (cuuint32_t)(2 * g.bm), (cuuint32_t)g.t_steps};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = fn(&tm_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(g.x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_error("cuTensorMapEncodeTiled (x rows of a pair) failed with code " + std::to_string((int)r));
+            return HSES_ERR_CUDA;
+        }
+    }
+    pa.kc = kc_of(rmax, g.rank);
+    pa.kslices = kslices_of(rmax, g.rank);
     pa.a_in_smem = a_fits(g) ? 1 : 0;
     pa.status = ctx->t.status_word;
     pa.dbg = nullptr;
@@ -400,15 +446,15 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         switch (rmax) {
             case 8:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<8><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(pa);
+                pair_lowrank_kernel<8><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
                 break;
             case 16:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<16><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(pa);
+                pair_lowrank_kernel<16><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
                 break;
             default:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<32><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(pa);
+                pair_lowrank_kernel<32><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
                 break;
         }
         HSES_LAUNCH_CHECK();

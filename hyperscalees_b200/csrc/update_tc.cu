@@ -101,13 +101,6 @@ __global__ void factor_split_kernel(const float* __restrict__ A, const float* __
     }
 }
 
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-
 struct UtArgs {
     int a, b, rank, bn;
     int n_tiles;        // output column tiles of bn
