@@ -311,14 +311,100 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         dist.destroy_process_group()
 
 
+def run_population_step(args, rank: int, local_rank: int, world: int):
+    """Secondary workload: one full ES step of the spiking MLP 784-128-128-128-10 (encode ->
+    perturbed forward over T = 8 steps -> fitness -> all-gather -> z-score -> update -> AdamW),
+    strong scaling: the population of --n-pop members is sharded over the ranks, the update is
+    replicated.  Reports member-evaluations/s = n_pop * bm * T per second."""
+    import torch
+    import torch.distributed as dist
+    from hyperscalees_b200 import core, models, noiser, parallel
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = core.get_context(local_rank)
+    dims, T, bm, n_total, r = [784, 128, 128, 128, 10], 8, args.bm, args.n_pop, args.rank
+    lo, hi = parallel.shard_range(n_total, rank, world)
+    n_local = hi - lo
+    g = np.random.Generator(np.random.PCG64(0))
+    img = g.random((n_total * bm, 784), dtype=np.float32)
+    img[g.random((n_total * bm, 784)) < 0.8] = 0.0          # MNIST-like sparsity, seed 0
+    labels = g.integers(0, 10, n_total * bm).astype(np.int32)
+    di = torch.as_tensor(img[lo * bm:hi * bm], device=dev)
+    dl = torch.as_tensor(labels[lo * bm:hi * bm], device=dev)
+    keys = models.default_base_keys(len(dims))
+    net = models.SnnMlp(dims, tau_m=20.0, v_th=0.3, seed=0, device=dev)
+    frozen, nz = noiser.init_noiser(net.params(), 0.02, 0.01, 0, False, 0, r, noiser.Solver.adamw(0.01))
+    step_obj = models.PopulationStep(net, frozen, nz, keys, T, n_local, bm, first_thread=lo,
+                                     cache=args.cache, n_total=n_total)
+
+    def step():
+        raw = step_obj.eval(di, dl, [1, 2, 3, 4 + rank])
+        full = parallel.allgather_fitness(raw, n_total) if world > 1 else raw
+        step_obj.update(full)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ctx.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    barrier()
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    clocks = sampler.stop() if sampler else None
+    if rank == 0:
+        ms_total = float(ms.item())
+        evals = n_total * bm * T
+        tot = sum(v[1] for v in prof.values())
+        line = {"metric": METRIC, "value": evals * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic",
+                "config": {"workload": f"population step: SNN MLP 784-128-128-128-10, n_pop {n_total}, bm {bm}, T 8, "
+                                       f"rank {r}, sigma 0.02, AdamW; factor cache {args.cache}",
+                           "n_pop": n_total, "bm": bm, "t_steps": T, "rank": r, "cache": args.cache,
+                           "parallelism": f"population sharded over {world} GPU(s), fitness all-gather, replicated update"},
+                "kernel_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+                "kernel_time_share": {k: round(v[1] / tot, 4) for k, v in prof.items()},
+                "gpu_launches": int(sum(v[0] for v in prof.values())), "clocks": clocks,
+                "device_status": ctx.device_status()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step"],
+                    help="microbench: the perturbed-linear layer the metric is quoted on (default); "
+                         "population_step: a full ES step of the spiking MLP (secondary figure)")
+    ap.add_argument("--bm", type=int, default=1, help="population_step: samples per member")
+    ap.add_argument("--rank", type=int, default=64, help="population_step: rank of the factors")
+    ap.add_argument("--cache", default="off", choices=["off", "auto"],
+                    help="population_step: keep the factors of an epoch bucket on the device")
     ap.add_argument("--n-pop", type=int, default=8192,
-                    help="members per GPU; smaller values give the reduced case used for ncu captures")
+                    help="microbench: members per GPU (smaller values give the reduced case used for ncu "
+                         "captures); population_step: members of the whole population")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()
@@ -328,6 +414,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload == "population_step":
+        run_population_step(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 

@@ -136,7 +136,7 @@ class PopulationStep:
 
     def __init__(self, net: SnnMlp, frozen: FrozenNoiserParams, noiser: NoiserParams,
                  base_keys: Sequence[int], T: int, n_pop: int, bm: int, first_thread: int = 0,
-                 reward: int = ops.REWARD_LOGLIK):
+                 reward: int = ops.REWARD_LOGLIK, cache: str = "off", n_total: Optional[int] = None):
         import ctypes as C
         from . import _lib
         from .core import get_context
@@ -153,6 +153,12 @@ class PopulationStep:
             self.moments = ([torch.zeros_like(p) for p in self.params], [torch.zeros_like(p) for p in self.params])
         self._ws = None
         self.caches = None
+        # "auto": generate every layer's factors once per epoch bucket (at the first eval of the
+        # bucket) and let the forward pass and the update read them; with noise_reuse == 0 the
+        # bucket never changes, so the generation cost is paid once per run
+        if cache not in ("off", "auto"):
+            raise ValueError("cache must be 'off' or 'auto'")
+        self.cache_policy, self.n_total, self._cache_bucket = cache, n_total, None
 
     def build_caches(self, epoch: int = 0, n_total: Optional[int] = None) -> int:
         """Generates the factors of every layer once and keeps them on the device
@@ -202,6 +208,13 @@ class PopulationStep:
              want_logits: bool = False, perturb: bool = True):
         """images (n_pop*bm, in) probabilities, labels int32 -> raw fitness (n_pop,)."""
         C = self.C
+        if self.cache_policy == "auto" and perturb:
+            nr = self.frozen.noise_reuse
+            bucket = 0 if nr == 0 else epoch // nr
+            if bucket != self._cache_bucket:
+                self.caches = None   # release the old bucket before allocating the new one
+                self.build_caches(epoch, self.n_total)
+                self._cache_bucket = bucket
         m, p = self._model(), self._args(epoch, perturb)
         need = int(self.L.hses_population_eval_workspace_bytes(C.byref(m), C.byref(p)))
         ws = self._scratch(need)

@@ -121,3 +121,26 @@ def test_population_step_with_caches_is_bit_equal():
     assert torch.equal(results[0][0], results[1][0])
     for p0, p1 in zip(results[0][1], results[1][1]):
         assert torch.equal(p0, p1)
+
+
+def test_population_step_auto_cache_follows_the_epoch_bucket():
+    """cache='auto' rebuilds the factor caches exactly when the epoch bucket changes and gives
+    the bits of the regenerating step in every epoch."""
+    from hyperscalees_b200 import models, noiser
+    dims, n_pop, bm, T, rank = [784, 128, 10], 16, 2, 4, 8
+    rng = np.random.default_rng(6)
+    img = torch.from_numpy(rng.random((n_pop * bm, 784), dtype=np.float32)).cuda()
+    labels = torch.from_numpy(rng.integers(0, 10, n_pop * bm, dtype=np.int32)).cuda()
+    keys = models.default_base_keys(len(dims))
+    net = models.SnnMlp(dims, tau_m=1.0, v_th=0.3, seed=4)
+    frozen, nz = noiser.init_noiser(net.params(), 0.2, 0.01, 0, False, 2, rank, noiser.Solver.sgd(0.01))
+    plain = models.PopulationStep(net, frozen, nz, keys, T, n_pop, bm)
+    auto = models.PopulationStep(net, frozen, nz, keys, T, n_pop, bm, cache="auto", n_total=n_pop)
+    seen = []
+    for epoch in range(4):                       # noise_reuse = 2: buckets 0, 0, 1, 1
+        want = plain.eval(img, labels, [1, 2, 3, 4], epoch=epoch)
+        got = auto.eval(img, labels, [1, 2, 3, 4], epoch=epoch)
+        assert torch.equal(want, got)
+        seen.append(auto.caches[0].data.data_ptr() if auto.caches else None)
+        assert auto.caches[0].desc.true_epoch == epoch // 2
+    assert seen[0] == seen[1] and seen[2] == seen[3]   # not rebuilt inside a bucket
