@@ -581,15 +581,22 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     const float4* cb4 = cache_b ? reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK) : nullptr;
     for (int k0 = 0; k0 < k; k0 += LT_KB) {
         const int kn = k - k0 < LT_KB ? k - k0 : LT_KB;  // multiple of 4
+        // Row k of the block is stored at row perm(k): inside every group of KSTEP rows the rows
+        // with the same k mod 4 are made neighbours, so that the lanes of a warp — which own four
+        // consecutive k each — read one contiguous 512-byte stretch per load (no bank conflicts).
         if (cb4) {
-            for (int i = tid; i < kn * RANK_G; i += LT_THREADS)
-                reinterpret_cast<float4*>(bs)[i] = __ldg(cb4 + (size_t)k0 * RANK_G + i);
+            for (int i = tid; i < kn * RANK_G; i += LT_THREADS) {
+                const int kr = i / RANK_G, c = i - kr * RANK_G;
+                const int pr = (kr / KSTEP) * KSTEP + (kr & 3) * KQ + ((kr % KSTEP) >> 2);
+                reinterpret_cast<float4*>(bs)[pr * RANK_G + c] = __ldg(cb4 + (size_t)k0 * RANK_G + i);
+            }
         } else if (tid < kn) {
+            const int pr = (tid / KSTEP) * KSTEP + (tid & 3) * KQ + ((tid % KSTEP) >> 2);
 #pragma unroll 1
             for (int q = 0; q < RANK; q += 4) {
                 float z[4];
                 next_normals4(sb, cal, z);
-                *reinterpret_cast<float4*>(bs + tid * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
+                *reinterpret_cast<float4*>(bs + pr * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
             }
             sb = jump_apply(hop_s, sb);
         }
@@ -597,11 +604,12 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         if (active) {
             const int kend = min(kpart * part_len + part_len, kn);
             for (int kk = kpart * part_len + 4 * kq; kk < kend; kk += KSTEP) {
-                const float* bq = bs + kk * RANK + qg * 4;
+                // rows kk..kk+3 live at perm(kk) + {0, KQ, 2KQ, 3KQ}
+                const float* bq = bs + ((kk / KSTEP) * KSTEP + ((kk % KSTEP) >> 2)) * RANK + qg * 4;
                 float4 b0 = *reinterpret_cast<const float4*>(bq);
-                float4 b1 = *reinterpret_cast<const float4*>(bq + RANK);
-                float4 b2 = *reinterpret_cast<const float4*>(bq + 2 * RANK);
-                float4 b3 = *reinterpret_cast<const float4*>(bq + 3 * RANK);
+                float4 b1 = *reinterpret_cast<const float4*>(bq + KQ * RANK);
+                float4 b2 = *reinterpret_cast<const float4*>(bq + 2 * KQ * RANK);
+                float4 b3 = *reinterpret_cast<const float4*>(bq + 3 * KQ * RANK);
 #pragma unroll
                 for (int r = 0; r < 8; ++r) {
                     float4 xv = __ldg(reinterpret_cast<const float4*>(xrow[r] + k0 + kk));
