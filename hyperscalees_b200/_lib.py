@@ -27,6 +27,7 @@ EXPORTS = [
     "hses_population_eval_workspace_bytes", "hses_population_eval", "hses_population_update_workspace_bytes",
     "hses_population_update", "hses_wkv7", "hses_spiking_attention",
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
+    "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
 ]
 
 
@@ -147,6 +148,11 @@ def load():
     L.hses_population_update.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64,
                                          C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                          vp, sz]
+    L.hses_population_grads_elems.restype = sz
+    L.hses_population_grads_elems.argtypes = [pm]
+    L.hses_population_grads.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64, i32, i64, vp, vp, sz]
+    L.hses_population_apply.argtypes = [vp, vp, pm, C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp),
+                                        C.POINTER(vp), vp]
     L.hses_wkv7.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp]
     L.hses_spiking_attention.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, f32, f32, f32, f32, i32,
                                          vp, vp]

@@ -272,4 +272,91 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
     return HSES_OK;
 }
 
+size_t hses_population_grads_elems(const hses_snn_model* m) {
+    if (m == nullptr || m->n_layers < 1 || m->dims == nullptr) return 0;
+    size_t n = 1;  // out_gain
+    for (int l = 0; l < m->n_layers; ++l) n += (size_t)m->dims[l + 1] * m->dims[l];
+    return n;
+}
+
+int hses_population_grads(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, float sigma, int32_t rank,
+                          int32_t epoch, int32_t noise_reuse, int32_t group_size, int32_t freeze_nonlora,
+                          uint64_t gain_key, const float* raw_fitness, int64_t n_total, int32_t first_thread,
+                          int64_t n_local, float* grads, void* workspace, size_t workspace_bytes) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(m != nullptr && m->n_layers >= 1 && m->dims != nullptr && m->keys != nullptr, "bad model");
+    HSES_REQUIRE(raw_fitness != nullptr && grads != nullptr, "NULL pointer");
+    HSES_REQUIRE(n_total >= 2 && n_total % 2 == 0, "the population must consist of whole antithetic pairs");
+    HSES_REQUIRE(first_thread >= 0 && first_thread % 2 == 0 && n_local >= 2 && n_local % 2 == 0 &&
+                     (int64_t)first_thread + n_local <= n_total,
+                 "the shard must consist of whole antithetic pairs inside the population");
+    size_t need = hses_population_update_workspace_bytes(m, rank, n_total);
+    HSES_REQUIRE(workspace != nullptr && workspace_bytes >= need && ((uintptr_t)workspace & 255u) == 0,
+                 "workspace too small or not 256-byte aligned; see hses_population_update_workspace_bytes");
+    size_t grad_elems = 0;
+    for (int l = 0; l < m->n_layers; ++l) grad_elems = std::max(grad_elems, (size_t)m->dims[l + 1] * m->dims[l]);
+    float* fit = reinterpret_cast<float*>(workspace);
+    void* upd_ws = fit + up64((size_t)n_total) + up64(grad_elems);
+    size_t upd_bytes = workspace_bytes - (up64((size_t)n_total) + up64(grad_elems)) * sizeof(float);
+    int rc = hses_convert_fitnesses(ctx, stream, raw_fitness, n_total, group_size, fit, nullptr);
+    if (rc != HSES_OK) return rc;
+    float* g = grads;
+    for (int l = 0; l < m->n_layers; ++l) {
+        int a = m->dims[l + 1], b = m->dims[l];
+        hses_update_args u{};
+        u.key = m->keys[l];
+        u.epoch = epoch;
+        u.noise_reuse = noise_reuse;
+        u.first_thread = first_thread;
+        u.n = n_local;
+        u.n_total = n_total;
+        u.rank = rank;
+        u.a = a;
+        u.b = b;
+        u.sigma = sigma;
+        u.fitness = fit + first_thread;
+        u.grad = g;
+        u.workspace = upd_ws;
+        u.workspace_bytes = upd_bytes;
+        u.mode = HSES_UPDATE_GRAD;
+        const hses_factor_cache* c = m->caches ? m->caches[l] : nullptr;
+        if (c && c->first_pair <= first_thread / 2 &&
+            (int64_t)c->first_pair + c->n_pairs >= (int64_t)first_thread / 2 + n_local / 2)
+            u.cache = c;
+        rc = hses_es_update_ex(ctx, stream, &u);
+        if (rc != HSES_OK) return rc;
+        g += (size_t)a * b;
+    }
+    // out_gain: PARAM-class leaf of shape (1,1), dense noise (eggroll.rs:331-350); frozen -> zero gradient
+    if (freeze_nonlora) {
+        HSES_CUDA(cudaMemsetAsync(g, 0, sizeof(float), as_stream(stream)));
+    } else {
+        rc = hses_es_update_dense(ctx, stream, gain_key, epoch, noise_reuse, first_thread, n_local, n_total, 1, sigma,
+                                  fit + first_thread, g);
+        if (rc != HSES_OK) return rc;
+    }
+    return HSES_OK;
+}
+
+int hses_population_apply(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_solver* solver,
+                          int32_t step, float* const* params, float* const* m_bufs, float* const* v_bufs,
+                          const float* grads) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(m != nullptr && m->n_layers >= 1 && m->dims != nullptr, "bad model");
+    HSES_REQUIRE(solver != nullptr && params != nullptr && grads != nullptr, "NULL pointer");
+    const bool moments = solver->kind != HSES_SGD;
+    HSES_REQUIRE(!moments || (m_bufs != nullptr && v_bufs != nullptr), "Adam needs moment buffers");
+    const float* g = grads;
+    for (int l = 0; l <= m->n_layers; ++l) {
+        int64_t len = l < m->n_layers ? (int64_t)m->dims[l + 1] * m->dims[l] : 1;
+        if (params[l] != nullptr) {
+            int rc = hses_solver_step(ctx, stream, solver, step, 1.0f, params[l], g, moments ? m_bufs[l] : nullptr,
+                                      moments ? v_bufs[l] : nullptr, len);
+            if (rc != HSES_OK) return rc;
+        }
+        g += len;
+    }
+    return HSES_OK;
+}
+
 }  // extern "C"

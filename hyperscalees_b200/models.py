@@ -229,6 +229,48 @@ class PopulationStep:
             logits.data_ptr() if want_logits else None, ws.data_ptr(), need))
         return (raw, logits) if want_logits else raw
 
+    def update_sharded(self, raw_fitness: torch.Tensor, epoch: int = 0, gain_key: Optional[int] = None,
+                       group=None, reduce_fn=None) -> None:
+        """Like update(), but this rank only contracts the factors of ITS members (first_thread ..
+        first_thread + n_pop - 1); the partial gradients of all parameters are summed with one
+        all-reduce (when torch.distributed is initialised) and every rank applies the same solver
+        step, so parameters stay identical on all ranks.  reduce_fn(grads), when given, replaces
+        the all-reduce (it must leave the sum over all shards in `grads`)."""
+        import torch.distributed as dist
+        C = self.C
+        m = self._model()
+        n_total = raw_fitness.numel()
+        need = int(self.L.hses_population_update_workspace_bytes(C.byref(m), self.frozen.rank, n_total))
+        ws = self._scratch(need)
+        elems = int(self.L.hses_population_grads_elems(C.byref(m)))
+        if getattr(self, "_grads", None) is None or self._grads.numel() != elems:
+            self._grads = torch.empty(elems, dtype=torch.float32, device=self.net.device)
+        gk = self.keys[len(self.net.weights)] if gain_key is None else gain_key
+        from .core import current_stream
+        self._lib.check(self.L.hses_population_grads(
+            self.ctx.handle, current_stream(), C.byref(m), self.noiser.sigma, self.frozen.rank, epoch,
+            self.frozen.noise_reuse, self.frozen.group_size, int(self.frozen.freeze_nonlora),
+            C.c_uint64(gk & ((1 << 64) - 1)), raw_fitness.data_ptr(), n_total, self.first_thread, self.n_pop,
+            self._grads.data_ptr(), ws.data_ptr(), need))
+        if reduce_fn is not None:
+            reduce_fn(self._grads)
+        elif dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self._grads, op=dist.ReduceOp.SUM, group=group)
+        sv = self.frozen.solver
+        kind = {"sgd": ops.SGD, "adam": ops.ADAM, "adamw": ops.ADAMW}[sv.kind]
+        desc = self._lib.SolverDesc(kind, sv.lr, sv.beta1, sv.beta2, sv.eps, sv.weight_decay if kind == ops.ADAMW else 0.0)
+        if kind != ops.SGD:
+            self.noiser.opt_state.step += 1
+        n = len(self.params)
+        pp = (C.c_void_p * n)(*[t.data_ptr() for t in self.params])
+        mp = vp = None
+        if self.moments is not None:
+            mp = (C.c_void_p * n)(*[t.data_ptr() for t in self.moments[0]])
+            vp = (C.c_void_p * n)(*[t.data_ptr() for t in self.moments[1]])
+        self._lib.check(self.L.hses_population_apply(
+            self.ctx.handle, current_stream(), C.byref(m), C.byref(desc), self.noiser.opt_state.step, pp, mp, vp,
+            self._grads.data_ptr()))
+
     def update(self, raw_fitness: torch.Tensor, epoch: int = 0, gain_key: Optional[int] = None) -> None:
         """raw_fitness: the FULL population's raw fitness (thread ids 0..n-1). Updates parameters in place."""
         C = self.C

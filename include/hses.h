@@ -384,6 +384,28 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
                            float* const* m_bufs, float* const* v_bufs, void* workspace /*device*/,
                            size_t workspace_bytes);
 
+/* The same second half in two calls, for ranks that split the update as well as the forward
+ * pass (the reference's multi-GPU script replicates the update,
+ * snn_mnist_train_multi_gpu.py:225-234; this is the partial-sum alternative): hses_population_grads z-scores the FULL fitness vector and
+ * writes the gradient contribution of members first_thread .. first_thread+n_local-1 (whole
+ * pairs) of every parameter, scaled for a population of n_total, into `grads` — the weight
+ * matrices back to back in layer order, dense, then one float for out_gain
+ * (hses_population_grads_elems() floats).  The caller sums `grads` over the ranks (one
+ * all-reduce) and hands the sum to hses_population_apply, which runs the solver step on every
+ * parameter.  With first_thread = 0 and n_local = n_total the pair equals
+ * hses_population_update. */
+size_t hses_population_grads_elems(const hses_snn_model* m);
+int hses_population_grads(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, float sigma,
+                          int32_t rank, int32_t epoch, int32_t noise_reuse, int32_t group_size,
+                          int32_t freeze_nonlora, uint64_t gain_key,
+                          const float* raw_fitness /*device, n_total*/, int64_t n_total,
+                          int32_t first_thread, int64_t n_local, float* grads /*device*/,
+                          void* workspace /*device, hses_population_update_workspace_bytes()*/,
+                          size_t workspace_bytes);
+int hses_population_apply(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m,
+                          const hses_solver* solver, int32_t step, float* const* params /*device*/,
+                          float* const* m_bufs, float* const* v_bufs, const float* grads /*device*/);
+
 /* ---- rwkv7_inner_loop, hyperscalees-models/src/llm.rs:235-296, for a batch of sequences.
  *      r, w, k, v, a, b, out: (n_seq, T, H, S) dense; state (n_seq, H, S, S) is read and left
  *      holding the final state; new_starts (n_seq, T) bytes or NULL zeroes the state before a

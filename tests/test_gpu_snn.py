@@ -200,3 +200,38 @@ def test_config0_full_size_properties(hs, oracle):
     step.update(raw)
     for b, a in zip(before[:-1], step.params[:-1]):
         assert (a - b).abs().max().item() > 0
+
+
+def test_sharded_update_equals_the_whole_update(hs):
+    """hses_population_grads + hses_population_apply: one shard covering the population gives the
+    bits of hses_population_update; two shards whose gradients are added give the same parameters
+    up to fp32 summation order."""
+    from hyperscalees_b200 import models, noiser
+    dims, n_pop, bm, T, rank = [784, 128, 10], 32, 2, 4, 64     # rank 64: the tensor-core contraction
+    img, labels = synth(n_pop * bm, seed=11)
+    keys = models.default_base_keys(len(dims))
+
+    def fresh(n_local, first):
+        net = models.SnnMlp(dims, tau_m=1.0, v_th=0.3, seed=5)
+        frozen, nz = noiser.init_noiser(net.params(), 0.2, 0.05, 0, False, 0, rank, noiser.Solver.adamw(0.05))
+        return models.PopulationStep(net, frozen, nz, keys, T, n_local, bm, first_thread=first), nz
+
+    whole, nz0 = fresh(n_pop, 0)
+    raw = whole.eval(dev(img), dev(labels), [5, 6, 7, 8])
+    before = [p.clone() for p in whole.params]
+    whole.update(raw)
+
+    one, nz1 = fresh(n_pop, 0)
+    one.update_sharded(raw)
+    for a, b in zip(whole.params, one.params):
+        assert torch.equal(a, b)
+    assert nz1.opt_state.step == 1
+
+    lo_half, _ = fresh(n_pop // 2, 0)
+    hi_half, _ = fresh(n_pop // 2, n_pop // 2)
+    hi_half.update_sharded(raw, reduce_fn=lambda g: None)          # leaves its partial gradients in _grads
+    partial_hi = hi_half._grads.clone()
+    lo_half.update_sharded(raw, reduce_fn=lambda g: g.add_(partial_hi))
+    for p0, a, b in zip(before, whole.params, lo_half.params):
+        moved = (a - p0).abs().max().item()
+        assert moved > 0 and (a - b).abs().max().item() <= 1e-3 * moved + 1e-7
