@@ -28,6 +28,7 @@ EXPORTS = [
     "hses_population_update", "hses_wkv7", "hses_spiking_attention",
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
+    "hses_convert_fitnesses_bs", "hses_vector_mul",
 ]
 
 
@@ -148,6 +149,8 @@ def load():
     L.hses_population_update.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64,
                                          C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                          vp, sz]
+    L.hses_convert_fitnesses_bs.argtypes = [vp, vp, vp, i64, i32, vp, vp]
+    L.hses_vector_mul.argtypes = [vp, vp, vp, vp, vp, i64]
     L.hses_population_grads_elems.restype = sz
     L.hses_population_grads_elems.argtypes = [pm]
     L.hses_population_grads.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64, i32, i64, vp, vp, sz]

@@ -252,6 +252,58 @@ __global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float
 
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
+// EggRollBS::convert_fitnesses (hyperscalees-noiser/src/eggroll_bs.rs:226-250), first pass: one
+// warp per row of the (Q, G) score matrix writes std + 1e-8 with var = E[x^2] - E[x]^2.
+__global__ void bs_row_std_kernel(const float* __restrict__ raw, int64_t q, int g, float* __restrict__ row_den) {
+    int64_t r = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    int lane = threadIdx.x & 31;
+    if (r >= q) return;
+    const float* s = raw + (size_t)r * g;
+    float sum = 0.0f, sumsq = 0.0f;
+    for (int j = lane; j < g; j += 32) {
+        float v = s[j];
+        sum += v;
+        sumsq = fmaf(v, v, sumsq);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        sumsq += __shfl_xor_sync(0xffffffffu, sumsq, off);
+    }
+    if (lane == 0) {
+        float mean = __fdiv_rn(sum, (float)g);
+        float var = __fsub_rn(__fdiv_rn(sumsq, (float)g), __fmul_rn(mean, mean));
+        row_den[r] = __fadd_rn(__fsqrt_rn(var), 1e-8f);
+    }
+}
+
+// Second pass: block j averages (S[q][j] - S[q][0]) / den[q] over the rows; columns 0 and 1 are zero.
+__global__ void bs_column_mean_kernel(const float* __restrict__ raw, int64_t q, int g,
+                                      const float* __restrict__ row_den, float* __restrict__ out) {
+    __shared__ float red[32];
+    int j = blockIdx.x;
+    float acc = 0.0f;
+    if (j >= 2) {
+        for (int64_t r = threadIdx.x; r < q; r += blockDim.x) {
+            const float* s = raw + (size_t)r * g;
+            acc += __fdiv_rn(__fsub_rn(s[j], s[0]), row_den[r]);
+        }
+    }
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+        out[j] = __fdiv_rn(t, (float)q);
+    }
+}
+
+__global__ void vector_mul_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                  float* __restrict__ out, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __fmul_rn(a[i], b[i]);
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -363,6 +415,37 @@ int hses_convert_fitnesses(hses_ctx* ctx, hses_stream stream, const float* raw, 
     HSES_REQUIRE(raw != nullptr && out != nullptr, "NULL pointer");
     HSES_KERNEL(ctx, as_stream(stream), "zscore");
     zscore_kernel<<<1, kZThreads, 0, as_stream(stream)>>>(raw, n, group_size, out, stats);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_convert_fitnesses_bs(hses_ctx* ctx, hses_stream stream, const float* raw, int64_t n,
+                              int32_t group_size, float* out, float* row_den) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(group_size >= 1 && n >= group_size && n % group_size == 0,
+                 "n must be a positive multiple of group_size");
+    HSES_REQUIRE(raw != nullptr && out != nullptr && row_den != nullptr, "NULL pointer");
+    int64_t q = n / group_size;
+    {
+        HSES_KERNEL(ctx, as_stream(stream), "bs_row_std");
+        bs_row_std_kernel<<<(unsigned)((q + 7) / 8), 256, 0, as_stream(stream)>>>(raw, q, group_size, row_den);
+        HSES_LAUNCH_CHECK();
+    }
+    {
+        HSES_KERNEL(ctx, as_stream(stream), "bs_column_mean");
+        bs_column_mean_kernel<<<(unsigned)group_size, 256, 0, as_stream(stream)>>>(raw, q, group_size, row_den, out);
+        HSES_LAUNCH_CHECK();
+    }
+    return HSES_OK;
+}
+
+int hses_vector_mul(hses_ctx* ctx, hses_stream stream, const float* a, const float* b, float* out, int64_t n) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 0, "n must be >= 0");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(a != nullptr && b != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "vector_mul");
+    vector_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(a, b, out, n);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -418,3 +418,52 @@ class AltEggRoll(EggRoll):
     uses sign(A_i) * (sigma * f_i / sqrt(rank)) and sign(B_i) (alteggroll.rs:65-90)."""
 
     sign_factors = True
+
+
+class EggRollBS(EggRoll):
+    """hyperscalees-noiser/src/eggroll_bs.rs: EggRoll with baseline subtraction, a member mask
+    and a trust-region clipped solver.
+
+    * noise of thread ids with `tid % group_size < 2` is zero (eggroll_bs.rs:73-125): such a
+      member's forward is the clean product and it contributes nothing to the update;
+    * convert_fitnesses turns the (Q, G) raw scores into G per-direction values (226-250);
+    * init_noiser wraps the solver in clip_by_global_norm (37-65)."""
+
+    @staticmethod
+    def init_noiser(params, sigma: float, _lr: float, group_size: int, freeze_nonlora: bool,
+                    noise_reuse: int, rank: int, trust_region_norm: float, solver: Solver):
+        return init_noiser(params, sigma, _lr, group_size, freeze_nonlora, noise_reuse, rank,
+                           Solver.trust_region(trust_region_norm, solver))
+
+    @staticmethod
+    def mask(info: IterInfo, group_size: int) -> float:
+        """eggroll_bs.rs:73-80."""
+        return 1.0 if group_size > 0 and info.thread_id % group_size >= 2 else 0.0
+
+    def do_mm(self, frozen, noiser, param, base_key, iterinfo, x):
+        if iterinfo is not None and self.mask(iterinfo, frozen.group_size) == 0.0:
+            iterinfo = None   # both factors are multiplied by the mask: the rank-r term vanishes
+        return super().do_mm(frozen, noiser, param, base_key, iterinfo, x)
+
+    def do_Tmm(self, frozen, noiser, param, base_key, iterinfo, x):  # noqa: N802
+        if iterinfo is not None and self.mask(iterinfo, frozen.group_size) == 0.0:
+            iterinfo = None
+        return super().do_Tmm(frozen, noiser, param, base_key, iterinfo, x)
+
+    def get_noisy_standard(self, frozen, noiser, param, base_key, iterinfo):
+        if iterinfo is not None and self.mask(iterinfo, frozen.group_size) == 0.0:
+            return param.clone()
+        return super().get_noisy_standard(frozen, noiser, param, base_key, iterinfo)
+
+    def convert_fitnesses(self, frozen: FrozenNoiserParams, noiser: NoiserParams,
+                          raw: torch.Tensor) -> torch.Tensor:
+        return ops.convert_fitnesses_bs(raw, frozen.group_size)
+
+    def grads(self, frozen, noiser, params, base_keys, fitnesses, iterinfos, es_classes):
+        """do_update (eggroll_bs.rs:198-224): EggRoll's update with every member's factors
+        multiplied by its mask, i.e. with masked fitnesses."""
+        infos = list(iterinfos)
+        m = torch.as_tensor(np.asarray([self.mask(i, frozen.group_size) for i in infos], dtype=np.float32),
+                            device=fitnesses.device)
+        return super().grads(frozen, noiser, params, base_keys, ops.vector_mul(fitnesses.contiguous(), m),
+                             infos, es_classes)

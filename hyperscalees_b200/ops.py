@@ -317,6 +317,31 @@ def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int,
     return out
 
 
+def convert_fitnesses_bs(raw: torch.Tensor, group_size: int) -> torch.Tensor:
+    """EggRollBS baseline-subtracted per-direction fitness (eggroll_bs.rs:226-250): (n,) -> (G,)."""
+    _check(raw, "raw", ndim=1)
+    n = raw.numel()
+    if group_size < 1 or n % group_size:
+        raise ValueError("n must be a positive multiple of group_size")
+    out = torch.empty(group_size, dtype=torch.float32, device=raw.device)
+    den = torch.empty(n // group_size, dtype=torch.float32, device=raw.device)
+    ctx = get_context(raw.device)
+    _lib.check(_lib.load().hses_convert_fitnesses_bs(ctx.handle, current_stream(), _ptr(raw), n, group_size,
+                                                     _ptr(out), _ptr(den)))
+    return out
+
+
+def vector_mul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    _check(a, "a", ndim=1)
+    _check(b, "b", ndim=1)
+    if a.numel() != b.numel():
+        raise ValueError("a and b must have the same length")
+    out = torch.empty_like(a)
+    ctx = get_context(a.device)
+    _lib.check(_lib.load().hses_vector_mul(ctx.handle, current_stream(), _ptr(a), _ptr(b), _ptr(out), a.numel()))
+    return out
+
+
 def es_update_dense(key: int, epoch: int, noise_reuse: int, shape: Tuple[int, int], sigma: float,
                     fitness_: torch.Tensor, first_thread: int = 0,
                     n_total: Optional[int] = None) -> torch.Tensor:

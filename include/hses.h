@@ -220,6 +220,18 @@ int hses_convert_fitnesses(hses_ctx* ctx, hses_stream stream, const float* raw /
                            int64_t n, int32_t group_size, float* out /*device*/,
                            float* stats /*device or NULL*/);
 
+/* ---- EggRollBS::convert_fitnesses, hyperscalees-noiser/src/eggroll_bs.rs:226-250: the raw
+ *      scores as (Q = n / group_size, G = group_size) rows; the first column of a row is its
+ *      baseline, Z = (S - baseline) / (row std + 1e-8), columns 0 and 1 are zeroed, and the
+ *      result is the mean of Z over the rows: G values in `out`.  row_den: device scratch of Q
+ *      floats. -------------------------------------------------------------- */
+int hses_convert_fitnesses_bs(hses_ctx* ctx, hses_stream stream, const float* raw /*device*/,
+                              int64_t n, int32_t group_size, float* out /*device, G*/,
+                              float* row_den /*device, Q*/);
+/* out[i] = a[i] * b[i]: applies EggRollBS's member mask (eggroll_bs.rs:73-80) to a fitness vector. */
+int hses_vector_mul(hses_ctx* ctx, hses_stream stream, const float* a /*device*/,
+                    const float* b /*device*/, float* out /*device*/, int64_t n);
+
 /* ---- simple_lora_update + do_update_with, eggroll.rs:353-404:
  *      grad(a,b) = -sqrt(N) * (1/N) * sum_i f_i A_i B_iᵀ with the factors
  *      regenerated from seeds.  Members are first_thread .. first_thread+n-1

@@ -306,6 +306,25 @@ void hso_convert_fitnesses(const float *raw, size_t n, int group_size, float *ou
     }
 }
 
+/* EggRollBS::convert_fitnesses, hyperscalees-noiser/src/eggroll_bs.rs:226-250: raw scores as
+ * (Q, G) rows; baseline = first column; Z = (S - b) / (row std + 1e-8), row var = E[x^2] - E[x]^2;
+ * columns 0 and 1 are zeroed; result = mean over rows (length G). */
+void hso_convert_fitnesses_bs(const float *raw, size_t n, int group_size, float *out) {
+    size_t g = (size_t)group_size, q = n / g;
+    for (size_t j = 0; j < g; ++j) out[j] = 0.0f;
+    for (size_t r = 0; r < q; ++r) {
+        const float *s = raw + r * g;
+        float sum = 0.0f, sumsq = 0.0f;
+        for (size_t j = 0; j < g; ++j) sum += s[j];
+        for (size_t j = 0; j < g; ++j) sumsq += s[j] * s[j];
+        float mean = sum / (float)g;
+        float std = sqrtf(sumsq / (float)g - mean * mean);
+        float den = std + 1e-8f;
+        for (size_t j = 2; j < g; ++j) out[j] += (s[j] - s[0]) / den;
+    }
+    for (size_t j = 0; j < g; ++j) out[j] = out[j] / (float)q;
+}
+
 /* ------------------------------------------------------------------------ */
 /* SNN forward for one member                                               */
 /* ------------------------------------------------------------------------ */

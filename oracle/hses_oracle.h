@@ -77,6 +77,7 @@ void hso_fitness(const float *logits, size_t n, int classes, const int32_t *labe
                  int reward, float *out);
 /* noiser.rs:517-537 */
 void hso_convert_fitnesses(const float *raw, size_t n, int group_size, float *out);
+void hso_convert_fitnesses_bs(const float *raw, size_t n, int group_size, float *out);
 
 /* ---- SNN forward for one member
  *      (snn.rs:253-282 generalised to a list of hidden layers) ------------ */

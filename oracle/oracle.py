@@ -190,6 +190,13 @@ def fitness(logits, labels, reward: int = REWARD_LOGLIK) -> np.ndarray:
     return out
 
 
+def convert_fitnesses_bs(raw, group_size: int) -> np.ndarray:
+    raw, rp = _f(raw)
+    out = np.empty(group_size, dtype=np.float32)
+    lib().hso_convert_fitnesses_bs(rp, C.c_size_t(raw.size), group_size, out.ctypes.data_as(_f32p))
+    return out
+
+
 def convert_fitnesses(raw, group_size: int = 0) -> np.ndarray:
     raw, rp = _f(raw)
     out = np.empty_like(raw)

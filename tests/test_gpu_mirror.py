@@ -133,3 +133,38 @@ def test_adam_step_counter_and_trust_region(hs, oracle):
     scale = oracle.clip_scale([g.cpu().numpy()], 1.0)
     want, _, _ = oracle.solver_update(oracle.ADAM, 1, p.cpu().numpy(), g.cpu().numpy() * np.float32(scale), lr=0.01)
     assert np.allclose(out[0].cpu().numpy(), want, atol=1e-5)
+
+
+def test_eggroll_bs_noiser(hs, oracle):
+    """EggRollBS (eggroll_bs.rs): masked members are clean, per-direction fitness, trust-region solver."""
+    from hyperscalees_b200 import noiser, ops
+    bs = noiser.EggRollBS()
+    p = torch.randn(6, 8, device="cuda")
+    frozen, nz = bs.init_noiser([p], 0.5, 0.1, 4, False, 0, 2, 1.0, noiser.Solver.sgd(0.1))
+    assert frozen.solver.kind == "trust_region" and frozen.group_size == 4
+    x = torch.randn(3, 8, device="cuda")
+    clean = bs.do_mm(frozen, nz, p, 9, None, x)
+    # eggroll_bs.rs:430-464: directions 0 and 1 of every group are silenced, the others are not
+    for tid, masked in ((0, True), (1, True), (2, False), (5, True), (6, False), (7, False)):
+        y = bs.do_mm(frozen, nz, p, 9, noiser.IterInfo(0, tid), x)
+        assert torch.equal(y, clean) == masked
+        plain = noiser.EggRoll().do_mm(frozen, nz, p, 9, noiser.IterInfo(0, tid), x)
+        if not masked:
+            assert torch.equal(y, plain)
+    # per-direction fitness against the oracle
+    raw = torch.randn(12 * 4, device="cuda") * 2 + 1
+    got = bs.convert_fitnesses(frozen, nz, raw).cpu().numpy()
+    want = oracle.convert_fitnesses_bs(raw.cpu().numpy(), 4)
+    assert got.shape == (4,) and got[0] == 0.0 and got[1] == 0.0
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-6)
+    # update: masked members contribute nothing
+    fit = torch.tensor([3.0, -2.0, 1.0, 0.5], device="cuda")
+    infos = [noiser.IterInfo(0, t) for t in range(4)]
+    (g_bs,) = bs.grads(frozen, nz, [p], [9], fit, infos, [noiser.MM_PARAM])
+    fit_masked = torch.tensor([0.0, 0.0, 1.0, 0.5], device="cuda")
+    (g_ref,) = noiser.EggRoll().grads(frozen, nz, [p], [9], fit_masked, infos, [noiser.MM_PARAM])
+    assert torch.equal(g_bs, g_ref)
+    # eggroll_bs.rs:508-530: the combined gradient is clipped to the trust-region norm
+    new = bs.do_updates(frozen, nz, [p], [9], fit * 100, infos, [noiser.MM_PARAM])
+    step = (p - new[0]) / 0.1
+    assert abs(float(step.norm()) - 1.0) <= 1e-3
