@@ -525,36 +525,92 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
 
     // ---- operand split of this CTA's x rows (one warp per row) ----
     const int n4 = k >> 2;
-    for (int lr = warp; lr < total_rows; lr += LT_THREADS / 32) {
-        const int64_t R = row_s[lr];
-        const float4* src = reinterpret_cast<const float4*>(x + (size_t)R * x_stride);
-        float m = 0.0f;
-        for (int i = lane; i < n4; i += 32) {
-            float4 v = src[i];
-            m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        }
+    auto finish_row = [&](int64_t R, float m, float& sc) {
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
         int e = 13 - ex;
         if (ex <= -127 || ex >= 128) e = 0;
         if (e > 100) e = 100;
         if (e < -100) e = -100;
-        float sc = __uint_as_float((uint32_t)(127 + e) << 23);
+        sc = __uint_as_float((uint32_t)(127 + e) << 23);
         if (lane == 0) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
-        uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R * k);
-        uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R * k);
-        for (int i = lane; i < n4; i += 32) {
-            float4 v = src[i];
-            float f[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-            uint32_t hb[4], lb[4];
+    };
+    auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
+        float f[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+        uint32_t hb[4], lb[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __half h = __float2half_rn(f[j]);
-                hb[j] = __half_as_ushort(h);
-                lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
+        for (int j = 0; j < 4; ++j) {
+            __half h = __float2half_rn(f[j]);
+            hb[j] = __half_as_ushort(h);
+            lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
+        }
+        h2 = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+        l2 = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+    };
+    if (n4 <= 256) {
+        // rows of up to 1024 values stay in registers between the maximum and the conversion, and a
+        // warp keeps two rows in flight: one trip to memory per row instead of two dependent ones
+        for (int lr = warp; lr < total_rows; lr += 2 * (LT_THREADS / 32)) {
+            const int lr1 = lr + LT_THREADS / 32;
+            const bool two = lr1 < total_rows;
+            const int64_t R0 = row_s[lr], R1 = row_s[two ? lr1 : lr];
+            const float4* s0 = reinterpret_cast<const float4*>(x + (size_t)R0 * x_stride);
+            const float4* s1 = reinterpret_cast<const float4*>(x + (size_t)R1 * x_stride);
+            float4 v0[8], v1[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = lane + 32 * j;
+                v0[j] = i < n4 ? __ldg(s0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[j] = (two && i < n4) ? __ldg(s1 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            dh[i] = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
-            dl[i] = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+            float m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                m0 = fmaxf(m0, fmaxf(fmaxf(fabsf(v0[j].x), fabsf(v0[j].y)), fmaxf(fabsf(v0[j].z), fabsf(v0[j].w))));
+                m1 = fmaxf(m1, fmaxf(fmaxf(fabsf(v1[j].x), fabsf(v1[j].y)), fmaxf(fabsf(v1[j].z), fabsf(v1[j].w))));
+            }
+            float sc0, sc1 = 1.0f;
+            finish_row(R0, m0, sc0);
+            if (two) finish_row(R1, m1, sc1);   // warp-uniform branch
+            uint2* dh0 = reinterpret_cast<uint2*>(xhi + (size_t)R0 * k);
+            uint2* dl0 = reinterpret_cast<uint2*>(xlo + (size_t)R0 * k);
+            uint2* dh1 = reinterpret_cast<uint2*>(xhi + (size_t)R1 * k);
+            uint2* dl1 = reinterpret_cast<uint2*>(xlo + (size_t)R1 * k);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = lane + 32 * j;
+                if (i < n4) {
+                    uint2 h2, l2;
+                    split4(v0[j], sc0, h2, l2);
+                    dh0[i] = h2;
+                    dl0[i] = l2;
+                    if (two) {
+                        split4(v1[j], sc1, h2, l2);
+                        dh1[i] = h2;
+                        dl1[i] = l2;
+                    }
+                }
+            }
+        }
+    } else {
+        for (int lr = warp; lr < total_rows; lr += LT_THREADS / 32) {
+            const int64_t R = row_s[lr];
+            const float4* src = reinterpret_cast<const float4*>(x + (size_t)R * x_stride);
+            float m = 0.0f;
+            for (int i = lane; i < n4; i += 32) {
+                float4 v = src[i];
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+            float sc;
+            finish_row(R, m, sc);
+            uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R * k);
+            uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R * k);
+            for (int i = lane; i < n4; i += 32) {
+                uint2 h2, l2;
+                split4(src[i], sc, h2, l2);
+                dh[i] = h2;
+                dl[i] = l2;
+            }
         }
     }
 
