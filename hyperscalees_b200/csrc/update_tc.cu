@@ -5,17 +5,19 @@
 // dominates the step (a multiple of 128, rank a multiple of 64).
 //
 //   launch 1  pair_weight_range   largest |f_2p - f_2p+1| -> one power-of-two scale for all weights
-//   launch 2  factor_split        raw factors (factor cache, or scratch pair_factors just filled)
-//                                 -> weighted A and B times fixed powers of two, each as fp16 hi + lo
-//   launch 3  update_tc           one CTA per (128 x bn output tile, K split): TMA brings the
-//                                 [128 x 64] / [bn x 64] hi and lo tiles of one pair at a time into
-//                                 128B-swizzled shared memory (3-D tensor maps over (q, row, pair)),
-//                                 tcgen05.mma kind::f16 accumulates hi*hi + hi*lo + lo*hi in TMEM
-//                                 over the split's pairs, four warps drain TMEM into the split's
-//                                 partial sums
-//   launch 4  update_tc_reduce    adds the splits in a fixed order, undoes the scales
-// Three fp16 passes keep the products fp32-equivalent; normals from 24-bit uniforms are bounded
-// by 5.8, so fixed scales cannot overflow.  No multicast, no cluster launch, bounded waits.
+//   launch 2  update_tc           one CTA per (128 x bn output tile, K split), eighteen warps:
+//       warps 2-17  converters: read the raw fp32 factors of one pair at a time straight from
+//                   global memory (factor cache, or scratch pair_factors just filled), apply the
+//                   pair weight and fixed powers of two, split into fp16 hi + lo and store the
+//                   [128 x 64] / [bn x 64] tiles into 128B-swizzled shared-memory stages
+//       warp 0      MMA issuer: tcgen05.mma kind::f16, hi*hi + hi*lo + lo*hi, fp32 accumulators
+//                   in TMEM over all pairs of the split
+//       warps 2-17  afterwards drain TMEM into the split's partial sums (four per TMEM quadrant)
+//   launch 3  update_tc_reduce    adds the splits in a fixed order, undoes the scales
+// The factors are read exactly once, as fp32, and never written back: the kernel is bound by
+// those bytes.  Three fp16 passes keep the products fp32-equivalent; normals from 24-bit
+// uniforms are bounded by 5.8, so fixed scales cannot overflow.  No multicast, no cluster
+// launch, bounded waits.
 #include <cuda.h>
 #include <cuda_fp16.h>
 
@@ -30,9 +32,10 @@ using namespace tc;
 
 constexpr int UT_BM = 128;
 constexpr int UT_BK = 64;
-constexpr int UT_THREADS = 192;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int UT_THREADS = 576;  // warp 0 MMA, warp 1 idle, warps 2-17 converters and epilogue
+constexpr int UT_CONV = 512;     // converter threads
 constexpr int kExpA = 12, kExpB = 11;  // A' = (w * 2^-e_w) * A * 2^12 <= 23.7e3, B' = B * 2^11 <= 11.9e3
-constexpr size_t kHalfChunkBytes = 384ull << 20;  // fp16 operand copies of one chunk of pairs
+constexpr size_t kRawChunkBytes = 384ull << 20;  // regenerated fp32 factors of one chunk of pairs
 
 // largest |f_even - f_odd| over the call's pairs -> exponent e with 2^e >= max (0 when all zero)
 __global__ void pair_weight_range_kernel(const float* __restrict__ fitness, int64_t pairs, int* __restrict__ e_out) {
@@ -55,53 +58,12 @@ __global__ void pair_weight_range_kernel(const float* __restrict__ fitness, int6
     }
 }
 
-__device__ __forceinline__ void split_store(const float (&f)[4], __half* hi, __half* lo, size_t i4) {
-    uint32_t hb[4], lb[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        __half h = __float2half_rn(f[j]);
-        hb[j] = __half_as_ushort(h);
-        lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
-    }
-    reinterpret_cast<uint2*>(hi)[i4] = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
-    reinterpret_cast<uint2*>(lo)[i4] = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
-}
-
-// One thread per four consecutive factor values (rank is a multiple of four, so they belong to
-// one pair).  weights: fitness of the chunk's first member on; sign_factors as in update.cu.
-__global__ void factor_split_kernel(const float* __restrict__ A, const float* __restrict__ B, int64_t pairs, int a,
-                                    int b, int rank, const float* __restrict__ fitness,
-                                    const int* __restrict__ e_w, int sign_factors, __half* __restrict__ ahi,
-                                    __half* __restrict__ alo, __half* __restrict__ bhi, __half* __restrict__ blo) {
-    const size_t na4 = (size_t)pairs * a * rank / 4, nb4 = (size_t)pairs * b * rank / 4;
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < na4) {
-        const int64_t p = (int64_t)(i / ((size_t)a * rank / 4));
-        float w = __fsub_rn(fitness[2 * p], fitness[2 * p + 1]);
-        float4 v = __ldg(reinterpret_cast<const float4*>(A) + i);
-        float f[4] = {v.x, v.y, v.z, v.w};
-        const float sc = ldexpf(1.0f, kExpA - *e_w);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (sign_factors) f[j] = f[j] > 0.0f ? 1.0f : f[j] < 0.0f ? -1.0f : 0.0f;
-            f[j] = __fmul_rn(__fmul_rn(f[j], w), sc);  // the scale is a power of two: exact
-        }
-        split_store(f, ahi, alo, i);
-    } else if (i < na4 + nb4) {
-        const size_t j4 = i - na4;
-        float4 v = __ldg(reinterpret_cast<const float4*>(B) + j4);
-        float f[4] = {v.x, v.y, v.z, v.w};
-        const float sc = ldexpf(1.0f, kExpB);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (sign_factors) f[j] = f[j] > 0.0f ? 1.0f : f[j] < 0.0f ? -1.0f : 0.0f;
-            f[j] = __fmul_rn(f[j], sc);
-        }
-        split_store(f, bhi, blo, j4);
-    }
-}
-
 struct UtArgs {
+    const float* A;     // raw (pairs, a, rank) of this chunk
+    const float* B;     // raw (pairs, b, rank)
+    const float* fitness;  // of the chunk's first member on
+    const int* e_w;
+    int sign_factors;
     int a, b, rank, bn;
     int n_tiles;        // output column tiles of bn
     int64_t pairs;      // pairs of this chunk
@@ -113,16 +75,34 @@ struct UtArgs {
     int* status;
 };
 
+// four fp32 values -> fp16 hi and lo halves of a 16-byte piece of a 128B-swizzled K-major tile
+__device__ __forceinline__ void convert_store(float4 v, float mul0, float mul1, int sign_factors, uint8_t* tile_hi,
+                                              uint8_t* tile_lo, int row, int f4) {
+    float f[4] = {v.x, v.y, v.z, v.w};
+    uint32_t hb[4], lb[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float x = f[j];
+        if (sign_factors) x = x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f;
+        x = __fmul_rn(__fmul_rn(x, mul0), mul1);  // mul1 is a power of two: exact
+        __half h = __float2half_rn(x);
+        hb[j] = __half_as_ushort(h);
+        lb[j] = __half_as_ushort(__float2half_rn(x - __half2float(h)));
+    }
+    // row r of the tile is 128 bytes; its 16-byte piece c sits at piece c ^ (r % 8) of the row
+    const int off = (row >> 3) * 1024 + (row & 7) * 128 + (((f4 >> 1) ^ (row & 7)) << 4) + ((f4 & 1) << 3);
+    *reinterpret_cast<uint2*>(tile_hi + off) = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+    *reinterpret_cast<uint2*>(tile_lo + off) = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+}
+
 __global__ void __launch_bounds__(UT_THREADS, 1)
-update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_constant__ CUtensorMap tm_alo,
-                 const __grid_constant__ CUtensorMap tm_bhi, const __grid_constant__ CUtensorMap tm_blo,
-                 const UtArgs g) {
+update_tc_kernel(const UtArgs g) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int a_bytes = UT_BM * UT_BK * 2, b_bytes = g.bn * UT_BK * 2;
     const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
-    uint64_t* full = bars;          // [stages]
-    uint64_t* empty = bars + 4;     // [stages]
+    uint64_t* full = bars;          // [stages] tiles converted
+    uint64_t* empty = bars + 4;     // [stages] MMAs finished reading the stage
     uint64_t* tfull = bars + 8;     // accumulator complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     __shared__ int abort_flag_s;
@@ -137,13 +117,13 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_consta
     if (threadIdx.x == 0) {
         abort_flag_s = 0;
         for (int s = 0; s < g.stages; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], UT_CONV);
             mbar_init(&empty[s], 1);
         }
         mbar_init(tfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(g.tmem_cols)
                      : "memory");
@@ -155,32 +135,6 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
-            bool ok = true;
-            int64_t it = 0;
-            for (int64_t p = p_lo; p < p_hi && ok; ++p) {
-                for (int qb = 0; qb < kq; ++qb, ++it) {
-                    int s = (int)(it % g.stages);
-                    uint32_t ph = (uint32_t)(it / g.stages) & 1;
-                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 11)) { ok = false; break; }
-                    uint8_t* st = smem + (size_t)s * stage_bytes;
-                    mbar_expect_tx(&full[s], (uint32_t)stage_bytes);
-                    tma_load_3d(st, &tm_ahi, qb * UT_BK, mt * UT_BM, (int)p, &full[s]);
-                    tma_load_3d(st + a_bytes, &tm_alo, qb * UT_BK, mt * UT_BM, (int)p, &full[s]);
-                    tma_load_3d(st + 2 * a_bytes, &tm_bhi, qb * UT_BK, nt * g.bn, (int)p, &full[s]);
-                    tma_load_3d(st + 2 * a_bytes + b_bytes, &tm_blo, qb * UT_BK, nt * g.bn, (int)p, &full[s]);
-                }
-            }
-            if (!ok) {
-                // copies already issued still land in this CTA's shared memory: give them a bounded moment
-                for (int s = 0; s < g.stages; ++s)
-                    for (uint32_t i = 0; i < 4096; ++i) {
-                        if (mbar_try(&full[s], 0) || mbar_try(&full[s], 1)) break;
-                        __nanosleep(256);
-                    }
-            }
-        }
-    } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(g.bn);
             bool ok = true;
@@ -203,17 +157,69 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_consta
             }
             if (ok && k_blocks > 0) umma_commit(tfull);
         }
-    } else {
-        // epilogue: warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32); lane = output row
-        const int q4 = warp & 3;
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------------ converters
+        const int ct = threadIdx.x - 64;        // 0..511
+        const int crow = ct >> 4, f4 = ct & 15;  // 32 rows per pass, 16 float4 per 64-value row
+        const float sc_a = ldexpf(1.0f, kExpA - *g.e_w), sc_b = ldexpf(1.0f, kExpB);
+        constexpr int A_PASSES = UT_BM / 32, B_PASSES = 256 / 32;
+        bool ok = true;
+        int64_t it = 0;
+        for (int64_t p = p_lo; p < p_hi && ok; ++p) {
+            const float w = __fsub_rn(g.fitness[2 * p], g.fitness[2 * p + 1]);
+            const float* Ap = g.A + (size_t)p * g.a * g.rank;
+            const float* Bp = g.B + (size_t)p * g.b * g.rank;
+            for (int qb = 0; qb < kq; ++qb, ++it) {
+                const int s = (int)(it % g.stages);
+                const uint32_t ph = (uint32_t)(it / g.stages) & 1;
+                const int q0 = qb * UT_BK + f4 * 4;
+                // every load of the k-block is issued before the first conversion: one trip to
+                // memory per k-block (rows past a, b or bn read as zero)
+                float4 va[A_PASSES], vb[B_PASSES];
+#pragma unroll
+                for (int u = 0; u < A_PASSES; ++u) {
+                    const int m = mt * UT_BM + u * 32 + crow;
+                    va[u] = m < g.a ? __ldg(reinterpret_cast<const float4*>(Ap + (size_t)m * g.rank + q0))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < B_PASSES; ++u) {
+                    const int row = u * 32 + crow;
+                    const int n = nt * g.bn + row;
+                    vb[u] = (row < g.bn && n < g.b)
+                                ? __ldg(reinterpret_cast<const float4*>(Bp + (size_t)n * g.rank + q0))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 11)) { ok = false; break; }
+                uint8_t* st = smem + (size_t)s * stage_bytes;
+#pragma unroll
+                for (int u = 0; u < A_PASSES; ++u)
+                    convert_store(va[u], w, sc_a, g.sign_factors, st, st + a_bytes, u * 32 + crow, f4);
+#pragma unroll
+                for (int u = 0; u < B_PASSES; ++u) {
+                    const int row = u * 32 + crow;
+                    if (row < g.bn)
+                        convert_store(vb[u], 1.0f, sc_b, g.sign_factors, st + 2 * a_bytes,
+                                      st + 2 * a_bytes + b_bytes, row, f4);
+                }
+                fence_proxy_async();   // the tensor core reads these generic-proxy stores
+                mbar_arrive(&full[s]);
+            }
+        }
+        // ------------------------------------------------------------------ epilogue
+        // warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32); lane = output row; the four warps of
+        // a quadrant take one quarter of the columns each
+        const int q4 = warp & 3, eh = (warp - 2) >> 2;
         const int m = mt * UT_BM + q4 * 32 + lane;
-        float* dst = g.partial + ((size_t)split * g.a + m) * g.b;
-        bool have = k_blocks > 0;
+        float* dst = g.partial + ((size_t)split * g.a + (m < g.a ? m : 0)) * g.b;
+        bool have = k_blocks > 0 && ok;
         if (have) have = mbar_wait(tfull, 0, abort_flag, g.status, 13);
         have = __all_sync(0xffffffffu, have);  // the TMEM loads below are warp-wide
         tc_fence_after();
         const int n0 = nt * g.bn;
-        for (int j0 = 0; j0 < g.bn; j0 += 8) {
+        const int quarter = (g.bn / 4 + 7) / 8 * 8;
+        const int j_lo = min(eh * quarter, g.bn), j_hi = eh == 3 ? g.bn : min((eh + 1) * quarter, g.bn);
+        for (int j0 = j_lo; j0 < j_hi; j0 += 8) {
             uint32_t acc[8];
             if (have) {
                 tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)j0, acc);
@@ -233,7 +239,7 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_ahi, const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(g.tmem_cols)
                      : "memory");
@@ -251,33 +257,12 @@ __global__ void update_tc_reduce_kernel(const float* __restrict__ partial, int s
     grad[i] = accumulate ? __fadd_rn(grad[i], s) : s;
 }
 
-// 3-D fp16 map over (q, row, pair): `rows` rows of `rank` values per pair; box (64, box_rows, 1)
-int make_map_3d(CUtensorMap* map, const __half* base, int rank, int rows, int64_t pairs, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) {
-        set_error("cuTensorMapEncodeTiled is not available from the driver");
-        return HSES_ERR_CUDA;
-    }
-    cuuint64_t dims[3] = {(cuuint64_t)rank, (cuuint64_t)rows, (cuuint64_t)pairs};
-    cuuint64_t strides[2] = {(cuuint64_t)rank * 2, (cuuint64_t)rank * 2 * (cuuint64_t)rows};
-    cuuint32_t box[3] = {(cuuint32_t)UT_BK, (cuuint32_t)box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string((int)r));
-        return HSES_ERR_CUDA;
-    }
-    return HSES_OK;
-}
-
 size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 }  // namespace
 
 bool update_tc_supports(int a, int b, int rank) {
-    // rows of A beyond a and rows of B beyond b are zero-filled by TMA, so only the rank is constrained
+    // rows of A beyond a and rows of B beyond b are written as zeros, so only the rank is constrained
     return a >= 1 && rank >= UT_BK && rank % UT_BK == 0 && b >= 1 && b <= (1 << 20) && a <= (1 << 20);
 }
 
@@ -288,21 +273,20 @@ UpdateTcPlan plan_update_tc(int a, int b, int rank, int64_t n, bool need_raw) {
     p.bn = ((b + tiles_n - 1) / tiles_n + 15) / 16 * 16;
     p.n_tiles = (b + p.bn - 1) / p.bn;
     p.m_tiles = (a + UT_BM - 1) / UT_BM;
-    size_t per_pair_half = (size_t)(a + b) * rank * 2 * 2;  // hi + lo
-    int64_t fit = (int64_t)(kHalfChunkBytes / per_pair_half);
+    // without a factor cache the factors are regenerated chunk by chunk into fp32 scratch
+    size_t per_pair = (size_t)(a + b) * rank * sizeof(float);
+    int64_t fit = (int64_t)(kRawChunkBytes / per_pair);
     if (fit < 1) fit = 1;
-    p.chunk_pairs = p.pairs < fit ? p.pairs : fit;
+    p.chunk_pairs = (need_raw && p.pairs > fit) ? fit : p.pairs;
     int tiles = p.n_tiles * p.m_tiles;
     // one CTA per SM fits (the operand stages take most of the shared memory): one full wave
     int want = 148 / tiles;
     if (want > p.chunk_pairs) want = (int)p.chunk_pairs;
     if (want < 1) want = 1;
     p.splits = want;
-    p.half_a = up256((size_t)p.chunk_pairs * a * rank * 2);
-    p.half_b = up256((size_t)p.chunk_pairs * b * rank * 2);
     p.partial_bytes = up256((size_t)p.splits * a * b * sizeof(float));
     p.raw_bytes = need_raw ? up256((size_t)p.chunk_pairs * (a + b) * rank * sizeof(float)) : 0;
-    p.bytes = 256 + 2 * p.half_a + 2 * p.half_b + p.partial_bytes + p.raw_bytes;
+    p.bytes = 256 + p.partial_bytes + p.raw_bytes;
     return p;
 }
 
@@ -313,12 +297,8 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
                  "workspace too small or not 256-byte aligned; see hses_es_update_workspace_bytes");
     uint8_t* base = reinterpret_cast<uint8_t*>(u.workspace);
     int* e_w = reinterpret_cast<int*>(base);
-    __half* ahi = reinterpret_cast<__half*>(base + 256);
-    __half* alo = reinterpret_cast<__half*>(base + 256 + p.half_a);
-    __half* bhi = reinterpret_cast<__half*>(base + 256 + 2 * p.half_a);
-    __half* blo = reinterpret_cast<__half*>(base + 256 + 2 * p.half_a + p.half_b);
-    float* partial = reinterpret_cast<float*>(base + 256 + 2 * p.half_a + 2 * p.half_b);
-    float* raw = reinterpret_cast<float*>(base + 256 + 2 * p.half_a + 2 * p.half_b + p.partial_bytes);
+    float* partial = reinterpret_cast<float*>(base + 256);
+    float* raw = reinterpret_cast<float*>(base + 256 + p.partial_bytes);
     const int32_t te = true_epoch_of(u.epoch, u.noise_reuse);
     const int32_t first_pair = u.first_thread / 2;
 
@@ -339,6 +319,8 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
         HSES_LAUNCH_CHECK();
     }
     UtArgs g{};
+    g.e_w = e_w;
+    g.sign_factors = u.sign_factors;
     g.a = a;
     g.b = b;
     g.rank = rank;
@@ -358,38 +340,24 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
     int chunk_idx = 0;
     for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
         const int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
-        const float *srcA, *srcB;
         if (u.cache) {
-            srcA = cA + (size_t)done * a * rank;
-            srcB = cB + (size_t)done * b * rank;
+            g.A = cA + (size_t)done * a * rank;
+            g.B = cB + (size_t)done * b * rank;
         } else {
             float* ra = raw;
             float* rb = raw + (size_t)cnt * a * rank;
             int rc = launch_pair_factors(ctx, st, u.key, te, first_pair + (int32_t)done, cnt, rank, a, b, nullptr, ra,
                                          rb);
             if (rc != HSES_OK) return rc;
-            srcA = ra;
-            srcB = rb;
+            g.A = ra;
+            g.B = rb;
         }
-        {
-            size_t n4 = (size_t)cnt * (a + b) * rank / 4;
-            HSES_KERNEL(ctx, st, "factor_split");
-            factor_split_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(srcA, srcB, cnt, a, b, rank,
-                                                                            u.fitness + 2 * done, e_w,
-                                                                            u.sign_factors, ahi, alo, bhi, blo);
-            HSES_LAUNCH_CHECK();
-        }
-        CUtensorMap tm_ahi, tm_alo, tm_bhi, tm_blo;
-        int rc = make_map_3d(&tm_ahi, ahi, rank, a, cnt, UT_BM);
-        if (rc == HSES_OK) rc = make_map_3d(&tm_alo, alo, rank, a, cnt, UT_BM);
-        if (rc == HSES_OK) rc = make_map_3d(&tm_bhi, bhi, rank, b, cnt, p.bn);
-        if (rc == HSES_OK) rc = make_map_3d(&tm_blo, blo, rank, b, cnt, p.bn);
-        if (rc != HSES_OK) return rc;
+        g.fitness = u.fitness + 2 * done;
         g.pairs = cnt;
         g.accumulate = chunk_idx > 0;
         dim3 grid((unsigned)(p.n_tiles * p.m_tiles), (unsigned)p.splits);
         HSES_KERNEL(ctx, st, "update_tc");
-        update_tc_kernel<<<grid, UT_THREADS, smem_bytes, st>>>(tm_ahi, tm_alo, tm_bhi, tm_blo, g);
+        update_tc_kernel<<<grid, UT_THREADS, smem_bytes, st>>>(g);
         HSES_LAUNCH_CHECK();
     }
     size_t len = (size_t)a * b;

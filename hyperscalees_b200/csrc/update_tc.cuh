@@ -8,7 +8,7 @@ namespace hses {
 struct UpdateTcPlan {
     int64_t pairs, chunk_pairs;
     int bn, n_tiles, m_tiles, splits;
-    size_t half_a, half_b, partial_bytes, raw_bytes, bytes;
+    size_t partial_bytes, raw_bytes, bytes;
 };
 
 // rank a multiple of 64: the shapes the tcgen05 contraction covers (ragged a and b are zero-filled)
