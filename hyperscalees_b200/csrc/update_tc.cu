@@ -6,10 +6,13 @@
 //
 //   launch 1  pair_weight_range   largest |f_2p - f_2p+1| -> one power-of-two scale for all weights
 //   launch 2  update_tc           one CTA per (128 x bn output tile, K split), eighteen warps:
-//       warps 2-17  converters: read the raw fp32 factors of one pair at a time straight from
-//                   global memory (factor cache, or scratch pair_factors just filled), apply the
-//                   pair weight and fixed powers of two, split into fp16 hi + lo and store the
-//                   [128 x 64] / [bn x 64] tiles into 128B-swizzled shared-memory stages
+//       warp 1      TMA producer: the raw fp32 [128 x 64] / [bn x 64] tiles of one pair at a time
+//                   (factor cache, or scratch pair_factors just filled) through 3-D tensor maps
+//                   over (q, row, pair) into a shared-memory stage
+//       warps 2-17  converters: read the landed fp32 values, apply the pair weight and fixed
+//                   powers of two, split into fp16 hi + lo and write the 128B-swizzled K-major
+//                   operand tiles over the same stage (an fp32 row and its hi + lo rows have the
+//                   same size)
 //       warp 0      MMA issuer: tcgen05.mma kind::f16, hi*hi + hi*lo + lo*hi, fp32 accumulators
 //                   in TMEM over all pairs of the split
 //       warps 2-17  afterwards drain TMEM into the split's partial sums (four per TMEM quadrant)
@@ -32,7 +35,7 @@ using namespace tc;
 
 constexpr int UT_BM = 128;
 constexpr int UT_BK = 64;
-constexpr int UT_THREADS = 576;  // warp 0 MMA, warp 1 idle, warps 2-17 converters and epilogue
+constexpr int UT_THREADS = 576;  // warp 0 MMA, warp 1 TMA, warps 2-17 converters and epilogue
 constexpr int UT_CONV = 512;     // converter threads
 constexpr int kExpA = 12, kExpB = 11;  // A' = (w * 2^-e_w) * A * 2^12 <= 23.7e3, B' = B * 2^11 <= 11.9e3
 constexpr size_t kRawChunkBytes = 384ull << 20;  // regenerated fp32 factors of one chunk of pairs
@@ -78,33 +81,38 @@ struct UtArgs {
 // four fp32 values -> fp16 hi and lo halves of a 16-byte piece of a 128B-swizzled K-major tile
 __device__ __forceinline__ void convert_store(float4 v, float mul0, float mul1, int sign_factors, uint8_t* tile_hi,
                                               uint8_t* tile_lo, int row, int f4) {
-    float f[4] = {v.x, v.y, v.z, v.w};
-    uint32_t hb[4], lb[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        float x = f[j];
-        if (sign_factors) x = x > 0.0f ? 1.0f : x < 0.0f ? -1.0f : 0.0f;
-        x = __fmul_rn(__fmul_rn(x, mul0), mul1);  // mul1 is a power of two: exact
-        __half h = __float2half_rn(x);
-        hb[j] = __half_as_ushort(h);
-        lb[j] = __half_as_ushort(__float2half_rn(x - __half2float(h)));
+    if (sign_factors) {  // uniform over the launch
+        v.x = v.x > 0.0f ? 1.0f : v.x < 0.0f ? -1.0f : 0.0f;
+        v.y = v.y > 0.0f ? 1.0f : v.y < 0.0f ? -1.0f : 0.0f;
+        v.z = v.z > 0.0f ? 1.0f : v.z < 0.0f ? -1.0f : 0.0f;
+        v.w = v.w > 0.0f ? 1.0f : v.w < 0.0f ? -1.0f : 0.0f;
     }
+    // mul1 is a power of two: the second product is exact
+    const float x0 = __fmul_rn(__fmul_rn(v.x, mul0), mul1), x1 = __fmul_rn(__fmul_rn(v.y, mul0), mul1);
+    const float x2 = __fmul_rn(__fmul_rn(v.z, mul0), mul1), x3 = __fmul_rn(__fmul_rn(v.w, mul0), mul1);
+    const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+    const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+    const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
     // row r of the tile is 128 bytes; its 16-byte piece c sits at piece c ^ (r % 8) of the row
     const int off = (row >> 3) * 1024 + (row & 7) * 128 + (((f4 >> 1) ^ (row & 7)) << 4) + ((f4 & 1) << 3);
-    *reinterpret_cast<uint2*>(tile_hi + off) = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
-    *reinterpret_cast<uint2*>(tile_lo + off) = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+    *reinterpret_cast<uint2*>(tile_hi + off) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+    *reinterpret_cast<uint2*>(tile_lo + off) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
 }
 
 __global__ void __launch_bounds__(UT_THREADS, 1)
-update_tc_kernel(const UtArgs g) {
+update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const UtArgs g) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int a_bytes = UT_BM * UT_BK * 2, b_bytes = g.bn * UT_BK * 2;
     const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)g.stages * stage_bytes);
     uint64_t* full = bars;          // [stages] tiles converted
     uint64_t* empty = bars + 4;     // [stages] MMAs finished reading the stage
-    uint64_t* tfull = bars + 8;     // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    uint64_t* landed = bars + 8;    // [stages] fp32 tiles arrived
+    uint64_t* readdone = bars + 12; // [stages] every converter has read its fp32 values
+    uint64_t* tfull = bars + 16;    // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,6 +127,8 @@ update_tc_kernel(const UtArgs g) {
         for (int s = 0; s < g.stages; ++s) {
             mbar_init(&full[s], UT_CONV);
             mbar_init(&empty[s], 1);
+            mbar_init(&landed[s], 1);
+            mbar_init(&readdone[s], UT_CONV);
         }
         mbar_init(tfull, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,6 +167,31 @@ update_tc_kernel(const UtArgs g) {
             }
             if (ok && k_blocks > 0) umma_commit(tfull);
         }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            int64_t it = 0;
+            for (int64_t p = p_lo; p < p_hi && ok; ++p) {
+                for (int qb = 0; qb < kq; ++qb, ++it) {
+                    const int s = (int)(it % g.stages);
+                    const uint32_t ph = (uint32_t)(it / g.stages) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 11)) { ok = false; break; }
+                    uint8_t* st = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&landed[s], (uint32_t)stage_bytes);  // boxes count in full, zero fill included
+                    tma_load_3d(st, &tm_a, qb * UT_BK, mt * UT_BM, (int)p, &landed[s]);
+                    tma_load_3d(st + 2 * a_bytes, &tm_b, qb * UT_BK, nt * g.bn, (int)p, &landed[s]);
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: give them a bounded moment
+                for (int s = 0; s < g.stages; ++s)
+                    for (uint32_t i = 0; i < 4096; ++i) {
+                        if (mbar_try(&landed[s], 0) || mbar_try(&landed[s], 1)) break;
+                        __nanosleep(256);
+                    }
+            }
+        }
     } else if (warp >= 2) {
         // ------------------------------------------------------------------ converters
         const int ct = threadIdx.x - 64;        // 0..511
@@ -167,31 +202,27 @@ update_tc_kernel(const UtArgs g) {
         int64_t it = 0;
         for (int64_t p = p_lo; p < p_hi && ok; ++p) {
             const float w = __fsub_rn(g.fitness[2 * p], g.fitness[2 * p + 1]);
-            const float* Ap = g.A + (size_t)p * g.a * g.rank;
-            const float* Bp = g.B + (size_t)p * g.b * g.rank;
             for (int qb = 0; qb < kq; ++qb, ++it) {
                 const int s = (int)(it % g.stages);
                 const uint32_t ph = (uint32_t)(it / g.stages) & 1;
-                const int q0 = qb * UT_BK + f4 * 4;
-                // every load of the k-block is issued before the first conversion: one trip to
-                // memory per k-block (rows past a, b or bn read as zero)
+                if (!mbar_wait(&landed[s], ph, abort_flag, g.status, 14)) { ok = false; break; }
+                uint8_t* st = smem + (size_t)s * stage_bytes;
+                // fp32 rows are 256 bytes; thread (crow, f4) owns the float4 f4 of rows crow + 32u
                 float4 va[A_PASSES], vb[B_PASSES];
 #pragma unroll
-                for (int u = 0; u < A_PASSES; ++u) {
-                    const int m = mt * UT_BM + u * 32 + crow;
-                    va[u] = m < g.a ? __ldg(reinterpret_cast<const float4*>(Ap + (size_t)m * g.rank + q0))
-                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                for (int u = 0; u < A_PASSES; ++u)
+                    va[u] = *reinterpret_cast<const float4*>(st + (size_t)(u * 32 + crow) * 256 + f4 * 16);
 #pragma unroll
                 for (int u = 0; u < B_PASSES; ++u) {
                     const int row = u * 32 + crow;
-                    const int n = nt * g.bn + row;
-                    vb[u] = (row < g.bn && n < g.b)
-                                ? __ldg(reinterpret_cast<const float4*>(Bp + (size_t)n * g.rank + q0))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                    vb[u] = row < g.bn ? *reinterpret_cast<const float4*>(st + 2 * a_bytes + (size_t)row * 256 + f4 * 16)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 11)) { ok = false; break; }
-                uint8_t* st = smem + (size_t)s * stage_bytes;
+                // the fp16 tiles overwrite the fp32 values: every converter must have read first
+                // (an mbarrier with a bounded wait rather than bar.sync: a role that gave up must
+                // not leave the others parked for good)
+                mbar_arrive(&readdone[s]);
+                if (!mbar_wait(&readdone[s], ph, abort_flag, g.status, 15)) { ok = false; break; }
 #pragma unroll
                 for (int u = 0; u < A_PASSES; ++u)
                     convert_store(va[u], w, sc_a, g.sign_factors, st, st + a_bytes, u * 32 + crow, f4);
@@ -255,6 +286,27 @@ __global__ void update_tc_reduce_kernel(const float* __restrict__ partial, int s
     for (int k = 0; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * len + i]);
     s = __fmul_rn(ldexpf(s, *e_w - kExpA - kExpB), scale);
     grad[i] = accumulate ? __fadd_rn(grad[i], s) : s;
+}
+
+// 3-D fp32 map over (q, row, pair): `rows` rows of `rank` values per pair; box (64, box_rows, 1), no swizzle
+int make_map_3d(CUtensorMap* map, const float* base, int rank, int rows, int64_t pairs, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return HSES_ERR_CUDA;
+    }
+    cuuint64_t dims[3] = {(cuuint64_t)rank, (cuuint64_t)rows, (cuuint64_t)pairs};
+    cuuint64_t strides[2] = {(cuuint64_t)rank * 4, (cuuint64_t)rank * 4 * (cuuint64_t)rows};
+    cuuint32_t box[3] = {(cuuint32_t)UT_BK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string((int)r));
+        return HSES_ERR_CUDA;
+    }
+    return HSES_OK;
 }
 
 size_t up256(size_t v) { return (v + 255) / 256 * 256; }
@@ -355,9 +407,13 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
         g.fitness = u.fitness + 2 * done;
         g.pairs = cnt;
         g.accumulate = chunk_idx > 0;
+        CUtensorMap tm_a, tm_b;
+        int mrc = make_map_3d(&tm_a, g.A, rank, a, cnt, UT_BM);
+        if (mrc == HSES_OK) mrc = make_map_3d(&tm_b, g.B, rank, b, cnt, p.bn);
+        if (mrc != HSES_OK) return mrc;
         dim3 grid((unsigned)(p.n_tiles * p.m_tiles), (unsigned)p.splits);
         HSES_KERNEL(ctx, st, "update_tc");
-        update_tc_kernel<<<grid, UT_THREADS, smem_bytes, st>>>(g);
+        update_tc_kernel<<<grid, UT_THREADS, smem_bytes, st>>>(tm_a, tm_b, g);
         HSES_LAUNCH_CHECK();
     }
     size_t len = (size_t)a * b;
