@@ -536,16 +536,12 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         if (lane == 0) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
     };
     auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
-        float f[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-        uint32_t hb[4], lb[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            __half h = __float2half_rn(f[j]);
-            hb[j] = __half_as_ushort(h);
-            lb[j] = __half_as_ushort(__float2half_rn(f[j] - __half2float(h)));
-        }
-        h2 = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
-        l2 = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+        const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
+        const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+        const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+        const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
+        h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
     };
     if (n4 <= 256) {
         // rows of up to 1024 values stay in registers between the maximum and the conversion, and a
