@@ -106,7 +106,8 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
         odd_s[tid] = (int)((g.first_thread + m_lo + rr / g.bm) & 1);
     }
     // rows this pair does not have read as zero (the copies never write them)
-    for (int i = tid; i < PP_STAGES * RMAX * xp; i += PP_THREADS) xs[i] = 0.0f;
+    if (rows < RMAX)
+        for (int i = tid; i < PP_STAGES * RMAX * xp; i += PP_THREADS) xs[i] = 0.0f;
     const float* Bp = g.B + (size_t)blockIdx.x * k * rank;
     const float* Ap = g.A + (size_t)blockIdx.x * a * rank;
     const int chunks = (k + kc - 1) / kc;
