@@ -1,5 +1,5 @@
 // Perturbed linear layer for populations whose antithetic pairs own only a few rows but
-// carry wide factors (one sample per member, rank 64..128: BASELINE's large-population
+// carry wide factors (one sample per member, rank 64..128: the large-population
 // configuration of do_mm, hyperscalees-noiser/src/eggroll.rs:419-446).
 //
 // With two members * bm * t_steps <= 32 rows per pair, the rank-r correction of a pair reads

@@ -167,7 +167,7 @@ def test_composite_eval_shards_like_a_whole_population(hs):
 
 
 def test_config0_full_size_properties(hs, oracle):
-    """BASELINE config 0 at full size (MLP 784-128-128-128-10, N = 256 members, 64 samples each,
+    """The small full-network configuration at full size (MLP 784-128-128-128-10, N = 256 members, 64 samples each,
     T = 8, rank 4, sigma 0.02): the step is deterministic, a subset of members matches the oracle,
     two half-population shards reproduce the whole, and the update moves every layer."""
     from hyperscalees_b200 import models, noiser
