@@ -11,7 +11,7 @@
 //                    accumulator buffers so the epilogue overlaps the next 256-column chunk
 //       warps 2-9    epilogue, two per TMEM quadrant: TMEM -> registers, undo the operand
 //                    scales, add t·(±s·A)ᵀ from the staged A rows, LIF step, store spikes
-//       warps 10-21  noise generators, three per quadrant: regenerate the A rows of the
+//       warps 10-25  noise generators, up to four per quadrant: regenerate the A rows of the
 //                    quadrant's antithetic pair into a shared-memory ring, ahead of the MMAs
 // Three fp16 passes on scaled hi/lo operands make every product fp32-equivalent (2^-21
 // relative residue); a single pass would break the spike tolerance.  No TMA multicast and no
@@ -33,8 +33,9 @@ using namespace tc;
 
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
 constexpr int BK = 64;            // fp16 elements per k-block = one 128 B swizzle row
-// warps: 0 TMA, 1 MMA, 2-9 epilogue (two per TMEM quadrant), 10-21 noise generators
-constexpr int NTHREADS = 704;
+// warps: 0 TMA, 1 MMA, 2-9 epilogue (two per TMEM quadrant), 10-25 noise generators
+constexpr int MAX_DEPTH = 4;       // ring slots (= generator warps) per TMEM quadrant, at most
+constexpr int NTHREADS = 32 * (10 + 4 * MAX_DEPTH);
 constexpr int EPI_WARP0 = 2;
 constexpr int GEN_WARP0 = 10;
 
@@ -66,7 +67,7 @@ struct TcArgs {
     const float* cache_a; // cached raw A rows (pair, a, rank) from the call's first pair on, or NULL
     LibmCal cal;
     int* status;
-    int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..3
+    int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..MAX_DEPTH
     unsigned long long* dbg;  // optional cycle counters of block 0 (role breakdown), or NULL
 };
 
@@ -76,8 +77,8 @@ struct TcSmem {
     static constexpr int X_BYTES = BM_TILE * BK * 2;
     static constexpr int W_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
-    static constexpr int HOP_BYTES = kJumpWords * 8;
-    static constexpr int TAB_BYTES = 1024 + 2 * 1024;  // log helper table + two threshold tables
+    static constexpr int HOP_BYTES = 0;     // the hop table and the filter thresholds are read through L1:
+    static constexpr int TAB_BYTES = 1024;  // only the logarithm's helper table is copied to shared memory
     static constexpr int BAR_BYTES = 384;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
@@ -98,9 +99,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* stage_base = smem;
-    uint64_t* hop_s = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
     double2* log_tab_s = reinterpret_cast<double2*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES);
-    uint32_t* delta_s = reinterpret_cast<uint32_t*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + 1024);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES);
     float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES +
                                               S::BAR_BYTES);
@@ -109,9 +108,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     uint64_t* empty = bars + 2 * S::STAGES;  // [STAGES] MMAs finished reading the stage
     uint64_t* tfull = bars + 3 * S::STAGES;  // [2] accumulator ready
     uint64_t* tempty = tfull + 2;            // [2] accumulator drained
-    uint64_t* afull = tempty + 2;            // [4][3] ring slot staged
-    uint64_t* aempty = afull + 12;           // [4][3] ring slot consumed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aempty + 12);
+    uint64_t* afull = tempty + 2;                     // [4][MAX_DEPTH] ring slot staged
+    uint64_t* aempty = afull + 4 * MAX_DEPTH;         // [4][MAX_DEPTH] ring slot consumed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aempty + 4 * MAX_DEPTH);
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
 
@@ -131,7 +130,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             mbar_init(&tfull[b], 1);
             mbar_init(&tempty[b], 256);
         }
-        for (int i = 0; i < 12; ++i) {
+        for (int i = 0; i < 4 * MAX_DEPTH; ++i) {
             mbar_init(&afull[i], 32);
             mbar_init(&aempty[i], 64);
         }
@@ -139,13 +138,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     }
     // small read-only tables go to shared memory: the epilogue's noise regeneration
     // looks them up for every normal
-    for (int i = threadIdx.x; i < kJumpWords; i += NTHREADS) hop_s[i] = g.hop ? g.hop[i] : 0ull;
     if (RG > 0) {
         for (int i = threadIdx.x; i < 64; i += NTHREADS) log_tab_s[i] = g.cal.log_tab[i];
-        for (int i = threadIdx.x; i < 256; i += NTHREADS) {
-            delta_s[i] = g.cal.log_delta[i];
-            delta_s[256 + i] = g.cal.cos_delta[i];
-        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -282,7 +276,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         // uses of this slot so far: (blocks_per_tile - slot + depth - 1) / depth per finished tile
                         uint32_t u = (uint32_t)tile_no * (uint32_t)((blocks_per_tile - slot + depth - 1) / depth) +
                                      (uint32_t)(blk / depth);
-                        if (!mbar_wait(&afull[q4 * 3 + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
+                        if (!mbar_wait(&afull[q4 * MAX_DEPTH + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
                         my_a = a_stage + (q4 * depth + slot) * 32 * RANK;
                     }
                     if (warp == EPI_WARP0) tick(8, t2);
@@ -339,7 +333,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         }
                     }
                     if (RG > 0) {
-                        mbar_arrive(&aempty[q4 * 3 + slot]);  // 64 arrivals (both warps) hand the slot back
+                        mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // 64 arrivals (both warps) hand the slot back
                     }
                     if (warp == EPI_WARP0) tick(9, t2);
                 }
@@ -358,8 +352,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         float* slot_a = a_stage + (gq * depth + gi) * 32 * RANK;
         LibmCal cal = g.cal;
         cal.log_tab = log_tab_s;
-        cal.log_delta = delta_s;
-        cal.cos_delta = delta_s + 256;
         const int blocks_per_tile = g.a / 32;
         const int sw = a_swizzle<RG>(lane);
         uint32_t used = 0;
@@ -375,21 +367,21 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     float4 v[RG > 0 ? RG : 1];
 #pragma unroll
                     for (int q = 0; q < RG; ++q) v[q] = __ldg(reinterpret_cast<const float4*>(src) + q);
-                    if (!mbar_wait(&aempty[gq * 3 + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
+                    if (!mbar_wait(&aempty[gq * MAX_DEPTH + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
 #pragma unroll
                     for (int q = 0; q < RG; ++q)
                         *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
                             make_float4(__fmul_rn(v[q].x, g.base_sigma), __fmul_rn(v[q].y, g.base_sigma),
                                         __fmul_rn(v[q].z, g.base_sigma), __fmul_rn(v[q].w, g.base_sigma));
                     src += (size_t)depth * 32 * RANK;
-                    mbar_arrive(&afull[gq * 3 + gi]);
+                    mbar_arrive(&afull[gq * MAX_DEPTH + gi]);
                 }
                 continue;
             }
             uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
             uint64_t a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)RANK * (uint64_t)(g.k + gi * 32 + lane));
             for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
-                if (!mbar_wait(&aempty[gq * 3 + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
+                if (!mbar_wait(&aempty[gq * MAX_DEPTH + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
 #pragma unroll 1
                 for (int q = 0; q < RG; ++q) {
                     float z[4];
@@ -398,8 +390,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
                                     __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));
                 }
-                a_state = jump_apply(hop_s, a_state);  // on to this generator's next block of rows
-                mbar_arrive(&afull[gq * 3 + gi]);      // 32 arrivals publish the slot
+                a_state = jump_apply(g.hop, a_state);  // on to this generator's next block of rows
+                mbar_arrive(&afull[gq * MAX_DEPTH + gi]);      // 32 arrivals publish the slot
             }
         }
     }
@@ -763,8 +755,8 @@ int launch_tc_rg(hses_ctx* ctx, cudaStream_t st, const CUtensorMap& tm_x, const 
 
 template <int BN>
 int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, TcArgs ta) {
-    // as many ring slots (and generator warps) per quadrant as shared memory allows, at most three
-    ta.ring_depth = 3;
+    // as many ring slots (and generator warps) per quadrant as shared memory allows, at most MAX_DEPTH
+    ta.ring_depth = MAX_DEPTH;
     while (ta.ring_depth > 1 && TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(ta.ring_depth, ta.rank) > TcSmem<BN>::LIMIT)
         --ta.ring_depth;
     if (g.perturb) {
