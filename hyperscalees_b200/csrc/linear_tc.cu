@@ -64,6 +64,7 @@ struct TcArgs {
     float* pot;
     const uint64_t* pow2; // T^(2^k) tables
     const uint64_t* hop;  // T^(2*rank*(32*ring_depth - 1))
+    const int* x_lo_flag; // 0 when every lo half of the split x is zero (x exactly representable in fp16)
     const float* cache_a; // cached raw A rows (pair, a, rank) from the call's first pair on, or NULL
     LibmCal cal;
     int* status;
@@ -163,6 +164,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            // inputs that are exact in fp16 (0/1 spikes, small integers) have an all-zero lo half:
+            // its tiles are neither loaded nor multiplied
+            const bool skip_xlo = *g.x_lo_flag == 0;
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c) {
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -172,9 +176,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
                         tick(0, t0);
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
-                        mbar_expect_tx(&full[s], 2 * S::X_BYTES + 2 * S::W_BYTES);
+                        mbar_expect_tx(&full[s], (skip_xlo ? 1 : 2) * S::X_BYTES + 2 * S::W_BYTES);
                         tma_load_2d(st, &tm_xhi, kb * BK, mt * BM_TILE, &full[s]);
-                        tma_load_2d(st + S::X_BYTES, &tm_xlo, kb * BK, mt * BM_TILE, &full[s]);
+                        if (!skip_xlo) tma_load_2d(st + S::X_BYTES, &tm_xlo, kb * BK, mt * BM_TILE, &full[s]);
                         tma_load_2d(st + 2 * S::X_BYTES, &tm_whi, kb * BK, c * BN, &full[s]);
                         tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
                     }
@@ -196,6 +200,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             const uint32_t idesc = make_idesc(BN);
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
+            const bool skip_xlo = *g.x_lo_flag == 0;
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                     int b = acc_it & 1;
@@ -218,8 +223,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 #pragma unroll
                         for (int ks = 0; ks < BK / 16; ++ks) {
                             uint64_t off = (uint64_t)(ks * 32 >> 4);  // 16 fp16 = 32 B along K
-                            umma_f16(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
-                            umma_f16(d, dxh + off, dwl + off, idesc, 1);
+                            if (!skip_xlo) umma_f16(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
+                            umma_f16(d, dxh + off, dwl + off, idesc, skip_xlo ? (uint32_t)((kb | ks) != 0) : 1u);
                             umma_f16(d, dxh + off, dwh + off, idesc, 1);
                         }
                         umma_commit(&empty[s]);
@@ -414,7 +419,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 // in the epilogue.  One warp per row; rows are multiples of four long and 16-byte aligned.
 __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t stride,
                                       __half* __restrict__ hi, __half* __restrict__ lo,
-                                      float* __restrict__ inv_scale) {
+                                      float* __restrict__ inv_scale, int* __restrict__ lo_flag) {
     int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (r >= rows) return;
@@ -436,6 +441,7 @@ __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows,
     if (lane == 0) inv_scale[r] = __uint_as_float((uint32_t)(127 - e) << 23);
     uint2* dh = reinterpret_cast<uint2*>(hi + (size_t)r * k);
     uint2* dl = reinterpret_cast<uint2*>(lo + (size_t)r * k);
+    uint32_t nz = 0;
     for (int i = lane; i < n4; i += 32) {
         float4 v = src[i];
         float f[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
@@ -447,9 +453,14 @@ __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows,
         }
         dh[i] = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16),
                            (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
-        dl[i] = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
-                           (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+        const uint2 lw = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
+                                    (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+        dl[i] = lw;
+        nz |= (lw.x | lw.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     }
+    // one flag per call tells the GEMM whether any lo half is non-zero (checked first: a set flag is not set again)
+    if (lo_flag != nullptr && __any_sync(0xffffffffu, nz != 0) && lane == 0 && *reinterpret_cast<volatile int*>(lo_flag) == 0)
+        atomicOr(lo_flag, 1);
 }
 
 // t[R, q] = sum_k x[R, k] * B_pair[k, q].  CTA (pair, chunk) takes up to LT_ROWS of the pair's rows
@@ -477,7 +488,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                  uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
                  int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                  __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
-                 const float* __restrict__ cache_b) {
+                 const float* __restrict__ cache_b, int* __restrict__ lo_flag) {
     constexpr int RANK = RANK_G * 4;
     constexpr int KQ = 32 / RANK_G;   // lanes along k
     constexpr int KSTEP = 4 * KQ;     // k covered by one pass of a warp
@@ -517,6 +528,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
 
     // ---- operand split of this CTA's x rows (one warp per row) ----
     const int n4 = k >> 2;
+    uint32_t lo_nz = 0;  // any non-zero lo half written by this thread
     auto finish_row = [&](int64_t R, float m, float& sc) {
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
@@ -534,6 +546,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
         h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
         l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     };
     if (n4 <= 256) {
         // rows of up to 1024 values stay in registers between the maximum and the conversion, and a
@@ -601,6 +614,10 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
             }
         }
     }
+
+    // one flag per call tells the GEMM whether any lo half is non-zero (a set flag is not set again)
+    if (__any_sync(0xffffffffu, lo_nz != 0) && lane == 0 && *reinterpret_cast<volatile int*>(lo_flag) == 0)
+        atomicOr(lo_flag, 1);
 
     // ---- t = x * B ----
     const int n_tiles = (total_rows + 7) >> 3;                     // 1..8
@@ -722,6 +739,7 @@ __device__ unsigned long long g_tc_dbg[16];
 struct TcScratch {
     __half *xhi, *xlo, *whi, *wlo;
     float *rs, *cs, *t;
+    int* lo_flag;  // set by the x split when a lo half is non-zero
     size_t bytes;
 };
 TcScratch tc_scratch(const hses_linear_args& g, void* base) {
@@ -737,7 +755,8 @@ TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     s.rs = reinterpret_cast<float*>(s.wlo + nw);
     s.cs = s.rs + up(rows);
     s.t = s.cs + up((size_t)g.a);
-    s.bytes = (2 * nx + 2 * nw) * sizeof(__half) + (up(rows) + up((size_t)g.a) + nt) * sizeof(float);
+    s.lo_flag = reinterpret_cast<int*>(s.t + nt);
+    s.bytes = (2 * nx + 2 * nw) * sizeof(__half) + (up(rows) + up((size_t)g.a) + nt + 64) * sizeof(float);
     return s;
 }
 
@@ -814,16 +833,17 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= sc.bytes && aligned16(g.workspace),
                  "workspace too small or misaligned; see hses_perturbed_linear_workspace_bytes");
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
+    HSES_CUDA(cudaMemsetAsync(sc.lo_flag, 0, sizeof(int), st));
     {
         HSES_KERNEL(ctx, st, "split_w");
         split_f16_rows_kernel<<<(unsigned)((g.a + 7) / 8), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
-                                                                        sc.whi, sc.wlo, sc.cs);
+                                                                        sc.whi, sc.wlo, sc.cs, nullptr);
         HSES_LAUNCH_CHECK();
     }
     if (!g.perturb) {  // with noise the pair kernel below splits x while it computes t
         HSES_KERNEL(ctx, st, "split_x");
         split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
-                                                                         sc.xlo, sc.rs);
+                                                                         sc.xlo, sc.rs, sc.lo_flag);
         HSES_LAUNCH_CHECK();
     }
     TcArgs ta{};
@@ -860,6 +880,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         if (crc != HSES_OK) return crc;
     }
     ta.cache_a = cache_a;
+    ta.x_lo_flag = sc.lo_flag;
     if (getenv("HSES_TC_DEBUG")) {
         void* p = nullptr;
         HSES_CUDA(cudaGetSymbolAddress(&p, g_tc_dbg));
@@ -875,7 +896,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
 #define HSES_LT(RG)                                                                                          \
     lowrank_t_kernel<RG><<<lt_grid, LT_THREADS, 0, st>>>(                                            \
         ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
-        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b)
+        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
         switch (g.rank / 4) {
             case 1: HSES_LT(1); break;

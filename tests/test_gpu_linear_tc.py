@@ -127,3 +127,23 @@ def test_host_pipeline_equals_single_call(hs):
     want = ops.perturbed_linear(x.cuda(), w, n_pop=n_pop, bm=bm, first_thread=6, **kw).cpu()
     assert torch.equal(out, want)
     status_ok()
+
+
+@pytest.mark.parametrize("perturb", [False, True])
+def test_tensor_path_with_inputs_exact_in_fp16(hs, oracle, perturb):
+    """0/1 spike inputs have an all-zero lo half: the kernel drops that pass.  The result must
+    equal the general path's to fp32 rounding, and switching back to inputs with a non-zero lo
+    half in the next call must bring the pass back."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(12)
+    n_pop, bm, k, a, rank = 8, 16, 256, 256, 16
+    spikes = (g.random((n_pop, bm, k)) < 0.2).astype(np.float32)
+    dense = g.standard_normal((n_pop, bm, k)).astype(np.float32)
+    w = (g.standard_normal((a, k)) / np.sqrt(k)).astype(np.float32)
+    kw = dict(n_pop=n_pop, bm=bm, sigma=0.5, rank=rank, key=KEY, perturb=perturb)
+    for x in (spikes, dense, spikes):
+        got = ops.perturbed_linear(dev(x), dev(w), algo=ops.ALGO_TENSOR, **kw)
+        ref = ops.perturbed_linear(dev(x), dev(w), algo=ops.ALGO_SIMT, **kw)
+        scale = max(ref.abs().max().item(), 1.0)
+        assert (got - ref).abs().max().item() <= 2e-5 * scale
+    status_ok()
