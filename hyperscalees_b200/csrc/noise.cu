@@ -68,7 +68,7 @@ __global__ void dense_noise_kernel(LibmCal cal, const uint64_t* __restrict__ pow
 // Dense-leaf update: block c owns elements [c*kChunk, (c+1)*kChunk); its
 // threads stride over the antithetic pairs, then reduce in a fixed order so
 // that every rank obtains the same bits.
-constexpr int kDenseThreads = 256;
+constexpr int kDenseThreads = 1024;  // few blocks (one per chunk of a leaf): all the parallelism is in the block
 __global__ void es_update_dense_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, uint64_t key,
                                        int32_t true_epoch, int32_t first_pair, int64_t n_pairs,
                                        int len, float sigma, float out_scale,
