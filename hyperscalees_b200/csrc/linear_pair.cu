@@ -107,7 +107,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
     }
     // rows this pair does not have read as zero (the copies never write them)
     if (rows < RMAX)
-        for (int i = tid; i < PP_STAGES * RMAX * xp; i += PP_THREADS) xs[i] = 0.0f;
+        for (int i = tid; i < PP_STAGES * RMAX * xp; i += (int)blockDim.x) xs[i] = 0.0f;
     const float* Bp = g.B + (size_t)blockIdx.x * k * rank;
     const float* Ap = g.A + (size_t)blockIdx.x * a * rank;
     const int chunks = (k + kc - 1) / kc;
@@ -204,7 +204,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
         }
     }
     __syncthreads();
-    for (int e = tid; e < RMAX * rank; e += PP_THREADS) {
+    for (int e = tid; e < RMAX * rank; e += (int)blockDim.x) {
         float sum = red[e];
         for (int p = 1; p < kslices; ++p) sum += red[(size_t)p * RMAX * rank + e];
         red[e] = sum;  // t[r][q], r = e / rank
@@ -233,7 +233,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
     const float gain = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
     const int nq4 = rank / 4;
     const int ngroups = (a + NC - 1) / NC;
-    for (int item = tid; item < ngroups * RG4; item += PP_THREADS) {
+    for (int item = tid; item < ngroups * RG4; item += (int)blockDim.x) {
         const int ng = item / RG4, prg = item - ng * RG4;
         const int n0 = ng * NC;
         float u[4][NC], base[4][NC];
@@ -306,8 +306,12 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
 
 // k-slices of a pass: as many as the block has threads for, at most 64 (a pass is at most 256
 // columns, the limit of a TMA box)
+// threads per CTA: the 8-row tile (a pair with at most 8 rows, e.g. the readout of one sample per
+// member) has too little work for 256 threads (measured: 0.25 ms with 128 threads, 0.33 ms with 256)
+int threads_of(int rmax) { return rmax == 8 ? 128 : PP_THREADS; }
 int kslices_of(int rmax, int rank) {
-    int ks = PP_THREADS / ((rmax / 8) * (rank / 8));
+    int ks = threads_of(rmax) / ((rmax / 8) * (rank / 8));
+    if (ks < 1) ks = 1;
     return ks > 64 ? 64 : ks;
 }
 // rows of B per pass: a multiple of 4 * kslices (every slice does the same number of steps),
@@ -447,15 +451,15 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         switch (rmax) {
             case 8:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<8><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<8><<<(unsigned)n_pairs, threads_of(8), smem, st>>>(tm_x, pa);
                 break;
             case 16:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<16><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<16><<<(unsigned)n_pairs, threads_of(16), smem, st>>>(tm_x, pa);
                 break;
             default:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<32><<<(unsigned)n_pairs, PP_THREADS, smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<32><<<(unsigned)n_pairs, threads_of(32), smem, st>>>(tm_x, pa);
                 break;
         }
         HSES_LAUNCH_CHECK();
