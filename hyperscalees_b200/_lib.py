@@ -29,6 +29,7 @@ EXPORTS = [
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
+    "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square",
 ]
 
 
@@ -151,6 +152,10 @@ def load():
                                          vp, sz]
     L.hses_convert_fitnesses_bs.argtypes = [vp, vp, vp, i64, i32, vp, vp]
     L.hses_vector_mul.argtypes = [vp, vp, vp, vp, vp, i64]
+    L.hses_layer_norm.argtypes = [vp, vp, vp, i64, i32, vp, vp, f32, vp]
+    L.hses_group_norm.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp, vp, f32, vp]
+    L.hses_token_shift_mix.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, vp]
+    L.hses_relu_square.argtypes = [vp, vp, vp, i64, vp]
     L.hses_population_grads_elems.restype = sz
     L.hses_population_grads_elems.argtypes = [pm]
     L.hses_population_grads.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64, i32, i64, vp, vp, sz]

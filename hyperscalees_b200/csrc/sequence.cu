@@ -125,6 +125,62 @@ __global__ void spiking_attention_kernel(const float* __restrict__ Q, const floa
     }
 }
 
+// ---------------------------------------------------------------------------
+// RWKV-7 block pieces around the recurrence (hyperscalees-models/src/llm.rs:64-213)
+// ---------------------------------------------------------------------------
+
+// Statistics of `cnt` contiguous values per (row, group): one warp per group.
+// layer_norm is the case of one group per row; var = E[x^2] - E[x]^2 as in the reference.
+__global__ void group_stats_norm_kernel(const float* __restrict__ x, int64_t n_groups_total, int groups, int inner,
+                                        int l, const float* __restrict__ weight, const float* __restrict__ bias,
+                                        float eps, float* __restrict__ out) {
+    int64_t gidx = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    int lane = threadIdx.x & 31;
+    if (gidx >= n_groups_total) return;
+    const int64_t cnt = (int64_t)inner * l;
+    const float* xg = x + (size_t)gidx * cnt;
+    float sum = 0.0f, sumsq = 0.0f;
+    for (int64_t j = lane; j < cnt; j += 32) {
+        float v = xg[j];
+        sum += v;
+        sumsq = fmaf(v, v, sumsq);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        sumsq += __shfl_xor_sync(0xffffffffu, sumsq, off);
+    }
+    const float mean = __fdiv_rn(sum, (float)cnt);
+    const float var = __fsub_rn(__fdiv_rn(sumsq, (float)cnt), __fmul_rn(mean, mean));
+    const float sd = __fsqrt_rn(__fadd_rn(var, eps));
+    const int g = (int)(gidx % groups);
+    float* og = out + (size_t)gidx * cnt;
+    for (int64_t j = lane; j < cnt; j += 32) {
+        int ch = g * inner + (int)(j / l);
+        float nv = __fdiv_rn(__fsub_rn(xg[j], mean), sd);
+        og[j] = __fadd_rn(__fmul_rn(nv, weight[ch]), bias[ch]);
+    }
+}
+
+// out = x + (prev - x) * coef with prev = the previous row (row 0: state), 0 at new starts
+__global__ void token_shift_mix_kernel(const float* __restrict__ x, int T, int c, const float* __restrict__ state,
+                                       const uint8_t* __restrict__ new_starts, const float* __restrict__ coef,
+                                       float* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)T * c) return;
+    int t = (int)(i / c), j = (int)(i - (int64_t)t * c);
+    float prev = t == 0 ? state[j] : x[i - c];
+    if (new_starts && new_starts[t]) prev = 0.0f;
+    float xv = x[i];
+    out[i] = __fadd_rn(xv, __fmul_rn(__fsub_rn(prev, xv), coef[j]));
+}
+
+__global__ void relu_square_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i] > 0.0f ? x[i] : 0.0f;
+    out[i] = __fmul_rn(v, v);
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -172,5 +228,59 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
+
+int hses_layer_norm(hses_ctx* ctx, hses_stream stream, const float* x, int64_t rows, int32_t c,
+                    const float* weight, const float* bias, float eps, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(rows >= 0 && c >= 1, "bad shape");
+    if (rows == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && weight != nullptr && bias != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "layer_norm");
+    group_stats_norm_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, as_stream(stream)>>>(x, rows, 1, c, 1, weight, bias,
+                                                                                      eps, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_group_norm(hses_ctx* ctx, hses_stream stream, const float* x, int64_t n, int32_t c, int32_t l,
+                    int32_t groups, const float* weight, const float* bias, float eps, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 0 && c >= 1 && l >= 1 && groups >= 1 && c % groups == 0, "bad shape");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && weight != nullptr && bias != nullptr && out != nullptr, "NULL pointer");
+    int64_t total = n * groups;
+    HSES_KERNEL(ctx, as_stream(stream), "group_norm");
+    group_stats_norm_kernel<<<(unsigned)((total + 7) / 8), 256, 0, as_stream(stream)>>>(x, total, groups, c / groups, l,
+                                                                                       weight, bias, eps, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x, int32_t T, int32_t c,
+                         const float* state, const uint8_t* new_starts, const float* coef, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(T >= 0 && c >= 1, "bad shape");
+    if (T == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && state != nullptr && coef != nullptr && out != nullptr, "NULL pointer");
+    HSES_REQUIRE(x != out, "token_shift_mix cannot run in place");
+    int64_t n = (int64_t)T * c;
+    HSES_KERNEL(ctx, as_stream(stream), "token_shift_mix");
+    token_shift_mix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state, new_starts, coef,
+                                                                                      out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x, int64_t n, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 0, "n must be >= 0");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "relu_square");
+    relu_square_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, n, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
 
 }  // extern "C"

@@ -296,3 +296,27 @@ class PopulationStep:
             self.frozen.noise_reuse, self.frozen.group_size, int(self.frozen.freeze_nonlora),
             C.c_uint64(gk & ((1 << 64) - 1)), raw_fitness.data_ptr(), n_total, C.byref(desc),
             self.noiser.opt_state.step, pp, mp, vp, ws.data_ptr(), need))
+
+
+class ChannelMixing:
+    """RWKV-7 ChannelMixing (hyperscalees-models/src/llm.rs:177-213): token shift with the
+    per-channel strength x_k, key projection, relu^2, value projection; bias-free Linear layers
+    (x @ W^T).  With `noise` = (noiser, frozen, params, base keys, iterinfo) the two projections
+    go through the noiser's do_mm, i.e. they carry the member's rank-r perturbation like every
+    MM weight of the reference's JAX model."""
+
+    def __init__(self, x_k: torch.Tensor, key_weight: torch.Tensor, value_weight: torch.Tensor):
+        self.x_k, self.key_weight, self.value_weight = x_k, key_weight, value_weight
+
+    def forward(self, x: torch.Tensor, state: torch.Tensor, length: int,
+                new_starts: Optional[torch.Tensor] = None, noise=None):
+        xk = ops.token_shift_mix(x, state, self.x_k, new_starts)
+        if noise is None:
+            k = ops.perturbed_linear(xk, self.key_weight, n_pop=1, bm=xk.shape[0], perturb=False)
+            k = ops.relu_square(k)
+            out = ops.perturbed_linear(k, self.value_weight, n_pop=1, bm=k.shape[0], perturb=False)
+        else:
+            nz, frozen, params, keys, info = noise
+            k = ops.relu_square(nz.do_mm(frozen, params, self.key_weight, keys[0], info, xk))
+            out = nz.do_mm(frozen, params, self.value_weight, keys[1], info, k)
+        return out, x[length - 1:length].clone()

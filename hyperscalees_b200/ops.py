@@ -469,3 +469,59 @@ def spiking_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: 
                                                   tokens, heads, width // heads, width, mode, beta, tau_m, v_th,
                                                   g_inh, n_iter, _ptr(O), _ptr(A)))
     return (O, A) if want_weights else O
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """llm.rs:64-84: normalise the last axis (var = E[x^2] - E[x]^2), then weight and bias."""
+    _check(x, "x")
+    x = x.contiguous()
+    c = x.shape[-1]
+    out = torch.empty_like(x)
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_layer_norm(ctx.handle, current_stream(), _ptr(x), x.numel() // c, c,
+                                           _ptr(weight.contiguous()), _ptr(bias.contiguous()), eps, _ptr(out)))
+    return out
+
+
+def group_norm(x: torch.Tensor, groups: int, weight: torch.Tensor, bias: torch.Tensor,
+               eps: float = 1e-5) -> torch.Tensor:
+    """GroupNorm.forward, llm.rs:90-145: x (n, c) or (n, c, l)."""
+    _check(x, "x")
+    if x.ndim not in (2, 3):
+        raise ValueError("GroupNorm rank unsupported")
+    x = x.contiguous()
+    n, c = x.shape[0], x.shape[1]
+    l = x.shape[2] if x.ndim == 3 else 1
+    if c % groups:
+        raise ValueError("channels must be a multiple of the group count")
+    out = torch.empty_like(x)
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_group_norm(ctx.handle, current_stream(), _ptr(x), n, c, l, groups,
+                                           _ptr(weight.contiguous()), _ptr(bias.contiguous()), eps, _ptr(out)))
+    return out
+
+
+def token_shift_mix(x: torch.Tensor, state: torch.Tensor, coef: torch.Tensor,
+                    new_starts: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x + (prev - x) * coef with prev the previous row (row 0: state), 0 at new starts."""
+    _check(x, "x", ndim=2)
+    x = x.contiguous()
+    T, c = x.shape
+    out = torch.empty_like(x)
+    ns = None
+    if new_starts is not None:
+        ns = new_starts.to(device=x.device, dtype=torch.uint8).contiguous()
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_token_shift_mix(ctx.handle, current_stream(), _ptr(x), T, c,
+                                                _ptr(state.contiguous().view(-1)), _ptr(ns),
+                                                _ptr(coef.contiguous().view(-1)), _ptr(out)))
+    return out
+
+
+def relu_square(x: torch.Tensor) -> torch.Tensor:
+    _check(x, "x")
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_relu_square(ctx.handle, current_stream(), _ptr(x), x.numel(), _ptr(out)))
+    return out

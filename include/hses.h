@@ -436,6 +436,28 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
                            int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
                            float* O, float* A_out /*device or NULL*/);
 
+/* ---- RWKV-7 block pieces around the recurrence, hyperscalees-models/src/llm.rs:64-213.
+ *      layer_norm (64-84): per row of c values, var = E[x^2] - E[x]^2, then weight and bias.
+ *      GroupNorm::forward (90-145): x (n, c, l) dense (l = 1 for the rank-2 form), statistics
+ *      over the (c / groups) * l values of a group, gamma and beta per channel.
+ *      token_shift_mix (192-206, and the same step of TimeMixing): out = x + (prev - x) * coef
+ *      with prev the previous row (row 0: the carried state, c values) and 0 where new_starts
+ *      (T bytes or NULL) marks the start of a sequence; not in place.
+ *      relu_square: k = relu(x)^2 of ChannelMixing (208).  ChannelMixing::forward is
+ *      token_shift_mix -> hses_perturbed_linear (key) -> relu_square -> hses_perturbed_linear
+ *      (value); the new state is row length-1 of x. ------------------------------------- */
+int hses_layer_norm(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t rows,
+                    int32_t c, const float* weight, const float* bias, float eps, float* out);
+int hses_group_norm(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t n, int32_t c,
+                    int32_t l, int32_t groups, const float* weight, const float* bias, float eps,
+                    float* out);
+int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x /*device (T,c)*/, int32_t T,
+                         int32_t c, const float* state /*device (c)*/,
+                         const uint8_t* new_starts /*device or NULL*/, const float* coef /*device (c)*/,
+                         float* out /*device (T,c)*/);
+int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t n,
+                     float* out /*device*/);
+
 #ifdef __cplusplus
 }
 #endif

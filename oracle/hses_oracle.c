@@ -730,3 +730,81 @@ void hso_spiking_attention(const float *Q, const float *K, const float *V, int t
     }
     free(row);
 }
+
+/* ------------------------------------------------------------------------ */
+/* RWKV-7 block pieces around the WKV recurrence                             */
+/* ------------------------------------------------------------------------ */
+
+/* layer_norm, hyperscalees-models/src/llm.rs:64-84: per row over the last axis,
+ * var = E[x^2] - E[x]^2, (x - mean) / sqrt(var + eps) * weight + bias. */
+void hso_layer_norm(const float *x, size_t rows, int c, const float *weight, const float *bias,
+                    float eps, float *out) {
+    for (size_t r = 0; r < rows; ++r) {
+        const float *xr = x + r * (size_t)c;
+        float sum = 0.0f, sumsq = 0.0f;
+        for (int j = 0; j < c; ++j) sum += xr[j];
+        for (int j = 0; j < c; ++j) sumsq += xr[j] * xr[j];
+        float mean = sum / (float)c;
+        float var = sumsq / (float)c - mean * mean;
+        float std = sqrtf(var + eps);
+        for (int j = 0; j < c; ++j) out[r * (size_t)c + j] = (xr[j] - mean) / std * weight[j] + bias[j];
+    }
+}
+
+/* GroupNorm::forward, llm.rs:90-145: x (n, c, l) (l = 1 for the rank-2 form), channels split
+ * into `groups`; statistics over the (c / groups) * l values of a group; gamma/beta per channel. */
+void hso_group_norm(const float *x, size_t n, int c, int l, int groups, const float *weight,
+                    const float *bias, float eps, float *out) {
+    int inner = c / groups;
+    size_t cnt = (size_t)inner * l;
+    for (size_t i = 0; i < n; ++i)
+        for (int g = 0; g < groups; ++g) {
+            const float *xg = x + (i * (size_t)c + (size_t)g * inner) * l;
+            float sum = 0.0f, sumsq = 0.0f;
+            for (size_t j = 0; j < cnt; ++j) sum += xg[j];
+            for (size_t j = 0; j < cnt; ++j) sumsq += xg[j] * xg[j];
+            float mean = sum / (float)cnt;
+            float var = sumsq / (float)cnt - mean * mean;
+            float std = sqrtf(var + eps);
+            for (int ch = 0; ch < inner; ++ch)
+                for (int t = 0; t < l; ++t) {
+                    size_t o = (i * (size_t)c + (size_t)g * inner + ch) * l + t;
+                    out[o] = weight[g * inner + ch] * ((x[o] - mean) / std) + bias[g * inner + ch];
+                }
+        }
+}
+
+/* The token shift of ChannelMixing / TimeMixing, llm.rs:192-206: sx = previous row (row 0: the
+ * carried state), zero where a new sequence starts, minus x; out = x + sx * coef. */
+void hso_token_shift_mix(const float *x, int T, int c, const float *state, const uint8_t *new_starts,
+                         const float *coef, float *out) {
+    for (int t = 0; t < T; ++t)
+        for (int j = 0; j < c; ++j) {
+            float prev = t == 0 ? state[j] : x[(size_t)(t - 1) * c + j];
+            if (new_starts && new_starts[t]) prev = 0.0f;
+            float sx = prev - x[(size_t)t * c + j];
+            out[(size_t)t * c + j] = x[(size_t)t * c + j] + sx * coef[j];
+        }
+}
+
+/* ChannelMixing::forward, llm.rs:192-213 with bias-free Linear layers (x @ W^T, common.rs:123-127):
+ * xk = token shift; k = relu(xk @ Wk^T)^2 (Wk: (f, c)); out = k @ Wv^T (Wv: (c, f));
+ * state_out = x[length - 1]. */
+void hso_channel_mix(const float *x, int T, int c, int f, const float *state, const uint8_t *new_starts,
+                     const float *x_k, const float *wk, const float *wv, int length, float *out,
+                     float *state_out) {
+    float *xk = (float *)malloc(sizeof(float) * (size_t)T * c);
+    float *k = (float *)malloc(sizeof(float) * (size_t)T * f);
+    hso_token_shift_mix(x, T, c, state, new_starts, x_k, xk);
+    for (int t = 0; t < T; ++t)
+        for (int j = 0; j < f; ++j) {
+            float d = dot_f32(xk + (size_t)t * c, wk + (size_t)j * c, c, 1, 1);
+            d = d > 0.0f ? d : 0.0f;
+            k[(size_t)t * f + j] = d * d;
+        }
+    for (int t = 0; t < T; ++t)
+        for (int j = 0; j < c; ++j) out[(size_t)t * c + j] = dot_f32(k + (size_t)t * f, wv + (size_t)j * f, f, 1, 1);
+    for (int j = 0; j < c; ++j) state_out[j] = x[(size_t)(length - 1) * c + j];
+    free(xk);
+    free(k);
+}

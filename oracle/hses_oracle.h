@@ -165,6 +165,15 @@ void hso_spiking_attention(const float *Q, const float *K, const float *V, int t
                            int mode, float beta, float tau_m, float v_th, float g_inh, int n_iter,
                            float *O, float *A);
 
+void hso_layer_norm(const float *x, size_t rows, int c, const float *weight, const float *bias,
+                    float eps, float *out);
+void hso_group_norm(const float *x, size_t n, int c, int l, int groups, const float *weight,
+                    const float *bias, float eps, float *out);
+void hso_token_shift_mix(const float *x, int T, int c, const float *state, const uint8_t *new_starts,
+                         const float *coef, float *out);
+void hso_channel_mix(const float *x, int T, int c, int f, const float *state, const uint8_t *new_starts,
+                     const float *x_k, const float *wk, const float *wv, int length, float *out,
+                     float *state_out);
 int hso_num_threads(void);
 
 #ifdef __cplusplus

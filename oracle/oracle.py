@@ -388,3 +388,44 @@ def spiking_attention(Q, K, V, mode=0, beta=1.0, tau_m=2.0, v_th=0.3, g_inh=0.5,
     lib().hso_spiking_attention(qp, kp, vp, tokens, d, mode, C.c_float(beta), C.c_float(tau_m), C.c_float(v_th),
                                 C.c_float(g_inh), n_iter, O.ctypes.data_as(_f32p), A.ctypes.data_as(_f32p))
     return O, A
+
+
+def layer_norm(x, weight, bias, eps=1e-5):
+    x, xp = _f(x); w, wp = _f(weight); b, bp = _f(bias)
+    c = x.shape[-1]
+    out = np.empty_like(x)
+    lib().hso_layer_norm(xp, C.c_size_t(x.size // c), c, wp, bp, C.c_float(eps), out.ctypes.data_as(_f32p))
+    return out
+
+
+def group_norm(x, groups, weight, bias, eps=1e-5):
+    """x (n, c) or (n, c, l)."""
+    x, xp = _f(x); w, wp = _f(weight); b, bp = _f(bias)
+    n, c = x.shape[0], x.shape[1]
+    l = x.shape[2] if x.ndim == 3 else 1
+    out = np.empty_like(x)
+    lib().hso_group_norm(xp, C.c_size_t(n), c, l, groups, wp, bp, C.c_float(eps), out.ctypes.data_as(_f32p))
+    return out
+
+
+def token_shift_mix(x, state, coef, new_starts=None):
+    x, xp = _f(x); st, sp = _f(state); cf, cp = _f(coef)
+    T, c = x.shape
+    ns = np.ascontiguousarray(new_starts, dtype=np.uint8) if new_starts is not None else None
+    out = np.empty_like(x)
+    lib().hso_token_shift_mix(xp, T, c, sp, ns.ctypes.data_as(_u8p) if ns is not None else None, cp,
+                              out.ctypes.data_as(_f32p))
+    return out
+
+
+def channel_mix(x, state, x_k, wk, wv, length, new_starts=None):
+    """ChannelMixing.forward: returns (out (T, c), state_out (c,))."""
+    x, xp = _f(x); st, sp = _f(state); xk, xkp = _f(x_k); wk, wkp = _f(wk); wv, wvp = _f(wv)
+    T, c = x.shape
+    f = wk.shape[0]
+    ns = np.ascontiguousarray(new_starts, dtype=np.uint8) if new_starts is not None else None
+    out = np.empty_like(x)
+    so = np.empty(c, dtype=np.float32)
+    lib().hso_channel_mix(xp, T, c, f, sp, ns.ctypes.data_as(_u8p) if ns is not None else None, xkp, wkp, wvp,
+                          length, out.ctypes.data_as(_f32p), so.ctypes.data_as(_f32p))
+    return out, so

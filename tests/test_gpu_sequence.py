@@ -72,3 +72,56 @@ def test_spiking_attention_matches_oracle(hs, oracle, mode, n_seq, tokens, heads
     if mode == 1:
         rows = A.sum(-1)
         assert ((np.abs(rows - 1.0) < 1e-4) | (rows == 0.0)).all()  # a row sums to one whenever any key fired
+
+
+def test_layer_and_group_norm_match_oracle():
+    """llm.rs:930-999 (hand-computed cases, via the oracle's pins) and random shapes."""
+    from hyperscalees_b200 import ops
+    from oracle import oracle
+    g = np.random.default_rng(3)
+    x = np.array([[1, 2, 3, 4], [10, 20, 30, 40]], dtype=np.float32)
+    w, b = np.array([2.0, 1.0, 0.5, 1.0], np.float32), np.array([1.0, 0.0, 0.5, -1.0], np.float32)
+    got = ops.layer_norm(dev(x), dev(w), dev(b)).cpu().numpy()
+    assert np.abs(got - np.array([[-1.6832, -0.4472, 0.7236, 0.3416]] * 2)).max() <= 1e-4
+    x = g.standard_normal((37, 768)).astype(np.float32) * 3 + 1
+    w, b = g.standard_normal(768).astype(np.float32), g.standard_normal(768).astype(np.float32)
+    assert np.allclose(ops.layer_norm(dev(x), dev(w), dev(b)).cpu().numpy(), oracle.layer_norm(x, w, b), rtol=1e-4, atol=1e-4)
+    # group norm: rank 3 (hand case) and the rank-2 form TimeMixing uses (groups = heads)
+    x3 = np.arange(1, 17, dtype=np.float32).reshape(2, 4, 2)
+    got = ops.group_norm(dev(x3), 2, dev(np.ones(4, np.float32)), dev(np.zeros(4, np.float32))).cpu().numpy()
+    assert np.abs(got.reshape(-1) - np.tile([-1.34164, -0.44721, 0.44721, 1.34164], 4)).max() <= 1e-4
+    x2 = g.standard_normal((50, 768)).astype(np.float32)
+    assert np.allclose(ops.group_norm(dev(x2), 12, dev(w), dev(b), eps=64e-5).cpu().numpy(),
+                       oracle.group_norm(x2, 12, w, b, eps=64e-5), rtol=1e-4, atol=1e-4)
+    x3 = g.standard_normal((5, 24, 7)).astype(np.float32)
+    w3, b3 = g.standard_normal(24).astype(np.float32), g.standard_normal(24).astype(np.float32)
+    assert np.allclose(ops.group_norm(dev(x3), 4, dev(w3), dev(b3)).cpu().numpy(), oracle.group_norm(x3, 4, w3, b3),
+                       rtol=1e-4, atol=1e-4)
+
+
+def test_channel_mixing_matches_oracle_and_reference_case():
+    """llm.rs:1003-1036 (T = 2, C = 1 hand case) and a random block with sequence restarts."""
+    from hyperscalees_b200 import models, ops
+    from oracle import oracle
+    cm = models.ChannelMixing(dev(np.array([2.0], np.float32)), dev(np.array([[1.0]], np.float32)),
+                              dev(np.array([[1.0]], np.float32)))
+    out, st = cm.forward(dev(np.array([[3.0], [5.0]], np.float32)), dev(np.array([[1.0]], np.float32)), 2,
+                         torch.tensor([0, 0]))
+    assert np.abs(out.cpu().numpy().reshape(-1) - np.array([0.0, 1.0])).max() <= 1e-4
+    assert abs(st.cpu().numpy().reshape(-1)[0] - 5.0) <= 1e-4
+    g = np.random.default_rng(8)
+    T, c, f = 33, 64, 256
+    x = g.standard_normal((T, c)).astype(np.float32)
+    state = g.standard_normal(c).astype(np.float32)
+    x_k = g.random(c).astype(np.float32)
+    wk = (g.standard_normal((f, c)) / np.sqrt(c)).astype(np.float32)
+    wv = (g.standard_normal((c, f)) / np.sqrt(f)).astype(np.float32)
+    ns = np.zeros(T, np.uint8); ns[[0, 9, 20]] = 1
+    cm = models.ChannelMixing(dev(x_k), dev(wk), dev(wv))
+    out, st = cm.forward(dev(x), dev(state), 30, torch.from_numpy(ns))
+    want, wst = oracle.channel_mix(x, state, x_k, wk, wv, 30, ns)
+    assert np.abs(out.cpu().numpy() - want).max() <= 1e-4 * max(np.abs(want).max(), 1.0)
+    assert np.array_equal(st.cpu().numpy().reshape(-1), wst)
+    # the token shift alone is exact
+    assert np.array_equal(ops.token_shift_mix(dev(x), dev(state), dev(x_k), torch.from_numpy(ns)).cpu().numpy(),
+                          oracle.token_shift_mix(x, state, x_k, ns))
