@@ -29,7 +29,7 @@ EXPORTS = [
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
-    "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square",
+    "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
 ]
 
 
@@ -156,6 +156,7 @@ def load():
     L.hses_group_norm.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp, vp, f32, vp]
     L.hses_token_shift_mix.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, vp]
     L.hses_relu_square.argtypes = [vp, vp, vp, i64, vp]
+    L.hses_rate_encode.argtypes = [vp, vp, vp, i64, f32, vp]
     L.hses_population_grads_elems.restype = sz
     L.hses_population_grads_elems.argtypes = [pm]
     L.hses_population_grads.argtypes = [vp, vp, pm, f32, i32, i32, i32, i32, i32, u64, vp, i64, i32, i64, vp, vp, sz]

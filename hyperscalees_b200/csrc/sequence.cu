@@ -115,6 +115,30 @@ __global__ void spiking_attention_kernel(const float* __restrict__ Q, const floa
         tot = __fadd_rn(tot, 1e-6f);
         for (int j = 0; j < tokens; ++j) hrow[j] = __fdiv_rn(cnt[j], tot);
     }
+    if (mode == 2) {
+        // continuous Hopfield relaxation then a stable softmax along the keys
+        // (hyperscalees-models/src/snn_transformer.rs:80-102)
+        const float one_over_tau = 1.0f / tau_m;
+        float u[kMaxTokens];
+        for (int j = 0; j < tokens; ++j) u[j] = hrow[j];
+        for (int it = 0; it < n_iter; ++it) {
+            float m = 0.0f;
+            for (int j = 0; j < tokens; ++j) m = __fadd_rn(m, u[j]);
+            m = __fdiv_rn(m, (float)tokens);
+            const float inh = __fmul_rn(m, g_inh);
+            for (int j = 0; j < tokens; ++j)
+                u[j] = __fadd_rn(u[j], __fmul_rn(__fsub_rn(__fadd_rn(-u[j], hrow[j]), inh), one_over_tau));
+        }
+        float mx = u[0];
+        for (int j = 1; j < tokens; ++j) mx = fmaxf(mx, u[j]);
+        float tot = 0.0f;
+        for (int j = 0; j < tokens; ++j) {
+            u[j] = expf(__fsub_rn(u[j], mx));
+            tot = __fadd_rn(tot, u[j]);
+        }
+        tot = __fadd_rn(tot, 1e-6f);
+        for (int j = 0; j < tokens; ++j) hrow[j] = __fdiv_rn(u[j], tot);
+    }
     if (A_out)
         for (int j = 0; j < tokens; ++j)
             A_out[(((size_t)seq * heads + h) * tokens + i) * tokens + j] = hrow[j];
@@ -181,6 +205,14 @@ __global__ void relu_square_kernel(const float* __restrict__ x, int64_t n, float
     out[i] = __fmul_rn(v, v);
 }
 
+// rate_encode, snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|))
+__global__ void rate_encode_kernel(const float* __restrict__ p, int64_t n, float gain, float* __restrict__ out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float ss = __fdiv_rn(p[i], __fadd_rn(fabsf(p[i]), 1.0f));
+    out[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(ss, gain))));
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -215,7 +247,7 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
     HSES_REQUIRE(n_seq >= 0 && tokens >= 1 && tokens <= kMaxTokens, "tokens must be in 1..128");
     HSES_REQUIRE(heads >= 1 && head_dim >= 1 && head_dim <= kMaxHeadDim, "head_dim must be in 1..64");
     HSES_REQUIRE(row_stride >= (int64_t)heads * head_dim, "row stride smaller than heads*head_dim");
-    HSES_REQUIRE(mode == 0 || mode == 1, "unknown mode");
+    HSES_REQUIRE(mode >= 0 && mode <= 2, "unknown mode");
     HSES_REQUIRE(mode == 0 || (tau_m != 0.0f && n_iter >= 1), "bad LIF parameters");
     HSES_REQUIRE(n_seq * heads < (1ll << 31), "too many (sequence, head) pairs");
     if (n_seq == 0) return HSES_OK;
@@ -282,5 +314,16 @@ int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x, int64_t 
     return HSES_OK;
 }
 
+
+int hses_rate_encode(hses_ctx* ctx, hses_stream stream, const float* p, int64_t n, float gain, float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(n >= 0, "n must be >= 0");
+    if (n == 0) return HSES_OK;
+    HSES_REQUIRE(p != nullptr && out != nullptr, "NULL pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "rate_encode");
+    rate_encode_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(p, n, gain, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
 
 }  // extern "C"

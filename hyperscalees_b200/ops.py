@@ -525,3 +525,13 @@ def relu_square(x: torch.Tensor) -> torch.Tensor:
     ctx = get_context(x.device)
     _lib.check(_lib.load().hses_relu_square(ctx.handle, current_stream(), _ptr(x), x.numel(), _ptr(out)))
     return out
+
+
+def rate_encode(p: torch.Tensor, gain: float) -> torch.Tensor:
+    """snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|))."""
+    _check(p, "p")
+    p = p.contiguous()
+    out = torch.empty_like(p)
+    ctx = get_context(p.device)
+    _lib.check(_lib.load().hses_rate_encode(ctx.handle, current_stream(), _ptr(p), p.numel(), gain, _ptr(out)))
+    return out

@@ -430,7 +430,10 @@ int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w,
  *      the Rust port keeps a continuous variant, hyperscalees-models/src/snn_transformer.rs:80-102).
  *      Q, K, V, O: (n_seq, tokens, heads*head_dim) with row_stride; mode 0: O = (beta Q K^T) V,
  *      the spike product without softmax; mode 1: LIF-count row softmax (n_iter LIF steps with
- *      global inhibition g_inh).  A_out (optional): (n_seq, heads, tokens, tokens) weights. ------ */
+ *      global inhibition g_inh); mode 2: the Rust port's continuous form — n_iter Hopfield
+ *      relaxations u <- u + (1/tau_m)(-u + H - g_inh * mean_key(u)) from u = H, then a stable
+ *      softmax along the keys (snn_transformer.rs:80-102).  A_out (optional): (n_seq, heads,
+ *      tokens, tokens) weights. ---------------------------------------------------------- */
 int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, const float* K, const float* V,
                            int64_t n_seq, int32_t tokens, int32_t heads, int32_t head_dim, int64_t row_stride,
                            int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
@@ -456,6 +459,9 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x /*dev
                          const uint8_t* new_starts /*device or NULL*/, const float* coef /*device (c)*/,
                          float* out /*device (T,c)*/);
 int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t n,
+                     float* out /*device*/);
+/* rate_encode, hyperscalees-models/src/snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|)). */
+int hses_rate_encode(hses_ctx* ctx, hses_stream stream, const float* p /*device*/, int64_t n, float gain,
                      float* out /*device*/);
 
 #ifdef __cplusplus

@@ -721,6 +721,25 @@ void hso_spiking_attention(const float *Q, const float *K, const float *V, int t
             tot += 1e-6f;
             for (int j = 0; j < tokens; ++j) row[j] = cnt[j] / tot;
         }
+        if (mode == 2) {
+            /* continuous_attention, hyperscalees-models/src/snn_transformer.rs:80-102: Hopfield
+             * relaxation u <- u + (1/tau)(-u + H - g*mean_key(u)) from u = H, n_iter steps, then
+             * a stable softmax along the keys with 1e-6 added to the denominator */
+            float one_over_tau = 1.0f / tau_m;
+            for (int j = 0; j < tokens; ++j) u[j] = row[j];
+            for (int it = 0; it < n_iter; ++it) {
+                float m = 0.0f;
+                for (int j = 0; j < tokens; ++j) m += u[j];
+                m = m / (float)tokens;
+                for (int j = 0; j < tokens; ++j) u[j] = u[j] + ((-u[j] + row[j]) - m * g_inh) * one_over_tau;
+            }
+            float mx = u[0];
+            for (int j = 1; j < tokens; ++j) if (u[j] > mx) mx = u[j];
+            float tot = 0.0f;
+            for (int j = 0; j < tokens; ++j) { cnt[j] = expf(u[j] - mx); tot += cnt[j]; }
+            tot += 1e-6f;
+            for (int j = 0; j < tokens; ++j) row[j] = cnt[j] / tot;
+        }
         if (A) memcpy(A + (size_t)i * tokens, row, sizeof(float) * (size_t)tokens);
         for (int c = 0; c < d; ++c) {
             float acc = 0.0f;
@@ -807,4 +826,12 @@ void hso_channel_mix(const float *x, int T, int c, int f, const float *state, co
     for (int j = 0; j < c; ++j) state_out[j] = x[(size_t)(length - 1) * c + j];
     free(xk);
     free(k);
+}
+
+/* rate_encode, snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|)). */
+void hso_rate_encode(const float *p, size_t n, float gain, float *out) {
+    for (size_t i = 0; i < n; ++i) {
+        float ss = p[i] / (fabsf(p[i]) + 1.0f);
+        out[i] = 1.0f / (1.0f + expf(-(ss * gain)));
+    }
 }

@@ -174,6 +174,7 @@ void hso_token_shift_mix(const float *x, int T, int c, const float *state, const
 void hso_channel_mix(const float *x, int T, int c, int f, const float *state, const uint8_t *new_starts,
                      const float *x_k, const float *wk, const float *wv, int length, float *out,
                      float *state_out);
+void hso_rate_encode(const float *p, size_t n, float gain, float *out);
 int hso_num_threads(void);
 
 #ifdef __cplusplus

@@ -429,3 +429,10 @@ def channel_mix(x, state, x_k, wk, wv, length, new_starts=None):
     lib().hso_channel_mix(xp, T, c, f, sp, ns.ctypes.data_as(_u8p) if ns is not None else None, xkp, wkp, wvp,
                           length, out.ctypes.data_as(_f32p), so.ctypes.data_as(_f32p))
     return out, so
+
+
+def rate_encode(p, gain):
+    p, pp = _f(p)
+    out = np.empty_like(p)
+    lib().hso_rate_encode(pp, C.c_size_t(p.size), C.c_float(gain), out.ctypes.data_as(_f32p))
+    return out

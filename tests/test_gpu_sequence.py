@@ -125,3 +125,26 @@ def test_channel_mixing_matches_oracle_and_reference_case():
     # the token shift alone is exact
     assert np.array_equal(ops.token_shift_mix(dev(x), dev(state), dev(x_k), torch.from_numpy(ns)).cpu().numpy(),
                           oracle.token_shift_mix(x, state, x_k, ns))
+
+
+def test_continuous_hopfield_attention_and_rate_encode(hs, oracle):
+    """snn_transformer.rs:80-116: continuous rates, Hopfield relaxation, softmax rows that sum to one
+    (the reference asserts the row sums in snn_attention.rs:374-399)."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(21)
+    n_seq, tokens, heads, hd = 3, 17, 4, 16
+    p = g.standard_normal((n_seq, tokens, heads * hd)).astype(np.float32) * 2
+    rates = ops.rate_encode(dev(p), 4.0).cpu().numpy()
+    assert np.abs(rates - oracle.rate_encode(p, 4.0)).max() <= 1e-6
+    assert (rates > 0).all() and (rates < 1).all()
+    Q, K, V = rates, np.roll(rates, 1, axis=1).copy(), np.roll(rates, 2, axis=2).copy()
+    O, A = ops.spiking_attention(dev(Q), dev(K), dev(V), heads, mode=2, beta=2.0, tau_m=2.0, v_th=0.0, g_inh=0.5,
+                                 n_iter=8, want_weights=True)
+    O, A = O.cpu().numpy(), A.cpu().numpy()
+    assert np.abs(A.sum(-1) - 1.0).max() <= 1e-4
+    for s in range(n_seq):
+        for h in range(heads):
+            sl = slice(h * hd, (h + 1) * hd)
+            wo, wa = oracle.spiking_attention(Q[s][:, sl], K[s][:, sl], V[s][:, sl], 2, 2.0, 2.0, 0.0, 0.5, 8)
+            assert np.abs(A[s, h] - wa).max() <= 2e-6
+            assert np.abs(O[s][:, sl] - wo).max() <= 1e-5
