@@ -29,7 +29,7 @@ EXPORTS = [
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
-    "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
+    "hses_einsum_pair_workspace_bytes", "hses_einsum_pair", "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
 ]
 
 
@@ -152,6 +152,9 @@ def load():
                                          vp, sz]
     L.hses_convert_fitnesses_bs.argtypes = [vp, vp, vp, i64, i32, vp, vp]
     L.hses_vector_mul.argtypes = [vp, vp, vp, vp, vp, i64]
+    L.hses_einsum_pair_workspace_bytes.restype = sz
+    L.hses_einsum_pair_workspace_bytes.argtypes = [i64, i32, i32, i32]
+    L.hses_einsum_pair.argtypes = [vp, vp, vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, vp, vp, vp, sz]
     L.hses_layer_norm.argtypes = [vp, vp, vp, i64, i32, vp, vp, f32, vp]
     L.hses_group_norm.argtypes = [vp, vp, vp, i64, i32, i32, i32, vp, vp, f32, vp]
     L.hses_token_shift_mix.argtypes = [vp, vp, vp, i32, i32, vp, vp, vp, vp]

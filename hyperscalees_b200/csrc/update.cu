@@ -188,6 +188,108 @@ static bool plan_update_static(int a, int b, int rank, int64_t n, UpdatePlan* ou
     return true;
 }
 
+// ---------------------------------------------------------------------------
+// einsum_pair_fused (hyperscalees/src/oxide.rs:318-462, kernel
+// hyperscalees-kernels/src/einsum_pair_fused_oxide.rs:94-227) for callers that bring their own
+// half-population factors: a_t (half*r, a) and b_t (half*r, b), row k = i*r + j belonging to
+// member pair (i, i + half);  g_raw = sum_k (s_i + s_{i+half}) a_t[k] (x) b_t[k],
+// g_ones = 2 * sum_k a_t[k] (x) b_t[k].  Split-K partial sums are added in a fixed order
+// (the reference merges with float atomics).
+// ---------------------------------------------------------------------------
+constexpr int EP_TM = 64, EP_TN = 64, EP_TK = 16, EP_THREADS = 256;
+__global__ void __launch_bounds__(EP_THREADS)
+einsum_pair_kernel(const float* __restrict__ a_t, int64_t a_s0, int64_t a_s1, const float* __restrict__ b_t, int64_t b_s0,
+                   int64_t b_s1,
+                   const float* __restrict__ scores, int64_t half, int r, int a, int b,
+                   float* __restrict__ partial) {
+    __shared__ __align__(16) float sa[EP_TK][EP_TM];
+    __shared__ __align__(16) float sw[EP_TK][EP_TM];
+    __shared__ __align__(16) float sb[EP_TK][EP_TN];
+    const int m0 = blockIdx.y * EP_TM, n0 = blockIdx.x * EP_TN;
+    const int split = blockIdx.z, splits = gridDim.z;
+    const int64_t K = half * r;
+    const int64_t k_lo = K * split / splits, k_hi = K * (split + 1) / splits;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    float raw[4][4], ones[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) raw[i][j] = ones[i][j] = 0.0f;
+    for (int64_t k0 = k_lo; k0 < k_hi; k0 += EP_TK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            int idx = tid + e * EP_THREADS;
+            int kk = idx >> 6, c = idx & 63;
+            int64_t kg = k0 + kk;
+            bool kin = kg < k_hi;
+            float f = 0.0f;
+            int64_t i = 0, j = 0;
+            if (kin) {
+                i = kg / r;
+                j = kg - i * r;
+                f = __fadd_rn(scores[i], scores[i + half]);
+            }
+            float av = (kin && m0 + c < a) ? a_t[(size_t)(i * a_s0 + j * a_s1) + m0 + c] : 0.0f;
+            sa[kk][c] = av;
+            sw[kk][c] = __fmul_rn(av, f);
+            sb[kk][c] = (kin && n0 + c < b) ? b_t[(size_t)(i * b_s0 + j * b_s1) + n0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < EP_TK; ++kk) {
+            float4 a4 = *reinterpret_cast<const float4*>(&sa[kk][ty * 4]);
+            float4 w4 = *reinterpret_cast<const float4*>(&sw[kk][ty * 4]);
+            float4 b4 = *reinterpret_cast<const float4*>(&sb[kk][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, wv[4] = {w4.x, w4.y, w4.z, w4.w};
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    raw[i][j] = fmaf(wv[i], bv[j], raw[i][j]);
+                    ones[i][j] = fmaf(av[i], bv[j], ones[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+    float* praw = partial + (size_t)split * 2 * a * b;
+    float* pones = praw + (size_t)a * b;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int m = m0 + ty * 4 + i;
+        if (m >= a) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int n = n0 + tx * 4 + j;
+            if (n >= b) continue;
+            praw[(size_t)m * b + n] = raw[i][j];
+            pones[(size_t)m * b + n] = ones[i][j];
+        }
+    }
+}
+
+__global__ void einsum_pair_reduce_kernel(const float* __restrict__ partial, int splits, size_t len,
+                                          float* __restrict__ g_raw, float* __restrict__ g_ones) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= len) return;
+    float sr = 0.0f, so = 0.0f;
+    for (int k = 0; k < splits; ++k) {
+        sr = __fadd_rn(sr, partial[(size_t)k * 2 * len + i]);
+        so = __fadd_rn(so, partial[(size_t)k * 2 * len + len + i]);
+    }
+    g_raw[i] = sr;
+    g_ones[i] = __fmul_rn(so, 2.0f);
+}
+
+static int einsum_pair_splits(int64_t half, int r, int a, int b) {
+    int tiles = ((a + EP_TM - 1) / EP_TM) * ((b + EP_TN - 1) / EP_TN);
+    int64_t kblocks = (half * r + 255) / 256;   // at least 256 rows of K per split
+    int want = (2 * 148 + tiles - 1) / tiles;
+    if (want > kblocks) want = (int)kblocks;
+    if (want > 256) want = 256;
+    return want < 1 ? 1 : want;
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -358,6 +460,41 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
     HSES_KERNEL(ctx, st, "update_reduce");
     update_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale,
                                                                        0, grad);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+size_t hses_einsum_pair_workspace_bytes(int64_t half, int32_t r, int32_t a, int32_t b) {
+    if (half < 1 || r < 1 || a < 1 || b < 1) return 0;
+    return (size_t)einsum_pair_splits(half, r, a, b) * 2 * (size_t)a * b * sizeof(float);
+}
+
+int hses_einsum_pair(hses_ctx* ctx, hses_stream stream, const float* a_t, int64_t a_stride0, int64_t a_stride1,
+                     const float* b_t, int64_t b_stride0, int64_t b_stride1, const float* scores, int64_t half,
+                     int32_t r, int32_t a, int32_t b, float* g_raw, float* g_ones, void* workspace,
+                     size_t workspace_bytes) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(half >= 1 && r >= 1 && a >= 1 && b >= 1, "bad shape");
+    HSES_REQUIRE(a_stride1 >= a && b_stride1 >= b && a_stride0 >= 0 && b_stride0 >= 0, "row stride smaller than the row");
+    HSES_REQUIRE(a_t != nullptr && b_t != nullptr && scores != nullptr && g_raw != nullptr && g_ones != nullptr,
+                 "NULL pointer");
+    HSES_REQUIRE(half * r < (1ll << 40), "K too large");
+    size_t need = hses_einsum_pair_workspace_bytes(half, r, a, b);
+    HSES_REQUIRE(workspace != nullptr && workspace_bytes >= need, "workspace too small; see hses_einsum_pair_workspace_bytes");
+    int splits = einsum_pair_splits(half, r, a, b);
+    HSES_REQUIRE((a + EP_TM - 1) / EP_TM <= 65535, "a too large");
+    cudaStream_t st = as_stream(stream);
+    float* partial = reinterpret_cast<float*>(workspace);
+    dim3 grid((unsigned)((b + EP_TN - 1) / EP_TN), (unsigned)((a + EP_TM - 1) / EP_TM), (unsigned)splits);
+    {
+        HSES_KERNEL(ctx, st, "einsum_pair");
+        einsum_pair_kernel<<<grid, EP_THREADS, 0, st>>>(a_t, a_stride0, a_stride1, b_t, b_stride0, b_stride1, scores, half, r, a,
+                                                        b, partial);
+        HSES_LAUNCH_CHECK();
+    }
+    size_t len = (size_t)a * b;
+    HSES_KERNEL(ctx, st, "einsum_pair_reduce");
+    einsum_pair_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, splits, len, g_raw, g_ones);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -3,7 +3,7 @@ the hyperscalees-kernels crate), kept under the same names so a trainer that
 called `oxide::lif_fused` / `oxide::poisson_encode_fused` finds them here."""
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -25,3 +25,12 @@ def poisson_encode_fused(images: torch.Tensor, t: int, seeds: Sequence[int]) -> 
     if t > 8:
         raise ValueError("poisson_encode_fused: t must be <= 8 (oxide.rs:578-580)")
     return ops.poisson_encode(images, t, seeds)
+
+
+def einsum_pair_fused(a_t: torch.Tensor, b_t: torch.Tensor,
+                      scores: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """oxide.rs:325-462: a_t (half, r, a), b_t (half, r, b) half-population factors with
+    innermost stride 1 (padded outer strides allowed), scores (n,) raw scores ->
+    (g_raw, g_ones), each (a, b): g_raw = sum_i (s_i + s_{half+i}) A_i (x) B_i,
+    g_ones = 2 * sum_i A_i (x) B_i.  The reference's `2a <= 256` limit does not apply."""
+    return ops.einsum_pair(a_t, b_t, scores)

@@ -342,6 +342,31 @@ def vector_mul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def einsum_pair(a_t: torch.Tensor, b_t: torch.Tensor, scores: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """g_raw, g_ones of the paired einsum over explicit half-population factors:
+    a_t (half, r, a), b_t (half, r, b) (innermost stride 1, outer strides free), scores (2*half,)."""
+    _check(a_t, "a_t", ndim=3)
+    _check(b_t, "b_t", ndim=3)
+    _check(scores, "scores", ndim=1)
+    half, r, a = a_t.shape
+    if b_t.shape[:2] != (half, r):
+        raise ValueError(f"b_t shape {tuple(b_t.shape)} does not match a_t {tuple(a_t.shape)}")
+    b = b_t.shape[2]
+    if half * r == 0:
+        raise ValueError("einsum_pair: empty K")
+    if scores.numel() != 2 * half:
+        raise ValueError("scores must hold 2*half values")
+    lib = _lib.load()
+    ws = torch.empty(lib.hses_einsum_pair_workspace_bytes(half, r, a, b), dtype=torch.uint8, device=a_t.device)
+    g_raw = torch.empty(a, b, dtype=torch.float32, device=a_t.device)
+    g_ones = torch.empty_like(g_raw)
+    ctx = get_context(a_t.device)
+    _lib.check(lib.hses_einsum_pair(ctx.handle, current_stream(), _ptr(a_t), a_t.stride(0), a_t.stride(1), _ptr(b_t),
+                                    b_t.stride(0), b_t.stride(1), _ptr(scores), half, r, a, b, _ptr(g_raw),
+                                    _ptr(g_ones), _ptr(ws), ws.numel()))
+    return g_raw, g_ones
+
+
 def es_update_dense(key: int, epoch: int, noise_reuse: int, shape: Tuple[int, int], sigma: float,
                     fitness_: torch.Tensor, first_thread: int = 0,
                     n_total: Optional[int] = None) -> torch.Tensor:

@@ -311,6 +311,21 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
                           int32_t rank, int32_t a, int32_t b, float sigma,
                           const float* fitness /*device*/, float* grad /*device (a,b) dense*/);
 
+/* ---- einsum_pair_fused, hyperscalees/src/oxide.rs:318-462 (kernel parameter list
+ *      hyperscalees-kernels/src/einsum_pair_fused_oxide.rs:96-113), for callers that bring
+ *      their own half-population factors instead of letting the library regenerate them:
+ *      a_t (half, r, a) and b_t (half, r, b) with element strides of dim 0 and dim 1 given
+ *      (innermost stride 1; padded row pitches allowed), row (i, j) shared by members i and
+ *      i + half; scores: n = 2*half raw scores.
+ *      g_raw = sum_k (s_i + s_{i+half}) a_t[k] (x) b_t[k], g_ones = 2 * sum_k a_t[k] (x) b_t[k],
+ *      both (a, b) dense, overwritten (no zero-initialisation needed, no 2a <= 256 limit). -- */
+size_t hses_einsum_pair_workspace_bytes(int64_t half, int32_t r, int32_t a, int32_t b);
+int hses_einsum_pair(hses_ctx* ctx, hses_stream stream, const float* a_t /*device*/, int64_t a_stride0,
+                     int64_t a_stride1, const float* b_t /*device*/, int64_t b_stride0, int64_t b_stride1,
+                     const float* scores /*device*/, int64_t half, int32_t r, int32_t a, int32_t b,
+                     float* g_raw /*device*/, float* g_ones /*device*/, void* workspace /*device*/,
+                     size_t workspace_bytes);
+
 /* ---- simple_full_update + do_update_with, eggroll.rs:331-350, 384-404, for
  *      dense (PARAM-class) leaves of `len` = rows*cols elements. ----------- */
 int hses_es_update_dense(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
