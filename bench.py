@@ -411,35 +411,36 @@ def run_streaming_kernels(args, local_rank: int):
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *shape: torch.rand(*shape, device=dev, generator=g)
     cases = {}
+    sh = max(1, args.shrink)   # divides the leading dimension of every case (reduced cases for ncu captures)
 
-    probs = rnd(131072, 784)
-    enc_out = torch.empty(8, 131072, 784, device=dev)
-    cases["poisson_encode [131072x784] -> T=8"] = (
+    probs = rnd(131072 // sh, 784)
+    enc_out = torch.empty(8, 131072 // sh, 784, device=dev)
+    cases[f"poisson_encode [{131072 // sh}x784] -> T=8"] = (
         lambda: ops.poisson_encode(probs, 8, (1, 2, 3, 4), out=enc_out), probs.numel() * 4 + enc_out.numel() * 4)
-    cur = rnd(8, 131072, 128)
-    v0 = torch.zeros(131072, 128, device=dev)
+    cur = rnd(8, 131072 // sh, 128)
+    v0 = torch.zeros(131072 // sh, 128, device=dev)
     lif_out = torch.empty_like(cur)
-    cases["lif_scan T=8 [131072x128]"] = (
+    cases[f"lif_scan T=8 [{131072 // sh}x128]"] = (
         lambda: ops.lif_scan(cur, 2.0, 1.0, v=v0, reset_mode=ops.RESET_SUBTRACT, out=lif_out), 2 * cur.numel() * 4 + 2 * v0.numel() * 4)
-    q, k, v = rnd(32768, 64, 64), rnd(32768, 64, 64), rnd(32768, 64, 64)
-    cases["spiking_attention mode 0 [32768 seq x 64 tok x 4 heads x 16]"] = (
+    q, k, v = rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64)
+    cases[f"spiking_attention mode 0 [{32768 // sh} seq x 64 tok x 4 heads x 16]"] = (
         lambda: ops.spiking_attention(q, k, v, 4, mode=0), 4 * q.numel() * 4)
     cases["spiking_attention mode 2 (relaxation + softmax)"] = (
         lambda: ops.spiking_attention(q, k, v, 4, mode=2), 4 * q.numel() * 4)
-    wk = [rnd(256, 256, 12, 64) * 0.5 for _ in range(6)]
+    wk = [rnd(256 // sh, 256, 12, 64) * 0.5 for _ in range(6)]
     wk[1] = 0.9 + 0.1 * wk[1]
-    state = torch.zeros(256, 12, 64, 64, device=dev)
-    cases["wkv7 [256 seq x 256 tok x 12 heads x 64]"] = (
+    state = torch.zeros(256 // sh, 12, 64, 64, device=dev)
+    cases[f"wkv7 [{256 // sh} seq x 256 tok x 12 heads x 64]"] = (
         lambda: ops.wkv7(*wk, state), 7 * wk[0].numel() * 4 + 2 * state.numel() * 4)
-    xn = rnd(262144, 768)
+    xn = rnd(262144 // sh, 768)
     wn, bn = torch.ones(768, device=dev), torch.zeros(768, device=dev)
-    cases["layer_norm [262144x768]"] = (lambda: ops.layer_norm(xn, wn, bn), 2 * xn.numel() * 4)
-    cases["group_norm 12 groups [262144x768]"] = (lambda: ops.group_norm(xn, 12, wn, bn), 2 * xn.numel() * 4)
-    cases["relu_square [201M]"] = (lambda: ops.relu_square(xn), 2 * xn.numel() * 4)
-    cases["rate_encode [201M]"] = (lambda: ops.rate_encode(xn, 4.0), 2 * xn.numel() * 4)
-    par, grd = rnd(1 << 26), rnd(1 << 26)
+    cases[f"layer_norm [{262144 // sh}x768]"] = (lambda: ops.layer_norm(xn, wn, bn), 2 * xn.numel() * 4)
+    cases[f"group_norm 12 groups [{262144 // sh}x768]"] = (lambda: ops.group_norm(xn, 12, wn, bn), 2 * xn.numel() * 4)
+    cases[f"relu_square [{262144 // sh}x768]"] = (lambda: ops.relu_square(xn), 2 * xn.numel() * 4)
+    cases[f"rate_encode [{262144 // sh}x768]"] = (lambda: ops.rate_encode(xn, 4.0), 2 * xn.numel() * 4)
+    par, grd = rnd((1 << 26) // sh), rnd((1 << 26) // sh)
     m1, m2 = torch.zeros_like(par), torch.zeros_like(par)
-    cases["solver_step AdamW [64M params]"] = (
+    cases[f"solver_step AdamW [{(1 << 26) // sh} params]"] = (
         lambda: ops.solver_step(ops.ADAMW, 1, par, grd, m1, m2, weight_decay=0.01), 7 * par.numel() * 4)
 
     peaks = measured_peaks()
@@ -489,6 +490,8 @@ def main():
     ap.add_argument("--n-pop", type=int, default=8192,
                     help="microbench: members per GPU (smaller values give the reduced case used for ncu "
                          "captures); population_step: members of the whole population")
+    ap.add_argument("--shrink", type=int, default=1,
+                    help="streaming_kernels: divide every case's leading dimension (reduced cases for ncu captures)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs (profiling runs)")
     args = ap.parse_args()

@@ -230,24 +230,60 @@ struct SolverConsts {
     float lr, beta1, beta2, eps, wd;
     float omb1, omb2, ibc1, ibc2, grad_scale;
 };
-__global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float* __restrict__ g,
-                              float* __restrict__ m, float* __restrict__ v, int64_t len) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= len) return;
-    float gi = c.grad_scale == 1.0f ? g[i] : __fmul_rn(g[i], c.grad_scale);
+__device__ __forceinline__ void solver_one(const SolverConsts& c, float& p, float g, float& m, float& v) {
+    float gi = c.grad_scale == 1.0f ? g : __fmul_rn(g, c.grad_scale);
     if (c.kind == HSES_SGD) {
-        p[i] = __fsub_rn(p[i], __fmul_rn(gi, c.lr));
+        p = __fsub_rn(p, __fmul_rn(gi, c.lr));
         return;
     }
-    float mn = __fadd_rn(__fmul_rn(m[i], c.beta1), __fmul_rn(gi, c.omb1));
-    float vn = __fadd_rn(__fmul_rn(v[i], c.beta2), __fmul_rn(__fmul_rn(gi, gi), c.omb2));
-    m[i] = mn;
-    v[i] = vn;
+    float mn = __fadd_rn(__fmul_rn(m, c.beta1), __fmul_rn(gi, c.omb1));
+    float vn = __fadd_rn(__fmul_rn(v, c.beta2), __fmul_rn(__fmul_rn(gi, gi), c.omb2));
+    m = mn;
+    v = vn;
     float mh = __fmul_rn(mn, c.ibc1), vh = __fmul_rn(vn, c.ibc2);
     float denom = __fadd_rn(__fsqrt_rn(vh), c.eps);
     float term = __fmul_rn(__fdiv_rn(mh, denom), -c.lr);
-    float pi = p[i];
-    p[i] = c.wd == 0.0f ? __fadd_rn(pi, term) : __fadd_rn(__fadd_rn(pi, term), __fmul_rn(pi, c.wd));
+    p = c.wd == 0.0f ? __fadd_rn(p, term) : __fadd_rn(__fadd_rn(p, term), __fmul_rn(p, c.wd));
+}
+
+// One 16-byte piece per thread (VEC4, all pointers 16-byte aligned); the last threads take the
+// len % 4 tail one value each.
+template <bool VEC4>
+__global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float* __restrict__ g,
+                              float* __restrict__ m, float* __restrict__ v, int64_t len) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool adam = c.kind != HSES_SGD;
+    if (VEC4) {
+        const int64_t n4 = len / 4;
+        if (i < n4) {
+            float4 pv = reinterpret_cast<float4*>(p)[i];
+            const float4 gv = reinterpret_cast<const float4*>(g)[i];
+            float4 mv = make_float4(0.f, 0.f, 0.f, 0.f), vv = mv;
+            if (adam) {
+                mv = reinterpret_cast<float4*>(m)[i];
+                vv = reinterpret_cast<float4*>(v)[i];
+            }
+            solver_one(c, pv.x, gv.x, mv.x, vv.x);
+            solver_one(c, pv.y, gv.y, mv.y, vv.y);
+            solver_one(c, pv.z, gv.z, mv.z, vv.z);
+            solver_one(c, pv.w, gv.w, mv.w, vv.w);
+            reinterpret_cast<float4*>(p)[i] = pv;
+            if (adam) {
+                reinterpret_cast<float4*>(m)[i] = mv;
+                reinterpret_cast<float4*>(v)[i] = vv;
+            }
+            return;
+        }
+        i = n4 * 4 + (i - n4);
+    }
+    if (i >= len) return;
+    float mi = adam ? m[i] : 0.0f, vi = adam ? v[i] : 0.0f, pi = p[i];
+    solver_one(c, pi, g[i], mi, vi);
+    p[i] = pi;
+    if (adam) {
+        m[i] = mi;
+        v[i] = vi;
+    }
 }
 
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
@@ -480,7 +516,13 @@ int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solve
         c.ibc2 = 1.0f / bc2;
     }
     HSES_KERNEL(ctx, as_stream(stream), "solver");
-    solver_kernel<<<(unsigned)((len + 255) / 256), 256, 0, as_stream(stream)>>>(c, param, grad, m, v, len);
+    const bool vec4 = ((((uintptr_t)param | (uintptr_t)grad | (uintptr_t)m | (uintptr_t)v) & 15u) == 0) && len >= 4;
+    if (vec4) {
+        int64_t work = len / 4 + len % 4;
+        solver_kernel<true><<<(unsigned)((work + 255) / 256), 256, 0, as_stream(stream)>>>(c, param, grad, m, v, len);
+    } else {
+        solver_kernel<false><<<(unsigned)((len + 255) / 256), 256, 0, as_stream(stream)>>>(c, param, grad, m, v, len);
+    }
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -4,56 +4,138 @@
 
 namespace hses {
 
+// Packed fp32 pairs (sm_100 f32x2 arithmetic): one instruction works on two independent IEEE
+// fp32 lanes.  Lane 0 is the low word: a pair loaded from memory holds (p[0], p[1]).
+// Measured on B200: a packed instruction issues at half the rate of a scalar one, so the lane
+// throughput is the same and only issue slots are saved; and the assembler contracts a packed
+// multiply followed by a packed add into a packed fma even when both carry .rn, so code that
+// needs two roundings per multiply-add cannot use the packed forms.  The kernels below that use
+// them (mode 0 of the attention, the WKV-7 recurrence) therefore round each multiply-add once.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 // ---------------------------------------------------------------------------
 // RWKV-7 inner loop (hyperscalees-models/src/llm.rs:235-296; models/llm/rwkv7.py:200-220):
 //   dec = exp(-exp(w));  sa = S a;  S = S * dec + v k^T + sa b^T;  out = S r
-// Thread i owns row i of the (S, S) state.  Operation order and rounding follow the
-// reference's op-by-op evaluation: (S*dec) + v*k, then + sa*b, dot products in index order.
+// Thread i owns rows 2i and 2i+1 of the (S, S) state as packed pairs.  Every multiply-add is one fused
+// operation (S*dec, then fma(v, k, .), then fma(sa, b, .)); the two dot products run as four
+// interleaved partial sums that are added at the end.  The reference rounds
+// each tensor operation separately: results agree to a few ulp per step (tested to 1e-5).
 // ---------------------------------------------------------------------------
 template <int S>
-__global__ void __launch_bounds__(S)
+__global__ void __launch_bounds__(S / 2)
 wkv7_kernel(const float* __restrict__ r, const float* __restrict__ w, const float* __restrict__ k,
             const float* __restrict__ v, const float* __restrict__ a, const float* __restrict__ b,
             const uint8_t* __restrict__ new_starts, int T, int H, float* __restrict__ state,
             float* __restrict__ out) {
-    __shared__ float sh[6][S];  // r, dec, k, v, a, b of the current step
+    __shared__ __align__(16) float shbuf[2][6][S];  // r, dec, k, v, a, b of a step
     const int seq = blockIdx.x / H, h = blockIdx.x % H, i = threadIdx.x;
-    float st[S];
-    float* sp = state + (((size_t)seq * H + h) * S + i) * S;
+    // rows 2i and 2i+1 of the state as S/2 packed pairs (st[2p], st[2p+1]) each: every 16-byte
+    // piece of a step vector read from shared memory feeds both rows
+    f32x2 sta[S / 2], stb[S / 2];
+    float* sp = state + (((size_t)seq * H + h) * S + 2 * i) * S;
 #pragma unroll
-    for (int j = 0; j < S; j += 4) {
-        float4 q = *reinterpret_cast<const float4*>(sp + j);
-        st[j] = q.x; st[j + 1] = q.y; st[j + 2] = q.z; st[j + 3] = q.w;
+    for (int p = 0; p < S / 2; p += 2) {
+        ulonglong2 q = *reinterpret_cast<const ulonglong2*>(sp + 2 * p);
+        sta[p] = q.x;
+        sta[p + 1] = q.y;
+        q = *reinterpret_cast<const ulonglong2*>(sp + S + 2 * p);
+        stb[p] = q.x;
+        stb[p + 1] = q.y;
     }
+    // The six vectors of a step go through a double-buffered shared-memory block (one barrier per
+    // step); those of the next step are fetched into registers while this step computes.
+    const size_t o0 = ((size_t)seq * T * H + h) * S + 2 * i, ostep = (size_t)H * S;
+    auto ld2 = [](const float* p) { return *reinterpret_cast<const float2*>(p); };
+    float2 nr = ld2(r + o0), nw = ld2(w + o0), nk = ld2(k + o0), nv = ld2(v + o0), na = ld2(a + o0), nb = ld2(b + o0);
     for (int t = 0; t < T; ++t) {
-        size_t o = (((size_t)seq * T + t) * H + h) * S + i;
+        const size_t o = o0 + (size_t)t * ostep;
+        float(*sh)[S] = shbuf[t & 1];
+        *reinterpret_cast<float2*>(&sh[0][2 * i]) = nr;
+        *reinterpret_cast<float2*>(&sh[1][2 * i]) = make_float2(expf(-expf(nw.x)), expf(-expf(nw.y)));
+        *reinterpret_cast<float2*>(&sh[2][2 * i]) = nk;
+        *reinterpret_cast<float2*>(&sh[4][2 * i]) = na;
+        *reinterpret_cast<float2*>(&sh[5][2 * i]) = nb;
+        const float via = nv.x, vib = nv.y;   // v of the thread's own rows
         __syncthreads();
-        sh[0][i] = r[o];
-        sh[1][i] = expf(-expf(w[o]));
-        sh[2][i] = k[o];
-        sh[3][i] = v[o];
-        sh[4][i] = a[o];
-        sh[5][i] = b[o];
-        __syncthreads();
+        if (t + 1 < T) {
+            const size_t on = o + ostep;
+            nr = ld2(r + on); nw = ld2(w + on); nk = ld2(k + on); nv = ld2(v + on); na = ld2(a + on); nb = ld2(b + on);
+        }
         if (new_starts && new_starts[(size_t)seq * T + t]) {
 #pragma unroll
-            for (int j = 0; j < S; ++j) st[j] = 0.0f;
+            for (int p = 0; p < S / 2; ++p) sta[p] = stb[p] = 0ull;
         }
-        float sa = 0.0f;
+        f32x2 saa_p = 0ull, saa_q = 0ull, sab_p = 0ull, sab_q = 0ull;   // (even, odd) partial sums, two chains per row
 #pragma unroll
-        for (int j = 0; j < S; ++j) sa = __fadd_rn(sa, __fmul_rn(st[j], sh[4][j]));
-        const float vi = sh[3][i];
-        float acc = 0.0f;
-#pragma unroll
-        for (int j = 0; j < S; ++j) {
-            float s1 = __fadd_rn(__fmul_rn(st[j], sh[1][j]), __fmul_rn(vi, sh[2][j]));
-            st[j] = __fadd_rn(s1, __fmul_rn(sa, sh[5][j]));
-            acc = __fadd_rn(acc, __fmul_rn(st[j], sh[0][j]));
+        for (int p = 0; p < S / 2; p += 2) {
+            const ulonglong2 av = *reinterpret_cast<const ulonglong2*>(&sh[4][2 * p]);
+            saa_p = fma2(sta[p], av.x, saa_p);
+            saa_q = fma2(sta[p + 1], av.y, saa_q);
+            sab_p = fma2(stb[p], av.x, sab_p);
+            sab_q = fma2(stb[p + 1], av.y, sab_q);
         }
-        out[o] = acc;
+        float e0, e1;
+        upk2(add2(saa_p, saa_q), e0, e1);
+        const float saa = __fadd_rn(e0, e1);
+        upk2(add2(sab_p, sab_q), e0, e1);
+        const float sab = __fadd_rn(e0, e1);
+        const f32x2 via2 = pk2(via, via), vib2 = pk2(vib, vib), saa2 = pk2(saa, saa), sab2 = pk2(sab, sab);
+        f32x2 acca_p = 0ull, acca_q = 0ull, accb_p = 0ull, accb_q = 0ull;
+#pragma unroll
+        for (int p = 0; p < S / 2; p += 2) {
+            const ulonglong2 dv = *reinterpret_cast<const ulonglong2*>(&sh[1][2 * p]);
+            const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(&sh[2][2 * p]);
+            const ulonglong2 bv = *reinterpret_cast<const ulonglong2*>(&sh[5][2 * p]);
+            const ulonglong2 rv = *reinterpret_cast<const ulonglong2*>(&sh[0][2 * p]);
+            sta[p] = fma2(saa2, bv.x, fma2(via2, kv.x, mul2(sta[p], dv.x)));
+            sta[p + 1] = fma2(saa2, bv.y, fma2(via2, kv.y, mul2(sta[p + 1], dv.y)));
+            stb[p] = fma2(sab2, bv.x, fma2(vib2, kv.x, mul2(stb[p], dv.x)));
+            stb[p + 1] = fma2(sab2, bv.y, fma2(vib2, kv.y, mul2(stb[p + 1], dv.y)));
+            acca_p = fma2(sta[p], rv.x, acca_p);
+            acca_q = fma2(sta[p + 1], rv.y, acca_q);
+            accb_p = fma2(stb[p], rv.x, accb_p);
+            accb_q = fma2(stb[p + 1], rv.y, accb_q);
+        }
+        float2 res;
+        upk2(add2(acca_p, acca_q), e0, e1);
+        res.x = __fadd_rn(e0, e1);
+        upk2(add2(accb_p, accb_q), e0, e1);
+        res.y = __fadd_rn(e0, e1);
+        *reinterpret_cast<float2*>(out + o) = res;
     }
 #pragma unroll
-    for (int j = 0; j < S; j += 4) *reinterpret_cast<float4*>(sp + j) = make_float4(st[j], st[j + 1], st[j + 2], st[j + 3]);
+    for (int p = 0; p < S / 2; p += 2) {
+        ulonglong2 q;
+        q.x = sta[p];
+        q.y = sta[p + 1];
+        *reinterpret_cast<ulonglong2*>(sp + 2 * p) = q;
+        q.x = stb[p];
+        q.y = stb[p + 1];
+        *reinterpret_cast<ulonglong2*>(sp + S + 2 * p) = q;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -149,6 +231,178 @@ __global__ void spiking_attention_kernel(const float* __restrict__ Q, const floa
     }
 }
 
+// Mode 0 for head sizes 16/32/64 with 16-byte aligned rows: the same sums in the same order as
+// the kernel above with one rounding per multiply-add (fma) instead of two; q and the output row
+// live in registers (compile-time head size), K and V
+// are staged with 16-byte loads and read back as broadcasts, and the score of key j is used as
+// soon as it is known, so no row of scores is kept.  Four keys are in flight at a time to give
+// the sequential dot products independent chains.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                         int tokens, int heads, int64_t row_stride, float beta, float* __restrict__ O,
+                         float* __restrict__ A_out) {
+    extern __shared__ __align__(16) float sm[];  // K (tokens, D) | V (tokens, D)
+    float4* ks4 = reinterpret_cast<float4*>(sm);
+    float4* vs4 = ks4 + tokens * (D / 4);
+    const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
+    constexpr int D4 = D / 4;
+    for (int e = threadIdx.x; e < tokens * D4; e += blockDim.x) {
+        int tk = e / D4, c4 = e - tk * D4;
+        ks4[e] = *reinterpret_cast<const float4*>(K + base + (size_t)tk * row_stride + c4 * 4);
+        vs4[e] = *reinterpret_cast<const float4*>(V + base + (size_t)tk * row_stride + c4 * 4);
+    }
+    __syncthreads();
+    const int i = threadIdx.x;
+    if (i >= tokens) return;
+    float q[D], acc[D];
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4) {
+        float4 v = *reinterpret_cast<const float4*>(Q + base + (size_t)i * row_stride + c4 * 4);
+        q[4 * c4] = v.x; q[4 * c4 + 1] = v.y; q[4 * c4 + 2] = v.z; q[4 * c4 + 3] = v.w;
+    }
+#pragma unroll
+    for (int c = 0; c < D; ++c) acc[c] = 0.0f;
+    float* arow = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i) * tokens : nullptr;
+    constexpr int JB = 4;
+    for (int j0 = 0; j0 < tokens; j0 += JB) {
+        float sc[JB];
+#pragma unroll
+        for (int u = 0; u < JB; ++u) sc[u] = 0.0f;
+#pragma unroll
+        for (int c4 = 0; c4 < D4; ++c4) {
+#pragma unroll
+            for (int u = 0; u < JB; ++u) {
+                const int j = j0 + u < tokens ? j0 + u : tokens - 1;
+                const float4 kv = ks4[j * D4 + c4];
+                sc[u] = fmaf(q[4 * c4], kv.x, sc[u]);
+                sc[u] = fmaf(q[4 * c4 + 1], kv.y, sc[u]);
+                sc[u] = fmaf(q[4 * c4 + 2], kv.z, sc[u]);
+                sc[u] = fmaf(q[4 * c4 + 3], kv.w, sc[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < JB; ++u) {
+            if (j0 + u < tokens) {
+                const float hj = __fmul_rn(beta, sc[u]);
+                if (arow) arow[j0 + u] = hj;
+#pragma unroll
+                for (int c4 = 0; c4 < D4; ++c4) {
+                    const float4 vv = vs4[(j0 + u) * D4 + c4];
+                    acc[4 * c4] = fmaf(hj, vv.x, acc[4 * c4]);
+                    acc[4 * c4 + 1] = fmaf(hj, vv.y, acc[4 * c4 + 1]);
+                    acc[4 * c4 + 2] = fmaf(hj, vv.z, acc[4 * c4 + 2]);
+                    acc[4 * c4 + 3] = fmaf(hj, vv.w, acc[4 * c4 + 3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4)
+        *reinterpret_cast<float4*>(O + base + (size_t)i * row_stride + c4 * 4) =
+            make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+}
+
+// The same for head sizes 16 and 32 on packed pairs.  The kernel above is bound by the rate at
+// which shared memory feeds registers (every thread reads all of K and V: 128 bytes per cycle and
+// SM), so here a thread owns TWO query rows and every 16-byte piece of K or V it loads feeds four
+// packed fmas.  K is staged transposed (Kt[c][j]) so that one piece holds column c of four
+// consecutive keys, i.e. two (key j, key j+1) pairs whose dot products with q advance together;
+// the V row of a key is consumed as (c, c+1) pairs.  Sums run in index order with one rounding
+// per multiply-add.
+template <int D>
+__global__ void __launch_bounds__(64)
+attention_product_packed_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                int tokens, int heads, int64_t row_stride, float beta, float* __restrict__ O,
+                                float* __restrict__ A_out) {
+    extern __shared__ __align__(16) float sm[];
+    const int tp = (tokens + 3) / 4 * 4 + 4;   // pitch of Kt: keys rounded up to four, plus four
+    float* kt = sm;                            // [D][tp]
+    float4* vs4 = reinterpret_cast<float4*>(sm + D * tp);  // [tokens][D]
+    const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
+    constexpr int D4 = D / 4;
+    const int padc = tp - tokens;
+    for (int e = threadIdx.x; e < D * padc; e += blockDim.x) kt[(e / padc) * tp + tokens + e % padc] = 0.0f;
+    for (int e = threadIdx.x; e < tokens * D4; e += blockDim.x) {
+        int tk = e / D4, c4 = e - tk * D4;
+        const float4 kv = *reinterpret_cast<const float4*>(K + base + (size_t)tk * row_stride + c4 * 4);
+        kt[(4 * c4) * tp + tk] = kv.x;
+        kt[(4 * c4 + 1) * tp + tk] = kv.y;
+        kt[(4 * c4 + 2) * tp + tk] = kv.z;
+        kt[(4 * c4 + 3) * tp + tk] = kv.w;
+        vs4[e] = *reinterpret_cast<const float4*>(V + base + (size_t)tk * row_stride + c4 * 4);
+    }
+    __syncthreads();
+    const int i0 = 2 * threadIdx.x;
+    if (i0 >= tokens) return;
+    const bool two = i0 + 1 < tokens;
+    const int i1 = two ? i0 + 1 : i0;
+    f32x2 qa[D], qb[D], acca[D / 2], accb[D / 2];
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4) {
+        const float4 va = *reinterpret_cast<const float4*>(Q + base + (size_t)i0 * row_stride + c4 * 4);
+        const float4 vb = *reinterpret_cast<const float4*>(Q + base + (size_t)i1 * row_stride + c4 * 4);
+        qa[4 * c4] = pk2(va.x, va.x); qa[4 * c4 + 1] = pk2(va.y, va.y);
+        qa[4 * c4 + 2] = pk2(va.z, va.z); qa[4 * c4 + 3] = pk2(va.w, va.w);
+        qb[4 * c4] = pk2(vb.x, vb.x); qb[4 * c4 + 1] = pk2(vb.y, vb.y);
+        qb[4 * c4 + 2] = pk2(vb.z, vb.z); qb[4 * c4 + 3] = pk2(vb.w, vb.w);
+    }
+#pragma unroll
+    for (int c = 0; c < D / 2; ++c) acca[c] = accb[c] = 0ull;
+    const f32x2 beta2 = pk2(beta, beta);
+    float* arow_a = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i0) * tokens : nullptr;
+    float* arow_b = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i1) * tokens : nullptr;
+    for (int j0 = 0; j0 < tokens; j0 += 4) {
+        f32x2 sa01 = 0ull, sa23 = 0ull, sb01 = 0ull, sb23 = 0ull;
+#pragma unroll
+        for (int c = 0; c < D; ++c) {
+            const ulonglong2 kv = *reinterpret_cast<const ulonglong2*>(kt + c * tp + j0);
+            sa01 = fma2(qa[c], kv.x, sa01);
+            sa23 = fma2(qa[c], kv.y, sa23);
+            sb01 = fma2(qb[c], kv.x, sb01);
+            sb23 = fma2(qb[c], kv.y, sb23);
+        }
+        float ha[4], hb[4];
+        upk2(mul2(beta2, sa01), ha[0], ha[1]);
+        upk2(mul2(beta2, sa23), ha[2], ha[3]);
+        upk2(mul2(beta2, sb01), hb[0], hb[1]);
+        upk2(mul2(beta2, sb23), hb[2], hb[3]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (j0 + u < tokens) {
+                if (arow_a) {
+                    arow_a[j0 + u] = ha[u];
+                    if (two) arow_b[j0 + u] = hb[u];
+                }
+                const f32x2 ha2 = pk2(ha[u], ha[u]), hb2 = pk2(hb[u], hb[u]);
+                const ulonglong2* vrow = reinterpret_cast<const ulonglong2*>(vs4 + (j0 + u) * D4);
+#pragma unroll
+                for (int c4 = 0; c4 < D4; ++c4) {
+                    const ulonglong2 vv = vrow[c4];
+                    acca[2 * c4] = fma2(ha2, vv.x, acca[2 * c4]);
+                    acca[2 * c4 + 1] = fma2(ha2, vv.y, acca[2 * c4 + 1]);
+                    accb[2 * c4] = fma2(hb2, vv.x, accb[2 * c4]);
+                    accb[2 * c4 + 1] = fma2(hb2, vv.y, accb[2 * c4 + 1]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4) {
+        ulonglong2 o;
+        o.x = acca[2 * c4];
+        o.y = acca[2 * c4 + 1];
+        *reinterpret_cast<ulonglong2*>(O + base + (size_t)i0 * row_stride + c4 * 4) = o;
+        if (two) {
+            o.x = accb[2 * c4];
+            o.y = accb[2 * c4 + 1];
+            *reinterpret_cast<ulonglong2*>(O + base + (size_t)i1 * row_stride + c4 * 4) = o;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // RWKV-7 block pieces around the recurrence (hyperscalees-models/src/llm.rs:64-213)
 // ---------------------------------------------------------------------------
@@ -185,32 +439,144 @@ __global__ void group_stats_norm_kernel(const float* __restrict__ x, int64_t n_g
     }
 }
 
-// out = x + (prev - x) * coef with prev = the previous row (row 0: state), 0 at new starts
+// The same statistics for groups of `cnt` contiguous values with l == 1, cnt a multiple of 4 and
+// 16-byte aligned groups: LPG lanes (a power of two <= 32) share a group, every lane keeps its
+// 16-byte pieces in registers between the statistics and the normalisation, so x is read once.
+template <int LPG, int NV>
+__global__ void __launch_bounds__(256)
+group_norm_regs_kernel(const float* __restrict__ x, int64_t n_groups_total, int groups, int cnt,
+                       const float* __restrict__ weight, const float* __restrict__ bias, float eps,
+                       float* __restrict__ out) {
+    constexpr int GPB = 256 / LPG;
+    const int sub = threadIdx.x / LPG, lane = threadIdx.x % LPG;
+    int64_t gidx = (int64_t)blockIdx.x * GPB + sub;
+    const bool live = gidx < n_groups_total;
+    if (!live) gidx = n_groups_total - 1;   // keep the lanes of a warp together for the shuffles
+    const int n4 = cnt / 4;
+    const float4* xg = reinterpret_cast<const float4*>(x + (size_t)gidx * cnt);
+    float4 v[NV];
+    float sum = 0.0f, sumsq = 0.0f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = lane + u * LPG;
+        v[u] = j < n4 ? xg[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+        sumsq = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, fmaf(v[u].w, v[u].w, sumsq))));
+    }
+#pragma unroll
+    for (int off = LPG / 2; off > 0; off >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        sumsq += __shfl_xor_sync(0xffffffffu, sumsq, off);
+    }
+    if (!live) return;
+    const float mean = __fdiv_rn(sum, (float)cnt);
+    const float var = __fsub_rn(__fdiv_rn(sumsq, (float)cnt), __fmul_rn(mean, mean));
+    const float sd = __fsqrt_rn(__fadd_rn(var, eps));
+    const int g = (int)(gidx % groups);
+    const float4* w4 = reinterpret_cast<const float4*>(weight + (size_t)g * cnt);
+    const float4* b4 = reinterpret_cast<const float4*>(bias + (size_t)g * cnt);
+    float4* og = reinterpret_cast<float4*>(out + (size_t)gidx * cnt);
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = lane + u * LPG;
+        if (j < n4) {
+            const float4 w = w4[j], b = b4[j];
+            float4 o;
+            o.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].x, mean), sd), w.x), b.x);
+            o.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].y, mean), sd), w.y), b.y);
+            o.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].z, mean), sd), w.z), b.z);
+            o.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].w, mean), sd), w.w), b.w);
+            og[j] = o;
+        }
+    }
+}
+
+// Launches the register-cached variant when the shape allows it; false = use the general kernel.
+static bool launch_group_norm_regs(cudaStream_t st, const float* x, int64_t total, int groups, int cnt,
+                                   const float* weight, const float* bias, float eps, float* out) {
+    if (cnt % 4 != 0 || cnt > 1024) return false;
+    if ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)weight | (uintptr_t)bias) & 15u) != 0) return false;
+    const int n4 = cnt / 4;
+#define HSES_GN(LPG, NV)                                                                                         \
+    group_norm_regs_kernel<LPG, NV><<<(unsigned)((total + 256 / LPG - 1) / (256 / LPG)), 256, 0, st>>>(          \
+        x, total, groups, cnt, weight, bias, eps, out)
+    if (n4 <= 4) HSES_GN(4, 1);
+    else if (n4 <= 8) HSES_GN(8, 1);
+    else if (n4 <= 16) HSES_GN(16, 1);
+    else if (n4 <= 32) HSES_GN(32, 1);
+    else if (n4 <= 64) HSES_GN(32, 2);
+    else if (n4 <= 128) HSES_GN(32, 4);
+    else HSES_GN(32, 8);
+#undef HSES_GN
+    return true;
+}
+
+// out = x + (prev - x) * coef with prev = the previous row (row 0: state), 0 at new starts.
+// VEC: 4 (rows and pointers 16-byte aligned, c a multiple of 4) or 1.
+template <int VEC>
 __global__ void token_shift_mix_kernel(const float* __restrict__ x, int T, int c, const float* __restrict__ state,
                                        const uint8_t* __restrict__ new_starts, const float* __restrict__ coef,
                                        float* __restrict__ out) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= (int64_t)T * c) return;
     int t = (int)(i / c), j = (int)(i - (int64_t)t * c);
-    float prev = t == 0 ? state[j] : x[i - c];
-    if (new_starts && new_starts[t]) prev = 0.0f;
-    float xv = x[i];
-    out[i] = __fadd_rn(xv, __fmul_rn(__fsub_rn(prev, xv), coef[j]));
+    const bool zero = new_starts && new_starts[t];
+    if (VEC == 4) {
+        float4 prev = t == 0 ? *reinterpret_cast<const float4*>(state + j) : *reinterpret_cast<const float4*>(x + i - c);
+        if (zero) prev = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 xv = *reinterpret_cast<const float4*>(x + i), cf = *reinterpret_cast<const float4*>(coef + j);
+        float4 o;
+        o.x = __fadd_rn(xv.x, __fmul_rn(__fsub_rn(prev.x, xv.x), cf.x));
+        o.y = __fadd_rn(xv.y, __fmul_rn(__fsub_rn(prev.y, xv.y), cf.y));
+        o.z = __fadd_rn(xv.z, __fmul_rn(__fsub_rn(prev.z, xv.z), cf.z));
+        o.w = __fadd_rn(xv.w, __fmul_rn(__fsub_rn(prev.w, xv.w), cf.w));
+        *reinterpret_cast<float4*>(out + i) = o;
+    } else {
+        float prev = t == 0 ? state[j] : x[i - c];
+        if (zero) prev = 0.0f;
+        float xv = x[i];
+        out[i] = __fadd_rn(xv, __fmul_rn(__fsub_rn(prev, xv), coef[j]));
+    }
 }
 
-__global__ void relu_square_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
-    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float v = x[i] > 0.0f ? x[i] : 0.0f;
-    out[i] = __fmul_rn(v, v);
-}
-
+struct ReluSquareOp {
+    __device__ __forceinline__ float operator()(float x) const {
+        float v = x > 0.0f ? x : 0.0f;
+        return __fmul_rn(v, v);
+    }
+};
 // rate_encode, snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|))
-__global__ void rate_encode_kernel(const float* __restrict__ p, int64_t n, float gain, float* __restrict__ out) {
+struct RateEncodeOp {
+    float gain;
+    __device__ __forceinline__ float operator()(float p) const {
+        float ss = __fdiv_rn(p, __fadd_rn(fabsf(p), 1.0f));
+        return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(ss, gain))));
+    }
+};
+// out[i] = op(x[i]): one 16-byte piece per thread when VEC4 (aligned pointers), the n % 4 tail
+// one value per thread
+template <bool VEC4, class Op>
+__global__ void map_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out, Op op) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float ss = __fdiv_rn(p[i], __fadd_rn(fabsf(p[i]), 1.0f));
-    out[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__fmul_rn(ss, gain))));
+    if (VEC4) {
+        const int64_t n4 = n / 4;
+        if (i < n4) {
+            const float4 v = reinterpret_cast<const float4*>(x)[i];
+            reinterpret_cast<float4*>(out)[i] = make_float4(op(v.x), op(v.y), op(v.z), op(v.w));
+            return;
+        }
+        i = n4 * 4 + (i - n4);
+    }
+    if (i < n) out[i] = op(x[i]);
+}
+template <class Op>
+static void launch_map(cudaStream_t st, const float* x, int64_t n, float* out, Op op) {
+    if (((((uintptr_t)x | (uintptr_t)out) & 15u) == 0) && n >= 4) {
+        int64_t work = n / 4 + n % 4;
+        map_kernel<true, Op><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(x, n, out, op);
+    } else {
+        map_kernel<false, Op><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, out, op);
+    }
 }
 
 }  // namespace hses
@@ -229,12 +595,14 @@ int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w,
     if (n_seq == 0) return HSES_OK;
     HSES_REQUIRE(r && w && k && v && a && b && state && out, "NULL pointer");
     HSES_REQUIRE(((uintptr_t)state & 15u) == 0, "state must be 16-byte aligned");
+    HSES_REQUIRE((((uintptr_t)r | (uintptr_t)w | (uintptr_t)k | (uintptr_t)v | (uintptr_t)a | (uintptr_t)b |
+                   (uintptr_t)out) & 7u) == 0, "r, w, k, v, a, b and out must be 8-byte aligned");
     HSES_KERNEL(ctx, as_stream(stream), "wkv7");
     unsigned grid = (unsigned)(n_seq * H);
     if (S == 64)
-        wkv7_kernel<64><<<grid, 64, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
+        wkv7_kernel<64><<<grid, 32, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
     else
-        wkv7_kernel<32><<<grid, 32, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
+        wkv7_kernel<32><<<grid, 16, 0, as_stream(stream)>>>(r, w, k, v, a, b, new_starts, T, H, state, out);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -255,6 +623,23 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
     int threads = (tokens + 31) / 32 * 32;
     size_t smem = (size_t)2 * tokens * head_dim * sizeof(float);
     HSES_KERNEL(ctx, as_stream(stream), "spiking_attention");
+    const bool aligned = ((((uintptr_t)Q | (uintptr_t)K | (uintptr_t)V | (uintptr_t)O) & 15u) == 0) && row_stride % 4 == 0;
+    if (mode == 0 && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64)) {
+        unsigned grid = (unsigned)(n_seq * heads);
+        cudaStream_t st = as_stream(stream);
+        const int threads2 = ((tokens + 1) / 2 + 31) / 32 * 32;   // two query rows per thread
+        const size_t smem_packed = ((size_t)head_dim * ((tokens + 3) / 4 * 4 + 4) + (size_t)tokens * head_dim) * sizeof(float);
+        if (head_dim == 16)
+            attention_product_packed_kernel<16><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
+                                                                                     beta, O, A_out);
+        else if (head_dim == 32)
+            attention_product_packed_kernel<32><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
+                                                                                     beta, O, A_out);
+        else
+            attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, O, A_out);
+        HSES_LAUNCH_CHECK();
+        return HSES_OK;
+    }
     spiking_attention_kernel<<<(unsigned)(n_seq * heads), threads, smem, as_stream(stream)>>>(
         Q, K, V, tokens, heads, head_dim, row_stride, mode, beta, tau_m, v_th, g_inh, n_iter, O, A_out);
     HSES_LAUNCH_CHECK();
@@ -268,6 +653,10 @@ int hses_layer_norm(hses_ctx* ctx, hses_stream stream, const float* x, int64_t r
     if (rows == 0) return HSES_OK;
     HSES_REQUIRE(x != nullptr && weight != nullptr && bias != nullptr && out != nullptr, "NULL pointer");
     HSES_KERNEL(ctx, as_stream(stream), "layer_norm");
+    if (launch_group_norm_regs(as_stream(stream), x, rows, 1, c, weight, bias, eps, out)) {
+        HSES_LAUNCH_CHECK();
+        return HSES_OK;
+    }
     group_stats_norm_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, as_stream(stream)>>>(x, rows, 1, c, 1, weight, bias,
                                                                                       eps, out);
     HSES_LAUNCH_CHECK();
@@ -282,6 +671,10 @@ int hses_group_norm(hses_ctx* ctx, hses_stream stream, const float* x, int64_t n
     HSES_REQUIRE(x != nullptr && weight != nullptr && bias != nullptr && out != nullptr, "NULL pointer");
     int64_t total = n * groups;
     HSES_KERNEL(ctx, as_stream(stream), "group_norm");
+    if (l == 1 && launch_group_norm_regs(as_stream(stream), x, total, groups, c / groups, weight, bias, eps, out)) {
+        HSES_LAUNCH_CHECK();
+        return HSES_OK;
+    }
     group_stats_norm_kernel<<<(unsigned)((total + 7) / 8), 256, 0, as_stream(stream)>>>(x, total, groups, c / groups, l,
                                                                                        weight, bias, eps, out);
     HSES_LAUNCH_CHECK();
@@ -297,8 +690,14 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x, int3
     HSES_REQUIRE(x != out, "token_shift_mix cannot run in place");
     int64_t n = (int64_t)T * c;
     HSES_KERNEL(ctx, as_stream(stream), "token_shift_mix");
-    token_shift_mix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state, new_starts, coef,
-                                                                                      out);
+    const bool vec4 = c % 4 == 0 &&
+                      ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)state | (uintptr_t)coef) & 15u) == 0);
+    if (vec4)
+        token_shift_mix_kernel<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state,
+                                                                                                 new_starts, coef, out);
+    else
+        token_shift_mix_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state,
+                                                                                             new_starts, coef, out);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -309,7 +708,7 @@ int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x, int64_t 
     if (n == 0) return HSES_OK;
     HSES_REQUIRE(x != nullptr && out != nullptr, "NULL pointer");
     HSES_KERNEL(ctx, as_stream(stream), "relu_square");
-    relu_square_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, n, out);
+    launch_map(as_stream(stream), x, n, out, ReluSquareOp{});
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -321,7 +720,7 @@ int hses_rate_encode(hses_ctx* ctx, hses_stream stream, const float* p, int64_t 
     if (n == 0) return HSES_OK;
     HSES_REQUIRE(p != nullptr && out != nullptr, "NULL pointer");
     HSES_KERNEL(ctx, as_stream(stream), "rate_encode");
-    rate_encode_kernel<<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(p, n, gain, out);
+    launch_map(as_stream(stream), p, n, out, RateEncodeOp{gain});
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -52,7 +52,8 @@ def test_wkv7_matches_oracle(hs, oracle, n_seq, T, H, S):
 
 
 @pytest.mark.parametrize("mode", [0, 1])
-@pytest.mark.parametrize("n_seq,tokens,heads,hd", [(2, 64, 4, 16), (3, 16, 1, 8), (1, 50, 2, 64)])
+@pytest.mark.parametrize("n_seq,tokens,heads,hd", [(2, 64, 4, 16), (3, 16, 1, 8), (1, 50, 2, 64), (2, 50, 2, 32),
+                                                   (1, 7, 3, 16), (1, 128, 1, 32)])
 def test_spiking_attention_matches_oracle(hs, oracle, mode, n_seq, tokens, heads, hd):
     from hyperscalees_b200 import ops
     g = np.random.default_rng(tokens + hd)
@@ -69,6 +70,9 @@ def test_spiking_attention_matches_oracle(hs, oracle, mode, n_seq, tokens, heads
                                               2.0, 0.3, 0.5, 8)
             assert np.array_equal(A[s, h], wa) or np.abs(A[s, h] - wa).max() <= 1e-6
             assert np.abs(O[s][:, sl] - wo).max() <= 1e-5 * max(1.0, np.abs(wo).max())
+            if mode == 0:
+                # rates that are multiples of 1/4: every score is exact, with or without fused multiply-adds
+                assert np.array_equal(A[s, h], wa)
     if mode == 1:
         rows = A.sum(-1)
         assert ((np.abs(rows - 1.0) < 1e-4) | (rows == 0.0)).all()  # a row sums to one whenever any key fired
