@@ -304,6 +304,154 @@ attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ 
             make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
 }
 
+// Modes 1 and 2 for head sizes 16/32/64 with 16-byte aligned rows.  Same operations in the same
+// order as the general kernel (two roundings per multiply-add: these modes end in threshold
+// decisions or a softmax), but q and the output row live in registers, K and V are read back as
+// 16-byte broadcasts, and the per-row arrays (scores, potentials, counts) sit in shared memory
+// with an odd pitch instead of local memory.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                      int tokens, int heads, int64_t row_stride, int mode, float beta, float tau_m, float v_th,
+                      float g_inh, int n_iter, float* __restrict__ O, float* __restrict__ A_out) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int D4 = D / 4;
+    const int pitch = tokens + 1;
+    float4* ks4 = reinterpret_cast<float4*>(sm);
+    float4* vs4 = ks4 + tokens * D4;
+    float* hs = sm + 2 * tokens * D;
+    float* us = hs + tokens * pitch;
+    float* cs = us + tokens * pitch;   // mode 1 only
+    const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
+    for (int e = threadIdx.x; e < tokens * D4; e += blockDim.x) {
+        int tk = e / D4, c4 = e - tk * D4;
+        ks4[e] = *reinterpret_cast<const float4*>(K + base + (size_t)tk * row_stride + c4 * 4);
+        vs4[e] = *reinterpret_cast<const float4*>(V + base + (size_t)tk * row_stride + c4 * 4);
+    }
+    __syncthreads();
+    const int i = threadIdx.x;
+    if (i >= tokens) return;
+    float q[D];
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4) {
+        float4 v = *reinterpret_cast<const float4*>(Q + base + (size_t)i * row_stride + c4 * 4);
+        q[4 * c4] = v.x; q[4 * c4 + 1] = v.y; q[4 * c4 + 2] = v.z; q[4 * c4 + 3] = v.w;
+    }
+    float* hrow = hs + i * pitch;
+    float* u = us + i * pitch;
+    float* cnt = cs + i * pitch;
+    float amax = 0.0f;
+    for (int j0 = 0; j0 < tokens; j0 += 4) {
+        float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int c4 = 0; c4 < D4; ++c4) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int j = j0 + k < tokens ? j0 + k : tokens - 1;
+                const float4 kv = ks4[j * D4 + c4];
+                sc[k] = __fadd_rn(sc[k], __fmul_rn(q[4 * c4], kv.x));
+                sc[k] = __fadd_rn(sc[k], __fmul_rn(q[4 * c4 + 1], kv.y));
+                sc[k] = __fadd_rn(sc[k], __fmul_rn(q[4 * c4 + 2], kv.z));
+                sc[k] = __fadd_rn(sc[k], __fmul_rn(q[4 * c4 + 3], kv.w));
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (j0 + k < tokens) {
+                const float hv = __fmul_rn(beta, sc[k]);
+                hrow[j0 + k] = hv;
+                amax = fmaxf(amax, fabsf(hv));
+            }
+    }
+    if (mode == 1) {
+        const float inv = __fadd_rn(amax, 1e-6f);
+        const float leak = 1.0f / tau_m;
+        for (int j = 0; j < tokens; ++j) {
+            hrow[j] = __fdiv_rn(hrow[j], inv);
+            u[j] = 0.0f;
+            cnt[j] = 0.0f;
+        }
+        // the counts are small integers: their sum is exact in any order, so the inhibition of
+        // an iteration is the running number of spikes before it
+        float G = 0.0f;
+        for (int it = 0; it < n_iter; ++it) {
+            const float inh = __fmul_rn(g_inh, G);
+            for (int j = 0; j < tokens; ++j) {
+                const float uj = u[j];
+                float cur = __fsub_rn(hrow[j], inh);
+                float c = __fadd_rn(uj, __fmul_rn(__fadd_rn(-uj, cur), leak));
+                float sp = c >= v_th ? 1.0f : 0.0f;
+                u[j] = __fmul_rn(c, __fadd_rn(-sp, 1.0f));
+                cnt[j] = __fadd_rn(cnt[j], sp);
+                G = __fadd_rn(G, sp);
+            }
+        }
+        const float tot = __fadd_rn(G, 1e-6f);
+        for (int j = 0; j < tokens; ++j) hrow[j] = __fdiv_rn(cnt[j], tot);
+    } else {
+        // continuous Hopfield relaxation then a stable softmax along the keys
+        // (hyperscalees-models/src/snn_transformer.rs:80-102)
+        const float one_over_tau = 1.0f / tau_m;
+        for (int j = 0; j < tokens; ++j) u[j] = hrow[j];
+        for (int it = 0; it < n_iter; ++it) {
+            float m = 0.0f;
+            for (int j = 0; j < tokens; ++j) m = __fadd_rn(m, u[j]);
+            m = __fdiv_rn(m, (float)tokens);
+            const float inh = __fmul_rn(m, g_inh);
+            for (int j = 0; j < tokens; ++j) {
+                const float uj = u[j];
+                u[j] = __fadd_rn(uj, __fmul_rn(__fsub_rn(__fadd_rn(-uj, hrow[j]), inh), one_over_tau));
+            }
+        }
+        float mx = u[0];
+        for (int j = 1; j < tokens; ++j) mx = fmaxf(mx, u[j]);
+        float tot = 0.0f;
+        for (int j = 0; j < tokens; ++j) {
+            const float e = expf(__fsub_rn(u[j], mx));
+            u[j] = e;
+            tot = __fadd_rn(tot, e);
+        }
+        tot = __fadd_rn(tot, 1e-6f);
+        for (int j = 0; j < tokens; ++j) hrow[j] = __fdiv_rn(u[j], tot);
+    }
+    float* arow = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i) * tokens : nullptr;
+    float acc[D];
+#pragma unroll
+    for (int c = 0; c < D; ++c) acc[c] = 0.0f;
+    for (int j = 0; j < tokens; ++j) {
+        const float hj = hrow[j];
+        if (arow) arow[j] = hj;
+#pragma unroll
+        for (int c4 = 0; c4 < D4; ++c4) {
+            const float4 vv = vs4[j * D4 + c4];
+            acc[4 * c4] = __fadd_rn(acc[4 * c4], __fmul_rn(hj, vv.x));
+            acc[4 * c4 + 1] = __fadd_rn(acc[4 * c4 + 1], __fmul_rn(hj, vv.y));
+            acc[4 * c4 + 2] = __fadd_rn(acc[4 * c4 + 2], __fmul_rn(hj, vv.z));
+            acc[4 * c4 + 3] = __fadd_rn(acc[4 * c4 + 3], __fmul_rn(hj, vv.w));
+        }
+    }
+#pragma unroll
+    for (int c4 = 0; c4 < D4; ++c4)
+        *reinterpret_cast<float4*>(O + base + (size_t)i * row_stride + c4 * 4) =
+            make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+}
+
+template <int D>
+static cudaError_t launch_attention_rows(cudaStream_t st, unsigned grid, int threads, size_t smem, const float* Q,
+                                         const float* K, const float* V, int tokens, int heads, int64_t row_stride,
+                                         int mode, float beta, float tau_m, float v_th, float g_inh, int n_iter,
+                                         float* O, float* A_out) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    attention_rows_kernel<D><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, mode, beta, tau_m, v_th,
+                                                          g_inh, n_iter, O, A_out);
+    return cudaSuccess;
+}
+
 // The same for head sizes 16 and 32 on packed pairs.  The kernel above is bound by the rate at
 // which shared memory feeds registers (every thread reads all of K and V: 128 bytes per cycle and
 // SM), so here a thread owns TWO query rows and every 16-byte piece of K or V it loads feeds four
@@ -637,6 +785,25 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
                                                                                      beta, O, A_out);
         else
             attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, O, A_out);
+        HSES_LAUNCH_CHECK();
+        return HSES_OK;
+    }
+    const size_t smem_rows = ((size_t)2 * tokens * head_dim + (size_t)(mode == 1 ? 3 : 2) * tokens * (tokens + 1)) *
+                             sizeof(float);
+    if (mode != 0 && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64) && smem_rows <= 200 * 1024) {
+        unsigned grid = (unsigned)(n_seq * heads);
+        cudaStream_t st = as_stream(stream);
+        cudaError_t e;
+        if (head_dim == 16)
+            e = launch_attention_rows<16>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+                                          tau_m, v_th, g_inh, n_iter, O, A_out);
+        else if (head_dim == 32)
+            e = launch_attention_rows<32>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+                                          tau_m, v_th, g_inh, n_iter, O, A_out);
+        else
+            e = launch_attention_rows<64>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+                                          tau_m, v_th, g_inh, n_iter, O, A_out);
+        HSES_REQUIRE(e == cudaSuccess, "cudaFuncSetAttribute failed");
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
