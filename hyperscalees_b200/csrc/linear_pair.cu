@@ -39,6 +39,7 @@ struct PairArgs {
     int kc;            // rows of B per pass, a multiple of 4 * kslices
     int kslices;       // k-slices a pass is split into (threads per slice: (RMAX / 8) * (rank / 8))
     int a_in_smem;     // A of the pair is copied to shared memory while t is computed
+    int a_swz;         // ... as 32-column boxes with the 128-byte swizzle (tensor map tm_a)
     int32_t first_thread;
     int32_t pair0;     // absolute index of the pair handled by block 0
     const float* A;    // raw (pairs, a, rank) from pair0 on
@@ -72,7 +73,8 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 // copied to shared memory in the background when it fits.
 template <int RMAX>
 __global__ void __launch_bounds__(PP_THREADS, 2)
-pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) {
+pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_a,
+                    const PairArgs g) {
     extern __shared__ __align__(128) float smem[];
     __shared__ int64_t row_s[32];
     __shared__ int odd_s[32];                 // the row's member has an odd thread id: A is negated
@@ -92,6 +94,10 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
     float* bbuf = smem + PP_STAGES * RMAX * xp;         // [PP_STAGES][kc][rank]; later the k-slice sums
     float* red = bbuf;                                  // [kslices][RMAX][rank]; slice 0 becomes t
     float* as = bbuf + (bbuf_floats > red_floats ? bbuf_floats : red_floats);  // [a][rank] when a_in_smem
+    // swizzled form: rank/32 boxes of [a][32], each starting on a 1024-byte boundary so that the
+    // 16-byte piece c of row n sits at piece c ^ (n & 7)
+    const int bstride = ((a * 128 + 1023) / 1024) * 256;   // floats between boxes
+    if (g.a_swz) as += ((1024u - (smem_u32(as) & 1023u)) & 1023u) / 4;
     const int32_t pair = g.pair0 + blockIdx.x;
     int64_t m_lo = (int64_t)pair * 2 - g.first_thread, m_hi = m_lo + 2;
     if (m_lo < 0) m_lo = 0;
@@ -129,7 +135,11 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
     };
     if (tid == 0) {
         fence_proxy_async();  // the zero fill above precedes the copy engine's writes
-        if (g.a_in_smem) {
+        if (g.a_swz) {
+            mbar_expect_tx(&bars[PP_STAGES], (uint32_t)(a * rank * 4));
+            for (int b = 0; b < rank / 32; ++b)
+                tma_load_2d(as + (size_t)b * bstride, &tm_a, 32 * b, (int)blockIdx.x * a, &bars[PP_STAGES]);
+        } else if (g.a_in_smem) {
             mbar_expect_tx(&bars[PP_STAGES], (uint32_t)(a * rank * 4));
             bulk_load(as, Ap, (uint32_t)(a * rank * 4), &bars[PP_STAGES]);
         }
@@ -203,11 +213,41 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
             *reinterpret_cast<float4*>(dst + q_hi) = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
         }
     }
+    // clean product under this thread's outputs of the second phase (swizzled form, first round of
+    // tasks): fetched here so that its latency hides behind the k-slice sums
+    constexpr int RGROUPS = RMAX / 8;
+    float base0[4][2];
+    auto load_base = [&](int task, float (&bs)[4][2]) {
+        const int rh = task & 1, rest = task >> 1;
+        const int rgp = rest % RGROUPS, cb = rest / RGROUPS;
+        const int nc0 = cb * 64 + (tid & 31);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int r = rgp * 8 + rh * 4 + jj;
+            const float* orow = g.out + (size_t)row_s[r < rows ? r : 0] * g.out_stride;
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+                const int n = nc0 + 32 * c2;
+                bs[jj][c2] = (r < rows && n < a) ? orow[n] : 0.0f;
+            }
+        }
+    };
+    const int tasks2 = RGROUPS * ((a + 63) >> 6) * 2;
+    if (g.a_swz && (tid >> 5) < tasks2) load_base(tid >> 5, base0);
     __syncthreads();
-    for (int e = tid; e < RMAX * rank; e += (int)blockDim.x) {
-        float sum = red[e];
-        for (int p = 1; p < kslices; ++p) sum += red[(size_t)p * RMAX * rank + e];
-        red[e] = sum;  // t[r][q], r = e / rank
+    {
+        // 16 bytes per thread and several slices in flight: the additions of an element keep their order
+        const int tot4 = RMAX * rank / 4;
+        float4* red4 = reinterpret_cast<float4*>(red);
+        for (int e4 = tid; e4 < tot4; e4 += (int)blockDim.x) {
+            float4 sum = red4[e4];
+#pragma unroll 4
+            for (int p = 1; p < kslices; ++p) {
+                const float4 v = red4[(size_t)p * tot4 + e4];
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            red4[e4] = sum;  // t[r][q], r = e / rank
+        }
     }
     if (g.a_in_smem && ok) ok = mbar_wait(&bars[PP_STAGES], 0, abort_flag, g.status, 21);
     __syncthreads();
@@ -224,6 +264,107 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const PairArgs g) 
     }
     const float* ts = red;
     tick(2);
+
+    if (g.a_swz) {
+        // ---- u = t * (s*A)ᵀ, swizzled A.  A warp takes a task = (8 rows, 64 columns, half of the
+        // rank); a lane owns columns lane and lane + 32 of the block, so the A pieces of a load are
+        // 32 different rows of one box column (conflict-free through the swizzle) and the t pieces
+        // are broadcasts: 10 loads feed 64 multiply-adds.  The two rank halves of a tile swap four
+        // rows each through shared memory and finish four rows each. ----
+        const float gain = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
+        const int nwarps = (int)blockDim.x >> 5, wid = tid >> 5, lane = tid & 31;
+        const int tasks = tasks2;
+        const int halfq = rank >> 3;              // 16-byte pieces per rank half
+        float* xch = red + RMAX * rank;           // [warp][lane][8]
+        for (int t0 = 0; t0 < tasks; t0 += nwarps) {
+            const int task = t0 + wid;
+            const bool live = task < tasks;
+            const int rh = task & 1, rest = task >> 1;
+            const int rgp = rest % RGROUPS, cb = rest / RGROUPS;
+            const int nc0 = cb * 64 + lane;       // columns nc0 and nc0 + 32
+            float acc[8][2], base[4][2];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = 0.0f;
+            if (live) {
+                if (t0 == 0) {
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) base[jj][0] = base0[jj][0], base[jj][1] = base0[jj][1];
+                } else {
+                    load_base(task, base);
+                }
+                const int n_a = nc0 < a ? nc0 : a - 1, n_b = nc0 + 32 < a ? nc0 + 32 : a - 1;
+                const float* trow = ts + (size_t)rgp * 8 * rank;
+                for (int i = 0; i < halfq; ++i) {
+                    const int q4 = rh * halfq + i;
+                    const float* box = as + (size_t)(q4 >> 3) * bstride;
+                    const int c = q4 & 7;
+                    const float4 va = *reinterpret_cast<const float4*>(box + n_a * 32 + ((c ^ (n_a & 7)) << 2));
+                    const float4 vb = *reinterpret_cast<const float4*>(box + n_b * 32 + ((c ^ (n_b & 7)) << 2));
+                    const float s = g.base_sigma;
+                    const float4 sa4 = make_float4(__fmul_rn(va.x, s), __fmul_rn(va.y, s), __fmul_rn(va.z, s), __fmul_rn(va.w, s));
+                    const float4 sb4 = make_float4(__fmul_rn(vb.x, s), __fmul_rn(vb.y, s), __fmul_rn(vb.z, s), __fmul_rn(vb.w, s));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 tv = *reinterpret_cast<const float4*>(trow + (size_t)j * rank + q4 * 4);
+                        acc[j][0] = fmaf(tv.x, sa4.x, acc[j][0]);
+                        acc[j][0] = fmaf(tv.y, sa4.y, acc[j][0]);
+                        acc[j][0] = fmaf(tv.z, sa4.z, acc[j][0]);
+                        acc[j][0] = fmaf(tv.w, sa4.w, acc[j][0]);
+                        acc[j][1] = fmaf(tv.x, sb4.x, acc[j][1]);
+                        acc[j][1] = fmaf(tv.y, sb4.y, acc[j][1]);
+                        acc[j][1] = fmaf(tv.z, sb4.z, acc[j][1]);
+                        acc[j][1] = fmaf(tv.w, sb4.w, acc[j][1]);
+                    }
+                }
+                // hand the other half's rows over
+                float4* xo = reinterpret_cast<float4*>(xch + ((size_t)wid * 32 + lane) * 8);
+                float o[8];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {   // static register indices: select with the half bit
+                    o[2 * jj] = rh ? acc[jj][0] : acc[4 + jj][0];
+                    o[2 * jj + 1] = rh ? acc[jj][1] : acc[4 + jj][1];
+                }
+                xo[0] = make_float4(o[0], o[1], o[2], o[3]);
+                xo[1] = make_float4(o[4], o[5], o[6], o[7]);
+            }
+            __syncthreads();
+            if (live) {
+                const float4* xi = reinterpret_cast<const float4*>(xch + ((size_t)(wid ^ 1) * 32 + lane) * 8);
+                const float4 p0 = xi[0], p1 = xi[1];
+                const float other[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int r = rgp * 8 + rh * 4 + jj;
+                    if (r < rows) {
+                        const int64_t R = row_s[r];
+                        const bool odd = odd_s[r] != 0;
+                        float* orow = g.out + (size_t)R * g.out_stride;
+                        float* prow = g.pot ? g.pot + (size_t)R * g.out_stride : nullptr;
+#pragma unroll
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            const int n = nc0 + 32 * c2;
+                            if (n < a) {
+                                const float mine = rh ? acc[4 + jj][c2] : acc[jj][c2];
+                                // the lower rank half first, whichever warp finishes the row
+                                const float u = rh ? __fadd_rn(other[2 * jj + c2], mine) : __fadd_rn(mine, other[2 * jj + c2]);
+                                float y = __fadd_rn(base[jj][c2], odd ? -u : u);
+                                if (g.lif) {
+                                    float cpot = __fmul_rn(y, g.leak);
+                                    if (prow) prow[n] = cpot;
+                                    orow[n] = cpot >= g.v_th ? 1.0f : 0.0f;
+                                } else {
+                                    orow[n] = __fmul_rn(y, gain);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (t0 + nwarps < tasks) __syncthreads();   // the exchange buffer is reused by the next round
+        }
+        tick(4);
+        return;
+    }
 
     // ---- u = t * (s*A)ᵀ and the final transform of the rows.  A thread owns 4 rows x NC
     // consecutive output columns; the clean product of its outputs is fetched first so that its
@@ -331,11 +472,25 @@ int rmax_of(const hses_linear_args& g) {
     return rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
 }
 
+// A goes to shared memory as swizzled 32-column boxes (conflict-free column-per-lane reads in the
+// second phase) when the rank is a multiple of 32, a box holds all rows (<= 256) and the
+// exchange buffer of that phase fits behind t in the k-slice area
+size_t a_swz_floats(const hses_linear_args& g) {
+    return (size_t)(g.rank / 32) * (((size_t)g.a * 128 + 1023) / 1024 * 256);
+}
+bool a_swizzled(int rmax, const hses_linear_args& g) {
+    if (!a_fits(g) || g.rank % 32 != 0 || g.a > 256) return false;
+    int kc = kc_of(rmax, g.rank), kslices = kslices_of(rmax, g.rank);
+    size_t bbuf = (size_t)PP_STAGES * kc * g.rank, red = (size_t)kslices * rmax * g.rank;
+    size_t area = bbuf > red ? bbuf : red;
+    return (size_t)rmax * g.rank + (size_t)threads_of(rmax) * 8 <= area && a_swz_floats(g) <= 2 * (size_t)PP_A_SMEM_FLOATS;
+}
+
 size_t pair_smem_bytes(int rmax, const hses_linear_args& g) {
     int kc = kc_of(rmax, g.rank), kslices = kslices_of(rmax, g.rank);
     size_t bbuf = (size_t)PP_STAGES * kc * g.rank, red = (size_t)kslices * rmax * g.rank;
-    size_t fl = (size_t)PP_STAGES * rmax * kc + (bbuf > red ? bbuf : red) +
-                (a_fits(g) ? (size_t)g.a * g.rank : 0);
+    size_t afl = a_swizzled(rmax, g) ? a_swz_floats(g) + 256 : (a_fits(g) ? (size_t)g.a * g.rank : 0);
+    size_t fl = (size_t)PP_STAGES * rmax * kc + (bbuf > red ? bbuf : red) + afl;
     return fl * sizeof(float);
 }
 
@@ -439,6 +594,7 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     pa.kc = kc_of(rmax, g.rank);
     pa.kslices = kslices_of(rmax, g.rank);
     pa.a_in_smem = a_fits(g) ? 1 : 0;
+    pa.a_swz = a_swizzled(rmax, g) ? 1 : 0;
     pa.status = ctx->t.status_word;
     pa.dbg = nullptr;
     if (getenv("HSES_TC_DEBUG")) {
@@ -447,19 +603,35 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         pa.dbg = reinterpret_cast<unsigned long long*>(dp);
     }
     auto launch = [&](int64_t n_pairs) -> int {
+        // A of the launch's pairs as (rank, pairs * a); a box is 32 columns of all rows of one pair
+        CUtensorMap tm_a = tm_x;   // a valid map also when the swizzled form is not used
+        if (pa.a_swz) {
+            EncodeTiledFn fn = encode_fn();
+            cuuint64_t dims[2] = {(cuuint64_t)g.rank, (cuuint64_t)n_pairs * g.a};
+            cuuint64_t strides[1] = {(cuuint64_t)g.rank * 4};
+            cuuint32_t box[2] = {32, (cuuint32_t)g.a};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = fn(&tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(pa.A), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) {
+                set_error("cuTensorMapEncodeTiled (A of a pair) failed with code " + std::to_string((int)r));
+                return HSES_ERR_CUDA;
+            }
+        }
         HSES_KERNEL(ctx, st, "pair_lowrank");
         switch (rmax) {
             case 8:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<8><<<(unsigned)n_pairs, threads_of(8), smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<8><<<(unsigned)n_pairs, threads_of(8), smem, st>>>(tm_x, tm_a, pa);
                 break;
             case 16:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<16><<<(unsigned)n_pairs, threads_of(16), smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<16><<<(unsigned)n_pairs, threads_of(16), smem, st>>>(tm_x, tm_a, pa);
                 break;
             default:
                 HSES_CUDA(cudaFuncSetAttribute(pair_lowrank_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                pair_lowrank_kernel<32><<<(unsigned)n_pairs, threads_of(32), smem, st>>>(tm_x, pa);
+                pair_lowrank_kernel<32><<<(unsigned)n_pairs, threads_of(32), smem, st>>>(tm_x, tm_a, pa);
                 break;
         }
         HSES_LAUNCH_CHECK();

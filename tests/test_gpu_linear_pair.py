@@ -16,6 +16,9 @@ pytestmark = pytest.mark.gpu
     (4, 2, 36, 50, 8, 3, 4),        # 12 rows per pair, general base product
     (2, 16, 64, 40, 128, 1, 0),     # 32 rows per pair, rank 128
     (4, 1, 20, 1100, 8, 2, 0),      # more output column groups than threads, A too large for shared memory
+    (6, 1, 128, 200, 32, 8, 0),     # swizzled A: four column blocks (two rounds of warp tasks), ragged last block
+    (4, 4, 64, 100, 64, 2, 2),      # swizzled A, 16 rows per pair, a not a multiple of 8
+    (2, 2, 40, 256, 32, 8, 0),      # swizzled A, 32 rows per pair, the largest box (256 rows)
 ])
 def test_pair_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
