@@ -443,6 +443,10 @@ def run_streaming_kernels(args, local_rank: int):
     cases[f"solver_step AdamW [{(1 << 26) // sh} params]"] = (
         lambda: ops.solver_step(ops.ADAMW, 1, par, grd, m1, m2, weight_decay=0.01), 7 * par.numel() * 4)
 
+    noise = torch.empty((1 << 28) // sh, device=dev)
+    cases[f"prng_normal_half [{noise.numel()} normals]"] = (
+        lambda: ops.prng_normal_half(noise.numel() // 128, 0.0, 1.0, (1, 2, 3, 4), out=noise), noise.numel() * 4)
+
     peaks = measured_peaks()
     sampler = ClockSampler(local_rank)
     ctx.profile_enable(True)

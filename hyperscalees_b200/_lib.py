@@ -29,7 +29,7 @@ EXPORTS = [
     "hses_factor_cache_bytes", "hses_factor_cache_build", "hses_es_update_ex",
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
-    "hses_einsum_pair_workspace_bytes", "hses_einsum_pair", "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
+    "hses_prng_normal_half", "hses_einsum_pair_workspace_bytes", "hses_einsum_pair", "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
 ]
 
 
@@ -152,6 +152,7 @@ def load():
                                          vp, sz]
     L.hses_convert_fitnesses_bs.argtypes = [vp, vp, vp, i64, i32, vp, vp]
     L.hses_vector_mul.argtypes = [vp, vp, vp, vp, vp, i64]
+    L.hses_prng_normal_half.argtypes = [vp, vp, vp, i64, C.c_float, C.c_float, C.POINTER(C.c_uint32)]
     L.hses_einsum_pair_workspace_bytes.restype = sz
     L.hses_einsum_pair_workspace_bytes.argtypes = [i64, i32, i32, i32]
     L.hses_einsum_pair.argtypes = [vp, vp, vp, i64, i64, vp, i64, i64, vp, i64, i32, i32, i32, vp, vp, vp, sz]

@@ -286,6 +286,48 @@ __global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float
     }
 }
 
+// ---------------------------------------------------------------------------
+// prng_normal_half (hyperscalees-kernels/src/lib.rs:26-143, wrapper oxide.rs:233-275): reference
+// thread t owns out[128t, 128t+128); its four state words start at 1000000007*t + seed_j, every
+// uniform advances three Tausworthe generators and one LCG, a Box-Muller pair keeps cos and sin.
+// The integer stream and the uniforms are exact; ln/sqrt/cos/sin are the device functions.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t taus_step(uint32_t z, int s1, int s2, int s3, uint32_t m) {
+    uint32_t b = ((z << s1) ^ z) >> s2;
+    return ((z & m) << s3) ^ b;
+}
+__device__ __forceinline__ float taus_unit(uint32_t (&st)[4]) {
+    st[0] = taus_step(st[0], 13, 19, 12, 4294967294u);
+    st[1] = taus_step(st[1], 2, 25, 4, 4294967288u);
+    st[2] = taus_step(st[2], 3, 11, 17, 4294967280u);
+    st[3] = st[3] * 1664525u + 1013904223u;
+    uint32_t r = st[0] ^ st[1] ^ st[2] ^ st[3];
+    return __fdiv_rn(__fadd_rn((float)(r >> 9), 1.0f), 8388609.0f);
+}
+__global__ void prng_normal_half_kernel(float* __restrict__ out, int64_t total_threads, float mean, float sd,
+                                        uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3) {
+    int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= total_threads) return;
+    const uint32_t s = 1000000007u * (uint32_t)t;
+    uint32_t st[4] = {s + s0, s + s1, s + s2, s + s3};
+    float4* dst = reinterpret_cast<float4*>(out + (size_t)t * 128);
+#pragma unroll 2
+    for (int i = 0; i < 32; ++i) {
+        float z[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float u0 = taus_unit(st), u1 = taus_unit(st);
+            const float coeff = __fmul_rn(__fsqrt_rn(__fmul_rn(logf(u0), -2.0f)), sd);
+            const float arg = __fmul_rn(__fmul_rn(2.0f, 3.14159274f), u1);
+            float sn, cs;
+            sincosf(arg, &sn, &cs);
+            z[2 * h] = __fadd_rn(__fmul_rn(cs, coeff), mean);
+            z[2 * h + 1] = __fadd_rn(__fmul_rn(sn, coeff), mean);
+        }
+        dst[i] = make_float4(z[0], z[1], z[2], z[3]);
+    }
+}
+
 static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
 // EggRollBS::convert_fitnesses (hyperscalees-noiser/src/eggroll_bs.rs:226-250), first pass: one
@@ -345,6 +387,20 @@ __global__ void vector_mul_kernel(const float* __restrict__ a, const float* __re
 using namespace hses;
 
 extern "C" {
+
+int hses_prng_normal_half(hses_ctx* ctx, hses_stream stream, float* out, int64_t total_threads, float mean,
+                          float std, const uint32_t seeds[4]) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(total_threads >= 0 && total_threads <= 0xffffffffll, "total_threads must fit 32 bits");
+    HSES_REQUIRE(seeds != nullptr, "seeds is NULL");
+    if (total_threads == 0) return HSES_OK;
+    HSES_REQUIRE(out != nullptr && aligned16(out), "out must be a 16-byte aligned device pointer");
+    HSES_KERNEL(ctx, as_stream(stream), "prng_normal_half");
+    prng_normal_half_kernel<<<(unsigned)((total_threads + 127) / 128), 128, 0, as_stream(stream)>>>(
+        out, total_threads, mean, std, seeds[0], seeds[1], seeds[2], seeds[3]);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
 
 int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs, int64_t batch,
                         int32_t in_dim, int64_t row_stride, int32_t T, const uint32_t seeds[4],

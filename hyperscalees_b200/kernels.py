@@ -34,3 +34,14 @@ def einsum_pair_fused(a_t: torch.Tensor, b_t: torch.Tensor,
     (g_raw, g_ones), each (a, b): g_raw = sum_i (s_i + s_{half+i}) A_i (x) B_i,
     g_ones = 2 * sum_i A_i (x) B_i.  The reference's `2a <= 256` limit does not apply."""
     return ops.einsum_pair(a_t, b_t, scores)
+
+
+def prng_normal_half(out: torch.Tensor, mean: float, std: float, seeds: Sequence[int]) -> None:
+    """oxide.rs:233-275: fill the contiguous 1-D tensor `out` (length a multiple of
+    N_VALUES_PER_THREAD) with N(mean, std) from the hybrid Tausworthe stream, with the four
+    seed words passed in instead of being drawn from the wall clock (oxide.rs:205-223)."""
+    if out.dim() != 1 or not out.is_contiguous():
+        raise ValueError("prng_normal_half: out must be a contiguous 1-D tensor (oxide.rs:225-232)")
+    if out.numel() % N_VALUES_PER_THREAD:
+        raise ValueError("prng_normal_half: length must be a multiple of N_VALUES_PER_THREAD")
+    ops.prng_normal_half(out.numel() // N_VALUES_PER_THREAD, mean, std, seeds, device=out.device, out=out)

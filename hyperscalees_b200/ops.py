@@ -119,6 +119,24 @@ def poisson_encode(probs: torch.Tensor, T: int, seeds: Sequence[int],
     return out
 
 
+def prng_normal_half(total_threads: int, mean: float, std: float, seeds: Sequence[int], device=None,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """total_threads * 128 normals of the hybrid Tausworthe stream (reference thread t fills
+    out[128t, 128t+128))."""
+    ctx = get_context(device)
+    n = total_threads * 128
+    if out is None:
+        out = torch.empty(n, dtype=torch.float32, device=torch.device("cuda", ctx.device))
+    else:
+        _check(out, "out", ndim=1)
+        if out.numel() != n:
+            raise ValueError("out must hold total_threads * 128 values")
+    sd = (C.c_uint32 * 4)(*[int(s) & 0xFFFFFFFF for s in seeds])
+    _lib.check(_lib.load().hses_prng_normal_half(ctx.handle, current_stream(), _ptr(out), total_threads,
+                                                 mean, std, sd))
+    return out
+
+
 def lif_scan(cur: torch.Tensor, tau_m: float, v_th: float, v: Optional[torch.Tensor] = None,
              reset_mode: int = RESET_HARD, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """cur (T, n, h) pitched -> spikes of the same layout; v (n, h) is updated in place."""

@@ -108,6 +108,15 @@ int hses_dense_noise(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t ep
                      int32_t first_thread, int64_t n_members, int32_t rows, int32_t cols,
                      float base_sigma, float* out /*device*/);
 
+/* ---- prng_normal_half, oxide.rs:233-275 / kernel hyperscalees-kernels/src/lib.rs:26-143: the
+ *      hybrid Tausworthe + LCG stream of the GPU trainer's half-noise buffers.  out holds
+ *      total_threads * 128 values (N_VALUES_PER_THREAD, lib.rs:19); reference thread t fills
+ *      out[128t, 128t+128) from states 1000000007*t + seeds[j].  Unlike the reference wrapper
+ *      (wall-clock seeds, oxide.rs:205-223) the four seed words are explicit.  The integer
+ *      stream and the uniforms are bit-exact; ln/sqrt/cos/sin are device functions. ---- */
+int hses_prng_normal_half(hses_ctx* ctx, hses_stream stream, float* out /*device*/, int64_t total_threads,
+                          float mean, float std, const uint32_t seeds[4]);
+
 /* ---- poisson_encode_fused, oxide.rs:573-625 /
  *      hyperscalees-kernels/src/poisson_encode_fused_oxide.rs:61-106.
  *      probs (batch, in_dim) pitched; out (T, batch, in_dim) with the same

@@ -159,3 +159,22 @@ def test_solver_parity(hs, oracle, kind):
         p, m, v = oracle.solver_update(kind, step, p, grad, m, v, lr=0.01, weight_decay=1e-4 if kind == 2 else 0.0)
         ops.solver_step(kind, step, dp, dev(grad), dm, dv, lr=0.01, weight_decay=1e-4 if kind == 2 else 0.0)
         assert np.allclose(dp.cpu().numpy(), p, atol=1e-6, rtol=1e-6)
+
+
+def test_prng_normal_half_matches_oracle(hs, oracle):
+    """Hybrid Tausworthe half-noise stream (hyperscalees-kernels/src/lib.rs:26-143): the integer
+    stream is exact, so every value agrees with the CPU restatement up to the device's
+    ln/sqrt/cos/sin (a few ulp of values up to ~6); moments as in the reference's own check."""
+    import torch
+    from hyperscalees_b200 import kernels
+    threads, seeds = 300, (11, 22, 33, 44)
+    out = torch.empty(threads * 128, device="cuda")
+    kernels.prng_normal_half(out, 0.5, 2.0, seeds)
+    got = out.cpu().numpy()
+    want = oracle.prng_normal_half(threads, 0.5, 2.0, seeds)
+    assert np.abs(got - want).max() <= 2e-5
+    assert (got == want).mean() > 0.5
+    z = (got - 0.5) / 2.0
+    assert abs(z.mean()) < 0.02 and abs(z.std() - 1.0) < 0.02
+    with pytest.raises(ValueError):
+        kernels.prng_normal_half(torch.empty(100, device="cuda"), 0.0, 1.0, seeds)
