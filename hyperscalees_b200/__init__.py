@@ -9,4 +9,4 @@ and CSV log of the trainer.
 """
 from . import _lib  # noqa: F401
 
-__all__ = ["core", "noiser", "models", "envs", "kernels", "ops", "parallel", "data"]
+__all__ = ["core", "noiser", "models", "snn_transformer", "envs", "kernels", "ops", "parallel", "data"]

@@ -167,7 +167,7 @@ def load():
     L.hses_population_apply.argtypes = [vp, vp, pm, C.POINTER(SolverDesc), i32, C.POINTER(vp), C.POINTER(vp),
                                         C.POINTER(vp), vp]
     L.hses_wkv7.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp]
-    L.hses_spiking_attention.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, f32, f32, f32, f32, i32,
+    L.hses_spiking_attention.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, f32, vp, f32, f32, f32, i32,
                                          vp, vp]
     for name in EXPORTS:
         fn = getattr(L, name)

@@ -149,13 +149,14 @@ wkv7_kernel(const float* __restrict__ r, const float* __restrict__ w, const floa
 constexpr int kMaxTokens = 128, kMaxHeadDim = 64;
 __global__ void spiking_attention_kernel(const float* __restrict__ Q, const float* __restrict__ K,
                                          const float* __restrict__ V, int tokens, int heads, int d,
-                                         int64_t row_stride, int mode, float beta, float tau_m, float v_th,
-                                         float g_inh, int n_iter, float* __restrict__ O,
+                                         int64_t row_stride, int mode, float beta, const float* __restrict__ beta_seq,
+                                         float tau_m, float v_th, float g_inh, int n_iter, float* __restrict__ O,
                                          float* __restrict__ A_out) {
     extern __shared__ float sm[];  // K (tokens, d) | V (tokens, d)
     float* ks = sm;
     float* vs = sm + tokens * d;
     const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    if (beta_seq) beta = beta_seq[seq];   // one scale per sequence (a member's own beta)
     const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * d;
     for (int e = threadIdx.x; e < tokens * d; e += blockDim.x) {
         int tk = e / d, c = e - tk * d;
@@ -240,12 +241,13 @@ __global__ void spiking_attention_kernel(const float* __restrict__ Q, const floa
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
-                         int tokens, int heads, int64_t row_stride, float beta, float* __restrict__ O,
-                         float* __restrict__ A_out) {
+                         int tokens, int heads, int64_t row_stride, float beta, const float* __restrict__ beta_seq,
+                         float* __restrict__ O, float* __restrict__ A_out) {
     extern __shared__ __align__(16) float sm[];  // K (tokens, D) | V (tokens, D)
     float4* ks4 = reinterpret_cast<float4*>(sm);
     float4* vs4 = ks4 + tokens * (D / 4);
     const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    if (beta_seq) beta = beta_seq[seq];   // one scale per sequence (a member's own beta)
     const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
     constexpr int D4 = D / 4;
     for (int e = threadIdx.x; e < tokens * D4; e += blockDim.x) {
@@ -312,8 +314,8 @@ attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ 
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
-                      int tokens, int heads, int64_t row_stride, int mode, float beta, float tau_m, float v_th,
-                      float g_inh, int n_iter, float* __restrict__ O, float* __restrict__ A_out) {
+                      int tokens, int heads, int64_t row_stride, int mode, float beta, const float* __restrict__ beta_seq,
+                      float tau_m, float v_th, float g_inh, int n_iter, float* __restrict__ O, float* __restrict__ A_out) {
     extern __shared__ __align__(16) float sm[];
     constexpr int D4 = D / 4;
     const int pitch = tokens + 1;
@@ -323,6 +325,7 @@ attention_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, 
     float* us = hs + tokens * pitch;
     float* cs = us + tokens * pitch;   // mode 1 only
     const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    if (beta_seq) beta = beta_seq[seq];   // one scale per sequence (a member's own beta)
     const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
     for (int e = threadIdx.x; e < tokens * D4; e += blockDim.x) {
         int tk = e / D4, c4 = e - tk * D4;
@@ -440,14 +443,14 @@ attention_rows_kernel(const float* __restrict__ Q, const float* __restrict__ K, 
 template <int D>
 static cudaError_t launch_attention_rows(cudaStream_t st, unsigned grid, int threads, size_t smem, const float* Q,
                                          const float* K, const float* V, int tokens, int heads, int64_t row_stride,
-                                         int mode, float beta, float tau_m, float v_th, float g_inh, int n_iter,
-                                         float* O, float* A_out) {
+                                         int mode, float beta, const float* beta_seq, float tau_m, float v_th,
+                                         float g_inh, int n_iter, float* O, float* A_out) {
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attention_rows_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
     }
-    attention_rows_kernel<D><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, mode, beta, tau_m, v_th,
+    attention_rows_kernel<D><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, mode, beta, beta_seq, tau_m, v_th,
                                                           g_inh, n_iter, O, A_out);
     return cudaSuccess;
 }
@@ -462,13 +465,14 @@ static cudaError_t launch_attention_rows(cudaStream_t st, unsigned grid, int thr
 template <int D>
 __global__ void __launch_bounds__(64)
 attention_product_packed_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
-                                int tokens, int heads, int64_t row_stride, float beta, float* __restrict__ O,
-                                float* __restrict__ A_out) {
+                                int tokens, int heads, int64_t row_stride, float beta,
+                                const float* __restrict__ beta_seq, float* __restrict__ O, float* __restrict__ A_out) {
     extern __shared__ __align__(16) float sm[];
     const int tp = (tokens + 3) / 4 * 4 + 4;   // pitch of Kt: keys rounded up to four, plus four
     float* kt = sm;                            // [D][tp]
     float4* vs4 = reinterpret_cast<float4*>(sm + D * tp);  // [tokens][D]
     const int seq = blockIdx.x / heads, h = blockIdx.x % heads;
+    if (beta_seq) beta = beta_seq[seq];   // one scale per sequence (a member's own beta)
     const size_t base = (size_t)seq * tokens * row_stride + (size_t)h * D;
     constexpr int D4 = D / 4;
     const int padc = tp - tokens;
@@ -757,8 +761,8 @@ int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w,
 
 int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, const float* K, const float* V,
                            int64_t n_seq, int32_t tokens, int32_t heads, int32_t head_dim, int64_t row_stride,
-                           int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
-                           float* O, float* A_out) {
+                           int32_t mode, float beta, const float* beta_per_seq, float tau_m, float v_th, float g_inh,
+                           int32_t n_iter, float* O, float* A_out) {
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     HSES_REQUIRE(n_seq >= 0 && tokens >= 1 && tokens <= kMaxTokens, "tokens must be in 1..128");
     HSES_REQUIRE(heads >= 1 && head_dim >= 1 && head_dim <= kMaxHeadDim, "head_dim must be in 1..64");
@@ -779,12 +783,12 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
         const size_t smem_packed = ((size_t)head_dim * ((tokens + 3) / 4 * 4 + 4) + (size_t)tokens * head_dim) * sizeof(float);
         if (head_dim == 16)
             attention_product_packed_kernel<16><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
-                                                                                     beta, O, A_out);
+                                                                                     beta, beta_per_seq, O, A_out);
         else if (head_dim == 32)
             attention_product_packed_kernel<32><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
-                                                                                     beta, O, A_out);
+                                                                                     beta, beta_per_seq, O, A_out);
         else
-            attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, O, A_out);
+            attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, beta_per_seq, O, A_out);
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
@@ -795,20 +799,20 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
         cudaStream_t st = as_stream(stream);
         cudaError_t e;
         if (head_dim == 16)
-            e = launch_attention_rows<16>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+            e = launch_attention_rows<16>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta, beta_per_seq,
                                           tau_m, v_th, g_inh, n_iter, O, A_out);
         else if (head_dim == 32)
-            e = launch_attention_rows<32>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+            e = launch_attention_rows<32>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta, beta_per_seq,
                                           tau_m, v_th, g_inh, n_iter, O, A_out);
         else
-            e = launch_attention_rows<64>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta,
+            e = launch_attention_rows<64>(st, grid, threads, smem_rows, Q, K, V, tokens, heads, row_stride, mode, beta, beta_per_seq,
                                           tau_m, v_th, g_inh, n_iter, O, A_out);
         HSES_REQUIRE(e == cudaSuccess, "cudaFuncSetAttribute failed");
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
     spiking_attention_kernel<<<(unsigned)(n_seq * heads), threads, smem, as_stream(stream)>>>(
-        Q, K, V, tokens, heads, head_dim, row_stride, mode, beta, tau_m, v_th, g_inh, n_iter, O, A_out);
+        Q, K, V, tokens, heads, head_dim, row_stride, mode, beta, beta_per_seq, tau_m, v_th, g_inh, n_iter, O, A_out);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -496,21 +496,25 @@ def wkv7(r, w, k, v, a, b, state: torch.Tensor, new_starts: Optional[torch.Tenso
 
 def spiking_attention(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int, mode: int = 0,
                       beta: float = 1.0, tau_m: float = 2.0, v_th: float = 0.3, g_inh: float = 0.5,
-                      n_iter: int = 8, want_weights: bool = False):
+                      n_iter: int = 8, want_weights: bool = False, beta_per_seq: Optional[torch.Tensor] = None):
     """Q, K, V: (n_seq, tokens, heads*head_dim) firing rates -> O of the same shape."""
     for t, name in ((Q, "Q"), (K, "K"), (V, "V")):
         _check(t, name, ndim=3)
         if not t.is_contiguous():
             raise ValueError(f"{name} must be contiguous")
     n_seq, tokens, width = Q.shape
+    if beta_per_seq is not None:
+        _check(beta_per_seq, "beta_per_seq")
+        if beta_per_seq.numel() != n_seq or not beta_per_seq.is_contiguous():
+            raise ValueError("beta_per_seq must hold one contiguous value per sequence")
     if width % heads:
         raise ValueError("the model width must be a multiple of heads")
     O = torch.empty_like(Q)
     A = torch.empty((n_seq, heads, tokens, tokens), dtype=torch.float32, device=Q.device) if want_weights else None
     ctx = get_context(Q.device)
     _lib.check(_lib.load().hses_spiking_attention(ctx.handle, current_stream(), _ptr(Q), _ptr(K), _ptr(V), n_seq,
-                                                  tokens, heads, width // heads, width, mode, beta, tau_m, v_th,
-                                                  g_inh, n_iter, _ptr(O), _ptr(A)))
+                                                  tokens, heads, width // heads, width, mode, beta, _ptr(beta_per_seq),
+                                                  tau_m, v_th, g_inh, n_iter, _ptr(O), _ptr(A)))
     return (O, A) if want_weights else O
 
 

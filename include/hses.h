@@ -456,12 +456,13 @@ int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w,
  *      the spike product without softmax; mode 1: LIF-count row softmax (n_iter LIF steps with
  *      global inhibition g_inh); mode 2: the Rust port's continuous form — n_iter Hopfield
  *      relaxations u <- u + (1/tau_m)(-u + H - g_inh * mean_key(u)) from u = H, then a stable
- *      softmax along the keys (snn_transformer.rs:80-102).  A_out (optional): (n_seq, heads,
- *      tokens, tokens) weights. ---------------------------------------------------------- */
+ *      softmax along the keys (snn_transformer.rs:80-102).  beta_per_seq (optional): n_seq scales
+ *      that replace beta, one per sequence (the per-member beta of forward_batched,
+ *      snn_transformer.rs:366-371).  A_out (optional): (n_seq, heads, tokens, tokens) weights. ---------------------------------------------------------- */
 int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, const float* K, const float* V,
                            int64_t n_seq, int32_t tokens, int32_t heads, int32_t head_dim, int64_t row_stride,
-                           int32_t mode, float beta, float tau_m, float v_th, float g_inh, int32_t n_iter,
-                           float* O, float* A_out /*device or NULL*/);
+                           int32_t mode, float beta, const float* beta_per_seq /*device or NULL*/, float tau_m,
+                           float v_th, float g_inh, int32_t n_iter, float* O, float* A_out /*device or NULL*/);
 
 /* ---- RWKV-7 block pieces around the recurrence, hyperscalees-models/src/llm.rs:64-213.
  *      layer_norm (64-84): per row of c values, var = E[x^2] - E[x]^2, then weight and bias.
