@@ -320,3 +320,88 @@ class ChannelMixing:
             k = ops.relu_square(nz.do_mm(frozen, params, self.key_weight, keys[0], info, xk))
             out = nz.do_mm(frozen, params, self.value_weight, keys[1], info, k)
         return out, x[length - 1:length].clone()
+
+
+class TimeMixing:
+    """RWKV-7 TimeMixing (hyperscalees-models/src/llm.rs:298-479) for one sequence x (T, C).
+
+    `weights` holds the reference's fields by name: vectors x_r, x_w, x_k, x_v, x_a, x_g, w0, v0,
+    a0, k_k, k_a (C,), r_k (H, S) or (C,); Linear weights receptance, key, value, output (C, C) as
+    (out, in); Tmm weights w1, v1, a1, g1 (C, k) and w2, v2, a2, g2 (k, C) as (in, out); ln_x_weight
+    and ln_x_bias (C,).  Token shifts, every projection, the recurrence and the per-head group norm
+    run through the library's kernels; gates and the readout bonus are tensor arithmetic.  With
+    `noise` = (noiser, frozen, params, {name: base key}, iterinfo) the Linear and Tmm products go
+    through the noiser's do_mm / do_Tmm and carry the member's rank-r perturbation."""
+
+    def __init__(self, weights: dict):
+        self.w = dict(weights)
+        # x @ W for the Tmm weights runs as x @ (W^T)^T through the clean linear kernel
+        self._t = {n: self.w[n].t().contiguous() for n in ("w1", "w2", "v1", "v2", "a1", "a2", "g1", "g2")
+                   if n in self.w}
+
+    def _linear(self, name: str, x: torch.Tensor, noise) -> torch.Tensor:
+        if noise is None:
+            return ops.perturbed_linear(x.contiguous(), self.w[name], n_pop=1, bm=x.shape[0], perturb=False)
+        nz, frozen, params, keys, info = noise
+        return nz.do_mm(frozen, params, self.w[name], keys[name], info, x.contiguous())
+
+    def _tmm(self, name: str, x: torch.Tensor, noise) -> torch.Tensor:
+        if noise is None:
+            return ops.perturbed_linear(x.contiguous(), self._t[name], n_pop=1, bm=x.shape[0], perturb=False)
+        nz, frozen, params, keys, info = noise
+        return nz.do_Tmm(frozen, params, self.w[name], keys[name], info, x.contiguous())
+
+    def forward(self, x: torch.Tensor, state: torch.Tensor, v_first: torch.Tensor, length: int,
+                new_starts: Optional[torch.Tensor], h: int, s_dim: int, layer_id: int, noise=None):
+        """x (T, C); state (1 + S, C): row 0 the previous token, rows 1.. the (H, S, S) recurrent
+        state flattened; returns (out (T, C), new state, v_first)."""
+        w = self.w
+        T, C = x.shape
+        x = x.contiguous()
+        prev = state[0].contiguous()
+        ns = None if new_starts is None else new_starts.to(device=x.device, dtype=torch.uint8).contiguous()
+        mix = lambda name: ops.token_shift_mix(x, prev, w[name], ns)
+        xr, xw, xk, xv, xa, xg = (mix(n) for n in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"))
+
+        r = self._linear("receptance", xr, noise)
+        inner_w = w["w0"].unsqueeze(0) + self._tmm("w2", torch.tanh(self._tmm("w1", xw, noise)), noise)
+        wdec = -torch.nn.functional.softplus(-inner_w) - 0.5
+        k = self._linear("key", xk, noise)
+        v = self._linear("value", xv, noise)
+        if layer_id == 0:
+            v_first = v.clone()
+        else:
+            sig = torch.sigmoid(w["v0"].unsqueeze(0) + self._tmm("v2", torch.tanh(self._tmm("v1", xv, noise)), noise))
+            v = v + (v_first - v) * sig
+        a = torch.sigmoid(w["a0"].unsqueeze(0) + self._tmm("a2", torch.tanh(self._tmm("a1", xa, noise)), noise))
+        g = self._tmm("g2", torch.sigmoid(self._tmm("g1", xg, noise)), noise)
+
+        kk3 = (k * w["k_k"].unsqueeze(0)).view(T, h, s_dim)
+        kk = (kk3 / kk3.pow(2).sum(dim=2, keepdim=True).sqrt().clamp_min(1e-12)).reshape(T, C)
+        k = k * (w["k_a"].unsqueeze(0) * (a - 1.0) + 1.0)
+
+        new_state = state.clone()
+        new_state[0] = x[length - 1]
+        s_run = state[1:1 + s_dim].reshape(1, h, s_dim, s_dim).contiguous().clone()
+        shp = lambda t_: t_.reshape(1, T, h, s_dim).contiguous()
+        r4, w4, k4, v4, a4, b4 = shp(r), shp(wdec), shp(k), shp(v), shp(-kk), shp(kk * a)
+        nsb = None if ns is None else ns.view(1, T)
+        if length >= T:
+            out = ops.wkv7(r4, w4, k4, v4, a4, b4, s_run, nsb)
+            s_keep = s_run
+        else:
+            # the state handed back is the one after token length-1; later tokens still produce outputs
+            cut = lambda t_, lo, hi: t_[:, lo:hi].contiguous()
+            o1 = ops.wkv7(*(cut(t_, 0, length) for t_ in (r4, w4, k4, v4, a4, b4)), s_run,
+                          None if nsb is None else nsb[:, :length].contiguous())
+            s_keep = s_run.clone()
+            o2 = ops.wkv7(*(cut(t_, length, T) for t_ in (r4, w4, k4, v4, a4, b4)), s_run,
+                          None if nsb is None else nsb[:, length:].contiguous())
+            out = torch.cat([o1, o2], dim=1)
+        new_state[1:1 + s_dim] = s_keep.reshape(s_dim, C)
+
+        y = ops.group_norm(out.reshape(T, C), h, w["ln_x_weight"], w["ln_x_bias"], eps=64e-5)
+        bonus = (r.view(T, h, s_dim) * k.view(T, h, s_dim) * w["r_k"].reshape(1, h, s_dim)).sum(dim=2, keepdim=True)
+        y = y + (bonus * v.view(T, h, s_dim)).reshape(T, C)
+        y = y * g
+        return self._linear("output", y, noise), new_state, v_first
