@@ -357,10 +357,12 @@ def run_population_step(args, rank: int, local_rank: int, world: int):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the sampler starts before the warm-up steps: nvidia-smi needs a few hundred ms to deliver its
+    # first line, longer than the timed region of a short run
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     ctx.profile_enable(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
