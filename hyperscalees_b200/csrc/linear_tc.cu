@@ -78,8 +78,8 @@ struct TcSmem {
     static constexpr int X_BYTES = BM_TILE * BK * 2;
     static constexpr int W_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
-    static constexpr int HOP_BYTES = 0;     // the hop table and the filter thresholds are read through L1:
-    static constexpr int TAB_BYTES = 1024;  // only the logarithm's helper table is copied to shared memory
+    static constexpr int HOP_BYTES = 0;     // the hop table is read through L1;
+    static constexpr int TAB_BYTES = 1536;  // the logarithm's helper table and the thresholds as 2 x 256 bytes
     static constexpr int BAR_BYTES = 384;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
@@ -141,6 +141,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     // looks them up for every normal
     if (RG > 0) {
         for (int i = threadIdx.x; i < 64; i += NTHREADS) log_tab_s[i] = g.cal.log_tab[i];
+        // thresholds of the rounding filter as bytes (ceil(log2)): 512 bytes instead of 2 KB
+        uint8_t* thr_s = reinterpret_cast<uint8_t*>(log_tab_s + 64);
+        for (int i = threadIdx.x; i < 256; i += NTHREADS) {
+            thr_s[i] = pack_threshold_log2(g.cal.log_delta[i]);
+            thr_s[256 + i] = pack_threshold_log2(g.cal.cos_delta[i]);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -357,6 +363,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         float* slot_a = a_stage + (gq * depth + gi) * 32 * RANK;
         LibmCal cal = g.cal;
         cal.log_tab = log_tab_s;
+        cal.log_delta = reinterpret_cast<const uint32_t*>(log_tab_s + 64);                         // byte tables, see
+        cal.cos_delta = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(log_tab_s + 64) + 256);  // next_normals4_t<true>
         const int blocks_per_tile = g.a / 32;
         const int sw = a_swizzle<RG>(lane);
         uint32_t used = 0;
@@ -390,7 +398,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 #pragma unroll 1
                 for (int q = 0; q < RG; ++q) {
                     float z[4];
-                    next_normals4(a_state, cal, z);
+                    next_normals4_t<true>(a_state, cal, z);
                     *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
                         make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
                                     __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));

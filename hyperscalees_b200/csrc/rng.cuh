@@ -305,7 +305,11 @@ HSES_HD float next_normal(uint64_t& state, const LibmCal& cal) {
 // calls; the work is laid out as independent chains (eight generator steps, four
 // logarithms, four cosines, then all bitmap reads issued together without
 // branches) so that table and bitmap latencies overlap instead of adding up.
-HSES_HD void next_normals4(uint64_t& state, const LibmCal& cal, float (&out)[4]) {
+// LOG2T: the two threshold tables are 256 bytes each holding ceil(log2(threshold)) (see
+// pack_thresholds_log2): a threshold rounded up only sends a few more candidates to the bitmap,
+// whose bit decides, so the values are the same; the tables then fit where 2 KB would not.
+template <bool LOG2T>
+HSES_HD void next_normals4_t(uint64_t& state, const LibmCal& cal, float (&out)[4]) {
     uint32_t iu[4], ju[4];
     uint64_t x = state;
 #pragma unroll
@@ -322,10 +326,16 @@ HSES_HD void next_normals4(uint64_t& state, const LibmCal& cal, float (&out)[4])
     for (int j = 0; j < 4; ++j) {
         uint32_t i = iu[j] ? iu[j] : 1u;  // the zero uniform is replaced below
         rl[j] = round_candidate(log_candidate(i, cal.log_tab));
-        nl[j] = rl[j].dist < cal.log_delta[i >> 16];
+        if (LOG2T)
+            nl[j] = rl[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.log_delta)[i >> 16]);
+        else
+            nl[j] = rl[j].dist < cal.log_delta[i >> 16];
         float theta = fmul(kTauF, (float)ju[j] * 5.9604644775390625e-08f);
         rc[j] = round_candidate(cos_candidate(theta));
-        nc[j] = rc[j].dist < cal.cos_delta[ju[j] >> 16];
+        if (LOG2T)
+            nc[j] = rc[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.cos_delta)[ju[j] >> 16]);
+        else
+            nc[j] = rc[j].dist < cal.cos_delta[ju[j] >> 16];
     }
     uint32_t wl[4], wc[4];
 #pragma unroll
@@ -342,6 +352,16 @@ HSES_HD void next_normals4(uint64_t& state, const LibmCal& cal, float (&out)[4])
         float lg = iu[j] ? u2f(lb) : cal.log_of_zero;
         out[j] = fmul(fsqrt(fmul(-2.0f, lg)), u2f(cb));
     }
+}
+
+HSES_HD void next_normals4(uint64_t& state, const LibmCal& cal, float (&out)[4]) {
+    next_normals4_t<false>(state, cal, out);
+}
+// ceil(log2(t)) of a 32-bit threshold as a byte (0 for t <= 1): dist < t implies dist < 2^byte
+HSES_HD uint8_t pack_threshold_log2(uint32_t t) {
+    uint8_t e = 0;
+    while (e < 31 && (1u << e) < t) ++e;
+    return e;
 }
 
 }  // namespace hses
