@@ -231,7 +231,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
 
     # end to end through the public call with host buffers: H2D of the inputs, the step, D2H of the
     # spikes, all inside the timed region; the library's host pipeline overlaps the three on streams
-    pipe = ops.HostPipeline(N_POP, BM, K_DIM, A_DIM, chunks=16, device=dev)
+    pipe = ops.HostPipeline(N_POP, BM, K_DIM, A_DIM, chunks=8, device=dev, taper=True)
 
     def e2e_step():
         pipe.run(x_host, w_dev, out_host, first_thread=first_thread, sigma=SIGMA, rank=RANK, key=KEY,

@@ -430,16 +430,36 @@ class HostPipeline:
     must be pinned.  Only single-time-step inputs (n_pop, bm, k) are cut this way.
     """
 
-    def __init__(self, n_pop: int, bm: int, k: int, a: int, chunks: int = 8, device=None):
+    def __init__(self, n_pop: int, bm: int, k: int, a: int, chunks: int = 8, device=None, taper: bool = False):
         ctx = get_context(device)
         self.dev = torch.device("cuda", ctx.device)
         if n_pop % (2 * chunks) != 0:
             raise ValueError("n_pop must be a multiple of 2*chunks (chunks hold whole antithetic pairs)")
-        self.n_pop, self.bm, self.k, self.a, self.chunks = n_pop, bm, k, a, chunks
-        self.mc = n_pop // chunks
+        self.n_pop, self.bm, self.k, self.a = n_pop, bm, k, a
+        self.sizes = self.chunk_sizes(n_pop, chunks, taper)
+        self.chunks = len(self.sizes)
+        self.mc = max(self.sizes)
         self.x_dev = [torch.empty((self.mc, bm, k), dtype=torch.float32, device=self.dev) for _ in range(2)]
         self.o_dev = [torch.empty((self.mc * bm, a), dtype=torch.float32, device=self.dev) for _ in range(2)]
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.dev) for _ in range(3))
+
+    @staticmethod
+    def chunk_sizes(n_pop: int, chunks: int, taper: bool):
+        """Members per chunk (all even).  Tapered: the first chunk is an eighth of a regular one and
+        the sizes double up to the regular size, mirrored at the end, so that the copy-in of the
+        first chunk and the copy-out of the last one, which nothing overlaps, are short."""
+        mc = n_pop // chunks
+        if not taper:
+            return [mc] * chunks
+        head, s = [], max(2, (mc // 8) // 2 * 2)
+        while s < mc:
+            head.append(s)
+            s *= 2
+        rest = n_pop - 2 * sum(head)
+        if rest <= 0:
+            return [mc] * chunks
+        mid = [mc] * (rest // mc) + ([rest % mc] if rest % mc else [])
+        return head + mid + head[::-1]
 
     def run(self, x_host: torch.Tensor, param: torch.Tensor, out_host: torch.Tensor, first_thread: int = 0, **kw):
         if not (x_host.is_pinned() and out_host.is_pinned()):
@@ -450,26 +470,27 @@ class HostPipeline:
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_event(start)
         ev_in, ev_run, ev_out = [], [], []
-        rows = self.mc * self.bm
-        for c in range(self.chunks):
+        lo = 0
+        for c, m in enumerate(self.sizes):
             b = c & 1
-            lo = c * self.mc
+            rows = m * self.bm
             with torch.cuda.stream(self.s_in):
                 if c >= 2:
                     self.s_in.wait_event(ev_run[c - 2])      # the kernels of chunk c-2 have read x_dev[b]
-                self.x_dev[b].copy_(x_host[lo:lo + self.mc], non_blocking=True)
+                self.x_dev[b][:m].copy_(x_host[lo:lo + m], non_blocking=True)
                 e = torch.cuda.Event(); e.record(self.s_in); ev_in.append(e)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(ev_in[c])
                 if c >= 2:
                     self.s_run.wait_event(ev_out[c - 2])     # o_dev[b] has been copied out
-                perturbed_linear(self.x_dev[b], param, n_pop=self.mc, bm=self.bm, first_thread=first_thread + lo,
-                                 out=self.o_dev[b], **kw)
+                perturbed_linear(self.x_dev[b][:m], param, n_pop=m, bm=self.bm, first_thread=first_thread + lo,
+                                 out=self.o_dev[b][:rows], **kw)
                 e = torch.cuda.Event(); e.record(self.s_run); ev_run.append(e)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(ev_run[c])
-                out_host[lo * self.bm:lo * self.bm + rows].copy_(self.o_dev[b], non_blocking=True)
+                out_host[lo * self.bm:lo * self.bm + rows].copy_(self.o_dev[b][:rows], non_blocking=True)
                 e = torch.cuda.Event(); e.record(self.s_out); ev_out.append(e)
+            lo += m
         cur.wait_event(ev_out[-1])
         cur.wait_event(ev_run[-1])
         return out_host

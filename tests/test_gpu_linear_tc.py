@@ -112,16 +112,19 @@ def test_tensor_path_refuses_unsupported_shapes(hs):
     assert out.shape == (15, 24)
 
 
-def test_host_pipeline_equals_single_call(hs):
+@pytest.mark.parametrize("taper", [False, True])
+def test_host_pipeline_equals_single_call(hs, taper):
     """The chunked, stream-overlapped host path gives the same spikes as one device call."""
     from hyperscalees_b200 import ops
     torch.manual_seed(1)
-    n_pop, bm, k, a = 64, 16, 128, 256
+    n_pop, bm, k, a = 128, 16, 128, 256
     x = torch.randn(n_pop, bm, k).pin_memory()
     w = torch.randn(a, k, device="cuda")
     out = torch.empty(n_pop * bm, a).pin_memory()
     kw = dict(sigma=0.05, rank=8, key=KEY, lif=True, tau_m=20.0, v_th=0.3)
-    pipe = ops.HostPipeline(n_pop, bm, k, a, chunks=4)
+    pipe = ops.HostPipeline(n_pop, bm, k, a, chunks=4, taper=taper)
+    assert sum(pipe.sizes) == n_pop and all(m % 2 == 0 for m in pipe.sizes)
+    assert (len(set(pipe.sizes)) > 1) == taper
     pipe.run(x, w, out, first_thread=6, **kw)
     torch.cuda.synchronize()
     want = ops.perturbed_linear(x.cuda(), w, n_pop=n_pop, bm=bm, first_thread=6, **kw).cpu()
