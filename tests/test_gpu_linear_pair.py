@@ -19,6 +19,8 @@ pytestmark = pytest.mark.gpu
     (6, 1, 128, 200, 32, 8, 0),     # swizzled A: four column blocks (two rounds of warp tasks), ragged last block
     (4, 4, 64, 100, 64, 2, 2),      # swizzled A, 16 rows per pair, a not a multiple of 8
     (2, 2, 40, 256, 32, 8, 0),      # swizzled A, 32 rows per pair, the largest box (256 rows)
+    (4, 3, 64, 72, 32, 2, 0),       # swizzled A, 12 of 16 tile rows used, ragged column block
+    (6, 1, 32, 10, 64, 1, 4),       # swizzled A, 2 of 8 tile rows, ten columns (one warp task pair)
 ])
 def test_pair_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
