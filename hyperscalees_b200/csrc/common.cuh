@@ -128,6 +128,17 @@ namespace hses {
 int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
                         int32_t first_pair, int64_t pairs, int rank, int a, int b,
                         const float* pair_weight, float* A, float* B);
+// lif_step (hyperscalees-models/src/snn.rs:53-65): charge, threshold, reset; returns the spike
+__device__ __forceinline__ float lif_update(float& v, float cur, float leak, float v_th, int reset) {
+    float d = __fadd_rn(-v, cur);
+    float m = __fmul_rn(d, leak);
+    float c = __fadd_rn(v, m);
+    float s = c >= v_th ? 1.0f : 0.0f;
+    v = reset == HSES_RESET_HARD ? __fmul_rn(c, __fadd_rn(-s, 1.0f)) : __fsub_rn(c, __fmul_rn(s, v_th));
+    return s;
+}
+
+
 }  // namespace hses
 
 static inline cudaStream_t as_stream(hses_stream s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -73,15 +73,6 @@ __global__ void poisson_kernel(const float* __restrict__ probs, int64_t batch, i
 // ---------------------------------------------------------------------------
 // LIF scan (snn.rs:53-97, lif_fused_oxide.rs:37-70)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float lif_update(float& v, float cur, float leak, float v_th, int reset) {
-    float d = __fadd_rn(-v, cur);
-    float m = __fmul_rn(d, leak);
-    float c = __fadd_rn(v, m);
-    float s = c >= v_th ? 1.0f : 0.0f;
-    v = reset == HSES_RESET_HARD ? __fmul_rn(c, __fadd_rn(-s, 1.0f)) : __fsub_rn(c, __fmul_rn(s, v_th));
-    return s;
-}
-
 template <int VEC>
 __global__ void lif_scan_kernel(const float* __restrict__ cur, int T, int64_t n, int h,
                                 int64_t stride, float* __restrict__ v_io, float leak, float v_th,

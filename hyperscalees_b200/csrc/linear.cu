@@ -281,6 +281,24 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     int rc = check_args(g);
     if (rc != HSES_OK) return rc;
+    if (g->lif == 2) {
+        HSES_REQUIRE(g->potentials == nullptr, "lif == 2 has no potentials output");
+        // the same choice of path as below
+        const bool pair_ok2 = pair_path_supports(*g);
+        const bool takes_pair = (g->algo == HSES_ALGO_PAIR && pair_ok2) ||
+                                (g->algo == HSES_ALGO_AUTO && !tensor_path_supports(*g) && pair_ok2);
+        if (takes_pair && pair_path_fuses_scan(*g))
+            return run_pair_path(ctx, as_stream(stream), *g);   // the scan runs in that kernel's last phase
+        // elsewhere: the currents go to `out` and are scanned in place
+        hses_linear_args h = *g;
+        h.lif = 0;
+        h.out_scale = 1.0f;
+        h.out_scale_ptr = nullptr;
+        rc = hses_perturbed_linear(ctx, stream, &h);
+        if (rc != HSES_OK) return rc;
+        return hses_lif_scan(ctx, stream, g->out, g->t_steps, g->n_pop * g->bm, g->a, g->out_row_stride, nullptr,
+                             g->tau_m, g->v_th, g->reset_mode, g->out);
+    }
     bool tc_ok = tensor_path_supports(*g);
     if (g->algo == HSES_ALGO_TENSOR && !tc_ok) {
         set_error("hses_perturbed_linear: the tensor-core path does not cover this shape");

@@ -13,6 +13,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t stream, const hses_linear_args& 
 // The path for few rows per antithetic pair and wide factors (linear_pair.cu): clean product
 // through the other paths, then one CTA per pair that streams the pair's factors once.
 bool pair_path_supports(const hses_linear_args& g);
+bool pair_path_fuses_scan(const hses_linear_args& g);   // lif == 2 is finished inside the per-pair kernel
 size_t pair_path_workspace_bytes(const hses_linear_args& g);
 int run_pair_path(hses_ctx* ctx, cudaStream_t stream, const hses_linear_args& g);
 

@@ -48,7 +48,8 @@ struct PairArgs {
     float* out;
     int64_t out_stride;
     float* pot;
-    int lif;
+    int lif;           // 0: y * gain; 1: one LIF step from v = 0; 2: LIF scan over the steps (swizzled form only)
+    int reset;
     float leak, v_th, out_scale;
     const float* out_scale_ptr;
     int* status;
@@ -276,6 +277,8 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         const int tasks = tasks2;
         const int halfq = rank >> 3;              // 16-byte pieces per rank half
         float* xch = red + RMAX * rank;           // [warp][lane][8]
+        const bool scan = g.lif == 2;
+        float* ytile = xch + nwarps * 32 * 8;     // [row][a]: currents of all steps, scanned at the end
         for (int t0 = 0; t0 < tasks; t0 += nwarps) {
             const int task = t0 + wid;
             const bool live = task < tasks;
@@ -348,7 +351,9 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                                 // the lower rank half first, whichever warp finishes the row
                                 const float u = rh ? __fadd_rn(other[2 * jj + c2], mine) : __fadd_rn(mine, other[2 * jj + c2]);
                                 float y = __fadd_rn(base[jj][c2], odd ? -u : u);
-                                if (g.lif) {
+                                if (scan) {
+                                    ytile[r * a + n] = y;
+                                } else if (g.lif) {
                                     float cpot = __fmul_rn(y, g.leak);
                                     if (prow) prow[n] = cpot;
                                     orow[n] = cpot >= g.v_th ? 1.0f : 0.0f;
@@ -361,6 +366,20 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 }
             }
             if (t0 + nwarps < tasks) __syncthreads();   // the exchange buffer is reused by the next round
+        }
+        if (scan) {
+            // run_lif over the steps (snn.rs:73-97): one thread per (row of a step, column), membrane
+            // from v = 0; lanes own neighbouring columns, so every store is a full line
+            __syncthreads();
+            for (int idx = tid; idx < rows_per_step * a; idx += (int)blockDim.x) {
+                const int rr = idx / a, n = idx - rr * a;
+                float v = 0.0f;
+                for (int step = 0; step < g.t_steps; ++step) {
+                    const int r = step * rows_per_step + rr;
+                    const float sp = lif_update(v, ytile[r * a + n], g.leak, g.v_th, g.reset);
+                    g.out[(size_t)row_s[r] * g.out_stride + n] = sp;
+                }
+            }
         }
         tick(4);
         return;
@@ -486,6 +505,15 @@ bool a_swizzled(int rmax, const hses_linear_args& g) {
     return (size_t)rmax * g.rank + (size_t)threads_of(rmax) * 8 <= area && a_swz_floats(g) <= 2 * (size_t)PP_A_SMEM_FLOATS;
 }
 
+// the currents of a pair (rows x a) fit behind t and the exchange buffer in the k-slice area
+bool scan_fits(int rmax, const hses_linear_args& g) {
+    if (!a_swizzled(rmax, g)) return false;
+    int kc = kc_of(rmax, g.rank), kslices = kslices_of(rmax, g.rank);
+    size_t bbuf = (size_t)PP_STAGES * kc * g.rank, red = (size_t)kslices * rmax * g.rank;
+    size_t area = bbuf > red ? bbuf : red;
+    return (size_t)rmax * g.rank + (size_t)threads_of(rmax) * 8 + (size_t)rmax * g.a <= area;
+}
+
 size_t pair_smem_bytes(int rmax, const hses_linear_args& g) {
     int kc = kc_of(rmax, g.rank), kslices = kslices_of(rmax, g.rank);
     size_t bbuf = (size_t)PP_STAGES * kc * g.rank, red = (size_t)kslices * rmax * g.rank;
@@ -516,6 +544,8 @@ int64_t chunk_pairs_of(const hses_linear_args& g, int64_t pairs) {
 }
 
 }  // namespace
+
+bool pair_path_fuses_scan(const hses_linear_args& g) { return g.potentials == nullptr && scan_fits(rmax_of(g), g); }
 
 bool pair_path_supports(const hses_linear_args& g) {
     if (!g.perturb) return false;
@@ -564,6 +594,7 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     pa.out_stride = g.out_row_stride;
     pa.pot = g.lif ? g.potentials : nullptr;
     pa.lif = g.lif;
+    pa.reset = g.reset_mode;
     pa.leak = g.lif ? 1.0f / g.tau_m : 0.0f;
     pa.v_th = g.v_th;
     pa.out_scale = g.out_scale;

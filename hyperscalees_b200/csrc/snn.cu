@@ -119,14 +119,15 @@ int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m,
         hses_linear_args g = layer_args(m, p, l, false);
         g.x = layer_in;
         g.x_row_stride = layer_in_stride;
-        g.out = cur;
+        // currents and the LIF scan over the T steps in one call: the per-pair path finishes the scan
+        // inside its kernel (the currents never reach memory), the other paths scan `out` in place
+        float* out_spk = spk[l & 1];
+        g.out = out_spk;
+        g.lif = 2;
+        g.v_th = m->v_th[l];
         g.workspace = lin_ws;
         g.workspace_bytes = f.lin_bytes;
         rc = hses_perturbed_linear(ctx, stream, &g);
-        if (rc != HSES_OK) return rc;
-        float* out_spk = spk[l & 1];
-        rc = hses_lif_scan(ctx, stream, cur, p->T, (int64_t)f.rows, m->dims[l + 1], m->dims[l + 1], nullptr,
-                           m->tau_m, m->v_th[l], m->reset_mode, out_spk);
         if (rc != HSES_OK) return rc;
         layer_in = out_spk;
         layer_in_stride = m->dims[l + 1];

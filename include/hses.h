@@ -187,7 +187,9 @@ typedef struct {
     int32_t first_thread;
     int32_t noise_reuse;
     int32_t perturb; /* 0: clean x·paramᵀ (iterinfo = None) */
-    int32_t lif;     /* 0: write y; 1: write spikes of one LIF step */
+    int32_t lif;     /* 0: write y; 1: write spikes of one LIF step; 2: write the spikes of a LIF scan over
+                        the t_steps from v0 = 0 (run_lif, snn.rs:73-97): row p of step t hands its membrane
+                        to row p of step t+1; potentials must be NULL */
     float tau_m;
     float v_th;
     int32_t reset_mode;

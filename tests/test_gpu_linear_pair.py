@@ -72,3 +72,25 @@ def test_auto_dispatch_prefers_the_pair_path(hs):
     with pytest.raises(HsesError):
         ops.perturbed_linear(torch.randn(4, 64, 16, device="cuda"), torch.randn(8, 16, device="cuda"),
                              n_pop=4, bm=64, sigma=0.1, rank=4, key=1, algo=ops.ALGO_PAIR)
+
+
+@pytest.mark.parametrize("n_pop,bm,k,a,rank,t_steps,reset", [
+    (8, 1, 784, 128, 64, 8, 0),     # per-pair path, scan inside the kernel (swizzled A)
+    (6, 2, 64, 100, 32, 4, 1),      # the same with a ragged column block and the subtractive reset
+    (4, 1, 36, 50, 8, 3, 0),        # per-pair path without the swizzled form: currents scanned in place
+    (8, 16, 64, 128, 4, 2, 0),      # tensor path: currents scanned in place
+])
+def test_fused_lif_scan_equals_linear_then_scan(n_pop, bm, k, a, rank, t_steps, reset):
+    """lif = 2 (LIF scan over the steps fused behind the layer) gives the bits of the two-call form."""
+    from hyperscalees_b200 import ops, core
+    g = np.random.default_rng(n_pop + k)
+    x = torch.as_tensor((g.random((t_steps, n_pop, bm, k)) < 0.3).astype(np.float32), device="cuda")
+    w = torch.as_tensor((g.standard_normal((a, k)) * 3.0 / np.sqrt(k)).astype(np.float32), device="cuda")
+    kw = dict(n_pop=n_pop, bm=bm, t_steps=t_steps, sigma=0.3, rank=rank, key=0x51ED, epoch=1, tau_m=2.0, v_th=0.5,
+              reset_mode=reset)
+    cur = ops.perturbed_linear(x, w, **kw)
+    want = ops.lif_scan(cur.view(t_steps, n_pop * bm, a), 2.0, 0.5, reset_mode=reset)
+    got = ops.perturbed_linear(x, w, lif=2, **kw)
+    assert core.get_context(0).device_status() == 0
+    assert 0.02 < want.mean().item() < 0.98
+    assert torch.equal(got.view_as(want), want)
