@@ -479,16 +479,59 @@ def run_streaming_kernels(args, local_rank: int):
                       "device_status": ctx.device_status()}), flush=True)
 
 
+def run_snn_transformer(args, local_rank: int):
+    """Secondary workload: forward_batched of the SNN-rate transformer (d_model 64, 4 heads, 2 blocks,
+    16 tokens of 49 inputs, T = 4 encoding steps) over a chunk of --n-pop members with rank-8 noise;
+    reports member-evaluations/s = n_pop * T per second.  One GPU."""
+    import torch
+    from hyperscalees_b200 import core, models
+    from hyperscalees_b200.snn_transformer import SnnTransformer, TrainNoise
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = core.get_context(local_rank)
+    n, T, nt, tin, d, H, blocks, classes, rank = args.n_pop, 4, 16, 49, 64, 4, 2, 10, 8
+    model = SnnTransformer(tin, nt, classes, d, H, blocks, device=dev, seed=2)
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = (torch.rand(T, n, nt * tin, device=dev, generator=g) < 0.2).float()
+    dn = lambda *s: torch.randn(*s, device=dev, generator=g) * 0.02
+    noise = TrainNoise(sigma=0.02, rank=rank, base_keys=models.default_base_keys(len(model.params())), epoch=0,
+                       first_thread=0, pos_emb=dn(n, nt, d), out_gain=dn(n, 1), beta=dn(n, 1))
+    for _ in range(max(args.warmup, 3)):
+        model.forward_batched(x, noise)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    ctx.profile_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        logits = model.forward_batched(x, noise)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    print(json.dumps({"metric": METRIC, "value": n * T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
+                      "data": "synthetic",
+                      "config": {"workload": f"SNN-rate transformer forward_batched: {n} members, T {T}, {nt} tokens x {tin}, "
+                                             f"d_model {d}, {H} heads, {blocks} blocks, rank {rank}, sigma 0.02"},
+                      "kernel_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+                      "gpu_launches": int(sum(v[0] for v in prof.values())), "clocks": sampler.stop(),
+                      "finite": bool(torch.isfinite(logits).all().item()), "device_status": ctx.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer"],
                     help="microbench: the perturbed-linear layer the metric is quoted on (default); "
                          "population_step: a full ES step of the spiking MLP (secondary figure); "
-                         "streaming_kernels: the HBM-bound kernels of the path, each timed alone")
+                         "streaming_kernels: the HBM-bound kernels of the path, each timed alone; "
+                         "snn_transformer: forward_batched of the SNN-rate transformer over --n-pop members")
     ap.add_argument("--bm", type=int, default=1, help="population_step: samples per member")
     ap.add_argument("--rank", type=int, default=64, help="population_step: rank of the factors")
     ap.add_argument("--cache", default="off", choices=["off", "auto"],
@@ -512,6 +555,9 @@ def main():
     elif args.workload == "streaming_kernels":
         if rank == 0:
             run_streaming_kernels(args, local_rank)
+    elif args.workload == "snn_transformer":
+        if rank == 0:
+            run_snn_transformer(args, local_rank)
     else:
         run_ours(args, rank, local_rank, world)
 
