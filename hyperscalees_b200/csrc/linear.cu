@@ -72,7 +72,7 @@ __global__ void lowrank_project_kernel(const float* __restrict__ x, int64_t rows
     }
 }
 
-constexpr int TM = 128, TN = 128, TK = 16, TT = 256;  // tile sizes, threads
+constexpr int TM = 128, TK = 16, TT = 256;  // row tile, k step, threads (the column tile is 16 * NJ)
 
 struct EpilogueArgs {
     int perturb, lif, reset;
@@ -88,22 +88,27 @@ struct EpilogueArgs {
     float* pot;
 };
 
-__global__ void __launch_bounds__(TT)
+// NJ = output columns per thread: 8 (a 128-column tile: columns {tc..tc+3, 64+tc..64+tc+3}) or, for
+// narrow layers, 4, 2 or 1 consecutive columns (tiles of 64, 32, 16 columns), so that a 16-wide
+// projection does not pay for a 128-wide tile.  The k loop of an output is the same in every form.
+template <int NJ>
+__global__ void __launch_bounds__(TT, 2)
 linear_simt_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t x_stride,
                    const float* __restrict__ w, int a, int64_t w_stride, EpilogueArgs ep) {
+    constexpr int TNJ = 16 * NJ;
     __shared__ __align__(16) float sx[TK][TM + 4];
-    __shared__ __align__(16) float sw[TK][TN + 4];
+    __shared__ __align__(16) float sw[TK][TNJ + 4];
     int64_t row0 = (int64_t)blockIdx.y * TM;
-    int col0 = blockIdx.x * TN;
+    int col0 = blockIdx.x * TNJ;
     int tid = threadIdx.x;
-    // a thread owns rows {tr..tr+3, 64+tr..64+tr+3} and the same pattern of
+    // a thread owns rows {tr..tr+3, 64+tr..64+tr+3} and (NJ = 8) the same pattern of
     // columns, so its shared-memory reads are two conflict-free float4 loads
-    int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
-    float acc[8][8];
+    int tr = (tid / 16) * 4, tc = (tid % 16) * (NJ == 8 ? 4 : NJ);
+    float acc[8][NJ];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < NJ; ++j) acc[i][j] = 0.0f;
 
     for (int k0 = 0; k0 < k; k0 += TK) {
         // each thread loads 8 elements of each tile: element e -> (row e/16, k e%16)
@@ -113,21 +118,28 @@ linear_simt_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t x_s
             int r = idx / TK, kk = idx % TK;
             int64_t gr = row0 + r;
             sx[kk][r] = (gr < rows && k0 + kk < k) ? x[(size_t)gr * x_stride + k0 + kk] : 0.0f;
-            int gc = col0 + r;
-            sw[kk][r] = (gc < a && k0 + kk < k) ? w[(size_t)gc * w_stride + k0 + kk] : 0.0f;
+            if (r < TNJ) {
+                int gc = col0 + r;
+                sw[kk][r] = (gc < a && k0 + kk < k) ? w[(size_t)gc * w_stride + k0 + kk] : 0.0f;
+            }
         }
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < TK; ++kk) {
-            float xa[8], wb[8];
+            float xa[8], wb[NJ];
             *reinterpret_cast<float4*>(&xa[0]) = *reinterpret_cast<const float4*>(&sx[kk][tr]);
             *reinterpret_cast<float4*>(&xa[4]) = *reinterpret_cast<const float4*>(&sx[kk][64 + tr]);
-            *reinterpret_cast<float4*>(&wb[0]) = *reinterpret_cast<const float4*>(&sw[kk][tc]);
-            *reinterpret_cast<float4*>(&wb[4]) = *reinterpret_cast<const float4*>(&sw[kk][64 + tc]);
+            if (NJ == 8) {
+                *reinterpret_cast<float4*>(&wb[0]) = *reinterpret_cast<const float4*>(&sw[kk][tc]);
+                *reinterpret_cast<float4*>(&wb[NJ == 8 ? 4 : 0]) = *reinterpret_cast<const float4*>(&sw[kk][64 + tc]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) wb[j] = sw[kk][tc + j];
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
+                for (int j = 0; j < NJ; ++j) acc[i][j] = fmaf(xa[i], wb[j], acc[i][j]);
         }
         __syncthreads();
     }
@@ -146,17 +158,43 @@ linear_simt_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t x_s
             tr_ = ep.t + (size_t)R * ep.rank;
             scale = (thread_id % 2 == 0) ? ep.base_sigma : -ep.base_sigma;
         }
+        // u[j] = sum_q t[R][q] * (scale * A[n_j][q]), q ascending; with a rank that is a multiple of
+        // four the row of t and the rows of A are read as 16-byte pieces, once per row and column
+        float u[NJ];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int n = col0 + (j < 4 ? tc + j : 64 + tc + j - 4);
+        for (int j = 0; j < NJ; ++j) u[j] = 0.0f;
+        if (ep.perturb) {
+            const bool vec = (ep.rank & 3) == 0 && (((uintptr_t)ep.A | (uintptr_t)ep.t) & 15u) == 0;
+            if (vec) {
+                for (int q4 = 0; q4 < ep.rank; q4 += 4) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(tr_ + q4);
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        int n = col0 + (NJ == 8 ? (j < 4 ? tc + j : 64 + tc + j - 4) : tc + j);
+                        if (n >= a) n = a - 1;
+                        const float4 a4 = *reinterpret_cast<const float4*>(Ap + (size_t)n * ep.rank + q4);
+                        u[j] = fmaf(t4.x, __fmul_rn(a4.x, scale), u[j]);
+                        u[j] = fmaf(t4.y, __fmul_rn(a4.y, scale), u[j]);
+                        u[j] = fmaf(t4.z, __fmul_rn(a4.z, scale), u[j]);
+                        u[j] = fmaf(t4.w, __fmul_rn(a4.w, scale), u[j]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    int n = col0 + (NJ == 8 ? (j < 4 ? tc + j : 64 + tc + j - 4) : tc + j);
+                    if (n >= a) continue;
+                    for (int q = 0; q < ep.rank; ++q)
+                        u[j] = fmaf(tr_[q], __fmul_rn(Ap[(size_t)n * ep.rank + q], scale), u[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            int n = col0 + (NJ == 8 ? (j < 4 ? tc + j : 64 + tc + j - 4) : tc + j);
             if (n >= a) continue;
             float y = acc[i][j];
-            if (ep.perturb) {
-                float u = 0.0f;
-                for (int q = 0; q < ep.rank; ++q)
-                    u = fmaf(tr_[q], __fmul_rn(Ap[(size_t)n * ep.rank + q], scale), u);
-                y = __fadd_rn(y, u);
-            }
+            if (ep.perturb) y = __fadd_rn(y, u[j]);
             size_t o = (size_t)R * ep.out_stride + n;
             if (ep.lif) {
                 // lif_step from v = 0: charged = 0 + ((-0) + y) * leak
@@ -251,10 +289,18 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     int64_t row_tiles = (rows + TM - 1) / TM;
     HSES_REQUIRE(row_tiles <= 65535ll * 32768ll, "too many rows");
     HSES_REQUIRE(row_tiles <= 65535, "too many rows for the SIMT path (rows/128 must be <= 65535)");
-    dim3 grid((unsigned)((g.a + TN - 1) / TN), (unsigned)row_tiles);
     HSES_KERNEL(ctx, st, "linear_simt");
-    linear_simt_kernel<<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a,
-                                            g.param_row_stride, ep);
+    // narrow layers take a narrower column tile
+    const int nj = g.a <= 16 ? 1 : g.a <= 32 ? 2 : g.a <= 64 ? 4 : 8;
+    dim3 grid((unsigned)((g.a + 16 * nj - 1) / (16 * nj)), (unsigned)row_tiles);
+    if (nj == 1)
+        linear_simt_kernel<1><<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a, g.param_row_stride, ep);
+    else if (nj == 2)
+        linear_simt_kernel<2><<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a, g.param_row_stride, ep);
+    else if (nj == 4)
+        linear_simt_kernel<4><<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a, g.param_row_stride, ep);
+    else
+        linear_simt_kernel<8><<<grid, TT, 0, st>>>(g.x, rows, g.k, g.x_row_stride, g.param, g.a, g.param_row_stride, ep);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
