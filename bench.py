@@ -143,6 +143,8 @@ def run_reference(args, rank: int, world: int):
         return
     from oracle import oracle as O
     O.build()
+    # every core this process may run on (a launcher such as torchrun pins OMP_NUM_THREADS to 1)
+    O.set_num_threads(len(os.sched_getaffinity(0)))
     # a bounded slice of the same workload: enough members for ~2 s of CPU work per step
     x, w = synth_inputs(0, 512)
     rates = []
@@ -297,6 +299,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
         if world == 1 and not args.kernel_only:
             from oracle import oracle as O
             O.build()
+            O.set_num_threads(len(os.sched_getaffinity(0)))
             r, sample, secs = cpu_rate(O, x_np, w_np, 12.0)
             cpu = {"value": r, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
                    "sample": f"{sample}, {secs:.1f} s; C restatement of the reference path, OpenMP over members"}

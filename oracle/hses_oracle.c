@@ -14,6 +14,12 @@
 #include <omp.h>
 #endif
 
+/* A launcher may pin OMP_NUM_THREADS to 1 for every rank; the timed CPU baseline asks for the
+ * cores the process may run on instead. */
+void hso_set_num_threads(int n) {
+    if (n >= 1) omp_set_num_threads(n);
+}
+
 int hso_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

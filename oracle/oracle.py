@@ -93,6 +93,10 @@ def num_threads() -> int:
     return int(lib().hso_num_threads())
 
 
+def set_num_threads(n: int) -> None:
+    lib().hso_set_num_threads(int(n))
+
+
 def noise_seed(key: int, true_epoch: int, true_thread: int) -> int:
     return int(lib().hso_noise_seed(C.c_uint64(key & (2**64 - 1)), true_epoch, true_thread))
 
