@@ -500,6 +500,8 @@ def run_snn_transformer(args, local_rank: int):
     dn = lambda *s: torch.randn(*s, device=dev, generator=g) * 0.02
     noise = TrainNoise(sigma=0.02, rank=rank, base_keys=models.default_base_keys(len(model.params())), epoch=0,
                        first_thread=0, pos_emb=dn(n, nt, d), out_gain=dn(n, 1), beta=dn(n, 1))
+    if args.cache == "auto":
+        noise.caches = model.build_caches(noise, n)   # a chunk's factors are generated once (forward + gradient share them)
     for _ in range(max(args.warmup, 3)):
         model.forward_batched(x, noise)
     torch.cuda.synchronize()
@@ -518,7 +520,7 @@ def run_snn_transformer(args, local_rank: int):
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f32",
                       "data": "synthetic",
                       "config": {"workload": f"SNN-rate transformer forward_batched: {n} members, T {T}, {nt} tokens x {tin}, "
-                                             f"d_model {d}, {H} heads, {blocks} blocks, rank {rank}, sigma 0.02"},
+                                             f"d_model {d}, {H} heads, {blocks} blocks, rank {rank}, sigma 0.02; factor cache {args.cache}"},
                       "kernel_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
                       "gpu_launches": int(sum(v[0] for v in prof.values())), "clocks": sampler.stop(),
                       "finite": bool(torch.isfinite(logits).all().item()), "device_status": ctx.device_status()}), flush=True)

@@ -36,6 +36,7 @@ class TrainNoise:
     first_thread: int = 0
     noise_reuse: int = 0
     mm_indices: Optional[Sequence[int]] = None      # None = every MM parameter
+    caches: Optional[dict] = None                   # parameter index -> ops.FactorCache (see build_caches)
     pos_emb: Optional[torch.Tensor] = None          # (n, num_tokens, d_model)
     out_gain: Optional[torch.Tensor] = None         # (n, 1)
     beta: Optional[torch.Tensor] = None             # (n, 1)
@@ -108,8 +109,25 @@ class SnnTransformer:
         if perturb:
             kw = dict(sigma=noise.sigma, rank=noise.rank, key=noise.base_keys[idx], epoch=noise.epoch,
                       first_thread=noise.first_thread, noise_reuse=noise.noise_reuse)
+            if noise.caches is not None and idx in noise.caches:
+                kw["cache"] = noise.caches[idx]
         y = ops.perturbed_linear(x, w, n_pop=n, bm=tokens, t_steps=t_steps, perturb=perturb, out=out, **kw)
         return y
+
+    def build_caches(self, noise: TrainNoise, n: int) -> dict:
+        """The chunk's factors of every MM parameter, generated once (what the reference trainer does
+        with `batched_lora_noise` before the forward and the gradient einsum of a chunk,
+        snn_transformer_train.rs:401-418).  Assign the result to `noise.caches`."""
+        if n % 2 or noise.first_thread % 2:
+            raise ValueError("a cache covers whole antithetic pairs: n and first_thread must be even")
+        caches = {}
+        for idx, (p, cls) in enumerate(zip(self.params(), self.es_map())):
+            if cls != MM_PARAM or (noise.mm_indices is not None and idx not in noise.mm_indices):
+                continue
+            a, b = p.shape
+            caches[idx] = ops.FactorCache(noise.base_keys[idx], noise.epoch, noise.noise_reuse, noise.rank, a, b,
+                                          n // 2, first_pair=noise.first_thread // 2, device=self.device)
+        return caches
 
     # ---- encode, snn_transformer.rs:305-339 ----
     def encode(self, x: torch.Tensor, noise: Optional[TrainNoise]) -> torch.Tensor:

@@ -81,6 +81,10 @@ def test_forward_batched_matches_oracle_composition(hs, oracle, perturbed):
     assert got.shape == (n, classes)
     assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
     if perturbed:
+        # factors generated once for the chunk give the bits of regenerated ones
+        noise.caches = model.build_caches(noise, n)
+        cached = model.forward_batched(torch.as_tensor(x, device="cuda"), noise).cpu().numpy()
+        assert np.array_equal(cached, got)
         # antithetic partners (thread ids 4 and 5) see different weights: their logits differ
         clean = model.forward_batched(torch.as_tensor(x, device="cuda"), None).cpu().numpy()
         assert np.abs(got - clean).max() > 1e-4
