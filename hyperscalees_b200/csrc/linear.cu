@@ -313,10 +313,21 @@ extern "C" {
 
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     if (g == nullptr || g->t_steps < 1 || g->n_pop < 1 || g->bm < 1 || g->k < 1 || g->a < 1) return 0;
+    if (g->lif == 2) {
+        // the per-pair path when it finishes the scan itself, else whatever the layer without the scan takes
+        const bool pair_ok2 = pair_path_supports(*g);
+        const bool takes_pair = (g->algo == HSES_ALGO_PAIR && pair_ok2) ||
+                                (g->algo == HSES_ALGO_AUTO && !tensor_path_supports(*g) && pair_ok2);
+        if (takes_pair && pair_path_fuses_scan(*g)) return pair_path_workspace_bytes(*g);
+        hses_linear_args h = *g;
+        h.lif = 0;
+        return hses_perturbed_linear_workspace_bytes(&h);
+    }
     // the tensor path always needs room for the split weights, the general path
     // only needs scratch when it perturbs
     if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_TENSOR) && tensor_path_supports(*g))
         return tensor_path_workspace_bytes(*g);
+    if (g->algo == HSES_ALGO_AUTO && small_path_supports(*g)) return small_path_workspace_bytes(*g);
     if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_PAIR) && pair_path_supports(*g))
         return pair_path_workspace_bytes(*g);
     if (g->algo == HSES_ALGO_TENSOR || g->algo == HSES_ALGO_PAIR || !g->perturb) return 0;
@@ -352,6 +363,7 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
     }
     if (g->algo == HSES_ALGO_TENSOR || (g->algo == HSES_ALGO_AUTO && tc_ok))
         return run_tensor_path(ctx, as_stream(stream), *g);
+    if (g->algo == HSES_ALGO_AUTO && small_path_supports(*g)) return run_small_path(ctx, as_stream(stream), *g);
     bool pair_ok = pair_path_supports(*g);
     if (g->algo == HSES_ALGO_PAIR && !pair_ok) {
         set_error("hses_perturbed_linear: the per-pair path does not cover this shape");

@@ -61,6 +61,7 @@ FwdPlan plan_forward(const hses_snn_model* m, const hses_pop_args* p) {
         g.param = reinterpret_cast<const float*>(0x100);
         g.out = reinterpret_cast<float*>(0x100);
         if (l == 0) g.x_row_stride = (m->dims[0] + 3) / 4 * 4;
+        if (l < m->n_layers - 1) g.lif = 2;   // hidden layers run with the fused scan (same choice of path as the call)
         f.lin_bytes = std::max(f.lin_bytes, hses_perturbed_linear_workspace_bytes(&g));
         // the first layer may arrive with another pitch: leave room for the general path too
         g.algo = HSES_ALGO_SIMT;

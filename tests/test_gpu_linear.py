@@ -106,3 +106,46 @@ def test_shape_errors_are_reported(hs):
         ops.perturbed_linear(x, w, n_pop=2, bm=4)
     with pytest.raises(ValueError):
         ops.perturbed_linear(x, torch.zeros(4, 16, device="cuda"), n_pop=3, bm=4)
+
+
+@pytest.mark.parametrize("n_pop,bm,k,a,rank,t_steps,first,lif", [
+    (16, 16, 64, 16, 8, 1, 0, False),    # a head projection of the transformer
+    (16, 16, 64, 64, 8, 1, 2, True),     # output / feed-forward projection, one LIF step, shifted thread ids
+    (6, 16, 49, 64, 8, 4, 0, False),     # the encoder: 128 rows per pair in four chunks of 32, k not a multiple of 4
+    (4, 3, 20, 10, 4, 2, 4, False),      # 12 rows per pair (partial chunk), ten columns, rank 4
+    (2, 1, 5, 3, 16, 1, 0, False),       # tiny everything, rank 16
+])
+def test_narrow_layer_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first, lif):
+    """Layers with k, a <= 64 and rank <= 16 take the persistent narrow-layer kernel (algo AUTO):
+    same results as the oracle and as the general path, with regenerated and with cached factors."""
+    from hyperscalees_b200 import ops, core
+    ctx = core.get_context(0)
+    g = np.random.default_rng(k * 100 + a)
+    x = g.standard_normal((t_steps, n_pop, bm, k)).astype(np.float32)
+    w = (g.standard_normal((a, k)) / np.sqrt(k)).astype(np.float32)
+    key, sigma = 0x77C0FFEE, 0.4
+    kw = dict(n_pop=n_pop, bm=bm, t_steps=t_steps, sigma=sigma, rank=rank, key=key, epoch=2, first_thread=first)
+    if lif:
+        kw.update(lif=True, tau_m=2.0, v_th=0.1)
+    xd, wd = torch.as_tensor(x, device="cuda"), torch.as_tensor(w, device="cuda")
+    ctx.profile_enable(True)
+    got = ops.perturbed_linear(xd, wd, **kw)
+    names = {n for n, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    assert "small_pair" in names
+    simt = ops.perturbed_linear(xd, wd, algo=ops.ALGO_SIMT, **kw)
+    cache = ops.FactorCache(key, 2, 0, rank, a, k, n_pop // 2, first_pair=first // 2)
+    cached = ops.perturbed_linear(xd, wd, cache=cache, **kw)
+    assert torch.equal(cached, got)
+    if lif:
+        assert (got != simt).float().mean().item() <= 1e-3
+    else:
+        want = np.empty((t_steps * n_pop * bm, a), np.float32)
+        for t in range(t_steps):
+            for i in range(n_pop):
+                r0 = (t * n_pop + i) * bm
+                want[r0:r0 + bm] = oracle.do_mm(x[t, i], w, sigma, rank, key, (2, first + i), 0, True)
+        scale = max(1.0, np.abs(want).max())
+        assert np.abs(got.cpu().numpy() - want).max() <= 2e-5 * scale
+        assert (got - simt).abs().max().item() <= 2e-5 * scale
+    assert ctx.device_status() == 0
