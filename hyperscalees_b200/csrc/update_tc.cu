@@ -2,7 +2,8 @@
 //   sum_p (f_2p - f_2p+1) * A_p B_pᵀ          (simple_lora_update, eggroll.rs:353-373, pair-folded)
 // as one dense contraction (a, K)·(K, b) over K = pairs * rank — the 2-D GEMM form of
 // lora_einsum_raw (eggroll.rs:726-738) — for the wide-rank, large-population case in which it
-// dominates the step (a multiple of 128, rank a multiple of 64).
+// dominates the step (rank from 48 up; ranks that are not multiples of 64 run with a zero-filled
+// last k-block).
 //
 //   launch 1  pair_weight_range   largest |f_2p - f_2p+1| -> one power-of-two scale for all weights
 //   launch 2  update_tc           one CTA per (128 x bn output tile, K split), eighteen warps:
@@ -119,7 +120,8 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int tile = blockIdx.x, split = blockIdx.y;
     const int mt = tile / g.n_tiles, nt = tile - mt * g.n_tiles;
     const int64_t p_lo = g.pairs * split / g.splits, p_hi = g.pairs * (split + 1) / g.splits;
-    const int kq = g.rank / UT_BK;                      // k-blocks per pair
+    const int kq = (g.rank + UT_BK - 1) / UT_BK;        // k-blocks per pair; columns past the rank of a ragged
+                                                        // last block arrive as zeros (TMA fill) and add nothing
     const int64_t k_blocks = (p_hi - p_lo) * kq;
 
     if (threadIdx.x == 0) {
@@ -315,7 +317,10 @@ size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 bool update_tc_supports(int a, int b, int rank) {
     // rows of A beyond a and rows of B beyond b are written as zeros, so only the rank is constrained
-    return a >= 1 && rank >= UT_BK && rank % UT_BK == 0 && b >= 1 && b <= (1 << 20) && a <= (1 << 20);
+    // (rows of 16-byte multiples for the tensor map; a last k-block filled to less than three quarters
+    // would mostly convert zeros)
+    return a >= 1 && rank >= 48 && rank % 4 == 0 && (rank % UT_BK == 0 || rank % UT_BK >= 32) && b >= 1 &&
+           b <= (1 << 20) && a <= (1 << 20);
 }
 
 UpdateTcPlan plan_update_tc(int a, int b, int rank, int64_t n, bool need_raw) {

@@ -94,6 +94,9 @@ def test_alteggroll_noiser_mirror(hs, oracle):
     (128, 16, 64, 2, 0),        # a single pair, the narrowest tile
     (10, 128, 64, 24, 0),       # readout layer: fewer rows than one tile
     (130, 70, 64, 6, 2),        # ragged in both directions
+    (128, 784, 96, 16, 0),      # rank 96: the second k-block of a pair is half zero fill
+    (40, 50, 48, 10, 2),        # rank 48: one k-block, three quarters full
+    (128, 128, 160, 6, 0),      # rank 160: three k-blocks, the last one half full
 ])
 def test_tensor_core_update_matches_oracle_and_general_kernel(hs, oracle, a, b, rank, n, first):
     """The tcgen05 contraction of the update against the oracle and against the fp32 kernel."""
