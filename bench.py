@@ -10,6 +10,16 @@ members (weak scaling, no data-path collective: the path emits spikes only).
 
 Metric: member-evaluations per second = n_pop * Bm * T (T = 1) per second.
 
+The same JSON line carries two more blocks, measured after the headline:
+  population_step  one full ES step of the spiking MLP 784-128-128-128-10 at 65 536 members of one
+                   sample, T = 8, rank 64 (ranks 96 and 128 too on one GPU): encode -> perturbed
+                   forward -> fitness -> all-gather -> z-score -> sharded update -> one gradient
+                   sum -> AdamW, STRONG scaling (the population is split over the N ranks, both
+                   exchanges inside the timed region), with a check that every rank ends a step
+                   with bit-identical parameters and that they match the single-GPU step;
+  streaming        the HBM-bound kernels of the path (encode, LIF scan, attention, WKV-7), each
+                   timed alone against the measured copy bandwidth.
+
     python bench.py --gpus N --steps K --warmup W            # the CUDA path
     python bench.py --impl reference --gpus N --steps K ...   # CPU restatement of the reference
 """
@@ -35,7 +45,7 @@ KEY = 0x3C6EF372FE94F82A          # base key of parameter index 1
 SIGMA, RANK, TAU_M, V_TH = 0.02, 16, 20.0, 0.3
 N_POP, BM, K_DIM, A_DIM = 8192, 16, 1024, 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by its members, from an ncu
-# capture of these kernels at n_pop = 2048 (its summary is kept in the profiles folder)
+# capture of these kernels at n_pop = 2048: constants of that capture, not a measurement of this run
 NCU_TRAFFIC_BYTES_PER_MEMBER = {"linear_tc": (209.6e6 + 92.7e6) / 2048, "lowrank_t": (157.0e6 + 107.0e6) / 2048}
 
 
@@ -162,8 +172,9 @@ def run_reference(args, rank: int, world: int):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": config_dict(args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"per step: {sample}; C restatement of the reference path, "
-                                       "OpenMP over members"},
+                             "sample": f"per step: {sample}; C restatement of the reference path, OpenMP over "
+                                       "members, register-blocked 4x4 SIMD base product (not a cache-blocked "
+                                       "library GEMM)"},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
             "note": "the reference's Rust/Burn CPU path cannot be built on this box (no Rust toolchain); "
@@ -269,6 +280,29 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                   "cache_build_ms": build_ms,
                   "note": "factors read from a device cache built once outside the timed region"}
         del cache
+    # ---- the two extra blocks of the line (see the module docstring) ----
+    pop_block, stream_block = None, None
+    if not args.kernel_only and not args.headline_only:
+        del x_dev, out_dev, pipe
+        torch.cuda.empty_cache()
+        comm = make_comm(ctx, world)
+        pop_block = population_step_case(rank, world, dev, ctx, comm, args.pop_members, 1, 64, "auto",
+                                         args.steps, args.warmup, check=True, single_gpu_leg=True)
+        if world == 1:
+            # the factors regenerated in registers in both halves of the step instead of cached
+            regen = population_step_case(rank, world, dev, ctx, comm, args.pop_members, 1, 64, "off",
+                                         max(2, args.steps // 4), 3, check=False, single_gpu_leg=False)
+            pop_block["regenerating"] = {k: regen[k] for k in ("ms_per_step", "member_evals_per_sec", "kernel_ms_per_step")}
+            pop_block["rank_sweep"] = {}
+            for r in (96, 128):
+                blk = population_step_case(rank, world, dev, ctx, comm, args.pop_members, 1, r, "auto",
+                                           args.steps, args.warmup, check=False, single_gpu_leg=False)
+                pop_block["rank_sweep"][str(r)] = {k: blk[k] for k in ("ms_per_step", "member_evals_per_sec",
+                                                                      "kernel_ms_per_step", "device_status")}
+            stream_block = streaming_block(dev, ctx, args.steps, args.warmup,
+                                           only=("poisson_encode", "lif_scan", "spiking_attention mode 0", "wkv7"))
+        if comm is not None:
+            comm.destroy()
     clocks = sampler.stop() if sampler else None
 
     evals_per_step = N_POP * BM * world
@@ -291,7 +325,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                                    "for algorithmic flops is one third of the peak",
                     "executed_tflops": 3.0 * achieved,
                     "traffic": NCU_TRAFFIC_BYTES_PER_MEMBER.get(top_name, 0) * N_POP or None,
-                    "traffic_source": "ncu capture at n_pop=2048 (profiles/), scaled by members per launch",
+                    "traffic_source": "constant from the committed ncu summary of this kernel (capture at n_pop = 2048), "
+                                      "scaled by the members of one launch; not measured in this run",
                     "algorithmic_flops_per_launch": flops,
                     "avg_launch_ms": per_launch_s * 1e3,
                     "kernel_time_share": {k: round(v[1] / sum(p[1] for p in prof.values()), 4) for k, v in prof.items()}}
@@ -302,27 +337,193 @@ def run_ours(args, rank: int, local_rank: int, world: int):
             O.set_num_threads(len(os.sched_getaffinity(0)))
             r, sample, secs = cpu_rate(O, x_np, w_np, 12.0)
             cpu = {"value": r, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
-                   "sample": f"{sample}, {secs:.1f} s; C restatement of the reference path, OpenMP over members"}
+                   "sample": f"{sample}, {secs:.1f} s; C restatement of the reference path, OpenMP over members, "
+                             "register-blocked 4x4 SIMD base product (not a cache-blocked library GEMM)"}
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": config_dict(world), "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
-                "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached}
+                "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached,
+                "population_step": pop_block, "streaming": stream_block}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_population_step(args, rank: int, local_rank: int, world: int):
-    """Secondary workload: one full ES step of the spiking MLP 784-128-128-128-10 (encode ->
-    perturbed forward over T = 8 steps -> fitness -> all-gather -> z-score -> update -> AdamW),
-    strong scaling: the population of --n-pop members is sharded over the ranks, the update is
-    replicated.  Reports member-evaluations/s = n_pop * bm * T per second."""
+POP_DIMS, POP_T = [784, 128, 128, 128, 10], 8
+
+
+def pop_inputs(n_total: int, bm: int):
+    """Seeded synthetic images of MNIST's shape (each pixel 0 with p = 0.8, else U(0,1); seed 0) and labels."""
+    g = np.random.Generator(np.random.PCG64(0))
+    img = g.random((n_total * bm, 784), dtype=np.float32)
+    img[g.random((n_total * bm, 784)) < 0.8] = 0.0
+    return img, g.integers(0, 10, n_total * bm).astype(np.int32)
+
+
+def population_step_case(rank: int, world: int, dev, ctx, comm, n_total: int, bm: int, r: int, cache: str,
+                         steps: int, warmup: int, check: bool, single_gpu_leg: bool):
+    """One full ES step of the spiking MLP, the population split over the ranks (strong scaling).
+    Per step and rank: encode -> forward -> fitness of its members; all-gather of the raw fitness;
+    z-score; contraction of its own members' factors; ONE sum of the flat gradient buffer; the same
+    AdamW step everywhere.  Both exchanges go through the library's communicator and are inside the
+    timed region.  Returns the block for the JSON line (every rank must call; rank 0's is printed)."""
     import torch
     import torch.distributed as dist
-    from hyperscalees_b200 import core, models, noiser, parallel
+    from hyperscalees_b200 import models, noiser, parallel
+
+    lo, hi = parallel.shard_range(n_total, rank, world)
+    img, labels = pop_inputs(n_total, bm)
+    di = torch.as_tensor(img[lo * bm:hi * bm], device=dev)
+    dl = torch.as_tensor(labels[lo * bm:hi * bm], device=dev)
+    keys = models.default_base_keys(len(POP_DIMS))
+
+    def make(first, n_local, cache_policy, whole):
+        net = models.SnnMlp(POP_DIMS, tau_m=20.0, v_th=0.3, seed=0, device=dev)
+        frozen, nz = noiser.init_noiser(net.params(), 0.02, 0.01, 0, False, 0, r, noiser.Solver.adamw(0.01))
+        return models.PopulationStep(net, frozen, nz, keys, POP_T, n_local, bm, first_thread=first,
+                                     cache=cache_policy, n_total=n_total if whole else None)
+
+    def sharded_step(st):
+        raw = st.eval(di, dl, [1, 2, 3, 4 + rank])
+        full = parallel.allgather_fitness(raw, n_total, comm=comm)
+        st.update_sharded(full, comm=comm)
+        return full
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def checksum(params):
+        # equal bit patterns give equal sums; the sums of all ranks are compared on rank 0
+        return [int(p.view(torch.int32).to(torch.int64).sum().item()) for p in params]
+
+    block = {"workload": f"population step: SNN MLP 784-128-128-128-10, n_pop {n_total}, bm {bm}, T {POP_T}, rank {r}, "
+                         f"sigma 0.02, AdamW; factor cache {cache}",
+             "n_pop": n_total, "rank": r, "scaling": "strong", "n_gpus": world,
+             "parallelism": f"population sharded over {world} GPU(s): fitness all-gather, per-shard partial gradients, "
+                            "one gradient sum, identical solver step on every rank"}
+
+    # ---- check: one step from fresh parameters on every rank, against the single-GPU step -------------
+    if check:
+        st = make(lo, hi - lo, cache, False)
+        full = sharded_step(st)
+        torch.cuda.synchronize()
+        sums = checksum(st.params)
+        fsum = int(full.view(torch.int32).to(torch.int64).sum().item())
+        gathered = [None] * world
+        if world > 1:
+            dist.all_gather_object(gathered, (sums, fsum))
+        else:
+            gathered = [(sums, fsum)]
+        block["params_bit_identical_on_all_ranks"] = all(gth == gathered[0] for gth in gathered)
+        if rank == 0:
+            # the same step on this GPU alone: the shards' forwards as separate calls (the encoder's
+            # stream is indexed inside a call's batch and seeded per rank), factors regenerated
+            # instead of cached, then the replicated update over the whole fitness vector
+            ref = make(0, n_total, "off", True)
+            raws = []
+            for q in range(world):
+                qlo, qhi = parallel.shard_range(n_total, q, world)
+                part = make(qlo, qhi - qlo, "off", False)
+                part.params, part.net.weights, part.net.out_gain = ref.params, ref.params[:-1], ref.params[-1]
+                raws.append(part.eval(torch.as_tensor(img[qlo * bm:qhi * bm], device=dev),
+                                      torch.as_tensor(labels[qlo * bm:qhi * bm], device=dev), [1, 2, 3, 4 + q]))
+                del part
+            raw_ref = torch.cat(raws)
+            block["fitness_bit_identical_to_single_gpu"] = bool(torch.equal(raw_ref, full))
+            ref.update(raw_ref)
+            torch.cuda.synchronize()
+            rel = max(((a - b).abs().max() / b.abs().max().clamp_min(1e-12)).item()
+                      for a, b in zip(st.params, ref.params))
+            block["params_max_rel_diff_to_single_gpu"] = rel
+            block["params_within_1e-3_of_single_gpu"] = bool(rel <= 1e-3)
+            del ref, raws, raw_ref
+        del st
+        torch.cuda.empty_cache()
+        barrier()
+
+    # ---- timed: K steps, both exchanges inside ------------------------------------------------------
+    st = make(lo, hi - lo, cache, False)
+    for _ in range(max(warmup, 3)):
+        sharded_step(st)
+    barrier()
+    ctx.profile_enable(False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        sharded_step(st)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    barrier()
+    launches = sum(v[0] for v in ctx.profile_read().values())
+    # second pass over the same K steps with per-kernel CUDA events (the exchanges included)
+    ctx.profile_enable(True)
+    for _ in range(steps):
+        sharded_step(st)
+    torch.cuda.synchronize()
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    status = ctx.device_status()
+    del st
+    torch.cuda.empty_cache()
+    ms_step = float(ms.item()) / steps
+    evals = n_total * bm * POP_T
+    block.update({"ms_per_step": ms_step, "member_evals_per_sec": evals / (ms_step * 1e-3),
+                  "gpu_launches_per_step": launches / steps,
+                  "kernel_ms_per_step": {k: round(v[1] / steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+                  "collective_ms_per_step": round(sum(v[1] for k, v in prof.items()
+                                                      if k in ("allgather_fitness", "allreduce_grads")) / steps, 4),
+                  "device_status": status})
+
+    # ---- the whole population on rank 0's GPU alone, in the same job: the strong-scaling yardstick --
+    if single_gpu_leg and world > 1:
+        barrier()
+        if rank == 0:
+            one = make(0, n_total, cache, True)
+            di1, dl1 = torch.as_tensor(img, device=dev), torch.as_tensor(labels, device=dev)
+
+            def one_step():
+                one.update(one.eval(di1, dl1, [1, 2, 3, 4]))
+
+            for _ in range(max(warmup, 3)):
+                one_step()
+            torch.cuda.synchronize()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            for _ in range(steps):
+                one_step()
+            f1.record()
+            torch.cuda.synchronize()
+            ms1 = f0.elapsed_time(f1) / steps
+            block["single_gpu_ms_per_step"] = ms1
+            block["speedup_over_single_gpu"] = ms1 / ms_step
+            del one, di1, dl1
+            torch.cuda.empty_cache()
+        barrier()
+    return block
+
+
+def make_comm(ctx, world: int):
+    """The library's own communicator (hses_comm_* behind the C ABI); its id travels through the
+    torch.distributed group that the launcher's environment already describes."""
+    if world == 1:
+        return None
+    from hyperscalees_b200 import parallel
+    return parallel.Comm.from_process_group(ctx)
+
+
+def run_population_step(args, rank: int, local_rank: int, world: int):
+    """--workload population_step: the block above alone, for one rank of the factors."""
+    import torch
+    import torch.distributed as dist
+    from hyperscalees_b200 import core
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -330,155 +531,134 @@ def run_population_step(args, rank: int, local_rank: int, world: int):
         os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=dev)
     ctx = core.get_context(local_rank)
-    dims, T, bm, n_total, r = [784, 128, 128, 128, 10], 8, args.bm, args.n_pop, args.rank
-    lo, hi = parallel.shard_range(n_total, rank, world)
-    n_local = hi - lo
-    g = np.random.Generator(np.random.PCG64(0))
-    img = g.random((n_total * bm, 784), dtype=np.float32)
-    img[g.random((n_total * bm, 784)) < 0.8] = 0.0          # MNIST-like sparsity, seed 0
-    labels = g.integers(0, 10, n_total * bm).astype(np.int32)
-    di = torch.as_tensor(img[lo * bm:hi * bm], device=dev)
-    dl = torch.as_tensor(labels[lo * bm:hi * bm], device=dev)
-    keys = models.default_base_keys(len(dims))
-    net = models.SnnMlp(dims, tau_m=20.0, v_th=0.3, seed=0, device=dev)
-    frozen, nz = noiser.init_noiser(net.params(), 0.02, 0.01, 0, False, 0, r, noiser.Solver.adamw(0.01))
-    # each rank caches the factors of its own members only: forward and update both read them
-    step_obj = models.PopulationStep(net, frozen, nz, keys, T, n_local, bm, first_thread=lo,
-                                     cache=args.cache, n_total=n_total if world == 1 else None)
-
-    def step():
-        raw = step_obj.eval(di, dl, [1, 2, 3, 4 + rank])
-        if world > 1:
-            # sharded update: every rank contracts its own members' factors, one all-reduce of the
-            # gradients (538 KB) follows the all-gather of the fitness (n_pop * 4 bytes)
-            step_obj.update_sharded(parallel.allgather_fitness(raw, n_total))
-        else:
-            step_obj.update(raw)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # the sampler starts before the warm-up steps: nvidia-smi needs a few hundred ms to deliver its
-    # first line, longer than the timed region of a short run
+    comm = make_comm(ctx, world)
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    ctx.profile_enable(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    barrier()
-    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
-    ctx.profile_enable(False)
+    block = population_step_case(rank, world, dev, ctx, comm, args.n_pop, args.bm, args.rank, args.cache,
+                                 args.steps, args.warmup, check=not args.kernel_only,
+                                 single_gpu_leg=not args.kernel_only)
     clocks = sampler.stop() if sampler else None
     if rank == 0:
-        ms_total = float(ms.item())
-        evals = n_total * bm * T
-        tot = sum(v[1] for v in prof.values())
-        line = {"metric": METRIC, "value": evals * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+        line = {"metric": METRIC, "value": block["member_evals_per_sec"], "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": block["ms_per_step"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic",
-                "config": {"workload": f"population step: SNN MLP 784-128-128-128-10, n_pop {n_total}, bm {bm}, T 8, "
-                                       f"rank {r}, sigma 0.02, AdamW; factor cache {args.cache}",
-                           "n_pop": n_total, "bm": bm, "t_steps": T, "rank": r, "cache": args.cache,
-                           "parallelism": f"population sharded over {world} GPU(s): fitness all-gather, per-shard partial "
-                                          "gradients, gradient all-reduce, identical solver step on every rank"},
-                "kernel_ms_per_step": {k: round(v[1] / args.steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
-                "kernel_time_share": {k: round(v[1] / tot, 4) for k, v in prof.items()},
-                "gpu_launches": int(sum(v[0] for v in prof.values())), "clocks": clocks,
-                "device_status": ctx.device_status()}
+                "data": "synthetic", "config": {"workload": block["workload"]}, "population_step": block,
+                "gpu_launches": int(block["gpu_launches_per_step"] * args.steps), "clocks": clocks}
         print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.destroy()
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_streaming_kernels(args, local_rank: int):
-    """Secondary workload: the HBM-bound kernels around the perturbed linear layer (Poisson
-    encode, LIF scan, spiking attention, WKV-7, norms, solver), each timed alone with CUDA
-    events on inputs larger than L2; reports algorithmic bytes / time against the measured
-    copy bandwidth.  One GPU."""
+def streaming_block(dev, ctx, steps: int, warmup: int, shrink: int = 1, only=None):
+    """The HBM-bound kernels around the perturbed linear layer, each timed alone with CUDA events on
+    inputs larger than L2; algorithmic bytes / time against the measured copy bandwidth.  `only`
+    keeps the cases whose name starts with one of the given prefixes."""
     import torch
-    from hyperscalees_b200 import core, ops
+    from hyperscalees_b200 import ops
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    ctx = core.get_context(local_rank)
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *shape: torch.rand(*shape, device=dev, generator=g)
-    cases = {}
-    sh = max(1, args.shrink)   # divides the leading dimension of every case (reduced cases for ncu captures)
-
-    probs = rnd(131072 // sh, 784)
-    enc_out = torch.empty(8, 131072 // sh, 784, device=dev)
-    cases[f"poisson_encode [{131072 // sh}x784] -> T=8"] = (
-        lambda: ops.poisson_encode(probs, 8, (1, 2, 3, 4), out=enc_out), probs.numel() * 4 + enc_out.numel() * 4)
-    cur = rnd(8, 131072 // sh, 128)
-    v0 = torch.zeros(131072 // sh, 128, device=dev)
-    lif_out = torch.empty_like(cur)
-    cases[f"lif_scan T=8 [{131072 // sh}x128]"] = (
-        lambda: ops.lif_scan(cur, 2.0, 1.0, v=v0, reset_mode=ops.RESET_SUBTRACT, out=lif_out), 2 * cur.numel() * 4 + 2 * v0.numel() * 4)
-    q, k, v = rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64)
-    cases[f"spiking_attention mode 0 [{32768 // sh} seq x 64 tok x 4 heads x 16]"] = (
-        lambda: ops.spiking_attention(q, k, v, 4, mode=0), 4 * q.numel() * 4)
-    cases["spiking_attention mode 2 (relaxation + softmax)"] = (
-        lambda: ops.spiking_attention(q, k, v, 4, mode=2), 4 * q.numel() * 4)
-    wk = [rnd(256 // sh, 256, 12, 64) * 0.5 for _ in range(6)]
-    wk[1] = 0.9 + 0.1 * wk[1]
-    state = torch.zeros(256 // sh, 12, 64, 64, device=dev)
-    cases[f"wkv7 [{256 // sh} seq x 256 tok x 12 heads x 64]"] = (
-        lambda: ops.wkv7(*wk, state), 7 * wk[0].numel() * 4 + 2 * state.numel() * 4)
-    xn = rnd(262144 // sh, 768)
-    wn, bn = torch.ones(768, device=dev), torch.zeros(768, device=dev)
-    cases[f"layer_norm [{262144 // sh}x768]"] = (lambda: ops.layer_norm(xn, wn, bn), 2 * xn.numel() * 4)
-    cases[f"group_norm 12 groups [{262144 // sh}x768]"] = (lambda: ops.group_norm(xn, 12, wn, bn), 2 * xn.numel() * 4)
-    cases[f"relu_square [{262144 // sh}x768]"] = (lambda: ops.relu_square(xn), 2 * xn.numel() * 4)
-    cases[f"rate_encode [{262144 // sh}x768]"] = (lambda: ops.rate_encode(xn, 4.0), 2 * xn.numel() * 4)
-    par, grd = rnd((1 << 26) // sh), rnd((1 << 26) // sh)
-    m1, m2 = torch.zeros_like(par), torch.zeros_like(par)
-    cases[f"solver_step AdamW [{(1 << 26) // sh} params]"] = (
-        lambda: ops.solver_step(ops.ADAMW, 1, par, grd, m1, m2, weight_decay=0.01), 7 * par.numel() * 4)
-
-    noise = torch.empty((1 << 28) // sh, device=dev)
-    cases[f"prng_normal_half [{noise.numel()} normals]"] = (
-        lambda: ops.prng_normal_half(noise.numel() // 128, 0.0, 1.0, (1, 2, 3, 4), out=noise), noise.numel() * 4)
-
+    sh = max(1, shrink)   # divides the leading dimension of every case (reduced cases for ncu captures)
     peaks = measured_peaks()
-    sampler = ClockSampler(local_rank)
-    ctx.profile_enable(True)
     out = {}
-    for name, (fn, nbytes) in cases.items():
-        for _ in range(max(args.warmup, 3)):
+
+    def run(name, build):
+        if only is not None and not any(name.startswith(p) for p in only):
+            return
+        fn, nbytes = build()
+        for _ in range(max(warmup, 3)):
             fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / args.steps
+        ms = e0.elapsed_time(e1) / steps
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1), "GB_per_s": round(gbs, 1),
                      "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 3)}
-    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+        del fn
+        torch.cuda.empty_cache()
+
+    def poisson():
+        probs = rnd(131072 // sh, 784)
+        enc_out = torch.empty(8, 131072 // sh, 784, device=dev)
+        return (lambda: ops.poisson_encode(probs, 8, (1, 2, 3, 4), out=enc_out)), probs.numel() * 4 + enc_out.numel() * 4
+
+    def lif():
+        cur = rnd(8, 131072 // sh, 128)
+        v0 = torch.zeros(131072 // sh, 128, device=dev)
+        lif_out = torch.empty_like(cur)
+        return (lambda: ops.lif_scan(cur, 2.0, 1.0, v=v0, reset_mode=ops.RESET_SUBTRACT, out=lif_out)), \
+            2 * cur.numel() * 4 + 2 * v0.numel() * 4
+
+    def attention(mode):
+        def build():
+            q, k, v = rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64)
+            return (lambda: ops.spiking_attention(q, k, v, 4, mode=mode)), 4 * q.numel() * 4
+        return build
+
+    def wkv():
+        wk = [rnd(256 // sh, 256, 12, 64) * 0.5 for _ in range(6)]
+        wk[1] = 0.9 + 0.1 * wk[1]
+        state = torch.zeros(256 // sh, 12, 64, 64, device=dev)
+        return (lambda: ops.wkv7(*wk, state)), 7 * wk[0].numel() * 4 + 2 * state.numel() * 4
+
+    def norm(kind):
+        def build():
+            xn = rnd(262144 // sh, 768)
+            wn, bn = torch.ones(768, device=dev), torch.zeros(768, device=dev)
+            fn = {"layer_norm": lambda: ops.layer_norm(xn, wn, bn), "group_norm": lambda: ops.group_norm(xn, 12, wn, bn),
+                  "relu_square": lambda: ops.relu_square(xn), "rate_encode": lambda: ops.rate_encode(xn, 4.0)}[kind]
+            return fn, 2 * xn.numel() * 4
+        return build
+
+    def solver():
+        par, grd = rnd((1 << 26) // sh), rnd((1 << 26) // sh)
+        m1, m2 = torch.zeros_like(par), torch.zeros_like(par)
+        return (lambda: ops.solver_step(ops.ADAMW, 1, par, grd, m1, m2, weight_decay=0.01)), 7 * par.numel() * 4
+
+    def prng():
+        noise = torch.empty((1 << 28) // sh, device=dev)
+        return (lambda: ops.prng_normal_half(noise.numel() // 128, 0.0, 1.0, (1, 2, 3, 4), out=noise)), noise.numel() * 4
+
+    run(f"poisson_encode [{131072 // sh}x784] -> T=8", poisson)
+    run(f"lif_scan T=8 [{131072 // sh}x128]", lif)
+    run(f"spiking_attention mode 0 [{32768 // sh} seq x 64 tok x 4 heads x 16]", attention(0))
+    run("spiking_attention mode 2 (relaxation + softmax)", attention(2))
+    run(f"wkv7 [{256 // sh} seq x 256 tok x 12 heads x 64]", wkv)
+    run(f"layer_norm [{262144 // sh}x768]", norm("layer_norm"))
+    run(f"group_norm 12 groups [{262144 // sh}x768]", norm("group_norm"))
+    run(f"relu_square [{262144 // sh}x768]", norm("relu_square"))
+    run(f"rate_encode [{262144 // sh}x768]", norm("rate_encode"))
+    run(f"solver_step AdamW [{(1 << 26) // sh} params]", solver)
+    run(f"prng_normal_half [{(1 << 28) // sh} normals]", prng)
+    return {"peak": {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}, "kernels": out,
+            "note": "each kernel timed alone, inputs larger than L2; GB/s = algorithmic bytes / CUDA-event time"}
+
+
+def run_streaming_kernels(args, local_rank: int):
+    """--workload streaming_kernels: every streaming kernel of the path, one GPU."""
+    import torch
+    from hyperscalees_b200 import core
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = core.get_context(local_rank)
+    sampler = ClockSampler(local_rank)
     ctx.profile_enable(False)
+    blk = streaming_block(dev, ctx, args.steps, args.warmup, args.shrink)
+    launches = sum(v[0] for v in ctx.profile_read().values())
     clocks = sampler.stop()
     print(json.dumps({"metric": "achieved HBM bandwidth of the streaming kernels", "unit": "GB/s", "n_gpus": 1,
                       "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
                       "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "streaming kernels, each timed alone; inputs larger than L2"},
-                      "peak": {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}, "kernels": out,
-                      "gpu_launches": int(sum(v[0] for v in prof.values())), "clocks": clocks,
+                      "peak": blk["peak"], "kernels": blk["kernels"],
+                      "gpu_launches": int(launches), "clocks": clocks,
                       "device_status": ctx.device_status()}), flush=True)
 
 
@@ -547,7 +727,11 @@ def main():
     ap.add_argument("--shrink", type=int, default=1,
                     help="streaming_kernels: divide every case's leading dimension (reduced cases for ncu captures)")
     ap.add_argument("--kernel-only", action="store_true",
-                    help="skip the end-to-end and CPU legs (profiling runs)")
+                    help="skip the end-to-end and CPU legs and the extra blocks (profiling runs)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="microbench: leave out the population_step and streaming blocks")
+    ap.add_argument("--pop-members", type=int, default=65536,
+                    help="microbench: population of the population_step block")
     args = ap.parse_args()
     globals()["N_POP"] = args.n_pop
     rank = int(os.environ.get("RANK", "0"))

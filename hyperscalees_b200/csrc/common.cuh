@@ -36,6 +36,11 @@ int get_hop_table(hses_ctx* ctx, uint64_t distance, const uint64_t** dev_tab);
 
 constexpr int kJumpLevels = 48;
 
+// Multiprocessor count the split-K planners size their grids for: that of the current CUDA
+// device, read once (the *_workspace_bytes entry points have no context to ask).  Every device
+// this library accepts is an sm_100 part, so a process sees one value.
+int plan_sm_count();
+
 // Per-context launch counters and optional CUDA-event timing of every kernel
 // the library launches (hses_profile_* in the C ABI).
 struct KernelStat {
@@ -124,10 +129,11 @@ namespace hses {
 // Raw factors of `pairs` antithetic pairs starting at first_pair:
 // A (pairs, a, r) and B (pairs, b, r), row-major.  When pair_weight is given
 // (device, 2 floats per pair: the fitnesses of the even and the odd member),
-// A is multiplied by (f_even - f_odd).
+// A is multiplied by (f_even - f_odd).  With no_alloc the launch uses no table that
+// would have to be allocated on first use (slower row-to-row advance, same values).
 int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
                         int32_t first_pair, int64_t pairs, int rank, int a, int b,
-                        const float* pair_weight, float* A, float* B);
+                        const float* pair_weight, float* A, float* B, bool no_alloc = false);
 // lif_step (hyperscalees-models/src/snn.rs:53-65): charge, threshold, reset; returns the spike
 __device__ __forceinline__ float lif_update(float& v, float cur, float leak, float v_th, int reset) {
     float d = __fadd_rn(-v, cur);

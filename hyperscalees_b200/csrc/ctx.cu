@@ -78,6 +78,18 @@ __global__ void candidates_kernel(const double2* __restrict__ log_tab, int which
     code[i] = r.dist | ((r.alt < r.bits) ? 0x80000000u : 0u);
 }
 
+int plan_sm_count() {
+    static int cached = 0;
+    if (cached > 0) return cached;
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+        cached = n;
+    else
+        return 148;  // no device visible (size queries on a host without a GPU): the B200's count
+    return cached;
+}
+
 static std::mutex g_tables_mutex;
 static std::map<int, std::shared_ptr<DeviceTables>> g_tables;
 

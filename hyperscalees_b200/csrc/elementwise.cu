@@ -73,10 +73,12 @@ __global__ void poisson_kernel(const float* __restrict__ probs, int64_t batch, i
 // ---------------------------------------------------------------------------
 // LIF scan (snn.rs:53-97, lif_fused_oxide.rs:37-70)
 // ---------------------------------------------------------------------------
+// cur and spikes may be the same buffer (the scan then runs in place: every element is read
+// before the same thread overwrites it), so neither pointer is declared restrict.
 template <int VEC>
-__global__ void lif_scan_kernel(const float* __restrict__ cur, int T, int64_t n, int h,
+__global__ void lif_scan_kernel(const float* cur, int T, int64_t n, int h,
                                 int64_t stride, float* __restrict__ v_io, float leak, float v_th,
-                                int reset, float* __restrict__ spikes) {
+                                int reset, float* spikes) {
     int64_t vec_per_row = h / VEC;
     int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= n * vec_per_row) return;

@@ -53,11 +53,7 @@ struct PairArgs {
     float leak, v_th, out_scale;
     const float* out_scale_ptr;
     int* status;
-    unsigned long long* dbg;
 };
-
-// phase cycle counters of block 0 of the last launch when HSES_TC_DEBUG is set in the environment
-__device__ unsigned long long g_pair_dbg[8];
 
 // plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -83,10 +79,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
     const int tid = threadIdx.x;
-    const long long t_start = clock64();
-    auto tick = [&](int slot) {
-        if (g.dbg != nullptr && blockIdx.x == 0 && tid == 0) g.dbg[slot] = (unsigned long long)(clock64() - t_start);
-    };
     const int rank = g.rank, k = g.k, a = g.a, kc = g.kc;
     const int xp = kc;
     const int bbuf_floats = PP_STAGES * kc * rank;
@@ -147,7 +139,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         for (int c = 0; c < PP_STAGES - 1 && c < chunks; ++c) issue(c);
     }
 
-    tick(0);
     // ---- t = x_rows * B.  A thread owns an 8 x 8 tile of t for one k-slice: rows rg, rg+RG, ...
     // and the columns 4qg..4qg+3 and rank/2+4qg..+3, so that every 16-byte shared-memory load
     // feeds 8..32 multiply-adds.  The eight lanes that share a load phase have the same rows (x
@@ -204,7 +195,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         }
         __syncthreads();
     }
-    tick(1);
     // k-slice sums: red[ks][row][q]
     if (active) {
 #pragma unroll
@@ -264,7 +254,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         return;
     }
     const float* ts = red;
-    tick(2);
 
     if (g.a_swz) {
         // ---- u = t * (s*A)ᵀ, swizzled A.  A warp takes a task = (8 rows, 64 columns, half of the
@@ -381,7 +370,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 }
             }
         }
-        tick(4);
         return;
     }
 
@@ -435,7 +423,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             }
             if (++q4 == nq4) q4 = 0;
         }
-        tick(3);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int r = prg + j * RG4;
@@ -461,7 +448,6 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             }
         }
     }
-    tick(4);
 }
 
 // k-slices of a pass: as many as the block has threads for, at most 64 (a pass is at most 256
@@ -627,12 +613,6 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     pa.a_in_smem = a_fits(g) ? 1 : 0;
     pa.a_swz = a_swizzled(rmax, g) ? 1 : 0;
     pa.status = ctx->t.status_word;
-    pa.dbg = nullptr;
-    if (getenv("HSES_TC_DEBUG")) {
-        void* dp = nullptr;
-        HSES_CUDA(cudaGetSymbolAddress(&dp, g_pair_dbg));
-        pa.dbg = reinterpret_cast<unsigned long long*>(dp);
-    }
     auto launch = [&](int64_t n_pairs) -> int {
         // A of the launch's pairs as (rank, pairs * a); a box is 32 columns of all rows of one pair
         CUtensorMap tm_a = tm_x;   // a valid map also when the swizzled form is not used
@@ -699,12 +679,3 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
 }
 
 }  // namespace hses
-
-// Diagnostic, not part of the declared ABI: phase cycle counters of block 0 of the last
-// per-pair launch made with HSES_TC_DEBUG set (synchronises the device).
-extern "C" int hses_internal_pair_cycles(unsigned long long* out8) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, hses::g_pair_dbg) != cudaSuccess) return 2;
-    if (cudaMemcpy(out8, p, sizeof(unsigned long long) * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return 2;
-    return 0;
-}

@@ -20,7 +20,6 @@
 // and the kernel returns.
 #include <cuda.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "linear.cuh"
 #include "tc_common.cuh"
@@ -69,7 +68,6 @@ struct TcArgs {
     LibmCal cal;
     int* status;
     int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..MAX_DEPTH
-    unsigned long long* dbg;  // optional cycle counters of block 0 (role breakdown), or NULL
 };
 
 template <int BN>
@@ -105,9 +103,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES +
                                               S::BAR_BYTES);
     uint64_t* full = bars;                   // [STAGES] TMA landed
-    uint64_t* xready = bars + S::STAGES;     // [STAGES] unused (kept so the barrier block keeps its layout)
-    uint64_t* empty = bars + 2 * S::STAGES;  // [STAGES] MMAs finished reading the stage
-    uint64_t* tfull = bars + 3 * S::STAGES;  // [2] accumulator ready
+    uint64_t* empty = bars + S::STAGES;      // [STAGES] MMAs finished reading the stage
+    uint64_t* tfull = bars + 2 * S::STAGES;  // [2] accumulator ready
     uint64_t* tempty = tfull + 2;            // [2] accumulator drained
     uint64_t* afull = tempty + 2;                     // [4][MAX_DEPTH] ring slot staged
     uint64_t* aempty = afull + 4 * MAX_DEPTH;         // [4][MAX_DEPTH] ring slot consumed
@@ -124,7 +121,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         abort_flag_s = 0;
         for (int s = 0; s < S::STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&xready[s], 128);
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -158,12 +154,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // role-level cycle accounting of block 0 (only when the host asked for it)
-    const bool dbg_on = g.dbg != nullptr && blockIdx.x == 0 && lane == 0;
-    auto tick = [&](int slot, long long t0) {
-        if (dbg_on) atomicAdd(&g.dbg[slot], (unsigned long long)(clock64() - t0));
-    };
-    const long long t_kernel = clock64();
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
@@ -178,9 +168,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         int s = it % S::STAGES;
                         uint32_t ph = (it / S::STAGES) & 1;
-                        long long t0 = clock64();
                         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
-                        tick(0, t0);
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
                         mbar_expect_tx(&full[s], (skip_xlo ? 1 : 2) * S::X_BYTES + 2 * S::W_BYTES);
                         tma_load_2d(st, &tm_xhi, kb * BK, mt * BM_TILE, &full[s]);
@@ -210,17 +198,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                     int b = acc_it & 1;
-                    long long t0 = clock64();
                     if (!mbar_wait(&tempty[b], ((acc_it >> 1) & 1) ^ 1, abort_flag, g.status, 2)) { ok = false; break; }
-                    tick(1, t0);
                     tc_fence_after();
                     uint32_t d = tmem_base + (uint32_t)(b * BN);
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                         int s = it % S::STAGES;
                         uint32_t ph = (it / S::STAGES) & 1;
-                        long long t1 = clock64();
                         if (!mbar_wait(&full[s], ph, abort_flag, g.status, 3)) { ok = false; break; }
-                        tick(2, t1);
                         tc_fence_after();
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
                         uint64_t dxh = make_smem_desc(st), dxl = make_smem_desc(st + S::X_BYTES);
@@ -271,16 +255,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             }
             for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                 int b = acc_it & 1;
-                long long t0 = clock64();
                 if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
-                if (warp == EPI_WARP0) tick(7, t0);
                 tc_fence_after();
                 for (int cb = 0; cb < BN / 32 && ok; ++cb) {
                     const int n0 = c * BN + cb * 32;
                     const int blk = n0 >> 5;  // 32-column block index inside this M tile
                     const float* my_a = nullptr;
                     int slot = 0;
-                    long long t2 = clock64();
                     if (RG > 0) {
                         // the generator warps of this quadrant have staged the A rows n0..n0+31
                         slot = blk % depth;
@@ -290,8 +271,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         if (!mbar_wait(&afull[q4 * MAX_DEPTH + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
                         my_a = a_stage + (q4 * depth + slot) * 32 * RANK;
                     }
-                    if (warp == EPI_WARP0) tick(8, t2);
-                    t2 = clock64();
                     float* orow = g.out + (size_t)R * g.out_stride + n0;
                     float* prow = (g.lif && g.pot) ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
 #pragma unroll 1
@@ -346,7 +325,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     if (RG > 0) {
                         mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // 64 arrivals (both warps) hand the slot back
                     }
-                    if (warp == EPI_WARP0) tick(9, t2);
                 }
                 tc_fence_before();
                 mbar_arrive(&tempty[b]);
@@ -409,7 +387,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         }
     }
 
-    if (threadIdx.x == 0) tick(11, t_kernel);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -741,9 +718,6 @@ int make_map(CUtensorMap* map, const __half* base, int64_t rows, int cols, int64
     return HSES_OK;
 }
 
-// cycle counters of the last launch when HSES_TC_DEBUG is set in the environment
-__device__ unsigned long long g_tc_dbg[16];
-
 struct TcScratch {
     __half *xhi, *xlo, *whi, *wlo;
     float *rs, *cs, *t;
@@ -881,7 +855,6 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.cal = ctx->cal();
     ta.status = ctx->t.status_word;
     ta.hop = nullptr;
-    ta.dbg = nullptr;
     const float *cache_a = nullptr, *cache_b = nullptr;
     if (g.perturb && g.cache) {
         int crc = resolve_factor_cache(g, &cache_a, &cache_b);
@@ -889,12 +862,6 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     }
     ta.cache_a = cache_a;
     ta.x_lo_flag = sc.lo_flag;
-    if (getenv("HSES_TC_DEBUG")) {
-        void* p = nullptr;
-        HSES_CUDA(cudaGetSymbolAddress(&p, g_tc_dbg));
-        HSES_CUDA(cudaMemsetAsync(p, 0, sizeof(unsigned long long) * 16, st));
-        ta.dbg = reinterpret_cast<unsigned long long*>(p);
-    }
     if (g.perturb) {
         const uint64_t* hop127 = nullptr;
         int rc = get_hop_table(ctx, 2ull * g.rank * (LT_KB - 1), &hop127);
@@ -920,12 +887,3 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
 }
 
 }  // namespace hses
-
-// Diagnostic, not part of the declared ABI: copies the role cycle counters of the
-// last tensor-path launch made with HSES_TC_DEBUG set (synchronises the device).
-extern "C" int hses_internal_tc_cycles(unsigned long long* out16) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, hses::g_tc_dbg) != cudaSuccess) return 2;
-    if (cudaMemcpy(out16, p, sizeof(unsigned long long) * 16, cudaMemcpyDeviceToHost) != cudaSuccess) return 2;
-    return 0;
-}

@@ -118,7 +118,9 @@ pair_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64
         delta_s[i] = cal.log_delta[i];
         delta_s[256 + i] = cal.cos_delta[i];
     }
-    for (int i = threadIdx.x; i < kJumpWords; i += blockDim.x) hop_s[i] = hop127[i];
+    // without a prebuilt hop table a thread advances with the per-context power-of-two tables instead
+    if (hop127)
+        for (int i = threadIdx.x; i < kJumpWords; i += blockDim.x) hop_s[i] = hop127[i];
     __syncthreads();
     cal.log_tab = log_tab_s;
     cal.log_delta = delta_s;
@@ -150,20 +152,24 @@ pair_factors_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64
                 dst[q] = weigh ? __fmul_rn(z, w) : z;
             }
         }
-        s = jump_apply(hop_s, s);
+        s = hop127 ? jump_apply(hop_s, s) : jump_by(pow2, s, 2ull * (uint64_t)rank * 127ull);
     }
 }
 
 int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
                         int32_t first_pair, int64_t pairs, int rank, int a, int b,
-                        const float* pair_weight, float* A, float* B) {
+                        const float* pair_weight, float* A, float* B, bool no_alloc) {
     int rows = a + b;
     int chunks = (rows + 128 * kPfBlocks - 1) / (128 * kPfBlocks);
     HSES_REQUIRE(chunks <= 65535, "a + b too large");
     HSES_REQUIRE(pairs >= 1 && pairs < (1ll << 31), "pair count out of range");
+    // the hop table of a rank is built (and allocated) on its first use; callers that must not
+    // allocate leave it out and the kernel advances with the context's power-of-two tables
     const uint64_t* hop127 = nullptr;
-    int rc = get_hop_table(ctx, 2ull * (uint64_t)rank * 127, &hop127);
-    if (rc != HSES_OK) return rc;
+    if (!no_alloc) {
+        int rc = get_hop_table(ctx, 2ull * (uint64_t)rank * 127, &hop127);
+        if (rc != HSES_OK) return rc;
+    }
     dim3 grid((unsigned)pairs, (unsigned)chunks);
     HSES_KERNEL(ctx, stream, "pair_factors");
     pair_factors_kernel<<<grid, 128, 0, stream>>>(ctx->cal(), ctx->t.jump_pow2, hop127, key, true_epoch,

@@ -787,8 +787,13 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
         else if (head_dim == 32)
             attention_product_packed_kernel<32><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
                                                                                      beta, beta_per_seq, O, A_out);
-        else
+        else {
+            // up to 64 KB for 128 tokens x 64 values: above the 48 KB a kernel gets without opting in
+            if (smem > 48 * 1024)
+                HSES_CUDA(cudaFuncSetAttribute(attention_product_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem));
             attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, beta_per_seq, O, A_out);
+        }
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
@@ -811,6 +816,8 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
+    if (smem > 48 * 1024)
+        HSES_CUDA(cudaFuncSetAttribute(spiking_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     spiking_attention_kernel<<<(unsigned)(n_seq * heads), threads, smem, as_stream(stream)>>>(
         Q, K, V, tokens, heads, head_dim, row_stride, mode, beta, beta_per_seq, tau_m, v_th, g_inh, n_iter, O, A_out);
     HSES_LAUNCH_CHECK();

@@ -37,7 +37,7 @@ static UpdatePlan plan_update(int a, int b, int rank, int64_t n) {
     if (fit < 1) fit = 1;
     p.chunk_pairs = p.pairs < fit ? p.pairs : fit;
     int tiles = ((a + UM - 1) / UM) * ((b + UN - 1) / UN);
-    int want = (2 * 148 + tiles - 1) / tiles;
+    int want = (2 * plan_sm_count() + tiles - 1) / tiles;
     if (want > 64) want = 64;
     if (want > p.chunk_pairs) want = (int)p.chunk_pairs;
     if (want < 1) want = 1;
@@ -142,15 +142,17 @@ static std::mutex g_static_mutex;
 static std::map<int, float*> g_static_ptr;  // device ordinal -> address of the array on that device
 
 static int static_scratch_for_device(int device, float** out) {
+    // checked on every call: a launch made while another GPU is current would hand that GPU
+    // this device's address
+    int current = -1;
+    HSES_CUDA(cudaGetDevice(&current));
+    HSES_REQUIRE(current == device, "the context's device must be the current CUDA device");
     std::lock_guard<std::mutex> lock(g_static_mutex);
     auto it = g_static_ptr.find(device);
     if (it != g_static_ptr.end()) {
         *out = it->second;
         return HSES_OK;
     }
-    int current = -1;
-    HSES_CUDA(cudaGetDevice(&current));
-    HSES_REQUIRE(current == device, "the context's device must be the current CUDA device");
     void* ptr = nullptr;
     HSES_CUDA(cudaGetSymbolAddress(&ptr, g_static_update_scratch));
     HSES_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned NULL");
@@ -168,7 +170,7 @@ static bool plan_update_static(int a, int b, int rank, int64_t n, UpdatePlan* ou
     size_t per_pair = (size_t)(a + b) * rank;
     size_t ab = (size_t)a * b;
     int tiles = ((a + UM - 1) / UM) * ((b + UN - 1) / UN);
-    int splits = (2 * 148 + tiles - 1) / tiles;
+    int splits = (2 * plan_sm_count() + tiles - 1) / tiles;
     if (splits > 16) splits = 16;
     // partial sums may take at most half of the array; the rest holds factors
     while (splits > 1 && up((size_t)splits * ab) > budget / 2) --splits;
@@ -284,7 +286,7 @@ __global__ void einsum_pair_reduce_kernel(const float* __restrict__ partial, int
 static int einsum_pair_splits(int64_t half, int r, int a, int b) {
     int tiles = ((a + EP_TM - 1) / EP_TM) * ((b + EP_TN - 1) / EP_TN);
     int64_t kblocks = (half * r + 255) / 256;   // at least 256 rows of K per split
-    int want = (2 * 148 + tiles - 1) / tiles;
+    int want = (2 * plan_sm_count() + tiles - 1) / tiles;
     if (want > kblocks) want = (int)kblocks;
     if (want > 256) want = 256;
     return want < 1 ? 1 : want;
@@ -446,7 +448,7 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
     for (int64_t done = 0; done < p.pairs; done += p.chunk_pairs, ++chunk_idx) {
         int64_t cnt = p.pairs - done < p.chunk_pairs ? p.pairs - done : p.chunk_pairs;
         rc = launch_pair_factors(ctx, st, key, te, first_thread / 2 + (int32_t)done, cnt, rank, a, b,
-                                 fitness + 2 * done, wsA, wsB);
+                                 fitness + 2 * done, wsA, wsB, /*no_alloc=*/true);
         if (rc != HSES_OK) return rc;
         HSES_KERNEL(ctx, st, "update_gemm");
         // the first chunk overwrites the partial sums, so nothing left behind by an

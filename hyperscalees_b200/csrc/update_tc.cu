@@ -337,7 +337,7 @@ UpdateTcPlan plan_update_tc(int a, int b, int rank, int64_t n, bool need_raw) {
     p.chunk_pairs = (need_raw && p.pairs > fit) ? fit : p.pairs;
     int tiles = p.n_tiles * p.m_tiles;
     // one CTA per SM fits (the operand stages take most of the shared memory): one full wave
-    int want = 148 / tiles;
+    int want = plan_sm_count() / tiles;
     if (want > p.chunk_pairs) want = (int)p.chunk_pairs;
     if (want < 1) want = 1;
     p.splits = want;

@@ -230,10 +230,11 @@ class PopulationStep:
         return (raw, logits) if want_logits else raw
 
     def update_sharded(self, raw_fitness: torch.Tensor, epoch: int = 0, gain_key: Optional[int] = None,
-                       group=None, reduce_fn=None) -> None:
+                       group=None, reduce_fn=None, comm=None) -> None:
         """Like update(), but this rank only contracts the factors of ITS members (first_thread ..
         first_thread + n_pop - 1); the partial gradients of all parameters are summed with one
-        all-reduce (when torch.distributed is initialised) and every rank applies the same solver
+        all-reduce (through `comm`, the library's own communicator, when given; else through
+        torch.distributed when it is initialised) and every rank applies the same solver
         step, so parameters stay identical on all ranks.  reduce_fn(grads), when given, replaces
         the all-reduce (it must leave the sum over all shards in `grads`)."""
         import torch.distributed as dist
@@ -254,6 +255,9 @@ class PopulationStep:
             self._grads.data_ptr(), ws.data_ptr(), need))
         if reduce_fn is not None:
             reduce_fn(self._grads)
+        elif comm is not None:
+            if comm.world > 1:
+                comm.allreduce_grads(self._grads)
         elif dist.is_initialized() and dist.get_world_size(group) > 1:
             dist.all_reduce(self._grads, op=dist.ReduceOp.SUM, group=group)
         sv = self.frozen.solver

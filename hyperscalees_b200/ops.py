@@ -166,13 +166,19 @@ _workspaces = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> Optional[torch.Tensor]:
-    """Grow-only scratch buffer per device (the library itself never allocates scratch)."""
+    """Grow-only scratch buffer per (device, current stream): the library itself never allocates
+    scratch, and calls on different streams must not share one.  A buffer that is outgrown is
+    handed back to the allocator tied to the stream whose kernels may still be using it."""
     if nbytes == 0:
         return None
-    buf = _workspaces.get(device)
+    stream = torch.cuda.current_stream(device)
+    slot = (device, stream.cuda_stream)
+    buf = _workspaces.get(slot)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            buf.record_stream(stream)
         buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _workspaces[device] = buf
+        _workspaces[slot] = buf
     return buf
 
 

@@ -37,7 +37,8 @@ enum hses_status {
     HSES_ERR_INVALID = 1,     /* bad argument / unsupported shape */
     HSES_ERR_CUDA = 2,        /* a CUDA runtime call failed */
     HSES_ERR_CALIBRATION = 3, /* libm calibration found a non-adjacent value */
-    HSES_ERR_UNSUPPORTED = 4  /* requested algorithm cannot run this shape */
+    HSES_ERR_UNSUPPORTED = 4, /* requested algorithm cannot run this shape */
+    HSES_ERR_COMM = 5         /* a collective or its communicator failed (a peer left, transport error) */
 };
 
 enum hses_reset_mode { HSES_RESET_HARD = 0, HSES_RESET_SUBTRACT = 1 };
@@ -129,7 +130,8 @@ int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs /*
 /* ---- lif_fused, oxide.rs:489-543 / lif_fused_oxide.rs:37-70, run_lif
  *      snn.rs:73-97.  cur and spikes are (T, n, h) pitched; v is (n, h)
  *      pitched, read as v0 and overwritten with the final potential, or NULL
- *      for v0 = 0 with no write-back. --------------------------------------- */
+ *      for v0 = 0 with no write-back.  spikes may be the same buffer as cur
+ *      (the scan then replaces the currents by the spikes). ------------------ */
 int hses_lif_scan(hses_ctx* ctx, hses_stream stream, const float* cur /*device*/, int32_t T,
                   int64_t n, int32_t h, int64_t row_stride, float* v /*device or NULL*/,
                   float tau_m, float v_th, int32_t reset_mode, float* spikes /*device*/);
@@ -490,6 +492,38 @@ int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x /*device*
 /* rate_encode, hyperscalees-models/src/snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|)). */
 int hses_rate_encode(hses_ctx* ctx, hses_stream stream, const float* p /*device*/, int64_t n, float gain,
                      float* out /*device*/);
+
+/* ---- collectives of the sharded population step.  The reference's product crates hold no
+ *      multi-GPU code; its recipe is the Python trainer
+ *      llm_experiments/snn_mnist_train_multi_gpu.py:187-234 (sharded forward, the fitness of all
+ *      shards on every device, replicated update), and the only NCCL plumbing in its tree is the
+ *      vendored runtime's (burn_impl/vendor/cubecl-cuda/src/compute/server.rs:277-388:
+ *      comm_init_rank from a unique id, all_reduce on a stream).  These entry points give a Rust
+ *      trainer the same two calls: one communicator per rank (= per process and GPU), built from
+ *      a 128-byte id that rank 0 creates and hands to the others out of band; an all-gather of
+ *      equally long fitness shards into thread-id order; an in-place sum of the flat gradient
+ *      buffer of hses_population_grads (every rank receives the same bits, so the ranks'
+ *      parameters stay identical after hses_population_apply).  Both are enqueued on the caller's
+ *      stream and return at once.  NCCL is loaded at run time (libnccl.so.2, or the library the
+ *      environment variable HSES_NCCL_LIBRARY names).  ctx may be NULL (no launch accounting).
+ *      Failures: a call that NCCL refuses, or hses_comm_async_error() reporting a failed
+ *      collective (a peer that left, a transport error), returns HSES_ERR_COMM and marks the
+ *      communicator broken; every later collective on it fails at once and hses_comm_destroy
+ *      aborts it instead of waiting for work that cannot finish.  A rank may leave only between
+ *      steps; the others should poll hses_comm_async_error (or their own heartbeat) before the
+ *      next launch. ------------------------------------------------------------------------ */
+#define HSES_COMM_ID_BYTES 128
+typedef struct hses_comm hses_comm;
+int hses_comm_unique_id(uint8_t* id /*host, HSES_COMM_ID_BYTES*/);
+int hses_comm_init(hses_ctx* ctx, const uint8_t* id /*host*/, int32_t rank, int32_t world, hses_comm** out);
+int hses_comm_rank(const hses_comm* comm);
+int hses_comm_world(const hses_comm* comm);
+int hses_comm_async_error(hses_comm* comm);
+int hses_comm_destroy(hses_comm* comm);
+int hses_comm_abort(hses_comm* comm);
+int hses_allgather_fitness(hses_comm* comm, hses_stream stream, const float* local /*device (n_local)*/,
+                           int64_t n_local, float* all /*device (world * n_local)*/);
+int hses_allreduce_grads(hses_comm* comm, hses_stream stream, float* grads /*device, in place*/, int64_t count);
 
 #ifdef __cplusplus
 }

@@ -160,6 +160,30 @@ static float dot_fast(const float *p, const float *q, int n) {
     return s;
 }
 
+/* Baseline-timing variant of the base product: a 4 x 4 block of outputs (four rows of x against
+ * four rows of the parameter) with sixteen SIMD accumulators, so that every loaded vector feeds
+ * four multiply-adds — the register blocking a tuned CPU GEMM such as the reference's backend
+ * applies.  Fused multiply-adds, lane-wise partial sums: for timing (acc mode 2) only. */
+__attribute__((target_clones("avx512f", "avx2,fma", "default")))
+static void base_block4x4(const float *x, const float *w, int b, float *y, int ystride) {
+    float acc[16][16];
+    for (int e = 0; e < 16; ++e)
+        for (int l = 0; l < 16; ++l) acc[e][l] = 0.0f;
+    int i = 0;
+    for (; i + 16 <= b; i += 16)
+        for (int r = 0; r < 4; ++r)
+            for (int c = 0; c < 4; ++c)
+                for (int l = 0; l < 16; ++l)
+                    acc[r * 4 + c][l] = __builtin_fmaf(x[(size_t)r * b + i + l], w[(size_t)c * b + i + l], acc[r * 4 + c][l]);
+    for (int r = 0; r < 4; ++r)
+        for (int c = 0; c < 4; ++c) {
+            float s = 0.0f;
+            for (int l = 0; l < 16; ++l) s += acc[r * 4 + c][l];
+            for (int k = i; k < b; ++k) s += x[(size_t)r * b + k] * w[(size_t)c * b + k];
+            y[(size_t)r * ystride + c] = s;
+        }
+}
+
 /* y = x·paramᵀ + (x·B)·Aᵀ with pre-generated factors; evaluation order of
  * eggroll.rs:427,443: base first, then t = x·B, u = t·Aᵀ, y = base + u. */
 static void mm_with_factors(const float *x, int bm, const float *param, int a, int b,
@@ -172,6 +196,18 @@ static void mm_with_factors(const float *x, int bm, const float *param, int a, i
                 t[(size_t)m * rank + q] =
                     acc64 == 1 ? dot_f64(x + (size_t)m * b, B + q, b, 1, rank)
                                : dot_f32(x + (size_t)m * b, B + q, b, 1, rank);
+    }
+    if (acc64 == 2 && bm % 4 == 0 && a % 4 == 0) {
+        /* blocked base product, then the rank-r term per output */
+        for (int m = 0; m < bm; m += 4)
+            for (int n = 0; n < a; n += 4)
+                base_block4x4(x + (size_t)m * b, param + (size_t)n * b, b, y + (size_t)m * a + n, a);
+        if (A)
+            for (int m = 0; m < bm; ++m)
+                for (int n = 0; n < a; ++n)
+                    y[(size_t)m * a + n] += dot_f32(t + (size_t)m * rank, A + (size_t)n * rank, rank, 1, 1);
+        free(t);
+        return;
     }
     for (int m = 0; m < bm; ++m) {
         for (int n = 0; n < a; ++n) {
@@ -458,6 +494,60 @@ void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
                    const int32_t *thread_ids, size_t n, int32_t noise_reuse,
                    float *out) {
     lora_grad_impl(sigma, key, a, b, rank, scores, epochs, thread_ids, n, noise_reuse, 0, out);
+}
+
+/* The sub-block out[m0..m1) x [n0..n1) of hso_lora_grad, for populations too large to contract
+ * whole on the CPU: the same stream positions and the same sum (eggroll.rs:353-373, 384-404),
+ * with the normals of the rows outside the block stepped over in the integer stream instead of
+ * evaluated, and the member sum kept in fp64 (a yardstick for fp32 sums of 10^4..10^5 terms). */
+void hso_lora_grad_block(float sigma, uint64_t key, int a, int b, int rank,
+                         const float *scores, const int32_t *epochs,
+                         const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                         int m0, int m1, int n0, int n1, float *out) {
+    (void)a;
+    float base_sigma = sigma / sqrtf((float)rank);
+    int bm = m1 - m0, bn = n1 - n0;
+    size_t blk = (size_t)bm * bn;
+    int nthreads = hso_num_threads();
+    double *partial = (double *)calloc(blk * (size_t)nthreads, sizeof(double));
+#pragma omp parallel num_threads(nthreads)
+    {
+        int t = 0;
+#ifdef _OPENMP
+        t = omp_get_thread_num();
+#endif
+        double *acc = partial + blk * (size_t)t;
+        float *A = (float *)malloc(sizeof(float) * (size_t)bm * rank);
+        float *B = (float *)malloc(sizeof(float) * (size_t)bn * rank);
+#pragma omp for schedule(static)
+        for (long i = 0; i < (long)n; ++i) {
+            int32_t te, tt;
+            float sign;
+            hso_epoch_thread_sign(epochs[i], thread_ids[i], noise_reuse, &te, &tt, &sign);
+            uint64_t s = hso_noise_seed(key, te, tt) | 1ull;
+            /* every normal consumes two generator outputs */
+            for (size_t k = 0; k < 2 * (size_t)rank * (size_t)n0; ++k) xs64_next(&s);
+            for (int e = 0; e < bn * rank; ++e) B[e] = xs64_normal(&s);
+            for (size_t k = 0; k < 2 * (size_t)rank * (size_t)(b - n1 + m0); ++k) xs64_next(&s);
+            float sc = sign * base_sigma;
+            for (int e = 0; e < bm * rank; ++e) A[e] = xs64_normal(&s) * sc;
+            float f = scores[i];
+            for (int p = 0; p < bm; ++p)
+                for (int q = 0; q < bn; ++q) {
+                    float d = dot_f32(A + (size_t)p * rank, B + (size_t)q * rank, rank, 1, 1);
+                    acc[(size_t)p * bn + q] += (double)(d * f);
+                }
+        }
+        free(A);
+        free(B);
+    }
+    float inv_n = 1.0f / (float)n, rootn = sqrtf((float)n);
+    for (size_t j = 0; j < blk; ++j) {
+        double sum = 0.0;
+        for (int t = 0; t < nthreads; ++t) sum += partial[blk * (size_t)t + j];
+        out[j] = -(((float)sum * inv_n) * rootn);
+    }
+    free(partial);
 }
 
 /* AltEggRoll (hyperscalees-noiser/src/alteggroll.rs:65-90 + do_update_with): the same update

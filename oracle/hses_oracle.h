@@ -107,6 +107,11 @@ void hso_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
                    const float *scores, const int32_t *epochs,
                    const int32_t *thread_ids, size_t n, int32_t noise_reuse,
                    float *out);
+/* rows [m0,m1) x columns [n0,n1) of the same gradient, member sum in fp64 */
+void hso_lora_grad_block(float sigma, uint64_t key, int a, int b, int rank,
+                         const float *scores, const int32_t *epochs,
+                         const int32_t *thread_ids, size_t n, int32_t noise_reuse,
+                         int m0, int m1, int n0, int n1, float *out);
 void hso_alt_lora_grad(float sigma, uint64_t key, int a, int b, int rank,
                    const float *scores, const int32_t *epochs,
                    const int32_t *thread_ids, size_t n, int32_t noise_reuse,

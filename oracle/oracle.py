@@ -262,6 +262,18 @@ def lora_grad(sigma, key, a, b, rank, scores, epochs, thread_ids, noise_reuse=0)
 
 
 
+def lora_grad_block(sigma, key, a, b, rank, scores, epochs, thread_ids, rows, cols, noise_reuse=0):
+    """Rows [rows[0], rows[1]) x columns [cols[0], cols[1]) of lora_grad, member sum in fp64."""
+    scores, sp = _f(scores)
+    epochs, ep = _i(epochs)
+    tids, tp = _i(thread_ids)
+    out = np.empty((rows[1] - rows[0], cols[1] - cols[0]), dtype=np.float32)
+    lib().hso_lora_grad_block(C.c_float(sigma), C.c_uint64(key), a, b, rank, sp, ep, tp,
+                              C.c_size_t(scores.size), noise_reuse, rows[0], rows[1], cols[0], cols[1],
+                              out.ctypes.data_as(_f32p))
+    return out
+
+
 def alt_lora_grad(sigma, key, a, b, rank, scores, epochs, thread_ids, noise_reuse=0):
     scores, sp = _f(scores)
     epochs, ep = _i(epochs)

@@ -77,6 +77,21 @@ def test_lif_scan_bit_exact(hs, oracle, T, n, h, pitch, reset, with_v0):
         assert np.array_equal(v.cpu().numpy().view(np.uint32), want_v.view(np.uint32))
 
 
+@pytest.mark.parametrize("h,pitch", [(128, 128), (100, 128), (7, 7)])
+def test_lif_scan_in_place_equals_out_of_place(hs, h, pitch):
+    """cur == spikes is allowed (the fallback of the fused LIF scan uses it): both the
+    16-byte-vector kernel (h, pitch multiples of 4) and the scalar one."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(h)
+    buf = torch.zeros((8, 19, pitch), device="cuda")
+    buf[:, :, :h] = dev((g.standard_normal((8, 19, h)) * 3).astype(np.float32))
+    cur = buf[:, :, :h]
+    want = ops.lif_scan(cur, 20.0, 0.3).clone()
+    got = ops.lif_scan(cur, 20.0, 0.3, out=cur)
+    assert got.data_ptr() == cur.data_ptr()
+    assert torch.equal(got, want)
+
+
 def test_lif_reference_cases(hs):
     # hyperscalees-models/src/snn.rs:707-742
     from hyperscalees_b200 import models

@@ -60,10 +60,13 @@ def test_config1_full_size_properties(hs, oracle):
     assert u0.abs().max().item() < 0.2 * clean.abs().max().item() and u1.abs().max().item() < 0.2 * clean.abs().max().item()
 
 
-def test_config3_full_size_properties(hs, oracle):
-    """Large-population SNN MLP 784-128-128-128-10, T = 8, N = 65 536 members of one sample, rank 64."""
-    from hyperscalees_b200 import models, noiser
-    dims, n_pop, bm, T, rank, sigma = [784, 128, 128, 128, 10], 65536, 1, 8, 64, 0.02
+@pytest.mark.parametrize("rank", [64, 96, 128])
+def test_config3_full_size_properties(hs, oracle, rank):
+    """Large-population SNN MLP 784-128-128-128-10, T = 8, N = 65 536 members of one sample, at the
+    three ranks the configuration sweeps (96 takes the zero-filled last k-block of the tensor-core
+    contraction, 64 and 128 whole k-blocks)."""
+    from hyperscalees_b200 import models, noiser, ops
+    dims, n_pop, bm, T, sigma = [784, 128, 128, 128, 10], 65536, 1, 8, 0.02
     g = np.random.Generator(np.random.PCG64(0))
     img = g.random((n_pop, 784), dtype=np.float32)
     img[g.random((n_pop, 784)) < 0.8] = 0.0
@@ -103,8 +106,35 @@ def test_config3_full_size_properties(hs, oracle):
     status_ok()
     assert torch.isfinite(raw_shard).all()
     check_members(raw_shard, img[lo:hi], labels[lo:hi], lo)
+    # the gradient of the first and of a hidden layer at full size, against sub-blocks of the CPU
+    # restatement's sum over all 65 536 members (corners and the ragged last column tile included)
+    fit = ops.convert_fitnesses(raw)
+    assert np.abs(fit.cpu().numpy() - oracle.convert_fitnesses(raw.cpu().numpy())).max() <= 1e-4
+    fit_h = fit.cpu().numpy()
+    epochs, tids = np.zeros(n_pop, np.int32), np.arange(n_pop, dtype=np.int32)
+    for layer, blocks in ((0, [((0, 6), (0, 6)), ((122, 128), (778, 784)), ((60, 64), (300, 306))]),
+                          (2, [((0, 6), (122, 128)), ((100, 104), (0, 6))])):
+        a_, b_ = dims[layer + 1], dims[layer]
+        grad = ops.es_update(keys[layer], 0, 0, rank, a_, b_, sigma, fit, cache=step.caches[layer])
+        regen = ops.es_update(keys[layer], 0, 0, rank, a_, b_, sigma, fit) if layer == 2 else None
+        status_ok()
+        gmax = grad.abs().max().item()
+        assert np.isfinite(gmax) and gmax > 0
+        if regen is not None:   # factors regenerated chunk by chunk instead of read from the cache: same bits
+            assert torch.equal(regen, grad)
+        gh = grad.cpu().numpy()
+        for rows, cols in blocks:
+            want = oracle.lora_grad_block(sigma, keys[layer], a_, b_, rank, fit_h, epochs, tids, rows, cols)
+            assert np.abs(gh[rows[0]:rows[1], cols[0]:cols[1]] - want).max() <= 1e-3 * gmax
     before = [p.clone() for p in step.params]
     step.update(raw)
     status_ok()
     for b, a in zip(before[:-1], step.params[:-1]):
         assert torch.isfinite(a).all() and (a - b).abs().max().item() > 0
+    # the first layer after the solver step is what one AdamW step on that gradient gives
+    grad0 = ops.es_update(keys[0], 0, 0, rank, dims[1], dims[0], sigma, fit, cache=step.caches[0])
+    want_p = oracle.solver_update(2, 1, before[0].cpu().numpy(), grad0.cpu().numpy(),
+                                  np.zeros_like(grad0.cpu().numpy()), np.zeros_like(grad0.cpu().numpy()),
+                                  lr=0.01, weight_decay=1e-4)
+    want_p = want_p[0] if isinstance(want_p, tuple) else want_p
+    assert np.abs(step.params[0].cpu().numpy() - want_p).max() <= 1e-3 * np.abs(want_p).max()

@@ -53,7 +53,7 @@ def test_wkv7_matches_oracle(hs, oracle, n_seq, T, H, S):
 
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("n_seq,tokens,heads,hd", [(2, 64, 4, 16), (3, 16, 1, 8), (1, 50, 2, 64), (2, 50, 2, 32),
-                                                   (1, 7, 3, 16), (1, 128, 1, 32)])
+                                                   (1, 7, 3, 16), (1, 128, 1, 32), (1, 128, 2, 64), (1, 100, 1, 64)])
 def test_spiking_attention_matches_oracle(hs, oracle, mode, n_seq, tokens, heads, hd):
     from hyperscalees_b200 import ops
     g = np.random.default_rng(tokens + hd)
@@ -131,12 +131,13 @@ def test_channel_mixing_matches_oracle_and_reference_case():
                           oracle.token_shift_mix(x, state, x_k, ns))
 
 
-def test_continuous_hopfield_attention_and_rate_encode(hs, oracle):
+@pytest.mark.parametrize("n_seq,tokens,heads,hd", [(3, 17, 4, 16), (1, 128, 1, 64)])
+def test_continuous_hopfield_attention_and_rate_encode(hs, oracle, n_seq, tokens, heads, hd):
     """snn_transformer.rs:80-116: continuous rates, Hopfield relaxation, softmax rows that sum to one
-    (the reference asserts the row sums in snn_attention.rs:374-399)."""
+    (the reference asserts the row sums in snn_attention.rs:374-399).  The second shape is the
+    largest the entry point takes (its rows do not fit the register kernel's shared memory)."""
     from hyperscalees_b200 import ops
     g = np.random.default_rng(21)
-    n_seq, tokens, heads, hd = 3, 17, 4, 16
     p = g.standard_normal((n_seq, tokens, heads * hd)).astype(np.float32) * 2
     rates = ops.rate_encode(dev(p), 4.0).cpu().numpy()
     assert np.abs(rates - oracle.rate_encode(p, 4.0)).max() <= 1e-6

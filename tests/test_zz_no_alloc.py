@@ -58,6 +58,30 @@ def test_static_update_matches_oracle(hs, oracle):
     assert np.abs(got.cpu().numpy() - want).max() <= 1e-3 * np.abs(want).max()
 
 
+def test_static_update_leaves_device_memory_alone(hs, oracle):
+    """A rank that no other call of this process has used: the entry point must not build (and
+    allocate) a per-rank table on the way.  Free device memory as the driver reports it and the
+    bytes torch's allocator holds are the same before and after."""
+    from hyperscalees_b200 import _lib, core
+    L = _lib.load()
+    ctx = core.get_context(0)
+    n, a, b, rank = 20, 33, 65, 7
+    f = np.random.default_rng(5).standard_normal(n).astype(np.float32)
+    fd = torch.as_tensor(f, device="cuda")
+    _static(L, ctx, fd, 8, 8, 2, 0.1)          # the one-off address lookup of the array happens here
+    grad = torch.empty((a, b), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    free0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.hses_es_update_static(ctx.handle, stream, C.c_uint64(KEY), 0, 0, 0, n, n, rank, a, b, 0.3,
+                                 C.c_void_p(fd.data_ptr()), C.c_void_p(grad.data_ptr()))
+    assert rc == 0, L.hses_last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_reserved() == reserved0
+    want = oracle.lora_grad(0.3, KEY, a, b, rank, f, [0] * n, list(range(n)), 0)
+    assert np.abs(grad.cpu().numpy() - want).max() <= 1e-3 * np.abs(want).max()
+
+
 def test_static_update_rejects_what_does_not_fit(hs):
     from hyperscalees_b200 import _lib, core
     L = _lib.load()
