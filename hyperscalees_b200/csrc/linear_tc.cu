@@ -10,9 +10,13 @@
 //                    (x_lo·W_hi + x_hi·W_lo + x_hi·W_hi), fp32 accumulators in TMEM, two
 //                    accumulator buffers so the epilogue overlaps the next 256-column chunk
 //       warps 2-9    epilogue, two per TMEM quadrant: TMEM -> registers, undo the operand
-//                    scales, add t·(±s·A)ᵀ from the staged A rows, LIF step, store spikes
-//       warps 10-25  noise generators, up to four per quadrant: regenerate the A rows of the
-//                    quadrant's antithetic pair into a shared-memory ring, ahead of the MMAs
+//                    scales, add t·(±s·A)ᵀ from the staged A rows (packed fp32 pairs), LIF
+//                    step, store spikes
+//       warps 10-25  noise generators, four per quadrant: regenerate the A rows of the
+//                    quadrant's antithetic pair, sixteen output columns at a time, into a
+//                    shared-memory ring of eight such items, ahead of the MMAs; an item is
+//                    produced by one generator warp and consumed by one epilogue warp, so a
+//                    generator always has a free slot to write while its last item is read
 // Three fp16 passes on scaled hi/lo operands make every product fp32-equivalent (2^-21
 // relative residue); a single pass would break the spike tolerance.  No TMA multicast and no
 // cluster launch is used anywhere.  Every barrier wait is bounded: a wait that runs out
@@ -33,17 +37,29 @@ using namespace tc;
 constexpr int BM_TILE = 128;      // rows per M tile (TMEM lanes)
 constexpr int BK = 64;            // fp16 elements per k-block = one 128 B swizzle row
 // warps: 0 TMA, 1 MMA, 2-9 epilogue (two per TMEM quadrant), 10-25 noise generators
-constexpr int MAX_DEPTH = 4;       // ring slots (= generator warps) per TMEM quadrant, at most
-constexpr int NTHREADS = 32 * (10 + 4 * MAX_DEPTH);
+constexpr int MAX_GENS = 4;        // generator warps per TMEM quadrant, at most
+constexpr int MAX_DEPTH = 8;       // ring slots (items) per TMEM quadrant, at most
+constexpr int NTHREADS = 32 * (10 + 4 * MAX_GENS);
 constexpr int EPI_WARP0 = 2;
 constexpr int GEN_WARP0 = 10;
 
-// Staged A rows are RANK floats long with no padding; 16-byte chunk q of row l is stored at
-// chunk q ^ a_swizzle(l), which spreads the eight lanes of a store phase over all banks.
+// One ring item holds the A rows of ROWS consecutive output columns of one antithetic pair.
+// With rank >= 8 two lanes share a row (each generates half of its rank values), an item covers 16
+// columns and belongs to one epilogue warp; with rank 4 a lane owns a row, an item covers 32
+// columns and both epilogue warps of the quadrant read it.  Inside a slot the value (q, n) sits
+// at float (q % NPL) * 32 + (q / NPL) * ROWS + n: the lanes of a store cover 32 consecutive
+// floats, and an epilogue warp reads four neighbouring columns of one q with a 16-byte broadcast.
 template <int RG>
-__device__ __forceinline__ int a_swizzle(int row) {
-    return RG <= 1 ? 0 : ((row * RG) >> 3) & (RG - 1);
-}
+struct Item {
+    static constexpr int RANK = RG * 4;
+    static constexpr int LPR = RG >= 2 ? 2 : 1;      // lanes per row
+    static constexpr int ROWS = 32 / LPR;
+    static constexpr int NPL = RG > 0 ? RANK / LPR : 4;  // normals per lane and item
+    static constexpr int SLOT_FLOATS = ROWS * RANK;
+    __device__ __forceinline__ static int at(int q, int n) { return (q % NPL) * 32 + (q / NPL) * ROWS + n; }
+};
+inline int item_rows(int rank) { return rank >= 8 ? 16 : 32; }
+inline int item_normals_per_lane(int rank) { return rank >= 8 ? rank / 2 : rank; }
 struct TcArgs {
     int64_t rows;
     int k, a;
@@ -62,12 +78,17 @@ struct TcArgs {
     int64_t out_stride;
     float* pot;
     const uint64_t* pow2; // T^(2^k) tables
-    const uint64_t* hop;  // T^(2*rank*(32*ring_depth - 1))
+    const uint64_t* hop;  // generator advance from the end of one item of a warp to its next one
     const int* x_lo_flag; // 0 when every lo half of the split x is zero (x exactly representable in fp16)
     const float* cache_a; // cached raw A rows (pair, a, rank) from the call's first pair on, or NULL
     LibmCal cal;
     int* status;
-    int ring_depth;       // slots (= active generator warps) per TMEM quadrant, 1..MAX_DEPTH
+    // Ring slots (items) per TMEM quadrant and active generator warps per quadrant.  A slot must
+    // always be written by the same generator warp and read by the same epilogue warp(s): waits
+    // are on barrier phase parity, and a waiter that could fall two phases behind would take an
+    // older phase for the one it waits for.  Hence ring_depth is a multiple of gens, and even
+    // when an item belongs to one of the two epilogue warps.
+    int ring_depth, gens;
 };
 
 template <int BN>
@@ -78,11 +99,11 @@ struct TcSmem {
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
     static constexpr int HOP_BYTES = 0;     // the hop table is read through L1;
     static constexpr int TAB_BYTES = 1536;  // the logarithm's helper table and the thresholds as 2 x 256 bytes
-    static constexpr int BAR_BYTES = 384;
+    static constexpr int BAR_BYTES = 608;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
-    // ring of staged A rows: 4 quadrants * depth slots * 32 rows * rank floats
-    static int a_bytes(int depth, int rank) { return 4 * depth * 32 * rank * 4; }
+    // ring of staged A rows: 4 quadrants * depth items * rows of an item * rank floats
+    static int a_bytes(int depth, int rank) { return 4 * depth * item_rows(rank) * rank * 4; }
 };
 
 // ----------------------------------------------------------------------- kernel
@@ -109,8 +130,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     uint64_t* afull = tempty + 2;                     // [4][MAX_DEPTH] ring slot staged
     uint64_t* aempty = afull + 4 * MAX_DEPTH;         // [4][MAX_DEPTH] ring slot consumed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aempty + 4 * MAX_DEPTH);
-    __shared__ int abort_flag_s;
-    volatile int* abort_flag = &abort_flag_s;
+    volatile int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (int)(g.rows / BM_TILE);
@@ -118,7 +138,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     const int k_blocks = (g.k + BK - 1) / BK;  // a ragged last block is zero-filled by TMA
 
     if (threadIdx.x == 0) {
-        abort_flag_s = 0;
+        *abort_flag = 0;
         for (int s = 0; s < S::STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -129,7 +149,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         }
         for (int i = 0; i < 4 * MAX_DEPTH; ++i) {
             mbar_init(&afull[i], 32);
-            mbar_init(&aempty[i], 64);
+            mbar_init(&aempty[i], Item<RG>::LPR == 2 ? 32 : 64);   // one or both epilogue warps read an item
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -225,22 +245,22 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         }
     } else if (warp < GEN_WARP0) {
         // ----------------------------------------------- epilogue (two warps per TMEM quadrant:
-        // warp (q4, eh) takes columns [16*eh, 16*eh+16) of every 32-column block.  Both warps
-        // therefore consume every use of every ring slot in order, so a waiter is never more than
-        // one barrier phase behind — alternating whole blocks between the warps would let a
-        // parity wait alias with an older phase.)
+        // warp (q4, eh) takes columns [16*eh, 16*eh+16) of every 32-column block, eight at a time:
+        // the TMEM load of eight accumulators is issued first and waited for only after the
+        // rank-r term of those columns has been summed from the staged A rows)
+        using IT = Item<RG>;
         constexpr int RANK = RG * 4;
         const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
         const int eh = (warp - EPI_WARP0) >> 2;
         const float out_scale = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
         const int depth = g.ring_depth;
-        const int blocks_per_tile = g.a / 32;
+        const int items_per_tile = g.a / IT::ROWS;
         uint32_t acc_it = 0;
-        int tile_no = 0;  // M tiles this CTA has finished: fixes how often each ring slot was used
+        uint32_t tile_no = 0;  // M tiles this CTA has finished: fixes how often each ring slot was used
         bool ok = true;
         for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++tile_no) {
             const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
-            float tq[RANK > 0 ? RANK : 1];
+            f32x2 tq2[RANK > 0 ? RANK : 1];
             bool odd_member = false;
             const float rs = g.row_scale[R];
             if (RG > 0) {
@@ -250,7 +270,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 #pragma unroll
                 for (int q = 0; q < RANK; q += 4) {
                     float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * RANK + q);
-                    tq[q] = tv.x; tq[q + 1] = tv.y; tq[q + 2] = tv.z; tq[q + 3] = tv.w;
+                    tq2[q] = pk2(tv.x, tv.x); tq2[q + 1] = pk2(tv.y, tv.y);
+                    tq2[q + 2] = pk2(tv.z, tv.z); tq2[q + 3] = pk2(tv.w, tv.w);
                 }
             }
             for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
@@ -258,50 +279,54 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                 if (!mbar_wait(&tfull[b], (acc_it >> 1) & 1, abort_flag, g.status, 6)) { ok = false; break; }
                 tc_fence_after();
                 for (int cb = 0; cb < BN / 32 && ok; ++cb) {
-                    const int n0 = c * BN + cb * 32;
-                    const int blk = n0 >> 5;  // 32-column block index inside this M tile
+                    const int n0 = c * BN + cb * 32 + eh * 16;   // first of this warp's sixteen columns
                     const float* my_a = nullptr;
                     int slot = 0;
                     if (RG > 0) {
-                        // the generator warps of this quadrant have staged the A rows n0..n0+31
-                        slot = blk % depth;
-                        // uses of this slot so far: (blocks_per_tile - slot + depth - 1) / depth per finished tile
-                        uint32_t u = (uint32_t)tile_no * (uint32_t)((blocks_per_tile - slot + depth - 1) / depth) +
-                                     (uint32_t)(blk / depth);
-                        if (!mbar_wait(&afull[q4 * MAX_DEPTH + slot], u & 1, abort_flag, g.status, 7)) { ok = false; break; }
-                        my_a = a_stage + (q4 * depth + slot) * 32 * RANK;
+                        // the item that holds these columns: one generator warp staged it
+                        const uint32_t item = tile_no * (uint32_t)items_per_tile +
+                                              (uint32_t)(IT::LPR == 2 ? (n0 >> 4) : (n0 >> 5));
+                        slot = (int)(item % (uint32_t)depth);
+                        if (!mbar_wait(&afull[q4 * MAX_DEPTH + slot], (item / (uint32_t)depth) & 1, abort_flag, g.status, 7)) {
+                            ok = false;
+                            break;
+                        }
+                        my_a = a_stage + (q4 * depth + slot) * IT::SLOT_FLOATS + (IT::LPR == 2 ? 0 : eh * 16);
                     }
                     float* orow = g.out + (size_t)R * g.out_stride + n0;
                     float* prow = (g.lif && g.pot) ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
 #pragma unroll 1
-                    for (int j0 = eh * 16; j0 < eh * 16 + 16; j0 += 8) {
+                    for (int j0 = 0; j0 < 16; j0 += 8) {
                         uint32_t acc[8];
-                        tmem_ld8(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + j0), acc);
-                        float y[8];
+                        tmem_ld8_issue(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + eh * 16 + j0), acc);
                         const float4 cs0 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0);
                         const float4 cs1 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0 + 4);
+                        // u[j] = sum_q t[q] * (base_sigma * A[n0+j0+j][q]), q ascending, one rounding per
+                        // multiply-add; two neighbouring columns advance together in one packed fma
+                        f32x2 u2[4] = {0ull, 0ull, 0ull, 0ull};
+                        if (RG > 0) {
+#pragma unroll
+                            for (int q = 0; q < RANK; ++q) {
+                                const ulonglong2 a01 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0));
+                                const ulonglong2 a23 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0 + 4));
+                                u2[0] = fma2(tq2[q], a01.x, u2[0]);
+                                u2[1] = fma2(tq2[q], a01.y, u2[1]);
+                                u2[2] = fma2(tq2[q], a23.x, u2[2]);
+                                u2[3] = fma2(tq2[q], a23.y, u2[3]);
+                            }
+                        }
+                        float u[8];
+                        upk2(u2[0], u[0], u[1]); upk2(u2[1], u[2], u[3]);
+                        upk2(u2[2], u[4], u[5]); upk2(u2[3], u[6], u[7]);
                         const float cs[8] = {cs0.x, cs0.y, cs0.z, cs0.w, cs1.x, cs1.y, cs1.z, cs1.w};
+                        tmem_ld_wait();
+                        float y[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            // undo the two power-of-two operand scales (exact)
+                            // undo the two power-of-two operand scales (exact); the member's sign is applied to
+                            // the finished sum (negating every term of a sum negates the sum exactly)
                             float v = __fmul_rn(__fmul_rn(__uint_as_float(acc[j]), rs), cs[j]);
-                            if (RG > 0) {
-                                // u = sum_q t[q] * (base_sigma * A[n0+j0+j][q]); the member's sign is applied to
-                                // the finished sum (negating every term of a sum negates the sum exactly)
-                                float u = 0.0f;
-                                const int row = j0 + j;
-                                const float4* ar = reinterpret_cast<const float4*>(my_a + row * RANK);
-                                const int sw = a_swizzle<RG>(row);
-#pragma unroll
-                                for (int q = 0; q < RG; ++q) {
-                                    float4 av = ar[q ^ sw];
-                                    u = fmaf(tq[4 * q + 0], av.x, u);
-                                    u = fmaf(tq[4 * q + 1], av.y, u);
-                                    u = fmaf(tq[4 * q + 2], av.z, u);
-                                    u = fmaf(tq[4 * q + 3], av.w, u);
-                                }
-                                v = __fadd_rn(v, odd_member ? -u : u);
-                            }
+                            if (RG > 0) v = __fadd_rn(v, odd_member ? -u[j] : u[j]);
                             y[j] = v;
                         }
                         if (g.lif) {
@@ -322,67 +347,74 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                                                 __fmul_rn(y[j + 2], out_scale), __fmul_rn(y[j + 3], out_scale));
                         }
                     }
-                    if (RG > 0) {
-                        mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // 64 arrivals (both warps) hand the slot back
-                    }
+                    if (RG > 0) mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // the item's reader(s) hand the slot back
                 }
                 tc_fence_before();
                 mbar_arrive(&tempty[b]);
             }
         }
-    } else if (RG > 0 && (warp - GEN_WARP0) / 4 < g.ring_depth) {
+    } else if (RG > 0 && (warp - GEN_WARP0) / 4 < g.gens) {
         // ------------------------------------------------------------ noise generators
-        // Generator (gq, gi) regenerates, for TMEM quadrant gq, the A rows of every 32-column
-        // block with index = gi (mod depth) into ring slot gi, scaled by base_sigma.  It runs
-        // ahead of the epilogue and never touches TMEM, so the regeneration overlaps the MMAs.
+        // Generator (gq, gi) regenerates, for TMEM quadrant gq, the A rows of every gens-th item
+        // (ROWS output columns of the quadrant's antithetic pair), scaled by base_sigma, into the
+        // ring slot the item maps to.  It runs ahead of the epilogue and never touches TMEM, so the
+        // regeneration overlaps the MMAs.
+        using IT = Item<RG>;
         constexpr int RANK = RG * 4;
         const int gq = (warp - GEN_WARP0) & 3, gi = (warp - GEN_WARP0) >> 2;
-        const int depth = g.ring_depth;
-        float* slot_a = a_stage + (gq * depth + gi) * 32 * RANK;
+        const int depth = g.ring_depth, GENS = g.gens;
         LibmCal cal = g.cal;
         cal.log_tab = log_tab_s;
         cal.log_delta = reinterpret_cast<const uint32_t*>(log_tab_s + 64);                         // byte tables, see
         cal.cos_delta = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(log_tab_s + 64) + 256);  // next_normals4_t<true>
-        const int blocks_per_tile = g.a / 32;
-        const int sw = a_swizzle<RG>(lane);
-        uint32_t used = 0;
+        const int items_per_tile = g.a / IT::ROWS;
+        const int n_local = lane % IT::ROWS, qoff = (lane / IT::ROWS) * IT::NPL;   // this lane's row and first rank index
+        float* const lane_a = a_stage + (size_t)gq * depth * IT::SLOT_FLOATS + (lane / IT::ROWS) * IT::ROWS + n_local;
+        uint32_t tile_no = 0;
         bool ok = true;
-        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
+        for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x, ++tile_no) {
             // every row of this quadrant's 32-row slice belongs to one antithetic pair
             int64_t member0 = (((int64_t)mt * BM_TILE + gq * 32) / g.bm) % g.n_pop;
             int32_t pair = (g.first_thread + (int32_t)member0) / 2;
-            if (g.cache_a) {
-                // the factors were generated earlier: stream this pair's rows from the cache
-                const float* src = g.cache_a + ((size_t)(pair - g.first_thread / 2) * g.a + gi * 32 + lane) * RANK;
-                for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
-                    float4 v[RG > 0 ? RG : 1];
-#pragma unroll
-                    for (int q = 0; q < RG; ++q) v[q] = __ldg(reinterpret_cast<const float4*>(src) + q);
-                    if (!mbar_wait(&aempty[gq * MAX_DEPTH + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
-#pragma unroll
-                    for (int q = 0; q < RG; ++q)
-                        *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
-                            make_float4(__fmul_rn(v[q].x, g.base_sigma), __fmul_rn(v[q].y, g.base_sigma),
-                                        __fmul_rn(v[q].z, g.base_sigma), __fmul_rn(v[q].w, g.base_sigma));
-                    src += (size_t)depth * 32 * RANK;
-                    mbar_arrive(&afull[gq * MAX_DEPTH + gi]);
-                }
-                continue;
+            // Items are numbered through all tiles of this CTA; this warp takes those with
+            // item % GENS == gi, so that a ring slot (item % depth, depth a multiple of GENS) is
+            // always written by the same warp.  it0: its first item inside this tile.
+            const int it0 = (int)(((uint32_t)gi + (uint32_t)GENS - (tile_no * (uint32_t)items_per_tile) % (uint32_t)GENS) % (uint32_t)GENS);
+            // cached factors: this lane's share of row (item * ROWS + n_local) of the pair, raw normals
+            const float* src = g.cache_a ? g.cache_a + ((size_t)(pair - g.first_thread / 2) * g.a + it0 * IT::ROWS + n_local) * RANK + qoff
+                                         : nullptr;
+            uint64_t a_state = 0;
+            if (!src) {
+                uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
+                a_state = jump_by(g.pow2, s0, 2ull * ((uint64_t)RANK * (uint64_t)(g.k + it0 * IT::ROWS + n_local) + (uint64_t)qoff));
             }
-            uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
-            uint64_t a_state = jump_by(g.pow2, s0, 2ull * (uint64_t)RANK * (uint64_t)(g.k + gi * 32 + lane));
-            for (int blk = gi; blk < blocks_per_tile; blk += depth, ++used) {
-                if (!mbar_wait(&aempty[gq * MAX_DEPTH + gi], (used & 1) ^ 1, abort_flag, g.status, 8)) { ok = false; break; }
-#pragma unroll 1
-                for (int q = 0; q < RG; ++q) {
-                    float z[4];
-                    next_normals4_t<true>(a_state, cal, z);
-                    *reinterpret_cast<float4*>(slot_a + lane * RANK + ((q ^ sw) << 2)) =
-                        make_float4(__fmul_rn(z[0], g.base_sigma), __fmul_rn(z[1], g.base_sigma),
-                                    __fmul_rn(z[2], g.base_sigma), __fmul_rn(z[3], g.base_sigma));
+            for (int it = it0; it < items_per_tile; it += GENS) {
+                const uint32_t item = tile_no * (uint32_t)items_per_tile + (uint32_t)it;
+                const int slot = (int)(item % (uint32_t)depth);
+                float4 v[IT::NPL / 4];
+                if (src) {   // the loads fly while the slot is waited for
+#pragma unroll
+                    for (int c4 = 0; c4 < IT::NPL / 4; ++c4) v[c4] = __ldg(reinterpret_cast<const float4*>(src) + c4);
+                    src += (size_t)GENS * IT::ROWS * RANK;
                 }
-                a_state = jump_apply(g.hop, a_state);  // on to this generator's next block of rows
-                mbar_arrive(&afull[gq * MAX_DEPTH + gi]);      // 32 arrivals publish the slot
+                if (!mbar_wait(&aempty[gq * MAX_DEPTH + slot], ((item / (uint32_t)depth) & 1) ^ 1, abort_flag, g.status, 8)) {
+                    ok = false;
+                    break;
+                }
+                float* dst = lane_a + slot * IT::SLOT_FLOATS;
+#pragma unroll 1
+                for (int c4 = 0; c4 < IT::NPL / 4; ++c4) {
+                    float z[4];
+                    if (src) {
+                        z[0] = v[c4].x; z[1] = v[c4].y; z[2] = v[c4].z; z[3] = v[c4].w;
+                    } else {
+                        next_normals4_t<true>(a_state, cal, z);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) dst[(4 * c4 + j) * 32] = __fmul_rn(z[j], g.base_sigma);
+                }
+                if (!src) a_state = jump_apply(g.hop, a_state);  // on to this generator's next item
+                mbar_arrive(&afull[gq * MAX_DEPTH + slot]);       // 32 arrivals publish the item
             }
         }
     }
@@ -756,13 +788,25 @@ int launch_tc_rg(hses_ctx* ctx, cudaStream_t st, const CUtensorMap& tm_x, const 
 
 template <int BN>
 int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const TcScratch& sc, TcArgs ta) {
-    // as many ring slots (and generator warps) per quadrant as shared memory allows, at most MAX_DEPTH
-    ta.ring_depth = MAX_DEPTH;
-    while (ta.ring_depth > 1 && TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(ta.ring_depth, ta.rank) > TcSmem<BN>::LIMIT)
-        --ta.ring_depth;
+    // Generator warps per quadrant and ring slots: the deepest ring that fits in shared memory under
+    // the rule stated at TcArgs (depth a multiple of the generator count, and even for 16-column
+    // items).  More slots than generators matter more than a fourth generator: a generator needs a
+    // free slot to write while the epilogue still reads its previous item.
+    ta.gens = 0;
+    ta.ring_depth = 0;
     if (g.perturb) {
+        const int choices[][2] = {{4, 8}, {3, 6}, {4, 4}, {2, 4}, {2, 2}, {1, 2}};   // (gens, depth), best first
+        for (auto& ch : choices) {
+            if (TcSmem<BN>::FIXED + TcSmem<BN>::a_bytes(ch[1], ta.rank) <= TcSmem<BN>::LIMIT) {
+                ta.gens = ch[0];
+                ta.ring_depth = ch[1];
+                break;
+            }
+        }
+        HSES_REQUIRE(ta.gens > 0, "linear_tc: the ring of staged factor rows does not fit in shared memory");
         const uint64_t* hop = nullptr;
-        int hrc = get_hop_table(ctx, 2ull * g.rank * (32ull * ta.ring_depth - 1), &hop);
+        // from the end of a lane's share of one item to the start of its share of the warp's next item
+        int hrc = get_hop_table(ctx, 2ull * ((uint64_t)g.rank * item_rows(g.rank) * ta.gens - item_normals_per_lane(g.rank)), &hop);
         if (hrc != HSES_OK) return hrc;
         ta.hop = hop;
     }
@@ -774,7 +818,7 @@ int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const T
     if (rc == HSES_OK) rc = make_map(&tm_wlo, sc.wlo, g.a, g.k, g.k, BN);
     if (rc != HSES_OK) return rc;
     using S = TcSmem<BN>;
-    int smem_bytes = S::FIXED + S::a_bytes(ta.ring_depth, ta.rank);
+    int smem_bytes = S::FIXED + (g.perturb ? S::a_bytes(ta.ring_depth, ta.rank) : 0);
     HSES_REQUIRE(smem_bytes <= S::LIMIT, "shared memory budget exceeded");
     int m_tiles = (int)(rows / BM_TILE);
     int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;

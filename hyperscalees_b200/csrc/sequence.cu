@@ -141,6 +141,7 @@ wkv7_kernel(const float* __restrict__ r, const float* __restrict__ w, const floa
 // ---------------------------------------------------------------------------
 // Spiking self-attention core on firing rates Q, K, V of shape (tokens, d) per (sequence, head).
 //   mode 0  spike product without softmax:  O = (beta * Q K^T) V
+//   mode 3  the same with a causal mask: the score of key j is zero for j > i (next-token models)
 //   mode 1  LIF-count row softmax (src/hyperscalees/models/snn_self_attention.py:45-98): each row
 //           of beta*QK^T is scaled by 1/(max|.| + 1e-6), then n_iter LIF steps with hard reset and
 //           global inhibition g_inh * sum(counts so far); weights = count / (sum(count) + 1e-6)
@@ -174,6 +175,7 @@ __global__ void spiking_attention_kernel(const float* __restrict__ Q, const floa
         float acc = 0.0f;
         for (int c = 0; c < d; ++c) acc = __fadd_rn(acc, __fmul_rn(q[c], ks[j * d + c]));
         hrow[j] = __fmul_rn(beta, acc);
+        if (mode == 3 && j > i) hrow[j] = 0.0f;   // causal spike product: a query sees keys 0..i only
         amax = fmaxf(amax, fabsf(hrow[j]));
     }
     if (mode == 1) {
@@ -242,7 +244,7 @@ template <int D>
 __global__ void __launch_bounds__(128)
 attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                          int tokens, int heads, int64_t row_stride, float beta, const float* __restrict__ beta_seq,
-                         float* __restrict__ O, float* __restrict__ A_out) {
+                         int causal, float* __restrict__ O, float* __restrict__ A_out) {
     extern __shared__ __align__(16) float sm[];  // K (tokens, D) | V (tokens, D)
     float4* ks4 = reinterpret_cast<float4*>(sm);
     float4* vs4 = ks4 + tokens * (D / 4);
@@ -287,7 +289,7 @@ attention_product_kernel(const float* __restrict__ Q, const float* __restrict__ 
 #pragma unroll
         for (int u = 0; u < JB; ++u) {
             if (j0 + u < tokens) {
-                const float hj = __fmul_rn(beta, sc[u]);
+                const float hj = (causal && j0 + u > i) ? 0.0f : __fmul_rn(beta, sc[u]);
                 if (arow) arow[j0 + u] = hj;
 #pragma unroll
                 for (int c4 = 0; c4 < D4; ++c4) {
@@ -466,7 +468,8 @@ template <int D>
 __global__ void __launch_bounds__(64)
 attention_product_packed_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
                                 int tokens, int heads, int64_t row_stride, float beta,
-                                const float* __restrict__ beta_seq, float* __restrict__ O, float* __restrict__ A_out) {
+                                const float* __restrict__ beta_seq, int causal, float* __restrict__ O,
+                                float* __restrict__ A_out) {
     extern __shared__ __align__(16) float sm[];
     const int tp = (tokens + 3) / 4 * 4 + 4;   // pitch of Kt: keys rounded up to four, plus four
     float* kt = sm;                            // [D][tp]
@@ -506,7 +509,10 @@ attention_product_packed_kernel(const float* __restrict__ Q, const float* __rest
     const f32x2 beta2 = pk2(beta, beta);
     float* arow_a = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i0) * tokens : nullptr;
     float* arow_b = A_out ? A_out + (((size_t)seq * heads + h) * tokens + i1) * tokens : nullptr;
-    for (int j0 = 0; j0 < tokens; j0 += 4) {
+    // with the causal mask the keys after this thread's second row contribute nothing: they are
+    // skipped, except that the weight rows, when asked for, are written in full
+    const int j_end = (causal && !A_out) ? min(tokens, i1 + 1) : tokens;
+    for (int j0 = 0; j0 < j_end; j0 += 4) {
         f32x2 sa01 = 0ull, sa23 = 0ull, sb01 = 0ull, sb23 = 0ull;
 #pragma unroll
         for (int c = 0; c < D; ++c) {
@@ -521,6 +527,13 @@ attention_product_packed_kernel(const float* __restrict__ Q, const float* __rest
         upk2(mul2(beta2, sa23), ha[2], ha[3]);
         upk2(mul2(beta2, sb01), hb[0], hb[1]);
         upk2(mul2(beta2, sb23), hb[2], hb[3]);
+        if (causal) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (j0 + u > i0) ha[u] = 0.0f;
+                if (j0 + u > i1) hb[u] = 0.0f;
+            }
+        }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             if (j0 + u < tokens) {
@@ -767,8 +780,10 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
     HSES_REQUIRE(n_seq >= 0 && tokens >= 1 && tokens <= kMaxTokens, "tokens must be in 1..128");
     HSES_REQUIRE(heads >= 1 && head_dim >= 1 && head_dim <= kMaxHeadDim, "head_dim must be in 1..64");
     HSES_REQUIRE(row_stride >= (int64_t)heads * head_dim, "row stride smaller than heads*head_dim");
-    HSES_REQUIRE(mode >= 0 && mode <= 2, "unknown mode");
-    HSES_REQUIRE(mode == 0 || (tau_m != 0.0f && n_iter >= 1), "bad LIF parameters");
+    HSES_REQUIRE(mode >= 0 && mode <= 3, "unknown mode");
+    HSES_REQUIRE(mode == 0 || mode == 3 || (tau_m != 0.0f && n_iter >= 1), "bad LIF parameters");
+    const int causal = mode == 3 ? 1 : 0;
+    const bool product = mode == 0 || mode == 3;
     HSES_REQUIRE(n_seq * heads < (1ll << 31), "too many (sequence, head) pairs");
     if (n_seq == 0) return HSES_OK;
     HSES_REQUIRE(Q && K && V && O, "NULL pointer");
@@ -776,30 +791,31 @@ int hses_spiking_attention(hses_ctx* ctx, hses_stream stream, const float* Q, co
     size_t smem = (size_t)2 * tokens * head_dim * sizeof(float);
     HSES_KERNEL(ctx, as_stream(stream), "spiking_attention");
     const bool aligned = ((((uintptr_t)Q | (uintptr_t)K | (uintptr_t)V | (uintptr_t)O) & 15u) == 0) && row_stride % 4 == 0;
-    if (mode == 0 && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64)) {
+    if (product && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64)) {
         unsigned grid = (unsigned)(n_seq * heads);
         cudaStream_t st = as_stream(stream);
         const int threads2 = ((tokens + 1) / 2 + 31) / 32 * 32;   // two query rows per thread
         const size_t smem_packed = ((size_t)head_dim * ((tokens + 3) / 4 * 4 + 4) + (size_t)tokens * head_dim) * sizeof(float);
         if (head_dim == 16)
             attention_product_packed_kernel<16><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
-                                                                                     beta, beta_per_seq, O, A_out);
+                                                                                     beta, beta_per_seq, causal, O, A_out);
         else if (head_dim == 32)
             attention_product_packed_kernel<32><<<grid, threads2, smem_packed, st>>>(Q, K, V, tokens, heads, row_stride,
-                                                                                     beta, beta_per_seq, O, A_out);
+                                                                                     beta, beta_per_seq, causal, O, A_out);
         else {
             // up to 64 KB for 128 tokens x 64 values: above the 48 KB a kernel gets without opting in
             if (smem > 48 * 1024)
                 HSES_CUDA(cudaFuncSetAttribute(attention_product_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)smem));
-            attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, beta_per_seq, O, A_out);
+            attention_product_kernel<64><<<grid, threads, smem, st>>>(Q, K, V, tokens, heads, row_stride, beta, beta_per_seq,
+                                                                      causal, O, A_out);
         }
         HSES_LAUNCH_CHECK();
         return HSES_OK;
     }
     const size_t smem_rows = ((size_t)2 * tokens * head_dim + (size_t)(mode == 1 ? 3 : 2) * tokens * (tokens + 1)) *
                              sizeof(float);
-    if (mode != 0 && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64) && smem_rows <= 200 * 1024) {
+    if (!product && aligned && (head_dim == 16 || head_dim == 32 || head_dim == 64) && smem_rows <= 200 * 1024) {
         unsigned grid = (unsigned)(n_seq * heads);
         cudaStream_t st = as_stream(stream);
         cudaError_t e;
