@@ -18,7 +18,9 @@ The same JSON line carries two more blocks, measured after the headline:
                    exchanges inside the timed region), with a check that every rank ends a step
                    with bit-identical parameters and that they match the single-GPU step;
   streaming        the HBM-bound kernels of the path (encode, LIF scan, attention, WKV-7), each
-                   timed alone against the measured copy bandwidth.
+                   timed alone against the measured copy bandwidth;
+  spiking_lm       (one GPU) the token-level spiking transformer at 4096 members x 32 sequences:
+                   ms per fitness evaluation of the whole population.
 
     python bench.py --gpus N --steps K --warmup W            # the CUDA path
     python bench.py --impl reference --gpus N --steps K ...   # CPU restatement of the reference
@@ -190,7 +192,6 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=dev)
     ctx = core.get_context(local_rank)
     peaks = measured_peaks()
@@ -281,7 +282,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                   "note": "factors read from a device cache built once outside the timed region"}
         del cache
     # ---- the two extra blocks of the line (see the module docstring) ----
-    pop_block, stream_block = None, None
+    pop_block, stream_block, lm_block = None, None, None
     if not args.kernel_only and not args.headline_only:
         del x_dev, out_dev, pipe
         torch.cuda.empty_cache()
@@ -301,6 +302,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                                                                       "kernel_ms_per_step", "device_status")}
             stream_block = streaming_block(dev, ctx, args.steps, args.warmup,
                                            only=("poisson_encode", "lif_scan", "spiking_attention mode 0", "wkv7"))
+            lm_block = spiking_lm_block(dev, ctx, 4096, 32, args.steps, args.warmup)
         if comm is not None:
             comm.destroy()
     clocks = sampler.stop() if sampler else None
@@ -346,7 +348,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
                 "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached,
-                "population_step": pop_block, "streaming": stream_block}
+                "population_step": pop_block, "streaming": stream_block, "spiking_lm": lm_block}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -528,7 +530,6 @@ def run_population_step(args, rank: int, local_rank: int, world: int):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=dev)
     ctx = core.get_context(local_rank)
     comm = make_comm(ctx, world)
@@ -662,6 +663,64 @@ def run_streaming_kernels(args, local_rank: int):
                       "device_status": ctx.device_status()}), flush=True)
 
 
+def spiking_lm_block(dev, ctx, n_pop: int, seqs: int, steps: int, warmup: int, chunk_members: int = 1024):
+    """BASELINE's token-level spiking transformer: d_model 64, 4 heads, 2 blocks, MLP ratio 4, vocab 256,
+    sequences of 64 uniform token ids, Q/K/V as LIF rates over T = 4, causal spike-product attention,
+    rank-8 noise on every matrix, `seqs` sequences per member; one step = the next-token
+    log-likelihood fitness of every member.  member-evals/s = n_pop * seqs * T per second."""
+    import torch
+    from hyperscalees_b200 import models
+    from hyperscalees_b200.spiking_lm import LmNoise, SpikingLM
+
+    vocab, L, d, H, blocks, T, rank = 256, 64, 64, 4, 2, 4, 8
+    model = SpikingLM(vocab, L, d, H, blocks, mlp_ratio=4, T=T, device=dev, seed=2)
+    g = torch.Generator(device=dev).manual_seed(2)
+    ids = torch.randint(0, vocab, (n_pop, seqs, L), device=dev, generator=g, dtype=torch.int32)
+    noise = LmNoise(0.02, rank, models.default_base_keys(len(model.params())), epoch=0, first_thread=0)
+    for _ in range(max(min(warmup, 3), 2)):
+        fit = model.fitness(ids, noise, chunk_members=chunk_members)
+    torch.cuda.synchronize()
+    steps = max(2, min(steps, 5))
+    ctx.profile_enable(False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fit = model.fitness(ids, noise, chunk_members=chunk_members)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = sum(v[0] for v in ctx.profile_read().values()) / steps
+    ctx.profile_enable(True)
+    model.fitness(ids, noise, chunk_members=chunk_members)
+    torch.cuda.synchronize()
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    return {"workload": f"token-level spiking transformer: {n_pop} members x {seqs} sequences x {L} tokens, vocab {vocab}, "
+                        f"d_model {d}, {H} heads, {blocks} blocks, MLP ratio 4, T {T}, rank {rank}, sigma 0.02, "
+                        f"chunks of {chunk_members} members",
+            "ms_per_step": ms, "member_evals_per_sec": n_pop * seqs * T / (ms * 1e-3),
+            "tokens_per_sec": n_pop * seqs * L / (ms * 1e-3), "gpu_launches_per_step": launches,
+            "kernel_ms_per_step": {k: round(v[1], 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+            "fitness_finite": bool(torch.isfinite(fit).all().item()), "fitness_mean": float(fit.mean().item()),
+            "device_status": ctx.device_status()}
+
+
+def run_spiking_lm(args, local_rank: int):
+    """--workload spiking_lm: the block above alone, one GPU."""
+    import torch
+    from hyperscalees_b200 import core
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ctx = core.get_context(local_rank)
+    sampler = ClockSampler(local_rank)
+    blk = spiking_lm_block(dev, ctx, args.n_pop, args.bm if args.bm > 1 else 32, args.steps, args.warmup, args.chunk)
+    print(json.dumps({"metric": METRIC, "value": blk["member_evals_per_sec"], "unit": UNIT, "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": blk["ms_per_step"],
+                      "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": blk["workload"]}, "spiking_lm": blk, "clocks": sampler.stop()}), flush=True)
+
+
 def run_snn_transformer(args, local_rank: int):
     """Secondary workload: forward_batched of the SNN-rate transformer (d_model 64, 4 heads, 2 blocks,
     16 tokens of 49 inputs, T = 4 encoding steps) over a chunk of --n-pop members with rank-8 noise;
@@ -712,7 +771,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer", "spiking_lm"],
                     help="microbench: the perturbed-linear layer the metric is quoted on (default); "
                          "population_step: a full ES step of the spiking MLP (secondary figure); "
                          "streaming_kernels: the HBM-bound kernels of the path, each timed alone; "
@@ -724,6 +783,7 @@ def main():
     ap.add_argument("--n-pop", type=int, default=8192,
                     help="microbench: members per GPU (smaller values give the reduced case used for ncu "
                          "captures); population_step: members of the whole population")
+    ap.add_argument("--chunk", type=int, default=1024, help="spiking_lm: members evaluated per pass")
     ap.add_argument("--shrink", type=int, default=1,
                     help="streaming_kernels: divide every case's leading dimension (reduced cases for ncu captures)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -747,6 +807,9 @@ def main():
     elif args.workload == "snn_transformer":
         if rank == 0:
             run_snn_transformer(args, local_rank)
+    elif args.workload == "spiking_lm":
+        if rank == 0:
+            run_spiking_lm(args, local_rank)
     else:
         run_ours(args, rank, local_rank, world)
 

@@ -30,6 +30,7 @@ EXPORTS = [
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
     "hses_prng_normal_half", "hses_einsum_pair_workspace_bytes", "hses_einsum_pair", "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
+    "hses_embedding", "hses_lif_rate", "hses_swish", "hses_add_inplace", "hses_token_fitness",
     "hses_comm_unique_id", "hses_comm_init", "hses_comm_rank", "hses_comm_world", "hses_comm_async_error",
     "hses_comm_destroy", "hses_comm_abort", "hses_allgather_fitness", "hses_allreduce_grads",
 ]
@@ -171,6 +172,11 @@ def load():
     L.hses_wkv7.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp]
     L.hses_spiking_attention.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, f32, vp, f32, f32, f32, i32,
                                          vp, vp]
+    L.hses_embedding.argtypes = [vp, vp, vp, i64, vp, i64, i32, i32, vp, i32, vp, vp, i32, i64, vp, i64]
+    L.hses_lif_rate.argtypes = [vp, vp, vp, i64, i32, f32, f32, i32, vp]
+    L.hses_swish.argtypes = [vp, vp, vp, i64, vp]
+    L.hses_add_inplace.argtypes = [vp, vp, vp, vp, i64]
+    L.hses_token_fitness.argtypes = [vp, vp, vp, i64, vp, i64, i32, i32, i32, f32, vp, vp]
     L.hses_comm_unique_id.argtypes = [vp]
     L.hses_comm_init.argtypes = [vp, vp, i32, i32, C.POINTER(vp)]
     L.hses_comm_rank.argtypes = [vp]

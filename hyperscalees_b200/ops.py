@@ -609,3 +609,91 @@ def rate_encode(p: torch.Tensor, gain: float) -> torch.Tensor:
     ctx = get_context(p.device)
     _lib.check(_lib.load().hses_rate_encode(ctx.handle, current_stream(), _ptr(p), p.numel(), gain, _ptr(out)))
     return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, pos: Optional[torch.Tensor] = None,
+              A: Optional[torch.Tensor] = None, B: Optional[torch.Tensor] = None,
+              rows_per_member: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """do_emb over a population: ids (rows,) int32 -> (rows, d) = table[ids] + A_m[ids] B_m^T + pos[row % L].
+    A (n, vocab, r) scaled by sign*sigma/sqrt(r) and B (n, d, r) as lora_factors returns them for a
+    parameter of shape (vocab, d); member m owns rows_per_member consecutive rows."""
+    _check(table, "table", ndim=2)
+    if ids.dtype != torch.int32 or not ids.is_cuda or not ids.is_contiguous():
+        raise ValueError("ids must be a contiguous CUDA int32 tensor")
+    rows = ids.numel()
+    vocab, d = table.shape
+    rank = 0
+    if A is not None:
+        _check(A, "A", ndim=3)
+        _check(B, "B", ndim=3)
+        if A.shape[1] != vocab or B.shape[1] != d or A.shape[2] != B.shape[2] or A.shape[0] != B.shape[0]:
+            raise ValueError("A must be (n, vocab, r) and B (n, d, r)")
+        if not (A.is_contiguous() and B.is_contiguous()):
+            raise ValueError("A and B must be contiguous")
+        rank = A.shape[2]
+        if rows_per_member < 1 or rows != A.shape[0] * rows_per_member:
+            raise ValueError("rows must equal members * rows_per_member")
+    L = 0
+    if pos is not None:
+        _check(pos, "pos", ndim=2)
+        if pos.shape[1] != d or not pos.is_contiguous():
+            raise ValueError("pos must be a contiguous (L, d) tensor")
+        L = pos.shape[0]
+    if out is None:
+        out = torch.empty((rows, d), dtype=torch.float32, device=table.device)
+    ctx = get_context(table.device)
+    _lib.check(_lib.load().hses_embedding(ctx.handle, current_stream(), ids.data_ptr(), rows, _ptr(table), table.stride(0),
+                                          vocab, d, _ptr(pos), L, _ptr(A), _ptr(B), rank, rows_per_member, _ptr(out),
+                                          out.stride(0)))
+    return out
+
+
+def lif_rate(cur: torch.Tensor, T: int, tau_m: float, v_th: float, reset_mode: int = RESET_HARD,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Firing rate over T steps of LIF neurons driven by the constant currents `cur` (any shape, dense)."""
+    _check(cur, "cur")
+    if not cur.is_contiguous():
+        raise ValueError("cur must be contiguous")
+    if out is None:
+        out = torch.empty_like(cur)
+    ctx = get_context(cur.device)
+    _lib.check(_lib.load().hses_lif_rate(ctx.handle, current_stream(), _ptr(cur), cur.numel(), T, tau_m, v_th, reset_mode,
+                                         _ptr(out)))
+    return out
+
+
+def swish(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _check(x, "x")
+    if not x.is_contiguous():
+        raise ValueError("x must be contiguous")
+    if out is None:
+        out = torch.empty_like(x)
+    ctx = get_context(x.device)
+    _lib.check(_lib.load().hses_swish(ctx.handle, current_stream(), _ptr(x), x.numel(), _ptr(out)))
+    return out
+
+
+def add_inplace(acc: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    _check(acc, "acc")
+    _check(y, "y")
+    if acc.shape != y.shape or not (acc.is_contiguous() and y.is_contiguous()):
+        raise ValueError("acc and y must be contiguous tensors of one shape")
+    ctx = get_context(acc.device)
+    _lib.check(_lib.load().hses_add_inplace(ctx.handle, current_stream(), _ptr(acc), _ptr(y), acc.numel()))
+    return acc
+
+
+def token_fitness(logits: torch.Tensor, ids: torch.Tensor, n_members: int, seqs: int, L: int,
+                  gain: float = 1.0) -> torch.Tensor:
+    """Per member the mean next-token log-likelihood: logits (n_members*seqs*L, vocab), ids the
+    int32 tokens in the same row order; position t is scored against the token at t+1."""
+    _check(logits, "logits", ndim=2)
+    rows, vocab = logits.shape
+    if rows != n_members * seqs * L or ids.numel() != rows or ids.dtype != torch.int32:
+        raise ValueError("logits and ids must hold n_members*seqs*L rows")
+    scratch = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    out = torch.empty(n_members, dtype=torch.float32, device=logits.device)
+    ctx = get_context(logits.device)
+    _lib.check(_lib.load().hses_token_fitness(ctx.handle, current_stream(), _ptr(logits), logits.stride(0), ids.data_ptr(),
+                                              n_members, seqs, L, vocab, gain, _ptr(scratch), _ptr(out)))
+    return out

@@ -457,7 +457,8 @@ int hses_wkv7(hses_ctx* ctx, hses_stream stream, const float* r, const float* w,
 /* ---- spiking self-attention core on firing rates (src/hyperscalees/models/snn_self_attention.py:45-98;
  *      the Rust port keeps a continuous variant, hyperscalees-models/src/snn_transformer.rs:80-102).
  *      Q, K, V, O: (n_seq, tokens, heads*head_dim) with row_stride; mode 0: O = (beta Q K^T) V,
- *      the spike product without softmax; mode 1: LIF-count row softmax (n_iter LIF steps with
+ *      the spike product without softmax; mode 3: the same with a causal mask (the score of key
+ *      j is zero for j > i: a token of a next-token model does not see later ones); mode 1: LIF-count row softmax (n_iter LIF steps with
  *      global inhibition g_inh); mode 2: the Rust port's continuous form — n_iter Hopfield
  *      relaxations u <- u + (1/tau_m)(-u + H - g_inh * mean_key(u)) from u = H, then a stable
  *      softmax along the keys (snn_transformer.rs:80-102).  beta_per_seq (optional): n_seq scales
@@ -492,6 +493,38 @@ int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x /*device*
 /* rate_encode, hyperscalees-models/src/snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|)). */
 int hses_rate_encode(hses_ctx* ctx, hses_stream stream, const float* p /*device*/, int64_t n, float gain,
                      float* out /*device*/);
+
+/* ---- pieces of the token-level spiking transformer (BASELINE's next-token form of the spiking
+ *      self-attention model; the reference has the LIF-coded Q/K/V of
+ *      src/hyperscalees/models/snn_self_attention.py:114-131 and the block structure of
+ *      hyperscalees-models/src/snn_transformer.rs:345-413, but no token embedding: do_emb is
+ *      unimplemented in both noisers, src/hyperscalees/noiser/eggroll.py:93 and
+ *      hyperscalees-noiser/src/eggroll.rs:943-954, whose comment gives the clean form param[x]).
+ *      hses_embedding: out[row] = table[ids[row]] + A_m[ids[row], :] B_m^T + pos[row % L]; A
+ *      (n, vocab, rank) already scaled by sign*sigma/sqrt(rank) and B (n, d, rank) as
+ *      hses_lora_factors writes them for a parameter of shape (a = vocab, b = d); member m owns
+ *      rows [m*rows_per_member, (m+1)*rows_per_member); A = B = NULL gives the clean gather, pos
+ *      NULL leaves the position term out.  An id outside [0, vocab) yields a row of zeros and sets
+ *      bit 15 of the context's device status word.
+ *      hses_lif_rate: out[i] = (1/T) * sum of the T spikes of lif_step (snn.rs:53-65) driven by
+ *      the constant current cur[i] from v = 0.
+ *      hses_swish: x * sigmoid(x) (snn_transformer.rs:404).  hses_add_inplace: acc += y.
+ *      hses_token_fitness: per member the mean over its seqs sequences and positions 0..L-2 of
+ *      log_softmax(gain * logits[s, t])[ids[s, t+1]]; per_token (n_members*seqs*L) is scratch that
+ *      ends up holding the per-position terms. ------------------------------------------------- */
+int hses_embedding(hses_ctx* ctx, hses_stream stream, const int32_t* ids /*device (rows)*/, int64_t rows,
+                   const float* table /*device (vocab,d)*/, int64_t table_stride, int32_t vocab, int32_t d,
+                   const float* pos /*device (L,d) or NULL*/, int32_t L, const float* A /*device or NULL*/,
+                   const float* B /*device or NULL*/, int32_t rank, int64_t rows_per_member,
+                   float* out /*device (rows,d)*/, int64_t out_stride);
+int hses_lif_rate(hses_ctx* ctx, hses_stream stream, const float* cur /*device*/, int64_t n, int32_t T,
+                  float tau_m, float v_th, int32_t reset_mode, float* out /*device*/);
+int hses_swish(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t n, float* out /*device*/);
+int hses_add_inplace(hses_ctx* ctx, hses_stream stream, float* acc /*device*/, const float* y /*device*/, int64_t n);
+int hses_token_fitness(hses_ctx* ctx, hses_stream stream, const float* logits /*device (n*seqs*L, vocab)*/,
+                       int64_t logits_stride, const int32_t* ids /*device (n*seqs*L)*/, int64_t n_members,
+                       int32_t seqs, int32_t L, int32_t vocab, float gain, float* per_token /*device scratch*/,
+                       float* fitness /*device (n_members)*/);
 
 /* ---- collectives of the sharded population step.  The reference's product crates hold no
  *      multi-GPU code; its recipe is the Python trainer

@@ -783,7 +783,8 @@ void hso_wkv7(const float *r, const float *w, const float *k, const float *v,
 /* src/hyperscalees/models/snn_self_attention.py:45-98 (row_softmax_lif,
  * self_attention_lif) for one head: Q, K, V are (tokens, d) firing rates.
  * mode 0 is the spike product without softmax, O = (beta Q K^T) V, which has no
- * reference counterpart beyond the two matmuls; mode 1 is the LIF-count row
+ * reference counterpart beyond the two matmuls (mode 3: the same with the scores of keys
+ * j > i set to zero, for next-token models); mode 1 is the LIF-count row
  * softmax: each row of beta*QK^T divided by (max|row| + 1e-6), n_iter LIF steps
  * (hard reset, lif_step of snn_attention.py) driven by row - g_inh*sum(counts),
  * weights = counts / (sum(counts) + 1e-6). */
@@ -798,6 +799,7 @@ void hso_spiking_attention(const float *Q, const float *K, const float *V, int t
             float acc = 0.0f;
             for (int c = 0; c < d; ++c) acc += Q[(size_t)i * d + c] * K[(size_t)j * d + c];
             row[j] = beta * acc;
+            if (mode == 3 && j > i) row[j] = 0.0f; /* causal spike product: keys after the query are masked */
             if (fabsf(row[j]) > amax) amax = fabsf(row[j]);
         }
         if (mode == 1) {

@@ -139,3 +139,32 @@ def test_config3_full_size_properties(hs, oracle, rank):
                                   lr=0.01, weight_decay=1e-4)
     want_p = want_p[0] if isinstance(want_p, tuple) else want_p
     assert np.abs(step.params[0].cpu().numpy() - want_p).max() <= 1e-3 * np.abs(want_p).max()
+
+
+def test_config2_full_size_sampled_members(hs, oracle):
+    """Token-level spiking transformer at BASELINE's size (4096 members x 32 sequences x 64 tokens,
+    d_model 64, 4 heads, 2 blocks, vocab 256, rank 8): deterministic, a chunk boundary does not
+    change a member's value, sampled members match the CPU composition."""
+    from hyperscalees_b200 import models
+    from hyperscalees_b200.spiking_lm import LmNoise, SpikingLM
+    from oracle import spiking_lm as SL
+    vocab, L, d, H, blocks, rank, sigma, n, seqs = 256, 64, 64, 4, 2, 8, 0.02, 4096, 32
+    m = SpikingLM(vocab, L, d, H, blocks, mlp_ratio=4, T=4, seed=2)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    ids = torch.randint(0, vocab, (n, seqs, L), device="cuda", generator=g, dtype=torch.int32)
+    keys = models.default_base_keys(len(m.params()))
+    noise = LmNoise(sigma, rank, keys)
+    fit = m.fitness(ids, noise, chunk_members=1024)
+    status_ok()
+    assert torch.isfinite(fit).all() and fit.std().item() > 0
+    assert torch.equal(m.fitness(ids, noise, chunk_members=1024), fit)
+    part = m.fitness(ids[1000:1064].contiguous(), LmNoise(sigma, rank, keys, first_thread=1000), chunk_members=64)
+    assert torch.equal(part, fit[1000:1064])
+    npm = {"emb": m.emb.cpu().numpy(), "pos_emb": m.pos_emb.cpu().numpy(), "out": m.out.cpu().numpy(),
+           "blocks": [{k: ([w.cpu().numpy() for w in v] if isinstance(v, list) else v.cpu().numpy())
+                       for k, v in blk.items()} for blk in m.blocks],
+           "T": m.T, "tau_m": m.tau_m, "v_th": m.v_th, "beta": m.beta, "num_heads": m.num_heads}
+    ih = ids.cpu().numpy()
+    for j in (0, 1, 2049, 4095):
+        want = SL.member_fitness(SL.member_forward(npm, ih[j], sigma, rank, keys, (0, j)), ih[j])
+        assert abs(fit[j].item() - want) <= 1e-3 * max(1.0, abs(want))
