@@ -61,7 +61,8 @@ class LinearArgs(C.Structure):
         ("tau_m", C.c_float), ("v_th", C.c_float), ("reset_mode", C.c_int32), ("out_scale", C.c_float), ("out_scale_ptr", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("cache", C.POINTER(FactorCacheDesc)),
+        ("cache", C.POINTER(FactorCacheDesc)), ("precision", C.c_int32),
+        ("factor_order", C.c_int32),
     ]
 
 

@@ -215,6 +215,9 @@ static int check_args(const hses_linear_args* g) {
                  "row stride smaller than the row");
     HSES_REQUIRE((double)g->t_steps * (double)g->n_pop * g->bm < 2147483648.0, "too many rows");
     HSES_REQUIRE(g->x != nullptr && g->param != nullptr && g->out != nullptr, "NULL pointer");
+    HSES_REQUIRE(g->precision == HSES_PRECISION_FP32 || g->precision == HSES_PRECISION_BF16, "unknown precision");
+    HSES_REQUIRE(g->factor_order == 0 || g->factor_order == 1, "unknown factor order");
+    HSES_REQUIRE(!(g->factor_order == 1 && g->cache != nullptr), "a factor cache holds the do_mm order only");
     if (g->perturb) {
         HSES_REQUIRE(g->rank >= 1 && g->rank <= 1024, "rank out of range");
         HSES_REQUIRE(g->first_thread >= 0 && g->noise_reuse >= 0, "negative thread id or noise_reuse");
@@ -275,8 +278,12 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
             if (rc != HSES_OK) return rc;
         } else {
             int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - ep.first_pair + 1;
-            int rc = launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse),
-                                         ep.first_pair, pairs, g.rank, g.a, g.k, nullptr, s.A, s.B);
+            // do_Tmm order: the output-side rows lead the stream, the input-side rows follow
+            int rc = g.factor_order == 1
+                         ? launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse), ep.first_pair, pairs,
+                                               g.rank, g.k, g.a, nullptr, s.B, s.A)
+                         : launch_pair_factors(ctx, st, g.key, true_epoch_of(g.epoch, g.noise_reuse), ep.first_pair, pairs,
+                                               g.rank, g.a, g.k, nullptr, s.A, s.B);
             if (rc != HSES_OK) return rc;
         }
         ep.A = fa;

@@ -534,7 +534,7 @@ int64_t chunk_pairs_of(const hses_linear_args& g, int64_t pairs) {
 bool pair_path_fuses_scan(const hses_linear_args& g) { return g.potentials == nullptr && scan_fits(rmax_of(g), g); }
 
 bool pair_path_supports(const hses_linear_args& g) {
-    if (!g.perturb) return false;
+    if (!g.perturb || g.factor_order != 0) return false;
     if (g.rank % 8 != 0 || g.rank > PP_THREADS || g.k % 4 != 0) return false;
     if ((int64_t)2 * g.bm * g.t_steps > 32) return false;
     if (g.first_thread % 2 != 0 || g.n_pop % 2 != 0) return false;

@@ -157,7 +157,7 @@ size_t up256s(size_t v) { return (v + 255) / 256 * 256; }
 }  // namespace
 
 bool small_path_supports(const hses_linear_args& g) {
-    if (!g.perturb || g.lif == 2) return false;
+    if (!g.perturb || g.lif == 2 || g.factor_order != 0) return false;
     if (g.k > SP_MAXK || g.a > SP_MAXA || g.rank > SP_MAXR) return false;
     if (g.first_thread % 2 != 0 || g.n_pop % 2 != 0) return false;
     // without a cache all factors of the call go to scratch at once

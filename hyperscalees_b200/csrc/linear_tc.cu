@@ -23,6 +23,7 @@
 // records a code in the context's status word, all roles leave their loops, TMEM is released
 // and the kernel returns.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "linear.cuh"
@@ -66,7 +67,10 @@ struct TcArgs {
     int bm;
     int64_t n_pop;
     int perturb, lif;
-    int rank;
+    int rank;        // columns of t and of a staged A row: the factor rank rounded up to a multiple of 4
+    int rank_true;   // the factor rank itself (1, 2, 3, or equal to rank)
+    int one_pass;    // 1: operands rounded to bf16, a single MMA pass (no hi/lo split)
+    int row_a0;      // first row of the output-side factor in a member's (a+k, rank) stream block
     uint64_t key;
     int32_t true_epoch, first_thread;
     float base_sigma, leak, v_th, out_scale;
@@ -182,7 +186,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             bool ok = true;
             // inputs that are exact in fp16 (0/1 spikes, small integers) have an all-zero lo half:
             // its tiles are neither loaded nor multiplied
-            const bool skip_xlo = *g.x_lo_flag == 0;
+            const bool skip_xlo = g.one_pass || *g.x_lo_flag == 0;
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c) {
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -190,11 +194,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         uint32_t ph = (it / S::STAGES) & 1;
                         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
                         uint8_t* st = stage_base + s * S::STAGE_BYTES;
-                        mbar_expect_tx(&full[s], (skip_xlo ? 1 : 2) * S::X_BYTES + 2 * S::W_BYTES);
+                        mbar_expect_tx(&full[s], (skip_xlo ? 1 : 2) * S::X_BYTES + (g.one_pass ? 1 : 2) * S::W_BYTES);
                         tma_load_2d(st, &tm_xhi, kb * BK, mt * BM_TILE, &full[s]);
                         if (!skip_xlo) tma_load_2d(st + S::X_BYTES, &tm_xlo, kb * BK, mt * BM_TILE, &full[s]);
                         tma_load_2d(st + 2 * S::X_BYTES, &tm_whi, kb * BK, c * BN, &full[s]);
-                        tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
+                        if (!g.one_pass) tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
                     }
                 }
             }
@@ -211,10 +215,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     } else if (warp == 1) {
         // --------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(BN);
+            const uint32_t idesc = g.one_pass ? make_idesc_bf16(BN) : make_idesc(BN);
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
-            const bool skip_xlo = *g.x_lo_flag == 0;
+            const bool skip_xlo = g.one_pass || *g.x_lo_flag == 0;
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c, ++acc_it) {
                     int b = acc_it & 1;
@@ -233,6 +237,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 #pragma unroll
                         for (int ks = 0; ks < BK / 16; ++ks) {
                             uint64_t off = (uint64_t)(ks * 32 >> 4);  // 16 fp16 = 32 B along K
+                            if (g.one_pass) {
+                                umma_f16(d, dxh + off, dwh + off, idesc, (kb | ks) != 0);
+                                continue;
+                            }
                             if (!skip_xlo) umma_f16(d, dxl + off, dwh + off, idesc, (kb | ks) != 0);
                             umma_f16(d, dxh + off, dwl + off, idesc, skip_xlo ? (uint32_t)((kb | ks) != 0) : 1u);
                             umma_f16(d, dxh + off, dwh + off, idesc, 1);
@@ -367,6 +375,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         cal.log_tab = log_tab_s;
         cal.log_delta = reinterpret_cast<const uint32_t*>(log_tab_s + 64);                         // byte tables, see
         cal.cos_delta = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(log_tab_s + 64) + 256);  // next_normals4_t<true>
+        LibmCal cal4 = g.cal;      // the one-at-a-time generator of ranks 1..3 reads the 32-bit thresholds
+        cal4.log_tab = log_tab_s;
         const int items_per_tile = g.a / IT::ROWS;
         const int n_local = lane % IT::ROWS, qoff = (lane / IT::ROWS) * IT::NPL;   // this lane's row and first rank index
         float* const lane_a = a_stage + (size_t)gq * depth * IT::SLOT_FLOATS + (lane / IT::ROWS) * IT::ROWS + n_local;
@@ -381,21 +391,27 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             // always written by the same warp.  it0: its first item inside this tile.
             const int it0 = (int)(((uint32_t)gi + (uint32_t)GENS - (tile_no * (uint32_t)items_per_tile) % (uint32_t)GENS) % (uint32_t)GENS);
             // cached factors: this lane's share of row (item * ROWS + n_local) of the pair, raw normals
-            const float* src = g.cache_a ? g.cache_a + ((size_t)(pair - g.first_thread / 2) * g.a + it0 * IT::ROWS + n_local) * RANK + qoff
+            // (ranks 1..3 run as rank 4 with zero columns: rt values per row in the stream and in a cache)
+            const int rt = g.rank_true;
+            const float* src = g.cache_a ? g.cache_a + ((size_t)(pair - g.first_thread / 2) * g.a + it0 * IT::ROWS + n_local) * rt + qoff
                                          : nullptr;
             uint64_t a_state = 0;
             if (!src) {
                 uint64_t s0 = noise_seed(g.key, g.true_epoch, pair) | 1ull;
-                a_state = jump_by(g.pow2, s0, 2ull * ((uint64_t)RANK * (uint64_t)(g.k + it0 * IT::ROWS + n_local) + (uint64_t)qoff));
+                a_state = jump_by(g.pow2, s0, 2ull * ((uint64_t)rt * (uint64_t)(g.row_a0 + it0 * IT::ROWS + n_local) + (uint64_t)qoff));
             }
             for (int it = it0; it < items_per_tile; it += GENS) {
                 const uint32_t item = tile_no * (uint32_t)items_per_tile + (uint32_t)it;
                 const int slot = (int)(item % (uint32_t)depth);
                 float4 v[IT::NPL / 4];
                 if (src) {   // the loads fly while the slot is waited for
+                    if (rt < 4) {
+                        v[0] = make_float4(__ldg(src), rt > 1 ? __ldg(src + 1) : 0.0f, rt > 2 ? __ldg(src + 2) : 0.0f, 0.0f);
+                    } else {
 #pragma unroll
-                    for (int c4 = 0; c4 < IT::NPL / 4; ++c4) v[c4] = __ldg(reinterpret_cast<const float4*>(src) + c4);
-                    src += (size_t)GENS * IT::ROWS * RANK;
+                        for (int c4 = 0; c4 < IT::NPL / 4; ++c4) v[c4] = __ldg(reinterpret_cast<const float4*>(src) + c4);
+                    }
+                    src += (size_t)GENS * IT::ROWS * rt;
                 }
                 if (!mbar_wait(&aempty[gq * MAX_DEPTH + slot], ((item / (uint32_t)depth) & 1) ^ 1, abort_flag, g.status, 8)) {
                     ok = false;
@@ -407,6 +423,11 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     float z[4];
                     if (src) {
                         z[0] = v[c4].x; z[1] = v[c4].y; z[2] = v[c4].z; z[3] = v[c4].w;
+                    } else if (rt < 4) {
+                        z[1] = z[2] = z[3] = 0.0f;
+                        z[0] = next_normal(a_state, cal4);
+                        if (rt > 1) z[1] = next_normal(a_state, cal4);
+                        if (rt > 2) z[2] = next_normal(a_state, cal4);
                     } else {
                         next_normals4_t<true>(a_state, cal, z);
                     }
@@ -434,14 +455,25 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 // (hi*hi + hi*lo + lo*hi, fp32 accumulate) give fp32-equivalent products at the fp16 tensor
 // rate and with half the shared-memory traffic of a TF32 split.  The scales are undone exactly
 // in the epilogue.  One warp per row; rows are multiples of four long and 16-byte aligned.
+// bf16 != 0: one-pass mode, hi = bf16(v) with no scale and no lo half (bf16 has the range of fp32).
 __global__ void split_f16_rows_kernel(const float* __restrict__ x, int64_t rows, int k, int64_t stride,
                                       __half* __restrict__ hi, __half* __restrict__ lo,
-                                      float* __restrict__ inv_scale, int* __restrict__ lo_flag) {
+                                      float* __restrict__ inv_scale, int* __restrict__ lo_flag, int bf16) {
     int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (r >= rows) return;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)r * stride);
     int n4 = k >> 2;
+    if (bf16) {
+        if (lane == 0) inv_scale[r] = 1.0f;
+        uint2* dh = reinterpret_cast<uint2*>(hi + (size_t)r * k);
+        for (int i = lane; i < n4; i += 32) {
+            const float4 v = src[i];
+            const __nv_bfloat162 b01 = __floats2bfloat162_rn(v.x, v.y), b23 = __floats2bfloat162_rn(v.z, v.w);
+            dh[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&b01), *reinterpret_cast<const uint32_t*>(&b23));
+        }
+        return;
+    }
     float m = 0.0f;
     for (int i = lane; i < n4; i += 32) {
         float4 v = src[i];
@@ -505,7 +537,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                  uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
                  int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                  __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
-                 const float* __restrict__ cache_b, int* __restrict__ lo_flag) {
+                 const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true, int row_b0) {
     constexpr int RANK = RANK_G * 4;
     constexpr int KQ = 32 / RANK_G;   // lanes along k
     constexpr int KSTEP = 4 * KQ;     // k covered by one pass of a warp
@@ -553,10 +585,17 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         if (ex <= -127 || ex >= 128) e = 0;
         if (e > 100) e = 100;
         if (e < -100) e = -100;
+        if (bf16) e = 0;   // one-pass mode: no scale
         sc = __uint_as_float((uint32_t)(127 + e) << 23);
         if (lane == 0) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
     };
     auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
+        if (bf16) {   // hi = bf16(v), the lo half is neither written nor read
+            const __nv_bfloat162 b01 = __floats2bfloat162_rn(v.x, v.y), b23 = __floats2bfloat162_rn(v.z, v.w);
+            h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&b01), *reinterpret_cast<const uint32_t*>(&b23));
+            l2 = make_uint2(0u, 0u);
+            return;
+        }
         const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
         const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
         const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
@@ -601,11 +640,11 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                     uint2 h2, l2;
                     split4(v0[j], sc0, h2, l2);
                     dh0[i] = h2;
-                    dl0[i] = l2;
+                    if (!bf16) dl0[i] = l2;
                     if (two) {
                         split4(v1[j], sc1, h2, l2);
                         dh1[i] = h2;
-                        dl1[i] = l2;
+                        if (!bf16) dl1[i] = l2;
                     }
                 }
             }
@@ -627,7 +666,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                 uint2 h2, l2;
                 split4(src[i], sc, h2, l2);
                 dh[i] = h2;
-                dl[i] = l2;
+                if (!bf16) dl[i] = l2;
             }
         }
     }
@@ -653,16 +692,25 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     uint64_t sb = 0;
     if (!cache_b) {
         sb = noise_seed(key, true_epoch, pair) | 1ull;
-        sb = jump_by(pow2, sb, 2ull * (uint64_t)RANK * (uint64_t)tid);
+        sb = jump_by(pow2, sb, 2ull * (uint64_t)rank_true * (uint64_t)(row_b0 + tid));   // row_b0: first input-side row
     }
     // cached raw B rows of this pair, (k, rank) row-major like the block in shared memory
+    // (ranks 1..3: rank_true values per row, the remaining columns of the block are zero)
     const float4* cb4 = cache_b ? reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK) : nullptr;
+    const float* cb1 = cache_b ? cache_b + (size_t)blockIdx.x * k * rank_true : nullptr;
     for (int k0 = 0; k0 < k; k0 += LT_KB) {
         const int kn = k - k0 < LT_KB ? k - k0 : LT_KB;  // multiple of 4
         // Row k of the block is stored at row perm(k): inside every group of KSTEP rows the rows
         // with the same k mod 4 are made neighbours, so that the lanes of a warp — which own four
         // consecutive k each — read one contiguous 512-byte stretch per load (no bank conflicts).
-        if (cb4) {
+        if (cb4 && rank_true < 4) {
+            for (int kr = tid; kr < kn; kr += LT_THREADS) {
+                const int pr = (kr / KSTEP) * KSTEP + (kr & 3) * KQ + ((kr % KSTEP) >> 2);
+                const float* row = cb1 + (size_t)(k0 + kr) * rank_true;
+                reinterpret_cast<float4*>(bs)[pr] = make_float4(__ldg(row), rank_true > 1 ? __ldg(row + 1) : 0.0f,
+                                                               rank_true > 2 ? __ldg(row + 2) : 0.0f, 0.0f);
+            }
+        } else if (cb4) {
             for (int i = tid; i < kn * RANK_G; i += LT_THREADS) {
                 const int kr = i / RANK_G, c = i - kr * RANK_G;
                 const int pr = (kr / KSTEP) * KSTEP + (kr & 3) * KQ + ((kr % KSTEP) >> 2);
@@ -670,11 +718,19 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
             }
         } else if (tid < kn) {
             const int pr = (tid / KSTEP) * KSTEP + (tid & 3) * KQ + ((tid % KSTEP) >> 2);
+            if (rank_true < 4) {
+                float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                z[0] = next_normal(sb, cal);
+                if (rank_true > 1) z[1] = next_normal(sb, cal);
+                if (rank_true > 2) z[2] = next_normal(sb, cal);
+                *reinterpret_cast<float4*>(bs + pr * RANK) = make_float4(z[0], z[1], z[2], z[3]);
+            } else {
 #pragma unroll 1
-            for (int q = 0; q < RANK; q += 4) {
-                float z[4];
-                next_normals4(sb, cal, z);
-                *reinterpret_cast<float4*>(bs + pr * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
+                for (int q = 0; q < RANK; q += 4) {
+                    float z[4];
+                    next_normals4(sb, cal, z);
+                    *reinterpret_cast<float4*>(bs + pr * RANK + q) = make_float4(z[0], z[1], z[2], z[3]);
+                }
             }
             sb = jump_apply(hop_s, sb);
         }
@@ -760,7 +816,7 @@ TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     auto up = [](size_t v) { return (v + 63) / 64 * 64; };
     size_t rows = (size_t)g.t_steps * g.n_pop * g.bm;
     size_t nw = up((size_t)g.a * g.k), nx = up(rows * g.k);   // fp16 elements
-    size_t nt = g.perturb ? up(rows * g.rank) : 0;             // floats
+    size_t nt = g.perturb ? up(rows * (size_t)((g.rank + 3) / 4 * 4)) : 0;   // floats: t has the padded rank
     TcScratch s;
     s.xhi = reinterpret_cast<__half*>(base);
     s.xlo = s.xhi + nx;
@@ -806,7 +862,8 @@ int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const T
         HSES_REQUIRE(ta.gens > 0, "linear_tc: the ring of staged factor rows does not fit in shared memory");
         const uint64_t* hop = nullptr;
         // from the end of a lane's share of one item to the start of its share of the warp's next item
-        int hrc = get_hop_table(ctx, 2ull * ((uint64_t)g.rank * item_rows(g.rank) * ta.gens - item_normals_per_lane(g.rank)), &hop);
+        const uint64_t per_lane = ta.rank_true < 4 ? (uint64_t)ta.rank_true : (uint64_t)item_normals_per_lane(ta.rank);
+        int hrc = get_hop_table(ctx, 2ull * ((uint64_t)ta.rank_true * item_rows(ta.rank) * ta.gens - per_lane), &hop);
         if (hrc != HSES_OK) return hrc;
         ta.hop = hop;
     }
@@ -844,7 +901,8 @@ bool tensor_path_supports(const hses_linear_args& g) {
     if (!aligned16(g.x) || !aligned16(g.param) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
     if (g.k > (1 << 20) || g.a > (1 << 20)) return false;
     if (g.perturb) {
-        if (g.rank != 4 && g.rank != 8 && g.rank != 16 && g.rank != 32) return false;
+        if (g.rank != 1 && g.rank != 2 && g.rank != 3 && g.rank != 4 && g.rank != 8 && g.rank != 16 && g.rank != 32)
+            return false;
         // every 32-row slice of a tile must belong to one antithetic pair
         bool pair_rows = (g.bm % 32 == 0) || (g.bm == 16 && g.first_thread % 2 == 0 && g.n_pop % 2 == 0);
         if (!pair_rows) return false;
@@ -859,17 +917,18 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     HSES_REQUIRE(g.workspace != nullptr && g.workspace_bytes >= sc.bytes && aligned16(g.workspace),
                  "workspace too small or misaligned; see hses_perturbed_linear_workspace_bytes");
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
+    const int one_pass = g.precision == HSES_PRECISION_BF16 ? 1 : 0;
     HSES_CUDA(cudaMemsetAsync(sc.lo_flag, 0, sizeof(int), st));
     {
         HSES_KERNEL(ctx, st, "split_w");
         split_f16_rows_kernel<<<(unsigned)((g.a + 7) / 8), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
-                                                                        sc.whi, sc.wlo, sc.cs, nullptr);
+                                                                        sc.whi, sc.wlo, sc.cs, nullptr, one_pass);
         HSES_LAUNCH_CHECK();
     }
     if (!g.perturb) {  // with noise the pair kernel below splits x while it computes t
         HSES_KERNEL(ctx, st, "split_x");
         split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
-                                                                         sc.xlo, sc.rs, sc.lo_flag);
+                                                                         sc.xlo, sc.rs, sc.lo_flag, one_pass);
         HSES_LAUNCH_CHECK();
     }
     TcArgs ta{};
@@ -880,7 +939,10 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.n_pop = g.n_pop;
     ta.perturb = g.perturb;
     ta.lif = g.lif;
-    ta.rank = g.perturb ? g.rank : 0;
+    ta.rank = g.perturb ? (g.rank + 3) / 4 * 4 : 0;
+    ta.rank_true = g.perturb ? g.rank : 0;
+    ta.one_pass = one_pass;
+    ta.row_a0 = g.factor_order == 1 ? 0 : g.k;
     ta.key = g.key;
     ta.true_epoch = true_epoch_of(g.epoch, g.noise_reuse);
     ta.first_thread = g.first_thread;
@@ -908,16 +970,16 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.x_lo_flag = sc.lo_flag;
     if (g.perturb) {
         const uint64_t* hop127 = nullptr;
-        int rc = get_hop_table(ctx, 2ull * g.rank * (LT_KB - 1), &hop127);
+        int rc = get_hop_table(ctx, 2ull * g.rank * (LT_KB - 1), &hop127);   // rank values per row in the stream
         if (rc != HSES_OK) return rc;
         int64_t pairs = (g.first_thread + g.n_pop - 1) / 2 - g.first_thread / 2 + 1;
         HSES_KERNEL(ctx, st, "lowrank_t");
 #define HSES_LT(RG)                                                                                          \
     lowrank_t_kernel<RG><<<lt_grid, LT_THREADS, 0, st>>>(                                            \
         ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
-        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag)
+        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
-        switch (g.rank / 4) {
+        switch ((g.rank + 3) / 4) {
             case 1: HSES_LT(1); break;
             case 2: HSES_LT(2); break;
             case 4: HSES_LT(4); break;

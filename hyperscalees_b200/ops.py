@@ -188,7 +188,8 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      lif: bool = False, tau_m: float = 20.0, v_th: float = 0.3,
                      reset_mode: int = RESET_HARD, out_scale: float = 1.0,
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
-                     algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None):
+                     algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None, precision: int = 0,
+                     tmm: bool = False):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
     the charged potentials.  With `cache` the factors are read from it instead of
@@ -219,6 +220,8 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.out, g.out_row_stride = out.data_ptr(), out.stride(0) if rows > 1 else max(out.stride(0), a)
     g.potentials = pot.data_ptr() if pot is not None else None
     g.algo = algo
+    g.precision = precision
+    g.factor_order = int(tmm)   # do_Tmm: param is the reference's (in, out) matrix transposed
     if cache is not None:
         g.cache = C.pointer(cache.desc)
     L = _lib.load()
@@ -277,6 +280,7 @@ def convert_fitnesses(raw: torch.Tensor, group_size: int = 0, want_stats: bool =
 
 
 UPDATE_GRAD, UPDATE_RAW_ACC = 0, 1
+PRECISION_FP32, PRECISION_BF16 = 0, 1
 
 
 class FactorCache:

@@ -49,6 +49,7 @@ enum hses_factor_layout {
     HSES_LAYOUT_NRA = 1  /* A (n,r,a), B (n,r,b): batched forward / einsum layout, snn.rs:472-476 */
 };
 enum hses_linear_algo { HSES_ALGO_AUTO = 0, HSES_ALGO_SIMT = 1, HSES_ALGO_TENSOR = 2, HSES_ALGO_PAIR = 3 };
+enum hses_precision { HSES_PRECISION_FP32 = 0, HSES_PRECISION_BF16 = 1 };
 
 const char* hses_last_error(void);
 int hses_version(void);
@@ -206,6 +207,19 @@ typedef struct {
     size_t workspace_bytes;
     const hses_factor_cache* cache; /* host pointer or NULL: take the factors from this cache
                                        instead of regenerating them (same results, bit for bit) */
+    int32_t precision; /* hses_precision of the base product x·paramᵀ: FP32 (default) keeps products
+                          fp32-equivalent (three fp16 passes on hi/lo halves); BF16 rounds x and param
+                          to bf16 and multiplies once with fp32 accumulation — the arithmetic of a
+                          model held in bf16 (the RWKV LM).  The rank-r term is fp32 in both.  Only the
+                          tensor-core path has the BF16 form; with HSES_ALGO_AUTO a shape it does not
+                          cover is computed in fp32 */
+    int32_t factor_order; /* 0: do_mm, the parameter is (a = out, k = in) and the factor rows of the
+                             input side come first in the member's stream (eggroll.rs:86-103, 419-446).
+                             1: do_Tmm (eggroll.rs:450-477): the reference parameter is stored (in, out)
+                             and its factor block puts the `out` rows first, then the `in` rows scaled by
+                             sign*sigma/sqrt(rank); `param` is still handed over as (a = out, k = in), i.e.
+                             transposed, and the call returns x·param_refᵀᵀ + (x·A)·Bᵀ.  Not combinable
+                             with a factor cache */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

@@ -150,3 +150,69 @@ def test_tensor_path_with_inputs_exact_in_fp16(hs, oracle, perturb):
         scale = max(ref.abs().max().item(), 1.0)
         assert (got - ref).abs().max().item() <= 2e-5 * scale
     status_ok()
+
+
+@pytest.mark.parametrize("rank", [1, 2, 3])
+@pytest.mark.parametrize("cached", [False, True])
+def test_tensor_path_small_ranks(hs, oracle, rank, cached):
+    """Ranks 1..3 run on the tensor-core path as rank 4 with zero columns: same stream positions
+    (rank values per row), same results as the CPU restatement."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(rank)
+    n_pop, bm, k, a, sigma = 6, 64, 192, 256, 0.3
+    x = g.standard_normal((n_pop, bm, k)).astype(np.float32)
+    w = g.standard_normal((a, k)).astype(np.float32)
+    cache = ops.FactorCache(KEY, 0, 0, rank, a, k, n_pairs=n_pop // 2, first_pair=1) if cached else None
+    got = ops.perturbed_linear(torch.as_tensor(x, device="cuda"), torch.as_tensor(w, device="cuda"), n_pop=n_pop,
+                               bm=bm, sigma=sigma, rank=rank, key=KEY, first_thread=2, algo=ops.ALGO_TENSOR,
+                               cache=cache).cpu().numpy().reshape(n_pop, bm, a)
+    for i in range(n_pop):
+        want = oracle.do_mm(x[i], w, sigma, rank, KEY, (0, 2 + i), acc64=True)
+        assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("rank,perturb", [(1, True), (16, True), (4, False)])
+def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb):
+    """precision = BF16: x and the parameter rounded to bf16, one pass, fp32 accumulation; the
+    rank-r term stays fp32.  Compared with the CPU product of the rounded operands plus the CPU
+    rank-r term."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(10 + rank)
+    n_pop, bm, k, a, sigma = 4, 64, 256, 384, 0.2
+    x = g.standard_normal((n_pop, bm, k)).astype(np.float32)
+    w = (g.standard_normal((a, k)) * 0.02).astype(np.float32)
+    rb = lambda v: torch.as_tensor(v).to(torch.bfloat16).to(torch.float32).numpy()
+    got = ops.perturbed_linear(torch.as_tensor(x, device="cuda"), torch.as_tensor(w, device="cuda"), n_pop=n_pop,
+                               bm=bm, sigma=sigma, rank=rank, key=KEY, perturb=perturb, algo=ops.ALGO_TENSOR,
+                               precision=ops.PRECISION_BF16).cpu().numpy().reshape(n_pop, bm, a)
+    for i in range(n_pop):
+        want = oracle.do_mm(rb(x[i]), rb(w), sigma, rank, KEY, None, acc64=True)
+        if perturb:
+            want = want + (oracle.do_mm(x[i], w, sigma, rank, KEY, (0, i), acc64=True) -
+                           oracle.do_mm(x[i], w, sigma, rank, KEY, None, acc64=True))
+        assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    # the fp32-equivalent mode differs from it by the bf16 rounding of the operands, nothing like 2e-5
+    full = ops.perturbed_linear(torch.as_tensor(x, device="cuda"), torch.as_tensor(w, device="cuda"), n_pop=n_pop,
+                                bm=bm, sigma=sigma, rank=rank, key=KEY, perturb=perturb,
+                                algo=ops.ALGO_TENSOR).cpu().numpy().reshape(n_pop, bm, a)
+    assert np.abs(full - got).max() > 1e-4 * np.abs(full).max()
+
+
+@pytest.mark.parametrize("algo_name,k,a,rank", [("TENSOR", 64, 256, 1), ("TENSOR", 192, 128, 4), ("SIMT", 96, 40, 1),
+                                                ("SIMT", 64, 32, 3)])
+def test_tmm_factor_order(hs, oracle, algo_name, k, a, rank):
+    """do_Tmm (eggroll.rs:450-477): x @ param + (x·A)·Bᵀ for a parameter stored (in, out), whose
+    factor block has the `out` rows first; the call takes the parameter transposed."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(k + a)
+    n_pop, bm, sigma = 4, 64, 0.25
+    x = g.standard_normal((n_pop, bm, k)).astype(np.float32)
+    p_ref = g.standard_normal((k, a)).astype(np.float32)          # (in, out)
+    got = ops.perturbed_linear(torch.as_tensor(x, device="cuda"), torch.as_tensor(p_ref.T.copy(), device="cuda"),
+                               n_pop=n_pop, bm=bm, sigma=sigma, rank=rank, key=KEY, first_thread=6, tmm=True,
+                               algo=getattr(ops, "ALGO_" + algo_name)).cpu().numpy().reshape(n_pop, bm, a)
+    bs = float(np.float32(sigma) / np.sqrt(np.float32(rank)))
+    for i in range(n_pop):
+        A, B = oracle.lora_params(bs, KEY, rank, 0, 6 + i, k, a, 0)      # A (in, r) scaled, B (out, r)
+        want = x[i].astype(np.float64) @ p_ref.astype(np.float64) + (x[i].astype(np.float64) @ A.astype(np.float64)) @ B.astype(np.float64).T
+        assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
