@@ -20,7 +20,9 @@ The same JSON line carries two more blocks, measured after the headline:
   streaming        the HBM-bound kernels of the path (encode, LIF scan, attention, WKV-7), each
                    timed alone against the measured copy bandwidth;
   spiking_lm       (one GPU) the token-level spiking transformer at 4096 members x 32 sequences:
-                   ms per fitness evaluation of the whole population.
+                   ms per fitness evaluation of the whole population;
+  rwkv_lm          the 12-layer RWKV-7 LM (d_model 768, vocab 50 277, context 256) evaluated by 1024
+                   members with rank-1 noise, bf16 products, the population split over the N ranks.
 
     python bench.py --gpus N --steps K --warmup W            # the CUDA path
     python bench.py --impl reference --gpus N --steps K ...   # CPU restatement of the reference
@@ -282,7 +284,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                   "note": "factors read from a device cache built once outside the timed region"}
         del cache
     # ---- the two extra blocks of the line (see the module docstring) ----
-    pop_block, stream_block, lm_block = None, None, None
+    pop_block, stream_block, lm_block, rwkv_block = None, None, None, None
     if not args.kernel_only and not args.headline_only:
         del x_dev, out_dev, pipe
         torch.cuda.empty_cache()
@@ -303,6 +305,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
             stream_block = streaming_block(dev, ctx, args.steps, args.warmup,
                                            only=("poisson_encode", "lif_scan", "spiking_attention mode 0", "wkv7"))
             lm_block = spiking_lm_block(dev, ctx, 4096, 32, args.steps, args.warmup)
+        rwkv_block = rwkv_lm_block(rank, world, dev, ctx, comm, 1024, args.steps, args.warmup)
         if comm is not None:
             comm.destroy()
     clocks = sampler.stop() if sampler else None
@@ -348,7 +351,8 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                 "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                         "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
                 "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached,
-                "population_step": pop_block, "streaming": stream_block, "spiking_lm": lm_block}
+                "population_step": pop_block, "streaming": stream_block, "spiking_lm": lm_block,
+                "rwkv_lm": rwkv_block}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -721,6 +725,98 @@ def run_spiking_lm(args, local_rank: int):
                       "config": {"workload": blk["workload"]}, "spiking_lm": blk, "clocks": sampler.stop()}), flush=True)
 
 
+def rwkv_lm_block(rank: int, world: int, dev, ctx, comm, n_pop: int, steps: int, warmup: int,
+                  chunk_members: int = 128):
+    """BASELINE's RWKV-style LM: 12 layers, d_model 768, vocab 50 277, context 256, bf16 weights
+    N(0, 0.02) with fp32 state and accumulation, rank-1 noise on every block matrix, one sequence of
+    uniform token ids per member; one step = the mean next-token log-likelihood of every member,
+    the population split over the ranks (strong scaling) and the fitness vector all-gathered."""
+    import torch
+    import torch.distributed as dist
+    from hyperscalees_b200 import parallel
+    from hyperscalees_b200.rwkv_lm import LmNoise, RwkvLM
+
+    n_layer, d, vocab, T = 12, 768, 50277, 256
+    model = RwkvLM(n_layer, d, vocab, head_size=64, device=dev, seed=4)
+    lo, hi = parallel.shard_range(n_pop, rank, world)
+    g = torch.Generator(device="cpu").manual_seed(4)
+    ids = torch.randint(0, vocab, (n_pop, T), generator=g, dtype=torch.int32)[lo:hi].to(dev)
+    noise = LmNoise(0.02, 1, first_thread=lo)
+
+    def step():
+        raw = model.fitness(ids, noise, chunk_members=chunk_members)
+        return parallel.allgather_fitness(raw, n_pop, comm=comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        fit = step()
+    barrier()
+    steps = max(2, min(steps, 3))
+    ctx.profile_enable(False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fit = step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    barrier()
+    launches = sum(v[0] for v in ctx.profile_read().values()) / steps
+    ctx.profile_enable(True)
+    step()
+    torch.cuda.synchronize()
+    prof = {k: v for k, v in ctx.profile_read().items() if v[0]}
+    ctx.profile_enable(False)
+    ms = float(ms.item())
+    # products of one step: 2 * rows * (sum of the block matrices' sizes * layers + head)
+    per_layer = 4 * d * d + 2 * 4 * d * d + 2 * d * (64 + 32 + 64 + 128)
+    flops = 2.0 * n_pop * T * (n_layer * per_layer + d * vocab)
+    peaks = measured_peaks()
+    blk = {"workload": f"RWKV-7 LM: {n_layer} layers, d_model {d}, vocab {vocab}, context {T}, {n_pop} members x 1 sequence, "
+                       f"bf16 products with fp32 accumulation, rank-1 noise, sigma 0.02; chunks of {chunk_members} members",
+           "n_gpus": world, "scaling": "strong", "ms_per_step": ms, "member_evals_per_sec": n_pop / (ms * 1e-3),
+           "tokens_per_sec": n_pop * T / (ms * 1e-3), "product_tflops": flops / (ms * 1e-3) / 1e12,
+           "frac_of_measured_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+           "gpu_launches_per_step": launches,
+           "kernel_ms_per_step": {k: round(v[1], 3) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
+           "fitness_finite": bool(torch.isfinite(fit).all().item()), "fitness_mean": float(fit.mean().item()),
+           "device_status": ctx.device_status()}
+    del model
+    torch.cuda.empty_cache()
+    return blk
+
+
+def run_rwkv_lm(args, rank: int, local_rank: int, world: int):
+    """--workload rwkv_lm: the block above alone."""
+    import torch
+    import torch.distributed as dist
+    from hyperscalees_b200 import core
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = core.get_context(local_rank)
+    comm = make_comm(ctx, world)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    blk = rwkv_lm_block(rank, world, dev, ctx, comm, args.n_pop, args.steps, args.warmup, args.chunk)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": blk["member_evals_per_sec"], "unit": UNIT, "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": blk["ms_per_step"],
+                          "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": blk["workload"]}, "rwkv_lm": blk, "clocks": sampler.stop()}), flush=True)
+    if comm is not None:
+        comm.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_snn_transformer(args, local_rank: int):
     """Secondary workload: forward_batched of the SNN-rate transformer (d_model 64, 4 heads, 2 blocks,
     16 tokens of 49 inputs, T = 4 encoding steps) over a chunk of --n-pop members with rank-8 noise;
@@ -771,7 +867,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer", "spiking_lm"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer", "spiking_lm", "rwkv_lm"],
                     help="microbench: the perturbed-linear layer the metric is quoted on (default); "
                          "population_step: a full ES step of the spiking MLP (secondary figure); "
                          "streaming_kernels: the HBM-bound kernels of the path, each timed alone; "
@@ -810,6 +906,8 @@ def main():
     elif args.workload == "spiking_lm":
         if rank == 0:
             run_spiking_lm(args, local_rank)
+    elif args.workload == "rwkv_lm":
+        run_rwkv_lm(args, rank, local_rank, world)
     else:
         run_ours(args, rank, local_rank, world)
 
