@@ -19,7 +19,7 @@ EXPORTS = [
     "hses_last_error", "hses_version", "hses_ctx_create", "hses_ctx_destroy",
     "hses_ctx_calibration_info", "hses_ctx_device_status", "hses_profile_enable", "hses_profile_count", "hses_profile_read",
     "hses_noise_seed", "hses_normal_fill", "hses_lora_factors",
-    "hses_dense_noise", "hses_poisson_encode", "hses_lif_scan",
+    "hses_dense_noise", "hses_poisson_encode", "hses_poisson_encode_dual", "hses_lif_scan",
     "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
     "hses_member_mean", "hses_convert_fitnesses", "hses_es_update_workspace_bytes",
     "hses_es_update", "hses_es_update_static_scratch_bytes", "hses_es_update_static",
@@ -62,7 +62,7 @@ class LinearArgs(C.Structure):
         ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("cache", C.POINTER(FactorCacheDesc)), ("precision", C.c_int32),
-        ("factor_order", C.c_int32),
+        ("factor_order", C.c_int32), ("x_half", C.c_void_p),
     ]
 
 
@@ -121,6 +121,7 @@ def load():
     L.hses_lora_factors.argtypes = [vp, vp, u64, i32, i32, vp, i32, i64, i32, i32, i32, f32, i32, vp, vp]
     L.hses_dense_noise.argtypes = [vp, vp, u64, i32, i32, vp, i32, i64, i32, i32, f32, vp]
     L.hses_poisson_encode.argtypes = [vp, vp, vp, i64, i32, i64, i32, C.POINTER(C.c_uint32), vp]
+    L.hses_poisson_encode_dual.argtypes = [vp, vp, vp, i64, i32, i64, i32, C.POINTER(C.c_uint32), vp, vp]
     L.hses_lif_scan.argtypes = [vp, vp, vp, i32, i64, i32, i64, vp, f32, f32, i32, vp]
     L.hses_perturbed_linear_workspace_bytes.restype = sz
     L.hses_perturbed_linear_workspace_bytes.argtypes = [C.POINTER(LinearArgs)]

@@ -1,5 +1,7 @@
 // HBM-bound elementwise kernels: Poisson encode, LIF scan, fitness, z-score,
 // solver step.  All of them stream their operands once; rows are pitched.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace hses {
@@ -32,9 +34,12 @@ __device__ __forceinline__ uint32_t xs32(uint32_t x) {
     return x;
 }
 
+// out_half (optional, dense rows of in_dim values): the same spikes as fp16 0/1, the operand
+// format of the tensor-core layer that follows, so that it need not convert them itself.
 template <int VEC>
 __global__ void poisson_kernel(const float* __restrict__ probs, int64_t batch, int in_dim,
-                               int64_t stride, int T, uint32_t mix, float* __restrict__ out) {
+                               int64_t stride, int T, uint32_t mix, float* __restrict__ out,
+                               __half* __restrict__ out_half) {
     int64_t vec_per_row = in_dim / VEC;
     int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= batch * vec_per_row) return;
@@ -67,6 +72,17 @@ __global__ void poisson_kernel(const float* __restrict__ probs, int64_t batch, i
             __stcs(reinterpret_cast<float4*>(dst), make_float4(s[0], s[1], s[2], s[3]));
         else
             dst[0] = s[0];
+        if (out_half) {
+            __half* dh = out_half + ((size_t)t * batch + row) * in_dim + col;
+            if constexpr (VEC == 4) {
+                // 1.0 in fp16 is 0x3C00
+                const uint32_t lo = (s[0] != 0.0f ? 0x3C00u : 0u) | (s[1] != 0.0f ? 0x3C000000u : 0u);
+                const uint32_t hi = (s[2] != 0.0f ? 0x3C00u : 0u) | (s[3] != 0.0f ? 0x3C000000u : 0u);
+                *reinterpret_cast<uint2*>(dh) = make_uint2(lo, hi);
+            } else {
+                dh[0] = __float2half_rn(s[0]);
+            }
+        }
     }
 }
 
@@ -398,7 +414,15 @@ int hses_prng_normal_half(hses_ctx* ctx, hses_stream stream, float* out, int64_t
 int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs, int64_t batch,
                         int32_t in_dim, int64_t row_stride, int32_t T, const uint32_t seeds[4],
                         float* out) {
+    return hses_poisson_encode_dual(ctx, stream, probs, batch, in_dim, row_stride, T, seeds, out, nullptr);
+}
+
+int hses_poisson_encode_dual(hses_ctx* ctx, hses_stream stream, const float* probs, int64_t batch,
+                             int32_t in_dim, int64_t row_stride, int32_t T, const uint32_t seeds[4],
+                             float* out, void* out_half) {
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(out_half == nullptr || (in_dim % 4 == 0 && ((uintptr_t)out_half & 7u) == 0),
+                 "the fp16 copy needs in_dim % 4 == 0 and an 8-byte aligned buffer");
     HSES_REQUIRE(batch >= 0 && in_dim >= 1 && row_stride >= in_dim, "bad shape");
     HSES_REQUIRE(T >= 1, "T must be >= 1");
     HSES_REQUIRE(seeds != nullptr, "seeds is NULL");
@@ -412,12 +436,12 @@ int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs, i
         int64_t total = batch * (in_dim / 4);
         HSES_KERNEL(ctx, as_stream(stream), "poisson_encode");
         poisson_kernel<4><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
-            probs, batch, in_dim, row_stride, T, mix, out);
+            probs, batch, in_dim, row_stride, T, mix, out, reinterpret_cast<__half*>(out_half));
     } else {
         int64_t total = batch * in_dim;
         HSES_KERNEL(ctx, as_stream(stream), "poisson_encode");
         poisson_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(
-            probs, batch, in_dim, row_stride, T, mix, out);
+            probs, batch, in_dim, row_stride, T, mix, out, reinterpret_cast<__half*>(out_half));
     }
     HSES_LAUNCH_CHECK();
     return HSES_OK;

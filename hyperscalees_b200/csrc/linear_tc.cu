@@ -270,7 +270,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             const int64_t R = (int64_t)mt * BM_TILE + q4 * 32 + lane;
             f32x2 tq2[RANK > 0 ? RANK : 1];
             bool odd_member = false;
-            const float rs = g.row_scale[R];
+            const float rs = g.row_scale ? g.row_scale[R] : 1.0f;
             if (RG > 0) {
                 int64_t member = (R / g.bm) % g.n_pop;
                 int32_t thread_id = g.first_thread + (int32_t)member;
@@ -925,7 +925,10 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
                                                                         sc.whi, sc.wlo, sc.cs, nullptr, one_pass);
         HSES_LAUNCH_CHECK();
     }
-    if (!g.perturb) {  // with noise the pair kernel below splits x while it computes t
+    // a caller-provided fp16 copy of an x that is exact in fp16 is the operand as it stands
+    const bool x_ready = !g.perturb && !one_pass && g.x_half != nullptr && aligned16(g.x_half);
+    if (x_ready) sc.xhi = reinterpret_cast<__half*>(const_cast<void*>(g.x_half));
+    if (!g.perturb && !x_ready) {  // with noise the pair kernel below splits x while it computes t
         HSES_KERNEL(ctx, st, "split_x");
         split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
                                                                          sc.xlo, sc.rs, sc.lo_flag, one_pass);
@@ -952,7 +955,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.out_scale = g.out_scale;
     ta.out_scale_ptr = g.out_scale_ptr;
     ta.t = sc.t;
-    ta.row_scale = sc.rs;
+    ta.row_scale = x_ready ? nullptr : sc.rs;   // NULL: no row was scaled
     ta.col_scale = sc.cs;
     ta.out = g.out;
     ta.out_stride = g.out_row_stride;

@@ -95,9 +95,11 @@ size_t hses_snn_forward_workspace_bytes(const hses_snn_model* m, const hses_pop_
     return plan_forward(m, p).bytes;
 }
 
-int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
-                     const float* spikes_in, int64_t in_stride, float* logits, void* workspace,
-                     size_t workspace_bytes) {
+// spikes_half: optional dense fp16 copy of the input spikes (T*rows, in) for the first layer's
+// tensor-core product.
+static int snn_forward_impl(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
+                            const float* spikes_in, int64_t in_stride, const void* spikes_half, float* logits,
+                            void* workspace, size_t workspace_bytes) {
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     int rc = check_model(m, p);
     if (rc != HSES_OK) return rc;
@@ -120,6 +122,7 @@ int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m,
         hses_linear_args g = layer_args(m, p, l, false);
         g.x = layer_in;
         g.x_row_stride = layer_in_stride;
+        if (l == 0) g.x_half = spikes_half;
         // currents and the LIF scan over the T steps in one call: the per-pair path finishes the scan
         // inside its kernel (the currents never reach memory), the other paths scan `out` in place
         float* out_spk = spk[l & 1];
@@ -158,13 +161,24 @@ int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m,
     return hses_perturbed_linear(ctx, stream, &g);
 }
 
+int hses_snn_forward(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
+                     const float* spikes_in, int64_t in_stride, float* logits, void* workspace,
+                     size_t workspace_bytes) {
+    return snn_forward_impl(ctx, stream, m, p, spikes_in, in_stride, nullptr, logits, workspace, workspace_bytes);
+}
+
+// The encoder can hand the first layer an fp16 copy of the spikes when a dense fp16 row is a
+// valid tensor-map row (16-byte pitch) and a valid vector store of the encoder.
+static bool eval_writes_half(const hses_snn_model* m) { return m->n_layers > 1 && m->dims[0] % 8 == 0; }
+
 size_t hses_population_eval_workspace_bytes(const hses_snn_model* m, const hses_pop_args* p) {
     if (check_model(m, p) != HSES_OK) return 0;
     FwdPlan f = plan_forward(m, p);
     size_t in_stride = (size_t)(m->dims[0] + 3) / 4 * 4;
     size_t extra = up64((size_t)p->T * f.rows * in_stride) + up64(f.rows * (size_t)m->dims[m->n_layers]) +
                    up64(f.rows);
-    return f.bytes + extra * sizeof(float);
+    size_t half = eval_writes_half(m) ? up64((size_t)p->T * f.rows * m->dims[0] / 2) : 0;   // in floats
+    return f.bytes + (extra + half) * sizeof(float);
 }
 
 int hses_population_eval(hses_ctx* ctx, hses_stream stream, const hses_snn_model* m, const hses_pop_args* p,
@@ -190,10 +204,14 @@ int hses_population_eval(hses_ctx* ctx, hses_stream stream, const hses_snn_model
     float* spikes = reinterpret_cast<float*>(base + f.bytes);
     float* logits = spikes + up64((size_t)p->T * f.rows * reserved);
     float* per_sample = logits + up64(f.rows * (size_t)classes);
-    rc = hses_poisson_encode(ctx, stream, images, (int64_t)f.rows, in, image_stride, p->T, seeds, spikes);
+    // the encoder writes the spikes twice in one pass: f32 (the layout every path reads) and, when
+    // the first layer's tensor-core product can take it, fp16 as that product's operand
+    void* spikes_half = eval_writes_half(m) ? static_cast<void*>(per_sample + up64(f.rows)) : nullptr;
+    rc = hses_poisson_encode_dual(ctx, stream, images, (int64_t)f.rows, in, image_stride, p->T, seeds, spikes,
+                                  spikes_half);
     if (rc != HSES_OK) return rc;
     float* lg = logits_out ? logits_out : logits;
-    rc = hses_snn_forward(ctx, stream, m, p, spikes, image_stride, lg, workspace, f.bytes);
+    rc = snn_forward_impl(ctx, stream, m, p, spikes, image_stride, spikes_half, lg, workspace, f.bytes);
     if (rc != HSES_OK) return rc;
     rc = hses_fitness(ctx, stream, lg, (int64_t)f.rows, classes, labels, reward, per_sample);
     if (rc != HSES_OK) return rc;

@@ -127,6 +127,13 @@ int hses_prng_normal_half(hses_ctx* ctx, hses_stream stream, float* out /*device
 int hses_poisson_encode(hses_ctx* ctx, hses_stream stream, const float* probs /*device*/,
                         int64_t batch, int32_t in_dim, int64_t row_stride, int32_t T,
                         const uint32_t seeds[4], float* out /*device*/);
+/* The same kernel, writing in the same pass a second copy of the spikes as fp16 0/1 in dense rows
+ * (T, batch, in_dim): the operand format of the tensor-core layer that follows (x_half of
+ * hses_linear_args), so that the layer does not have to read and convert the f32 spikes again.
+ * out_half NULL gives hses_poisson_encode. */
+int hses_poisson_encode_dual(hses_ctx* ctx, hses_stream stream, const float* probs /*device*/,
+                             int64_t batch, int32_t in_dim, int64_t row_stride, int32_t T,
+                             const uint32_t seeds[4], float* out /*device*/, void* out_half /*device or NULL*/);
 
 /* ---- lif_fused, oxide.rs:489-543 / lif_fused_oxide.rs:37-70, run_lif
  *      snn.rs:73-97.  cur and spikes are (T, n, h) pitched; v is (n, h)
@@ -220,6 +227,10 @@ typedef struct {
                              sign*sigma/sqrt(rank); `param` is still handed over as (a = out, k = in), i.e.
                              transposed, and the call returns x·param_refᵀᵀ + (x·A)·Bᵀ.  Not combinable
                              with a factor cache */
+    const void* x_half; /* device or NULL: the matrix x once more as dense fp16 rows (rows, k), for
+                           callers whose x is exact in fp16 and who have that copy anyway (the 0/1
+                           spikes hses_poisson_encode_dual writes).  The tensor-core path then takes
+                           it as its operand instead of converting x; x itself is still required */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

@@ -193,3 +193,40 @@ def test_prng_normal_half_matches_oracle(hs, oracle):
     assert abs(z.mean()) < 0.02 and abs(z.std() - 1.0) < 0.02
     with pytest.raises(ValueError):
         kernels.prng_normal_half(torch.empty(100, device="cuda"), 0.0, 1.0, seeds)
+
+
+def test_poisson_encode_dual_writes_the_same_spikes_as_fp16(hs):
+    """hses_poisson_encode_dual through the C ABI: the fp16 copy equals the f32 spikes, and the
+    tensor-core layer fed with it (x_half) returns what it returns from the f32 spikes alone."""
+    import ctypes as C
+    from hyperscalees_b200 import _lib, core, ops
+    L = _lib.load()
+    ctx = core.get_context(0)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    batch, in_dim, T = 256, 784, 4
+    probs = torch.rand(batch, in_dim, device="cuda", generator=g)
+    out = torch.empty(T, batch, in_dim, device="cuda")
+    half = torch.empty(T, batch, in_dim, device="cuda", dtype=torch.float16)
+    sd = (C.c_uint32 * 4)(1, 2, 3, 4)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = L.hses_poisson_encode_dual(ctx.handle, stream, C.c_void_p(probs.data_ptr()), batch, in_dim, in_dim, T, sd,
+                                    C.c_void_p(out.data_ptr()), C.c_void_p(half.data_ptr()))
+    assert rc == 0, L.hses_last_error()
+    assert torch.equal(out, ops.poisson_encode(probs, T, [1, 2, 3, 4]))
+    assert torch.equal(half.float(), out)
+    # clean tensor-core product with and without the ready-made operand
+    w = torch.randn(128, in_dim, device="cuda", generator=g)
+    want = ops.perturbed_linear(out, w, n_pop=batch, bm=1, t_steps=T, perturb=False, algo=ops.ALGO_TENSOR)
+    ga = _lib.LinearArgs()
+    res = torch.empty_like(want)
+    ga.x, ga.t_steps, ga.n_pop, ga.bm, ga.k, ga.x_row_stride = out.data_ptr(), T, batch, 1, in_dim, in_dim
+    ga.param, ga.a, ga.param_row_stride = w.data_ptr(), 128, in_dim
+    ga.out, ga.out_row_stride, ga.out_scale, ga.algo = res.data_ptr(), 128, 1.0, ops.ALGO_TENSOR
+    ga.x_half = half.data_ptr()
+    need = int(L.hses_perturbed_linear_workspace_bytes(C.byref(ga)))
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    ga.workspace, ga.workspace_bytes = ws.data_ptr(), need
+    ctx.profile_enable(False)
+    assert L.hses_perturbed_linear(ctx.handle, stream, C.byref(ga)) == 0, L.hses_last_error()
+    assert "split_x" not in {k for k, v in ctx.profile_read().items() if v[0]}
+    assert torch.equal(res, want)
