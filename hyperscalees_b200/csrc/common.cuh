@@ -134,6 +134,11 @@ namespace hses {
 int launch_pair_factors(hses_ctx* ctx, cudaStream_t stream, uint64_t key, int32_t true_epoch,
                         int32_t first_pair, int64_t pairs, int rank, int a, int b,
                         const float* pair_weight, float* A, float* B, bool no_alloc = false);
+// One solver step (hses_solver_step's arithmetic) over several tensors in one launch; gradients
+// back to back in `grads`, tensors with a NULL parameter skipped.
+int solver_step_multi(hses_ctx* ctx, cudaStream_t st, const hses_solver* solver, int32_t step, int n_tensors,
+                      float* const* params, float* const* m_bufs, float* const* v_bufs, const int64_t* lens,
+                      const float* grads);
 // lif_step (hyperscalees-models/src/snn.rs:53-65): charge, threshold, reset; returns the spike
 __device__ __forceinline__ float lif_update(float& v, float cur, float leak, float v_th, int reset) {
     float d = __fadd_rn(-v, cur);

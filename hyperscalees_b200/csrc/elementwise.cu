@@ -234,6 +234,7 @@ __global__ void zscore_kernel(const float* __restrict__ raw, int64_t n, int grou
 // ---------------------------------------------------------------------------
 // solver (noiser.rs:155-224)
 // ---------------------------------------------------------------------------
+constexpr int kSolverMulti = 12;
 struct SolverConsts {
     int kind;
     float lr, beta1, beta2, eps, wd;
@@ -292,6 +293,33 @@ __global__ void solver_kernel(SolverConsts c, float* __restrict__ p, const float
     if (adam) {
         m[i] = mi;
         v[i] = vi;
+    }
+}
+
+// The same step for up to kSolverMulti parameter tensors in one launch (the leaves of a small
+// model): block b works on the tensor whose block range contains it; grads are one flat buffer
+// in tensor order.
+struct SolverMulti {
+    int n;
+    float* p[kSolverMulti];
+    float* m[kSolverMulti];
+    float* v[kSolverMulti];
+    int64_t len[kSolverMulti];
+    int64_t goff[kSolverMulti];
+    int first_block[kSolverMulti + 1];
+};
+__global__ void solver_multi_kernel(SolverConsts c, SolverMulti d, const float* __restrict__ grads) {
+    int t = 0;
+    while (t + 1 < d.n && (int)blockIdx.x >= d.first_block[t + 1]) ++t;
+    const int64_t i = (int64_t)(blockIdx.x - d.first_block[t]) * blockDim.x + threadIdx.x;
+    if (i >= d.len[t] || d.p[t] == nullptr) return;
+    const bool adam = c.kind != HSES_SGD;
+    float mi = adam ? d.m[t][i] : 0.0f, vi = adam ? d.v[t][i] : 0.0f, pi = d.p[t][i];
+    solver_one(c, pi, grads[d.goff[t] + i], mi, vi);
+    d.p[t][i] = pi;
+    if (adam) {
+        d.m[t][i] = mi;
+        d.v[t][i] = vi;
     }
 }
 
@@ -558,6 +586,61 @@ int hses_vector_mul(hses_ctx* ctx, hses_stream stream, const float* a, const flo
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
+
+}  // extern "C"
+
+namespace hses {
+// One solver step over several parameter tensors whose gradients sit back to back in `grads`
+// (tensors with a NULL parameter pointer are skipped but still take their place in `grads`).
+int solver_step_multi(hses_ctx* ctx, cudaStream_t st, const hses_solver* solver, int32_t step, int n_tensors,
+                      float* const* params, float* const* m_bufs, float* const* v_bufs, const int64_t* lens,
+                      const float* grads) {
+    HSES_REQUIRE(solver->kind == HSES_SGD || solver->kind == HSES_ADAM || solver->kind == HSES_ADAMW,
+                 "unknown solver kind");
+    const bool moments = solver->kind != HSES_SGD;
+    HSES_REQUIRE(!moments || step >= 1, "step is the counter after the increment (>= 1)");
+    SolverConsts c{};
+    c.kind = solver->kind;
+    c.lr = solver->lr;
+    c.grad_scale = 1.0f;
+    if (moments) {
+        float t = (float)step;
+        c.beta1 = solver->beta1;
+        c.beta2 = solver->beta2;
+        c.eps = solver->eps;
+        c.wd = solver->kind == HSES_ADAMW ? solver->weight_decay : 0.0f;
+        c.omb1 = 1.0f - solver->beta1;
+        c.omb2 = 1.0f - solver->beta2;
+        c.ibc1 = 1.0f / (1.0f - powf(solver->beta1, t));
+        c.ibc2 = 1.0f / (1.0f - powf(solver->beta2, t));
+    }
+    int64_t goff = 0;
+    for (int t0 = 0; t0 < n_tensors; t0 += kSolverMulti) {
+        SolverMulti d{};
+        d.n = n_tensors - t0 < kSolverMulti ? n_tensors - t0 : kSolverMulti;
+        int blocks = 0;
+        for (int t = 0; t < d.n; ++t) {
+            d.p[t] = params[t0 + t];
+            d.m[t] = moments ? m_bufs[t0 + t] : nullptr;
+            d.v[t] = moments ? v_bufs[t0 + t] : nullptr;
+            HSES_REQUIRE(d.p[t] == nullptr || !moments || (d.m[t] != nullptr && d.v[t] != nullptr), "Adam needs moment buffers");
+            d.len[t] = lens[t0 + t];
+            d.goff[t] = goff;
+            goff += lens[t0 + t];
+            d.first_block[t] = blocks;
+            blocks += (int)((lens[t0 + t] + 255) / 256);
+        }
+        d.first_block[d.n] = blocks;
+        if (blocks == 0) continue;
+        HSES_KERNEL(ctx, st, "solver");
+        solver_multi_kernel<<<(unsigned)blocks, 256, 0, st>>>(c, d, grads);
+        HSES_LAUNCH_CHECK();
+    }
+    return HSES_OK;
+}
+}  // namespace hses
+
+extern "C" {
 
 int hses_solver_step(hses_ctx* ctx, hses_stream stream, const hses_solver* solver, int32_t step,
                      float grad_scale, float* param, const float* grad, float* m, float* v,

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "update_tc.cuh"
 
 namespace hses {
 
@@ -250,6 +251,7 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
     if (rc != HSES_OK) return rc;
     const bool moments = solver->kind != HSES_SGD;
     HSES_REQUIRE(!moments || (m_bufs != nullptr && v_bufs != nullptr), "Adam needs moment buffers");
+    bool range_valid = false;
     for (int l = 0; l < m->n_layers; ++l) {
         int a = m->dims[l + 1], b = m->dims[l];
         hses_update_args u{};
@@ -270,8 +272,12 @@ int hses_population_update(hses_ctx* ctx, hses_stream stream, const hses_snn_mod
         u.mode = HSES_UPDATE_GRAD;
         const hses_factor_cache* c = m->caches ? m->caches[l] : nullptr;
         if (c && c->first_pair == 0 && c->n_pairs >= n_total / 2) u.cache = c;
-        rc = hses_es_update_ex(ctx, stream, &u);
+        // the layers share the fitness vector and the workspace: the pair-weight range that the
+        // first tensor-core layer leaves at the start of the workspace serves the following ones
+        bool took_tc = false;
+        rc = es_update_ex_impl(ctx, stream, &u, range_valid, &took_tc);
         if (rc != HSES_OK) return rc;
+        range_valid = took_tc;
         rc = hses_solver_step(ctx, stream, solver, step, 1.0f, params[l], grad, moments ? m_bufs[l] : nullptr,
                               moments ? v_bufs[l] : nullptr, (int64_t)a * b);
         if (rc != HSES_OK) return rc;
@@ -321,6 +327,7 @@ int hses_population_grads(hses_ctx* ctx, hses_stream stream, const hses_snn_mode
     int rc = hses_convert_fitnesses(ctx, stream, raw_fitness, n_total, group_size, fit, nullptr);
     if (rc != HSES_OK) return rc;
     float* g = grads;
+    bool range_valid = false;
     for (int l = 0; l < m->n_layers; ++l) {
         int a = m->dims[l + 1], b = m->dims[l];
         hses_update_args u{};
@@ -343,8 +350,10 @@ int hses_population_grads(hses_ctx* ctx, hses_stream stream, const hses_snn_mode
         if (c && c->first_pair <= first_thread / 2 &&
             (int64_t)c->first_pair + c->n_pairs >= (int64_t)first_thread / 2 + n_local / 2)
             u.cache = c;
-        rc = hses_es_update_ex(ctx, stream, &u);
+        bool took_tc = false;
+        rc = es_update_ex_impl(ctx, stream, &u, range_valid, &took_tc);
         if (rc != HSES_OK) return rc;
+        range_valid = took_tc;
         g += (size_t)a * b;
     }
     // out_gain: PARAM-class leaf of shape (1,1), dense noise (eggroll.rs:331-350); frozen -> zero gradient
@@ -366,17 +375,11 @@ int hses_population_apply(hses_ctx* ctx, hses_stream stream, const hses_snn_mode
     HSES_REQUIRE(solver != nullptr && params != nullptr && grads != nullptr, "NULL pointer");
     const bool moments = solver->kind != HSES_SGD;
     HSES_REQUIRE(!moments || (m_bufs != nullptr && v_bufs != nullptr), "Adam needs moment buffers");
-    const float* g = grads;
-    for (int l = 0; l <= m->n_layers; ++l) {
-        int64_t len = l < m->n_layers ? (int64_t)m->dims[l + 1] * m->dims[l] : 1;
-        if (params[l] != nullptr) {
-            int rc = hses_solver_step(ctx, stream, solver, step, 1.0f, params[l], g, moments ? m_bufs[l] : nullptr,
-                                      moments ? v_bufs[l] : nullptr, len);
-            if (rc != HSES_OK) return rc;
-        }
-        g += len;
-    }
-    return HSES_OK;
+    // every leaf in one launch: the step's cost is launches, not arithmetic
+    std::vector<int64_t> lens((size_t)m->n_layers + 1);
+    for (int l = 0; l <= m->n_layers; ++l) lens[l] = l < m->n_layers ? (int64_t)m->dims[l + 1] * m->dims[l] : 1;
+    return solver_step_multi(ctx, as_stream(stream), solver, step, m->n_layers + 1, params, m_bufs, v_bufs,
+                             lens.data(), grads);
 }
 
 }  // extern "C"

@@ -309,6 +309,14 @@ size_t hses_es_update_workspace_bytes(int32_t a, int32_t b, int32_t rank, int64_
 }
 
 int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args* args) {
+    return es_update_ex_impl(ctx, stream, args, false, nullptr);
+}
+
+}  // extern "C"
+
+int hses::es_update_ex_impl(hses_ctx* ctx, hses_stream stream, const hses_update_args* args, bool reuse_range,
+                            bool* took_tc) {
+    if (took_tc) *took_tc = false;
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     HSES_REQUIRE(args != nullptr, "args is NULL");
     const hses_update_args& u = *args;
@@ -332,7 +340,8 @@ int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args*
         // wide factors on tile-aligned shapes: the contraction runs on the tensor cores
         float nf = (float)u.n_total;
         float sc = u.mode == HSES_UPDATE_GRAD ? -(base_sigma_tc * (1.0f / nf)) * sqrtf(nf) : base_sigma_tc;
-        return run_update_tc(ctx, st, u, sc);
+        if (took_tc) *took_tc = true;
+        return run_update_tc(ctx, st, u, sc, reuse_range);
     }
     UpdatePlan p = plan_update(a, b, rank, u.n);
     HSES_REQUIRE(u.workspace != nullptr && u.workspace_bytes >= p.bytes,
@@ -387,6 +396,8 @@ int hses_es_update_ex(hses_ctx* ctx, hses_stream stream, const hses_update_args*
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
+
+extern "C" {
 
 int hses_es_update(hses_ctx* ctx, hses_stream stream, uint64_t key, int32_t epoch,
                    int32_t noise_reuse, int32_t first_thread, int64_t n, int64_t n_total,

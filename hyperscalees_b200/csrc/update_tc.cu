@@ -347,7 +347,7 @@ UpdateTcPlan plan_update_tc(int a, int b, int rank, int64_t n, bool need_raw) {
     return p;
 }
 
-int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, float scale) {
+int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, float scale, bool reuse_range) {
     const int a = u.a, b = u.b, rank = u.rank;
     UpdateTcPlan p = plan_update_tc(a, b, rank, u.n, u.cache == nullptr);
     HSES_REQUIRE(u.workspace != nullptr && u.workspace_bytes >= p.bytes && ((uintptr_t)u.workspace & 255u) == 0,
@@ -370,7 +370,7 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
         cA = c.data + (size_t)(first_pair - c.first_pair) * a * rank;
         cB = c.data + (size_t)c.n_pairs * a * rank + (size_t)(first_pair - c.first_pair) * b * rank;
     }
-    {
+    if (!reuse_range) {
         HSES_KERNEL(ctx, st, "pair_weight_range");
         pair_weight_range_kernel<<<1, 1024, 0, st>>>(u.fitness, p.pairs, e_w);
         HSES_LAUNCH_CHECK();
