@@ -102,7 +102,7 @@ struct TcSmem {
     static constexpr int W_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
     static constexpr int HOP_BYTES = 0;     // the hop table is read through L1;
-    static constexpr int TAB_BYTES = 1536;  // the logarithm's helper table and the thresholds as 2 x 256 bytes
+    static constexpr int TAB_BYTES = 1280;  // the logarithm's helper table and the thresholds as 2 x 128 bytes
     static constexpr int BAR_BYTES = 608;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
@@ -161,11 +161,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     // looks them up for every normal
     if (RG > 0) {
         for (int i = threadIdx.x; i < 64; i += NTHREADS) log_tab_s[i] = g.cal.log_tab[i];
-        // thresholds of the rounding filter as bytes (ceil(log2)): 512 bytes instead of 2 KB
+        // thresholds of the rounding filter as bytes (ceil(log2)), one per 1/128 of the input range
+        // (the larger of the two 1/256 thresholds): 256 bytes instead of 2 KB
         uint8_t* thr_s = reinterpret_cast<uint8_t*>(log_tab_s + 64);
-        for (int i = threadIdx.x; i < 256; i += NTHREADS) {
-            thr_s[i] = pack_threshold_log2(g.cal.log_delta[i]);
-            thr_s[256 + i] = pack_threshold_log2(g.cal.cos_delta[i]);
+        for (int i = threadIdx.x; i < 128; i += NTHREADS) {
+            const uint32_t tl = max(g.cal.log_delta[2 * i], g.cal.log_delta[2 * i + 1]);
+            const uint32_t tc_ = max(g.cal.cos_delta[2 * i], g.cal.cos_delta[2 * i + 1]);
+            thr_s[i] = pack_threshold_log2(tl);
+            thr_s[128 + i] = pack_threshold_log2(tc_);
         }
     }
     if (warp == 1) {
@@ -374,7 +377,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         LibmCal cal = g.cal;
         cal.log_tab = log_tab_s;
         cal.log_delta = reinterpret_cast<const uint32_t*>(log_tab_s + 64);                         // byte tables, see
-        cal.cos_delta = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(log_tab_s + 64) + 256);  // next_normals4_t<true>
+        cal.cos_delta = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(log_tab_s + 64) + 128);  // next_normals4_t<true, 17>
         LibmCal cal4 = g.cal;      // the one-at-a-time generator of ranks 1..3 reads the 32-bit thresholds
         cal4.log_tab = log_tab_s;
         const int items_per_tile = g.a / IT::ROWS;
@@ -429,7 +432,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         if (rt > 1) z[1] = next_normal(a_state, cal4);
                         if (rt > 2) z[2] = next_normal(a_state, cal4);
                     } else {
-                        next_normals4_t<true>(a_state, cal, z);
+                        next_normals4_t<true, 17>(a_state, cal, z);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) dst[(4 * c4 + j) * 32] = __fmul_rn(z[j], g.base_sigma);

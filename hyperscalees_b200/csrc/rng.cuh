@@ -308,7 +308,9 @@ HSES_HD float next_normal(uint64_t& state, const LibmCal& cal) {
 // LOG2T: the two threshold tables are 256 bytes each holding ceil(log2(threshold)) (see
 // pack_thresholds_log2): a threshold rounded up only sends a few more candidates to the bitmap,
 // whose bit decides, so the values are the same; the tables then fit where 2 KB would not.
-template <bool LOG2T>
+// TSHIFT: the byte tables are indexed by input >> TSHIFT (16: 256 entries; 17: 128 entries, each the
+// larger of two neighbouring thresholds — again only a few more candidates for the bitmap).
+template <bool LOG2T, int TSHIFT = 16>
 HSES_HD void next_normals4_t(uint64_t& state, const LibmCal& cal, float (&out)[4]) {
     uint32_t iu[4], ju[4];
     uint64_t x = state;
@@ -327,13 +329,13 @@ HSES_HD void next_normals4_t(uint64_t& state, const LibmCal& cal, float (&out)[4
         uint32_t i = iu[j] ? iu[j] : 1u;  // the zero uniform is replaced below
         rl[j] = round_candidate(log_candidate(i, cal.log_tab));
         if (LOG2T)
-            nl[j] = rl[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.log_delta)[i >> 16]);
+            nl[j] = rl[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.log_delta)[i >> TSHIFT]);
         else
             nl[j] = rl[j].dist < cal.log_delta[i >> 16];
         float theta = fmul(kTauF, (float)ju[j] * 5.9604644775390625e-08f);
         rc[j] = round_candidate(cos_candidate(theta));
         if (LOG2T)
-            nc[j] = rc[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.cos_delta)[ju[j] >> 16]);
+            nc[j] = rc[j].dist < (1u << reinterpret_cast<const uint8_t*>(cal.cos_delta)[ju[j] >> TSHIFT]);
         else
             nc[j] = rc[j].dist < cal.cos_delta[ju[j] >> 16];
     }
