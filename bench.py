@@ -284,7 +284,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                   "note": "factors read from a device cache built once outside the timed region"}
         del cache
     # ---- the two extra blocks of the line (see the module docstring) ----
-    pop_block, stream_block, lm_block, rwkv_block = None, None, None, None
+    pop_block, stream_block, lm_block, rwkv_block, einsum_block = None, None, None, None, None
     if not args.kernel_only and not args.headline_only:
         del x_dev, out_dev, pipe
         torch.cuda.empty_cache()
@@ -305,6 +305,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
             stream_block = streaming_block(dev, ctx, args.steps, args.warmup,
                                            only=("poisson_encode", "lif_scan", "spiking_attention mode 0", "wkv7"))
             lm_block = spiking_lm_block(dev, ctx, 4096, 32, args.steps, args.warmup)
+            einsum_block = einsum_pair_block(dev, ctx, args.steps, args.warmup)
         rwkv_block = rwkv_lm_block(rank, world, dev, ctx, comm, 1024, args.steps, args.warmup)
         if comm is not None:
             comm.destroy()
@@ -352,10 +353,56 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                         "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(out_host.numel() * 4)},
                 "gpu_launches": int(launches), "clocks": clocks, "factor_cache": cached,
                 "population_step": pop_block, "streaming": stream_block, "spiking_lm": lm_block,
-                "rwkv_lm": rwkv_block}
+                "rwkv_lm": rwkv_block, "einsum_pair": einsum_block}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def einsum_pair_block(dev, ctx, steps: int, warmup: int, half: int = 6000, r: int = 64, a: int = 256, b: int = 784):
+    """The explicit-input paired einsum (the GPU trainer's einsum_pair_fused) at the shape the reference
+    quotes its kernel on: M = 256, N = 784, K = half*r = 384 000.  Times the call on 16-byte aligned
+    operands (tensor-core kernel) and on the same values shifted by one float (fp32 kernel), and
+    compares a sub-block of both outputs with an fp64 product."""
+    import torch
+    from hyperscalees_b200 import ops
+    g = torch.Generator(device=dev).manual_seed(7)
+    flat_a = torch.randn(half * r * a + 4, device=dev, generator=g)
+    flat_b = torch.randn(half * r * b + 4, device=dev, generator=g)
+    scores = torch.randn(2 * half, device=dev, generator=g)
+    peaks = measured_peaks()
+    nbytes = 4.0 * half * r * (a + b)
+    out = {"shape": {"M": a, "N": b, "K": half * r, "half": half, "r": r},
+           "reference_figure": "7.2 ms for the reference's own kernel and 8.4-8.9 ms for its cuBLAS TF32 route, both on an RTX 4090 (docs/cuda_oxide_integration_plan.md:283-299)"}
+    for name, off in (("tensor_core", 0), ("fp32_kernel", 1)):
+        a_t = flat_a[off:off + half * r * a].view(half, r, a)
+        b_t = flat_b[off:off + half * r * b].view(half, r, b)
+        for _ in range(max(warmup, 3)):
+            g_raw, g_ones = ops.einsum_pair(a_t, b_t, scores)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = steps if off == 0 else max(2, steps // 4)
+        e0.record()
+        for _ in range(n):
+            g_raw, g_ones = ops.einsum_pair(a_t, b_t, scores)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n
+        w = (scores[:half] + scores[half:]).double().repeat_interleave(r)
+        A = a_t[:, :, :32].double().reshape(-1, 32)
+        B = b_t[:, :, b - 48:].double().reshape(-1, 48)
+        ref_raw, ref_ones = (A * w[:, None]).T @ B, 2.0 * (A.T @ B)
+        err = max(((g_raw[:32, b - 48:].double() - ref_raw).abs().max() / ref_raw.abs().max()).item(),
+                  ((g_ones[:32, b - 48:].double() - ref_ones).abs().max() / ref_ones.abs().max()).item())
+        out[name] = {"ms": round(ms, 4), "GB_per_s": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                     "frac_of_measured_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                     "algorithmic_tflops": round(2 * 2.0 * a * b * half * r / (ms * 1e-3) / 1e12, 1),
+                     "max_err_over_largest_entry": float(f"{err:.3g}")}
+        del a_t, b_t, g_raw, g_ones
+    out["device_status"] = int(ctx.device_status())
+    del flat_a, flat_b
+    torch.cuda.empty_cache()
+    return out
 
 
 POP_DIMS, POP_T = [784, 128, 128, 128, 10], 8
@@ -867,7 +914,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer", "spiking_lm", "rwkv_lm"],
+    ap.add_argument("--workload", default="microbench", choices=["microbench", "population_step", "streaming_kernels", "snn_transformer", "spiking_lm", "rwkv_lm", "einsum_pair"],
                     help="microbench: the perturbed-linear layer the metric is quoted on (default); "
                          "population_step: a full ES step of the spiking MLP (secondary figure); "
                          "streaming_kernels: the HBM-bound kernels of the path, each timed alone; "
@@ -908,6 +955,14 @@ def main():
             run_spiking_lm(args, local_rank)
     elif args.workload == "rwkv_lm":
         run_rwkv_lm(args, rank, local_rank, world)
+    elif args.workload == "einsum_pair":
+        if rank == 0:
+            import torch
+            from hyperscalees_b200 import core
+            dev = torch.device("cuda", local_rank)
+            torch.cuda.set_device(dev)
+            blk = einsum_pair_block(dev, core.get_context(local_rank), args.steps, args.warmup)
+            print(json.dumps({"workload": "einsum_pair", **blk}), flush=True)
     else:
         run_ours(args, rank, local_rank, world)
 

@@ -16,6 +16,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "einsum_tc.cuh"
 #include "update_tc.cuh"
 
 namespace hses {
@@ -479,7 +480,9 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
 
 size_t hses_einsum_pair_workspace_bytes(int64_t half, int32_t r, int32_t a, int32_t b) {
     if (half < 1 || r < 1 || a < 1 || b < 1) return 0;
-    return (size_t)einsum_pair_splits(half, r, a, b) * 2 * (size_t)a * b * sizeof(float);
+    size_t simt = (size_t)einsum_pair_splits(half, r, a, b) * 2 * (size_t)a * b * sizeof(float);
+    size_t tc = plan_einsum_tc(half, r, a, b).bytes;   // whichever kernel the pointers and strides allow
+    return simt > tc ? simt : tc;
 }
 
 int hses_einsum_pair(hses_ctx* ctx, hses_stream stream, const float* a_t, int64_t a_stride0, int64_t a_stride1,
@@ -494,9 +497,14 @@ int hses_einsum_pair(hses_ctx* ctx, hses_stream stream, const float* a_t, int64_
     HSES_REQUIRE(half * r < (1ll << 40), "K too large");
     size_t need = hses_einsum_pair_workspace_bytes(half, r, a, b);
     HSES_REQUIRE(workspace != nullptr && workspace_bytes >= need, "workspace too small; see hses_einsum_pair_workspace_bytes");
+    cudaStream_t st = as_stream(stream);
+    // long contractions over 16-byte aligned operands run on the tensor cores
+    if (einsum_tc_supports(a_t, a_stride0, a_stride1, b_t, b_stride0, b_stride1, half, r, a, b) &&
+        ((uintptr_t)workspace & 255u) == 0)
+        return run_einsum_tc(ctx, st, a_t, a_stride0, a_stride1, b_t, b_stride0, b_stride1, scores, half, r, a, b, g_raw,
+                             g_ones, workspace, workspace_bytes);
     int splits = einsum_pair_splits(half, r, a, b);
     HSES_REQUIRE((a + EP_TM - 1) / EP_TM <= 65535, "a too large");
-    cudaStream_t st = as_stream(stream);
     float* partial = reinterpret_cast<float*>(workspace);
     dim3 grid((unsigned)((b + EP_TN - 1) / EP_TN), (unsigned)((a + EP_TM - 1) / EP_TM), (unsigned)splits);
     {

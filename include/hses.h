@@ -356,7 +356,12 @@ int hses_es_update_static(hses_ctx* ctx, hses_stream stream, uint64_t key, int32
  *      (innermost stride 1; padded row pitches allowed), row (i, j) shared by members i and
  *      i + half; scores: n = 2*half raw scores.
  *      g_raw = sum_k (s_i + s_{i+half}) a_t[k] (x) b_t[k], g_ones = 2 * sum_k a_t[k] (x) b_t[k],
- *      both (a, b) dense, overwritten (no zero-initialisation needed, no 2a <= 256 limit). -- */
+ *      both (a, b) dense, overwritten (no zero-initialisation needed, no 2a <= 256 limit).
+ *      Contractions of 32768 rows and more whose bases and strides are multiples of 16 bytes (r
+ *      from 32 up, or a divisor of 64) and whose workspace is 256-byte aligned run on the tensor
+ *      cores with fp32-equivalent three-pass fp16 products (each operand scaled by a power of two
+ *      found from its largest magnitude); all others on an fp32 kernel.  Both add their split-K
+ *      partial sums in a fixed order: the same inputs give the same bits on every call. -- */
 size_t hses_einsum_pair_workspace_bytes(int64_t half, int32_t r, int32_t a, int32_t b);
 int hses_einsum_pair(hses_ctx* ctx, hses_stream stream, const float* a_t /*device*/, int64_t a_stride0,
                      int64_t a_stride1, const float* b_t /*device*/, int64_t b_stride0, int64_t b_stride1,
