@@ -202,8 +202,13 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         constexpr int A_PASSES = UT_BM / 32, B_PASSES = 256 / 32;
         bool ok = true;
         int64_t it = 0;
+        // the pair weight is fetched one pair ahead: its load latency would otherwise sit between the
+        // arrival of a stage and the first converted value
+        float2 f_next = p_lo < p_hi ? make_float2(__ldg(g.fitness + 2 * p_lo), __ldg(g.fitness + 2 * p_lo + 1))
+                                    : make_float2(0.f, 0.f);
         for (int64_t p = p_lo; p < p_hi && ok; ++p) {
-            const float w = __fsub_rn(g.fitness[2 * p], g.fitness[2 * p + 1]);
+            const float w = __fsub_rn(f_next.x, f_next.y);
+            if (p + 1 < p_hi) f_next = make_float2(__ldg(g.fitness + 2 * p + 2), __ldg(g.fitness + 2 * p + 3));
             for (int qb = 0; qb < kq; ++qb, ++it) {
                 const int s = (int)(it % g.stages);
                 const uint32_t ph = (uint32_t)(it / g.stages) & 1;
