@@ -21,6 +21,10 @@ pytestmark = pytest.mark.gpu
     (2, 2, 40, 256, 32, 8, 0),      # swizzled A, 32 rows per pair, the largest box (256 rows)
     (4, 3, 64, 72, 32, 2, 0),       # swizzled A, 12 of 16 tile rows used, ragged column block
     (6, 1, 32, 10, 64, 1, 4),       # swizzled A, 2 of 8 tile rows, ten columns (one warp task pair)
+    (6, 1, 128, 128, 64, 8, 2),     # config-3 hidden layer, shard offset
+    (4, 1, 64, 128, 32, 3, 0),      # the same with 6 of 8 tile rows
+    (4, 2, 96, 256, 96, 8, 0),      # 256 outputs, 32 rows per pair, three rank boxes
+    (4, 1, 64, 128, 128, 8, 0),     # rank 128
 ])
 def test_pair_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
@@ -79,6 +83,9 @@ def test_auto_dispatch_prefers_the_pair_path(hs):
     (6, 2, 64, 100, 32, 4, 1),      # the same with a ragged column block and the subtractive reset
     (4, 1, 36, 50, 8, 3, 0),        # per-pair path without the swizzled form: currents scanned in place
     (8, 16, 64, 128, 4, 2, 0),      # tensor path: currents scanned in place
+    (4, 2, 64, 128, 32, 8, 1),      # two samples per member, subtractive reset
+    (4, 1, 96, 256, 64, 4, 0),      # 256 outputs, 8 rows per pair
+    (6, 1, 128, 128, 64, 3, 0),     # 6 of 8 tile rows
 ])
 def test_fused_lif_scan_equals_linear_then_scan(n_pop, bm, k, a, rank, t_steps, reset):
     """lif = 2 (LIF scan over the steps fused behind the layer) gives the bits of the two-call form."""
