@@ -80,7 +80,7 @@ struct UtArgs {
 };
 
 // four fp32 values -> fp16 hi and lo halves of a 16-byte piece of a 128B-swizzled K-major tile
-__device__ __forceinline__ void convert_store(float4 v, float mul0, float mul1, int sign_factors, uint8_t* tile_hi,
+__device__ __forceinline__ void convert_store(float4 v, float mul, int sign_factors, uint8_t* tile_hi,
                                               uint8_t* tile_lo, int row, int f4) {
     if (sign_factors) {  // uniform over the launch
         v.x = v.x > 0.0f ? 1.0f : v.x < 0.0f ? -1.0f : 0.0f;
@@ -88,9 +88,9 @@ __device__ __forceinline__ void convert_store(float4 v, float mul0, float mul1, 
         v.z = v.z > 0.0f ? 1.0f : v.z < 0.0f ? -1.0f : 0.0f;
         v.w = v.w > 0.0f ? 1.0f : v.w < 0.0f ? -1.0f : 0.0f;
     }
-    // mul1 is a power of two: the second product is exact
-    const float x0 = __fmul_rn(__fmul_rn(v.x, mul0), mul1), x1 = __fmul_rn(__fmul_rn(v.y, mul0), mul1);
-    const float x2 = __fmul_rn(__fmul_rn(v.z, mul0), mul1), x3 = __fmul_rn(__fmul_rn(v.w, mul0), mul1);
+    // mul = weight * power of two: one rounding, the same value as (v * weight) * power of two
+    const float x0 = __fmul_rn(v.x, mul), x1 = __fmul_rn(v.y, mul);
+    const float x2 = __fmul_rn(v.z, mul), x3 = __fmul_rn(v.w, mul);
     const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
     const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
     const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
@@ -207,7 +207,7 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         float2 f_next = p_lo < p_hi ? make_float2(__ldg(g.fitness + 2 * p_lo), __ldg(g.fitness + 2 * p_lo + 1))
                                     : make_float2(0.f, 0.f);
         for (int64_t p = p_lo; p < p_hi && ok; ++p) {
-            const float w = __fsub_rn(f_next.x, f_next.y);
+            const float w_sc = __fmul_rn(__fsub_rn(f_next.x, f_next.y), sc_a);   // exact: sc_a is a power of two
             if (p + 1 < p_hi) f_next = make_float2(__ldg(g.fitness + 2 * p + 2), __ldg(g.fitness + 2 * p + 3));
             for (int qb = 0; qb < kq; ++qb, ++it) {
                 const int s = (int)(it % g.stages);
@@ -232,12 +232,12 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (!mbar_wait(&readdone[s], ph, abort_flag, g.status, 15)) { ok = false; break; }
 #pragma unroll
                 for (int u = 0; u < A_PASSES; ++u)
-                    convert_store(va[u], w, sc_a, g.sign_factors, st, st + a_bytes, u * 32 + crow, f4);
+                    convert_store(va[u], w_sc, g.sign_factors, st, st + a_bytes, u * 32 + crow, f4);
 #pragma unroll
                 for (int u = 0; u < B_PASSES; ++u) {
                     const int row = u * 32 + crow;
                     if (row < g.bn)
-                        convert_store(vb[u], 1.0f, sc_b, g.sign_factors, st + 2 * a_bytes,
+                        convert_store(vb[u], sc_b, g.sign_factors, st + 2 * a_bytes,
                                       st + 2 * a_bytes + b_bytes, row, f4);
                 }
                 fence_proxy_async();   // the tensor core reads these generic-proxy stores
