@@ -10,7 +10,7 @@
 //      shape allows), written to `out`;
 //   2. one CTA per pair that streams the pair's raw factors once from memory — a factor cache,
 //      or a scratch chunk that pair_factors has just filled — computes t = x_rows·B (k-slices
-//      in registers, reduced through shared memory), then u = t·(s·A)ᵀ, and finishes the rows
+//      in registers, reduced through shared memory), then u = (s·t)·Aᵀ, and finishes the rows
 //      in place: out = f(out ± u) with f the readout gain or the LIF step.
 #include <stdlib.h>
 
@@ -237,7 +237,9 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 const float4 v = red4[(size_t)p * tot4 + e4];
                 sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
-            red4[e4] = sum;  // t[r][q], r = e / rank
+            // sigma goes onto t here (rows x rank values) rather than onto A in the second phase (a x rank)
+            const float sg = g.base_sigma;
+            red4[e4] = make_float4(__fmul_rn(sum.x, sg), __fmul_rn(sum.y, sg), __fmul_rn(sum.z, sg), __fmul_rn(sum.w, sg));  // s*t[r][q], r = e / rank
         }
     }
     if (g.a_in_smem && ok) ok = mbar_wait(&bars[PP_STAGES], 0, abort_flag, g.status, 21);
@@ -256,7 +258,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const float* ts = red;
 
     if (g.a_swz) {
-        // ---- u = t * (s*A)ᵀ, swizzled A.  A warp takes a task = (8 rows, 64 columns, half of the
+        // ---- u = (s*t) * Aᵀ, swizzled A.  A warp takes a task = (8 rows, 64 columns, half of the
         // rank); a lane owns columns lane and lane + 32 of the block, so the A pieces of a load are
         // 32 different rows of one box column (conflict-free through the swizzle) and the t pieces
         // are broadcasts: 10 loads feed 64 multiply-adds.  The two rank halves of a tile swap four
@@ -292,9 +294,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const int c = q4 & 7;
                     const float4 va = *reinterpret_cast<const float4*>(box + n_a * 32 + ((c ^ (n_a & 7)) << 2));
                     const float4 vb = *reinterpret_cast<const float4*>(box + n_b * 32 + ((c ^ (n_b & 7)) << 2));
-                    const float s = g.base_sigma;
-                    const float4 sa4 = make_float4(__fmul_rn(va.x, s), __fmul_rn(va.y, s), __fmul_rn(va.z, s), __fmul_rn(va.w, s));
-                    const float4 sb4 = make_float4(__fmul_rn(vb.x, s), __fmul_rn(vb.y, s), __fmul_rn(vb.z, s), __fmul_rn(vb.w, s));
+                    const float4 sa4 = va, sb4 = vb;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const float4 tv = *reinterpret_cast<const float4*>(trow + (size_t)j * rank + q4 * 4);
@@ -373,7 +373,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         return;
     }
 
-    // ---- u = t * (s*A)ᵀ and the final transform of the rows.  A thread owns 4 rows x NC
+    // ---- u = (s*t) * Aᵀ and the final transform of the rows.  A thread owns 4 rows x NC
     // consecutive output columns; the clean product of its outputs is fetched first so that its
     // latency hides behind the multiply-adds. ----
     constexpr int NC = 2;
@@ -407,8 +407,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 const int n = n0 + c4 < a ? n0 + c4 : a - 1;   // a ragged last group repeats the last column
                 const float4* an = reinterpret_cast<const float4*>(abase + (size_t)n * rank) + q4;
                 float4 v = g.a_in_smem ? *an : __ldg(an);
-                av[c4] = make_float4(__fmul_rn(v.x, g.base_sigma), __fmul_rn(v.y, g.base_sigma),
-                                     __fmul_rn(v.z, g.base_sigma), __fmul_rn(v.w, g.base_sigma));
+                av[c4] = v;
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
