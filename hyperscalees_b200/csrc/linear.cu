@@ -5,6 +5,8 @@
 // This file holds the dispatcher and the general fp32 SIMT path, which takes
 // any shape and pitch.  The tensor-core path for tile-aligned shapes lives in
 // linear_tc.cu.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "linear.cuh"
 
@@ -312,6 +314,32 @@ static int run_simt(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     return HSES_OK;
 }
 
+// spikes (0/1 in f32, pitched rows) once more as dense fp16 rows; a is a multiple of 8
+__global__ void spikes_to_half_kernel(const float* __restrict__ src, int64_t rows, int a, int64_t stride,
+                                      __half* __restrict__ dst) {
+    const int a8 = a >> 3;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * a8) return;
+    const int64_t r = i / a8;
+    const int c = (int)(i - r * a8) * 8;
+    const float4 v0 = *reinterpret_cast<const float4*>(src + r * stride + c);
+    const float4 v1 = *reinterpret_cast<const float4*>(src + r * stride + c + 4);
+    const __half2 h0 = __floats2half2_rn(v0.x, v0.y), h1 = __floats2half2_rn(v0.z, v0.w);
+    const __half2 h2 = __floats2half2_rn(v1.x, v1.y), h3 = __floats2half2_rn(v1.z, v1.w);
+    *reinterpret_cast<uint4*>(dst + r * a + c) =
+        make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                   *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+}
+
+// does the call end in the per-pair kernel with the scan inside it (the one kernel that writes out_half itself)?
+static bool ends_in_pair_scan(const hses_linear_args& g) {
+    if (g.lif != 2) return false;
+    const bool pair_ok = pair_path_supports(g);
+    const bool takes_pair = (g.algo == HSES_ALGO_PAIR && pair_ok) ||
+                            (g.algo == HSES_ALGO_AUTO && !tensor_path_supports(g) && pair_ok);
+    return takes_pair && pair_path_fuses_scan(g);
+}
+
 }  // namespace hses
 
 using namespace hses;
@@ -345,6 +373,24 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
     HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
     int rc = check_args(g);
     if (rc != HSES_OK) return rc;
+    if (g->out_half != nullptr) {
+        HSES_REQUIRE(g->lif != 0, "out_half is the spike output of a layer with lif = 1 or 2");
+        HSES_REQUIRE(g->a % 8 == 0 && ((uintptr_t)g->out_half & 15u) == 0 && g->out_row_stride % 4 == 0 &&
+                         ((uintptr_t)g->out & 15u) == 0,
+                     "out_half needs a multiple of 8 outputs and 16-byte aligned rows");
+        if (!ends_in_pair_scan(*g)) {
+            hses_linear_args h = *g;
+            h.out_half = nullptr;
+            rc = hses_perturbed_linear(ctx, stream, &h);
+            if (rc != HSES_OK) return rc;
+            const int64_t rows = (int64_t)g->t_steps * g->n_pop * g->bm, n8 = rows * (g->a / 8);
+            HSES_KERNEL(ctx, as_stream(stream), "spikes_to_half");
+            spikes_to_half_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, as_stream(stream)>>>(
+                g->out, rows, g->a, g->out_row_stride, reinterpret_cast<__half*>(g->out_half));
+            HSES_LAUNCH_CHECK();
+            return HSES_OK;
+        }
+    }
     if (g->lif == 2) {
         HSES_REQUIRE(g->potentials == nullptr, "lif == 2 has no potentials output");
         // the same choice of path as below

@@ -14,6 +14,8 @@
 //      in place: out = f(out ± u) with f the readout gain or the LIF step.
 #include <stdlib.h>
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "linear.cuh"
 #include "tc_common.cuh"
@@ -48,6 +50,7 @@ struct PairArgs {
     float* out;
     int64_t out_stride;
     float* pot;
+    __half* out_half;  // dense fp16 copy of the spikes (row stride a), written by the fused scan
     int lif;           // 0: y * gain; 1: one LIF step from v = 0; 2: LIF scan over the steps (swizzled form only)
     int reset;
     float leak, v_th, out_scale;
@@ -367,6 +370,7 @@ pair_lowrank_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const int r = step * rows_per_step + rr;
                     const float sp = lif_update(v, ytile[r * a + n], g.leak, g.v_th, g.reset);
                     g.out[(size_t)row_s[r] * g.out_stride + n] = sp;
+                    if (g.out_half) g.out_half[(size_t)row_s[r] * a + n] = __float2half_rn(sp);
                 }
             }
         }
@@ -515,6 +519,7 @@ hses_linear_args base_call(const hses_linear_args& g) {
     b.out_scale_ptr = nullptr;
     b.potentials = nullptr;
     b.cache = nullptr;
+    b.out_half = nullptr;
     b.algo = HSES_ALGO_AUTO;
     return b;
 }
@@ -578,6 +583,7 @@ int run_pair_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     pa.out = g.out;
     pa.out_stride = g.out_row_stride;
     pa.pot = g.lif ? g.potentials : nullptr;
+    pa.out_half = g.lif == 2 ? reinterpret_cast<__half*>(g.out_half) : nullptr;
     pa.lif = g.lif;
     pa.reset = g.reset_mode;
     pa.leak = g.lif ? 1.0f / g.tau_m : 0.0f;

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "linear.cuh"
 #include "update_tc.cuh"
 
 namespace hses {
@@ -16,7 +17,7 @@ namespace {
 size_t up64(size_t v) { return (v + 63) / 64 * 64; }
 
 struct FwdPlan {
-    size_t rows, maxh, cur, spk, rate, lin_bytes, bytes;
+    size_t rows, maxh, cur, spk, rate, half, lin_bytes, bytes;
 };
 
 hses_linear_args layer_args(const hses_snn_model* m, const hses_pop_args* p, int l, bool readout) {
@@ -69,7 +70,10 @@ FwdPlan plan_forward(const hses_snn_model* m, const hses_pop_args* p) {
         f.lin_bytes = std::max(f.lin_bytes, hses_perturbed_linear_workspace_bytes(&g));
     }
     f.lin_bytes = up64(f.lin_bytes);
-    f.bytes = (f.cur + 2 * f.spk + f.rate) * sizeof(float) + f.lin_bytes;
+    // hidden layers hand their spikes to the next hidden layer as fp16 as well (its tensor-core
+    // operand): two buffers of half the size of a spike buffer, when there is such a hand-over
+    f.half = m->n_layers > 2 ? up64((f.spk + 1) / 2) : 0;
+    f.bytes = (f.cur + 2 * f.spk + f.rate + 2 * f.half) * sizeof(float) + f.lin_bytes;
     return f;
 }
 
@@ -114,16 +118,40 @@ static int snn_forward_impl(hses_ctx* ctx, hses_stream stream, const hses_snn_mo
     float* cur = reinterpret_cast<float*>(workspace);
     float* spk[2] = {cur + f.cur, cur + f.cur + f.spk};
     float* rate = cur + f.cur + 2 * f.spk;
-    void* lin_ws = rate + f.rate;
+    float* half_buf[2] = {rate + f.rate, rate + f.rate + f.half};
+    void* lin_ws = rate + f.rate + 2 * f.half;
 
     const float* layer_in = spikes_in;
     int64_t layer_in_stride = in_stride;
     const int L = m->n_layers;
+    const void* next_half = nullptr;
     for (int l = 0; l < L - 1; ++l) {
         hses_linear_args g = layer_args(m, p, l, false);
         g.x = layer_in;
         g.x_row_stride = layer_in_stride;
         if (l == 0) g.x_half = spikes_half;
+        // a hidden layer that feeds another hidden layer writes its spikes as fp16 too, and the
+        // layer after it takes that copy as the operand of its tensor-core product
+        const void* in_half = l > 0 ? next_half : nullptr;
+        if (l > 0) g.x_half = in_half;
+        next_half = nullptr;
+        if (l + 1 < L - 1 && m->dims[l + 1] % 8 == 0 && f.half) {
+            // only when the next layer's clean product is the unperturbed tensor-core one (the per-pair
+            // path's first launch, or a clean forward): the other kernels read the f32 spikes
+            hses_linear_args n = layer_args(m, p, l + 1, false);
+            n.x = spk[l & 1];
+            n.out = spk[(l + 1) & 1];
+            n.lif = 2;
+            hses_linear_args nc = n;
+            nc.perturb = 0;
+            nc.lif = 0;
+            const bool clean_tc = tensor_path_supports(nc);
+            const bool wants = n.perturb ? (!tensor_path_supports(n) && pair_path_supports(n) && clean_tc) : clean_tc;
+            if (wants) {
+                g.out_half = half_buf[l & 1];
+                next_half = half_buf[l & 1];
+            }
+        }
         // currents and the LIF scan over the T steps in one call: the per-pair path finishes the scan
         // inside its kernel (the currents never reach memory), the other paths scan `out` in place
         float* out_spk = spk[l & 1];

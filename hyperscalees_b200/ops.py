@@ -189,11 +189,13 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      reset_mode: int = RESET_HARD, out_scale: float = 1.0,
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
                      algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None, precision: int = 0,
-                     tmm: bool = False):
+                     tmm: bool = False, x_half: Optional[torch.Tensor] = None,
+                     out_half: Optional[torch.Tensor] = None):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
     the charged potentials.  With `cache` the factors are read from it instead of
-    being regenerated (same bits)."""
+    being regenerated (same bits).  x_half: x once more as dense fp16 (rows, k) when it is exact
+    there; out_half: a dense fp16 (rows, a) tensor that receives the spikes as well (lif only)."""
     _check(x, "x")
     _check(param, "param", ndim=2)
     rows, k, xs = _rows_2d(x, "x")
@@ -222,6 +224,14 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.algo = algo
     g.precision = precision
     g.factor_order = int(tmm)   # do_Tmm: param is the reference's (in, out) matrix transposed
+    if x_half is not None:
+        if x_half.dtype != torch.float16 or not x_half.is_contiguous() or x_half.numel() != rows * k:
+            raise ValueError("x_half must be a contiguous fp16 tensor of rows*k values")
+        g.x_half = x_half.data_ptr()
+    if out_half is not None:
+        if out_half.dtype != torch.float16 or not out_half.is_contiguous() or out_half.numel() != rows * a:
+            raise ValueError("out_half must be a contiguous fp16 tensor of rows*a values")
+        g.out_half = out_half.data_ptr()
     if cache is not None:
         g.cache = C.pointer(cache.desc)
     L = _lib.load()

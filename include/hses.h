@@ -231,6 +231,10 @@ typedef struct {
                            callers whose x is exact in fp16 and who have that copy anyway (the 0/1
                            spikes hses_poisson_encode_dual writes).  The tensor-core path then takes
                            it as its operand instead of converting x; x itself is still required */
+    void* out_half;     /* device or NULL: with lif = 1 or 2, the spikes once more as dense fp16 rows
+                           (rows, a), written by the kernel that finishes the layer where it can (the
+                           per-pair kernel with the fused scan), else by one conversion pass: the
+                           x_half of the layer that follows.  a must be a multiple of 8 */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

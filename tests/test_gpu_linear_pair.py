@@ -101,3 +101,29 @@ def test_fused_lif_scan_equals_linear_then_scan(n_pop, bm, k, a, rank, t_steps, 
     assert core.get_context(0).device_status() == 0
     assert 0.02 < want.mean().item() < 0.98
     assert torch.equal(got.view_as(want), want)
+
+
+@pytest.mark.parametrize("n_pop,bm,k,a,rank,t_steps,algo", [
+    (8, 1, 128, 128, 64, 8, "auto"),    # per-pair kernel with the scan inside: writes the fp16 copy itself
+    (4, 1, 36, 48, 8, 3, "auto"),       # per-pair path without the fused scan: one conversion pass
+    (8, 16, 64, 128, 4, 2, "auto"),     # tensor path: scan in place, then the conversion pass
+])
+def test_out_half_is_the_spikes_and_feeds_the_next_layer(n_pop, bm, k, a, rank, t_steps, algo):
+    """out_half receives the layer's spikes as fp16; handed to the next layer as x_half it gives the
+    bits that layer computes from the f32 spikes."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(n_pop + a)
+    x = torch.as_tensor((g.random((t_steps, n_pop, bm, k)) < 0.3).astype(np.float32), device="cuda")
+    w = torch.as_tensor((g.standard_normal((a, k)) * 3.0 / np.sqrt(k)).astype(np.float32), device="cuda")
+    kw = dict(n_pop=n_pop, bm=bm, t_steps=t_steps, sigma=0.3, rank=rank, key=0x51ED, epoch=1, tau_m=2.0, v_th=0.5)
+    rows = t_steps * n_pop * bm
+    half = torch.full((rows, a), 7.0, dtype=torch.float16, device="cuda")
+    spikes = ops.perturbed_linear(x, w, lif=2, out_half=half, **kw)
+    plain = ops.perturbed_linear(x, w, lif=2, **kw)
+    assert torch.equal(spikes, plain)
+    assert torch.equal(half.float(), spikes)
+    w2 = torch.as_tensor((g.standard_normal((128, a)) * 2.0 / np.sqrt(a)).astype(np.float32), device="cuda")
+    kw2 = dict(kw, key=0x77)
+    nxt = ops.perturbed_linear(spikes, w2, lif=2, **kw2)
+    nxt_h = ops.perturbed_linear(spikes, w2, lif=2, x_half=half, **kw2)
+    assert torch.equal(nxt, nxt_h)
