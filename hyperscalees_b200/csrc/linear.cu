@@ -331,6 +331,16 @@ __global__ void spikes_to_half_kernel(const float* __restrict__ src, int64_t row
                    *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
 }
 
+// Narrow layers (at most 64 inputs and outputs) stay on the kernel that keeps W in shared memory when a
+// pair owns few rows, or when the factors have to be regenerated (the tensor-core path regenerates the
+// output-side factor once per 128-row tile: with thousands of rows per pair that is the same few values
+// over and over, each time behind a jump into the stream).  With a factor cache and many rows per pair
+// the tensor-core path, which also takes narrow outputs, is the faster one.
+static bool prefers_small_path(const hses_linear_args& g) {
+    if (g.algo != HSES_ALGO_AUTO || g.lif == 2 || !small_path_supports(g)) return false;
+    return (int64_t)2 * g.bm * g.t_steps <= 256 || (g.perturb && g.cache == nullptr);
+}
+
 // does the call end in the per-pair kernel with the scan inside it (the one kernel that writes out_half itself)?
 static bool ends_in_pair_scan(const hses_linear_args& g) {
     if (g.lif != 2) return false;
@@ -360,6 +370,7 @@ size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     }
     // the tensor path always needs room for the split weights, the general path
     // only needs scratch when it perturbs
+    if (prefers_small_path(*g)) return small_path_workspace_bytes(*g);
     if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_TENSOR) && tensor_path_supports(*g))
         return tensor_path_workspace_bytes(*g);
     if (g->algo == HSES_ALGO_AUTO && small_path_supports(*g)) return small_path_workspace_bytes(*g);
@@ -409,6 +420,7 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
         return hses_lif_scan(ctx, stream, g->out, g->t_steps, g->n_pop * g->bm, g->a, g->out_row_stride, nullptr,
                              g->tau_m, g->v_th, g->reset_mode, g->out);
     }
+    if (prefers_small_path(*g)) return run_small_path(ctx, as_stream(stream), *g);
     bool tc_ok = tensor_path_supports(*g);
     if (g->algo == HSES_ALGO_TENSOR && !tc_ok) {
         set_error("hses_perturbed_linear: the tensor-core path does not cover this shape");

@@ -138,7 +138,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (int)(g.rows / BM_TILE);
-    const int n_chunks = g.a / BN;
+    const int n_chunks = (g.a + BN - 1) / BN;   // columns past a in the last chunk: zero rows of W (TMA fill), never stored
     const int k_blocks = (g.k + BK - 1) / BK;  // a ragged last block is zero-filled by TMA
 
     if (threadIdx.x == 0) {
@@ -291,6 +291,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                 tc_fence_after();
                 for (int cb = 0; cb < BN / 32 && ok; ++cb) {
                     const int n0 = c * BN + cb * 32 + eh * 16;   // first of this warp's sixteen columns
+                    if (n0 >= g.a) continue;                     // ragged last chunk: no such columns, no such item
                     const float* my_a = nullptr;
                     int slot = 0;
                     if (RG > 0) {
@@ -607,7 +608,34 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
         lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     };
-    if (n4 <= 256) {
+    if (n4 <= 32) {
+        // short rows (up to 128 values): one 16-byte piece per lane covers a row, so a warp keeps eight
+        // rows in flight, one trip to memory for all of them
+        for (int lr0 = warp * 8; lr0 < total_rows; lr0 += 8 * (LT_THREADS / 32)) {
+            float4 v[8];
+            int64_t R[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool valid = lr0 + j < total_rows;   // warp-uniform
+                R[j] = row_s[valid ? lr0 + j : lr0];
+                v[j] = (valid && lane < n4) ? __ldg(reinterpret_cast<const float4*>(x + (size_t)R[j] * x_stride) + lane)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (lr0 + j >= total_rows) break;
+                const float m = fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w)));
+                float sc;
+                finish_row(R[j], m, sc);
+                if (lane < n4) {
+                    uint2 h2, l2;
+                    split4(v[j], sc, h2, l2);
+                    reinterpret_cast<uint2*>(xhi + (size_t)R[j] * k)[lane] = h2;
+                    if (!bf16) reinterpret_cast<uint2*>(xlo + (size_t)R[j] * k)[lane] = l2;
+                }
+            }
+        }
+    } else if (n4 <= 256) {
         // rows of up to 1024 values stay in registers between the maximum and the conversion, and a
         // warp keeps two rows in flight: one trip to memory per row instead of two dependent ones
         for (int lr = warp; lr < total_rows; lr += 2 * (LT_THREADS / 32)) {
@@ -679,6 +707,32 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         atomicOr(lo_flag, 1);
 
     // ---- t = x * B ----
+    if (k <= 128 && cache_b != nullptr && rank_true >= 4) {
+        // Short rows with the factors at hand (a layer of a model whose members own thousands of rows):
+        // the whole of B is one block, and a k-slice layout would spend more on adding the slices than on
+        // the products.  Four threads share a row, each owns RANK/4 columns of t and walks over k in order.
+        const float4* cb = reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK);
+        for (int i = tid; i < k * RANK_G; i += LT_THREADS) reinterpret_cast<float4*>(bs)[i] = __ldg(cb + i);
+        __syncthreads();
+        const int lr = tid >> 2, q0 = (tid & 3) * RANK_G;   // row of the CTA, first of this thread's columns
+        if (lr < total_rows) {
+            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row_s[lr] * x_stride);
+            float acc[RANK_G];
+#pragma unroll
+            for (int j = 0; j < RANK_G; ++j) acc[j] = 0.0f;
+            for (int k4 = 0; k4 < n4; ++k4) {
+                const float4 xv = __ldg(xr + k4);
+                const float xs4[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int j = 0; j < RANK_G; ++j) acc[j] = fmaf(xs4[u], bs[(4 * k4 + u) * RANK + q0 + j], acc[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < RANK_G; ++j) t[(size_t)row_s[lr] * RANK + q0 + j] = acc[j];
+        }
+        return;
+    }
     const int n_tiles = (total_rows + 7) >> 3;                     // 1..8
     const int ksplit = n_tiles <= 1 ? 8 : n_tiles <= 2 ? 4 : n_tiles <= 4 ? 2 : 1;
     const bool active = warp < n_tiles * ksplit;
@@ -899,7 +953,11 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
 bool tensor_path_supports(const hses_linear_args& g) {
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
-    if (rows % BM_TILE != 0 || g.k % 8 != 0 || g.a % 128 != 0) return false;
+    if (rows % BM_TILE != 0 || g.k % 8 != 0) return false;
+    // Output columns come in 16-column pieces per epilogue warp and 16- or 32-column ring items; a
+    // ragged last chunk is fine as long as every ring slot keeps one reader: whole 32-column blocks,
+    // or a single 16-column item per tile
+    if (g.a % 32 != 0 && !(g.a == 16 && (!g.perturb || g.rank >= 8))) return false;
     if (g.x_row_stride % 4 != 0 || g.out_row_stride % 4 != 0 || g.param_row_stride % 4 != 0) return false;
     if (!aligned16(g.x) || !aligned16(g.param) || !aligned16(g.out) || (g.potentials && !aligned16(g.potentials))) return false;
     if (g.k > (1 << 20) || g.a > (1 << 20)) return false;

@@ -101,6 +101,13 @@ class SpikingLM:
         if noise is not None:
             kw = dict(sigma=noise.sigma, rank=noise.rank, key=noise.base_keys[idx], epoch=noise.epoch,
                       first_thread=noise.first_thread, noise_reuse=noise.noise_reuse)
+            if noise.first_thread % 2 == 0 and n % 2 == 0:
+                # A member owns thousands of rows here and its factors a few hundred values: they are
+                # generated once per call into a factor cache (same bits as regenerating them in the
+                # kernels), which lets narrow layers take the tensor-core path as well
+                a, k = w.shape
+                kw["cache"] = ops.FactorCache(noise.base_keys[idx], noise.epoch, noise.noise_reuse, noise.rank, a, k,
+                                              n // 2, first_pair=noise.first_thread // 2, device=self.device)
         return ops.perturbed_linear(x, w, n_pop=n, bm=rows_per_member, perturb=noise is not None, out=out, **kw)
 
     def forward_population(self, ids: torch.Tensor, noise: Optional[LmNoise] = None) -> torch.Tensor:

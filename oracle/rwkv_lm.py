@@ -33,11 +33,11 @@ def layer_norm(x, wb):
 def product(x, w_out_in, noise, key, tmm, rows_in_call=None):
     """x (T, in), weight held (out, in).  noise = (sigma, rank, epoch, thread_id, noise_reuse) or None.
     The operands are rounded to bf16 where the library's bf16 product exists (its tensor-core
-    kernel: output width a multiple of 128, input width a multiple of 8, the call's rows a multiple
-    of 128); the narrow first stages of the TMM pairs are fp32 products."""
+    kernel: output width a multiple of 32, input width a multiple of 8, the call's rows a multiple
+    of 128); anything else is an fp32 product."""
     out_dim, in_dim = w_out_in.shape
     rows = x.shape[0] if rows_in_call is None else rows_in_call
-    if out_dim % 128 == 0 and in_dim % 8 == 0 and rows % 128 == 0:
+    if out_dim % 32 == 0 and in_dim % 8 == 0 and rows % 128 == 0:
         base = (bf16r(x).astype(np.float64) @ bf16r(w_out_in).astype(np.float64).T)
     else:
         base = x.astype(np.float64) @ w_out_in.astype(np.float64).T

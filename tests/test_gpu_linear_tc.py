@@ -25,6 +25,12 @@ def status_ok():
     (4, 32, 96, 128, 8, 1, 1),      # bm = 32: one member per warp slice, odd first member
     (2, 64, 800, 128, 4, 2, 0),     # SNN-like first layer (k = 800 = 25 k-blocks)
     (40, 16, 64, 384, 4, 1, 0),     # more tiles than one wave would need on a small grid? no: exercises a = 3*128
+    (4, 64, 64, 16, 8, 1, 0),       # one 16-column item per tile (a per-head projection): the other columns of the
+                                    # 128-wide MMA are zero rows of W and are never stored
+    (4, 32, 256, 64, 8, 2, 2),      # a = 64: half a column tile, 16-column items
+    (8, 32, 64, 96, 4, 1, 0),       # a = 96 with 32-column items (rank 4): three items per tile
+    (8, 16, 96, 160, 16, 1, 0),     # two chunks of 128, the second one ragged
+    (4, 64, 128, 320, 1, 1, 0),     # rank 1 (as rank 4), three chunks of 128, the last one half used
 ])
 def test_tensor_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
