@@ -928,7 +928,8 @@ def main():
                          "captures); population_step: members of the whole population")
     ap.add_argument("--chunk", type=int, default=1024, help="spiking_lm: members evaluated per pass")
     ap.add_argument("--shrink", type=int, default=1,
-                    help="streaming_kernels: divide every case's leading dimension (reduced cases for ncu captures)")
+                    help="streaming_kernels, einsum_pair: divide every case's leading dimension (reduced cases for "
+                         "ncu captures)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs and the extra blocks (profiling runs)")
     ap.add_argument("--headline-only", action="store_true",
@@ -961,7 +962,8 @@ def main():
             from hyperscalees_b200 import core
             dev = torch.device("cuda", local_rank)
             torch.cuda.set_device(dev)
-            blk = einsum_pair_block(dev, core.get_context(local_rank), args.steps, args.warmup)
+            blk = einsum_pair_block(dev, core.get_context(local_rank), args.steps, args.warmup,
+                                    half=6000 // max(1, args.shrink))
             print(json.dumps({"workload": "einsum_pair", **blk}), flush=True)
     else:
         run_ours(args, rank, local_rank, world)
