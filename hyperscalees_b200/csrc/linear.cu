@@ -332,13 +332,13 @@ __global__ void spikes_to_half_kernel(const float* __restrict__ src, int64_t row
 }
 
 // Narrow layers (at most 64 inputs and outputs) stay on the kernel that keeps W in shared memory when a
-// pair owns few rows, or when the factors have to be regenerated (the tensor-core path regenerates the
-// output-side factor once per 128-row tile: with thousands of rows per pair that is the same few values
-// over and over, each time behind a jump into the stream).  With a factor cache and many rows per pair
-// the tensor-core path, which also takes narrow outputs, is the faster one.
+// pair owns few rows; with many rows per pair the tensor-core path, which also takes narrow outputs, is
+// the faster one — by 2.4x when the factors come from a cache; when they have to be regenerated it
+// regenerates the output-side factor once per 128-row tile and is the slower one, but the choice must
+// not depend on the cache: a call with and without one returns the same bits.
 static bool prefers_small_path(const hses_linear_args& g) {
     if (g.algo != HSES_ALGO_AUTO || g.lif == 2 || !small_path_supports(g)) return false;
-    return (int64_t)2 * g.bm * g.t_steps <= 256 || (g.perturb && g.cache == nullptr);
+    return (int64_t)2 * g.bm * g.t_steps <= 256;
 }
 
 // does the call end in the per-pair kernel with the scan inside it (the one kernel that writes out_half itself)?

@@ -707,32 +707,6 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         atomicOr(lo_flag, 1);
 
     // ---- t = x * B ----
-    if (k <= 128 && cache_b != nullptr && rank_true >= 4) {
-        // Short rows with the factors at hand (a layer of a model whose members own thousands of rows):
-        // the whole of B is one block, and a k-slice layout would spend more on adding the slices than on
-        // the products.  Four threads share a row, each owns RANK/4 columns of t and walks over k in order.
-        const float4* cb = reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK);
-        for (int i = tid; i < k * RANK_G; i += LT_THREADS) reinterpret_cast<float4*>(bs)[i] = __ldg(cb + i);
-        __syncthreads();
-        const int lr = tid >> 2, q0 = (tid & 3) * RANK_G;   // row of the CTA, first of this thread's columns
-        if (lr < total_rows) {
-            const float4* xr = reinterpret_cast<const float4*>(x + (size_t)row_s[lr] * x_stride);
-            float acc[RANK_G];
-#pragma unroll
-            for (int j = 0; j < RANK_G; ++j) acc[j] = 0.0f;
-            for (int k4 = 0; k4 < n4; ++k4) {
-                const float4 xv = __ldg(xr + k4);
-                const float xs4[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int j = 0; j < RANK_G; ++j) acc[j] = fmaf(xs4[u], bs[(4 * k4 + u) * RANK + q0 + j], acc[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < RANK_G; ++j) t[(size_t)row_s[lr] * RANK + q0 + j] = acc[j];
-        }
-        return;
-    }
     const int n_tiles = (total_rows + 7) >> 3;                     // 1..8
     const int ksplit = n_tiles <= 1 ? 8 : n_tiles <= 2 ? 4 : n_tiles <= 4 ? 2 : 1;
     const bool active = warp < n_tiles * ksplit;

@@ -240,30 +240,21 @@ struct Rounded {
     uint32_t dist;   // |low29 - 2^28|: 0 at the midpoint, 2^28 on an fp32 value
 };
 HSES_HD Rounded round_candidate(double y) {
+    // The rounding itself is the hardware's fp64 -> fp32 conversion (the conversion pipe is nearly idle
+    // in this code, the integer pipe is what bounds it).  The other neighbour lies one step up in
+    // magnitude when the discarded bits are below the midpoint and one step down otherwise.  An exact
+    // midpoint would make that rule name the wrong neighbour for an even mantissa; the candidates
+    // (logarithms and cosines of fp32 arguments) never are, and the calibration would refuse a
+    // context in which the host's value is neither `bits` nor `alt`.
     Rounded r;
 #if defined(__CUDA_ARCH__)
-    // Word-wise form of the code below.  The fp32 exponent field is the low
-    // eight bits of the fp64 one with bit 7 inverted (the biases differ by 896);
-    // rounding to nearest-even is an integer increment of the truncated pattern.
-    uint32_t hi = (uint32_t)__double2hiint(y), lo = (uint32_t)__double2loint(y);
-    uint32_t low = lo & 0x1fffffffu;
-    uint32_t fs = __funnelshift_l(lo, hi, 3);
-    uint32_t trunc = ((fs ^ 0x40000000u) & 0x7fffffffu) | (hi & 0x80000000u);
-    uint32_t up = (low + (trunc & 1u)) > 0x10000000u ? 1u : 0u;
-    r.bits = trunc + up;
-    r.alt = trunc + 1u - up;
-    r.dist = (uint32_t)abs((int32_t)low - 0x10000000);
+    const uint32_t low = (uint32_t)__double2loint(y) & 0x1fffffffu;
 #else
-    uint64_t yb = d2u(y);
-    uint32_t low = (uint32_t)(yb & 0x1fffffffull);
-    r.bits = f2u(d2f_rn(y));
-    // truncated fp32 pattern: rebias the exponent (1023 -> 127), keep 23 bits
-    uint32_t sign = (uint32_t)(yb >> 63) << 31;
-    uint32_t ex = (uint32_t)((yb >> 52) & 0x7ff) - 896u;
-    uint32_t trunc = sign | (ex << 23) | (uint32_t)((yb >> 29) & 0x7fffffu);
-    r.alt = (r.bits == trunc) ? trunc + 1u : trunc;
-    r.dist = low >= 0x10000000u ? low - 0x10000000u : 0x10000000u - low;
+    const uint32_t low = (uint32_t)(d2u(y) & 0x1fffffffull);
 #endif
+    r.bits = f2u(d2f_rn(y));
+    r.alt = low >= 0x10000000u ? r.bits - 1u : r.bits + 1u;
+    r.dist = low >= 0x10000000u ? low - 0x10000000u : 0x10000000u - low;
     return r;
 }
 
