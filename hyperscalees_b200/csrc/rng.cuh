@@ -236,8 +236,9 @@ HSES_HD double cos_candidate(float theta) {
 // the rounding midpoint.
 struct Rounded {
     uint32_t bits;   // round-to-nearest result
-    uint32_t alt;    // the other bracketing fp32 value
+    uint32_t alt;    // the other bracketing fp32 value: bits + step
     uint32_t dist;   // |low29 - 2^28|: 0 at the midpoint, 2^28 on an fp32 value
+    int32_t step;    // +1 or -1
 };
 HSES_HD Rounded round_candidate(double y) {
     // The rounding itself is the hardware's fp64 -> fp32 conversion (the conversion pipe is nearly idle
@@ -253,9 +254,19 @@ HSES_HD Rounded round_candidate(double y) {
     const uint32_t low = (uint32_t)(d2u(y) & 0x1fffffffull);
 #endif
     r.bits = f2u(d2f_rn(y));
-    r.alt = low >= 0x10000000u ? r.bits - 1u : r.bits + 1u;
+    r.step = low >= 0x10000000u ? -1 : 1;
+    r.alt = r.bits + (uint32_t)r.step;
     r.dist = low >= 0x10000000u ? low - 0x10000000u : 0x10000000u - low;
     return r;
+}
+
+// bit (i mod 32) of a bitmap word
+HSES_HD uint32_t bit_of(uint32_t word, uint32_t i) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_r(word, 0u, i) & 1u;   // the funnel shift takes its count modulo 32
+#else
+    return (word >> (i & 31u)) & 1u;
+#endif
 }
 
 HSES_HD float apply_flip(const Rounded& r, uint32_t idx, const uint32_t* __restrict__ flip,
@@ -340,8 +351,10 @@ HSES_HD void next_normals4_t(uint64_t& state, const LibmCal& cal, float (&out)[4
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         uint32_t i = iu[j] ? iu[j] : 1u;
-        uint32_t lb = ((wl[j] >> (i & 31u)) & 1u) ? rl[j].alt : rl[j].bits;
-        uint32_t cb = ((wc[j] >> (ju[j] & 31u)) & 1u) ? rc[j].alt : rc[j].bits;
+        // the bitmap's bit times the step to the other neighbour: a multiply-add (FMA pipe) instead of
+        // a compare and a select (integer pipe, the one that bounds this code)
+        uint32_t lb = rl[j].bits + (uint32_t)((int32_t)bit_of(wl[j], i) * rl[j].step);
+        uint32_t cb = rc[j].bits + (uint32_t)((int32_t)bit_of(wc[j], ju[j]) * rc[j].step);
         float lg = iu[j] ? u2f(lb) : cal.log_of_zero;
         out[j] = fmul(fsqrt(fmul(-2.0f, lg)), u2f(cb));
     }
