@@ -283,6 +283,40 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                   "cache_build_ms": build_ms,
                   "note": "factors read from a device cache built once outside the timed region"}
         del cache
+    # What bounds the dominant kernel: the clean product alone, and the regeneration of the step's
+    # factors alone (the kernel regenerates the output-side half inside its epilogue), both timed here
+    floors = None
+    if rank == 0:
+        def clean_step():
+            ops.perturbed_linear(x_dev, w_dev, n_pop=N_POP, bm=BM, perturb=False, lif=True, tau_m=TAU_M, v_th=V_TH,
+                                 out=out_dev)
+
+        def regen_all():
+            ops.FactorCache(KEY, 0, 0, RANK, A_DIM, K_DIM, n_pairs=N_POP // 2, first_pair=first_thread // 2, device=dev)
+
+        for fn in (clean_step, regen_all):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        for _ in range(5):
+            clean_step()
+        e[1].record()
+        for _ in range(5):
+            regen_all()
+        e[2].record()
+        torch.cuda.synchronize()
+        normals = (N_POP // 2) * (A_DIM + K_DIM) * RANK
+        regen_ms = e[1].elapsed_time(e[2]) / 5
+        floors = {"clean_product_step_ms": e[0].elapsed_time(e[1]) / 5,
+                  "regenerate_all_factors_ms": regen_ms, "normals_per_step": normals,
+                  "generator_G_normals_per_s": normals / (regen_ms * 1e-3) / 1e9,
+                  "note": "the step without noise (operand split + GEMM + LIF), and one stand-alone pass that "
+                          "regenerates every factor of the step bit-exactly (about 146 instructions per normal); the "
+                          "step's kernels do both, half of the factors in each of its two launches"}
+    if world > 1:
+        dist.barrier()
     # ---- the two extra blocks of the line (see the module docstring) ----
     pop_block, stream_block, lm_block, rwkv_block, einsum_block = None, None, None, None, None
     if not args.kernel_only and not args.headline_only:
@@ -335,6 +369,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                                       "scaled by the members of one launch; not measured in this run",
                     "algorithmic_flops_per_launch": flops,
                     "avg_launch_ms": per_launch_s * 1e3,
+                    "floors": floors,
                     "kernel_time_share": {k: round(v[1] / sum(p[1] for p in prof.values()), 4) for k, v in prof.items()}}
         cpu = None
         if world == 1 and not args.kernel_only:
@@ -618,7 +653,9 @@ def streaming_block(dev, ctx, steps: int, warmup: int, shrink: int = 1, only=Non
     def run(name, build):
         if only is not None and not any(name.startswith(p) for p in only):
             return
-        fn, nbytes = build()
+        built = build()
+        fn, nbytes = built[0], built[1]
+        fmas = built[2] if len(built) > 2 else None
         for _ in range(max(warmup, 3)):
             fn()
         torch.cuda.synchronize()
@@ -632,6 +669,14 @@ def streaming_block(dev, ctx, steps: int, warmup: int, shrink: int = 1, only=Non
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": round(ms, 4), "algorithmic_MB": round(nbytes / 1e6, 1), "GB_per_s": round(gbs, 1),
                      "frac_of_measured_hbm": round(gbs / peaks["hbm_gbs"], 3)}
+        if fmas is not None:
+            # kernels whose arithmetic, not their bytes, sets the floor: fp32 multiply-adds against the
+            # rate of the fp32 pipes (SMs x 128 lanes x the device's SM clock limit)
+            props = torch.cuda.get_device_properties(dev)
+            khz = getattr(props, "clock_rate", 0) or 1965000   # the device's SM clock limit, kHz
+            peak = props.multi_processor_count * 128 * khz * 1e3
+            out[name]["algorithmic_GFMA"] = round(fmas / 1e9, 2)
+            out[name]["frac_of_fp32_fma_peak"] = round(fmas / (ms * 1e-3) / peak, 3)
         del fn
         torch.cuda.empty_cache()
 
@@ -650,14 +695,18 @@ def streaming_block(dev, ctx, steps: int, warmup: int, shrink: int = 1, only=Non
     def attention(mode):
         def build():
             q, k, v = rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64), rnd(32768 // sh, 64, 64)
-            return (lambda: ops.spiking_attention(q, k, v, 4, mode=mode)), 4 * q.numel() * 4
+            # per head and sequence: scores 64 x 64 x 16 and the weighted sum 64 x 64 x 16
+            fm = (32768 // sh) * 4 * 2 * 64 * 64 * 16
+            return (lambda: ops.spiking_attention(q, k, v, 4, mode=mode)), 4 * q.numel() * 4, fm
         return build
 
     def wkv():
         wk = [rnd(256 // sh, 256, 12, 64) * 0.5 for _ in range(6)]
         wk[1] = 0.9 + 0.1 * wk[1]
         state = torch.zeros(256 // sh, 12, 64, 64, device=dev)
-        return (lambda: ops.wkv7(*wk, state)), 7 * wk[0].numel() * 4 + 2 * state.numel() * 4
+        # per token and head: decay, (S a) b^T, v k^T on the 64 x 64 state, S a and the readout S r
+        fm = (256 // sh) * 256 * 12 * 5 * 64 * 64
+        return (lambda: ops.wkv7(*wk, state)), 7 * wk[0].numel() * 4 + 2 * state.numel() * 4, fm
 
     def norm(kind):
         def build():
