@@ -607,51 +607,71 @@ __global__ void group_stats_norm_kernel(const float* __restrict__ x, int64_t n_g
 // The same statistics for groups of `cnt` contiguous values with l == 1, cnt a multiple of 4 and
 // 16-byte aligned groups: LPG lanes (a power of two <= 32) share a group, every lane keeps its
 // 16-byte pieces in registers between the statistics and the normalisation, so x is read once.
-template <int LPG, int NV>
+// A lane group walks over GPT consecutive groups with all their loads issued first: a short group
+// (64 values are one 16-byte piece per lane) would otherwise leave one load in flight per thread.
+template <int LPG, int NV, int GPT>
 __global__ void __launch_bounds__(256)
 group_norm_regs_kernel(const float* __restrict__ x, int64_t n_groups_total, int groups, int cnt,
                        const float* __restrict__ weight, const float* __restrict__ bias, float eps,
                        float* __restrict__ out) {
     constexpr int GPB = 256 / LPG;
     const int sub = threadIdx.x / LPG, lane = threadIdx.x % LPG;
-    int64_t gidx = (int64_t)blockIdx.x * GPB + sub;
-    const bool live = gidx < n_groups_total;
-    if (!live) gidx = n_groups_total - 1;   // keep the lanes of a warp together for the shuffles
+    const int64_t g0 = ((int64_t)blockIdx.x * GPB + sub) * GPT;
     const int n4 = cnt / 4;
-    const float4* xg = reinterpret_cast<const float4*>(x + (size_t)gidx * cnt);
-    float4 v[NV];
-    float sum = 0.0f, sumsq = 0.0f;
+    float4 v[GPT][NV];
+    float sum[GPT], sumsq[GPT];
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-        const int j = lane + u * LPG;
-        v[u] = j < n4 ? xg[j] : make_float4(0.f, 0.f, 0.f, 0.f);
-        sum += (v[u].x + v[u].y) + (v[u].z + v[u].w);
-        sumsq = fmaf(v[u].x, v[u].x, fmaf(v[u].y, v[u].y, fmaf(v[u].z, v[u].z, fmaf(v[u].w, v[u].w, sumsq))));
+    for (int t = 0; t < GPT; ++t) {
+        int64_t gidx = g0 + t;
+        if (gidx >= n_groups_total) gidx = n_groups_total - 1;   // keep the lanes of a warp together for the shuffles
+        const float4* xg = reinterpret_cast<const float4*>(x + (size_t)gidx * cnt);
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int j = lane + u * LPG;
+            v[t][u] = j < n4 ? xg[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
 #pragma unroll
-    for (int off = LPG / 2; off > 0; off >>= 1) {
-        sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        sumsq += __shfl_xor_sync(0xffffffffu, sumsq, off);
-    }
-    if (!live) return;
-    const float mean = __fdiv_rn(sum, (float)cnt);
-    const float var = __fsub_rn(__fdiv_rn(sumsq, (float)cnt), __fmul_rn(mean, mean));
-    const float sd = __fsqrt_rn(__fadd_rn(var, eps));
-    const int g = (int)(gidx % groups);
-    const float4* w4 = reinterpret_cast<const float4*>(weight + (size_t)g * cnt);
-    const float4* b4 = reinterpret_cast<const float4*>(bias + (size_t)g * cnt);
-    float4* og = reinterpret_cast<float4*>(out + (size_t)gidx * cnt);
+    for (int t = 0; t < GPT; ++t) {
+        sum[t] = 0.0f;
+        sumsq[t] = 0.0f;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-        const int j = lane + u * LPG;
-        if (j < n4) {
-            const float4 w = w4[j], b = b4[j];
-            float4 o;
-            o.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].x, mean), sd), w.x), b.x);
-            o.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].y, mean), sd), w.y), b.y);
-            o.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].z, mean), sd), w.z), b.z);
-            o.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[u].w, mean), sd), w.w), b.w);
-            og[j] = o;
+        for (int u = 0; u < NV; ++u) {
+            sum[t] += (v[t][u].x + v[t][u].y) + (v[t][u].z + v[t][u].w);
+            sumsq[t] = fmaf(v[t][u].x, v[t][u].x, fmaf(v[t][u].y, v[t][u].y,
+                            fmaf(v[t][u].z, v[t][u].z, fmaf(v[t][u].w, v[t][u].w, sumsq[t]))));
+        }
+#pragma unroll
+        for (int off = LPG / 2; off > 0; off >>= 1) {
+            sum[t] += __shfl_xor_sync(0xffffffffu, sum[t], off);
+            sumsq[t] += __shfl_xor_sync(0xffffffffu, sumsq[t], off);
+        }
+    }
+    // the group's position in its row, once per thread (a 64-bit remainder per group would cost as much
+    // as the normalisation of a short group)
+    int g = n_groups_total <= 0xffffffffll ? (int)((uint32_t)g0 % (uint32_t)groups) : (int)(g0 % groups);
+#pragma unroll
+    for (int t = 0; t < GPT; ++t, g = g + 1 == groups ? 0 : g + 1) {
+        const int64_t gidx = g0 + t;
+        if (gidx >= n_groups_total) break;
+        const float mean = __fdiv_rn(sum[t], (float)cnt);
+        const float var = __fsub_rn(__fdiv_rn(sumsq[t], (float)cnt), __fmul_rn(mean, mean));
+        const float sd = __fsqrt_rn(__fadd_rn(var, eps));
+        const float4* w4 = reinterpret_cast<const float4*>(weight + (size_t)g * cnt);
+        const float4* b4 = reinterpret_cast<const float4*>(bias + (size_t)g * cnt);
+        float4* og = reinterpret_cast<float4*>(out + (size_t)gidx * cnt);
+#pragma unroll
+        for (int u = 0; u < NV; ++u) {
+            const int j = lane + u * LPG;
+            if (j < n4) {
+                const float4 w = w4[j], b = b4[j];
+                float4 o;
+                o.x = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[t][u].x, mean), sd), w.x), b.x);
+                o.y = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[t][u].y, mean), sd), w.y), b.y);
+                o.z = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[t][u].z, mean), sd), w.z), b.z);
+                o.w = __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(v[t][u].w, mean), sd), w.w), b.w);
+                og[j] = o;
+            }
         }
     }
 }
@@ -662,16 +682,16 @@ static bool launch_group_norm_regs(cudaStream_t st, const float* x, int64_t tota
     if (cnt % 4 != 0 || cnt > 1024) return false;
     if ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)weight | (uintptr_t)bias) & 15u) != 0) return false;
     const int n4 = cnt / 4;
-#define HSES_GN(LPG, NV)                                                                                         \
-    group_norm_regs_kernel<LPG, NV><<<(unsigned)((total + 256 / LPG - 1) / (256 / LPG)), 256, 0, st>>>(          \
-        x, total, groups, cnt, weight, bias, eps, out)
-    if (n4 <= 4) HSES_GN(4, 1);
-    else if (n4 <= 8) HSES_GN(8, 1);
-    else if (n4 <= 16) HSES_GN(16, 1);
-    else if (n4 <= 32) HSES_GN(32, 1);
-    else if (n4 <= 64) HSES_GN(32, 2);
-    else if (n4 <= 128) HSES_GN(32, 4);
-    else HSES_GN(32, 8);
+#define HSES_GN(LPG, NV, GPT)                                                                                    \
+    group_norm_regs_kernel<LPG, NV, GPT><<<(unsigned)((total + (256 / LPG) * GPT - 1) / ((256 / LPG) * GPT)), 256, 0, \
+                                           st>>>(x, total, groups, cnt, weight, bias, eps, out)
+    if (n4 <= 4) HSES_GN(4, 1, 4);
+    else if (n4 <= 8) HSES_GN(8, 1, 4);
+    else if (n4 <= 16) HSES_GN(16, 1, 4);
+    else if (n4 <= 32) HSES_GN(32, 1, 4);
+    else if (n4 <= 64) HSES_GN(32, 2, 2);
+    else if (n4 <= 128) HSES_GN(32, 4, 1);
+    else HSES_GN(32, 8, 1);
 #undef HSES_GN
     return true;
 }
