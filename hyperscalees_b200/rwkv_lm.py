@@ -106,6 +106,12 @@ class RwkvLM:
         if noise is not None:
             kw = dict(sigma=noise.sigma, rank=noise.rank, key=self.keys[layer][name], epoch=noise.epoch,
                       first_thread=noise.first_thread, noise_reuse=noise.noise_reuse, tmm=tmm)
+            if not tmm and noise.first_thread % 2 == 0 and n % 2 == 0:
+                # a member owns T rows and its rank-r factors a few thousand values: generated once per call
+                # into a factor cache (the bits the kernels would regenerate tile by tile)
+                a, k = w.shape
+                kw["cache"] = ops.FactorCache(self.keys[layer][name], noise.epoch, noise.noise_reuse, noise.rank, a, k,
+                                              n // 2, first_pair=noise.first_thread // 2, device=self.device)
         return ops.perturbed_linear(x, w, n_pop=n, bm=T, perturb=noise is not None, precision=ops.PRECISION_BF16, **kw)
 
     def forward_hidden(self, ids: torch.Tensor, noise: Optional[LmNoise] = None) -> torch.Tensor:
