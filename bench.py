@@ -822,7 +822,7 @@ def run_spiking_lm(args, local_rank: int):
 
 
 def rwkv_lm_block(rank: int, world: int, dev, ctx, comm, n_pop: int, steps: int, warmup: int,
-                  chunk_members: int = 128):
+                  chunk_members: int = 1024):
     """BASELINE's RWKV-style LM: 12 layers, d_model 768, vocab 50 277, context 256, bf16 weights
     N(0, 0.02) with fp32 state and accumulation, rank-1 noise on every block matrix, one sequence of
     uniform token ids per member; one step = the mean next-token log-likelihood of every member,
