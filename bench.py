@@ -452,7 +452,7 @@ def pop_inputs(n_total: int, bm: int):
 
 
 def population_step_case(rank: int, world: int, dev, ctx, comm, n_total: int, bm: int, r: int, cache: str,
-                         steps: int, warmup: int, check: bool, single_gpu_leg: bool):
+                         steps: int, warmup: int, check: bool, single_gpu_leg: bool, exchange: str = "nccl"):
     """One full ES step of the spiking MLP, the population split over the ranks (strong scaling).
     Per step and rank: encode -> forward -> fitness of its members; all-gather of the raw fitness;
     z-score; contraction of its own members' factors; ONE sum of the flat gradient buffer; the same
@@ -474,9 +474,13 @@ def population_step_case(rank: int, world: int, dev, ctx, comm, n_total: int, bm
         return models.PopulationStep(net, frozen, nz, keys, POP_T, n_local, bm, first_thread=first,
                                      cache=cache_policy, n_total=n_total if whole else None)
 
+    # exchange "peer": the fitness vector travels through the library's peer-memory kernels (stores into
+    # every rank's window over NVLink, a bounded wait) instead of the all-gather
+    px = parallel.PeerExchange(n_total, ctx) if (exchange == "peer" and world > 1) else None
+
     def sharded_step(st):
         raw = st.eval(di, dl, [1, 2, 3, 4 + rank])
-        full = parallel.allgather_fitness(raw, n_total, comm=comm)
+        full = px.exchange(raw) if px is not None else parallel.allgather_fitness(raw, n_total, comm=comm)
         st.update_sharded(full, comm=comm)
         return full
 
@@ -567,8 +571,13 @@ def population_step_case(rank: int, world: int, dev, ctx, comm, n_total: int, bm
                   "gpu_launches_per_step": launches / steps,
                   "kernel_ms_per_step": {k: round(v[1] / steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][1])},
                   "collective_ms_per_step": round(sum(v[1] for k, v in prof.items()
-                                                      if k in ("allgather_fitness", "allreduce_grads")) / steps, 4),
+                                                      if k in ("allgather_fitness", "allreduce_grads", "fitness_exchange",
+                                                               "fitness_wait")) / steps, 4),
+                  "fitness_exchange": "peer memory (hses_fitness_exchange)" if px is not None
+                  else "all-gather (hses_allgather_fitness)",
                   "device_status": status})
+    if px is not None:
+        px.destroy()
 
     # ---- the whole population on rank 0's GPU alone, in the same job: the strong-scaling yardstick --
     if single_gpu_leg and world > 1:
@@ -622,7 +631,7 @@ def run_population_step(args, rank: int, local_rank: int, world: int):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     block = population_step_case(rank, world, dev, ctx, comm, args.n_pop, args.bm, args.rank, args.cache,
                                  args.steps, args.warmup, check=not args.kernel_only,
-                                 single_gpu_leg=not args.kernel_only)
+                                 single_gpu_leg=not args.kernel_only, exchange=args.exchange)
     clocks = sampler.stop() if sampler else None
     if rank == 0:
         line = {"metric": METRIC, "value": block["member_evals_per_sec"], "unit": UNIT, "n_gpus": world,
@@ -979,6 +988,9 @@ def main():
     ap.add_argument("--shrink", type=int, default=1,
                     help="streaming_kernels, einsum_pair: divide every case's leading dimension (reduced cases for "
                          "ncu captures)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="population_step: how the fitness vector reaches every rank (the library's all-gather, or "
+                         "its peer-memory kernels)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU legs and the extra blocks (profiling runs)")
     ap.add_argument("--headline-only", action="store_true",

@@ -21,6 +21,8 @@ EXPORTS = [
     "hses_noise_seed", "hses_normal_fill", "hses_lora_factors",
     "hses_dense_noise", "hses_poisson_encode", "hses_poisson_encode_dual", "hses_lif_scan",
     "hses_perturbed_linear_workspace_bytes", "hses_perturbed_linear", "hses_time_mean", "hses_fitness",
+    "hses_peer_window_bytes", "hses_peer_alloc", "hses_peer_open", "hses_peer_close", "hses_peer_free",
+    "hses_fitness_publish", "hses_fitness_wait", "hses_fitness_exchange",
     "hses_member_mean", "hses_convert_fitnesses", "hses_es_update_workspace_bytes",
     "hses_es_update", "hses_es_update_static_scratch_bytes", "hses_es_update_static",
     "hses_es_update_dense", "hses_solver_step", "hses_snn_forward_workspace_bytes", "hses_snn_forward",
@@ -127,6 +129,15 @@ def load():
     L.hses_perturbed_linear_workspace_bytes.argtypes = [C.POINTER(LinearArgs)]
     L.hses_perturbed_linear.argtypes = [vp, vp, C.POINTER(LinearArgs)]
     L.hses_time_mean.argtypes = [vp, vp, vp, i32, i64, i32, i64, vp, i64]
+    L.hses_peer_window_bytes.argtypes = [i64]
+    L.hses_peer_window_bytes.restype = C.c_size_t
+    L.hses_peer_alloc.argtypes = [vp, i64, C.POINTER(vp), vp]
+    L.hses_peer_open.argtypes = [vp, vp, C.POINTER(vp)]
+    L.hses_peer_close.argtypes = [vp]
+    L.hses_peer_free.argtypes = [vp]
+    L.hses_fitness_publish.argtypes = [vp, vp, vp, i64, i64, i64, C.POINTER(vp), i32, i32, C.c_uint32]
+    L.hses_fitness_wait.argtypes = [vp, vp, vp, i64, i32, C.c_uint32, vp]
+    L.hses_fitness_exchange.argtypes = [vp, vp, vp, i64, i64, i64, C.POINTER(vp), i32, i32, C.c_uint32, vp]
     L.hses_fitness.argtypes = [vp, vp, vp, i64, i32, vp, i32, vp]
     L.hses_member_mean.argtypes = [vp, vp, vp, i64, i32, vp]
     L.hses_convert_fitnesses.argtypes = [vp, vp, vp, i64, i32, vp, vp]

@@ -173,6 +173,74 @@ def allreduce_grads(grads, group: Optional[dist.ProcessGroup] = None, comm: Opti
             dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
 
 
+class PeerExchange:
+    """The fitness exchange over peer memory instead of a collective (hses_fitness_publish /
+    hses_fitness_wait): every rank's kernel stores its shard into every rank's window over NVLink and
+    raises a flag; a bounded wait kernel collects the vector.  The windows are shared through CUDA
+    IPC handles, which travel through torch.distributed (any backend).  All ranks of one node."""
+
+    def __init__(self, n_pop: int, ctx=None, group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+        from . import _lib, core
+        self.ctx = ctx if ctx is not None else core.get_context()
+        self.lib = _lib.load()
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.n_pop = n_pop
+        self.tag = 0
+        own = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        _lib.check(self.lib.hses_peer_alloc(self.ctx.handle, n_pop, C.byref(own), handle))
+        self.own = own.value
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.windows = (C.c_void_p * self.world)()
+        self.opened = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.windows[r] = self.own
+                continue
+            w = C.c_void_p()
+            buf = (C.c_uint8 * 64).from_buffer_copy(h)
+            _lib.check(self.lib.hses_peer_open(self.ctx.handle, buf, C.byref(w)))
+            self.windows[r] = w.value
+            self.opened.append(w.value)
+        dist.barrier(group=group)   # every window is mapped everywhere before the first store
+
+    def exchange(self, local: torch.Tensor, out: Optional[torch.Tensor] = None, publish: bool = True) -> torch.Tensor:
+        """local: this rank's shard (shard_range order).  Returns the (n_pop,) vector once all shards of this
+        step have arrived; when one does not, the context's device status carries bit 9 and the result is
+        not valid.  publish=False withholds this rank's shard (tests of the bounded wait)."""
+        from . import _lib
+        from .core import current_stream
+        lo, hi = shard_range(self.n_pop, self.rank, self.world)
+        if local.numel() != hi - lo or local.dtype != torch.float32 or not local.is_contiguous():
+            raise ValueError("local must be this rank's contiguous f32 shard")
+        if out is None:
+            out = torch.empty(self.n_pop, dtype=torch.float32, device=local.device)
+        self.tag += 1
+        st = current_stream()
+        if publish:   # the usual step: one launch stores this rank's shard everywhere and waits for the others'
+            _lib.check(self.lib.hses_fitness_exchange(self.ctx.handle, st, local.data_ptr(), hi - lo, lo, self.n_pop,
+                                                      self.windows, self.rank, self.world, self.tag, out.data_ptr()))
+        else:
+            _lib.check(self.lib.hses_fitness_wait(self.ctx.handle, st, self.own, self.n_pop, self.world, self.tag,
+                                                  out.data_ptr()))
+        return out
+
+    def destroy(self) -> None:
+        """Unmaps the peers' windows and frees this rank's.  Call it on every rank, with no exchange in flight."""
+        from . import _lib
+        torch.cuda.synchronize()
+        for w in self.opened:
+            _lib.check(self.lib.hses_peer_close(w))
+        self.opened = []
+        if dist.is_initialized():
+            dist.barrier()   # nobody frees a window that a peer still has mapped and may write
+        if self.own:
+            _lib.check(self.lib.hses_peer_free(self.own))
+            self.own = None
+
+
 class RankLeft(CommError):
     """A peer announced that it left, or stopped announcing steps."""
 

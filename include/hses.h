@@ -592,6 +592,35 @@ int hses_allgather_fitness(hses_comm* comm, hses_stream stream, const float* loc
                            int64_t n_local, float* all /*device (world * n_local)*/);
 int hses_allreduce_grads(hses_comm* comm, hses_stream stream, float* grads /*device, in place*/, int64_t count);
 
+/* ---- the fitness exchange without a library collective: peer memory over NVLink.
+ *      Every rank owns a WINDOW of device memory (two copies of the population's raw-fitness
+ *      vector, steps alternate between them, and one flag word per rank and copy) that the other
+ *      ranks of the node map through a CUDA IPC handle.  hses_fitness_publish (one kernel) stores
+ *      this rank's shard into every rank's window and then raises this rank's flag there with the
+ *      step's tag; hses_fitness_wait (one kernel) waits until all `world` flags of its own window
+ *      carry the tag and copies the vector to `out`.  The wait is bounded (about a second): when a
+ *      shard does not arrive it sets bit 9 of the context's device status word, leaves `out`
+ *      untouched and returns — read hses_ctx_device_status before trusting `out`.  Tags are the
+ *      step number (>= 1, increasing by one); all ranks use the same tag in the same step.  Plain
+ *      stores and loads only (no multicast).  world <= 16.  The reference exchanges the vector
+ *      through the host (llm_experiments/snn_mnist_train_multi_gpu.py:225-234, 291). --------- */
+size_t hses_peer_window_bytes(int64_t n_total);
+/* allocates and clears this rank's window; `handle` (64 bytes) is what the other ranks open */
+int hses_peer_alloc(hses_ctx* ctx, int64_t n_total, void** window /*device, out*/, uint8_t handle[64] /*out*/);
+int hses_peer_open(hses_ctx* ctx, const uint8_t handle[64], void** window /*peer device memory, out*/);
+int hses_peer_close(void* window /*from hses_peer_open*/);
+int hses_peer_free(void* window /*from hses_peer_alloc*/);
+/* windows: HOST array of `world` device pointers, entry r = rank r's window (own one included) */
+int hses_fitness_publish(hses_ctx* ctx, hses_stream stream, const float* local /*device*/, int64_t n_local,
+                         int64_t offset, int64_t n_total, void* const* windows /*host*/, int32_t rank,
+                         int32_t world, uint32_t tag);
+int hses_fitness_wait(hses_ctx* ctx, hses_stream stream, const void* own_window /*device*/, int64_t n_total,
+                      int32_t world, uint32_t tag, float* out /*device, n_total*/);
+/* both in one launch: the step's usual call (a rank's stores are under way while it waits for the others') */
+int hses_fitness_exchange(hses_ctx* ctx, hses_stream stream, const float* local /*device*/, int64_t n_local,
+                          int64_t offset, int64_t n_total, void* const* windows /*host*/, int32_t rank,
+                          int32_t world, uint32_t tag, float* out /*device, n_total*/);
+
 #ifdef __cplusplus
 }
 #endif

@@ -110,3 +110,68 @@ def test_two_gpu_step_identical_parameters_and_single_gpu_parity(hs):
         whole.update(raw)
     for got, want in zip(res[0][3], [p.cpu().numpy() for p in whole.params]):
         assert np.abs(got - want).max() <= 1e-3 * max(np.abs(want).max(), 1e-6)
+
+
+def _peer_main(rank, world, port, n_pop, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from hyperscalees_b200 import core, parallel
+    ctx = core.get_context(rank)
+    comm = parallel.Comm.from_process_group(ctx)
+    px = parallel.PeerExchange(n_pop, ctx)
+    lo, hi = parallel.shard_range(n_pop, rank, world)
+    same, statuses = [], []
+    for step in range(5):
+        g = torch.Generator(device=dev).manual_seed(100 * step + rank)
+        local = torch.randn(hi - lo, device=dev, generator=g)
+        got = px.exchange(local)
+        want = parallel.allgather_fitness(local, n_pop, comm=comm)
+        torch.cuda.synchronize()
+        same.append(bool(torch.equal(got, want)))
+    statuses.append(ctx.device_status())
+    # a step in which rank 1 withholds its shard (the failure is made on the host: no kernel is asked to
+    # misbehave): every wait runs out after about a second, says so in the status word, and returns
+    sentinel = torch.full((n_pop,), -7.0, device=dev)
+    local = torch.ones(hi - lo, device=dev)
+    px.exchange(local, out=sentinel, publish=(rank != 1))
+    torch.cuda.synchronize()
+    statuses.append(ctx.device_status())
+    untouched = bool((sentinel == -7.0).all().item())
+    dist.barrier()
+    # the next step works again
+    got = px.exchange(local * (rank + 1))
+    want = parallel.allgather_fitness(local * (rank + 1), n_pop, comm=comm)
+    torch.cuda.synchronize()
+    same.append(bool(torch.equal(got, want)))
+    statuses.append(ctx.device_status())
+    px.destroy()
+    comm.destroy()
+    dist.destroy_process_group()
+    q.put((rank, same, statuses, untouched))
+
+
+def test_peer_memory_fitness_exchange_and_its_bounded_wait(hs):
+    """The peer-memory exchange returns the all-gather's bits; when a rank withholds its shard the
+    other ranks' waits run out (bit 9 of the device status), the output is left alone, nothing
+    hangs, and the next step works."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    import torch.multiprocessing as mp
+    n_pop, world = 4096, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_peer_main, args=(r, world, port, n_pop, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted((q.get(timeout=600) for _ in procs), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=120)
+    for rank, same, statuses, untouched in res:
+        assert all(same), f"rank {rank}: exchange differs from the all-gather"
+        assert statuses[0] == 0 and statuses[2] == 0
+        assert statuses[1] == 1 << 9, f"rank {rank}: the withheld shard was not noticed"
+        assert untouched
