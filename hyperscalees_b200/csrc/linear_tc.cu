@@ -541,7 +541,8 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
                  uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
                  int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                  __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
-                 const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true, int row_b0) {
+                 const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true, int row_b0,
+                 int skip_split) {
     constexpr int RANK = RANK_G * 4;
     constexpr int KQ = 32 / RANK_G;   // lanes along k
     constexpr int KSTEP = 4 * KQ;     // k covered by one pass of a warp
@@ -608,7 +609,9 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
         l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
         lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     };
-    if (n4 <= 32) {
+    if (skip_split) {
+        // the operand split of these rows is already in the workspace (an earlier projection of the same x)
+    } else if (n4 <= 32) {
         // short rows (up to 128 values): one 16-byte piece per lane covers a row, so a warp keeps eight
         // rows in flight, one trip to memory for all of them
         for (int lr0 = warp * 8; lr0 < total_rows; lr0 += 8 * (LT_THREADS / 32)) {
@@ -953,7 +956,8 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
                  "workspace too small or misaligned; see hses_perturbed_linear_workspace_bytes");
     int64_t rows = (int64_t)g.t_steps * g.n_pop * g.bm;
     const int one_pass = g.precision == HSES_PRECISION_BF16 ? 1 : 0;
-    HSES_CUDA(cudaMemsetAsync(sc.lo_flag, 0, sizeof(int), st));
+    const bool reuse_split = g.x_split_valid != 0;   // x's operand split of the previous call is still in the workspace
+    if (!reuse_split) HSES_CUDA(cudaMemsetAsync(sc.lo_flag, 0, sizeof(int), st));
     {
         HSES_KERNEL(ctx, st, "split_w");
         split_f16_rows_kernel<<<(unsigned)((g.a + 7) / 8), 256, 0, st>>>(g.param, g.a, g.k, g.param_row_stride,
@@ -963,7 +967,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     // a caller-provided fp16 copy of an x that is exact in fp16 is the operand as it stands
     const bool x_ready = !g.perturb && !one_pass && g.x_half != nullptr && aligned16(g.x_half);
     if (x_ready) sc.xhi = reinterpret_cast<__half*>(const_cast<void*>(g.x_half));
-    if (!g.perturb && !x_ready) {  // with noise the pair kernel below splits x while it computes t
+    if (!g.perturb && !x_ready && !reuse_split) {  // with noise the pair kernel below splits x while it computes t
         HSES_KERNEL(ctx, st, "split_x");
         split_f16_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(g.x, rows, g.k, g.x_row_stride, sc.xhi,
                                                                          sc.xlo, sc.rs, sc.lo_flag, one_pass);
@@ -1015,7 +1019,8 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
 #define HSES_LT(RG)                                                                                          \
     lowrank_t_kernel<RG><<<lt_grid, LT_THREADS, 0, st>>>(                                            \
         ctx->cal(), ctx->t.jump_pow2, hop127, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,     \
-        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0)
+        g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0, \
+        reuse_split ? 1 : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
         switch ((g.rank + 3) / 4) {
             case 1: HSES_LT(1); break;

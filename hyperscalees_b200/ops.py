@@ -190,12 +190,14 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
                      algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None, precision: int = 0,
                      tmm: bool = False, x_half: Optional[torch.Tensor] = None,
-                     out_half: Optional[torch.Tensor] = None):
+                     out_half: Optional[torch.Tensor] = None, reuse_x_split: bool = False):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
     the charged potentials.  With `cache` the factors are read from it instead of
     being regenerated (same bits).  x_half: x once more as dense fp16 (rows, k) when it is exact
-    there; out_half: a dense fp16 (rows, a) tensor that receives the spikes as well (lif only)."""
+    there; out_half: a dense fp16 (rows, a) tensor that receives the spikes as well (lif only).
+    reuse_x_split: the previous call on this device and stream had the same x and the same shapes
+    (another projection of the same activation): its operand split of x is taken as it stands."""
     _check(x, "x")
     _check(param, "param", ndim=2)
     rows, k, xs = _rows_2d(x, "x")
@@ -224,6 +226,7 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.algo = algo
     g.precision = precision
     g.factor_order = int(tmm)   # do_Tmm: param is the reference's (in, out) matrix transposed
+    g.x_split_valid = int(reuse_x_split)
     if x_half is not None:
         if x_half.dtype != torch.float16 or not x_half.is_contiguous() or x_half.numel() != rows * k:
             raise ValueError("x_half must be a contiguous fp16 tensor of rows*k values")

@@ -96,7 +96,9 @@ class SpikingLM:
         return 2 + len(self.blocks) * (3 * self.num_heads + 3)
 
     def nn(self, idx: int, x: torch.Tensor, w: torch.Tensor, n: int, rows_per_member: int,
-           noise: Optional[LmNoise], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           noise: Optional[LmNoise], out: Optional[torch.Tensor] = None, same_x: bool = False) -> torch.Tensor:
+        """same_x: the call right before this one projected the same x with a matrix of the same shape (the
+        per-head Q/K/V of a block): the tensor-core path keeps that call's fp16 operand split of x."""
         kw = {}
         if noise is not None:
             kw = dict(sigma=noise.sigma, rank=noise.rank, key=noise.base_keys[idx], epoch=noise.epoch,
@@ -108,7 +110,8 @@ class SpikingLM:
                 a, k = w.shape
                 kw["cache"] = ops.FactorCache(noise.base_keys[idx], noise.epoch, noise.noise_reuse, noise.rank, a, k,
                                               n // 2, first_pair=noise.first_thread // 2, device=self.device)
-        return ops.perturbed_linear(x, w, n_pop=n, bm=rows_per_member, perturb=noise is not None, out=out, **kw)
+        return ops.perturbed_linear(x, w, n_pop=n, bm=rows_per_member, perturb=noise is not None, out=out,
+                                    reuse_x_split=same_x, **kw)
 
     def forward_population(self, ids: torch.Tensor, noise: Optional[LmNoise] = None) -> torch.Tensor:
         """ids (n, seqs, L) int32: member j evaluates its own `seqs` sequences -> logits
@@ -135,9 +138,10 @@ class SpikingLM:
             for h in range(H):
                 # head h's currents land in columns [h*hd, (h+1)*hd): the layout the attention kernel reads
                 sl = slice(h * hd, (h + 1) * hd)
-                self.nn(base + 3 * h, x, blk["q"][h], n, rpm, noise, out=qc[:, sl])
-                self.nn(base + 3 * h + 1, x, blk["k"][h], n, rpm, noise, out=kc[:, sl])
-                self.nn(base + 3 * h + 2, x, blk["v"][h], n, rpm, noise, out=vc[:, sl])
+                # twelve projections of one x: only the first one splits it into tensor-core operands
+                self.nn(base + 3 * h, x, blk["q"][h], n, rpm, noise, out=qc[:, sl], same_x=h > 0)
+                self.nn(base + 3 * h + 1, x, blk["k"][h], n, rpm, noise, out=kc[:, sl], same_x=True)
+                self.nn(base + 3 * h + 2, x, blk["v"][h], n, rpm, noise, out=vc[:, sl], same_x=True)
             # LIF over T steps on the constant currents, firing rates in place
             for buf in (qc, kc, vc):
                 ops.lif_rate(buf, self.T, self.tau_m, self.v_th, out=buf)

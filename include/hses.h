@@ -235,6 +235,12 @@ typedef struct {
                            (rows, a), written by the kernel that finishes the layer where it can (the
                            per-pair kernel with the fused scan), else by one conversion pass: the
                            x_half of the layer that follows.  a must be a multiple of 8 */
+    int32_t x_split_valid; /* 1: the previous call on this workspace had the same x, the same shapes
+                           (t_steps, n_pop, bm, k, a, rank, perturb, precision) and took the tensor-core
+                           path, and nothing else has written the workspace since: its fp16 operand
+                           split of x is still there and is not computed again (several projections of
+                           one activation, e.g. the per-head Q/K/V of a block).  Ignored by the other
+                           paths */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

@@ -222,3 +222,28 @@ def test_tmm_factor_order(hs, oracle, algo_name, k, a, rank):
         A, B = oracle.lora_params(bs, KEY, rank, 0, 6 + i, k, a, 0)      # A (in, r) scaled, B (out, r)
         want = x[i].astype(np.float64) @ p_ref.astype(np.float64) + (x[i].astype(np.float64) @ A.astype(np.float64)) @ B.astype(np.float64).T
         assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("perturb,cached", [(False, False), (True, False), (True, True)])
+def test_operand_split_of_x_is_reused_across_projections(hs, perturb, cached):
+    """Several projections of one activation (the per-head Q/K/V of a block): with reuse_x_split the
+    second call keeps the first call's fp16 split of x and returns the bits of a call that splits again."""
+    from hyperscalees_b200 import ops, core
+    g = np.random.default_rng(21)
+    n_pop, bm, k, a, rank = 4, 64, 64, 16, 8
+    x = dev(g.standard_normal((n_pop, bm, k)).astype(np.float32))
+    w1 = dev((g.standard_normal((a, k)) / 8).astype(np.float32))
+    w2 = dev((g.standard_normal((a, k)) / 8).astype(np.float32))
+    kw = dict(n_pop=n_pop, bm=bm, perturb=perturb, algo=ops.ALGO_TENSOR)
+    def call(w, key, **extra):
+        k2 = dict(kw)
+        if perturb:
+            k2.update(sigma=0.3, rank=rank, key=key)
+            if cached:
+                k2["cache"] = ops.FactorCache(key, 0, 0, rank, a, k, n_pairs=n_pop // 2)
+        return ops.perturbed_linear(x, w, **k2, **extra)
+    want = call(w2, 7).clone()
+    call(w1, 5)
+    got = call(w2, 7, reuse_x_split=True)
+    assert core.get_context(0).device_status() == 0
+    assert torch.equal(got, want)
