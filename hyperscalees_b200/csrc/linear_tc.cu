@@ -818,6 +818,216 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     }
 }
 
+// The prepass for layers whose rows fit the registers of a warp (k <= 1024) and whose whole B fits
+// the shared memory of a CTA (ranks 4, 8, 16).  Phase 1: the 256 threads regenerate (or copy from
+// the factor cache) all k rows of the pair's B into shared memory.  Phase 2: a warp loads two x rows
+// into registers ONCE and does everything with them there: the row maximum, the fp16 operand split,
+// and t = x * B, each lane multiplying the 4-value pieces it holds with the matching rows of B and
+// the warp adding its lanes' sums with a halving exchange.  lowrank_t_kernel reads x a second time,
+// 128 bytes per row and trip, for its t product and spends as long waiting for those trips as on
+// the generation.  Two CTAs share an SM, so one generates while the other streams x.
+// B row kr is stored at row p = (kr / 128) * 128 + (kr % 4) * 32 + (kr % 128) / 4, its 16-byte
+// chunk c at chunk (c + p / (8 / RANK_G)) % RANK_G: the lanes of a warp, which hold pieces
+// 32 apart, then read consecutive rows, eight of them covering all banks.
+template <int RANK_G>
+__global__ void __launch_bounds__(LT_THREADS, 2)
+lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
+                      uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
+                      int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
+                      __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
+                      const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int row_b0,
+                      int skip_split) {
+    constexpr int RANK = RANK_G * 4;
+    constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
+    extern __shared__ __align__(16) float bsm[];   // ceil(k / 128) * 128 rows of RANK floats
+    __shared__ double2 log_tab_s[64];
+    __shared__ uint32_t delta_s[512];
+    __shared__ int64_t row_s[LT_ROWS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (!cache_b) {
+        for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
+        for (int i = tid; i < 256; i += LT_THREADS) {
+            delta_s[i] = cal.log_delta[i];
+            delta_s[256 + i] = cal.cos_delta[i];
+        }
+        cal.log_tab = log_tab_s;
+        cal.log_delta = delta_s;
+        cal.cos_delta = delta_s + 256;
+    }
+    const int32_t first_pair = first_thread / 2;
+    const int32_t pair = first_pair + blockIdx.x;
+    int64_t m_lo = (int64_t)pair * 2 - first_thread, m_hi = m_lo + 2;
+    if (m_lo < 0) m_lo = 0;
+    if (m_hi > n_pop) m_hi = n_pop;
+    const int rows_per_step = (int)(m_hi - m_lo) * bm;
+    const int row0 = blockIdx.y * LT_ROWS;
+    const int total_rows = min(LT_ROWS, rows_per_step * t_steps - row0);
+    if (total_rows <= 0) return;
+    if (tid < LT_ROWS) {
+        int lr = row0 + (tid < total_rows ? tid : total_rows - 1);  // rows past the end repeat the last one
+        int step = lr / rows_per_step, rr = lr - step * rows_per_step;
+        row_s[tid] = ((int64_t)step * n_pop + m_lo) * bm + rr;
+    }
+    __syncthreads();
+
+    // ---- phase 1: B of this pair ----
+    float4* bsm4 = reinterpret_cast<float4*>(bsm);
+    auto stored_row = [](int kr) { return (kr & ~127) + (kr & 3) * 32 + ((kr & 127) >> 2); };
+    if (cache_b) {
+        const float4* cb4 = reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK);
+        for (int i = tid; i < k * RANK_G; i += LT_THREADS) {
+            const int kr = i / RANK_G, c = i - kr * RANK_G;
+            const int p = stored_row(kr);
+            bsm4[p * RANK_G + ((c + p / RP) % RANK_G)] = __ldg(cb4 + i);
+        }
+    } else {
+        const int rpt = (k + LT_THREADS - 1) / LT_THREADS;   // rows per thread
+        const int kr0 = tid * rpt, kr1 = min(kr0 + rpt, k);
+        if (kr0 < k) {
+            uint64_t sb = noise_seed(key, true_epoch, pair) | 1ull;
+            sb = jump_by(pow2, sb, 2ull * (uint64_t)RANK * (uint64_t)(row_b0 + kr0));   // row_b0: first input-side row
+#pragma unroll 1
+            for (int kr = kr0; kr < kr1; ++kr) {
+                const int p = stored_row(kr);
+#pragma unroll 1
+                for (int c = 0; c < RANK_G; ++c) {
+                    float z[4];
+                    next_normals4(sb, cal, z);
+                    bsm4[p * RANK_G + ((c + p / RP) % RANK_G)] = make_float4(z[0], z[1], z[2], z[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- phase 2: split and t of two rows per warp and round ----
+    const int n4 = k >> 2;
+    uint32_t lo_nz = 0;  // any non-zero lo half written by this thread
+    auto finish_row = [&](int64_t R, float m, float& sc) {
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
+        int e = 13 - ex;
+        if (ex <= -127 || ex >= 128) e = 0;
+        if (e > 100) e = 100;
+        if (e < -100) e = -100;
+        if (bf16) e = 0;   // one-pass mode: no scale
+        sc = __uint_as_float((uint32_t)(127 + e) << 23);
+        if (lane == 0 && !skip_split) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
+    };
+    auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
+        if (bf16) {   // hi = bf16(v), the lo half is neither written nor read
+            const __nv_bfloat162 b01 = __floats2bfloat162_rn(v.x, v.y), b23 = __floats2bfloat162_rn(v.z, v.w);
+            h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&b01), *reinterpret_cast<const uint32_t*>(&b23));
+            l2 = make_uint2(0u, 0u);
+            return;
+        }
+        const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
+        const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+        const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+        const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
+        h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
+    };
+    constexpr int NW = LT_THREADS / 32;
+    for (int lr = warp; lr < total_rows; lr += 2 * NW) {
+        const int lr1 = lr + NW;
+        const bool two = lr1 < total_rows;
+        const int64_t R0 = row_s[lr], R1 = row_s[two ? lr1 : lr];
+        const float4* s0 = reinterpret_cast<const float4*>(x + (size_t)R0 * x_stride);
+        const float4* s1 = reinterpret_cast<const float4*>(x + (size_t)R1 * x_stride);
+        float4 v0[8], v1[8];   // streaming loads: x passes once and must not push the jump tables out of L1
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = lane + 32 * j;
+            v0[j] = i < n4 ? __ldcs(s0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v1[j] = (two && i < n4) ? __ldcs(s1 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (!skip_split) {
+            float m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                m0 = fmaxf(m0, fmaxf(fmaxf(fabsf(v0[j].x), fabsf(v0[j].y)), fmaxf(fabsf(v0[j].z), fabsf(v0[j].w))));
+                m1 = fmaxf(m1, fmaxf(fmaxf(fabsf(v1[j].x), fabsf(v1[j].y)), fmaxf(fabsf(v1[j].z), fabsf(v1[j].w))));
+            }
+            float sc0, sc1 = 1.0f;
+            finish_row(R0, m0, sc0);
+            if (two) finish_row(R1, m1, sc1);   // warp-uniform branch
+            uint2* dh0 = reinterpret_cast<uint2*>(xhi + (size_t)R0 * k);
+            uint2* dl0 = reinterpret_cast<uint2*>(xlo + (size_t)R0 * k);
+            uint2* dh1 = reinterpret_cast<uint2*>(xhi + (size_t)R1 * k);
+            uint2* dl1 = reinterpret_cast<uint2*>(xlo + (size_t)R1 * k);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = lane + 32 * j;
+                if (i < n4) {
+                    uint2 h2, l2;
+                    split4(v0[j], sc0, h2, l2);
+                    dh0[i] = h2;
+                    if (!bf16) dl0[i] = l2;
+                    if (two) {
+                        split4(v1[j], sc1, h2, l2);
+                        dh1[i] = h2;
+                        if (!bf16) dl1[i] = l2;
+                    }
+                }
+            }
+        }
+        // t of the two rows, two q per packed fp32 instruction: acc2[row * RANK / 2 + q / 2]
+        f32x2 acc2[RANK];
+#pragma unroll
+        for (int i = 0; i < RANK; ++i) acc2[i] = 0ull;
+        const ulonglong2* bsm2 = reinterpret_cast<const ulonglong2*>(bsm);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (lane + 32 * j < n4) {
+                const f32x2 xa[4] = {pk2(v0[j].x, v0[j].x), pk2(v0[j].y, v0[j].y), pk2(v0[j].z, v0[j].z), pk2(v0[j].w, v0[j].w)};
+                const f32x2 xb[4] = {pk2(v1[j].x, v1[j].x), pk2(v1[j].y, v1[j].y), pk2(v1[j].z, v1[j].z), pk2(v1[j].w, v1[j].w)};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int p = j * 128 + e * 32 + lane;
+#pragma unroll
+                    for (int c = 0; c < RANK_G; ++c) {
+                        const ulonglong2 b = bsm2[p * RANK_G + ((c + p / RP) % RANK_G)];
+                        acc2[2 * c] = fma2(xa[e], b.x, acc2[2 * c]);
+                        acc2[2 * c + 1] = fma2(xa[e], b.y, acc2[2 * c + 1]);
+                        acc2[RANK / 2 + 2 * c] = fma2(xb[e], b.x, acc2[RANK / 2 + 2 * c]);
+                        acc2[RANK / 2 + 2 * c + 1] = fma2(xb[e], b.y, acc2[RANK / 2 + 2 * c + 1]);
+                    }
+                }
+            }
+        }
+        float acc[2 * RANK];
+#pragma unroll
+        for (int i = 0; i < RANK; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+        // halving exchange: after the step with distance off a lane keeps the half of its values
+        // that its bit `off` selects, summed with its partner's; 2 * RANK values end up one per
+        // group of 32 / (2 * RANK) lanes, value index = lane / group
+        int off = 16;
+#pragma unroll
+        for (int n = 2 * RANK; n > 1; n >>= 1) {
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < n / 2; ++i) {
+                const float send = up ? acc[i] : acc[i + n / 2];
+                const float keep = up ? acc[i + n / 2] : acc[i];
+                acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+            off >>= 1;
+        }
+        for (; off > 0; off >>= 1) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
+        constexpr int GROUP = 32 / (2 * RANK) > 0 ? 32 / (2 * RANK) : 1;
+        const int idx = lane / GROUP;
+        if (lane % GROUP == 0) {
+            const int row = idx / RANK, q = idx - row * RANK;
+            if (row == 0 || two) t[(size_t)(row ? R1 : R0) * RANK + q] = acc[0];
+        }
+    }
+    // one flag per call tells the GEMM whether any lo half is non-zero (a set flag is not set again)
+    if (__any_sync(0xffffffffu, lo_nz != 0) && lane == 0 && *reinterpret_cast<volatile int*>(lo_flag) == 0)
+        atomicOr(lo_flag, 1);
+}
+
 // ------------------------------------------------------------------- host side
 // 2-D fp16 map over (rows, cols) with `stride` elements between rows; box = (64, box_rows).
 int make_map(CUtensorMap* map, const __half* base, int64_t rows, int cols, int64_t stride, int box_rows) {
@@ -1022,6 +1232,25 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0, \
         reuse_split ? 1 : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
+        if ((g.rank == 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024) {
+            // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel)
+            const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * g.rank * sizeof(float);   // at most 64 KB
+#define HSES_LTR(RG)                                                                                          \
+    do {                                                                                                      \
+        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       65536));                                                               \
+        lowrank_t_rows_kernel<RG><<<lt_grid, LT_THREADS, b_bytes, st>>>(                                      \
+            ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
+            g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass,        \
+            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0);                                              \
+    } while (0)
+            switch (g.rank / 4) {
+                case 1: HSES_LTR(1); break;
+                case 2: HSES_LTR(2); break;
+                default: HSES_LTR(4); break;
+            }
+#undef HSES_LTR
+        } else
         switch ((g.rank + 3) / 4) {
             case 1: HSES_LT(1); break;
             case 2: HSES_LT(2); break;

@@ -31,6 +31,8 @@ def status_ok():
     (8, 32, 64, 96, 4, 1, 0),       # a = 96 with 32-column items (rank 4): three items per tile
     (8, 16, 96, 160, 16, 1, 0),     # two chunks of 128, the second one ragged
     (4, 64, 128, 320, 1, 1, 0),     # rank 1 (as rank 4), three chunks of 128, the last one half used
+    (4, 16, 1024, 128, 16, 1, 0),   # the widest layer of the rows prepass: all 64 KB of a pair's B in shared memory
+    (5, 16, 1000, 128, 8, 3, 1),    # k not a multiple of 128 there, three time steps, pairs cut at both ends
 ])
 def test_tensor_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
