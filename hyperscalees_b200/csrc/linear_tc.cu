@@ -818,7 +818,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     }
 }
 
-// The prepass for layers whose rows fit the registers of a warp (k <= 1024) and whose whole B fits
+// The prepass for layers whose rows fit the registers of a warp (512 <= k <= 1024) and whose whole B fits
 // the shared memory of a CTA (ranks 4, 8, 16).  Phase 1: the 256 threads regenerate (or copy from
 // the factor cache) all k rows of the pair's B into shared memory.  Phase 2: a warp loads two x rows
 // into registers ONCE and does everything with them there: the row maximum, the fp16 operand split,
@@ -1232,8 +1232,10 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0, \
         reuse_split ? 1 : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
-        if ((g.rank == 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024) {
-            // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel)
+        if ((g.rank == 4 || g.rank == 8 || g.rank == 16) && g.k >= 512 && g.k <= 1024) {
+            // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel); short rows
+            // (the 64- and 256-wide layers of the token-level models, thousands of rows per pair) are
+            // faster in the block kernel, which keeps eight of them in flight per warp
             const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * g.rank * sizeof(float);   // at most 64 KB
 #define HSES_LTR(RG)                                                                                          \
     do {                                                                                                      \
