@@ -279,10 +279,13 @@ class Heartbeat:
         while pending:
             still = []
             for r in pending:
+                # a peer that has published this step takes part in it, whatever it says afterwards:
+                # a rank leaves only between steps, so its goodbye concerns the next one
+                if self._read("step", r, -1) >= step:
+                    continue
                 if self._read("left", r, 0) == 1:
                     raise RankLeft(f"rank {r} left before step {step}")
-                if self._read("step", r, -1) < step:
-                    still.append(r)
+                still.append(r)
             pending = still
             if pending:
                 if time.monotonic() > deadline:
