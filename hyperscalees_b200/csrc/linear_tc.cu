@@ -819,7 +819,8 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
 }
 
 // The prepass for layers whose rows fit the registers of a warp (512 <= k <= 1024) and whose whole B fits
-// the shared memory of a CTA (ranks 4, 8, 16).  Phase 1: the 256 threads regenerate (or copy from
+// the shared memory of a CTA (ranks 1..4, 8, 16; ranks below 4 as rank 4 with zero columns, rank_true
+// values per row in the stream and in the cache).  Phase 1: the 256 threads regenerate (or copy from
 // the factor cache) all k rows of the pair's B into shared memory.  Phase 2: a warp loads two x rows
 // into registers ONCE and does everything with them there: the row maximum, the fp16 operand split,
 // and t = x * B, each lane multiplying the 4-value pieces it holds with the matching rows of B and
@@ -835,8 +836,8 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
                       int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                       __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
-                      const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int row_b0,
-                      int skip_split) {
+                      const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true,
+                      int row_b0, int skip_split) {
     constexpr int RANK = RANK_G * 4;
     constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
     extern __shared__ __align__(16) float bsm[];   // ceil(k / 128) * 128 rows of RANK floats
@@ -873,7 +874,14 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
     // ---- phase 1: B of this pair ----
     float4* bsm4 = reinterpret_cast<float4*>(bsm);
     auto stored_row = [](int kr) { return (kr & ~127) + (kr & 3) * 32 + ((kr & 127) >> 2); };
-    if (cache_b) {
+    if (cache_b && rank_true < 4) {
+        const float* cb1 = cache_b + (size_t)blockIdx.x * k * rank_true;
+        for (int kr = tid; kr < k; kr += LT_THREADS) {
+            const float* row = cb1 + (size_t)kr * rank_true;
+            bsm4[stored_row(kr)] = make_float4(__ldg(row), rank_true > 1 ? __ldg(row + 1) : 0.0f,
+                                               rank_true > 2 ? __ldg(row + 2) : 0.0f, 0.0f);
+        }
+    } else if (cache_b) {
         const float4* cb4 = reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK);
         for (int i = tid; i < k * RANK_G; i += LT_THREADS) {
             const int kr = i / RANK_G, c = i - kr * RANK_G;
@@ -885,10 +893,18 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         const int kr0 = tid * rpt, kr1 = min(kr0 + rpt, k);
         if (kr0 < k) {
             uint64_t sb = noise_seed(key, true_epoch, pair) | 1ull;
-            sb = jump_by(pow2, sb, 2ull * (uint64_t)RANK * (uint64_t)(row_b0 + kr0));   // row_b0: first input-side row
+            sb = jump_by(pow2, sb, 2ull * (uint64_t)rank_true * (uint64_t)(row_b0 + kr0));   // row_b0: first input-side row
 #pragma unroll 1
             for (int kr = kr0; kr < kr1; ++kr) {
                 const int p = stored_row(kr);
+                if (rank_true < 4) {
+                    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    z[0] = next_normal(sb, cal);
+                    if (rank_true > 1) z[1] = next_normal(sb, cal);
+                    if (rank_true > 2) z[2] = next_normal(sb, cal);
+                    bsm4[p] = make_float4(z[0], z[1], z[2], z[3]);
+                    continue;
+                }
 #pragma unroll 1
                 for (int c = 0; c < RANK_G; ++c) {
                     float z[4];
@@ -1232,21 +1248,21 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0, \
         reuse_split ? 1 : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
-        if ((g.rank == 4 || g.rank == 8 || g.rank == 16) && g.k >= 512 && g.k <= 1024) {
+        if ((g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k >= 512 && g.k <= 1024) {
             // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel); short rows
             // (the 64- and 256-wide layers of the token-level models, thousands of rows per pair) are
             // faster in the block kernel, which keeps eight of them in flight per warp
-            const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * g.rank * sizeof(float);   // at most 64 KB
+            const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * (g.rank < 4 ? 4 : g.rank) * sizeof(float);   // at most 64 KB
 #define HSES_LTR(RG)                                                                                          \
     do {                                                                                                      \
         HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                        65536));                                                               \
         lowrank_t_rows_kernel<RG><<<lt_grid, LT_THREADS, b_bytes, st>>>(                                      \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
-            g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass,        \
+            g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
             g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0);                                              \
     } while (0)
-            switch (g.rank / 4) {
+            switch ((g.rank + 3) / 4) {
                 case 1: HSES_LTR(1); break;
                 case 2: HSES_LTR(2); break;
                 default: HSES_LTR(4); break;

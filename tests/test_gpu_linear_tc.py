@@ -31,8 +31,8 @@ def status_ok():
     (8, 32, 64, 96, 4, 1, 0),       # a = 96 with 32-column items (rank 4): three items per tile
     (8, 16, 96, 160, 16, 1, 0),     # two chunks of 128, the second one ragged
     (4, 64, 128, 320, 1, 1, 0),     # rank 1 (as rank 4), three chunks of 128, the last one half used
-    (4, 16, 1024, 128, 16, 1, 0),   # the widest layer of the rows prepass: all 64 KB of a pair's B in shared memory
-    (5, 16, 1000, 128, 8, 3, 1),    # k not a multiple of 128 there, three time steps, pairs cut at both ends
+    (8, 16, 1024, 128, 16, 1, 0),   # the widest layer of the rows prepass: all 64 KB of a pair's B in shared memory
+    (4, 32, 1000, 128, 8, 3, 1),    # k not a multiple of 128 there, three time steps, pairs cut at both ends
 ])
 def test_tensor_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
@@ -162,12 +162,13 @@ def test_tensor_path_with_inputs_exact_in_fp16(hs, oracle, perturb):
 
 @pytest.mark.parametrize("rank", [1, 2, 3])
 @pytest.mark.parametrize("cached", [False, True])
-def test_tensor_path_small_ranks(hs, oracle, rank, cached):
+@pytest.mark.parametrize("k", [192, 640])   # the block prepass, and the one that keeps a pair's whole B on chip
+def test_tensor_path_small_ranks(hs, oracle, rank, cached, k):
     """Ranks 1..3 run on the tensor-core path as rank 4 with zero columns: same stream positions
     (rank values per row), same results as the CPU restatement."""
     from hyperscalees_b200 import ops
     g = np.random.default_rng(rank)
-    n_pop, bm, k, a, sigma = 6, 64, 192, 256, 0.3
+    n_pop, bm, a, sigma = 6, 64, 256, 0.3
     x = g.standard_normal((n_pop, bm, k)).astype(np.float32)
     w = g.standard_normal((a, k)).astype(np.float32)
     cache = ops.FactorCache(KEY, 0, 0, rank, a, k, n_pairs=n_pop // 2, first_pair=1) if cached else None
@@ -179,14 +180,14 @@ def test_tensor_path_small_ranks(hs, oracle, rank, cached):
         assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("rank,perturb", [(1, True), (16, True), (4, False)])
-def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb):
+@pytest.mark.parametrize("rank,perturb,k", [(1, True, 256), (16, True, 256), (4, False, 256), (1, True, 768)])
+def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb, k):
     """precision = BF16: x and the parameter rounded to bf16, one pass, fp32 accumulation; the
     rank-r term stays fp32.  Compared with the CPU product of the rounded operands plus the CPU
     rank-r term."""
     from hyperscalees_b200 import ops
     g = np.random.default_rng(10 + rank)
-    n_pop, bm, k, a, sigma = 4, 64, 256, 384, 0.2
+    n_pop, bm, a, sigma = 4, 64, 384, 0.2
     x = g.standard_normal((n_pop, bm, k)).astype(np.float32)
     w = (g.standard_normal((a, k)) * 0.02).astype(np.float32)
     rb = lambda v: torch.as_tensor(v).to(torch.bfloat16).to(torch.float32).numpy()
@@ -207,7 +208,7 @@ def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb):
 
 
 @pytest.mark.parametrize("algo_name,k,a,rank", [("TENSOR", 64, 256, 1), ("TENSOR", 192, 128, 4), ("SIMT", 96, 40, 1),
-                                                ("SIMT", 64, 32, 3)])
+                                                ("SIMT", 64, 32, 3), ("TENSOR", 768, 128, 1), ("TENSOR", 512, 256, 8)])
 def test_tmm_factor_order(hs, oracle, algo_name, k, a, rank):
     """do_Tmm (eggroll.rs:450-477): x @ param + (x·A)·Bᵀ for a parameter stored (in, out), whose
     factor block has the `out` rows first; the call takes the parameter transposed."""
