@@ -818,19 +818,21 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     }
 }
 
-// The prepass for layers whose rows fit the registers of a warp (512 <= k <= 1024) and whose whole B fits
+// The prepass for layers whose rows fit the registers of a warp (k <= 1024) and whose whole B fits
 // the shared memory of a CTA (ranks 1..4, 8, 16; ranks below 4 as rank 4 with zero columns, rank_true
 // values per row in the stream and in the cache).  Phase 1: the 256 threads regenerate (or copy from
-// the factor cache) all k rows of the pair's B into shared memory.  Phase 2: a warp loads two x rows
-// into registers ONCE and does everything with them there: the row maximum, the fp16 operand split,
-// and t = x * B, each lane multiplying the 4-value pieces it holds with the matching rows of B and
-// the warp adding its lanes' sums with a halving exchange.  lowrank_t_kernel reads x a second time,
-// 128 bytes per row and trip, for its t product and spends as long waiting for those trips as on
-// the generation.  Two CTAs share an SM, so one generates while the other streams x.
+// the factor cache) all k rows of the pair's B into shared memory, each thread a run of consecutive
+// rows, which are consecutive in the stream.  Phase 2: a warp loads RPR x rows into registers ONCE,
+// NJ 16-byte pieces per lane and row (2 rows of up to 1024 values, 4 of up to 256, 8 of up to 128:
+// as many as the registers hold), and does everything with them there: the row maximum, the fp16
+// operand split, and t = x * B, each lane multiplying the pieces it holds with the matching rows of
+// B and the warp adding its lanes' sums with a halving exchange.  lowrank_t_kernel reads x a second
+// time, 128 bytes per row and trip, for its t product and spends as long waiting for those trips as
+// on the generation.
 // B row kr is stored at row p = (kr / 128) * 128 + (kr % 4) * 32 + (kr % 128) / 4, its 16-byte
 // chunk c at chunk (c + p / (8 / RANK_G)) % RANK_G: the lanes of a warp, which hold pieces
 // 32 apart, then read consecutive rows, eight of them covering all banks.
-template <int RANK_G>
+template <int RANK_G, int NJ, int RPR>
 __global__ void __launch_bounds__(LT_THREADS, 2)
 lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
@@ -916,7 +918,7 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
     }
     __syncthreads();
 
-    // ---- phase 2: split and t of two rows per warp and round ----
+    // ---- phase 2: split and t of RPR rows per warp and round, NJ 16-byte pieces per lane and row ----
     const int n4 = k >> 2;
     uint32_t lo_nz = 0;  // any non-zero lo half written by this thread
     auto finish_row = [&](int64_t R, float m, float& sc) {
@@ -946,97 +948,111 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     };
     constexpr int NW = LT_THREADS / 32;
-    for (int lr = warp; lr < total_rows; lr += 2 * NW) {
-        const int lr1 = lr + NW;
-        const bool two = lr1 < total_rows;
-        const int64_t R0 = row_s[lr], R1 = row_s[two ? lr1 : lr];
-        const float4* s0 = reinterpret_cast<const float4*>(x + (size_t)R0 * x_stride);
-        const float4* s1 = reinterpret_cast<const float4*>(x + (size_t)R1 * x_stride);
-        float4 v0[8], v1[8];   // streaming loads: x passes once and must not push the jump tables out of L1
+    constexpr int N = RPR * RANK;   // sums of a warp and round: N[row * RANK + q]
+    const ulonglong2* bsm2 = reinterpret_cast<const ulonglong2*>(bsm);
+    for (int lr0 = warp * RPR; lr0 < total_rows; lr0 += NW * RPR) {
+        float4 v[RPR][NJ];   // streaming loads: x passes once and must not push the jump tables out of L1
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int i = lane + 32 * j;
-            v0[j] = i < n4 ? __ldcs(s0 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            v1[j] = (two && i < n4) ? __ldcs(s1 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < RPR; ++r) {
+            const bool valid = lr0 + r < total_rows;   // warp-uniform
+            const float4* src = reinterpret_cast<const float4*>(x + (size_t)row_s[valid ? lr0 + r : lr0] * x_stride);
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const int i = lane + 32 * j;
+                v[r][j] = (valid && i < n4) ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
         if (!skip_split) {
-            float m0 = 0.0f, m1 = 0.0f;
+            float sc[RPR];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                m0 = fmaxf(m0, fmaxf(fmaxf(fabsf(v0[j].x), fabsf(v0[j].y)), fmaxf(fabsf(v0[j].z), fabsf(v0[j].w))));
-                m1 = fmaxf(m1, fmaxf(fmaxf(fabsf(v1[j].x), fabsf(v1[j].y)), fmaxf(fabsf(v1[j].z), fabsf(v1[j].w))));
+            for (int r = 0; r < RPR; ++r) {
+                float m = 0.0f;
+#pragma unroll
+                for (int j = 0; j < NJ; ++j)
+                    m = fmaxf(m, fmaxf(fmaxf(fabsf(v[r][j].x), fabsf(v[r][j].y)), fmaxf(fabsf(v[r][j].z), fabsf(v[r][j].w))));
+                sc[r] = 1.0f;
+                if (lr0 + r < total_rows) finish_row(row_s[lr0 + r], m, sc[r]);   // warp-uniform branch
             }
-            float sc0, sc1 = 1.0f;
-            finish_row(R0, m0, sc0);
-            if (two) finish_row(R1, m1, sc1);   // warp-uniform branch
-            uint2* dh0 = reinterpret_cast<uint2*>(xhi + (size_t)R0 * k);
-            uint2* dl0 = reinterpret_cast<uint2*>(xlo + (size_t)R0 * k);
-            uint2* dh1 = reinterpret_cast<uint2*>(xhi + (size_t)R1 * k);
-            uint2* dl1 = reinterpret_cast<uint2*>(xlo + (size_t)R1 * k);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int i = lane + 32 * j;
-                if (i < n4) {
-                    uint2 h2, l2;
-                    split4(v0[j], sc0, h2, l2);
-                    dh0[i] = h2;
-                    if (!bf16) dl0[i] = l2;
-                    if (two) {
-                        split4(v1[j], sc1, h2, l2);
-                        dh1[i] = h2;
-                        if (!bf16) dl1[i] = l2;
+            for (int r = 0; r < RPR; ++r) {
+                if (lr0 + r < total_rows) {
+                    const int64_t R = row_s[lr0 + r];
+                    uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R * k);
+                    uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R * k);
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        const int i = lane + 32 * j;
+                        if (i < n4) {
+                            uint2 h2, l2;
+                            split4(v[r][j], sc[r], h2, l2);
+                            dh[i] = h2;
+                            if (!bf16) dl[i] = l2;
+                        }
                     }
                 }
             }
         }
-        // t of the two rows, two q per packed fp32 instruction: acc2[row * RANK / 2 + q / 2]
-        f32x2 acc2[RANK];
+        // t of the rows, two q per packed fp32 instruction: acc2[(row * RANK + q) / 2]
+        f32x2 acc2[N / 2];
 #pragma unroll
-        for (int i = 0; i < RANK; ++i) acc2[i] = 0ull;
-        const ulonglong2* bsm2 = reinterpret_cast<const ulonglong2*>(bsm);
+        for (int i = 0; i < N / 2; ++i) acc2[i] = 0ull;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             if (lane + 32 * j < n4) {
-                const f32x2 xa[4] = {pk2(v0[j].x, v0[j].x), pk2(v0[j].y, v0[j].y), pk2(v0[j].z, v0[j].z), pk2(v0[j].w, v0[j].w)};
-                const f32x2 xb[4] = {pk2(v1[j].x, v1[j].x), pk2(v1[j].y, v1[j].y), pk2(v1[j].z, v1[j].z), pk2(v1[j].w, v1[j].w)};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int p = j * 128 + e * 32 + lane;
+                    f32x2 xe[RPR];
+#pragma unroll
+                    for (int r = 0; r < RPR; ++r) {
+                        const float xv = e == 0 ? v[r][j].x : e == 1 ? v[r][j].y : e == 2 ? v[r][j].z : v[r][j].w;
+                        xe[r] = pk2(xv, xv);
+                    }
 #pragma unroll
                     for (int c = 0; c < RANK_G; ++c) {
                         const ulonglong2 b = bsm2[p * RANK_G + ((c + p / RP) % RANK_G)];
-                        acc2[2 * c] = fma2(xa[e], b.x, acc2[2 * c]);
-                        acc2[2 * c + 1] = fma2(xa[e], b.y, acc2[2 * c + 1]);
-                        acc2[RANK / 2 + 2 * c] = fma2(xb[e], b.x, acc2[RANK / 2 + 2 * c]);
-                        acc2[RANK / 2 + 2 * c + 1] = fma2(xb[e], b.y, acc2[RANK / 2 + 2 * c + 1]);
+#pragma unroll
+                        for (int r = 0; r < RPR; ++r) {
+                            acc2[r * (RANK / 2) + 2 * c] = fma2(xe[r], b.x, acc2[r * (RANK / 2) + 2 * c]);
+                            acc2[r * (RANK / 2) + 2 * c + 1] = fma2(xe[r], b.y, acc2[r * (RANK / 2) + 2 * c + 1]);
+                        }
                     }
                 }
             }
         }
-        float acc[2 * RANK];
+        float acc[N];
 #pragma unroll
-        for (int i = 0; i < RANK; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-        // halving exchange: after the step with distance off a lane keeps the half of its values
-        // that its bit `off` selects, summed with its partner's; 2 * RANK values end up one per
-        // group of 32 / (2 * RANK) lanes, value index = lane / group
-        int off = 16;
+        for (int i = 0; i < N / 2; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+        // halving exchange: in the step with distance off a lane keeps the half of its values that its
+        // bit `off` selects, summed with its partner's.  After the five steps a lane holds N / 32
+        // finished sums from index lane * N / 32 on (N >= 32), or groups of 32 / N lanes hold the sum
+        // of index lane / group (N < 32: the last steps add single values).
 #pragma unroll
-        for (int n = 2 * RANK; n > 1; n >>= 1) {
-            const bool up = (lane & off) != 0;
+        for (int s = 0; s < 5; ++s) {
+            const int n = N >> s, off = 16 >> s;
+            if (n > 1) {
+                const bool up = (lane & off) != 0;
 #pragma unroll
-            for (int i = 0; i < n / 2; ++i) {
-                const float send = up ? acc[i] : acc[i + n / 2];
-                const float keep = up ? acc[i + n / 2] : acc[i];
-                acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                for (int i = 0; i < n / 2; ++i) {
+                    const float send = up ? acc[i] : acc[i + n / 2];
+                    const float keep = up ? acc[i + n / 2] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            } else {
+                acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
             }
-            off >>= 1;
         }
-        for (; off > 0; off >>= 1) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
-        constexpr int GROUP = 32 / (2 * RANK) > 0 ? 32 / (2 * RANK) : 1;
-        const int idx = lane / GROUP;
+        constexpr int NF = N >= 32 ? N / 32 : 1;      // finished sums per lane
+        constexpr int GROUP = N >= 32 ? 1 : 32 / N;   // lanes holding the same sum
         if (lane % GROUP == 0) {
+            const int idx = (lane / GROUP) * NF;      // NF consecutive q of one row
             const int row = idx / RANK, q = idx - row * RANK;
-            if (row == 0 || two) t[(size_t)(row ? R1 : R0) * RANK + q] = acc[0];
+            if (lr0 + row < total_rows) {
+                float* dst = t + (size_t)row_s[lr0 + row] * RANK + q;
+                if (NF == 1) dst[0] = acc[0];
+                else if (NF == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+                else *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[NF > 2 ? 2 : 0], acc[NF > 3 ? 3 : 0]);
+            }
         }
     }
     // one flag per call tells the GEMM whether any lo half is non-zero (a set flag is not set again)
@@ -1248,25 +1264,31 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, g.factor_order == 1 ? g.a : 0, \
         reuse_split ? 1 : 0)
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
-        if ((g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k >= 512 && g.k <= 1024) {
-            // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel); short rows
-            // (the 64- and 256-wide layers of the token-level models, thousands of rows per pair) are
-            // faster in the block kernel, which keeps eight of them in flight per warp
+        if ((g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024) {
+            // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel)
             const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * (g.rank < 4 ? 4 : g.rank) * sizeof(float);   // at most 64 KB
-#define HSES_LTR(RG)                                                                                          \
+#define HSES_LTR(RG, NJ, RPR)                                                                                 \
     do {                                                                                                      \
-        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                       65536));                                                               \
-        lowrank_t_rows_kernel<RG><<<lt_grid, LT_THREADS, b_bytes, st>>>(                                      \
+        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG, NJ, RPR>,                                    \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));                  \
+        lowrank_t_rows_kernel<RG, NJ, RPR><<<lt_grid, LT_THREADS, b_bytes, st>>>(                             \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
             g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
             g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0);                                              \
     } while (0)
+            // rows in flight per warp: as many as the registers hold (16 pieces, 64 sums)
+#define HSES_LTR_K(RG, RPR1, RPR2)                                                                            \
+    do {                                                                                                      \
+        if (g.k <= 128) HSES_LTR(RG, 1, RPR1);                                                                \
+        else if (g.k <= 256) HSES_LTR(RG, 2, RPR2);                                                           \
+        else HSES_LTR(RG, 8, 2);                                                                              \
+    } while (0)
             switch ((g.rank + 3) / 4) {
-                case 1: HSES_LTR(1); break;
-                case 2: HSES_LTR(2); break;
-                default: HSES_LTR(4); break;
+                case 1: HSES_LTR_K(1, 8, 4); break;
+                case 2: HSES_LTR_K(2, 8, 4); break;
+                default: HSES_LTR_K(4, 4, 2); break;
             }
+#undef HSES_LTR_K
 #undef HSES_LTR
         } else
         switch ((g.rank + 3) / 4) {
