@@ -832,7 +832,7 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
 // B row kr is stored at row p = (kr / 128) * 128 + (kr % 4) * 32 + (kr % 128) / 4, its 16-byte
 // chunk c at chunk (c + p / (8 / RANK_G)) % RANK_G: the lanes of a warp, which hold pieces
 // 32 apart, then read consecutive rows, eight of them covering all banks.
-template <int RANK_G, int NJ, int RPR>
+template <int RANK_G, int NJ, int RPR, bool HALF>
 __global__ void __launch_bounds__(LT_THREADS, 2)
 lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
@@ -842,10 +842,11 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       int row_b0, int skip_split) {
     constexpr int RANK = RANK_G * 4;
     constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
+    constexpr int ROWS_CTA = HALF ? 2 * LT_ROWS : LT_ROWS;   // x rows per CTA
     extern __shared__ __align__(16) float bsm[];   // ceil(k / 128) * 128 rows of RANK floats
     __shared__ double2 log_tab_s[64];
     __shared__ uint32_t delta_s[512];
-    __shared__ int64_t row_s[LT_ROWS];
+    __shared__ int64_t row_s[ROWS_CTA];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (!cache_b) {
         for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
@@ -863,10 +864,10 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
     if (m_lo < 0) m_lo = 0;
     if (m_hi > n_pop) m_hi = n_pop;
     const int rows_per_step = (int)(m_hi - m_lo) * bm;
-    const int row0 = blockIdx.y * LT_ROWS;
-    const int total_rows = min(LT_ROWS, rows_per_step * t_steps - row0);
+    const int row0 = blockIdx.y * ROWS_CTA;
+    const int total_rows = min(ROWS_CTA, rows_per_step * t_steps - row0);
     if (total_rows <= 0) return;
-    if (tid < LT_ROWS) {
+    if (tid < ROWS_CTA) {
         int lr = row0 + (tid < total_rows ? tid : total_rows - 1);  // rows past the end repeat the last one
         int step = lr / rows_per_step, rr = lr - step * rows_per_step;
         row_s[tid] = ((int64_t)step * n_pop + m_lo) * bm + rr;
@@ -921,8 +922,13 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
     // ---- phase 2: split and t of RPR rows per warp and round, NJ 16-byte pieces per lane and row ----
     const int n4 = k >> 2;
     uint32_t lo_nz = 0;  // any non-zero lo half written by this thread
-    auto finish_row = [&](int64_t R, float m, float& sc) {
-        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    // HALF: rows of up to 64 values take half a warp each, so a warp works on 2 * RPR rows at a time
+    constexpr int W = HALF ? 16 : 32;              // lanes per row
+    constexpr int RSTEP = HALF ? 2 : 1;            // rows between a lane's consecutive rows
+    const int li = lane & (W - 1), hs = HALF ? lane >> 4 : 0;
+    auto finish_row = [&](int64_t R, float m, float& sc, bool valid) {
+#pragma unroll
+        for (int off = W / 2; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
         int e = 13 - ex;
         if (ex <= -127 || ex >= 128) e = 0;
@@ -930,7 +936,7 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         if (e < -100) e = -100;
         if (bf16) e = 0;   // one-pass mode: no scale
         sc = __uint_as_float((uint32_t)(127 + e) << 23);
-        if (lane == 0 && !skip_split) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
+        if (li == 0 && valid) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
     };
     auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
         if (bf16) {   // hi = bf16(v), the lo half is neither written nor read
@@ -948,17 +954,19 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
     };
     constexpr int NW = LT_THREADS / 32;
-    constexpr int N = RPR * RANK;   // sums of a warp and round: N[row * RANK + q]
+    constexpr int RW = RPR * RSTEP;   // rows of a warp and round
+    constexpr int N = RPR * RANK;     // sums of a lane group and round: N[row * RANK + q]
     const ulonglong2* bsm2 = reinterpret_cast<const ulonglong2*>(bsm);
-    for (int lr0 = warp * RPR; lr0 < total_rows; lr0 += NW * RPR) {
+    for (int lr0 = warp * RW; lr0 < total_rows; lr0 += NW * RW) {
         float4 v[RPR][NJ];   // streaming loads: x passes once and must not push the jump tables out of L1
 #pragma unroll
         for (int r = 0; r < RPR; ++r) {
-            const bool valid = lr0 + r < total_rows;   // warp-uniform
-            const float4* src = reinterpret_cast<const float4*>(x + (size_t)row_s[valid ? lr0 + r : lr0] * x_stride);
+            const int lr = lr0 + r * RSTEP + hs;
+            const bool valid = lr < total_rows;   // the same for all lanes of a row
+            const float4* src = reinterpret_cast<const float4*>(x + (size_t)row_s[valid ? lr : lr0] * x_stride);
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
-                const int i = lane + 32 * j;
+                const int i = li + 32 * j;
                 v[r][j] = (valid && i < n4) ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
@@ -966,22 +974,23 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
             float sc[RPR];
 #pragma unroll
             for (int r = 0; r < RPR; ++r) {
+                const int lr = lr0 + r * RSTEP + hs;
                 float m = 0.0f;
 #pragma unroll
                 for (int j = 0; j < NJ; ++j)
                     m = fmaxf(m, fmaxf(fmaxf(fabsf(v[r][j].x), fabsf(v[r][j].y)), fmaxf(fabsf(v[r][j].z), fabsf(v[r][j].w))));
-                sc[r] = 1.0f;
-                if (lr0 + r < total_rows) finish_row(row_s[lr0 + r], m, sc[r]);   // warp-uniform branch
+                finish_row(row_s[lr < total_rows ? lr : lr0], m, sc[r], lr < total_rows);
             }
 #pragma unroll
             for (int r = 0; r < RPR; ++r) {
-                if (lr0 + r < total_rows) {
-                    const int64_t R = row_s[lr0 + r];
+                const int lr = lr0 + r * RSTEP + hs;
+                if (lr < total_rows) {
+                    const int64_t R = row_s[lr];
                     uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R * k);
                     uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R * k);
 #pragma unroll
                     for (int j = 0; j < NJ; ++j) {
-                        const int i = lane + 32 * j;
+                        const int i = li + 32 * j;
                         if (i < n4) {
                             uint2 h2, l2;
                             split4(v[r][j], sc[r], h2, l2);
@@ -998,10 +1007,10 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         for (int i = 0; i < N / 2; ++i) acc2[i] = 0ull;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
-            if (lane + 32 * j < n4) {
+            if (li + 32 * j < n4) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int p = j * 128 + e * 32 + lane;
+                    const int p = j * 128 + e * 32 + li;
                     f32x2 xe[RPR];
 #pragma unroll
                     for (int r = 0; r < RPR; ++r) {
@@ -1023,13 +1032,14 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         float acc[N];
 #pragma unroll
         for (int i = 0; i < N / 2; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-        // halving exchange: in the step with distance off a lane keeps the half of its values that its
-        // bit `off` selects, summed with its partner's.  After the five steps a lane holds N / 32
-        // finished sums from index lane * N / 32 on (N >= 32), or groups of 32 / N lanes hold the sum
-        // of index lane / group (N < 32: the last steps add single values).
+        // halving exchange over the W lanes of a row group: in the step with distance off a lane keeps
+        // the half of its values that its bit `off` selects, summed with its partner's.  After the
+        // steps a lane holds N / W finished sums from index li * N / W on (N >= W), or groups of W / N
+        // lanes hold the sum of index li / group (N < W: the last steps add single values).
+        constexpr int STEPS = HALF ? 4 : 5;
 #pragma unroll
-        for (int s = 0; s < 5; ++s) {
-            const int n = N >> s, off = 16 >> s;
+        for (int s = 0; s < STEPS; ++s) {
+            const int n = N >> s, off = (W / 2) >> s;
             if (n > 1) {
                 const bool up = (lane & off) != 0;
 #pragma unroll
@@ -1042,13 +1052,14 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                 acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
             }
         }
-        constexpr int NF = N >= 32 ? N / 32 : 1;      // finished sums per lane
-        constexpr int GROUP = N >= 32 ? 1 : 32 / N;   // lanes holding the same sum
-        if (lane % GROUP == 0) {
-            const int idx = (lane / GROUP) * NF;      // NF consecutive q of one row
+        constexpr int NF = N >= W ? N / W : 1;      // finished sums per lane
+        constexpr int GROUP = N >= W ? 1 : W / N;   // lanes holding the same sum
+        if (li % GROUP == 0) {
+            const int idx = (li / GROUP) * NF;      // NF consecutive q of one row
             const int row = idx / RANK, q = idx - row * RANK;
-            if (lr0 + row < total_rows) {
-                float* dst = t + (size_t)row_s[lr0 + row] * RANK + q;
+            const int lr = lr0 + row * RSTEP + hs;
+            if (lr < total_rows) {
+                float* dst = t + (size_t)row_s[lr] * RANK + q;
                 if (NF == 1) dst[0] = acc[0];
                 else if (NF == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
                 else *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[NF > 2 ? 2 : 0], acc[NF > 3 ? 3 : 0]);
@@ -1267,21 +1278,24 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         if ((g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024) {
             // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel)
             const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * (g.rank < 4 ? 4 : g.rank) * sizeof(float);   // at most 64 KB
-#define HSES_LTR(RG, NJ, RPR)                                                                                 \
+#define HSES_LTR(RG, NJ, RPR, HALF)                                                                               \
     do {                                                                                                      \
-        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG, NJ, RPR>,                                    \
+        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG, NJ, RPR, HALF>,                              \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));                  \
-        lowrank_t_rows_kernel<RG, NJ, RPR><<<lt_grid, LT_THREADS, b_bytes, st>>>(                             \
+        lowrank_t_rows_kernel<RG, NJ, RPR, HALF><<<HALF ? lt_grid2 : lt_grid, LT_THREADS, b_bytes, st>>>(     \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
             g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
             g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0);                                              \
     } while (0)
-            // rows in flight per warp: as many as the registers hold (16 pieces, 64 sums)
+            // rows in flight per warp: as many as the registers hold (16 pieces, 64 sums); rows of up to 64
+            // values take half a warp each, and a CTA twice the rows
+            dim3 lt_grid2(lt_grid.x, (lt_grid.y + 1) / 2);
 #define HSES_LTR_K(RG, RPR1, RPR2)                                                                            \
     do {                                                                                                      \
-        if (g.k <= 128) HSES_LTR(RG, 1, RPR1);                                                                \
-        else if (g.k <= 256) HSES_LTR(RG, 2, RPR2);                                                           \
-        else HSES_LTR(RG, 8, 2);                                                                              \
+        if (g.k <= 64) HSES_LTR(RG, 1, RPR1, true);                                                           \
+        else if (g.k <= 128) HSES_LTR(RG, 1, RPR1, false);                                                    \
+        else if (g.k <= 256) HSES_LTR(RG, 2, RPR2, false);                                                    \
+        else HSES_LTR(RG, 8, 2, false);                                                                       \
     } while (0)
             switch ((g.rank + 3) / 4) {
                 case 1: HSES_LTR_K(1, 8, 4); break;
