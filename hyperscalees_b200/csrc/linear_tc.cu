@@ -93,17 +93,21 @@ struct TcArgs {
     // older phase for the one it waits for.  Hence ring_depth is a multiple of gens, and even
     // when an item belongs to one of the two epilogue warps.
     int ring_depth, gens;
+    // Operand ring: stages in use and bytes per stage.  The one-pass mode loads one x tile and one W
+    // tile per k-block instead of two of each, so the same shared memory holds twice the stages.
+    int n_stages, stage_bytes;
 };
 
 template <int BN>
 struct TcSmem {
-    static constexpr int STAGES = BN == 256 ? 2 : 3;
+    static constexpr int STAGES = BN == 256 ? 2 : 3;   // with both halves of both operands in a stage
+    static constexpr int MAX_STAGES = 2 * STAGES;      // with one half of each (one-pass mode)
     static constexpr int X_BYTES = BM_TILE * BK * 2;
     static constexpr int W_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = 2 * X_BYTES + 2 * W_BYTES;
     static constexpr int HOP_BYTES = 0;     // the hop table is read through L1;
     static constexpr int TAB_BYTES = 1280;  // the logarithm's helper table and the thresholds as 2 x 128 bytes
-    static constexpr int BAR_BYTES = 608;
+    static constexpr int BAR_BYTES = 656;
     static constexpr int FIXED = STAGES * STAGE_BYTES + HOP_BYTES + TAB_BYTES + BAR_BYTES + 1024;
     static constexpr int LIMIT = 232448;  // 227 KB of dynamic shared memory per CTA
     // ring of staged A rows: 4 quadrants * depth items * rows of an item * rank floats
@@ -128,8 +132,8 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     float* a_stage = reinterpret_cast<float*>(smem + S::STAGES * S::STAGE_BYTES + S::HOP_BYTES + S::TAB_BYTES +
                                               S::BAR_BYTES);
     uint64_t* full = bars;                   // [STAGES] TMA landed
-    uint64_t* empty = bars + S::STAGES;      // [STAGES] MMAs finished reading the stage
-    uint64_t* tfull = bars + 2 * S::STAGES;  // [2] accumulator ready
+    uint64_t* empty = bars + S::MAX_STAGES;      // [MAX_STAGES] MMAs finished reading the stage
+    uint64_t* tfull = bars + 2 * S::MAX_STAGES;  // [2] accumulator ready
     uint64_t* tempty = tfull + 2;            // [2] accumulator drained
     uint64_t* afull = tempty + 2;                     // [4][MAX_DEPTH] ring slot staged
     uint64_t* aempty = afull + 4 * MAX_DEPTH;         // [4][MAX_DEPTH] ring slot consumed
@@ -140,10 +144,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
     const int m_tiles = (int)(g.rows / BM_TILE);
     const int n_chunks = (g.a + BN - 1) / BN;   // columns past a in the last chunk: zero rows of W (TMA fill), never stored
     const int k_blocks = (g.k + BK - 1) / BK;  // a ragged last block is zero-filled by TMA
+    // inside a stage: x hi, (x lo,) W hi, (W lo); the one-pass mode packs the two tiles it loads
+    const int w_off = g.one_pass ? TcSmem<BN>::X_BYTES : 2 * TcSmem<BN>::X_BYTES;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int s = 0; s < S::STAGES; ++s) {
+        for (int s = 0; s < S::MAX_STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -193,22 +199,22 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
             for (int mt = blockIdx.x; mt < m_tiles && ok; mt += gridDim.x) {
                 for (int c = 0; c < n_chunks && ok; ++c) {
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                        int s = it % S::STAGES;
-                        uint32_t ph = (it / S::STAGES) & 1;
+                        int s = it % g.n_stages;
+                        uint32_t ph = (it / g.n_stages) & 1;
                         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, g.status, 1)) { ok = false; break; }
-                        uint8_t* st = stage_base + s * S::STAGE_BYTES;
+                        uint8_t* st = stage_base + s * g.stage_bytes;
                         mbar_expect_tx(&full[s], (skip_xlo ? 1 : 2) * S::X_BYTES + (g.one_pass ? 1 : 2) * S::W_BYTES);
                         tma_load_2d(st, &tm_xhi, kb * BK, mt * BM_TILE, &full[s]);
                         if (!skip_xlo) tma_load_2d(st + S::X_BYTES, &tm_xlo, kb * BK, mt * BM_TILE, &full[s]);
-                        tma_load_2d(st + 2 * S::X_BYTES, &tm_whi, kb * BK, c * BN, &full[s]);
-                        if (!g.one_pass) tma_load_2d(st + 2 * S::X_BYTES + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
+                        tma_load_2d(st + w_off, &tm_whi, kb * BK, c * BN, &full[s]);
+                        if (!g.one_pass) tma_load_2d(st + w_off + S::W_BYTES, &tm_wlo, kb * BK, c * BN, &full[s]);
                     }
                 }
             }
             if (!ok) {
                 // copies already issued still land in this CTA's shared memory: give them a
                 // bounded moment before the block is torn down
-                for (int s = 0; s < S::STAGES; ++s)
+                for (int s = 0; s < g.n_stages; ++s)
                     for (uint32_t i = 0; i < 4096; ++i) {
                         if (mbar_try(&full[s], 0) || mbar_try(&full[s], 1)) break;
                         __nanosleep(256);
@@ -229,14 +235,14 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     tc_fence_after();
                     uint32_t d = tmem_base + (uint32_t)(b * BN);
                     for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                        int s = it % S::STAGES;
-                        uint32_t ph = (it / S::STAGES) & 1;
+                        int s = it % g.n_stages;
+                        uint32_t ph = (it / g.n_stages) & 1;
                         if (!mbar_wait(&full[s], ph, abort_flag, g.status, 3)) { ok = false; break; }
                         tc_fence_after();
-                        uint8_t* st = stage_base + s * S::STAGE_BYTES;
+                        uint8_t* st = stage_base + s * g.stage_bytes;
                         uint64_t dxh = make_smem_desc(st), dxl = make_smem_desc(st + S::X_BYTES);
-                        uint64_t dwh = make_smem_desc(st + 2 * S::X_BYTES);
-                        uint64_t dwl = make_smem_desc(st + 2 * S::X_BYTES + S::W_BYTES);
+                        uint64_t dwh = make_smem_desc(st + w_off);
+                        uint64_t dwl = make_smem_desc(st + w_off + S::W_BYTES);
 #pragma unroll
                         for (int ks = 0; ks < BK / 16; ++ks) {
                             uint64_t off = (uint64_t)(ks * 32 >> 4);  // 16 fp16 = 32 B along K
@@ -1162,6 +1168,8 @@ int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const T
     if (rc == HSES_OK) rc = make_map(&tm_wlo, sc.wlo, g.a, g.k, g.k, BN);
     if (rc != HSES_OK) return rc;
     using S = TcSmem<BN>;
+    ta.n_stages = ta.one_pass ? S::MAX_STAGES : S::STAGES;
+    ta.stage_bytes = ta.one_pass ? S::X_BYTES + S::W_BYTES : S::STAGE_BYTES;
     int smem_bytes = S::FIXED + (g.perturb ? S::a_bytes(ta.ring_depth, ta.rank) : 0);
     HSES_REQUIRE(smem_bytes <= S::LIMIT, "shared memory budget exceeded");
     int m_tiles = (int)(rows / BM_TILE);
