@@ -114,6 +114,27 @@ struct TcSmem {
     static int a_bytes(int depth, int rank) { return 4 * depth * item_rows(rank) * rank * 4; }
 };
 
+// Eight consecutive floats of an output row: one 256-bit store when `wide` (p on a 32-byte boundary),
+// else two 16-byte stores.  streaming: written once and not read again by this kernel.
+__device__ __forceinline__ void store8(float* p, const float (&v)[8], bool wide, bool streaming) {
+    if (wide) {
+        if (streaming)
+            asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]),
+                         "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                         : "memory");
+        else
+            asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(v[0]), "f"(v[1]),
+                         "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                         : "memory");
+    } else if (streaming) {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+        __stcs(reinterpret_cast<float4*>(p + 4), make_float4(v[4], v[5], v[6], v[7]));
+    } else {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 // ----------------------------------------------------------------------- kernel
 // RG = rank / 4 (0: clean product, no noise).  The rank is a template parameter so that the
 // per-column dot product unrolls exactly and the epilogue loop stays small enough for the
@@ -270,6 +291,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
         const int eh = (warp - EPI_WARP0) >> 2;
         const float out_scale = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
+        // every 8-column piece of every output row starts on a 32-byte boundary
+        const bool wide_out = (reinterpret_cast<uintptr_t>(g.out) & 31) == 0 && (g.out_stride & 7) == 0 &&
+                              (!g.pot || (reinterpret_cast<uintptr_t>(g.pot) & 31) == 0);
         const int depth = g.ring_depth;
         const int items_per_tile = g.a / IT::ROWS;
         uint32_t acc_it = 0;
@@ -347,22 +371,24 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                             if (RG > 0) v = __fadd_rn(v, odd_member ? -u[j] : u[j]);
                             y[j] = v;
                         }
+                        // eight consecutive outputs of a row are one 32-byte sector: a single 256-bit store
+                        // where the row starts on a sector boundary (half the store instructions and half
+                        // the data-path cycles of two 16-byte stores, which is what the epilogue spends
+                        // most of its time on once the product is a single pass)
                         if (g.lif) {
+                            float cv[8], sv[8];
 #pragma unroll
-                            for (int j = 0; j < 8; j += 4) {
-                                float4 cv = make_float4(__fmul_rn(y[j], g.leak), __fmul_rn(y[j + 1], g.leak),
-                                                        __fmul_rn(y[j + 2], g.leak), __fmul_rn(y[j + 3], g.leak));
-                                if (prow) *reinterpret_cast<float4*>(prow + j0 + j) = cv;
-                                float4 sv = make_float4(cv.x >= g.v_th ? 1.0f : 0.0f, cv.y >= g.v_th ? 1.0f : 0.0f,
-                                                        cv.z >= g.v_th ? 1.0f : 0.0f, cv.w >= g.v_th ? 1.0f : 0.0f);
-                                __stcs(reinterpret_cast<float4*>(orow + j0 + j), sv);
+                            for (int j = 0; j < 8; ++j) {
+                                cv[j] = __fmul_rn(y[j], g.leak);
+                                sv[j] = cv[j] >= g.v_th ? 1.0f : 0.0f;
                             }
+                            if (prow) store8(prow + j0, cv, wide_out, false);
+                            store8(orow + j0, sv, wide_out, true);
                         } else {
+                            float o[8];
 #pragma unroll
-                            for (int j = 0; j < 8; j += 4)
-                                *reinterpret_cast<float4*>(orow + j0 + j) =
-                                    make_float4(__fmul_rn(y[j], out_scale), __fmul_rn(y[j + 1], out_scale),
-                                                __fmul_rn(y[j + 2], out_scale), __fmul_rn(y[j + 3], out_scale));
+                            for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(y[j], out_scale);
+                            store8(orow + j0, o, wide_out, false);
                         }
                     }
                     if (RG > 0) mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // the item's reader(s) hand the slot back
