@@ -288,6 +288,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
         // rank-r term of those columns has been summed from the staged A rows)
         using IT = Item<RG>;
         constexpr int RANK = RG * 4;
+        // 8-column pieces in flight: with rank <= 4 the registers hold two, and nothing else would
+        // cover the latency of the accumulator load
+        constexpr int H = RG <= 1 ? 2 : 1;
         const int q4 = warp & 3;  // TMEM lane quadrant this warp may read (warp id mod 4)
         const int eh = (warp - EPI_WARP0) >> 2;
         const float out_scale = g.out_scale_ptr ? *g.out_scale_ptr : g.out_scale;
@@ -338,57 +341,76 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     float* orow = g.out + (size_t)R * g.out_stride + n0;
                     float* prow = (g.lif && g.pot) ? g.pot + (size_t)R * g.out_stride + n0 : nullptr;
 #pragma unroll 1
-                    for (int j0 = 0; j0 < 16; j0 += 8) {
-                        uint32_t acc[8];
-                        tmem_ld8_issue(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(b * BN + cb * 32 + eh * 16 + j0), acc);
-                        const float4 cs0 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0);
-                        const float4 cs1 = *reinterpret_cast<const float4*>(g.col_scale + n0 + j0 + 4);
+                    for (int j0 = 0; j0 < 16; j0 += 8 * H) {
+                        uint32_t acc[H][8];
+#pragma unroll
+                        for (int h = 0; h < H; ++h)
+                            tmem_ld8_issue(tmem_base + ((uint32_t)(q4 * 32) << 16) +
+                                           (uint32_t)(b * BN + cb * 32 + eh * 16 + j0 + 8 * h), acc[h]);
+                        float cs[H][8];
+#pragma unroll
+                        for (int h = 0; h < H; ++h) {
+                            // the one-pass mode scales nothing: no loads then
+                            const float4 cs0 = g.one_pass ? make_float4(1.f, 1.f, 1.f, 1.f)
+                                                          : *reinterpret_cast<const float4*>(g.col_scale + n0 + j0 + 8 * h);
+                            const float4 cs1 = g.one_pass ? make_float4(1.f, 1.f, 1.f, 1.f)
+                                                          : *reinterpret_cast<const float4*>(g.col_scale + n0 + j0 + 8 * h + 4);
+                            cs[h][0] = cs0.x; cs[h][1] = cs0.y; cs[h][2] = cs0.z; cs[h][3] = cs0.w;
+                            cs[h][4] = cs1.x; cs[h][5] = cs1.y; cs[h][6] = cs1.z; cs[h][7] = cs1.w;
+                        }
                         // u[j] = sum_q t[q] * (base_sigma * A[n0+j0+j][q]), q ascending, one rounding per
                         // multiply-add; two neighbouring columns advance together in one packed fma
-                        f32x2 u2[4] = {0ull, 0ull, 0ull, 0ull};
+                        f32x2 u2[H][4];
+#pragma unroll
+                        for (int h = 0; h < H; ++h) u2[h][0] = u2[h][1] = u2[h][2] = u2[h][3] = 0ull;
                         if (RG > 0) {
 #pragma unroll
                             for (int q = 0; q < RANK; ++q) {
-                                const ulonglong2 a01 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0));
-                                const ulonglong2 a23 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0 + 4));
-                                u2[0] = fma2(tq2[q], a01.x, u2[0]);
-                                u2[1] = fma2(tq2[q], a01.y, u2[1]);
-                                u2[2] = fma2(tq2[q], a23.x, u2[2]);
-                                u2[3] = fma2(tq2[q], a23.y, u2[3]);
+#pragma unroll
+                                for (int h = 0; h < H; ++h) {
+                                    const ulonglong2 a01 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0 + 8 * h));
+                                    const ulonglong2 a23 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0 + 8 * h + 4));
+                                    u2[h][0] = fma2(tq2[q], a01.x, u2[h][0]);
+                                    u2[h][1] = fma2(tq2[q], a01.y, u2[h][1]);
+                                    u2[h][2] = fma2(tq2[q], a23.x, u2[h][2]);
+                                    u2[h][3] = fma2(tq2[q], a23.y, u2[h][3]);
+                                }
                             }
                         }
-                        float u[8];
-                        upk2(u2[0], u[0], u[1]); upk2(u2[1], u[2], u[3]);
-                        upk2(u2[2], u[4], u[5]); upk2(u2[3], u[6], u[7]);
-                        const float cs[8] = {cs0.x, cs0.y, cs0.z, cs0.w, cs1.x, cs1.y, cs1.z, cs1.w};
                         tmem_ld_wait();
-                        float y[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            // undo the two power-of-two operand scales (exact); the member's sign is applied to
-                            // the finished sum (negating every term of a sum negates the sum exactly)
-                            float v = __fmul_rn(__fmul_rn(__uint_as_float(acc[j]), rs), cs[j]);
-                            if (RG > 0) v = __fadd_rn(v, odd_member ? -u[j] : u[j]);
-                            y[j] = v;
-                        }
-                        // eight consecutive outputs of a row are one 32-byte sector: a single 256-bit store
-                        // where the row starts on a sector boundary (half the store instructions and half
-                        // the data-path cycles of two 16-byte stores, which is what the epilogue spends
-                        // most of its time on once the product is a single pass)
-                        if (g.lif) {
-                            float cv[8], sv[8];
+                        for (int h = 0; h < H; ++h) {
+                            float u[8];
+                            upk2(u2[h][0], u[0], u[1]); upk2(u2[h][1], u[2], u[3]);
+                            upk2(u2[h][2], u[4], u[5]); upk2(u2[h][3], u[6], u[7]);
+                            float y[8];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                cv[j] = __fmul_rn(y[j], g.leak);
-                                sv[j] = cv[j] >= g.v_th ? 1.0f : 0.0f;
+                                // undo the two power-of-two operand scales (exact); the member's sign is applied to
+                                // the finished sum (negating every term of a sum negates the sum exactly)
+                                float v = __fmul_rn(__fmul_rn(__uint_as_float(acc[h][j]), rs), cs[h][j]);
+                                if (RG > 0) v = __fadd_rn(v, odd_member ? -u[j] : u[j]);
+                                y[j] = v;
                             }
-                            if (prow) store8(prow + j0, cv, wide_out, false);
-                            store8(orow + j0, sv, wide_out, true);
-                        } else {
-                            float o[8];
+                            // eight consecutive outputs of a row are one 32-byte sector: a single 256-bit store
+                            // where the row starts on a sector boundary (half the store instructions and half
+                            // the data-path cycles of two 16-byte stores, which is what the epilogue spends
+                            // most of its time on once the product is a single pass)
+                            if (g.lif) {
+                                float cv[8], sv[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(y[j], out_scale);
-                            store8(orow + j0, o, wide_out, false);
+                                for (int j = 0; j < 8; ++j) {
+                                    cv[j] = __fmul_rn(y[j], g.leak);
+                                    sv[j] = cv[j] >= g.v_th ? 1.0f : 0.0f;
+                                }
+                                if (prow) store8(prow + j0 + 8 * h, cv, wide_out, false);
+                                store8(orow + j0 + 8 * h, sv, wide_out, true);
+                            } else {
+                                float o[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) o[j] = __fmul_rn(y[j], out_scale);
+                                store8(orow + j0 + 8 * h, o, wide_out, false);
+                            }
                         }
                     }
                     if (RG > 0) mbar_arrive(&aempty[q4 * MAX_DEPTH + slot]);  // the item's reader(s) hand the slot back
