@@ -136,10 +136,11 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8], bool wide,
 }
 
 // ----------------------------------------------------------------------- kernel
+// R1: the factor rank is 1 (run as RG = 1): the epilogue leaves out the three zero columns of t and A.
 // RG = rank / 4 (0: clean product, no noise).  The rank is a template parameter so that the
 // per-column dot product unrolls exactly and the epilogue loop stays small enough for the
 // instruction cache.
-template <int BN, int RG>
+template <int BN, int RG, bool R1 = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_constant__ CUtensorMap tm_xlo,
                  const __grid_constant__ CUtensorMap tm_whi, const __grid_constant__ CUtensorMap tm_wlo,
@@ -365,7 +366,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                         for (int h = 0; h < H; ++h) u2[h][0] = u2[h][1] = u2[h][2] = u2[h][3] = 0ull;
                         if (RG > 0) {
 #pragma unroll
-                            for (int q = 0; q < RANK; ++q) {
+                            for (int q = 0; q < (R1 ? 1 : RANK); ++q) {   // zero columns add nothing
 #pragma unroll
                                 for (int h = 0; h < H; ++h) {
                                     const ulonglong2 a01 = *reinterpret_cast<const ulonglong2*>(my_a + IT::at(q, j0 + 8 * h));
@@ -1171,14 +1172,14 @@ TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     return s;
 }
 
-template <int BN, int RG>
+template <int BN, int RG, bool R1 = false>
 int launch_tc_rg(hses_ctx* ctx, cudaStream_t st, const CUtensorMap& tm_x, const CUtensorMap& tm_xlo,
                  const CUtensorMap& tm_whi, const CUtensorMap& tm_wlo, const TcArgs& ta, int grid,
                  int smem_bytes) {
-    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN, RG, R1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    smem_bytes));
     HSES_KERNEL(ctx, st, "linear_tc");
-    linear_tc_kernel<BN, RG><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_xlo, tm_whi, tm_wlo, ta);
+    linear_tc_kernel<BN, RG, R1><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_xlo, tm_whi, tm_wlo, ta);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -1224,7 +1225,9 @@ int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const T
     int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;
     switch (ta.rank / 4) {
         case 0: return launch_tc_rg<BN, 0>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
-        case 1: return launch_tc_rg<BN, 1>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        case 1:
+            if (ta.rank_true == 1) return launch_tc_rg<BN, 1, true>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+            return launch_tc_rg<BN, 1>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
         case 2: return launch_tc_rg<BN, 2>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
         case 4: return launch_tc_rg<BN, 4>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
         case 8: return launch_tc_rg<BN, 8>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
