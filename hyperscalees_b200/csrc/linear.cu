@@ -237,8 +237,9 @@ static int check_args(const hses_linear_args* g) {
 int resolve_factor_cache(const hses_linear_args& g, const float** A, const float** B) {
     HSES_REQUIRE(g.cache != nullptr && g.cache->data != nullptr, "factor cache is NULL");
     const hses_factor_cache& c = *g.cache;
+    const int groups = g.n_groups > 1 ? g.n_groups : 1;   // grouped layout: B is (n_pairs, groups, k, rank)
     HSES_REQUIRE(c.key == g.key && c.true_epoch == true_epoch_of(g.epoch, g.noise_reuse) &&
-                     c.rank == g.rank && c.a == g.a && c.b == g.k,
+                     c.rank == g.rank && c.a == g.a && c.b == g.k * groups,
                  "factor cache was built for another parameter, epoch bucket or shape");
     int32_t first_pair = g.first_thread / 2;
     int64_t last_pair = ((int64_t)g.first_thread + g.n_pop - 1) / 2;
@@ -370,6 +371,7 @@ size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     }
     // the tensor path always needs room for the split weights, the general path
     // only needs scratch when it perturbs
+    if (g->n_groups > 1) return tensor_path_supports(*g) ? tensor_path_workspace_bytes(*g) : 0;
     if (prefers_small_path(*g)) return small_path_workspace_bytes(*g);
     if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_TENSOR) && tensor_path_supports(*g))
         return tensor_path_workspace_bytes(*g);
@@ -419,6 +421,15 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
         if (rc != HSES_OK) return rc;
         return hses_lif_scan(ctx, stream, g->out, g->t_steps, g->n_pop * g->bm, g->a, g->out_row_stride, nullptr,
                              g->tau_m, g->v_th, g->reset_mode, g->out);
+    }
+    if (g->n_groups > 1) {
+        // several parameters stacked in one call: the tensor-core path or nothing
+        if ((g->algo != HSES_ALGO_AUTO && g->algo != HSES_ALGO_TENSOR) || !tensor_path_supports(*g)) {
+            set_error("hses_perturbed_linear: n_groups > 1 needs the tensor-core path, a grouped factor cache and "
+                      "shapes it covers");
+            return HSES_ERR_UNSUPPORTED;
+        }
+        return run_tensor_path(ctx, as_stream(stream), *g);
     }
     if (prefers_small_path(*g)) return run_small_path(ctx, as_stream(stream), *g);
     bool tc_ok = tensor_path_supports(*g);

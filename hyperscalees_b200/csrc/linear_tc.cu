@@ -74,7 +74,9 @@ struct TcArgs {
     uint64_t key;
     int32_t true_epoch, first_thread;
     float base_sigma, leak, v_th, out_scale;
-    const float* t;       // (rows, rank)
+    const float* t;       // (rows, t_stride): rank columns per group of output columns
+    int t_stride;         // floats between rows of t: groups * rank
+    int group_cols;       // output columns per group (several stacked parameters), 0: one parameter
     const float* out_scale_ptr;  // device gain overriding out_scale, or NULL
     const float* row_scale;  // (rows): 2^-e of the power-of-two scale applied to each x row
     const float* col_scale;  // (a):    the same for each row of the parameter
@@ -314,7 +316,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                 odd_member = (thread_id & 1) != 0;  // sign -1: A of the pair is negated for this row
 #pragma unroll
                 for (int q = 0; q < RANK; q += 4) {
-                    float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * RANK + q);
+                    float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * g.t_stride + q);
                     tq2[q] = pk2(tv.x, tv.x); tq2[q + 1] = pk2(tv.y, tv.y);
                     tq2[q + 2] = pk2(tv.z, tv.z); tq2[q + 3] = pk2(tv.w, tv.w);
                 }
@@ -328,6 +330,16 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     if (n0 >= g.a) continue;                     // ragged last chunk: no such columns, no such item
                     const float* my_a = nullptr;
                     int slot = 0;
+                    if (RG > 0 && g.group_cols) {
+                        // stacked parameters: these columns' group has its own t (its own B)
+                        const float* tg = g.t + (size_t)R * g.t_stride + (n0 / g.group_cols) * RANK;
+#pragma unroll
+                        for (int q = 0; q < RANK; q += 4) {
+                            float4 tv = *reinterpret_cast<const float4*>(tg + q);
+                            tq2[q] = pk2(tv.x, tv.x); tq2[q + 1] = pk2(tv.y, tv.y);
+                            tq2[q + 2] = pk2(tv.z, tv.z); tq2[q + 3] = pk2(tv.w, tv.w);
+                        }
+                    }
                     if (RG > 0) {
                         // the item that holds these columns: one generator warp staged it
                         const uint32_t item = tile_no * (uint32_t)items_per_tile +
@@ -894,7 +906,7 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                       __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
                       const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true,
-                      int row_b0, int skip_split) {
+                      int row_b0, int skip_split, int n_groups) {
     constexpr int RANK = RANK_G * 4;
     constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
     constexpr int ROWS_CTA = HALF ? 2 * LT_ROWS : LT_ROWS;   // x rows per CTA
@@ -932,19 +944,28 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
     // ---- phase 1: B of this pair ----
     float4* bsm4 = reinterpret_cast<float4*>(bsm);
     auto stored_row = [](int kr) { return (kr & ~127) + (kr & 3) * 32 + ((kr & 127) >> 2); };
+    // several stacked parameters (n_groups > 1, cached factors only): group g's B block sits at
+    // bsm + g * gstride floats and came from cache block (pair, g)
+    const int gstride = ((k + 127) & ~127) * RANK;
     if (cache_b && rank_true < 4) {
-        const float* cb1 = cache_b + (size_t)blockIdx.x * k * rank_true;
-        for (int kr = tid; kr < k; kr += LT_THREADS) {
-            const float* row = cb1 + (size_t)kr * rank_true;
-            bsm4[stored_row(kr)] = make_float4(__ldg(row), rank_true > 1 ? __ldg(row + 1) : 0.0f,
-                                               rank_true > 2 ? __ldg(row + 2) : 0.0f, 0.0f);
+        for (int grp = 0; grp < n_groups; ++grp) {
+            const float* cb1 = cache_b + ((size_t)blockIdx.x * n_groups + grp) * k * rank_true;
+            float4* dst = bsm4 + grp * (gstride / 4);
+            for (int kr = tid; kr < k; kr += LT_THREADS) {
+                const float* row = cb1 + (size_t)kr * rank_true;
+                dst[stored_row(kr)] = make_float4(__ldg(row), rank_true > 1 ? __ldg(row + 1) : 0.0f,
+                                                  rank_true > 2 ? __ldg(row + 2) : 0.0f, 0.0f);
+            }
         }
     } else if (cache_b) {
-        const float4* cb4 = reinterpret_cast<const float4*>(cache_b + (size_t)blockIdx.x * k * RANK);
-        for (int i = tid; i < k * RANK_G; i += LT_THREADS) {
-            const int kr = i / RANK_G, c = i - kr * RANK_G;
-            const int p = stored_row(kr);
-            bsm4[p * RANK_G + ((c + p / RP) % RANK_G)] = __ldg(cb4 + i);
+        for (int grp = 0; grp < n_groups; ++grp) {
+            const float4* cb4 = reinterpret_cast<const float4*>(cache_b + ((size_t)blockIdx.x * n_groups + grp) * k * RANK);
+            float4* dst = bsm4 + grp * (gstride / 4);
+            for (int i = tid; i < k * RANK_G; i += LT_THREADS) {
+                const int kr = i / RANK_G, c = i - kr * RANK_G;
+                const int p = stored_row(kr);
+                dst[p * RANK_G + ((c + p / RP) % RANK_G)] = __ldg(cb4 + i);
+            }
         }
     } else {
         const int rpt = (k + LT_THREADS - 1) / LT_THREADS;   // rows per thread
@@ -1056,68 +1077,71 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                 }
             }
         }
-        // t of the rows, two q per packed fp32 instruction: acc2[(row * RANK + q) / 2]
-        f32x2 acc2[N / 2];
+        for (int grp = 0; grp < n_groups; ++grp) {
+            const ulonglong2* bg = bsm2 + grp * (gstride / 4);
+            // t of the rows, two q per packed fp32 instruction: acc2[(row * RANK + q) / 2]
+            f32x2 acc2[N / 2];
 #pragma unroll
-        for (int i = 0; i < N / 2; ++i) acc2[i] = 0ull;
+            for (int i = 0; i < N / 2; ++i) acc2[i] = 0ull;
 #pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-            if (li + 32 * j < n4) {
+            for (int j = 0; j < NJ; ++j) {
+                if (li + 32 * j < n4) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int p = j * 128 + e * 32 + li;
-                    f32x2 xe[RPR];
-#pragma unroll
-                    for (int r = 0; r < RPR; ++r) {
-                        const float xv = e == 0 ? v[r][j].x : e == 1 ? v[r][j].y : e == 2 ? v[r][j].z : v[r][j].w;
-                        xe[r] = pk2(xv, xv);
-                    }
-#pragma unroll
-                    for (int c = 0; c < RANK_G; ++c) {
-                        const ulonglong2 b = bsm2[p * RANK_G + ((c + p / RP) % RANK_G)];
+                    for (int e = 0; e < 4; ++e) {
+                        const int p = j * 128 + e * 32 + li;
+                        f32x2 xe[RPR];
 #pragma unroll
                         for (int r = 0; r < RPR; ++r) {
-                            acc2[r * (RANK / 2) + 2 * c] = fma2(xe[r], b.x, acc2[r * (RANK / 2) + 2 * c]);
-                            acc2[r * (RANK / 2) + 2 * c + 1] = fma2(xe[r], b.y, acc2[r * (RANK / 2) + 2 * c + 1]);
+                            const float xv = e == 0 ? v[r][j].x : e == 1 ? v[r][j].y : e == 2 ? v[r][j].z : v[r][j].w;
+                            xe[r] = pk2(xv, xv);
+                        }
+#pragma unroll
+                        for (int c = 0; c < RANK_G; ++c) {
+                            const ulonglong2 b = bg[p * RANK_G + ((c + p / RP) % RANK_G)];
+#pragma unroll
+                            for (int r = 0; r < RPR; ++r) {
+                                acc2[r * (RANK / 2) + 2 * c] = fma2(xe[r], b.x, acc2[r * (RANK / 2) + 2 * c]);
+                                acc2[r * (RANK / 2) + 2 * c + 1] = fma2(xe[r], b.y, acc2[r * (RANK / 2) + 2 * c + 1]);
+                            }
                         }
                     }
                 }
             }
-        }
-        float acc[N];
+            float acc[N];
 #pragma unroll
-        for (int i = 0; i < N / 2; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
-        // halving exchange over the W lanes of a row group: in the step with distance off a lane keeps
-        // the half of its values that its bit `off` selects, summed with its partner's.  After the
-        // steps a lane holds N / W finished sums from index li * N / W on (N >= W), or groups of W / N
-        // lanes hold the sum of index li / group (N < W: the last steps add single values).
-        constexpr int STEPS = HALF ? 4 : 5;
+            for (int i = 0; i < N / 2; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+            // halving exchange over the W lanes of a row group: in the step with distance off a lane keeps
+            // the half of its values that its bit `off` selects, summed with its partner's.  After the
+            // steps a lane holds N / W finished sums from index li * N / W on (N >= W), or groups of W / N
+            // lanes hold the sum of index li / group (N < W: the last steps add single values).
+            constexpr int STEPS = HALF ? 4 : 5;
 #pragma unroll
-        for (int s = 0; s < STEPS; ++s) {
-            const int n = N >> s, off = (W / 2) >> s;
-            if (n > 1) {
-                const bool up = (lane & off) != 0;
+            for (int s = 0; s < STEPS; ++s) {
+                const int n = N >> s, off = (W / 2) >> s;
+                if (n > 1) {
+                    const bool up = (lane & off) != 0;
 #pragma unroll
-                for (int i = 0; i < n / 2; ++i) {
-                    const float send = up ? acc[i] : acc[i + n / 2];
-                    const float keep = up ? acc[i + n / 2] : acc[i];
-                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                    for (int i = 0; i < n / 2; ++i) {
+                        const float send = up ? acc[i] : acc[i + n / 2];
+                        const float keep = up ? acc[i + n / 2] : acc[i];
+                        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                    }
+                } else {
+                    acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
                 }
-            } else {
-                acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
             }
-        }
-        constexpr int NF = N >= W ? N / W : 1;      // finished sums per lane
-        constexpr int GROUP = N >= W ? 1 : W / N;   // lanes holding the same sum
-        if (li % GROUP == 0) {
-            const int idx = (li / GROUP) * NF;      // NF consecutive q of one row
-            const int row = idx / RANK, q = idx - row * RANK;
-            const int lr = lr0 + row * RSTEP + hs;
-            if (lr < total_rows) {
-                float* dst = t + (size_t)row_s[lr] * RANK + q;
-                if (NF == 1) dst[0] = acc[0];
-                else if (NF == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
-                else *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[NF > 2 ? 2 : 0], acc[NF > 3 ? 3 : 0]);
+            constexpr int NF = N >= W ? N / W : 1;      // finished sums per lane
+            constexpr int GROUP = N >= W ? 1 : W / N;   // lanes holding the same sum
+            if (li % GROUP == 0) {
+                const int idx = (li / GROUP) * NF;      // NF consecutive q of one row
+                const int row = idx / RANK, q = idx - row * RANK;
+                const int lr = lr0 + row * RSTEP + hs;
+                if (lr < total_rows) {
+                    float* dst = t + ((size_t)row_s[lr] * n_groups + grp) * RANK + q;
+                    if (NF == 1) dst[0] = acc[0];
+                    else if (NF == 2) *reinterpret_cast<float2*>(dst) = make_float2(acc[0], acc[1]);
+                    else *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[NF > 2 ? 2 : 0], acc[NF > 3 ? 3 : 0]);
+                }
             }
         }
     }
@@ -1154,11 +1178,16 @@ struct TcScratch {
     int* lo_flag;  // set by the x split when a lo half is non-zero
     size_t bytes;
 };
+// shared memory of one group's B in lowrank_t_rows_kernel: whole 128-row groups of the padded rank
+static size_t rows_prepass_b_bytes(int k, int rank) {
+    return (size_t)((k + 127) / 128) * 128 * (rank < 4 ? 4 : rank) * sizeof(float);
+}
+
 TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     auto up = [](size_t v) { return (v + 63) / 64 * 64; };
     size_t rows = (size_t)g.t_steps * g.n_pop * g.bm;
     size_t nw = up((size_t)g.a * g.k), nx = up(rows * g.k);   // fp16 elements
-    size_t nt = g.perturb ? up(rows * (size_t)((g.rank + 3) / 4 * 4)) : 0;   // floats: t has the padded rank
+    size_t nt = g.perturb ? up(rows * (size_t)((g.rank + 3) / 4 * 4) * (size_t)(g.n_groups > 1 ? g.n_groups : 1)) : 0;   // floats: t has the padded rank, once per group
     TcScratch s;
     s.xhi = reinterpret_cast<__half*>(base);
     s.xlo = s.xhi + nx;
@@ -1257,6 +1286,15 @@ bool tensor_path_supports(const hses_linear_args& g) {
         bool pair_rows = (g.bm % 32 == 0) || (g.bm == 16 && g.first_thread % 2 == 0 && g.n_pop % 2 == 0);
         if (!pair_rows) return false;
     }
+    if (g.n_groups > 1) {
+        // stacked parameters: cached factors, the rows prepass with all groups' B in shared memory, and
+        // groups that are whole ring items
+        if (!g.perturb || g.cache == nullptr || g.factor_order != 0 || g.a % g.n_groups != 0) return false;
+        if (!(g.rank <= 4 || g.rank == 8 || g.rank == 16) || g.k > 1024) return false;
+        const int gc = g.a / g.n_groups;
+        if (gc % 32 != 0 && !(gc % 16 == 0 && g.rank >= 8)) return false;
+        if ((size_t)g.n_groups * rows_prepass_b_bytes(g.k, g.rank) > 65536) return false;
+    }
     return true;
 }
 
@@ -1306,6 +1344,8 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
     ta.out_scale = g.out_scale;
     ta.out_scale_ptr = g.out_scale_ptr;
     ta.t = sc.t;
+    ta.t_stride = ta.rank * (g.n_groups > 1 ? g.n_groups : 1);
+    ta.group_cols = g.n_groups > 1 ? g.a / g.n_groups : 0;
     ta.row_scale = x_ready ? nullptr : sc.rs;   // NULL: no row was scaled
     ta.col_scale = sc.cs;
     ta.out = g.out;
@@ -1336,7 +1376,8 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         dim3 lt_grid((unsigned)pairs, (unsigned)((2 * (int64_t)g.bm * g.t_steps + LT_ROWS - 1) / LT_ROWS));
         if ((g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024) {
             // whole B of a pair in shared memory, x rows read once (see lowrank_t_rows_kernel)
-            const size_t b_bytes = (size_t)((g.k + 127) / 128) * 128 * (g.rank < 4 ? 4 : g.rank) * sizeof(float);   // at most 64 KB
+            const int groups = g.n_groups > 1 ? g.n_groups : 1;
+            const size_t b_bytes = groups * rows_prepass_b_bytes(g.k, g.rank);   // at most 64 KB
 #define HSES_LTR(RG, NJ, RPR, HALF)                                                                               \
     do {                                                                                                      \
         HSES_CUDA(cudaFuncSetAttribute(lowrank_t_rows_kernel<RG, NJ, RPR, HALF>,                              \
@@ -1344,7 +1385,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         lowrank_t_rows_kernel<RG, NJ, RPR, HALF><<<HALF ? lt_grid2 : lt_grid, LT_THREADS, b_bytes, st>>>(     \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
             g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
-            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0);                                              \
+            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, groups);                                      \
     } while (0)
             // rows in flight per warp: as many as the registers hold (16 pieces, 64 sums); rows of up to 64
             // values take half a warp each, and a CTA twice the rows

@@ -190,12 +190,14 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
                      algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None, precision: int = 0,
                      tmm: bool = False, x_half: Optional[torch.Tensor] = None,
-                     out_half: Optional[torch.Tensor] = None, reuse_x_split: bool = False):
+                     out_half: Optional[torch.Tensor] = None, reuse_x_split: bool = False, n_groups: int = 1):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
     the charged potentials.  With `cache` the factors are read from it instead of
     being regenerated (same bits).  x_half: x once more as dense fp16 (rows, k) when it is exact
     there; out_half: a dense fp16 (rows, a) tensor that receives the spikes as well (lif only).
+    n_groups: `param` stacks that many parameters of equal shape along its rows, each with its own noise;
+    `cache` must then be a GroupedFactorCache over them and `key` its key (tensor-core path only).
     reuse_x_split: the previous call on this device and stream had the same x and the same shapes
     (another projection of the same activation): its operand split of x is taken as it stands."""
     _check(x, "x")
@@ -227,6 +229,7 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.precision = precision
     g.factor_order = int(tmm)   # do_Tmm: param is the reference's (in, out) matrix transposed
     g.x_split_valid = int(reuse_x_split)
+    g.n_groups = int(n_groups)
     if x_half is not None:
         if x_half.dtype != torch.float16 or not x_half.is_contiguous() or x_half.numel() != rows * k:
             raise ValueError("x_half must be a contiguous fp16 tensor of rows*k values")
@@ -325,6 +328,32 @@ class FactorCache:
     def B(self) -> torch.Tensor:
         """(n_pairs, b, rank) raw normals."""
         return self.data[self.n_pairs * self.a * self.rank:].view(self.n_pairs, self.b, self.rank)
+
+
+class GroupedFactorCache:
+    """The factors of several parameters of one shape (a_g, b) in the layout a grouped perturbed_linear
+    call reads: A (n_pairs, G * a_g, rank) with the parameters' A blocks stacked like the parameters, then
+    B (n_pairs, G, b, rank).  Assembled on the device from one FactorCache per parameter; the descriptor
+    carries the first parameter's key, which the call passes as `key`."""
+
+    def __init__(self, caches: Sequence["FactorCache"]):
+        c0 = caches[0]
+        for c in caches:
+            if (c.n_pairs, c.rank, c.a, c.b) != (c0.n_pairs, c0.rank, c0.a, c0.b) or \
+                    (c.desc.true_epoch, c.desc.first_pair) != (c0.desc.true_epoch, c0.desc.first_pair):
+                raise ValueError("grouped caches must share shape, pairs and epoch bucket")
+        G = len(caches)
+        na = c0.n_pairs * G * c0.a * c0.rank
+        self.data = torch.empty(na + c0.n_pairs * G * c0.b * c0.rank, dtype=torch.float32, device=c0.data.device)
+        torch.cat([c.A for c in caches], dim=1, out=self.data[:na].view(c0.n_pairs, G * c0.a, c0.rank))
+        torch.stack([c.B for c in caches], dim=1, out=self.data[na:].view(c0.n_pairs, G, c0.b, c0.rank))
+        self.desc = _lib.FactorCacheDesc()
+        self.desc.data = self.data.data_ptr()
+        self.desc.key = c0.desc.key
+        self.desc.true_epoch, self.desc.first_pair = c0.desc.true_epoch, c0.desc.first_pair
+        self.desc.n_pairs, self.desc.rank = c0.n_pairs, c0.rank
+        self.desc.a, self.desc.b = G * c0.a, G * c0.b
+        self.n_groups, self.key = G, int(c0.desc.key)
 
 
 def es_update(key: int, epoch: int, noise_reuse: int, rank: int, a: int, b: int, sigma: float,

@@ -113,6 +113,31 @@ class SpikingLM:
         return ops.perturbed_linear(x, w, n_pop=n, bm=rows_per_member, perturb=noise is not None, out=out,
                                     reuse_x_split=same_x, **kw)
 
+    def nn_heads(self, idxs, x: torch.Tensor, ws, n: int, rows_per_member: int, noise: Optional[LmNoise],
+                 out: torch.Tensor, same_x: bool) -> bool:
+        """The per-head projections `ws` (parameters idxs) of one x in ONE call: the heads' matrices stacked
+        along the rows, every head with its own noise, columns [h*hd, (h+1)*hd) of `out` for head h.  x is
+        read once instead of once per head.  Returns False when the shapes do not allow it (the caller then
+        projects head by head)."""
+        hd = ws[0].shape[0]
+        if noise is None:
+            ops.perturbed_linear(x, torch.cat(list(ws), 0), n_pop=n, bm=rows_per_member, perturb=False, out=out,
+                                 reuse_x_split=same_x)
+            return True
+        groupable = (noise.first_thread % 2 == 0 and n % 2 == 0 and noise.rank in (1, 2, 3, 4, 8, 16) and
+                     (hd % 32 == 0 or (hd % 16 == 0 and noise.rank >= 8)))
+        if not groupable:
+            return False
+        k = ws[0].shape[1]
+        caches = [ops.FactorCache(noise.base_keys[i], noise.epoch, noise.noise_reuse, noise.rank, hd, k, n // 2,
+                                  first_pair=noise.first_thread // 2, device=self.device) for i in idxs]
+        grouped = ops.GroupedFactorCache(caches)
+        ops.perturbed_linear(x, torch.cat(list(ws), 0), n_pop=n, bm=rows_per_member, sigma=noise.sigma,
+                             rank=noise.rank, key=grouped.key, epoch=noise.epoch, first_thread=noise.first_thread,
+                             noise_reuse=noise.noise_reuse, cache=grouped, n_groups=len(ws), out=out,
+                             reuse_x_split=same_x)
+        return True
+
     def forward_population(self, ids: torch.Tensor, noise: Optional[LmNoise] = None) -> torch.Tensor:
         """ids (n, seqs, L) int32: member j evaluates its own `seqs` sequences -> logits
         (n*seqs*L, vocab), before the output gain."""
@@ -135,13 +160,19 @@ class SpikingLM:
         beta = torch.full((n * seqs,), self.beta, device=self.device)
         for b, blk in enumerate(self.blocks):
             base = self.block_base(b)
-            for h in range(H):
-                # head h's currents land in columns [h*hd, (h+1)*hd): the layout the attention kernel reads
-                sl = slice(h * hd, (h + 1) * hd)
-                # twelve projections of one x: only the first one splits it into tensor-core operands
-                self.nn(base + 3 * h, x, blk["q"][h], n, rpm, noise, out=qc[:, sl], same_x=h > 0)
-                self.nn(base + 3 * h + 1, x, blk["k"][h], n, rpm, noise, out=kc[:, sl], same_x=True)
-                self.nn(base + 3 * h + 2, x, blk["v"][h], n, rpm, noise, out=vc[:, sl], same_x=True)
+            # head h's currents land in columns [h*hd, (h+1)*hd): the layout the attention kernel reads.
+            # The heads of Q, of K and of V go out as three grouped calls (x read three times instead of
+            # twelve, split into tensor-core operands once); head by head where the shapes do not allow it
+            grouped = True
+            for j, (name, buf) in enumerate((("q", qc), ("k", kc), ("v", vc))):
+                grouped = grouped and self.nn_heads([base + 3 * h + j for h in range(H)], x, blk[name], n, rpm, noise,
+                                                    buf, same_x=j > 0)
+            if not grouped:
+                for h in range(H):
+                    sl = slice(h * hd, (h + 1) * hd)
+                    self.nn(base + 3 * h, x, blk["q"][h], n, rpm, noise, out=qc[:, sl], same_x=h > 0)
+                    self.nn(base + 3 * h + 1, x, blk["k"][h], n, rpm, noise, out=kc[:, sl], same_x=True)
+                    self.nn(base + 3 * h + 2, x, blk["v"][h], n, rpm, noise, out=vc[:, sl], same_x=True)
             # LIF over T steps on the constant currents, firing rates in place
             for buf in (qc, kc, vc):
                 ops.lif_rate(buf, self.T, self.tau_m, self.v_th, out=buf)

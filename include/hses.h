@@ -241,6 +241,15 @@ typedef struct {
                            split of x is still there and is not computed again (several projections of
                            one activation, e.g. the per-head Q/K/V of a block).  Ignored by the other
                            paths */
+    int32_t n_groups;   /* 0 or 1: one parameter.  G >= 2: `param` holds G parameters of a / G rows each,
+                           stacked along the rows, every one with its own noise (the per-head projections of
+                           one activation in one call: x is read once instead of G times).  The factors come
+                           from `cache`, which the caller assembles in the grouped layout: A (n_pairs, a, rank)
+                           with the groups' A blocks stacked like the parameter, then B (n_pairs, G, k, rank);
+                           its descriptor has b = G * k and the key the call passes as `key`.  Tensor-core
+                           path only (k <= 1024, rank 1..4, 8 or 16, a / G a multiple of 32, or of 16 with
+                           rank >= 8, the G blocks of B within 64 KB); other shapes return
+                           HSES_ERR_UNSUPPORTED.  Column c of the result belongs to group c / (a / G) */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

@@ -250,3 +250,40 @@ def test_operand_split_of_x_is_reused_across_projections(hs, perturb, cached):
     got = call(w2, 7, reuse_x_split=True)
     assert core.get_context(0).device_status() == 0
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("G,hd,k,rank,bm", [(4, 16, 64, 8, 32), (3, 32, 96, 4, 64), (2, 64, 256, 16, 16),
+                                            (2, 32, 640, 1, 32)])
+def test_grouped_projections_equal_the_separate_calls(hs, G, hd, k, rank, bm):
+    """n_groups: G parameters stacked along the rows, each with its own noise, in one call that reads x
+    once.  Every column must come out as in the call that projects its parameter alone."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(G * 100 + hd)
+    n_pop, first = 8, 2
+    x = dev(g.standard_normal((n_pop, bm, k)).astype(np.float32))
+    ws = [dev((g.standard_normal((hd, k)) / np.sqrt(k)).astype(np.float32)) for _ in range(G)]
+    keys = [KEY + 977 * j for j in range(G)]
+    kw = dict(n_pop=n_pop, bm=bm, sigma=0.3, rank=rank, epoch=2, first_thread=first, noise_reuse=1)
+    caches = [ops.FactorCache(keys[j], 2, 1, rank, hd, k, n_pop // 2, first_pair=first // 2) for j in range(G)]
+    alone = [ops.perturbed_linear(x, ws[j], key=keys[j], cache=caches[j], algo=ops.ALGO_TENSOR, **kw) for j in range(G)]
+    status_ok()
+    grouped = ops.GroupedFactorCache(caches)
+    got = ops.perturbed_linear(x, torch.cat(ws, 0), key=grouped.key, cache=grouped, n_groups=G, **kw)
+    status_ok()
+    want = torch.cat(alone, 1)
+    scale = max(float(want.abs().max()), 1.0)
+    assert float((got - want).abs().max()) <= 1e-6 * scale
+    # a second projection of the same x keeps the operand split of the first
+    again = ops.perturbed_linear(x, torch.cat(ws, 0), key=grouped.key, cache=grouped, n_groups=G, reuse_x_split=True, **kw)
+    assert torch.equal(again, got)
+
+
+def test_grouped_projections_refuse_what_they_do_not_cover(hs):
+    from hyperscalees_b200 import ops, _lib
+    x = torch.randn(8, 32, 64, device="cuda")
+    ws = [torch.randn(16, 64, device="cuda") for _ in range(2)]
+    caches = [ops.FactorCache(KEY + j, 0, 0, 4, 16, 64, 4) for j in range(2)]
+    grouped = ops.GroupedFactorCache(caches)
+    with pytest.raises(_lib.HsesError):   # 16-column groups need rank >= 8 (a ring item of rank 4 spans 32 columns)
+        ops.perturbed_linear(x, torch.cat(ws, 0), n_pop=8, bm=32, sigma=0.1, rank=4, key=grouped.key, cache=grouped,
+                             n_groups=2)
