@@ -287,3 +287,28 @@ def test_grouped_projections_refuse_what_they_do_not_cover(hs):
     with pytest.raises(_lib.HsesError):   # 16-column groups need rank >= 8 (a ring item of rank 4 spans 32 columns)
         ops.perturbed_linear(x, torch.cat(ws, 0), n_pop=8, bm=32, sigma=0.1, rank=4, key=grouped.key, cache=grouped,
                              n_groups=2)
+
+
+@pytest.mark.parametrize("extra", [dict(t_steps=2), dict(lif=True, tau_m=2.0, v_th=0.05), dict(precision=1)])
+def test_grouped_projections_with_steps_lif_and_one_pass(hs, extra):
+    """The grouped call in the other modes of the tensor-core path: several time steps, the fused LIF
+    step, bf16 operands in one pass."""
+    from hyperscalees_b200 import ops
+    G, hd, k, rank, bm, n_pop, first = 2, 32, 128, 8, 32, 8, 0
+    t_steps = extra.get("t_steps", 1)
+    g = np.random.default_rng(5)
+    x = dev(g.standard_normal((t_steps, n_pop, bm, k)).astype(np.float32))
+    ws = [dev((g.standard_normal((hd, k)) / np.sqrt(k)).astype(np.float32)) for _ in range(G)]
+    keys = [KEY + 31 * j for j in range(G)]
+    kw = dict(n_pop=n_pop, bm=bm, sigma=0.3, rank=rank, epoch=0, first_thread=first, noise_reuse=0, **extra)
+    caches = [ops.FactorCache(keys[j], 0, 0, rank, hd, k, n_pop // 2) for j in range(G)]
+    alone = [ops.perturbed_linear(x, ws[j], key=keys[j], cache=caches[j], algo=ops.ALGO_TENSOR, **kw) for j in range(G)]
+    grouped = ops.GroupedFactorCache(caches)
+    got = ops.perturbed_linear(x, torch.cat(ws, 0), key=grouped.key, cache=grouped, n_groups=G, **kw)
+    status_ok()
+    want = torch.cat(alone, 1)
+    if extra.get("lif"):
+        assert float((got != want).float().mean()) <= 1e-4   # 0/1 spikes; a current on the threshold may flip
+        assert 0.02 < float(want.mean()) < 0.98
+    else:
+        assert float((got - want).abs().max()) <= 1e-6 * max(float(want.abs().max()), 1.0)
