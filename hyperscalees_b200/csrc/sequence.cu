@@ -724,6 +724,97 @@ __global__ void token_shift_mix_kernel(const float* __restrict__ x, int T, int c
     }
 }
 
+// ---- element-wise work of TimeMixing::forward around the recurrence (llm.rs:396-440 before it,
+// 462-472 after it), one warp per (row, head): the head's S values sit S / 32 per lane, the two sums
+// over a head (the norm of kk, the bonus) are warp reductions.
+//   before: w    = -softplus(-(w0 + w_lin)) - 0.5                                   (llm.rs:400)
+//           v    = v_raw                         in layer 0 (v_lin == NULL), else
+//                  v_raw + (v_first - v_raw) * sigmoid(v0 + v_lin)                  (llm.rs:405-415)
+//           a    = sigmoid(a0 + a_lin)
+//           kk   = (k_raw * k_k) / max(|k_raw * k_k|_2 over the head, 1e-12)        (llm.rs:426-433)
+//           k    = k_raw * (k_a * (a - 1) + 1)                                      (llm.rs:437)
+//           outputs w, v, k, -kk and kk * a: the recurrence's decay, value, key, a and b inputs
+//   after:  y = (y_norm + (sum over the head of r * k * r_k) * v) * gate            (llm.rs:462-472)
+__device__ __forceinline__ float sigmoid_f(float z) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))); }
+
+template <int PER>
+__global__ void __launch_bounds__(256)
+rwkv_mix_prepare_kernel(int64_t heads_total, int H, const float* __restrict__ w_lin, const float* __restrict__ v_raw,
+                        const float* __restrict__ v_lin, const float* __restrict__ v_first,
+                        const float* __restrict__ a_lin, const float* __restrict__ k_raw,
+                        const float* __restrict__ w0, const float* __restrict__ v0, const float* __restrict__ a0,
+                        const float* __restrict__ k_k, const float* __restrict__ k_a, float* __restrict__ w_out,
+                        float* __restrict__ v_out, float* __restrict__ k_out, float* __restrict__ nkk_out,
+                        float* __restrict__ kka_out) {
+    constexpr int S = 32 * PER;
+    const int64_t wi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wi >= heads_total) return;   // warp-uniform
+    const int lane = threadIdx.x & 31;
+    const int h = (int)(wi % H);
+    const int64_t base = wi * S;     // (row * H + h) * S: rows are (H, S) dense
+    const int cbase = h * S;
+    float kk[PER], a[PER];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int s = lane + 32 * i;
+        const int64_t e = base + s;
+        const int c = cbase + s;
+        const float iw = __fadd_rn(__ldg(w0 + c), __ldg(w_lin + e));
+        // softplus(-iw) = max(-iw, 0) + log1p(exp(-|iw|))
+        const float sp = __fadd_rn(fmaxf(-iw, 0.0f), log1pf(expf(-fabsf(iw))));
+        w_out[e] = __fsub_rn(-sp, 0.5f);
+        const float vr = __ldg(v_raw + e);
+        float v = vr;
+        if (v_lin != nullptr) {
+            const float sg = sigmoid_f(__fadd_rn(__ldg(v0 + c), __ldg(v_lin + e)));
+            v = __fadd_rn(vr, __fmul_rn(__fsub_rn(__ldg(v_first + e), vr), sg));
+        }
+        v_out[e] = v;
+        a[i] = sigmoid_f(__fadd_rn(__ldg(a0 + c), __ldg(a_lin + e)));
+        const float kr = __ldg(k_raw + e);
+        kk[i] = __fmul_rn(kr, __ldg(k_k + c));
+        ss = fmaf(kk[i], kk[i], ss);
+        k_out[e] = __fmul_rn(kr, __fadd_rn(__fmul_rn(__ldg(k_a + c), __fsub_rn(a[i], 1.0f)), 1.0f));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float nrm = fmaxf(sqrtf(ss), 1e-12f);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int64_t e = base + lane + 32 * i;
+        const float q = __fdiv_rn(kk[i], nrm);
+        nkk_out[e] = -q;
+        kka_out[e] = __fmul_rn(q, a[i]);
+    }
+}
+
+template <int PER>
+__global__ void __launch_bounds__(256)
+rwkv_mix_finish_kernel(int64_t heads_total, int H, const float* __restrict__ y_norm, const float* __restrict__ r,
+                       const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ gate,
+                       const float* __restrict__ r_k, float* __restrict__ out) {
+    constexpr int S = 32 * PER;
+    const int64_t wi = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wi >= heads_total) return;
+    const int lane = threadIdx.x & 31;
+    const int h = (int)(wi % H);
+    const int64_t base = wi * S;
+    float bonus = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int s = lane + 32 * i;
+        bonus = __fadd_rn(bonus, __fmul_rn(__fmul_rn(__ldg(r + base + s), __ldg(k + base + s)), __ldg(r_k + h * S + s)));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) bonus += __shfl_xor_sync(0xffffffffu, bonus, off);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int64_t e = base + lane + 32 * i;
+        out[e] = __fmul_rn(__fadd_rn(__ldg(y_norm + e), __fmul_rn(bonus, __ldg(v + e))), __ldg(gate + e));
+    }
+}
+
 struct ReluSquareOp {
     __device__ __forceinline__ float operator()(float x) const {
         float v = x > 0.0f ? x : 0.0f;
@@ -912,6 +1003,48 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x, int3
     else
         token_shift_mix_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state,
                                                                                              new_starts, coef, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_rwkv_mix_prepare(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_t H, int32_t S, const float* w_lin,
+                          const float* v_raw, const float* v_lin, const float* v_first, const float* a_lin,
+                          const float* k_raw, const float* w0, const float* v0, const float* a0, const float* k_k,
+                          const float* k_a, float* w_out, float* v_out, float* k_out, float* nkk_out, float* kka_out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(rows >= 0 && H >= 1 && (S == 32 || S == 64 || S == 128), "head size must be 32, 64 or 128");
+    if (rows == 0) return HSES_OK;
+    HSES_REQUIRE(w_lin && v_raw && a_lin && k_raw && w0 && a0 && k_k && k_a && w_out && v_out && k_out && nkk_out && kka_out,
+                 "NULL pointer");
+    HSES_REQUIRE(v_lin == nullptr || (v0 != nullptr && v_first != nullptr), "v_lin needs v0 and v_first");
+    const int64_t heads_total = rows * H;
+    const unsigned grid = (unsigned)((heads_total + 7) / 8);
+    HSES_KERNEL(ctx, as_stream(stream), "rwkv_mix_prepare");
+#define HSES_MIXP(PER)                                                                                           \
+    rwkv_mix_prepare_kernel<PER><<<grid, 256, 0, as_stream(stream)>>>(heads_total, H, w_lin, v_raw, v_lin, v_first, \
+                                                                      a_lin, k_raw, w0, v0, a0, k_k, k_a, w_out,  \
+                                                                      v_out, k_out, nkk_out, kka_out)
+    if (S == 32) HSES_MIXP(1);
+    else if (S == 64) HSES_MIXP(2);
+    else HSES_MIXP(4);
+#undef HSES_MIXP
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_rwkv_mix_finish(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_t H, int32_t S, const float* y_norm,
+                         const float* r, const float* k, const float* v, const float* gate, const float* r_k,
+                         float* out) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(rows >= 0 && H >= 1 && (S == 32 || S == 64 || S == 128), "head size must be 32, 64 or 128");
+    if (rows == 0) return HSES_OK;
+    HSES_REQUIRE(y_norm && r && k && v && gate && r_k && out, "NULL pointer");
+    const int64_t heads_total = rows * H;
+    const unsigned grid = (unsigned)((heads_total + 7) / 8);
+    HSES_KERNEL(ctx, as_stream(stream), "rwkv_mix_finish");
+    if (S == 32) rwkv_mix_finish_kernel<1><<<grid, 256, 0, as_stream(stream)>>>(heads_total, H, y_norm, r, k, v, gate, r_k, out);
+    else if (S == 64) rwkv_mix_finish_kernel<2><<<grid, 256, 0, as_stream(stream)>>>(heads_total, H, y_norm, r, k, v, gate, r_k, out);
+    else rwkv_mix_finish_kernel<4><<<grid, 256, 0, as_stream(stream)>>>(heads_total, H, y_norm, r, k, v, gate, r_k, out);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -638,6 +638,39 @@ def token_shift_mix(x: torch.Tensor, state: torch.Tensor, coef: torch.Tensor,
     return out
 
 
+def rwkv_mix_prepare(w_lin, v_raw, v_lin, v_first, a_lin, k_raw, w0, v0, a0, k_k, k_a, H: int):
+    """TimeMixing's element-wise work before the recurrence (llm.rs:396-440) in one pass: all (rows, C) dense.
+    v_lin / v_first / v0 None: layer 0 (v = v_raw).  Returns (w, v, k, -kk, kk*a)."""
+    rows, Cw = w_lin.shape
+    S = Cw // H
+    big = [w_lin, v_raw, a_lin, k_raw] + ([v_lin, v_first] if v_lin is not None else [])
+    for t in big:
+        _check(t, "input", ndim=2)
+        if tuple(t.shape) != (rows, Cw) or not t.is_contiguous():
+            raise ValueError("inputs must be contiguous (rows, H*S)")
+    outs = [torch.empty_like(w_lin) for _ in range(5)]
+    ctx = get_context(w_lin.device)
+    c = lambda t: None if t is None else _ptr(t.contiguous())
+    _lib.check(_lib.load().hses_rwkv_mix_prepare(ctx.handle, current_stream(), rows, H, S, _ptr(w_lin), _ptr(v_raw),
+                                                 c(v_lin), c(v_first), _ptr(a_lin), _ptr(k_raw), c(w0), c(v0), c(a0),
+                                                 c(k_k), c(k_a), *[_ptr(o) for o in outs]))
+    return tuple(outs)
+
+
+def rwkv_mix_finish(y_norm, r, k, v, gate, r_k, H: int) -> torch.Tensor:
+    """(y_norm + (sum over each head of r * k * r_k) * v) * gate, llm.rs:462-472; (rows, C) dense."""
+    rows, Cw = y_norm.shape
+    for t in (y_norm, r, k, v, gate):
+        _check(t, "input", ndim=2)
+        if tuple(t.shape) != (rows, Cw) or not t.is_contiguous():
+            raise ValueError("inputs must be contiguous (rows, H*S)")
+    out = torch.empty_like(y_norm)
+    ctx = get_context(y_norm.device)
+    _lib.check(_lib.load().hses_rwkv_mix_finish(ctx.handle, current_stream(), rows, H, Cw // H, _ptr(y_norm), _ptr(r),
+                                                _ptr(k), _ptr(v), _ptr(gate), _ptr(r_k.contiguous()), _ptr(out)))
+    return out
+
+
 def relu_square(x: torch.Tensor) -> torch.Tensor:
     _check(x, "x")
     x = x.contiguous()

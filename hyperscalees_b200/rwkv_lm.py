@@ -132,32 +132,29 @@ class RwkvLM:
             mix = lambda name: ops.token_shift_mix(xa_, zero_c, w[name], ns)
             xr, xw, xk, xv, xa, xg = (mix(nm) for nm in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"))
             r = mm("receptance", xr)
-            inner_w = w["w0"].unsqueeze(0) + mm("w2", torch.tanh(mm("w1", xw)))
-            wdec = -torch.nn.functional.softplus(-inner_w) - 0.5
+            # the products of the block; everything element-wise between them and the recurrence, and after
+            # it, runs in two kernels (ops.rwkv_mix_prepare / rwkv_mix_finish) instead of some thirty passes
+            w_lin = mm("w2", torch.tanh(mm("w1", xw)))
             k = mm("key", xk)
             v = mm("value", xv)
+            v_lin = None if l == 0 else mm("v2", torch.tanh(mm("v1", xv)))
+            a_lin = mm("a2", torch.tanh(mm("a1", xa)))
+            gate = mm("g2", torch.sigmoid(mm("g1", xg)))
+            wdec, v, k, nkk, kka = ops.rwkv_mix_prepare(w_lin, v, v_lin, v_first, a_lin, k, w["w0"],
+                                                        None if l == 0 else w["v0"], w["a0"], w["k_k"], w["k_a"], H)
             if l == 0:
                 v_first = v
-            else:
-                sig = torch.sigmoid(w["v0"].unsqueeze(0) + mm("v2", torch.tanh(mm("v1", xv))))
-                v = v + (v_first - v) * sig
-            a = torch.sigmoid(w["a0"].unsqueeze(0) + mm("a2", torch.tanh(mm("a1", xa))))
-            gate = mm("g2", torch.sigmoid(mm("g1", xg)))
-            kk3 = (k * w["k_k"].unsqueeze(0)).view(rows, H, S)
-            kk = (kk3 / kk3.pow(2).sum(dim=2, keepdim=True).sqrt().clamp_min(1e-12)).reshape(rows, C)
-            k = k * (w["k_a"].unsqueeze(0) * (a - 1.0) + 1.0)
-            shp = lambda t_: t_.reshape(n, T, H, S).contiguous()
+            shp = lambda t_: t_.view(n, T, H, S)
             state = torch.zeros(n, H, S, S, device=self.device)
-            out = ops.wkv7(shp(r), shp(wdec), shp(k), shp(v), shp(-kk), shp(kk * a), state)
+            out = ops.wkv7(shp(r), shp(wdec), shp(k), shp(v), shp(nkk), shp(kka), state)
             y = ops.group_norm(out.reshape(rows, C), H, *w["ln_x"], eps=64e-5)
-            bonus = (r.view(rows, H, S) * k.view(rows, H, S) * w["r_k"].view(1, H, S)).sum(dim=2, keepdim=True)
-            y = (y + (bonus * v.view(rows, H, S)).reshape(rows, C)) * gate
-            x = x + mm("output", y)
-            del xr, xw, xk, xv, xa, xg, r, k, v, a, gate, kk, kk3, out, y, bonus, inner_w, wdec, state
+            y = ops.rwkv_mix_finish(y, r, k, v, gate, w["r_k"].reshape(-1), H)
+            ops.add_inplace(x, mm("output", y))
+            del xr, xw, xk, xv, xa, xg, r, k, v, gate, out, y, wdec, state, nkk, kka, w_lin, v_lin, a_lin
             # ---- ChannelMixing, llm.rs:192-213 ----
             xc = ops.layer_norm(x, *w["ln2"])
             kf = ops.relu_square(mm("ffn_key", ops.token_shift_mix(xc, zero_c, w["ffn_x_k"], ns)))
-            x = x + mm("ffn_value", kf)
+            ops.add_inplace(x, mm("ffn_value", kf))
             del xc, kf
         return ops.layer_norm(x, *self.ln_out)
 

@@ -537,6 +537,22 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x /*dev
                          int32_t c, const float* state /*device (c)*/,
                          const uint8_t* new_starts /*device or NULL*/, const float* coef /*device (c)*/,
                          float* out /*device (T,c)*/);
+/* The element-wise work of TimeMixing::forward around the recurrence (llm.rs:396-440 and 462-472), all
+ * tensors (rows, H*S) dense, parameters H*S values:
+ *   prepare: w = -softplus(-(w0 + w_lin)) - 0.5;  v = v_raw in layer 0 (v_lin NULL), else
+ *            v_raw + (v_first - v_raw) * sigmoid(v0 + v_lin);  a = sigmoid(a0 + a_lin);
+ *            kk = k_raw * k_k normalised per head (L2, floor 1e-12);  k = k_raw * (k_a * (a - 1) + 1);
+ *            outputs w, v, k, -kk, kk * a (the decay, value, key, a and b inputs of hses_wkv7);
+ *   finish:  out = (y_norm + (sum over the head of r * k * r_k) * v) * gate.
+ * Head size 32, 64 or 128. */
+int hses_rwkv_mix_prepare(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_t H, int32_t S, const float* w_lin,
+                          const float* v_raw, const float* v_lin /*or NULL*/, const float* v_first /*or NULL*/,
+                          const float* a_lin, const float* k_raw, const float* w0, const float* v0 /*or NULL*/,
+                          const float* a0, const float* k_k, const float* k_a, float* w_out, float* v_out,
+                          float* k_out, float* nkk_out, float* kka_out);
+int hses_rwkv_mix_finish(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_t H, int32_t S, const float* y_norm,
+                         const float* r, const float* k, const float* v, const float* gate, const float* r_k,
+                         float* out);
 int hses_relu_square(hses_ctx* ctx, hses_stream stream, const float* x /*device*/, int64_t n,
                      float* out /*device*/);
 /* rate_encode, hyperscalees-models/src/snn_transformer.rs:109-116: sigmoid(gain * p / (1 + |p|)). */

@@ -70,3 +70,34 @@ def test_population_fitness_matches_the_cpu_composition(hs, oracle, perturb):
         assert np.abs(logits[0] - logits[1]).max() > 0     # antithetic partners differ
     else:
         assert np.abs(fit - fit[0]).max() > 0              # different sequences, different fitness
+
+
+@pytest.mark.parametrize("H,S,layer0", [(3, 64, True), (3, 64, False), (4, 32, False), (2, 128, False)])
+def test_time_mixing_elementwise_kernels_against_the_composition(hs, H, S, layer0):
+    """hses_rwkv_mix_prepare / hses_rwkv_mix_finish (llm.rs:396-440, 462-472) against the same formulas written
+    out with array operations in fp64."""
+    import torch
+    from hyperscalees_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(H * S)
+    rows, C = 37, H * S
+    rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=g)
+    w_lin, v_raw, v_lin, v_first, a_lin, k_raw = (rnd(rows, C) * 2 for _ in range(6))
+    w0, v0, a0, k_k, k_a = (rnd(C) for _ in range(5))
+    got = ops.rwkv_mix_prepare(w_lin, v_raw, None if layer0 else v_lin, None if layer0 else v_first, a_lin, k_raw,
+                               w0, None if layer0 else v0, a0, k_k, k_a, H)
+    d = lambda t: t.double()
+    sig = torch.sigmoid
+    w_want = -torch.nn.functional.softplus(-(d(w0) + d(w_lin))) - 0.5
+    v_want = d(v_raw) if layer0 else d(v_raw) + (d(v_first) - d(v_raw)) * sig(d(v0) + d(v_lin))
+    a = sig(d(a0) + d(a_lin))
+    kk3 = (d(k_raw) * d(k_k)).view(rows, H, S)
+    kk = (kk3 / kk3.pow(2).sum(dim=2, keepdim=True).sqrt().clamp_min(1e-12)).reshape(rows, C)
+    k_want = d(k_raw) * (d(k_a) * (a - 1.0) + 1.0)
+    for name, gt, wt in zip(("w", "v", "k", "-kk", "kk*a"), got, (w_want, v_want, k_want, -kk, kk * a)):
+        err = float((d(gt) - wt).abs().max())
+        assert err <= 2e-6 * max(1.0, float(wt.abs().max())), (name, err)
+    y_norm, r, gate, r_k = rnd(rows, C), rnd(rows, C), rnd(rows, C), rnd(H, S)
+    out = ops.rwkv_mix_finish(y_norm, r, got[2], got[1], gate, r_k.reshape(-1), H)
+    bonus = (d(r).view(rows, H, S) * d(got[2]).view(rows, H, S) * d(r_k).view(1, H, S)).sum(dim=2, keepdim=True)
+    want = (d(y_norm) + (bonus * d(got[1]).view(rows, H, S)).reshape(rows, C)) * d(gate)
+    assert float((d(out) - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
