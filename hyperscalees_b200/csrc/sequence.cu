@@ -737,6 +737,26 @@ __global__ void token_shift_mix_kernel(const float* __restrict__ x, int T, int c
 //   after:  y = (y_norm + (sum over the head of r * k * r_k) * v) * gate            (llm.rs:462-472)
 __device__ __forceinline__ float sigmoid_f(float z) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z))); }
 
+// PER consecutive floats of a lane as one 4-, 8- or 16-byte access
+template <int PER>
+__device__ __forceinline__ void ld_per(const float* __restrict__ p, float (&v)[PER]) {
+    if (PER == 4) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(p));
+        v[0] = q.x; v[1] = q.y; v[2 % PER] = q.z; v[3 % PER] = q.w;
+    } else if (PER == 2) {
+        const float2 q = __ldg(reinterpret_cast<const float2*>(p));
+        v[0] = q.x; v[1 % PER] = q.y;
+    } else {
+        v[0] = __ldg(p);
+    }
+}
+template <int PER>
+__device__ __forceinline__ void st_per(float* __restrict__ p, const float (&v)[PER]) {
+    if (PER == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2 % PER], v[3 % PER]);
+    else if (PER == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1 % PER]);
+    else p[0] = v[0];
+}
+
 template <int PER>
 __global__ void __launch_bounds__(256)
 rwkv_mix_prepare_kernel(int64_t heads_total, int H, const float* __restrict__ w_lin, const float* __restrict__ v_raw,
@@ -751,42 +771,46 @@ rwkv_mix_prepare_kernel(int64_t heads_total, int H, const float* __restrict__ w_
     if (wi >= heads_total) return;   // warp-uniform
     const int lane = threadIdx.x & 31;
     const int h = (int)(wi % H);
-    const int64_t base = wi * S;     // (row * H + h) * S: rows are (H, S) dense
-    const int cbase = h * S;
-    float kk[PER], a[PER];
+    const int64_t e0 = wi * S + lane * PER;   // (row * H + h) * S + the lane's PER consecutive values
+    const int c0 = h * S + lane * PER;
+    float wl[PER], vr[PER], al[PER], kr[PER], p_w0[PER], p_a0[PER], p_kk[PER], p_ka[PER];
+    ld_per<PER>(w_lin + e0, wl); ld_per<PER>(v_raw + e0, vr); ld_per<PER>(a_lin + e0, al); ld_per<PER>(k_raw + e0, kr);
+    ld_per<PER>(w0 + c0, p_w0); ld_per<PER>(a0 + c0, p_a0); ld_per<PER>(k_k + c0, p_kk); ld_per<PER>(k_a + c0, p_ka);
+    float vl[PER], vf[PER], p_v0[PER];
+    if (v_lin != nullptr) {
+        ld_per<PER>(v_lin + e0, vl); ld_per<PER>(v_first + e0, vf); ld_per<PER>(v0 + c0, p_v0);
+    }
+    float kk[PER], a[PER], wo[PER], vo[PER], ko[PER];
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-        const int s = lane + 32 * i;
-        const int64_t e = base + s;
-        const int c = cbase + s;
-        const float iw = __fadd_rn(__ldg(w0 + c), __ldg(w_lin + e));
+        const float iw = __fadd_rn(p_w0[i], wl[i]);
         // softplus(-iw) = max(-iw, 0) + log1p(exp(-|iw|))
         const float sp = __fadd_rn(fmaxf(-iw, 0.0f), log1pf(expf(-fabsf(iw))));
-        w_out[e] = __fsub_rn(-sp, 0.5f);
-        const float vr = __ldg(v_raw + e);
-        float v = vr;
+        wo[i] = __fsub_rn(-sp, 0.5f);
+        float v = vr[i];
         if (v_lin != nullptr) {
-            const float sg = sigmoid_f(__fadd_rn(__ldg(v0 + c), __ldg(v_lin + e)));
-            v = __fadd_rn(vr, __fmul_rn(__fsub_rn(__ldg(v_first + e), vr), sg));
+            const float sg = sigmoid_f(__fadd_rn(p_v0[i], vl[i]));
+            v = __fadd_rn(vr[i], __fmul_rn(__fsub_rn(vf[i], vr[i]), sg));
         }
-        v_out[e] = v;
-        a[i] = sigmoid_f(__fadd_rn(__ldg(a0 + c), __ldg(a_lin + e)));
-        const float kr = __ldg(k_raw + e);
-        kk[i] = __fmul_rn(kr, __ldg(k_k + c));
+        vo[i] = v;
+        a[i] = sigmoid_f(__fadd_rn(p_a0[i], al[i]));
+        kk[i] = __fmul_rn(kr[i], p_kk[i]);
         ss = fmaf(kk[i], kk[i], ss);
-        k_out[e] = __fmul_rn(kr, __fadd_rn(__fmul_rn(__ldg(k_a + c), __fsub_rn(a[i], 1.0f)), 1.0f));
+        ko[i] = __fmul_rn(kr[i], __fadd_rn(__fmul_rn(p_ka[i], __fsub_rn(a[i], 1.0f)), 1.0f));
     }
+    st_per<PER>(w_out + e0, wo); st_per<PER>(v_out + e0, vo); st_per<PER>(k_out + e0, ko);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
     const float nrm = fmaxf(sqrtf(ss), 1e-12f);
+    float nk[PER], ka[PER];
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-        const int64_t e = base + lane + 32 * i;
         const float q = __fdiv_rn(kk[i], nrm);
-        nkk_out[e] = -q;
-        kka_out[e] = __fmul_rn(q, a[i]);
+        nk[i] = -q;
+        ka[i] = __fmul_rn(q, a[i]);
     }
+    st_per<PER>(nkk_out + e0, nk); st_per<PER>(kka_out + e0, ka);
 }
 
 template <int PER>
@@ -799,20 +823,18 @@ rwkv_mix_finish_kernel(int64_t heads_total, int H, const float* __restrict__ y_n
     if (wi >= heads_total) return;
     const int lane = threadIdx.x & 31;
     const int h = (int)(wi % H);
-    const int64_t base = wi * S;
+    const int64_t e0 = wi * S + lane * PER;
+    float rv[PER], kv[PER], rk[PER], yn[PER], vv[PER], gv[PER], o[PER];
+    ld_per<PER>(r + e0, rv); ld_per<PER>(k + e0, kv); ld_per<PER>(r_k + h * S + lane * PER, rk);
+    ld_per<PER>(y_norm + e0, yn); ld_per<PER>(v + e0, vv); ld_per<PER>(gate + e0, gv);
     float bonus = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int s = lane + 32 * i;
-        bonus = __fadd_rn(bonus, __fmul_rn(__fmul_rn(__ldg(r + base + s), __ldg(k + base + s)), __ldg(r_k + h * S + s)));
-    }
+    for (int i = 0; i < PER; ++i) bonus = __fadd_rn(bonus, __fmul_rn(__fmul_rn(rv[i], kv[i]), rk[i]));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) bonus += __shfl_xor_sync(0xffffffffu, bonus, off);
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int64_t e = base + lane + 32 * i;
-        out[e] = __fmul_rn(__fadd_rn(__ldg(y_norm + e), __fmul_rn(bonus, __ldg(v + e))), __ldg(gate + e));
-    }
+    for (int i = 0; i < PER; ++i) o[i] = __fmul_rn(__fadd_rn(yn[i], __fmul_rn(bonus, vv[i])), gv[i]);
+    st_per<PER>(out + e0, o);
 }
 
 struct ReluSquareOp {
