@@ -32,7 +32,7 @@ EXPORTS = [
     "hses_population_grads_elems", "hses_population_grads", "hses_population_apply",
     "hses_convert_fitnesses_bs", "hses_vector_mul",
     "hses_prng_normal_half", "hses_einsum_pair_workspace_bytes", "hses_einsum_pair", "hses_layer_norm", "hses_group_norm", "hses_token_shift_mix", "hses_relu_square", "hses_rate_encode",
-    "hses_rwkv_mix_prepare", "hses_rwkv_mix_finish",
+    "hses_rwkv_mix_prepare", "hses_rwkv_mix_finish", "hses_token_shift_mix_multi",
     "hses_embedding", "hses_lif_rate", "hses_swish", "hses_add_inplace", "hses_token_fitness",
     "hses_comm_unique_id", "hses_comm_init", "hses_comm_rank", "hses_comm_world", "hses_comm_async_error",
     "hses_comm_destroy", "hses_comm_abort", "hses_allgather_fitness", "hses_allreduce_grads",
@@ -179,6 +179,7 @@ def load():
     L.hses_relu_square.argtypes = [vp, vp, vp, i64, vp]
     L.hses_rwkv_mix_prepare.argtypes = [vp, vp, i64, i32, i32] + [vp] * 16
     L.hses_rwkv_mix_finish.argtypes = [vp, vp, i64, i32, i32] + [vp] * 7
+    L.hses_token_shift_mix_multi.argtypes = [vp, vp, vp, i32, i32, vp, vp, i32, C.POINTER(vp), C.POINTER(vp)]
     L.hses_rate_encode.argtypes = [vp, vp, vp, i64, f32, vp]
     L.hses_population_grads_elems.restype = sz
     L.hses_population_grads_elems.argtypes = [pm]

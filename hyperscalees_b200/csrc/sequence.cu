@@ -724,6 +724,33 @@ __global__ void token_shift_mix_kernel(const float* __restrict__ x, int T, int c
     }
 }
 
+// The same for several coefficient vectors at once (TimeMixing mixes one x six ways, llm.rs:381-392):
+// x and its previous row are read once, out[m] = x + (prev - x) * coef[m].  16-byte accesses.
+constexpr int kMaxMixes = 8;
+struct MixPtrs {
+    const float* coef[kMaxMixes];
+    float* out[kMaxMixes];
+};
+__global__ void token_shift_mix_multi_kernel(const float* __restrict__ x, int T, int c, const float* __restrict__ state,
+                                             const uint8_t* __restrict__ new_starts, int n_mix, MixPtrs p) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= (int64_t)T * c) return;
+    const int t = (int)(i / c), j = (int)(i - (int64_t)t * c);
+    float4 prev = t == 0 ? *reinterpret_cast<const float4*>(state + j) : *reinterpret_cast<const float4*>(x + i - c);
+    if (new_starts && new_starts[t]) prev = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 xv = *reinterpret_cast<const float4*>(x + i);
+    const float4 d = make_float4(__fsub_rn(prev.x, xv.x), __fsub_rn(prev.y, xv.y), __fsub_rn(prev.z, xv.z),
+                                 __fsub_rn(prev.w, xv.w));
+#pragma unroll
+    for (int m = 0; m < kMaxMixes; ++m) {
+        if (m >= n_mix) break;
+        const float4 cf = __ldg(reinterpret_cast<const float4*>(p.coef[m] + j));
+        __stcs(reinterpret_cast<float4*>(p.out[m] + i),
+               make_float4(__fadd_rn(xv.x, __fmul_rn(d.x, cf.x)), __fadd_rn(xv.y, __fmul_rn(d.y, cf.y)),
+                           __fadd_rn(xv.z, __fmul_rn(d.z, cf.z)), __fadd_rn(xv.w, __fmul_rn(d.w, cf.w))));
+    }
+}
+
 // ---- element-wise work of TimeMixing::forward around the recurrence (llm.rs:396-440 before it,
 // 462-472 after it), one warp per (row, head): the head's S values sit S / 32 per lane, the two sums
 // over a head (the norm of kk, the bonus) are warp reductions.
@@ -1025,6 +1052,36 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x, int3
     else
         token_shift_mix_kernel<1><<<(unsigned)((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state,
                                                                                              new_starts, coef, out);
+    HSES_LAUNCH_CHECK();
+    return HSES_OK;
+}
+
+int hses_token_shift_mix_multi(hses_ctx* ctx, hses_stream stream, const float* x, int32_t T, int32_t c,
+                               const float* state, const uint8_t* new_starts, int32_t n_mix, const float* const* coefs,
+                               float* const* outs) {
+    HSES_REQUIRE(ctx != nullptr, "ctx is NULL");
+    HSES_REQUIRE(T >= 0 && c >= 1 && n_mix >= 1 && n_mix <= kMaxMixes, "bad shape (at most 8 mixes)");
+    if (T == 0) return HSES_OK;
+    HSES_REQUIRE(x != nullptr && state != nullptr && coefs != nullptr && outs != nullptr, "NULL pointer");
+    MixPtrs p{};
+    uintptr_t bits = (uintptr_t)x | (uintptr_t)state;
+    for (int m = 0; m < n_mix; ++m) {
+        HSES_REQUIRE(coefs[m] != nullptr && outs[m] != nullptr && outs[m] != x, "NULL or aliasing pointer");
+        p.coef[m] = coefs[m];
+        p.out[m] = outs[m];
+        bits |= (uintptr_t)coefs[m] | (uintptr_t)outs[m];
+    }
+    if (c % 4 != 0 || (bits & 15u) != 0) {   // no 16-byte accesses: one mix at a time
+        for (int m = 0; m < n_mix; ++m) {
+            int rc = hses_token_shift_mix(ctx, stream, x, T, c, state, new_starts, coefs[m], outs[m]);
+            if (rc != HSES_OK) return rc;
+        }
+        return HSES_OK;
+    }
+    const int64_t n = (int64_t)T * c;
+    HSES_KERNEL(ctx, as_stream(stream), "token_shift_mix");
+    token_shift_mix_multi_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, as_stream(stream)>>>(x, T, c, state, new_starts,
+                                                                                                 n_mix, p);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }

@@ -638,6 +638,27 @@ def token_shift_mix(x: torch.Tensor, state: torch.Tensor, coef: torch.Tensor,
     return out
 
 
+def token_shift_mix_multi(x: torch.Tensor, state: torch.Tensor, coefs: Sequence[torch.Tensor],
+                          new_starts: Optional[torch.Tensor] = None):
+    """token_shift_mix for several coefficient vectors of one x (the six mixes of TimeMixing, llm.rs:381-392):
+    x and its previous rows are read once.  Returns one tensor per coefficient vector."""
+    _check(x, "x", ndim=2)
+    x = x.contiguous()
+    T, c = x.shape
+    n = len(coefs)
+    outs = [torch.empty_like(x) for _ in range(n)]
+    cfs = [cf.contiguous().view(-1) for cf in coefs]
+    ns = None
+    if new_starts is not None:
+        ns = new_starts.to(device=x.device, dtype=torch.uint8).contiguous()
+    ctx = get_context(x.device)
+    cp = (C.c_void_p * n)(*[t.data_ptr() for t in cfs])
+    op = (C.c_void_p * n)(*[t.data_ptr() for t in outs])
+    _lib.check(_lib.load().hses_token_shift_mix_multi(ctx.handle, current_stream(), _ptr(x), T, c,
+                                                      _ptr(state.contiguous().view(-1)), _ptr(ns), n, cp, op))
+    return outs
+
+
 def rwkv_mix_prepare(w_lin, v_raw, v_lin, v_first, a_lin, k_raw, w0, v0, a0, k_k, k_a, H: int):
     """TimeMixing's element-wise work before the recurrence (llm.rs:396-440) in one pass: all (rows, C) dense.
     v_lin / v_first / v0 None: layer 0 (v = v_raw).  Returns (w, v, k, -kk, kk*a)."""

@@ -129,8 +129,8 @@ class RwkvLM:
             mm = lambda name, z: self._mm(l, name, z.contiguous(), n, T, noise)
             # ---- TimeMixing, llm.rs:348-479 ----
             xa_ = ops.layer_norm(x, *w["ln1"])
-            mix = lambda name: ops.token_shift_mix(xa_, zero_c, w[name], ns)
-            xr, xw, xk, xv, xa, xg = (mix(nm) for nm in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g"))
+            xr, xw, xk, xv, xa, xg = ops.token_shift_mix_multi(
+                xa_, zero_c, [w[nm] for nm in ("x_r", "x_w", "x_k", "x_v", "x_a", "x_g")], ns)
             r = mm("receptance", xr)
             # the products of the block; everything element-wise between them and the recurrence, and after
             # it, runs in two kernels (ops.rwkv_mix_prepare / rwkv_mix_finish) instead of some thirty passes

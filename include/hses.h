@@ -537,6 +537,11 @@ int hses_token_shift_mix(hses_ctx* ctx, hses_stream stream, const float* x /*dev
                          int32_t c, const float* state /*device (c)*/,
                          const uint8_t* new_starts /*device or NULL*/, const float* coef /*device (c)*/,
                          float* out /*device (T,c)*/);
+/* hses_token_shift_mix for n_mix (at most 8) coefficient vectors of one x: coefs and outs are host arrays of
+ * device pointers; x and its previous rows are read once (the six mixes of TimeMixing, llm.rs:381-392). */
+int hses_token_shift_mix_multi(hses_ctx* ctx, hses_stream stream, const float* x /*device (T,c)*/, int32_t T, int32_t c,
+                               const float* state, const uint8_t* new_starts /*or NULL*/, int32_t n_mix,
+                               const float* const* coefs /*host*/, float* const* outs /*host*/);
 /* The element-wise work of TimeMixing::forward around the recurrence (llm.rs:396-440 and 462-472), all
  * tensors (rows, H*S) dense, parameters H*S values:
  *   prepare: w = -softplus(-(w0 + w_lin)) - 0.5;  v = v_raw in layer 0 (v_lin NULL), else

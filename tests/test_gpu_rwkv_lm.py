@@ -101,3 +101,19 @@ def test_time_mixing_elementwise_kernels_against_the_composition(hs, H, S, layer
     bonus = (d(r).view(rows, H, S) * d(got[2]).view(rows, H, S) * d(r_k).view(1, H, S)).sum(dim=2, keepdim=True)
     want = (d(y_norm) + (bonus * d(got[1]).view(rows, H, S)).reshape(rows, C)) * d(gate)
     assert float((d(out) - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max()))
+
+
+def test_token_shift_mix_of_several_coefficient_vectors(hs):
+    """hses_token_shift_mix_multi gives what one hses_token_shift_mix call per coefficient vector gives."""
+    import torch
+    from hyperscalees_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(11)
+    T, c = 50, 96
+    x = torch.randn(T, c, device="cuda", generator=g)
+    state = torch.randn(c, device="cuda", generator=g)
+    ns = torch.zeros(T, dtype=torch.uint8, device="cuda")
+    ns[[0, 17, 33]] = 1
+    coefs = [torch.rand(c, device="cuda", generator=g) for _ in range(6)]
+    got = ops.token_shift_mix_multi(x, state, coefs, ns)
+    for cf, o in zip(coefs, got):
+        assert torch.equal(o, ops.token_shift_mix(x, state, cf, ns))
