@@ -139,10 +139,12 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8], bool wide,
 
 // ----------------------------------------------------------------------- kernel
 // R1: the factor rank is 1 (run as RG = 1): the epilogue leaves out the three zero columns of t and A.
+// GRP: several stacked parameters (n_groups): an instance of its own, so that the reload of t per column
+// group costs the other calls neither registers nor instructions (it made the rank-16 epilogue spill).
 // RG = rank / 4 (0: clean product, no noise).  The rank is a template parameter so that the
 // per-column dot product unrolls exactly and the epilogue loop stays small enough for the
 // instruction cache.
-template <int BN, int RG, bool R1 = false>
+template <int BN, int RG, bool R1 = false, bool GRP = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_constant__ CUtensorMap tm_xlo,
                  const __grid_constant__ CUtensorMap tm_whi, const __grid_constant__ CUtensorMap tm_wlo,
@@ -316,7 +318,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                 odd_member = (thread_id & 1) != 0;  // sign -1: A of the pair is negated for this row
 #pragma unroll
                 for (int q = 0; q < RANK; q += 4) {
-                    float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * g.t_stride + q);
+                    float4 tv = *reinterpret_cast<const float4*>(g.t + (size_t)R * (GRP ? g.t_stride : RANK) + q);
                     tq2[q] = pk2(tv.x, tv.x); tq2[q + 1] = pk2(tv.y, tv.y);
                     tq2[q + 2] = pk2(tv.z, tv.z); tq2[q + 3] = pk2(tv.w, tv.w);
                 }
@@ -330,7 +332,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tm_xhi, const __grid_consta
                     if (n0 >= g.a) continue;                     // ragged last chunk: no such columns, no such item
                     const float* my_a = nullptr;
                     int slot = 0;
-                    if (RG > 0 && g.group_cols) {
+                    if (GRP && RG > 0) {
                         // stacked parameters: these columns' group has its own t (its own B)
                         const float* tg = g.t + (size_t)R * g.t_stride + (n0 / g.group_cols) * RANK;
 #pragma unroll
@@ -1201,14 +1203,14 @@ TcScratch tc_scratch(const hses_linear_args& g, void* base) {
     return s;
 }
 
-template <int BN, int RG, bool R1 = false>
+template <int BN, int RG, bool R1 = false, bool GRP = false>
 int launch_tc_rg(hses_ctx* ctx, cudaStream_t st, const CUtensorMap& tm_x, const CUtensorMap& tm_xlo,
                  const CUtensorMap& tm_whi, const CUtensorMap& tm_wlo, const TcArgs& ta, int grid,
                  int smem_bytes) {
-    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN, RG, R1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    HSES_CUDA(cudaFuncSetAttribute(linear_tc_kernel<BN, RG, R1, GRP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    smem_bytes));
     HSES_KERNEL(ctx, st, "linear_tc");
-    linear_tc_kernel<BN, RG, R1><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_xlo, tm_whi, tm_wlo, ta);
+    linear_tc_kernel<BN, RG, R1, GRP><<<grid, NTHREADS, smem_bytes, st>>>(tm_x, tm_xlo, tm_whi, tm_wlo, ta);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
@@ -1252,6 +1254,15 @@ int launch_tc(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g, const T
     HSES_REQUIRE(smem_bytes <= S::LIMIT, "shared memory budget exceeded");
     int m_tiles = (int)(rows / BM_TILE);
     int grid = m_tiles < ctx->sm_count ? m_tiles : ctx->sm_count;
+    if (ta.group_cols) {   // stacked parameters: ranks 1..4, 8, 16 (tensor_path_supports)
+        switch (ta.rank / 4) {
+            case 1:
+                if (ta.rank_true == 1) return launch_tc_rg<BN, 1, true, true>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+                return launch_tc_rg<BN, 1, false, true>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+            case 2: return launch_tc_rg<BN, 2, false, true>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+            case 4: return launch_tc_rg<BN, 4, false, true>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
+        }
+    }
     switch (ta.rank / 4) {
         case 0: return launch_tc_rg<BN, 0>(ctx, st, tm_x, tm_xlo, tm_whi, tm_wlo, ta, grid, smem_bytes);
         case 1:
