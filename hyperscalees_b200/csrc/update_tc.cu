@@ -284,13 +284,24 @@ update_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
-// grad (+)= scale * 2^(e_w - kExpA - kExpB) * sum over splits, splits added in index order
-__global__ void update_tc_reduce_kernel(const float* __restrict__ partial, int splits, size_t len, float scale,
-                                        const int* __restrict__ e_w, int accumulate, float* __restrict__ grad) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= len) return;
+// grad (+)= scale * 2^(e_w - kExpA - kExpB) * sum over splits.  A block of eight warps takes 32 elements:
+// warp w adds the splits w, w + 8, .. in index order, then the eight sums are added in warp order (a fixed
+// order, the same on every rank).  One thread per element walking all splits had so few threads on the
+// 128 x 128 layers (64 blocks) that the launch took 12 us, most of it the latency of 148 loads in a row.
+__global__ void __launch_bounds__(256)
+update_tc_reduce_kernel(const float* __restrict__ partial, int splits, size_t len, float scale,
+                        const int* __restrict__ e_w, int accumulate, float* __restrict__ grad) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t i = (size_t)blockIdx.x * 32 + lane;
     float s = 0.0f;
-    for (int k = 0; k < splits; ++k) s = __fadd_rn(s, partial[(size_t)k * len + i]);
+    if (i < len)
+        for (int k = warp; k < splits; k += 8) s = __fadd_rn(s, partial[(size_t)k * len + i]);
+    part[warp][lane] = s;
+    __syncthreads();
+    if (warp != 0 || i >= len) return;
+#pragma unroll
+    for (int w = 1; w < 8; ++w) s = __fadd_rn(s, part[w][lane]);
     s = __fmul_rn(ldexpf(s, *e_w - kExpA - kExpB), scale);
     grad[i] = accumulate ? __fadd_rn(grad[i], s) : s;
 }
@@ -428,7 +439,7 @@ int run_update_tc(hses_ctx* ctx, cudaStream_t st, const hses_update_args& u, flo
     }
     size_t len = (size_t)a * b;
     HSES_KERNEL(ctx, st, "update_reduce");
-    update_tc_reduce_kernel<<<(unsigned)((len + 255) / 256), 256, 0, st>>>(partial, p.splits, len, scale, e_w,
+    update_tc_reduce_kernel<<<(unsigned)((len + 31) / 32), 256, 0, st>>>(partial, p.splits, len, scale, e_w,
                                                                           u.mode == HSES_UPDATE_RAW_ACC, u.grad);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
