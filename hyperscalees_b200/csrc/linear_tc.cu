@@ -1152,6 +1152,274 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
         atomicOr(lo_flag, 1);
 }
 
+// The rows prepass for rows longer than a warp's registers (1024 < k, B of the pair within 64 KB: rank <= 4
+// up to k = 4096, rank 8 up to 2048): the row passes through the registers 1024 values at a time, once for
+// the maximum (not in the one-pass mode) and once for the split and t, whose sums stay in registers over
+// the pieces.  The block kernel walks such a row four values per lane and trip.
+template <int RANK_G>
+__global__ void __launch_bounds__(LT_THREADS, 2)
+lowrank_t_long_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
+                      uint64_t key, int32_t true_epoch, int32_t first_thread, const float* __restrict__ x,
+                      int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
+                      __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
+                      const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true,
+                      int row_b0, int skip_split, int n_groups) {
+    constexpr int RANK = RANK_G * 4;
+    constexpr int NJ = 8, RPR = 2;   // 1024 values of two rows in flight per warp
+    constexpr bool HALF = false;
+    constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
+    constexpr int ROWS_CTA = HALF ? 2 * LT_ROWS : LT_ROWS;   // x rows per CTA
+    extern __shared__ __align__(16) float bsm[];   // ceil(k / 128) * 128 rows of RANK floats
+    __shared__ double2 log_tab_s[64];
+    __shared__ uint32_t delta_s[512];
+    __shared__ int64_t row_s[ROWS_CTA];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (!cache_b) {
+        for (int i = tid; i < 64; i += LT_THREADS) log_tab_s[i] = cal.log_tab[i];
+        for (int i = tid; i < 256; i += LT_THREADS) {
+            delta_s[i] = cal.log_delta[i];
+            delta_s[256 + i] = cal.cos_delta[i];
+        }
+        cal.log_tab = log_tab_s;
+        cal.log_delta = delta_s;
+        cal.cos_delta = delta_s + 256;
+    }
+    const int32_t first_pair = first_thread / 2;
+    const int32_t pair = first_pair + blockIdx.x;
+    int64_t m_lo = (int64_t)pair * 2 - first_thread, m_hi = m_lo + 2;
+    if (m_lo < 0) m_lo = 0;
+    if (m_hi > n_pop) m_hi = n_pop;
+    const int rows_per_step = (int)(m_hi - m_lo) * bm;
+    const int row0 = blockIdx.y * ROWS_CTA;
+    const int total_rows = min(ROWS_CTA, rows_per_step * t_steps - row0);
+    if (total_rows <= 0) return;
+    if (tid < ROWS_CTA) {
+        int lr = row0 + (tid < total_rows ? tid : total_rows - 1);  // rows past the end repeat the last one
+        int step = lr / rows_per_step, rr = lr - step * rows_per_step;
+        row_s[tid] = ((int64_t)step * n_pop + m_lo) * bm + rr;
+    }
+    __syncthreads();
+
+    // ---- phase 1: B of this pair ----
+    float4* bsm4 = reinterpret_cast<float4*>(bsm);
+    auto stored_row = [](int kr) { return (kr & ~127) + (kr & 3) * 32 + ((kr & 127) >> 2); };
+    // several stacked parameters (n_groups > 1, cached factors only): group g's B block sits at
+    // bsm + g * gstride floats and came from cache block (pair, g)
+    const int gstride = ((k + 127) & ~127) * RANK;
+    if (cache_b && rank_true < 4) {
+        for (int grp = 0; grp < n_groups; ++grp) {
+            const float* cb1 = cache_b + ((size_t)blockIdx.x * n_groups + grp) * k * rank_true;
+            float4* dst = bsm4 + grp * (gstride / 4);
+            for (int kr = tid; kr < k; kr += LT_THREADS) {
+                const float* row = cb1 + (size_t)kr * rank_true;
+                dst[stored_row(kr)] = make_float4(__ldg(row), rank_true > 1 ? __ldg(row + 1) : 0.0f,
+                                                  rank_true > 2 ? __ldg(row + 2) : 0.0f, 0.0f);
+            }
+        }
+    } else if (cache_b) {
+        for (int grp = 0; grp < n_groups; ++grp) {
+            const float4* cb4 = reinterpret_cast<const float4*>(cache_b + ((size_t)blockIdx.x * n_groups + grp) * k * RANK);
+            float4* dst = bsm4 + grp * (gstride / 4);
+            for (int i = tid; i < k * RANK_G; i += LT_THREADS) {
+                const int kr = i / RANK_G, c = i - kr * RANK_G;
+                const int p = stored_row(kr);
+                dst[p * RANK_G + ((c + p / RP) % RANK_G)] = __ldg(cb4 + i);
+            }
+        }
+    } else {
+        const int rpt = (k + LT_THREADS - 1) / LT_THREADS;   // rows per thread
+        const int kr0 = tid * rpt, kr1 = min(kr0 + rpt, k);
+        if (kr0 < k) {
+            uint64_t sb = noise_seed(key, true_epoch, pair) | 1ull;
+            sb = jump_by(pow2, sb, 2ull * (uint64_t)rank_true * (uint64_t)(row_b0 + kr0));   // row_b0: first input-side row
+#pragma unroll 1
+            for (int kr = kr0; kr < kr1; ++kr) {
+                const int p = stored_row(kr);
+                if (rank_true < 4) {
+                    float z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    z[0] = next_normal(sb, cal);
+                    if (rank_true > 1) z[1] = next_normal(sb, cal);
+                    if (rank_true > 2) z[2] = next_normal(sb, cal);
+                    bsm4[p] = make_float4(z[0], z[1], z[2], z[3]);
+                    continue;
+                }
+#pragma unroll 1
+                for (int c = 0; c < RANK_G; ++c) {
+                    float z[4];
+                    next_normals4(sb, cal, z);
+                    bsm4[p * RANK_G + ((c + p / RP) % RANK_G)] = make_float4(z[0], z[1], z[2], z[3]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- phase 2: split and t of RPR rows per warp and round, NJ 16-byte pieces per lane and row ----
+    const int n4 = k >> 2;
+    uint32_t lo_nz = 0;  // any non-zero lo half written by this thread
+    // HALF: rows of up to 64 values take half a warp each, so a warp works on 2 * RPR rows at a time
+    constexpr int W = HALF ? 16 : 32;              // lanes per row
+    constexpr int RSTEP = HALF ? 2 : 1;            // rows between a lane's consecutive rows
+    const int li = lane & (W - 1), hs = HALF ? lane >> 4 : 0;
+    auto finish_row = [&](int64_t R, float m, float& sc, bool valid) {
+#pragma unroll
+        for (int off = W / 2; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        int ex = (int)((__float_as_uint(m) >> 23) & 0xffu) - 127;
+        int e = 13 - ex;
+        if (ex <= -127 || ex >= 128) e = 0;
+        if (e > 100) e = 100;
+        if (e < -100) e = -100;
+        if (bf16) e = 0;   // one-pass mode: no scale
+        sc = __uint_as_float((uint32_t)(127 + e) << 23);
+        if (li == 0 && valid) inv_scale[R] = __uint_as_float((uint32_t)(127 - e) << 23);
+    };
+    auto split4 = [&](float4 v, float sc, uint2& h2, uint2& l2) {
+        if (bf16) {   // hi = bf16(v), the lo half is neither written nor read
+            const __nv_bfloat162 b01 = __floats2bfloat162_rn(v.x, v.y), b23 = __floats2bfloat162_rn(v.z, v.w);
+            h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&b01), *reinterpret_cast<const uint32_t*>(&b23));
+            l2 = make_uint2(0u, 0u);
+            return;
+        }
+        const float x0 = v.x * sc, x1 = v.y * sc, x2 = v.z * sc, x3 = v.w * sc;
+        const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+        const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+        const __half2 l01 = __floats2half2_rn(x0 - b01.x, x1 - b01.y), l23 = __floats2half2_rn(x2 - b23.x, x3 - b23.y);
+        h2 = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        l2 = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        lo_nz |= (l2.x | l2.y) & 0x7fff7fffu;  // a lo half of -0 is still zero
+    };
+    constexpr int NW = LT_THREADS / 32;
+    constexpr int RW = RPR * RSTEP;   // rows of a warp and round
+    constexpr int N = RPR * RANK;     // sums of a lane group and round: N[row * RANK + q]
+    const ulonglong2* bsm2 = reinterpret_cast<const ulonglong2*>(bsm);
+    for (int lr0 = warp * RW; lr0 < total_rows; lr0 += NW * RW) {
+        const float4* src[RPR];
+        bool valid[RPR];
+        int64_t R[RPR];
+#pragma unroll
+        for (int r = 0; r < RPR; ++r) {
+            valid[r] = lr0 + r < total_rows;   // warp-uniform
+            R[r] = row_s[valid[r] ? lr0 + r : lr0];
+            src[r] = reinterpret_cast<const float4*>(x + (size_t)R[r] * x_stride);
+        }
+        // the scale of a row needs the maximum of the whole row: one pass of its own (the one-pass mode
+        // scales nothing and skips it; the second read of the row then comes from L2)
+        float sc[RPR];
+#pragma unroll
+        for (int r = 0; r < RPR; ++r) sc[r] = 1.0f;
+        if (!skip_split) {
+            float m[RPR];
+#pragma unroll
+            for (int r = 0; r < RPR; ++r) m[r] = 0.0f;
+            if (!bf16) {
+                for (int c4 = 0; c4 < n4; c4 += 32 * NJ) {
+                    float4 v[RPR][NJ];
+#pragma unroll
+                    for (int r = 0; r < RPR; ++r)
+#pragma unroll
+                        for (int j = 0; j < NJ; ++j) {
+                            const int i = c4 + lane + 32 * j;
+                            v[r][j] = (valid[r] && i < n4) ? __ldg(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                    for (int r = 0; r < RPR; ++r)
+#pragma unroll
+                        for (int j = 0; j < NJ; ++j)
+                            m[r] = fmaxf(m[r], fmaxf(fmaxf(fabsf(v[r][j].x), fabsf(v[r][j].y)),
+                                                     fmaxf(fabsf(v[r][j].z), fabsf(v[r][j].w))));
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RPR; ++r) finish_row(R[r], m[r], sc[r], valid[r]);
+        }
+        f32x2 acc2[N / 2];
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) acc2[i] = 0ull;
+        for (int c4 = 0; c4 < n4; c4 += 32 * NJ) {
+            float4 v[RPR][NJ];
+#pragma unroll
+            for (int r = 0; r < RPR; ++r)
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    const int i = c4 + lane + 32 * j;
+                    v[r][j] = (valid[r] && i < n4) ? __ldcs(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            if (!skip_split) {
+#pragma unroll
+                for (int r = 0; r < RPR; ++r) {
+                    if (valid[r]) {
+                        uint2* dh = reinterpret_cast<uint2*>(xhi + (size_t)R[r] * k);
+                        uint2* dl = reinterpret_cast<uint2*>(xlo + (size_t)R[r] * k);
+#pragma unroll
+                        for (int j = 0; j < NJ; ++j) {
+                            const int i = c4 + lane + 32 * j;
+                            if (i < n4) {
+                                uint2 h2, l2;
+                                split4(v[r][j], sc[r], h2, l2);
+                                dh[i] = h2;
+                                if (!bf16) dl[i] = l2;
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                if (c4 + lane + 32 * j < n4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int p = 4 * c4 + j * 128 + e * 32 + lane;   // stored row of B row 4 * piece + e
+                        f32x2 xe[RPR];
+#pragma unroll
+                        for (int r = 0; r < RPR; ++r) {
+                            const float xv = e == 0 ? v[r][j].x : e == 1 ? v[r][j].y : e == 2 ? v[r][j].z : v[r][j].w;
+                            xe[r] = pk2(xv, xv);
+                        }
+#pragma unroll
+                        for (int c = 0; c < RANK_G; ++c) {
+                            const ulonglong2 b = bsm2[p * RANK_G + ((c + p / RP) % RANK_G)];
+#pragma unroll
+                            for (int r = 0; r < RPR; ++r) {
+                                acc2[r * (RANK / 2) + 2 * c] = fma2(xe[r], b.x, acc2[r * (RANK / 2) + 2 * c]);
+                                acc2[r * (RANK / 2) + 2 * c + 1] = fma2(xe[r], b.y, acc2[r * (RANK / 2) + 2 * c + 1]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) upk2(acc2[i], acc[2 * i], acc[2 * i + 1]);
+        // halving exchange, see lowrank_t_rows_kernel
+#pragma unroll
+        for (int s = 0; s < 5; ++s) {
+            const int n = N >> s, off = 16 >> s;
+            if (n > 1) {
+                const bool up = (lane & off) != 0;
+#pragma unroll
+                for (int i = 0; i < n / 2; ++i) {
+                    const float send = up ? acc[i] : acc[i + n / 2];
+                    const float keep = up ? acc[i + n / 2] : acc[i];
+                    acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            } else {
+                acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
+            }
+        }
+        constexpr int NF = N >= 32 ? N / 32 : 1;
+        constexpr int GROUP = N >= 32 ? 1 : 32 / N;
+        if (lane % GROUP == 0) {
+            const int idx = (lane / GROUP) * NF;
+            const int row = idx / RANK, q = idx - row * RANK;
+            if (lr0 + row < total_rows) t[(size_t)row_s[lr0 + row] * RANK + q] = acc[0];
+        }
+    }
+    // one flag per call tells the GEMM whether any lo half is non-zero (a set flag is not set again)
+    if (__any_sync(0xffffffffu, lo_nz != 0) && lane == 0 && *reinterpret_cast<volatile int*>(lo_flag) == 0)
+        atomicOr(lo_flag, 1);
+}
+
 // ------------------------------------------------------------------- host side
 // 2-D fp16 map over (rows, cols) with `stride` elements between rows; box = (64, box_rows).
 int make_map(CUtensorMap* map, const __half* base, int64_t rows, int cols, int64_t stride, int box_rows) {
@@ -1415,6 +1683,21 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
             }
 #undef HSES_LTR_K
 #undef HSES_LTR
+        } else if ((g.rank <= 4 || g.rank == 8) && g.k > 1024 && rows_prepass_b_bytes(g.k, g.rank) <= 65536) {
+            // long rows with B still within shared memory (see lowrank_t_long_kernel)
+            const size_t b_bytes = rows_prepass_b_bytes(g.k, g.rank);
+#define HSES_LTL(RG)                                                                                          \
+    do {                                                                                                      \
+        HSES_CUDA(cudaFuncSetAttribute(lowrank_t_long_kernel<RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       65536));                                                               \
+        lowrank_t_long_kernel<RG><<<lt_grid, LT_THREADS, b_bytes, st>>>(                                      \
+            ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
+            g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
+            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, 1);                                           \
+    } while (0)
+            if (g.rank <= 4) HSES_LTL(1);
+            else HSES_LTL(2);
+#undef HSES_LTL
         } else
         switch ((g.rank + 3) / 4) {
             case 1: HSES_LT(1); break;

@@ -33,6 +33,8 @@ def status_ok():
     (4, 64, 128, 320, 1, 1, 0),     # rank 1 (as rank 4), three chunks of 128, the last one half used
     (8, 16, 1024, 128, 16, 1, 0),   # the widest layer of the rows prepass: all 64 KB of a pair's B in shared memory
     (4, 32, 1000, 128, 8, 3, 1),    # k not a multiple of 128 there, three time steps, pairs cut at both ends
+    (4, 32, 2048, 128, 4, 1, 0),    # rows longer than a warp's registers: the long-row prepass
+    (4, 32, 1160, 128, 8, 2, 1),    # the same with rank 8, a ragged last piece, two time steps
 ])
 def test_tensor_path_matches_oracle(hs, oracle, n_pop, bm, k, a, rank, t_steps, first):
     from hyperscalees_b200 import ops
@@ -162,7 +164,7 @@ def test_tensor_path_with_inputs_exact_in_fp16(hs, oracle, perturb):
 
 @pytest.mark.parametrize("rank", [1, 2, 3])
 @pytest.mark.parametrize("cached", [False, True])
-@pytest.mark.parametrize("k", [192, 640])   # the block prepass, and the one that keeps a pair's whole B on chip
+@pytest.mark.parametrize("k", [192, 640, 1536])   # short rows, rows in registers, rows in pieces
 def test_tensor_path_small_ranks(hs, oracle, rank, cached, k):
     """Ranks 1..3 run on the tensor-core path as rank 4 with zero columns: same stream positions
     (rank values per row), same results as the CPU restatement."""
@@ -180,7 +182,8 @@ def test_tensor_path_small_ranks(hs, oracle, rank, cached, k):
         assert np.abs(got[i] - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
 
 
-@pytest.mark.parametrize("rank,perturb,k", [(1, True, 256), (16, True, 256), (4, False, 256), (1, True, 768)])
+@pytest.mark.parametrize("rank,perturb,k", [(1, True, 256), (16, True, 256), (4, False, 256), (1, True, 768),
+                                               (1, True, 3072)])
 def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb, k):
     """precision = BF16: x and the parameter rounded to bf16, one pass, fp32 accumulation; the
     rank-r term stays fp32.  Compared with the CPU product of the rounded operands plus the CPU
@@ -204,11 +207,12 @@ def test_tensor_path_bf16_one_pass(hs, oracle, rank, perturb, k):
     full = ops.perturbed_linear(torch.as_tensor(x, device="cuda"), torch.as_tensor(w, device="cuda"), n_pop=n_pop,
                                 bm=bm, sigma=sigma, rank=rank, key=KEY, perturb=perturb,
                                 algo=ops.ALGO_TENSOR).cpu().numpy().reshape(n_pop, bm, a)
-    assert np.abs(full - got).max() > 1e-4 * np.abs(full).max()
+    assert np.abs(full - got).max() > 3e-5 * np.abs(full).max()   # (the rounding errors average out as k grows)
 
 
 @pytest.mark.parametrize("algo_name,k,a,rank", [("TENSOR", 64, 256, 1), ("TENSOR", 192, 128, 4), ("SIMT", 96, 40, 1),
-                                                ("SIMT", 64, 32, 3), ("TENSOR", 768, 128, 1), ("TENSOR", 512, 256, 8)])
+                                                ("SIMT", 64, 32, 3), ("TENSOR", 768, 128, 1), ("TENSOR", 512, 256, 8),
+                                                ("TENSOR", 1280, 128, 8)])
 def test_tmm_factor_order(hs, oracle, algo_name, k, a, rank):
     """do_Tmm (eggroll.rs:450-477): x @ param + (x·A)·Bᵀ for a parameter stored (in, out), whose
     factor block has the `out` rows first; the call takes the parameter transposed."""
