@@ -65,7 +65,7 @@ class LinearArgs(C.Structure):
         ("out_row_stride", C.c_int64), ("potentials", C.c_void_p), ("algo", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("cache", C.POINTER(FactorCacheDesc)), ("precision", C.c_int32),
-        ("factor_order", C.c_int32), ("x_half", C.c_void_p), ("out_half", C.c_void_p), ("x_split_valid", C.c_int32), ("n_groups", C.c_int32),
+        ("factor_order", C.c_int32), ("x_half", C.c_void_p), ("out_half", C.c_void_p), ("x_split_valid", C.c_int32), ("n_groups", C.c_int32), ("x_op", C.c_int32),
     ]
 
 

@@ -371,7 +371,7 @@ size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* g) {
     }
     // the tensor path always needs room for the split weights, the general path
     // only needs scratch when it perturbs
-    if (g->n_groups > 1) return tensor_path_supports(*g) ? tensor_path_workspace_bytes(*g) : 0;
+    if (g->n_groups > 1 || g->x_op != HSES_X_NONE) return tensor_path_supports(*g) ? tensor_path_workspace_bytes(*g) : 0;
     if (prefers_small_path(*g)) return small_path_workspace_bytes(*g);
     if ((g->algo == HSES_ALGO_AUTO || g->algo == HSES_ALGO_TENSOR) && tensor_path_supports(*g))
         return tensor_path_workspace_bytes(*g);
@@ -421,6 +421,15 @@ int hses_perturbed_linear(hses_ctx* ctx, hses_stream stream, const hses_linear_a
         if (rc != HSES_OK) return rc;
         return hses_lif_scan(ctx, stream, g->out, g->t_steps, g->n_pop * g->bm, g->a, g->out_row_stride, nullptr,
                              g->tau_m, g->v_th, g->reset_mode, g->out);
+    }
+    if (g->x_op != HSES_X_NONE) {
+        // an activation on the input: only where the prepass of the tensor-core path can apply it on the fly
+        HSES_REQUIRE(g->x_op == HSES_X_RELU_SQUARE, "unknown x_op");
+        if ((g->algo != HSES_ALGO_AUTO && g->algo != HSES_ALGO_TENSOR) || !tensor_path_supports(*g)) {
+            set_error("hses_perturbed_linear: x_op needs the tensor-core path with the rows prepass");
+            return HSES_ERR_UNSUPPORTED;
+        }
+        return run_tensor_path(ctx, as_stream(stream), *g);
     }
     if (g->n_groups > 1) {
         // several parameters stacked in one call: the tensor-core path or nothing

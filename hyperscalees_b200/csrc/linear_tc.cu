@@ -887,6 +887,15 @@ lowrank_t_kernel(LibmCal cal, const uint64_t* __restrict__ pow2, const uint64_t*
     }
 }
 
+// x_op of hses_linear_args on a piece of x as it arrives in registers
+__device__ __forceinline__ float4 apply_x_op(float4 v, int x_op) {
+    if (x_op == HSES_X_RELU_SQUARE) {
+        const float a = fmaxf(v.x, 0.0f), b = fmaxf(v.y, 0.0f), c = fmaxf(v.z, 0.0f), d = fmaxf(v.w, 0.0f);
+        v = make_float4(__fmul_rn(a, a), __fmul_rn(b, b), __fmul_rn(c, c), __fmul_rn(d, d));
+    }
+    return v;
+}
+
 // The prepass for layers whose rows fit the registers of a warp (k <= 1024) and whose whole B fits
 // the shared memory of a CTA (ranks 1..4, 8, 16; ranks below 4 as rank 4 with zero columns, rank_true
 // values per row in the stream and in the cache).  Phase 1: the 256 threads regenerate (or copy from
@@ -908,7 +917,7 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                       __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
                       const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true,
-                      int row_b0, int skip_split, int n_groups) {
+                      int row_b0, int skip_split, int n_groups, int x_op) {
     constexpr int RANK = RANK_G * 4;
     constexpr int RP = 8 / RANK_G;    // rows of B per 128 bytes
     constexpr int ROWS_CTA = HALF ? 2 * LT_ROWS : LT_ROWS;   // x rows per CTA
@@ -1045,7 +1054,7 @@ lowrank_t_rows_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {
                 const int i = li + 32 * j;
-                v[r][j] = (valid && i < n4) ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v[r][j] = apply_x_op((valid && i < n4) ? __ldcs(src + i) : make_float4(0.f, 0.f, 0.f, 0.f), x_op);
             }
         }
         if (!skip_split) {
@@ -1163,7 +1172,7 @@ lowrank_t_long_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
                       int64_t x_stride, int t_steps, int64_t n_pop, int bm, int k, float* __restrict__ t,
                       __half* __restrict__ xhi, __half* __restrict__ xlo, float* __restrict__ inv_scale,
                       const float* __restrict__ cache_b, int* __restrict__ lo_flag, int bf16, int rank_true,
-                      int row_b0, int skip_split, int n_groups) {
+                      int row_b0, int skip_split, int n_groups, int x_op) {
     constexpr int RANK = RANK_G * 4;
     constexpr int NJ = 8, RPR = 2;   // 1024 values of two rows in flight per warp
     constexpr bool HALF = false;
@@ -1319,7 +1328,7 @@ lowrank_t_long_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
 #pragma unroll
                         for (int j = 0; j < NJ; ++j) {
                             const int i = c4 + lane + 32 * j;
-                            v[r][j] = (valid[r] && i < n4) ? __ldg(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            v[r][j] = apply_x_op((valid[r] && i < n4) ? __ldg(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f), x_op);
                         }
 #pragma unroll
                     for (int r = 0; r < RPR; ++r)
@@ -1342,7 +1351,7 @@ lowrank_t_long_kernel(LibmCal cal, const uint64_t* __restrict__ pow2,
 #pragma unroll
                 for (int j = 0; j < NJ; ++j) {
                     const int i = c4 + lane + 32 * j;
-                    v[r][j] = (valid[r] && i < n4) ? __ldcs(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[r][j] = apply_x_op((valid[r] && i < n4) ? __ldcs(src[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f), x_op);
                 }
             if (!skip_split) {
 #pragma unroll
@@ -1565,6 +1574,13 @@ bool tensor_path_supports(const hses_linear_args& g) {
         bool pair_rows = (g.bm % 32 == 0) || (g.bm == 16 && g.first_thread % 2 == 0 && g.n_pop % 2 == 0);
         if (!pair_rows) return false;
     }
+    if (g.x_op != HSES_X_NONE) {
+        // the prepasses that hold x in registers apply it there; nothing else does
+        if (!g.perturb || g.lif == 2 || g.x_half != nullptr || g.x_split_valid) return false;
+        const bool rows_ok = (g.rank <= 4 || g.rank == 8 || g.rank == 16) && g.k <= 1024;
+        const bool long_ok = (g.rank <= 4 || g.rank == 8) && g.k > 1024 && rows_prepass_b_bytes(g.k, g.rank) <= 65536;
+        if (!rows_ok && !long_ok) return false;
+    }
     if (g.n_groups > 1) {
         // stacked parameters: cached factors, the rows prepass with all groups' B in shared memory, and
         // groups that are whole ring items
@@ -1664,7 +1680,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         lowrank_t_rows_kernel<RG, NJ, RPR, HALF><<<HALF ? lt_grid2 : lt_grid, LT_THREADS, b_bytes, st>>>(     \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
             g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
-            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, groups);                                      \
+            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, groups, g.x_op);                                      \
     } while (0)
             // rows in flight per warp: as many as the registers hold (16 pieces, 64 sums); rows of up to 64
             // values take half a warp each, and a CTA twice the rows
@@ -1693,7 +1709,7 @@ int run_tensor_path(hses_ctx* ctx, cudaStream_t st, const hses_linear_args& g) {
         lowrank_t_long_kernel<RG><<<lt_grid, LT_THREADS, b_bytes, st>>>(                                      \
             ctx->cal(), ctx->t.jump_pow2, g.key, ta.true_epoch, g.first_thread, g.x, g.x_row_stride,          \
             g.t_steps, g.n_pop, g.bm, g.k, sc.t, sc.xhi, sc.xlo, sc.rs, cache_b, sc.lo_flag, one_pass, g.rank, \
-            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, 1);                                           \
+            g.factor_order == 1 ? g.a : 0, reuse_split ? 1 : 0, 1, g.x_op);                                           \
     } while (0)
             if (g.rank <= 4) HSES_LTL(1);
             else HSES_LTL(2);

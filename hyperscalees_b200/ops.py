@@ -190,12 +190,15 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
                      out: Optional[torch.Tensor] = None, want_potentials: bool = False,
                      algo: int = ALGO_AUTO, cache: Optional["FactorCache"] = None, precision: int = 0,
                      tmm: bool = False, x_half: Optional[torch.Tensor] = None,
-                     out_half: Optional[torch.Tensor] = None, reuse_x_split: bool = False, n_groups: int = 1):
+                     out_half: Optional[torch.Tensor] = None, reuse_x_split: bool = False, n_groups: int = 1,
+                     x_relu_square: bool = False):
     """do_mm over a population (+ optional LIF step).  x: (..., k) with
     t_steps*n_pop*bm rows; param: (a, k).  Returns out (rows, a) and, if asked,
     the charged potentials.  With `cache` the factors are read from it instead of
     being regenerated (same bits).  x_half: x once more as dense fp16 (rows, k) when it is exact
     there; out_half: a dense fp16 (rows, a) tensor that receives the spikes as well (lif only).
+    x_relu_square: the layer's input is relu(x)^2; applied where the tensor-core path's prepass reads x, or, for
+    calls that path does not take this way, by one pass of its own before the call.
     n_groups: `param` stacks that many parameters of equal shape along its rows, each with its own noise;
     `cache` must then be a GroupedFactorCache over them and `key` its key (tensor-core path only).
     reuse_x_split: the previous call on this device and stream had the same x and the same shapes
@@ -230,6 +233,7 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
     g.factor_order = int(tmm)   # do_Tmm: param is the reference's (in, out) matrix transposed
     g.x_split_valid = int(reuse_x_split)
     g.n_groups = int(n_groups)
+    g.x_op = 1 if x_relu_square else 0
     if x_half is not None:
         if x_half.dtype != torch.float16 or not x_half.is_contiguous() or x_half.numel() != rows * k:
             raise ValueError("x_half must be a contiguous fp16 tensor of rows*k values")
@@ -242,6 +246,12 @@ def perturbed_linear(x: torch.Tensor, param: torch.Tensor, *, n_pop: int, bm: in
         g.cache = C.pointer(cache.desc)
     L = _lib.load()
     need = int(L.hses_perturbed_linear_workspace_bytes(C.byref(g)))
+    if g.x_op and need == 0:
+        # not a call whose prepass applies the activation on the fly (0: the tensor-core path, which always
+        # needs scratch, does not take it): one pass of its own, then the plain call
+        xa = relu_square(x.reshape(rows, k) if x.is_contiguous() else x.contiguous().reshape(rows, k))
+        g.x, g.x_row_stride, g.x_op = xa.data_ptr(), k, 0
+        need = int(L.hses_perturbed_linear_workspace_bytes(C.byref(g)))
     ws = _workspace(x.device, need)
     g.workspace = ws.data_ptr() if ws is not None else None
     g.workspace_bytes = need

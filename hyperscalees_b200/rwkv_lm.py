@@ -99,7 +99,8 @@ class RwkvLM:
                      for l in range(n_layer)]
 
     # ---- one product of the stack: clean, or with every member's rank-r term ----
-    def _mm(self, layer: int, name: str, x: torch.Tensor, n: int, T: int, noise: Optional[LmNoise]) -> torch.Tensor:
+    def _mm(self, layer: int, name: str, x: torch.Tensor, n: int, T: int, noise: Optional[LmNoise],
+            x_relu_square: bool = False) -> torch.Tensor:
         w = self.layers[layer][name]
         tmm = name in TMM_1 or name in TMM_2
         kw = {}
@@ -112,7 +113,8 @@ class RwkvLM:
                 a, k = w.shape
                 kw["cache"] = ops.FactorCache(self.keys[layer][name], noise.epoch, noise.noise_reuse, noise.rank, a, k,
                                               n // 2, first_pair=noise.first_thread // 2, device=self.device)
-        return ops.perturbed_linear(x, w, n_pop=n, bm=T, perturb=noise is not None, precision=ops.PRECISION_BF16, **kw)
+        return ops.perturbed_linear(x, w, n_pop=n, bm=T, perturb=noise is not None, precision=ops.PRECISION_BF16,
+                                    x_relu_square=x_relu_square, **kw)
 
     def forward_hidden(self, ids: torch.Tensor, noise: Optional[LmNoise] = None) -> torch.Tensor:
         """ids (n, T) int32 -> the (n*T, C) activations after ln_out."""
@@ -153,8 +155,9 @@ class RwkvLM:
             del xr, xw, xk, xv, xa, xg, r, k, v, gate, out, y, wdec, state, nkk, kka, w_lin, v_lin, a_lin
             # ---- ChannelMixing, llm.rs:192-213 ----
             xc = ops.layer_norm(x, *w["ln2"])
-            kf = ops.relu_square(mm("ffn_key", ops.token_shift_mix(xc, zero_c, w["ffn_x_k"], ns)))
-            ops.add_inplace(x, mm("ffn_value", kf))
+            # k = relu(key(x))^2 (llm.rs:208) is applied where the value product's prepass reads its input
+            kf = mm("ffn_key", ops.token_shift_mix(xc, zero_c, w["ffn_x_k"], ns))
+            ops.add_inplace(x, self._mm(l, "ffn_value", kf, n, T, noise, x_relu_square=True))
             del xc, kf
         return ops.layer_norm(x, *self.ln_out)
 

@@ -50,6 +50,7 @@ enum hses_factor_layout {
 };
 enum hses_linear_algo { HSES_ALGO_AUTO = 0, HSES_ALGO_SIMT = 1, HSES_ALGO_TENSOR = 2, HSES_ALGO_PAIR = 3 };
 enum hses_precision { HSES_PRECISION_FP32 = 0, HSES_PRECISION_BF16 = 1 };
+enum hses_x_op { HSES_X_NONE = 0, HSES_X_RELU_SQUARE = 1 };
 
 const char* hses_last_error(void);
 int hses_version(void);
@@ -250,6 +251,11 @@ typedef struct {
                            path only (k <= 1024, rank 1..4, 8 or 16, a / G a multiple of 32, or of 16 with
                            rank >= 8, the G blocks of B within 64 KB); other shapes return
                            HSES_ERR_UNSUPPORTED.  Column c of the result belongs to group c / (a / G) */
+    int32_t x_op;       /* 0: x as it is.  HSES_X_RELU_SQUARE: the layer's input is relu(x)^2 (ChannelMixing's
+                           k = relu(key(x))^2, llm.rs:208), applied where the tensor-core path's prepass reads x,
+                           so that the activation costs no pass of its own.  Calls with noise whose prepass keeps
+                           B in shared memory only (rank 1..4, 8, 16 and k within its limits); other calls return
+                           HSES_ERR_UNSUPPORTED and the caller applies hses_relu_square first */
 } hses_linear_args;
 /* Scratch the call needs for these shapes and this algo (0 is possible). */
 size_t hses_perturbed_linear_workspace_bytes(const hses_linear_args* args);

@@ -316,3 +316,20 @@ def test_grouped_projections_with_steps_lif_and_one_pass(hs, extra):
         assert 0.02 < float(want.mean()) < 0.98
     else:
         assert float((got - want).abs().max()) <= 1e-6 * max(float(want.abs().max()), 1.0)
+
+
+@pytest.mark.parametrize("k,rank,precision,perturb", [(256, 8, 0, True), (640, 1, 1, True), (3072, 1, 1, True),
+                                                      (1536, 4, 0, True), (256, 8, 0, False), (2304, 16, 0, True)])
+def test_relu_square_on_the_input_equals_the_pass_of_its_own(hs, k, rank, precision, perturb):
+    """x_op: the layer's input is relu(x)^2, applied where the prepass reads x (rows in registers, short or
+    in pieces), or — clean calls, shapes whose prepass is the block kernel — by one pass before the call."""
+    from hyperscalees_b200 import ops
+    g = np.random.default_rng(k + rank)
+    n_pop, bm, a = 8, 32, 128
+    x = dev(g.standard_normal((n_pop, bm, k)).astype(np.float32))
+    w = dev((g.standard_normal((a, k)) / np.sqrt(k)).astype(np.float32))
+    kw = dict(n_pop=n_pop, bm=bm, sigma=0.3, rank=rank, key=KEY, precision=precision, perturb=perturb)
+    want = ops.perturbed_linear(ops.relu_square(x), w, **kw)
+    got = ops.perturbed_linear(x, w, x_relu_square=True, **kw)
+    status_ok()
+    assert torch.equal(got, want)
