@@ -70,18 +70,28 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, int64_t rows, 
     *reinterpret_cast<float4*>(out + (size_t)row * out_stride + c) = v;
 }
 
-__global__ void lif_rate_kernel(const float* __restrict__ cur, int64_t n, int T, float leak, float v_th, int reset,
+// TC: the number of steps when it is known at compile time (the loop unrolls, the reset mode is a constant
+// and the division by a power of two a multiplication with the same result), 0: any T
+template <int TC, int RESET>
+__global__ void lif_rate_kernel(const float* __restrict__ cur, int64_t n, int T_run, float leak, float v_th, int reset_run,
                                 float* __restrict__ out) {
+    const int T = TC ? TC : T_run;
+    const int reset = TC ? RESET : reset_run;
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t n4 = n >> 2;
     if (i < n4) {
-        const float4 c4 = reinterpret_cast<const float4*>(cur)[i];
+        const float4 c4 = __ldcs(reinterpret_cast<const float4*>(cur) + i);
         const float c[4] = {c4.x, c4.y, c4.z, c4.w};
         float r[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             float v = 0.0f, s = 0.0f;
-            for (int t = 0; t < T; ++t) s = __fadd_rn(s, lif_update(v, c[j], leak, v_th, reset));
+#pragma unroll
+            for (int t = 0; t < (TC ? TC : 1); ++t) {
+                if (TC) s = __fadd_rn(s, lif_update(v, c[j], leak, v_th, reset));
+            }
+            if (!TC)
+                for (int t = 0; t < T; ++t) s = __fadd_rn(s, lif_update(v, c[j], leak, v_th, reset));
             r[j] = __fdiv_rn(s, (float)T);
         }
         reinterpret_cast<float4*>(out)[i] = make_float4(r[0], r[1], r[2], r[3]);
@@ -96,7 +106,6 @@ __global__ void lif_rate_kernel(const float* __restrict__ cur, int64_t n, int T,
     }
 }
 
-// y = x * sigmoid(x), optionally added onto `res` (out = res + y) when res is given
 __global__ void swish_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t n4 = n >> 2;
@@ -202,8 +211,16 @@ int hses_lif_rate(hses_ctx* ctx, hses_stream stream, const float* cur, int64_t n
     HSES_REQUIRE((((uintptr_t)cur | (uintptr_t)out) & 15u) == 0, "cur and out must be 16-byte aligned");
     int64_t work = n / 4 + n % 4;
     HSES_KERNEL(ctx, as_stream(stream), "lif_rate");
-    lif_rate_kernel<<<(unsigned)((work + 255) / 256), 256, 0, as_stream(stream)>>>(cur, n, T, 1.0f / tau_m, v_th,
-                                                                                  reset_mode, out);
+    const unsigned grid = (unsigned)((work + 255) / 256);
+    const float leak = 1.0f / tau_m;
+    if (T == 4 && reset_mode == HSES_RESET_HARD)
+        lif_rate_kernel<4, HSES_RESET_HARD><<<grid, 256, 0, as_stream(stream)>>>(cur, n, T, leak, v_th, reset_mode, out);
+    else if (T == 4)
+        lif_rate_kernel<4, HSES_RESET_SUBTRACT><<<grid, 256, 0, as_stream(stream)>>>(cur, n, T, leak, v_th, reset_mode, out);
+    else if (T == 8 && reset_mode == HSES_RESET_HARD)
+        lif_rate_kernel<8, HSES_RESET_HARD><<<grid, 256, 0, as_stream(stream)>>>(cur, n, T, leak, v_th, reset_mode, out);
+    else
+        lif_rate_kernel<0, 0><<<grid, 256, 0, as_stream(stream)>>>(cur, n, T, leak, v_th, reset_mode, out);
     HSES_LAUNCH_CHECK();
     return HSES_OK;
 }
