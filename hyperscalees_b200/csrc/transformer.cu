@@ -149,12 +149,35 @@ __global__ void token_loglik_kernel(const float* __restrict__ logits, int64_t lo
         return;
     }
     const float* row = logits + (size_t)w * logits_stride;
-    float mx = -INFINITY;
-    for (int c = lane; c < vocab; c += 32) mx = fmaxf(mx, __fmul_rn(row[c], gain));
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    float s = 0.0f;
-    for (int c = lane; c < vocab; c += 32) s += expf(__fmul_rn(row[c], gain) - mx);
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    // One pass with a running maximum (a row of a 50 277-word vocabulary is 200 KB and thousands of rows are
+    // in flight: a second pass would come from HBM again, and the kernel is bound by those bytes).  A lane
+    // keeps the maximum mx of what it has seen and s = sum exp(x - mx); a new maximum rescales s, which is
+    // rare after the first few values.  Rows that start on a 16-byte boundary are read 16 bytes per lane.
+    const int v4 = (((uintptr_t)row & 15u) == 0) ? vocab >> 2 : 0;
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    float mx = -INFINITY, s = 0.0f;
+    auto take = [&](float raw) {
+        const float xv = __fmul_rn(raw, gain);
+        if (xv > mx) {
+            s = fmaf(s, expf(mx - xv), 1.0f);
+            mx = xv;
+        } else {
+            s += expf(xv - mx);
+        }
+    };
+#pragma unroll 4
+    for (int c = lane; c < v4; c += 32) {
+        const float4 q = __ldcs(row4 + c);
+        take(q.x); take(q.y); take(q.z); take(q.w);
+    }
+    for (int c = 4 * v4 + lane; c < vocab; c += 32) take(row[c]);
+    for (int off = 16; off > 0; off >>= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, mx, off), so = __shfl_xor_sync(0xffffffffu, s, off);
+        const float mn = fmaxf(mx, mo);
+        // a lane that saw nothing has mx = -inf and s = 0: its term is 0 * exp(-inf) = 0
+        s = (mx == mn ? s : s * expf(mx - mn)) + (mo == mn ? so : so * expf(mo - mn));
+        mx = mn;
+    }
     if (lane == 0) {
         const int target = ids[w + 1];
         lp[w] = (target >= 0 && target < vocab) ? (__fmul_rn(row[target], gain) - mx) - logf(s) : 0.0f;
