@@ -1096,6 +1096,15 @@ int hses_rwkv_mix_prepare(hses_ctx* ctx, hses_stream stream, int64_t rows, int32
     HSES_REQUIRE(w_lin && v_raw && a_lin && k_raw && w0 && a0 && k_k && k_a && w_out && v_out && k_out && nkk_out && kka_out,
                  "NULL pointer");
     HSES_REQUIRE(v_lin == nullptr || (v0 != nullptr && v_first != nullptr), "v_lin needs v0 and v_first");
+    {   // a lane reads and writes S / 32 consecutive floats at once
+        uintptr_t bits = 0;
+        for (const void* q : {(const void*)w_lin, (const void*)v_raw, (const void*)v_lin, (const void*)v_first,
+                              (const void*)a_lin, (const void*)k_raw, (const void*)w0, (const void*)v0, (const void*)a0,
+                              (const void*)k_k, (const void*)k_a, (const void*)w_out, (const void*)v_out,
+                              (const void*)k_out, (const void*)nkk_out, (const void*)kka_out})
+            bits |= (uintptr_t)q;
+        HSES_REQUIRE((bits & 15u) == 0, "pointers must be 16-byte aligned");
+    }
     const int64_t heads_total = rows * H;
     const unsigned grid = (unsigned)((heads_total + 7) / 8);
     HSES_KERNEL(ctx, as_stream(stream), "rwkv_mix_prepare");
@@ -1118,6 +1127,9 @@ int hses_rwkv_mix_finish(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_
     HSES_REQUIRE(rows >= 0 && H >= 1 && (S == 32 || S == 64 || S == 128), "head size must be 32, 64 or 128");
     if (rows == 0) return HSES_OK;
     HSES_REQUIRE(y_norm && r && k && v && gate && r_k && out, "NULL pointer");
+    HSES_REQUIRE((((uintptr_t)y_norm | (uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)gate | (uintptr_t)r_k |
+                   (uintptr_t)out) & 15u) == 0,
+                 "pointers must be 16-byte aligned");
     const int64_t heads_total = rows * H;
     const unsigned grid = (unsigned)((heads_total + 7) / 8);
     HSES_KERNEL(ctx, as_stream(stream), "rwkv_mix_finish");

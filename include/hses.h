@@ -555,7 +555,7 @@ int hses_token_shift_mix_multi(hses_ctx* ctx, hses_stream stream, const float* x
  *            kk = k_raw * k_k normalised per head (L2, floor 1e-12);  k = k_raw * (k_a * (a - 1) + 1);
  *            outputs w, v, k, -kk, kk * a (the decay, value, key, a and b inputs of hses_wkv7);
  *   finish:  out = (y_norm + (sum over the head of r * k * r_k) * v) * gate.
- * Head size 32, 64 or 128. */
+ * Head size 32, 64 or 128; every pointer 16-byte aligned. */
 int hses_rwkv_mix_prepare(hses_ctx* ctx, hses_stream stream, int64_t rows, int32_t H, int32_t S, const float* w_lin,
                           const float* v_raw, const float* v_lin /*or NULL*/, const float* v_first /*or NULL*/,
                           const float* a_lin, const float* k_raw, const float* w0, const float* v0 /*or NULL*/,
