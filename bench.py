@@ -50,7 +50,7 @@ SIGMA, RANK, TAU_M, V_TH = 0.02, 16, 20.0, 0.3
 N_POP, BM, K_DIM, A_DIM = 8192, 16, 1024, 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch divided by its members, from an ncu
 # capture of these kernels at n_pop = 2048: constants of that capture, not a measurement of this run
-NCU_TRAFFIC_BYTES_PER_MEMBER = {"linear_tc": (209.6e6 + 92.7e6) / 2048, "lowrank_t": (137.9e6 + 79.8e6) / 2048}
+NCU_TRAFFIC_BYTES_PER_MEMBER = {"linear_tc": (192.4e6 + 90.7e6) / 2048, "lowrank_t": (137.9e6 + 79.8e6) / 2048}
 
 
 def measured_peaks():
